@@ -1,0 +1,211 @@
+/*
+ * C-ABI of the B200 NVFP4 linear library (libmimfer_b200.so).
+ *
+ * Everything here has C linkage and takes plain pointers and sizes.  The
+ * first group keeps the names, argument meaning and error behaviour of the
+ * mimfer appliance so the library drops in behind its dispatcher; each
+ * declaration cites the reference interface it replaces (paths are relative
+ * to the mimfer source tree).  The second group is new surface the reference
+ * has no counterpart for (global scale, split-K workspace, tile selection,
+ * the quantising packer, the op-list engine); it is named mm_f4_* / mm_lin_*.
+ *
+ * Threading: one host thread per process drives one device, exactly like the
+ * reference runtime (src/cuda/cuda_rt.c:15-18 keeps process-global statics).
+ */
+#ifndef MIMFER_B200_H
+#define MIMFER_B200_H
+
+#include "mimfer_abi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ======================================================================
+ * 1. Reference-named surface
+ * ====================================================================== */
+
+/* Replaces kx_op_gemm_f4 in src/kernels/cuda/cx.cu:358-376 (CPU twin
+ * src/kernels/cpu/cx.c:197-216).  y = bf16(gs * sum_k x[m][k] * W[r][k]),
+ * fp32 accumulation; gs is the weight's global scale (1.0f unless registered
+ * with mm_f4_gscale_set).  Launches on the compute stream of the runtime
+ * below.  Outside graph capture it synchronises that stream and reports
+ * launch / device errors (reference: kx_sync, cx.cu:83-100); while capturing
+ * it only enqueues.  Returns MM_ERR_SHAPE when n1 % 16 != 0 or an extent is
+ * zero, MM_ERR_STATE on NULL operands or an uninitialised runtime,
+ * MM_ERR_CUDA on launch/sync failure, MM_ERR_TIMEOUT when a bounded
+ * device-side wait gave up.  Allocates nothing. */
+mm_status kx_op_gemm_f4(const mm_kcall *kc);
+
+/* Replaces kx_op_qkv in src/kernels/cuda/cx.cu:327-335.  The reference
+ * planner hands this op the NVFP4 payload and scale pointers of a fused qkv
+ * weight (src/plan/plan.c:272-275) but both reference kernel sets read them
+ * as bf16; here a non-NULL `d` operand routes to the NVFP4 kernels with the
+ * GEMM_F4 operand meaning, and a NULL `d` returns MM_ERR_UNSUPPORTED (the
+ * bf16 GEMM is outside this library). */
+mm_status kx_op_qkv(const mm_kcall *kc);
+
+/* Replaces mm_kx_invoke in src/kernels/kx.c:15-47 for the opcodes this
+ * library owns: OP_GEMM_F4, OP_QKV (fp4 form) and OP_NOP.  Same NULL checks
+ * (kc, kc->op, kc->e -> MM_ERR_STATE); any other opcode returns
+ * MM_ERR_UNSUPPORTED. */
+mm_status mm_kx_invoke(const mm_kcall *kc);
+
+/* Replaces kx_cuda_oppref in src/kernels/cuda/cx.cu (declared in
+ * src/kernels/kx.h:43): 1 for the opcodes listed above, else 0. */
+int kx_cuda_oppref(int op);
+
+/* Runtime shim, replacing the parts of src/cuda/cuda_rt.c the launcher and
+ * the engine use (declared in include/mimfer/cuda_rt.h:38-106).  Two
+ * non-blocking streams, capture on the compute stream, no device allocation.
+ * When this library is linked into a mimfer build these come from mimfer's
+ * own cuda_rt.c instead (leave csrc/cuda/rt.c out of the link). */
+int        mm_cuda_enabled(void);                       /* cuda_rt.h:41 */
+mm_status  mm_cuda_device_count(int *n_out);            /* cuda_rt.h:43 */
+mm_status  mm_cuda_init(int device_ordinal);            /* cuda_rt.h:46 */
+mm_status  mm_cuda_shutdown(void);                      /* cuda_rt.h:47 */
+void      *mm_cuda_stream_raw(mm_stream_id id);         /* cuda_rt.h:106 (cudaStream_t) */
+int        mm_cuda_capturing(void);                     /* cuda_rt.h:94 */
+mm_status  mm_stream_sync(mm_stream_id st);             /* cuda_rt.h:57 */
+mm_status  mm_h2d_async(void *dst, const void *src, size_t n, mm_stream_id st); /* :60 */
+mm_status  mm_d2h_async(void *dst, const void *src, size_t n, mm_stream_id st); /* :61 */
+mm_status  mm_mset_async(void *dst, int value, size_t n, mm_stream_id st);      /* :62 */
+
+typedef struct mm_graph mm_graph;                       /* cuda_rt.h:65 */
+mm_status  mm_graph_create(mm_graph **out);             /* :66 */
+mm_status  mm_graph_capture_begin(mm_graph *g);         /* :68 */
+mm_status  mm_graph_commit(mm_graph *g, const void *window_base,
+                           size_t window_bytes, int hit_ratio_pct); /* :71 */
+mm_status  mm_graph_launch(mm_graph *g, mm_stream_id st);           /* :73 */
+void       mm_graph_destroy(mm_graph *g);                           /* :74 */
+
+/* Logging, replacing mm_log in src/core/mimfer.c:37-60. Level 0 = errors
+ * only ... 3 = debug; default 1. */
+void mm_log_set_level(int level);
+
+/* ======================================================================
+ * 2. New surface (no counterpart in the reference)
+ * ====================================================================== */
+
+/* ---- global scale ------------------------------------------------------
+ * The reference weight view carries payload + block scales only
+ * (include/mimfer/tensor.h:121-126); NVFP4 checkpoints add one fp32 scale per
+ * tensor.  The descriptor has no free slot for it, so it is registered per
+ * weight, keyed by the block-scale base pointer (`d` of the descriptor).
+ * Unregistered weights use 1.0f, which is bit-for-bit the reference maths. */
+mm_status mm_f4_gscale_set(const void *scale_base, float gs);
+float     mm_f4_gscale_get(const void *scale_base);
+void      mm_f4_gscale_clear(void);
+
+/* ---- split-K workspace ---------------------------------------------------
+ * The launcher allocates nothing (reference rule: include/mimfer/alloc.h:4-29);
+ * split-K variants need fp32 partials plus arrival counters.  The owner of the
+ * activation arena donates a block once (the role the reference reserves as
+ * e->ab.part, include/mimfer/engine.h:98).  Without a workspace the selector
+ * only returns variants that need none.  The block is zeroed here, on the
+ * compute stream; it must be 256-byte aligned device memory. */
+mm_status mm_f4_workspace_set(void *dev_ptr, size_t bytes);
+size_t    mm_f4_workspace_bytes(void);
+
+/* ---- tile / variant selection (pure host C, no CUDA) ---------------------- */
+typedef enum mm_f4_variant {
+    MM_F4_V_ROWWARP = 0,  /* any K%16==0: one warp per weight row, shuffles  */
+    MM_F4_V_STREAM  = 1,  /* decode: TMA-staged weight stream + warp MMA     */
+    MM_F4_V_UMMA    = 2   /* prefill: tcgen05 kind::f16, TMEM accumulators   */
+} mm_f4_variant;
+
+typedef struct mm_f4_shape {
+    uint32_t M, K, N;
+    uint32_t sm_count;        /* SMs of the device (148 on B200)            */
+    uint32_t ptr_align;       /* min alignment in bytes of x/payload/scale/y */
+    size_t   ws_bytes;        /* workspace available (0 = none)              */
+} mm_f4_shape;
+
+typedef struct mm_f4_plan {
+    int      variant;         /* mm_f4_variant                                */
+    uint32_t m_tiles;         /* STREAM: 8-row activation tiles (1, 2 or 4)   */
+    uint32_t tile_m, tile_n;  /* UMMA: CTA tile; STREAM: tile_n = W rows/CTA  */
+    uint32_t split_k;         /* >= 1                                         */
+    uint32_t k_steps;         /* K / 256 (STREAM) or K / 64 (UMMA)            */
+    uint32_t stages;          /* smem pipeline depth                          */
+    uint32_t grid_x, grid_y, grid_z;
+    uint32_t threads;
+    uint32_t smem_bytes;      /* dynamic shared memory per CTA                */
+    size_t   ws_needed;       /* bytes of workspace this plan uses            */
+} mm_f4_plan;
+
+/* Deterministic: the same shape always yields the same plan.  Returns
+ * MM_ERR_SHAPE for K%16 != 0 or a zero extent. */
+mm_status mm_f4_select(const mm_f4_shape *s, mm_f4_plan *out);
+/* Force a variant (tests, sweeps); MM_ERR_UNSUPPORTED if the shape cannot run
+ * on it. */
+mm_status mm_f4_select_variant(const mm_f4_shape *s, int variant, mm_f4_plan *out);
+/* Override for kx_op_gemm_f4: -1 = automatic (default). */
+void      mm_f4_force_variant(int variant);
+
+/* ---- flat launch ---------------------------------------------------------
+ * Same maths as kx_op_gemm_f4 with the operands spelled out; enqueues on
+ * `stream` (a cudaStream_t; NULL = the compute stream) and does not
+ * synchronise.  Device pointers. */
+mm_status mm_f4_linear(const void *x, const void *payload, const void *scale,
+                       float gs, void *y, uint32_t M, uint32_t K, uint32_t N,
+                       void *stream);
+
+/* Host-buffer form: copies x (pinned or pageable host memory) to `x_dev`,
+ * runs the op on resident device weights, copies y back to `y_host` and
+ * synchronises.  This is the call the end-to-end benchmark times. */
+mm_status mm_f4_linear_host(const void *x_host, void *x_dev,
+                            const void *payload_dev, const void *scale_dev,
+                            float gs, void *y_dev, void *y_host,
+                            uint32_t M, uint32_t K, uint32_t N);
+
+/* Reads and clears the device-side status word that bounded waits set. */
+mm_status mm_f4_device_status(unsigned *flags_out);
+/* Count of kernels this library launched since the last call (then reset). */
+unsigned long long mm_f4_launch_count(int reset);
+
+/* Device decode probe: for every (nibble n, scale byte s) writes the fp32
+ * bits of the dequantised weight as each kernel family computes it, to two
+ * device arrays of 4096 uint32 (index s*16+n): the tensor-core operand path
+ * (bf16 operand, rescaled) and the row-warp fp32 path. */
+mm_status mm_f4_decode_probe(uint32_t *out_mma_dev, uint32_t *out_f32_dev);
+
+/* ---- timing on the compute stream (events with timing enabled) ----------- */
+mm_status mm_time_begin(void);
+mm_status mm_time_end(float *ms_out);        /* synchronises */
+
+/* ---- quantising packer + seeded generator (host) --------------------------
+ * W fp32 [N][K] row-major -> payload [N][K/2], scales [N][K/16], *gs.
+ * gs = max|W| / (6*448); block scale = e4m3_rne_sat(amax_block / (6*gs));
+ * nibble = e2m1_rne_sat(w / (decode(scale) * gs)).  Layout as
+ * include/mimfer/tensor.h:17-19. */
+mm_status mm_f4_pack(const float *W, uint32_t N, uint32_t K,
+                     uint8_t *payload, uint8_t *scales, float *gs_out);
+/* out[i] = mean + std * normal(), splitmix64 (include/mimfer/mimfer.h:149-155)
+ * + Box-Muller, one stream per row of `cols` values so rows can be generated
+ * in parallel with identical results. */
+void mm_fill_normal_f32(float *out, uint64_t rows, uint64_t cols,
+                        uint64_t seed, float mean, float std);
+void mm_f32_to_bf16(const float *in, uint16_t *out, uint64_t n);
+void mm_bf16_to_f32(const uint16_t *in, float *out, uint64_t n);
+/* Generate + pack one weight without materialising fp32 W (row blocks). gs is
+ * computed in a first pass over the same stream. */
+mm_status mm_f4_make_weight(uint32_t N, uint32_t K, uint64_t seed, float std,
+                            uint8_t *payload, uint8_t *scales, float *gs_out);
+
+/* ---- op-list engine (graph-captured sequence of linears) ------------------ */
+typedef struct mm_lin_engine mm_lin_engine;
+mm_status mm_lin_engine_create(mm_lin_engine **out, uint32_t max_ops);
+mm_status mm_lin_engine_add(mm_lin_engine *e, const mm_op_desc *op);
+uint32_t  mm_lin_engine_n_ops(const mm_lin_engine *e);
+/* Capture all ops into one CUDA graph (reference pattern:
+ * src/plan/plan.c:479-507). */
+mm_status mm_lin_engine_capture(mm_lin_engine *e);
+/* Replay the graph (or dispatch op by op if not captured); no sync. */
+mm_status mm_lin_engine_launch(mm_lin_engine *e);
+void      mm_lin_engine_destroy(mm_lin_engine *e);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MIMFER_B200_H */

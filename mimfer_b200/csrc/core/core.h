@@ -1,0 +1,43 @@
+/* Internal helpers shared by the host C sources: logging and the
+ * check-and-return macros (policy as in include/mimfer/mimfer.h:100-118 of the
+ * mimfer tree: log once, return the status, no unwinding). */
+#ifndef MMB_CORE_H
+#define MMB_CORE_H
+
+#include "mimfer_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+void mmb_log(int lvl, const char *file, int line, const char *fmt, ...)
+    __attribute__((format(printf, 4, 5)));
+
+#define MM_LOGE(...) mmb_log(0, __FILE__, __LINE__, __VA_ARGS__)
+#define MM_LOGW(...) mmb_log(1, __FILE__, __LINE__, __VA_ARGS__)
+#define MM_LOGI(...) mmb_log(2, __FILE__, __LINE__, __VA_ARGS__)
+#define MM_LOGD(...) mmb_log(3, __FILE__, __LINE__, __VA_ARGS__)
+
+#define MM_CHECK(expr)                                                   \
+    do {                                                                 \
+        mm_status s_ = (expr);                                           \
+        if (s_ != MM_OK) {                                               \
+            MM_LOGE("%s: %s", #expr, mm_status_str(s_));                 \
+            return s_;                                                   \
+        }                                                                \
+    } while (0)
+
+#define MM_REQUIRE(cond, code)                                           \
+    do {                                                                 \
+        if (!(cond)) {                                                   \
+            MM_LOGE("required: %s", #cond);                              \
+            return (code);                                               \
+        }                                                                \
+    } while (0)
+
+static inline size_t mmb_align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+#ifdef __cplusplus
+}
+#endif
+#endif

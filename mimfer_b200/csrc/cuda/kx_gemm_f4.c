@@ -1,0 +1,330 @@
+/*
+ * The launcher: mimfer's operator ABI on one side, the sm_100a kernels on the
+ * other.  Thin on purpose: validate, pick a plan (csrc/plan/select.c), encode
+ * the TMA descriptors, launch.  No device allocation happens here
+ * (reference rule: include/mimfer/alloc.h:4-29); split-K scratch is donated by
+ * the caller through mm_f4_workspace_set.
+ *
+ * kx_op_gemm_f4 replaces src/kernels/cuda/cx.cu:358-376; its error and
+ * synchronisation behaviour follows kx_sync (cx.cu:83-100): synchronise the
+ * compute stream and surface errors per op, except while a graph is being
+ * captured.
+ */
+#include "../core/core.h"
+#include "../kernels/launch.h"
+#include <cuda.h>
+#include <cuda_runtime_api.h>
+#include <string.h>
+
+int mmb_stream_init(void);
+int mmb_umma_init(void);
+
+/* ------------------------------------------------------------------ state */
+typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                              const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                              const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static struct {
+    int        ready;
+    int        sm_count;
+    encode_fn  encode;
+    unsigned  *status_dev;
+    unsigned  *status_host;      /* pinned */
+    void      *ws;
+    size_t     ws_bytes;
+    int        forced_variant;
+    unsigned long long launches;
+} G = { .forced_variant = -1 };
+
+/* global-scale registry: open addressing on the scale base pointer */
+#define GS_SLOTS 4096u
+static struct { const void *key; float gs; } g_gs[GS_SLOTS];
+static unsigned g_gs_used;
+
+static unsigned gs_hash(const void *p)
+{
+    uint64_t v = (uint64_t)(uintptr_t)p;
+    v ^= v >> 33; v *= 0xff51afd7ed558ccdull; v ^= v >> 29;
+    return (unsigned)v & (GS_SLOTS - 1u);
+}
+
+mm_status mm_f4_gscale_set(const void *scale_base, float gs)
+{
+    MM_REQUIRE(scale_base, MM_ERR_STATE);
+    MM_REQUIRE(gs == gs && gs > 0.0f && gs < 3.0e38f, MM_ERR_RANGE);
+    unsigned h = gs_hash(scale_base);
+    for (unsigned i = 0; i < GS_SLOTS; i++, h = (h + 1u) & (GS_SLOTS - 1u)) {
+        if (g_gs[h].key == scale_base) { g_gs[h].gs = gs; return MM_OK; }
+        if (!g_gs[h].key) {
+            if (g_gs_used + 1u >= GS_SLOTS) return MM_ERR_CAPACITY;
+            g_gs[h].key = scale_base; g_gs[h].gs = gs; g_gs_used++;
+            return MM_OK;
+        }
+    }
+    return MM_ERR_CAPACITY;
+}
+
+float mm_f4_gscale_get(const void *scale_base)
+{
+    unsigned h = gs_hash(scale_base);
+    for (unsigned i = 0; i < GS_SLOTS; i++, h = (h + 1u) & (GS_SLOTS - 1u)) {
+        if (g_gs[h].key == scale_base) return g_gs[h].gs;
+        if (!g_gs[h].key) break;
+    }
+    return 1.0f;
+}
+
+void mm_f4_gscale_clear(void)
+{
+    memset(g_gs, 0, sizeof g_gs);
+    g_gs_used = 0;
+}
+
+void mm_f4_force_variant(int variant) { G.forced_variant = variant; }
+
+unsigned long long mm_f4_launch_count(int reset)
+{
+    unsigned long long n = G.launches;
+    if (reset) G.launches = 0;
+    return n;
+}
+
+/* ------------------------------------------------------------------ setup */
+#define CK(call)                                                              \
+    do {                                                                      \
+        cudaError_t e_ = (call);                                              \
+        if (e_ != cudaSuccess) {                                              \
+            MM_LOGE("cuda: %s: %s", #call, cudaGetErrorString(e_));           \
+            return MM_ERR_CUDA;                                               \
+        }                                                                     \
+    } while (0)
+
+static mm_status ensure_ready(void)
+{
+    if (G.ready)
+        return MM_OK;
+    MM_REQUIRE(mm_cuda_stream_raw(MM_ST_COMPUTE) != NULL, MM_ERR_STATE);   /* mm_cuda_init first */
+    int dev = 0;
+    CK(cudaGetDevice(&dev));
+    CK(cudaDeviceGetAttribute(&G.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    int major = 0;
+    CK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    MM_REQUIRE(major == 10, MM_ERR_DEVICE);
+    void *fn = NULL;
+    enum cudaDriverEntryPointQueryResult qr;
+    CK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr));
+    MM_REQUIRE(fn && qr == cudaDriverEntryPointSuccess, MM_ERR_CUDA);
+    G.encode = (encode_fn)fn;
+    CK((cudaError_t)mmb_stream_init());
+    CK((cudaError_t)mmb_umma_init());
+    CK((cudaError_t)mmb_status_word(&G.status_dev));
+    CK(cudaHostAlloc((void **)&G.status_host, 64, cudaHostAllocDefault));
+    *G.status_host = 0;
+    CK(cudaMemsetAsync(G.status_dev, 0, sizeof(unsigned), (cudaStream_t)mm_cuda_stream_raw(MM_ST_COMPUTE)));
+    G.ready = 1;
+    return MM_OK;
+}
+
+mm_status mm_f4_workspace_set(void *dev_ptr, size_t bytes)
+{
+    MM_CHECK(ensure_ready());
+    if (!dev_ptr || bytes <= MMB_WS_COUNTER_B) {
+        G.ws = NULL;
+        G.ws_bytes = 0;
+        return dev_ptr ? MM_ERR_RANGE : MM_OK;
+    }
+    MM_REQUIRE(((uintptr_t)dev_ptr & 255u) == 0, MM_ERR_SHAPE);
+    CK(cudaMemsetAsync(dev_ptr, 0, MMB_WS_COUNTER_B, (cudaStream_t)mm_cuda_stream_raw(MM_ST_COMPUTE)));
+    G.ws = dev_ptr;
+    G.ws_bytes = bytes;
+    return MM_OK;
+}
+
+size_t mm_f4_workspace_bytes(void) { return G.ws_bytes; }
+
+/* ------------------------------------------------------ TMA descriptors */
+static mm_status encode_2d(unsigned char out[128], CUtensorMapDataType dt, unsigned esize,
+                           const void *base, uint64_t inner, uint64_t outer, uint32_t box_inner,
+                           uint32_t box_outer, CUtensorMapSwizzle sw)
+{
+    CUtensorMap map;
+    cuuint64_t dims[2] = { inner, outer };
+    cuuint64_t strides[1] = { inner * esize };
+    cuuint32_t box[2] = { box_inner, box_outer };
+    cuuint32_t estr[2] = { 1, 1 };
+    CUresult r = G.encode(&map, dt, 2, (void *)(uintptr_t)base, dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        MM_LOGE("cuTensorMapEncodeTiled failed: %d (inner %llu outer %llu box %u x %u)", (int)r,
+                (unsigned long long)inner, (unsigned long long)outer, box_inner, box_outer);
+        return MM_ERR_CUDA;
+    }
+    memcpy(out, &map, 128);
+    return MM_OK;
+}
+
+/* ------------------------------------------------------------------ launch */
+static uint32_t min_align(const void *a, const void *b, const void *c, const void *d)
+{
+    uintptr_t v = (uintptr_t)a | (uintptr_t)b | (uintptr_t)c | (uintptr_t)d | 256u;
+    return (uint32_t)(v & (~v + 1u));
+}
+
+mm_status mm_f4_linear(const void *x, const void *payload, const void *scale, float gs, void *y,
+                       uint32_t M, uint32_t K, uint32_t N, void *stream)
+{
+    MM_REQUIRE(x && payload && scale && y, MM_ERR_STATE);
+    if (M == 0 || N == 0 || K == 0 || K % 16 != 0)
+        return MM_ERR_SHAPE;               /* e4m3 group scale spans 16 columns */
+    MM_CHECK(ensure_ready());
+    if (!stream)
+        stream = mm_cuda_stream_raw(MM_ST_COMPUTE);
+
+    mmb_args a;
+    memset(&a, 0, sizeof a);
+    a.x = x; a.payload = payload; a.scale = scale; a.y = y;
+    a.gs = gs; a.M = M; a.K = K; a.N = N;
+    a.ws = G.ws;
+
+    mm_f4_shape sh = { M, K, N, (uint32_t)G.sm_count, min_align(x, payload, scale, y), G.ws_bytes };
+    if (sh.ptr_align < 16)
+        return MM_ERR_SHAPE;               /* arena slots are >= 16-byte aligned */
+    mm_status st = G.forced_variant >= 0 ? mm_f4_select_variant(&sh, G.forced_variant, &a.plan)
+                                         : mm_f4_select(&sh, &a.plan);
+    if (st != MM_OK)
+        return st;
+
+    int err = 0;
+    switch (a.plan.variant) {
+    case MM_F4_V_ROWWARP:
+        err = mmb_launch_rowwarp(&a, stream);
+        break;
+    case MM_F4_V_STREAM:
+        MM_CHECK(encode_2d(a.tm_payload, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, payload, K / 2, N, 128,
+                           MMB_ST_ROWS, CU_TENSOR_MAP_SWIZZLE_128B));
+        MM_CHECK(encode_2d(a.tm_scale, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, scale, K / 16, N, 16,
+                           MMB_ST_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE));
+        err = mmb_launch_stream(&a, stream);
+        break;
+    case MM_F4_V_UMMA:
+        MM_CHECK(encode_2d(a.tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, MMB_UM_KBLOCK,
+                           a.plan.tile_m, CU_TENSOR_MAP_SWIZZLE_128B));
+        MM_CHECK(encode_2d(a.tm_payload, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, payload, K / 2, N, 32,
+                           a.plan.tile_n, CU_TENSOR_MAP_SWIZZLE_NONE));
+        MM_CHECK(encode_2d(a.tm_scale, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, scale, K / 16, N, 16,
+                           a.plan.tile_n, CU_TENSOR_MAP_SWIZZLE_NONE));
+        err = mmb_launch_umma(&a, stream);
+        break;
+    default:
+        return MM_ERR_UNSUPPORTED;
+    }
+    if (err) {
+        MM_LOGE("cuda: launch (variant %d, M %u K %u N %u): %s", a.plan.variant, M, K, N,
+                cudaGetErrorString((cudaError_t)err));
+        return MM_ERR_CUDA;
+    }
+    G.launches++;
+    return MM_OK;
+}
+
+/* Synchronise the compute stream and collect launch/device errors, unless a
+ * capture is in progress (then only launch errors can be seen). */
+static mm_status finish_op(void)
+{
+    cudaStream_t cs = (cudaStream_t)mm_cuda_stream_raw(MM_ST_COMPUTE);
+    if (!mm_cuda_capturing()) {
+        CK(cudaMemcpyAsync(G.status_host, G.status_dev, sizeof(unsigned), cudaMemcpyDeviceToHost, cs));
+        CK(cudaStreamSynchronize(cs));
+        if (*G.status_host) {
+            unsigned f = *G.status_host;
+            *G.status_host = 0;
+            CK(cudaMemsetAsync(G.status_dev, 0, sizeof(unsigned), cs));
+            MM_LOGE("device status 0x%x after op", f);
+            return (f & MMB_DEV_TIMEOUT) ? MM_ERR_TIMEOUT : MM_ERR_CUDA;
+        }
+    }
+    CK(cudaGetLastError());
+    return MM_OK;
+}
+
+mm_status mm_f4_device_status(unsigned *flags_out)
+{
+    MM_REQUIRE(flags_out, MM_ERR_STATE);
+    MM_CHECK(ensure_ready());
+    cudaStream_t cs = (cudaStream_t)mm_cuda_stream_raw(MM_ST_COMPUTE);
+    CK(cudaMemcpyAsync(G.status_host, G.status_dev, sizeof(unsigned), cudaMemcpyDeviceToHost, cs));
+    CK(cudaMemsetAsync(G.status_dev, 0, sizeof(unsigned), cs));
+    CK(cudaStreamSynchronize(cs));
+    *flags_out = *G.status_host;
+    *G.status_host = 0;
+    return MM_OK;
+}
+
+mm_status kx_op_gemm_f4(const mm_kcall *kc)
+{
+    MM_REQUIRE(kc && kc->op, MM_ERR_STATE);
+    const mm_op_desc *op = kc->op;
+    if (op->n1 % 16 != 0)
+        return MM_ERR_SHAPE;
+    MM_REQUIRE(op->a && op->b && op->c && op->d, MM_ERR_STATE);
+    MM_REQUIRE(mm_cuda_stream_raw(MM_ST_COMPUTE) != NULL, MM_ERR_STATE);
+    mm_status st = mm_f4_linear(op->a, op->b, op->d, mm_f4_gscale_get(op->d), op->c, op->n0,
+                                op->n1, op->n2, mm_cuda_stream_raw(MM_ST_COMPUTE));
+    if (st != MM_OK)
+        return st;
+    return finish_op();
+}
+
+mm_status kx_op_qkv(const mm_kcall *kc)
+{
+    MM_REQUIRE(kc && kc->op, MM_ERR_STATE);
+    if (!kc->op->d)
+        return MM_ERR_UNSUPPORTED;     /* bf16 fused qkv: not this library's op */
+    return kx_op_gemm_f4(kc);
+}
+
+int kx_cuda_oppref(int op)
+{
+    return op == OP_GEMM_F4 || op == OP_QKV || op == OP_NOP;
+}
+
+mm_status mm_kx_invoke(const mm_kcall *kc)
+{
+    if (!kc || !kc->op || !kc->e)
+        return MM_ERR_STATE;
+    switch (kc->op->op) {
+    case OP_GEMM_F4: return kx_op_gemm_f4(kc);
+    case OP_QKV:     return kx_op_qkv(kc);
+    case OP_NOP:     return MM_OK;
+    default:
+        MM_LOGE("kx: opcode %d is not served by the NVFP4 linear library", kc->op->op);
+        return MM_ERR_UNSUPPORTED;
+    }
+}
+
+mm_status mm_f4_linear_host(const void *x_host, void *x_dev, const void *payload_dev,
+                            const void *scale_dev, float gs, void *y_dev, void *y_host,
+                            uint32_t M, uint32_t K, uint32_t N)
+{
+    MM_REQUIRE(x_host && x_dev && y_dev && y_host, MM_ERR_STATE);
+    MM_REQUIRE(!mm_cuda_capturing(), MM_ERR_BUSY);
+    MM_CHECK(mm_h2d_async(x_dev, x_host, (size_t)M * K * 2u, MM_ST_COMPUTE));
+    mm_status st = mm_f4_linear(x_dev, payload_dev, scale_dev, gs, y_dev, M, K, N, NULL);
+    if (st != MM_OK)
+        return st;
+    MM_CHECK(mm_d2h_async(y_host, y_dev, (size_t)M * N * 2u, MM_ST_COMPUTE));
+    return finish_op();
+}
+
+mm_status mm_f4_decode_probe(uint32_t *out_mma_dev, uint32_t *out_f32_dev)
+{
+    MM_REQUIRE(out_mma_dev && out_f32_dev, MM_ERR_STATE);
+    MM_CHECK(ensure_ready());
+    cudaStream_t cs = (cudaStream_t)mm_cuda_stream_raw(MM_ST_COMPUTE);
+    CK((cudaError_t)mmb_launch_decode_probe(out_mma_dev, out_f32_dev, cs));
+    G.launches++;
+    CK(cudaStreamSynchronize(cs));
+    return MM_OK;
+}

@@ -1,0 +1,104 @@
+/*
+ * Op-list engine: a fixed sequence of NVFP4 linear ops, dispatched one by one
+ * or captured once into a CUDA graph and replayed.
+ *
+ * In mimfer the planner fills a flat array of address-fixed descriptors
+ * (src/plan/plan.c:386-473), runs them through the dispatcher
+ * (plan_run_ops, plan.c:119-130) and captures that walk into a graph at load
+ * (capture_one, plan.c:479-507; launch, plan.c:132-138).  This engine is the
+ * same mechanism restricted to the ops this library serves; the descriptors
+ * are the reference's mm_op_desc, so a reference plan's linear ops can be
+ * appended unchanged.
+ */
+#include "../core/core.h"
+#include <stdlib.h>
+#include <string.h>
+
+struct mm_lin_engine {
+    mm_op_desc *ops;
+    uint32_t    n_ops, max_ops;
+    mm_graph   *graph;
+    int         captured;
+};
+
+mm_status mm_lin_engine_create(mm_lin_engine **out, uint32_t max_ops)
+{
+    MM_REQUIRE(out && max_ops > 0, MM_ERR_STATE);
+    mm_lin_engine *e = (mm_lin_engine *)calloc(1, sizeof *e);
+    if (!e)
+        return MM_ERR_NOMEM;
+    e->ops = (mm_op_desc *)calloc(max_ops, sizeof(mm_op_desc));
+    if (!e->ops) {
+        free(e);
+        return MM_ERR_NOMEM;
+    }
+    e->max_ops = max_ops;
+    *out = e;
+    return MM_OK;
+}
+
+mm_status mm_lin_engine_add(mm_lin_engine *e, const mm_op_desc *op)
+{
+    MM_REQUIRE(e && op, MM_ERR_STATE);
+    MM_REQUIRE(!e->captured, MM_ERR_BUSY);
+    MM_REQUIRE(e->n_ops < e->max_ops, MM_ERR_CAPACITY);
+    MM_REQUIRE(kx_cuda_oppref(op->op), MM_ERR_UNSUPPORTED);
+    if (op->op != OP_NOP) {
+        MM_REQUIRE(op->a && op->b && op->c && op->d, MM_ERR_STATE);
+        if (op->n0 == 0 || op->n1 == 0 || op->n2 == 0 || op->n1 % 16 != 0)
+            return MM_ERR_SHAPE;
+    }
+    e->ops[e->n_ops++] = *op;
+    return MM_OK;
+}
+
+uint32_t mm_lin_engine_n_ops(const mm_lin_engine *e) { return e ? e->n_ops : 0; }
+
+static mm_status run_ops(mm_lin_engine *e)
+{
+    mm_kcall kc;
+    kc.e = (const mm_engine *)e;      /* the dispatcher only tests it for NULL */
+    kc.stream = NULL;
+    for (uint32_t i = 0; i < e->n_ops; i++) {
+        kc.op = &e->ops[i];
+        mm_status st = mm_kx_invoke(&kc);
+        if (st != MM_OK) {
+            MM_LOGE("engine: op %u (%s) failed: %s", i, e->ops[i].note, mm_status_str(st));
+            return st;
+        }
+    }
+    return MM_OK;
+}
+
+mm_status mm_lin_engine_capture(mm_lin_engine *e)
+{
+    MM_REQUIRE(e && e->n_ops > 0, MM_ERR_STATE);
+    if (!e->graph)
+        MM_CHECK(mm_graph_create(&e->graph));
+    MM_CHECK(mm_graph_capture_begin(e->graph));
+    mm_status st = run_ops(e);
+    mm_status st2 = mm_graph_commit(e->graph, NULL, 0, 0);   /* always ends the capture */
+    if (st != MM_OK)
+        return st;
+    if (st2 != MM_OK)
+        return st2;
+    e->captured = 1;
+    return MM_OK;
+}
+
+mm_status mm_lin_engine_launch(mm_lin_engine *e)
+{
+    MM_REQUIRE(e && e->n_ops > 0, MM_ERR_STATE);
+    if (e->captured)
+        return mm_graph_launch(e->graph, MM_ST_COMPUTE);
+    return run_ops(e);
+}
+
+void mm_lin_engine_destroy(mm_lin_engine *e)
+{
+    if (!e)
+        return;
+    mm_graph_destroy(e->graph);
+    free(e->ops);
+    free(e);
+}

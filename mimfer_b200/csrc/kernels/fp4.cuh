@@ -1,0 +1,96 @@
+/*
+ * NVFP4 decode on the device.  Two forms, both bit-exact with the mimfer
+ * decoders (include/mimfer/tensor.h:90-118):
+ *
+ *  fp32 form   e2m1_f32(n) * e4m3_f32(s), used by the row-warp kernel.
+ *
+ *  bf16 operand form, used by both tensor-core kernels.  A nibble's three
+ *  magnitude bits (e1 e0 m) are placed at bits 8..6 of a bf16: the exponent
+ *  field becomes e and the top mantissa bit m, which reads as the e2m1 value
+ *  times 2^-126 for every code, the two subnormal codes (0, 0.5) included
+ *  because a bf16 with exponent field 0 is subnormal in the same way.  One
+ *  packed bf16 multiply by (e4m3 scale * 2^118), looked up from a 256-entry
+ *  table so that 0x7f/0xff give 0 and the scale's sign is kept, yields
+ *  value * scale * 2^-8 exactly: e2m1 x e4m3 needs at most 6 significant
+ *  bits.  The 2^8 is returned in the epilogue together with the global scale.
+ */
+#pragma once
+#include <cstdint>
+#include <cuda_bf16.h>
+
+namespace mmb {
+
+__device__ __forceinline__ float e4m3_f32(uint32_t b)
+{
+    if ((b & 0x7fu) == 0x7fu)
+        return 0.0f;
+    uint32_t e = (b >> 3) & 15u, m = b & 7u;
+    float mag = e ? __uint_as_float(((e + 120u) << 23) | (m << 20))
+                  : static_cast<float>(m) * 0.001953125f;          /* m * 2^-9 */
+    return (b & 0x80u) ? -mag : mag;
+}
+
+__device__ __forceinline__ float e2m1_f32(uint32_t n)
+{
+    uint32_t e = (n >> 1) & 3u, m = n & 1u;
+    float mag = e ? __uint_as_float(((e + 126u) << 23) | (m << 22)) : 0.5f * static_cast<float>(m);
+    return (n & 8u) ? -mag : mag;
+}
+
+/* Table entry for scale byte b: bf16x2 (c, c) with c = e4m3(b) * 2^118. */
+__device__ __forceinline__ uint32_t scale_lut_entry(uint32_t b)
+{
+    float c = e4m3_f32(b) * 3.3230699894622813e35f;                /* 2^118, exact */
+    uint32_t hi = __float_as_uint(c) >> 16;                        /* <= 4 significant bits */
+    return hi | (hi << 16);
+}
+
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b)
+{
+    uint32_t d;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
+{
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+/* Eight nibbles n0..n7 of `w` (n0 lowest) -> four bf16x2 registers holding
+ * (n0,n4) (n1,n5) (n2,n6) (n3,n7), low half first, each already multiplied by
+ * the scale entry c.  nibble * 0x1040 copies the nibble to bits 15..12 and
+ * 9..6 of its half-word; the mask keeps the sign at bit 15 and the magnitude
+ * at bits 8..6. */
+__device__ __forceinline__ void unpack8_paired(uint32_t w, uint32_t c, uint32_t (&q)[4])
+{
+    const uint32_t keep = 0x81c081c0u;
+    uint32_t hi = w >> 8;
+    q[0] = mul_bf16x2(((w & 0x000f000fu) * 0x1040u) & keep, c);
+    q[1] = mul_bf16x2(((w & 0x00f000f0u) * 0x0104u) & keep, c);
+    q[2] = mul_bf16x2(((hi & 0x000f000fu) * 0x1040u) & keep, c);
+    q[3] = mul_bf16x2(((hi & 0x00f000f0u) * 0x0104u) & keep, c);
+}
+
+/* Same eight weights in column order: (n0,n1) (n2,n3) (n4,n5) (n6,n7). */
+__device__ __forceinline__ uint4 unpack8_natural(uint32_t w, uint32_t c)
+{
+    uint32_t q[4];
+    unpack8_paired(w, c, q);
+    uint4 r;
+    r.x = prmt(q[0], q[1], 0x5410u);
+    r.y = prmt(q[2], q[3], 0x5410u);
+    r.z = prmt(q[0], q[1], 0x7632u);
+    r.w = prmt(q[2], q[3], 0x7632u);
+    return r;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+{
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+} // namespace mmb

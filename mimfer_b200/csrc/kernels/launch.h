@@ -1,0 +1,82 @@
+/*
+ * Launch interface between the C launcher (csrc/cuda/kx_gemm_f4.c) and the
+ * kernels (the .cu files under csrc/kernels).  One POD argument block per op; the tile and
+ * grid numbers come from the selector (csrc/plan/select.c) and the smem
+ * footprints below are the single definition both sides use.
+ */
+#ifndef MMB_LAUNCH_H
+#define MMB_LAUNCH_H
+
+#include "mimfer_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- STREAM (decode) geometry ------------------------------------------- */
+#define MMB_ST_ROWS        256u   /* weight rows per CTA (8 warps x 32 rows)   */
+#define MMB_ST_KSTEP       256u   /* weights along K per pipeline stage        */
+#define MMB_ST_CONSUMERS   8u     /* MMA warps; +1 producer warp               */
+#define MMB_ST_THREADS     ((MMB_ST_CONSUMERS + 1u) * 32u)
+#define MMB_ST_PAYLOAD_B   (MMB_ST_ROWS * 128u)            /* SW128 box        */
+#define MMB_ST_SCALE_B     (MMB_ST_ROWS * 16u)
+#define MMB_ST_X_B(mt)     ((mt) * 8u * MMB_ST_KSTEP * 2u)
+#define MMB_ST_STAGE_B(mt) (MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B + MMB_ST_X_B(mt))
+#define MMB_ST_FIXED_B     (1024u /* scale LUT */ + 256u /* barriers */ + 1024u /* align slack */)
+
+/* ---- UMMA (prefill) geometry ---------------------------------------------- */
+#define MMB_UM_KBLOCK      64u    /* bf16 elements per smem row (128 B swizzle) */
+#define MMB_UM_KGROUP      256u   /* weights covered by one scale box (16 B)    */
+#define MMB_UM_DEQ_WARPS   8u
+#define MMB_UM_THREADS     ((2u + MMB_UM_DEQ_WARPS) * 32u)
+#define MMB_UM_PAY_SLOTS(bn) ((bn) >= 256u ? 2u : 4u)
+#define MMB_UM_SC_SLOTS    2u
+#define MMB_UM_A_B(bm)     ((bm) * MMB_UM_KBLOCK * 2u)
+#define MMB_UM_B_B(bn)     ((bn) * MMB_UM_KBLOCK * 2u)
+#define MMB_UM_PAY_B(bn)   ((bn) * 32u)
+#define MMB_UM_SC_B(bn)    ((bn) * 16u)
+#define MMB_UM_FIXED_B     (1024u /* scale LUT */ + 512u /* barriers, tmem slot */ + 1024u /* align slack */)
+#define MMB_UM_SMEM_B(bm, bn, st)                                              \
+    ((st) * (MMB_UM_A_B(bm) + MMB_UM_B_B(bn)) + MMB_UM_PAY_SLOTS(bn) * MMB_UM_PAY_B(bn) + \
+     MMB_UM_SC_SLOTS * MMB_UM_SC_B(bn) + MMB_UM_FIXED_B)
+
+#define MMB_SMEM_MAX       232448u   /* 227 KiB opt-in limit per CTA on sm_100 */
+
+/* Workspace layout: [counters: MMB_WS_COUNTER_B bytes][fp32 partials]. */
+#define MMB_WS_COUNTER_B   16384u
+#define MMB_WS_MAX_TILES   (MMB_WS_COUNTER_B / 4u)
+
+/* Device status word bits. */
+#define MMB_DEV_TIMEOUT    1u
+#define MMB_DEV_BADARG     2u
+
+typedef struct mmb_args {
+    const void *x;        /* bf16 [M][K]        */
+    const void *payload;  /* u8   [N][K/2]      */
+    const void *scale;    /* u8   [N][K/16]     */
+    void       *y;        /* bf16 [M][N]        */
+    float       gs;
+    uint32_t    M, K, N;
+    void       *ws;       /* workspace base or NULL */
+    mm_f4_plan  plan;
+    /* 128-byte TMA descriptors, filled by the launcher (opaque here) */
+    unsigned char tm_payload[128] __attribute__((aligned(64)));
+    unsigned char tm_scale[128] __attribute__((aligned(64)));
+    unsigned char tm_x[128] __attribute__((aligned(64)));
+} mmb_args;
+
+/* Each returns a cudaError_t value (0 = success) from the launch. `stream`
+ * is a cudaStream_t. */
+int mmb_launch_rowwarp(const mmb_args *a, void *stream);
+int mmb_launch_stream(const mmb_args *a, void *stream);
+int mmb_launch_umma(const mmb_args *a, void *stream);
+int mmb_launch_decode_probe(uint32_t *out_mma, uint32_t *out_f32, void *stream);
+/* One-time per-process setup (smem opt-in attributes). */
+int mmb_kernels_init(void);
+/* Address of the device status word. */
+int mmb_status_word(unsigned **dev_ptr);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

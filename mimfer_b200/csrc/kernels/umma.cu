@@ -1,0 +1,290 @@
+/*
+ * UMMA: the prefill kernel of the NVFP4 linear op (M > 32, tensor-bound).
+ *
+ * y[M][N] tile of BM x BN per CTA, accumulated in tensor memory by
+ * tcgen05.mma kind::f16 (bf16 x bf16 -> fp32).  Activations stay bf16 in the
+ * reference (src/kernels/cpu/cx.c:211), so the weights are dequantised to bf16
+ * in shared memory; e2m1 x e4m3 fits a bf16 exactly, so every product the
+ * tensor core forms is the reference's product.
+ *
+ * Warp roles (10 warps):
+ *   warp 0      TMA producer: activation tile (BM x 64 bf16, 128-byte swizzle),
+ *               packed payload (BN rows x 32 B per 64-wide K block) and block
+ *               scales (BN rows x 16 B per 256-wide K group).
+ *   warp 1      owns tensor memory; one lane issues the MMAs and commits.
+ *   warps 2-9   dequantise: 16-byte shared load of 32 nibbles, unpack + scale
+ *               in registers (fp4.cuh), 16-byte stores into the K-major
+ *               swizzled B tile, fence.proxy.async, mbarrier hand-off to warp 1.
+ *               After the K loop the same warps drain tensor memory:
+ *               tcgen05.ld, times global scale, bf16, 16-byte global stores.
+ *
+ * Operand roles: A = activations (BM/128 tiles of 128 rows), B = weights
+ * (BN rows), so accumulator lane = activation row and column = output
+ * feature, which makes the epilogue's rows contiguous in y.
+ *
+ * It replaces the one-thread-per-output kernel of the reference
+ * (src/kernels/cuda/cx.cu:345-356) for the prefill regime; the design the
+ * reference only sketches is "dequant + bf16 mma gemm"
+ * (include/mimfer/plan.h:51-52).
+ */
+#include "fp4.cuh"
+#include "ptx.cuh"
+
+namespace mmb {
+
+struct UmmaParams {
+    uint16_t *y;
+    unsigned *status;
+    float     gs;
+    uint32_t  M, K, N;
+    uint32_t  k_blocks;      /* K / 64 */
+    uint32_t  stages;
+};
+
+template <int BM, int BN>
+__global__ void __launch_bounds__(MMB_UM_THREADS, 1)
+f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ TmaDesc tm_payload,
+               const __grid_constant__ TmaDesc tm_scale, const UmmaParams p)
+{
+    constexpr uint32_t A_B = MMB_UM_A_B(BM), B_B = MMB_UM_B_B(BN);
+    constexpr uint32_t PAY_B = MMB_UM_PAY_B(BN), SC_B = MMB_UM_SC_B(BN);
+    constexpr uint32_t HALVES = BM / 128;
+    constexpr uint32_t PAY_SLOTS = MMB_UM_PAY_SLOTS(BN);
+    constexpr uint32_t TMEM_COLS = HALVES * BN;              /* 128, 256 or 512 */
+    constexpr uint32_t ITEMS = BN * 2 / (MMB_UM_DEQ_WARPS * 32);
+    constexpr uint32_t IDESC = umma_idesc_bf16(128, BN);
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t ST = p.stages;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sm_a = base;
+    const uint32_t sm_b = sm_a + ST * A_B;
+    const uint32_t sm_pay = sm_b + ST * B_B;
+    const uint32_t sm_sc = sm_pay + PAY_SLOTS * PAY_B;
+    const uint32_t lut = sm_sc + MMB_UM_SC_SLOTS * SC_B;
+    const uint32_t bars = lut + 1024u;
+    /* barrier map (8 bytes each) */
+    const uint32_t full_a = bars;                       /* [ST] TMA -> MMA              */
+    const uint32_t full_b = full_a + 8u * ST;           /* [ST] dequant -> MMA          */
+    const uint32_t empty_ab = full_b + 8u * ST;         /* [ST] MMA done -> TMA, dequant */
+    const uint32_t full_pay = empty_ab + 8u * ST;       /* [PAY_SLOTS]                  */
+    const uint32_t empty_pay = full_pay + 8u * PAY_SLOTS;
+    const uint32_t full_sc = empty_pay + 8u * PAY_SLOTS;
+    const uint32_t empty_sc = full_sc + 8u * MMB_UM_SC_SLOTS;
+    const uint32_t accum_full = empty_sc + 8u * MMB_UM_SC_SLOTS;
+    const uint32_t tmem_slot = accum_full + 8u;
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    const uint32_t KB = p.k_blocks;
+
+    if (tid < 256u)
+        sts32(lut + tid * 4u, scale_lut_entry(tid));
+    if (tid == 0) {
+        for (uint32_t s = 0; s < ST; s++) {
+            mbar_init(full_a + 8u * s, 1u);
+            mbar_init(full_b + 8u * s, MMB_UM_DEQ_WARPS);
+            mbar_init(empty_ab + 8u * s, 1u);
+        }
+        for (uint32_t s = 0; s < PAY_SLOTS; s++) {
+            mbar_init(full_pay + 8u * s, 1u);
+            mbar_init(empty_pay + 8u * s, MMB_UM_DEQ_WARPS);
+        }
+        for (uint32_t s = 0; s < MMB_UM_SC_SLOTS; s++) {
+            mbar_init(full_sc + 8u * s, 1u);
+            mbar_init(empty_sc + 8u * s, MMB_UM_DEQ_WARPS);
+        }
+        mbar_init(accum_full, 1u);
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = lds32(tmem_slot);
+
+    if (warp == 0) {
+        /* ------------------------------ TMA producer ---------------------- */
+        if (lane == 0) {
+            for (uint32_t kb = 0; kb < KB; kb++) {
+                const uint32_t s = kb % ST, ps = kb % PAY_SLOTS;
+                if ((kb & 3u) == 0) {
+                    const uint32_t grp = kb >> 2, ss = grp % MMB_UM_SC_SLOTS;
+                    if (grp >= MMB_UM_SC_SLOTS)
+                        mbar_wait(empty_sc + 8u * ss, ((grp / MMB_UM_SC_SLOTS) - 1u) & 1u, p.status);
+                    mbar_expect_tx(full_sc + 8u * ss, SC_B);
+                    tma_load_2d(sm_sc + ss * SC_B, &tm_scale, static_cast<int>(grp * 16u),
+                                static_cast<int>(n0), full_sc + 8u * ss);
+                }
+                if (kb >= PAY_SLOTS)
+                    mbar_wait(empty_pay + 8u * ps, ((kb / PAY_SLOTS) - 1u) & 1u, p.status);
+                mbar_expect_tx(full_pay + 8u * ps, PAY_B);
+                tma_load_2d(sm_pay + ps * PAY_B, &tm_payload, static_cast<int>(kb * 32u),
+                            static_cast<int>(n0), full_pay + 8u * ps);
+                if (kb >= ST)
+                    mbar_wait(empty_ab + 8u * s, ((kb / ST) - 1u) & 1u, p.status);
+                mbar_expect_tx(full_a + 8u * s, A_B);
+                tma_load_2d(sm_a + s * A_B, &tm_x, static_cast<int>(kb * MMB_UM_KBLOCK),
+                            static_cast<int>(m0), full_a + 8u * s);
+            }
+        }
+    } else if (warp == 1) {
+        /* ------------------------------ MMA issue -------------------------- */
+        if (lane == 0) {
+            for (uint32_t kb = 0; kb < KB; kb++) {
+                const uint32_t s = kb % ST, par = (kb / ST) & 1u;
+                mbar_wait(full_a + 8u * s, par, p.status);
+                mbar_wait(full_b + 8u * s, par, p.status);
+                tc_fence_after();
+#pragma unroll
+                for (uint32_t k = 0; k < MMB_UM_KBLOCK / 16u; k++) {
+                    const uint64_t bd = umma_desc_sw128(sm_b + s * B_B + k * 32u);
+#pragma unroll
+                    for (uint32_t h = 0; h < HALVES; h++) {
+                        const uint64_t ad = umma_desc_sw128(sm_a + s * A_B + h * 16384u + k * 32u);
+                        umma_bf16(tmem_base + h * BN, ad, bd, IDESC, (kb | k) ? 1u : 0u);
+                    }
+                }
+                umma_commit(empty_ab + 8u * s);
+            }
+            umma_commit(accum_full);
+        }
+    } else {
+        /* ------------------------------ dequantise -------------------------- */
+        const uint32_t td = tid - 64u;                       /* 0..255 */
+        for (uint32_t kb = 0; kb < KB; kb++) {
+            const uint32_t s = kb % ST, ps = kb % PAY_SLOTS;
+            const uint32_t grp = kb >> 2, ss = grp % MMB_UM_SC_SLOTS, j = kb & 3u;
+            if (j == 0)
+                mbar_wait(full_sc + 8u * ss, (grp / MMB_UM_SC_SLOTS) & 1u, p.status);
+            mbar_wait(full_pay + 8u * ps, (kb / PAY_SLOTS) & 1u, p.status);
+            if (kb >= ST)
+                mbar_wait(empty_ab + 8u * s, ((kb / ST) - 1u) & 1u, p.status);
+            const uint32_t pay = sm_pay + ps * PAY_B, scl = sm_sc + ss * SC_B;
+            const uint32_t bt = sm_b + s * B_B;
+#pragma unroll
+            for (uint32_t item = 0; item < ITEMS; item++) {
+                const uint32_t idx = td + item * 256u;
+                const uint32_t n = idx >> 1, half = idx & 1u;
+                const uint4 raw = lds128(pay + n * 32u + half * 16u);
+                const uint32_t sc2 = lds16(scl + n * 16u + j * 4u + half * 2u);
+                const uint32_t c0 = lds32(lut + (sc2 & 255u) * 4u);
+                const uint32_t c1 = lds32(lut + (sc2 >> 8) * 4u);
+                const uint32_t rowb = bt + n * 128u, sw = n & 7u, ch = half * 4u;
+                sts128(rowb + (((ch + 0u) ^ sw) << 4), unpack8_natural(raw.x, c0));
+                sts128(rowb + (((ch + 1u) ^ sw) << 4), unpack8_natural(raw.y, c0));
+                sts128(rowb + (((ch + 2u) ^ sw) << 4), unpack8_natural(raw.z, c1));
+                sts128(rowb + (((ch + 3u) ^ sw) << 4), unpack8_natural(raw.w, c1));
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(full_b + 8u * s);
+                mbar_arrive(empty_pay + 8u * ps);
+                if (j == 3u)
+                    mbar_arrive(empty_sc + 8u * ss);
+            }
+        }
+
+        /* ------------------------------ epilogue --------------------------- */
+        mbar_wait(accum_full, 0u, p.status);
+        tc_fence_after();
+        const float out_scale = p.gs * 256.0f;      /* undo the 2^-8 of the operand form */
+        const uint32_t quad = warp & 3u;            /* TMEM lanes this warp may read   */
+        const uint32_t pair = (warp - 2u) >> 2;     /* two warps share a quadrant       */
+        constexpr uint32_t CHUNKS = HALVES * (BN / 32);
+        for (uint32_t c = pair; c < CHUNKS; c += 2u) {
+            const uint32_t h = c / (BN / 32), cc = c % (BN / 32);
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + h * BN + cc * 32u, r);
+            tmem_ld_wait();
+            const uint32_t m = m0 + h * 128u + quad * 32u + lane;
+            const uint32_t n = n0 + cc * 32u;
+            if (m < p.M && n < p.N) {
+                uint16_t *dst = p.y + static_cast<size_t>(m) * p.N + n;
+                if (n + 32u <= p.N) {
+#pragma unroll
+                    for (int v = 0; v < 4; v++) {
+                        uint4 o;
+                        o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]) * out_scale,
+                                          __uint_as_float(r[8 * v + 1]) * out_scale);
+                        o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]) * out_scale,
+                                          __uint_as_float(r[8 * v + 3]) * out_scale);
+                        o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]) * out_scale,
+                                          __uint_as_float(r[8 * v + 5]) * out_scale);
+                        o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]) * out_scale,
+                                          __uint_as_float(r[8 * v + 7]) * out_scale);
+                        *reinterpret_cast<uint4 *>(dst + 8 * v) = o;
+                    }
+                } else {
+                    for (uint32_t e = 0; e < 32u && n + e < p.N; e++) {
+                        __nv_bfloat16 hv = __float2bfloat16_rn(__uint_as_float(r[e]) * out_scale);
+                        dst[e] = *reinterpret_cast<uint16_t *>(&hv);
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int BM, int BN>
+static int launch_tile(const mmb_args *a, unsigned *status, cudaStream_t st)
+{
+    UmmaParams p;
+    p.y = static_cast<uint16_t *>(a->y);
+    p.status = status;
+    p.gs = a->gs;
+    p.M = a->M; p.K = a->K; p.N = a->N;
+    p.k_blocks = a->plan.k_steps;
+    p.stages = a->plan.stages;
+    TmaDesc tx, tp, ts;
+    memcpy(tx.bytes, a->tm_x, 128);
+    memcpy(tp.bytes, a->tm_payload, 128);
+    memcpy(ts.bytes, a->tm_scale, 128);
+    dim3 grid(a->plan.grid_x, a->plan.grid_y), block(MMB_UM_THREADS);
+    f4_umma_kernel<BM, BN><<<grid, block, a->plan.smem_bytes, st>>>(tx, tp, ts, p);
+    return static_cast<int>(cudaGetLastError());
+}
+
+template <int BM, int BN>
+static int set_smem()
+{
+    return static_cast<int>(cudaFuncSetAttribute(f4_umma_kernel<BM, BN>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 MMB_SMEM_MAX));
+}
+
+} // namespace mmb
+
+extern "C" int mmb_umma_init(void)
+{
+    int e;
+    if ((e = mmb::set_smem<256, 256>())) return e;
+    if ((e = mmb::set_smem<256, 128>())) return e;
+    if ((e = mmb::set_smem<128, 256>())) return e;
+    return mmb::set_smem<128, 128>();
+}
+
+extern "C" int mmb_launch_umma(const mmb_args *a, void *stream)
+{
+    unsigned *status = nullptr;
+    int e = mmb_status_word(&status);
+    if (e) return e;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint32_t bm = a->plan.tile_m, bn = a->plan.tile_n;
+    if (bm == 256 && bn == 256) return mmb::launch_tile<256, 256>(a, status, st);
+    if (bm == 256 && bn == 128) return mmb::launch_tile<256, 128>(a, status, st);
+    if (bm == 128 && bn == 256) return mmb::launch_tile<128, 256>(a, status, st);
+    if (bm == 128 && bn == 128) return mmb::launch_tile<128, 128>(a, status, st);
+    return static_cast<int>(cudaErrorInvalidValue);
+}

@@ -1,0 +1,160 @@
+/*
+ * Tile and variant selection for the NVFP4 linear op: pure host C, no CUDA,
+ * deterministic (a shape always maps to the same plan, so captured graphs and
+ * direct dispatch agree).
+ *
+ * The mimfer planner emits OP_GEMM_F4 without choosing a kernel
+ * (src/plan/plan.c:204-220); its descriptor comment only sketches the intent,
+ * "M<=8: split-K gemv, else dequant + bf16 mma gemm" (include/mimfer/plan.h:51-52).
+ * This file is that choice for B200:
+ *
+ *   STREAM   M <= 32.  HBM-bound.  One CTA streams 256 weight rows through a
+ *            TMA pipeline; K is split across CTAs until about one CTA per SM
+ *            exists, partials meet in the workspace in a fixed order.
+ *   UMMA     M > 32.  tcgen05 tiles of tile_m x tile_n; the tile shape is the
+ *            one with the lowest modelled time (waves x per-tile cost).
+ *   ROWWARP  anything the two above cannot take (K not a multiple of 256,
+ *            unaligned pointers).  Always valid for K % 16 == 0.
+ */
+#include "../core/core.h"
+#include "../kernels/launch.h"
+#include <string.h>
+
+static uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
+
+static int fast_path_ok(const mm_f4_shape *s)
+{
+    /* TMA: 16-byte aligned bases, row pitches K/2 and K/16 multiples of 16 B */
+    return s->K % 256 == 0 && s->ptr_align >= 16 && s->ptr_align % 16 == 0;
+}
+
+static void plan_rowwarp(const mm_f4_shape *s, mm_f4_plan *p)
+{
+    memset(p, 0, sizeof *p);
+    p->variant = MM_F4_V_ROWWARP;
+    p->split_k = 1;
+    p->threads = 256;                       /* 8 warps = 8 weight rows per CTA */
+    p->grid_x = ceil_div(s->N, 8);
+    p->grid_y = ceil_div(s->M, 4);          /* 4 activation rows per pass      */
+    p->grid_z = 1;
+    if (p->grid_y > 65535) p->grid_y = 65535;
+}
+
+static mm_status plan_stream(const mm_f4_shape *s, mm_f4_plan *p)
+{
+    if (!fast_path_ok(s) || s->M > 32)
+        return MM_ERR_UNSUPPORTED;
+    memset(p, 0, sizeof *p);
+    p->variant = MM_F4_V_STREAM;
+    p->m_tiles = s->M <= 8 ? 1 : (s->M <= 16 ? 2 : 4);
+    p->tile_n = MMB_ST_ROWS;
+    p->tile_m = p->m_tiles * 8;
+    p->k_steps = s->K / MMB_ST_KSTEP;
+    p->grid_x = ceil_div(s->N, MMB_ST_ROWS);
+    p->threads = MMB_ST_THREADS;
+
+    /* split K until roughly one CTA per SM, keeping >= 4 steps per slice */
+    uint32_t sms = s->sm_count ? s->sm_count : 148;
+    uint32_t sk = sms / p->grid_x;
+    if (sk < 1) sk = 1;
+    uint32_t max_by_steps = p->k_steps / 4 ? p->k_steps / 4 : 1;
+    if (sk > max_by_steps) sk = max_by_steps;
+    if (sk > 32) sk = 32;
+    if (p->grid_x > MMB_WS_MAX_TILES) sk = 1;
+    while (sk > 1) {
+        size_t need = MMB_WS_COUNTER_B + (size_t)sk * p->tile_m * s->N * 4u;
+        if (need <= s->ws_bytes) { p->ws_needed = need; break; }
+        sk--;
+    }
+    p->split_k = sk;
+    p->grid_y = sk;
+    p->grid_z = 1;
+
+    uint32_t stage = MMB_ST_STAGE_B(p->m_tiles);
+    uint32_t st = (MMB_SMEM_MAX - MMB_ST_FIXED_B) / stage;
+    if (st > 6) st = 6;
+    uint32_t per = ceil_div(p->k_steps, sk);
+    if (st > per) st = per;
+    if (st < 1) st = 1;
+    p->stages = st;
+    p->smem_bytes = st * stage + MMB_ST_FIXED_B;
+    return MM_OK;
+}
+
+/* modelled cost of one CTA tile, arbitrary units: MMA time grows with
+ * tile_m*tile_n; narrow tiles run the tensor pipe less efficiently because
+ * operand traffic per MAC rises. */
+static double umma_tile_cost(uint32_t bm, uint32_t bn)
+{
+    double eff = (bm == 256 && bn == 256) ? 1.0 : ((bm == 256 || bn == 256) ? 0.85 : 0.7);
+    return (double)bm * bn / eff;
+}
+
+static mm_status plan_umma(const mm_f4_shape *s, mm_f4_plan *p)
+{
+    static const uint32_t cand[4][2] = { {256, 256}, {256, 128}, {128, 256}, {128, 128} };
+    if (!fast_path_ok(s) || s->N % 8 != 0)
+        return MM_ERR_UNSUPPORTED;
+    uint32_t sms = s->sm_count ? s->sm_count : 148;
+    double best = 0.0;
+    int best_i = -1;
+    for (int i = 0; i < 4; i++) {
+        uint32_t bm = cand[i][0], bn = cand[i][1];
+        uint32_t tiles = ceil_div(s->M, bm) * ceil_div(s->N, bn);
+        uint32_t waves = ceil_div(tiles, sms);
+        double t = (double)waves * umma_tile_cost(bm, bn);
+        if (best_i < 0 || t < best * 0.999) { best = t; best_i = i; }
+    }
+    memset(p, 0, sizeof *p);
+    p->variant = MM_F4_V_UMMA;
+    p->tile_m = cand[best_i][0];
+    p->tile_n = cand[best_i][1];
+    p->split_k = 1;
+    p->k_steps = s->K / MMB_UM_KBLOCK;
+    p->grid_x = ceil_div(s->N, p->tile_n);
+    p->grid_y = ceil_div(s->M, p->tile_m);
+    p->grid_z = 1;
+    p->threads = MMB_UM_THREADS;
+    uint32_t st = 6;
+    while (st > 2 && MMB_UM_SMEM_B(p->tile_m, p->tile_n, st) > MMB_SMEM_MAX) st--;
+    p->stages = st;
+    p->smem_bytes = MMB_UM_SMEM_B(p->tile_m, p->tile_n, st);
+    if (p->smem_bytes > MMB_SMEM_MAX)
+        return MM_ERR_UNSUPPORTED;
+    return MM_OK;
+}
+
+static mm_status check_shape(const mm_f4_shape *s, mm_f4_plan *out)
+{
+    if (!s || !out)
+        return MM_ERR_STATE;
+    if (s->M == 0 || s->N == 0 || s->K == 0 || s->K % 16 != 0)
+        return MM_ERR_SHAPE;
+    return MM_OK;
+}
+
+mm_status mm_f4_select_variant(const mm_f4_shape *s, int variant, mm_f4_plan *out)
+{
+    mm_status st = check_shape(s, out);
+    if (st != MM_OK)
+        return st;
+    switch (variant) {
+    case MM_F4_V_ROWWARP: plan_rowwarp(s, out); return MM_OK;
+    case MM_F4_V_STREAM:  return plan_stream(s, out);
+    case MM_F4_V_UMMA:    return plan_umma(s, out);
+    default:              return MM_ERR_RANGE;
+    }
+}
+
+mm_status mm_f4_select(const mm_f4_shape *s, mm_f4_plan *out)
+{
+    mm_status st = check_shape(s, out);
+    if (st != MM_OK)
+        return st;
+    if (s->M <= 32 && plan_stream(s, out) == MM_OK)
+        return MM_OK;
+    if (s->M > 32 && plan_umma(s, out) == MM_OK)
+        return MM_OK;
+    plan_rowwarp(s, out);
+    return MM_OK;
+}

@@ -1,0 +1,70 @@
+"""Tensor-parallel NVFP4 linear: output features sharded across ranks.
+
+Rank p of tp owns weight rows [p*N/tp, (p+1)*N/tp).  Payload and block scales
+are row-major by output feature (include/mimfer/tensor.h:17-19 in the mimfer
+tree), so a shard is a contiguous byte range of each buffer and no 16-wide
+scale group is ever split.  Activations are replicated.  Each rank computes
+y[:, shard] with the single-GPU op, then the slices are all-gathered (NCCL over
+NVLink; gloo on CPU in the tests) into [tp][M][N/tp] and laid out as [M][N].
+The reference has no multi-GPU path; this is new surface.
+"""
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(N, rank, world):
+    if N % world != 0:
+        raise ValueError(f"N={N} is not divisible by the tensor-parallel degree {world}")
+    per = N // world
+    return rank * per, (rank + 1) * per
+
+
+class TpLinear:
+    """`local_op(x, w_shard, y_shard)` computes the shard; by default it is the
+    CUDA op enqueued on the runtime's compute stream."""
+
+    def __init__(self, weight, rank, world, rt=None, group=None, local_op=None, max_m=None):
+        self.rank, self.world, self.group, self.rt = rank, world, group, rt
+        self.N, self.K = weight.N, weight.K
+        n0, n1 = shard_bounds(weight.N, rank, world)
+        self.shard = weight.rows(n0, n1)
+        self.local_op = local_op
+        if local_op is None:
+            if rt is None:
+                raise RuntimeError("TpLinear without a local_op needs the CUDA runtime")
+            self.shard.to_device(rt.device)
+            self.local_op = lambda x, w, y: rt.linear_async(x, w, y)
+        self._bufs = {}
+
+    def _buffers(self, M, like):
+        if M not in self._bufs:
+            ns = self.N // self.world
+            kw = dict(dtype=like.dtype, device=like.device)
+            self._bufs[M] = (torch.empty((M, ns), **kw), torch.empty((self.world, M, ns), **kw),
+                             torch.empty((M, self.N), **kw))
+        return self._bufs[M]
+
+    def forward(self, x):
+        """x: [M][K] replicated.  Returns y [M][N], complete on every rank.
+        On CUDA everything is enqueued on the runtime's compute stream."""
+        M = x.shape[0]
+        y_local, gathered, y = self._buffers(M, x)
+        if self.rt is not None and x.is_cuda:
+            with torch.cuda.stream(self.rt.torch_stream()):
+                self.local_op(x, self.shard, y_local)
+                self._gather(y_local, gathered, y, M)
+        else:
+            self.local_op(x, self.shard, y_local)
+            self._gather(y_local, gathered, y, M)
+        return y
+
+    def _gather(self, y_local, gathered, y, M):
+        if self.world == 1:
+            y.copy_(y_local)
+            return
+        dist.all_gather_into_tensor(gathered.view(-1), y_local.view(-1), group=self.group)
+        if M == 1:
+            y.view(-1).copy_(gathered.view(-1))
+        else:
+            ns = self.N // self.world
+            y.view(M, self.world, ns).copy_(gathered.permute(1, 0, 2))

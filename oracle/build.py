@@ -1,0 +1,72 @@
+"""Build recipe for the CPU oracle (test infrastructure, not product code).
+
+  liboracle.so            plain-C restatement of the reference algorithm
+                          (oracle/nvfp4_oracle.c)
+  _ref/libmimfer_ref.so   the reference's own CPU kernel, compiled from the
+                          sources where they lie in the read-only reference
+                          tree (src/kernels/cpu/cx.c + src/core/mimfer.c) plus
+                          oracle/ref_driver.c.  Only built when that tree is
+                          mounted; the prebuilt file is used otherwise.
+
+Run:  python oracle/build.py
+"""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+REF = os.environ.get("MIMFER_REFERENCE", "/root/reference")
+
+ORACLE_SO = os.path.join(HERE, "liboracle.so")
+REF_SO = os.path.join(HERE, "_ref", "libmimfer_ref.so")
+
+# -std=c11: ISO mode keeps -ffp-contract=off, so gcc forms no FMA; no
+# -march=native.  These are the flags that matter for bit-identity with the
+# reference host build (reference Makefile:8-11,32,41-46).
+CFLAGS = ["-std=c11", "-O2", "-fPIC", "-shared", "-fopenmp", "-Wall", "-Wextra"]
+
+
+def _newer(target, sources):
+    if not os.path.exists(target):
+        return False
+    t = os.path.getmtime(target)
+    return all(os.path.exists(s) and os.path.getmtime(s) <= t for s in sources)
+
+
+def build_oracle(force=False):
+    src = [os.path.join(HERE, "nvfp4_oracle.c")]
+    if not force and _newer(ORACLE_SO, src):
+        return ORACLE_SO
+    subprocess.check_call(["gcc", *CFLAGS, *src, "-o", ORACLE_SO])
+    return ORACLE_SO
+
+
+def reference_available():
+    return os.path.isfile(os.path.join(REF, "src", "kernels", "cpu", "cx.c"))
+
+
+def build_ref(force=False):
+    """Returns the path of the reference library, or None if it can be neither
+    built (no reference tree) nor found prebuilt."""
+    if not reference_available():
+        return REF_SO if os.path.exists(REF_SO) else None
+    src = [os.path.join(REF, "src", "kernels", "cpu", "cx.c"),
+           os.path.join(REF, "src", "core", "mimfer.c"),
+           os.path.join(HERE, "ref_driver.c")]
+    if not force and _newer(REF_SO, src):
+        return REF_SO
+    os.makedirs(os.path.dirname(REF_SO), exist_ok=True)
+    inc = ["-I" + os.path.join(REF, "include"),
+           "-I" + os.path.join(REF, "src", "kernels"),
+           "-I" + os.path.join(REF, "src", "model"),
+           "-I" + os.path.join(ROOT, "include")]
+    # the reference sources are compiled without -Wextra noise control: they are not ours
+    flags = [f for f in CFLAGS if f not in ("-Wall", "-Wextra")]
+    subprocess.check_call(["gcc", *flags, *inc, *src, "-lm", "-o", REF_SO])
+    return REF_SO
+
+
+if __name__ == "__main__":
+    print(build_oracle(force="--force" in sys.argv))
+    print(build_ref(force="--force" in sys.argv))

@@ -1,0 +1,91 @@
+"""Generate the golden fixtures from the reference's own CPU kernel.
+
+Needs oracle/_ref/libmimfer_ref.so, i.e. the mimfer tree mounted where
+oracle/build.py looks for it; the fixtures are committed so the tests do not.
+
+  decode_products.npz   every (scale byte, nibble) product, read out of the
+                        reference kx_op_gemm_f4 (src/kernels/cpu/cx.c:197-216)
+                        with one-hot activations; nibble in the low and in the
+                        high half of a byte; second scale block of a row.
+  random_bytes.npz      payload and scale bytes drawn uniformly (all 256 scale
+                        codes incl. 0x7f/0xff and negative scales), inputs stored.
+  seeded_<M>x<K>x<N>.npz  weights from the library's packer + generator (seed 0,
+                        N(0, 0.02)), activations seed 1 N(0, 1); stores the
+                        reference output, the global scale the packer chose and
+                        FNV-1a checksums of the generated inputs.
+
+Run:  python tests/golden/make_golden.py
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+import mimfer_b200 as mm                      # noqa: E402
+from oracle.pyoracle import Reference        # noqa: E402
+
+SEEDED = [(1, 256, 64), (3, 512, 40), (5, 1024, 96), (8, 768, 33), (16, 2048, 128),
+          (2, 5120, 64), (33, 256, 72)]
+
+
+def fnv1a64(a):
+    h = 1469598103934665603
+    for b in np.ascontiguousarray(a).view(np.uint8).ravel().tolist():
+        h = ((h ^ b) * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+    return np.uint64(h)
+
+
+def decode_products(ref):
+    one = 0x3F80                                         # bf16 1.0
+    out = {}
+    for name, col in (("low_nibble_col0", 0), ("high_nibble_col1", 1), ("second_block_col17", 17)):
+        K = 32
+        payload = np.zeros((4096, K // 2), np.uint8)
+        scales = np.zeros((4096, K // 16), np.uint8)
+        s = np.repeat(np.arange(256, dtype=np.uint8), 16)
+        n = np.tile(np.arange(16, dtype=np.uint8), 256)
+        payload[:, col // 2] = n << 4 if col & 1 else n
+        scales[:, col // 16] = s
+        x = np.zeros((1, K), np.uint16)
+        x[0, col] = one
+        rc, y = ref.gemm_f4(x, payload, scales)
+        assert rc == 0
+        out[name] = y[0].copy()                          # bf16 bits, index s*16+n
+    return out
+
+
+def main():
+    ref = Reference()
+    if not ref.available:
+        sys.exit("reference library not available; cannot regenerate fixtures")
+    np.savez_compressed(os.path.join(HERE, "decode_products.npz"), **decode_products(ref))
+
+    rng = np.random.Generator(np.random.PCG64(20250101))
+    M, K, N = 4, 512, 96
+    payload = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
+    scales = rng.integers(0, 256, (N, K // 16), dtype=np.uint8)
+    scales[0, :4] = (0x7F, 0xFF, 0x80, 0x00)
+    x = mm.make_activations(M, K, seed=7)
+    rc, y = ref.gemm_f4(x, payload, scales)
+    assert rc == 0
+    np.savez_compressed(os.path.join(HERE, "random_bytes.npz"), x=x, payload=payload, scales=scales, y=y)
+
+    for (M, K, N) in SEEDED:
+        w = mm.make_weight(N, K, seed=0, std=0.02)
+        x = mm.make_activations(M, K, seed=1)
+        rc, y = ref.gemm_f4(x, w.payload, w.scales)
+        assert rc == 0
+        np.savez_compressed(os.path.join(HERE, f"seeded_{M}x{K}x{N}.npz"), y=y,
+                            gs=np.float32(w.gs), payload_fnv=fnv1a64(w.payload),
+                            scales_fnv=fnv1a64(w.scales), x_fnv=fnv1a64(x))
+    # K % 16 != 0 is an error in the reference
+    rc, _ = ref.gemm_f4(np.zeros((1, 24), np.uint16), np.zeros((2, 12), np.uint8), np.zeros((2, 2), np.uint8))
+    np.savez_compressed(os.path.join(HERE, "status.npz"), k_not_multiple_of_16=np.int32(rc))
+    print("fixtures written to", HERE)
+
+
+if __name__ == "__main__":
+    main()

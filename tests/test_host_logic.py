@@ -1,0 +1,96 @@
+"""Launcher and engine behaviour that needs no GPU: argument checks come before
+any CUDA call, the global-scale registry, descriptor validation."""
+import ctypes as C
+
+import pytest
+
+from mimfer_b200 import _lib as L
+
+
+def kcall(op=L.OP_GEMM_F4, a=1, b=1, c=1, d=1, M=1, K=256, N=8, e=1):
+    desc = L.MmOpDesc()
+    desc.op, desc.layer = op, -1
+    desc.a, desc.b, desc.c, desc.d = a, b, c, d
+    desc.n0, desc.n1, desc.n2 = M, K, N
+    return L.MmKcall(C.pointer(desc), e, None), desc
+
+
+def test_dispatcher_null_checks(lib):
+    assert lib.mm_kx_invoke(None) == L.MM_ERR_STATE
+    kc, _ = kcall(e=None)
+    assert lib.mm_kx_invoke(C.byref(kc)) == L.MM_ERR_STATE       # reference: kx.c:19-20
+    kc = L.MmKcall(None, 1, None)
+    assert lib.mm_kx_invoke(C.byref(kc)) == L.MM_ERR_STATE
+
+
+def test_dispatcher_routes_only_owned_opcodes(lib):
+    lib.mm_log_set_level(-1)
+    for op in range(19):
+        assert lib.kx_cuda_oppref(op) == (1 if op in (L.OP_GEMM_F4, L.OP_QKV, L.OP_NOP) else 0)
+    kc, _ = kcall(op=L.OP_NOP)
+    assert lib.mm_kx_invoke(C.byref(kc)) == L.MM_OK
+    kc, _ = kcall(op=L.OP_GEMM_BF16)
+    assert lib.mm_kx_invoke(C.byref(kc)) == L.MM_ERR_UNSUPPORTED
+    kc, _ = kcall(op=L.OP_QKV, d=None)
+    assert lib.mm_kx_invoke(C.byref(kc)) == L.MM_ERR_UNSUPPORTED  # bf16 qkv is not served
+    lib.mm_log_set_level(1)
+
+
+def test_gemm_f4_argument_errors_precede_cuda(lib):
+    lib.mm_log_set_level(-1)
+    kc, _ = kcall(K=24)
+    assert lib.kx_op_gemm_f4(C.byref(kc)) == L.MM_ERR_SHAPE      # reference: cx.cu:365-366
+    kc, _ = kcall(a=None)
+    assert lib.kx_op_gemm_f4(C.byref(kc)) == L.MM_ERR_STATE
+    # runtime not initialised on a CPU-only machine -> state error, never a crash
+    kc, _ = kcall()
+    assert lib.kx_op_gemm_f4(C.byref(kc)) in (L.MM_ERR_STATE, L.MM_ERR_CUDA)
+    assert lib.mm_f4_linear(None, 1, 1, 1.0, 1, 1, 256, 8, None) == L.MM_ERR_STATE
+    assert lib.mm_f4_linear(1, 1, 1, 1.0, 1, 0, 256, 8, None) == L.MM_ERR_SHAPE
+    lib.mm_log_set_level(1)
+
+
+def test_global_scale_registry(lib):
+    lib.mm_f4_gscale_clear()
+    assert lib.mm_f4_gscale_get(0x1000) == 1.0                   # unregistered = reference maths
+    for i in range(1, 200):
+        assert lib.mm_f4_gscale_set(0x1000 * i, 0.5 * i) == L.MM_OK
+    for i in range(1, 200):
+        assert lib.mm_f4_gscale_get(0x1000 * i) == 0.5 * i
+    assert lib.mm_f4_gscale_set(0x1000, 3.0) == L.MM_OK and lib.mm_f4_gscale_get(0x1000) == 3.0
+    lib.mm_log_set_level(-1)
+    assert lib.mm_f4_gscale_set(None, 1.0) == L.MM_ERR_STATE
+    assert lib.mm_f4_gscale_set(0x10, 0.0) == L.MM_ERR_RANGE
+    assert lib.mm_f4_gscale_set(0x10, float("nan")) == L.MM_ERR_RANGE
+    lib.mm_log_set_level(1)
+    lib.mm_f4_gscale_clear()
+    assert lib.mm_f4_gscale_get(0x1000) == 1.0
+
+
+def test_engine_validates_descriptors(lib):
+    lib.mm_log_set_level(-1)
+    h = C.c_void_p()
+    assert lib.mm_lin_engine_create(C.byref(h), 2) == L.MM_OK
+    _, good = kcall()
+    _, bad_k = kcall(K=24)
+    _, bad_op = kcall(op=L.OP_GEMM_BF16)
+    _, null = kcall(b=None)
+    assert lib.mm_lin_engine_add(h, C.byref(bad_k)) == L.MM_ERR_SHAPE
+    assert lib.mm_lin_engine_add(h, C.byref(bad_op)) == L.MM_ERR_UNSUPPORTED
+    assert lib.mm_lin_engine_add(h, C.byref(null)) == L.MM_ERR_STATE
+    assert lib.mm_lin_engine_add(h, C.byref(good)) == L.MM_OK
+    assert lib.mm_lin_engine_add(h, C.byref(good)) == L.MM_OK
+    assert lib.mm_lin_engine_add(h, C.byref(good)) == L.MM_ERR_CAPACITY
+    assert lib.mm_lin_engine_n_ops(h) == 2
+    lib.mm_lin_engine_destroy(h)
+    lib.mm_log_set_level(1)
+
+
+def test_runtime_refuses_without_gpu(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    import mimfer_b200
+    with pytest.raises(RuntimeError):
+        mimfer_b200.Runtime(0)
+    assert lib.mm_cuda_stream_raw(0) is None and lib.mm_cuda_capturing() == 0

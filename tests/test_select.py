@@ -1,0 +1,63 @@
+"""Tile / variant selection (pure host C)."""
+import pytest
+
+import mimfer_b200 as mm
+from mimfer_b200 import V_ROWWARP, V_STREAM, V_UMMA
+
+WS = 64 << 20
+SMEM_MAX = 232448
+
+
+def test_decode_shapes_use_stream_and_fill_the_gpu(lib):
+    for M in (1, 2, 4, 8, 16):
+        for (K, N) in ((5120, 34816), (17408, 5120), (5120, 5120)):
+            p = mm.select_plan(M, K, N, ws_bytes=WS)
+            assert p.variant == V_STREAM
+            assert p.m_tiles * 8 >= M and p.m_tiles in (1, 2, 4)
+            assert p.k_steps == K // 256 and p.grid_x == -(-N // 256)
+            assert 100 <= p.grid_x * p.grid_y <= 148
+            assert p.smem_bytes <= SMEM_MAX and p.stages >= 2
+            if p.split_k > 1:
+                assert p.ws_needed <= WS and p.k_steps // p.split_k >= 4
+
+
+def test_no_workspace_means_no_split(lib):
+    p = mm.select_plan(16, 17408, 5120, ws_bytes=0)
+    assert p.variant == V_STREAM and p.split_k == 1 and p.ws_needed == 0
+
+
+def test_prefill_shapes_use_umma(lib):
+    for M in (512, 2048, 8192):
+        for (K, N) in ((5120, 34816), (17408, 5120), (5120, 6144), (5120, 1024), (6144, 5120)):
+            p = mm.select_plan(M, K, N)
+            assert p.variant == V_UMMA
+            assert p.tile_m in (128, 256) and p.tile_n in (128, 256)
+            assert p.grid_x == -(-N // p.tile_n) and p.grid_y == -(-M // p.tile_m)
+            assert p.smem_bytes <= SMEM_MAX and p.stages >= 2 and p.k_steps == K // 64
+    assert (mm.select_plan(8192, 5120, 34816).tile_m, mm.select_plan(8192, 5120, 34816).tile_n) == (256, 256)
+
+
+def test_odd_shapes_fall_to_rowwarp(lib):
+    assert mm.select_plan(3, 48, 7).variant == V_ROWWARP                 # K % 256 != 0
+    assert mm.select_plan(64, 528, 100).variant == V_ROWWARP
+    assert mm.select_plan(4, 512, 64, ptr_align=8).variant == V_ROWWARP   # TMA needs 16-byte bases
+    assert mm.select_plan(100, 512, 102).variant == V_ROWWARP         # UMMA stores need N % 8 == 0
+
+
+def test_deterministic(lib):
+    a = mm.select_plan(16, 5120, 34816, ws_bytes=WS).as_dict()
+    for _ in range(3):
+        assert mm.select_plan(16, 5120, 34816, ws_bytes=WS).as_dict() == a
+
+
+def test_errors(lib):
+    for bad in ((0, 256, 8), (1, 0, 8), (1, 256, 0), (1, 24, 8)):
+        with pytest.raises(mm.MimferError) as e:
+            mm.select_plan(*bad)
+        assert e.value.status == 4
+    with pytest.raises(mm.MimferError) as e:
+        mm.select_plan(64, 512, 64, variant=V_STREAM)            # M too large for the decode kernel
+    assert e.value.status == 7
+    with pytest.raises(mm.MimferError) as e:
+        mm.select_plan(4, 48, 64, variant=V_UMMA)
+    assert e.value.status == 7
