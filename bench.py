@@ -1,0 +1,454 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 linear op (OP_GEMM_F4) on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--case NAME]
+
+One "step" is one pass of the hot path over one batch of synthetic input:
+
+  N = 1   the decode sweep: M in {1,2,4,8,16} on gate+up (K=5120 -> N=34816) and
+          down (K=17408 -> N=5120); ten ops, each on its own copy of the weights
+          (750 MB per step, larger than L2), replayed as one captured graph.
+          value = packed weight bytes (payload + block scales) / time, GB/s.
+  N > 1   tensor-parallel linears: gate+up and the LM head (K=5120 -> N=151936),
+          split along N, at M=32, each followed by the all-gather of the output
+          slices (NCCL over NVLink).  value = whole-weight bytes / time, GB/s.
+
+The JSON line also carries the prefill GEMM sweep ("prefill": TFLOP/s against
+the dense bf16 tensor roofline), the 64-layer decode step ("decode_step"), the
+like-for-like tensor-parallel series at every N ("tp"), the end-to-end number
+through the host-buffer C-ABI call ("e2e"), the roofline of the dominant
+kernel and the reference CPU kernel timed on this host ("cpu_baseline").
+
+Synthetic data: weights N(0, 0.02) seed 0 packed by the library's packer,
+activations N(0, 1) seed 1 rounded to bf16.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "NVFP4 linear: decode GEMV weight GB/s vs HBM peak (prefill GEMM TFLOP/s in 'prefill')"
+SHAPES = {  # name: (K, N)
+    "gate_up": (5120, 34816), "down": (17408, 5120), "q": (5120, 6144), "k": (5120, 1024),
+    "v": (5120, 1024), "o": (6144, 5120), "lm_head": (5120, 151936),
+}
+DECODE_M = (1, 2, 4, 8, 16)
+PREFILL_M = (512, 2048, 8192)
+HBM_FALLBACK_GBS, TENSOR_FALLBACK_TFS = 6650.0, 1590.0
+
+
+def wbytes(K, N):
+    """packed payload + block scales"""
+    return N * K // 2 + N * K // 16
+
+
+def alg_bytes(M, K, N):
+    """algorithmic bytes of one op: W (payload + scales + global scale) + x + y"""
+    return wbytes(K, N) + 4 + 2 * M * K + 2 * M * N
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm": d["hbm_gbs"], "tensor_burst": d["bf16_tflops"],
+                "tensor_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "src": "measured"}
+    return {"hbm": HBM_FALLBACK_GBS, "tensor_burst": TENSOR_FALLBACK_TFS,
+            "tensor_sustained": 1400.0, "src": "fallback"}
+
+
+class Clocks:
+    """Samples nvidia-smi every 200 ms while a timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "power_w_max": None, "samples": 0}
+        if not self.path or not os.path.exists(self.path):
+            return out
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1])); pw.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        os.unlink(self.path)
+        if sm:
+            busy = [s for s, p in zip(sm, pw) if p > 0.5 * max(pw)] or sm
+            out.update(sm_mhz=statistics.median(busy), sm_max_mhz=max(mx), power_w_max=max(pw),
+                       reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# --------------------------------------------------------------------------- our arm
+class Bench:
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+        import mimfer_b200 as mm
+        self.torch, self.dist, self.mm, self.args = torch, dist, mm, args
+        self.rank = int(os.environ.get("RANK", 0))
+        self.world = int(os.environ.get("WORLD_SIZE", 1))
+        self.local = int(os.environ.get("LOCAL_RANK", 0))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the NVFP4 kernels have no CPU path")
+        torch.cuda.set_device(self.local)
+        if self.world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+        self.rt = mm.Runtime.get(self.local)
+        self.dev = self.rt.device
+        self._wcache = {}
+
+    # -- helpers ---------------------------------------------------------------
+    def weight(self, name, rows=None):
+        """Host weight (cached), optionally a row shard; device copies are made per use."""
+        K, N = SHAPES[name]
+        if name not in self._wcache:
+            self._wcache[name] = self.mm.make_weight(N, K, seed=0, std=0.02)
+        w = self._wcache[name]
+        return w if rows is None else w.rows(*rows)
+
+    def dev_weight(self, w):
+        return self.mm.NvFp4Weight(w.payload, w.scales, w.gs, w.N, w.K).to_device(self.dev)
+
+    def acts(self, M, K):
+        return self.rt.to_device_bf16(self.mm.make_activations(M, K, seed=1))
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def timed(self, fn, steps, warmup):
+        """ms per step: events on the compute stream, max over ranks."""
+        for _ in range(max(warmup, 3)):
+            fn()
+        self.rt.sync()
+        self.barrier()
+        self.rt.time_begin()
+        for _ in range(steps):
+            fn()
+        ms = self.rt.time_end()
+        self.barrier()
+        if self.world > 1:
+            t = self.torch.tensor([ms], device=self.dev)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            ms = float(t.item())
+        status = self.rt.device_status()
+        if status:
+            raise RuntimeError(f"device status 0x{status:x} after timed region")
+        return ms / steps
+
+    def engine(self, ops):
+        """ops: list of (x, w_dev, y). Captured into one graph."""
+        eng = self.mm.LinearEngine(self.rt, max_ops=len(ops) + 1)
+        for x, w, y in ops:
+            eng.add(x, w, y)
+        eng.launch()                  # direct dispatch once: errors surface per op
+        self.rt.sync()
+        eng.capture()
+        return eng
+
+    def empty(self, M, N):
+        return self.torch.empty((M, N), dtype=self.torch.bfloat16, device=self.dev)
+
+    # -- workloads -------------------------------------------------------------
+    def decode_sweep(self, steps, warmup, ms_list=DECODE_M, names=("gate_up", "down")):
+        ops, wb, ab = [], 0, 0
+        for name in names:
+            K, N = SHAPES[name]
+            hw = self.weight(name)
+            for M in ms_list:
+                ops.append((self.acts(M, K), self.dev_weight(hw), self.empty(M, N)))
+                wb += wbytes(K, N)
+                ab += alg_bytes(M, K, N)
+        eng = self.engine(ops)
+        ms = self.timed(eng.launch, steps, warmup)
+        res = {"ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "alg_gbs": ab / ms / 1e6,
+               "ops": len(ops), "weight_bytes": wb, "alg_bytes_per_launch": ab / len(ops),
+               "avg_launch_us": ms * 1e3 / len(ops)}
+        return res, ops, eng
+
+    def decode_e2e(self, ops, steps, warmup):
+        """Same ops through mm_f4_linear_host: pinned host x in, pinned host y out."""
+        torch = self.torch
+        host = []
+        for x, w, y in ops:
+            host.append((x.cpu().pin_memory(), x, w, y, torch.empty(y.shape, dtype=y.dtype).pin_memory()))
+        h2d = sum(h[0].numel() * 2 for h in host)
+        d2h = sum(h[4].numel() * 2 for h in host)
+
+        def step():
+            for xh, xd, w, yd, yh in host:
+                self.rt.linear_host(xh, xd, w, yd, yh)
+        for _ in range(max(warmup, 3)):
+            step()
+        self.barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        self.torch.cuda.synchronize()
+        sec = (time.perf_counter() - t0) / steps
+        wb = sum(wbytes(w.K, w.N) for _, w, _ in ops)
+        return {"value": wb / sec / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": sec * 1e3,
+                "timing": "host wall clock around synchronous calls"}
+
+    def prefill_sweep(self, steps, warmup, ms_list=PREFILL_M, names=("gate_up", "down", "q", "k", "v", "o")):
+        per, ops, flops = [], [], 0
+        for name in names:
+            K, N = SHAPES[name]
+            w = self.dev_weight(self.weight(name))
+            for M in ms_list:
+                x, y = self.acts(M, K), self.empty(M, N)
+                ops.append((x, w, y))
+                f = 2.0 * M * N * K
+                flops += f
+                ms = self.timed(lambda: self.rt.linear_async(x, w, y), max(2, steps // 4), 3)
+                per.append({"op": name, "M": M, "ms": round(ms, 4), "tflops": round(f / ms / 1e9, 1)})
+        eng = self.engine(ops)
+        ms = self.timed(eng.launch, max(2, steps // 4), 3)
+        eng.close()
+        return {"ms_per_step": ms, "tflops": flops / ms / 1e9, "ops": len(ops), "per_op": per}
+
+    def decode_step_64(self, steps, warmup, layers=64, M=16):
+        names = ("q", "k", "v", "o", "gate_up", "down")
+        base = {n: self.weight(n) for n in names}
+        ops, wb = [], 0
+        for layer in range(layers):
+            for n in names:
+                K, N = SHAPES[n]
+                ops.append((self.acts(M, K) if layer == 0 else ops[names.index(n)][0],
+                            self.dev_weight(base[n]), self.empty(M, N) if layer == 0 else ops[names.index(n)][2]))
+                wb += wbytes(K, N)
+        eng = self.engine(ops)
+        ms = self.timed(eng.launch, max(2, steps // 2), 3)
+        eng.close()
+        return {"layers": layers, "M": M, "ops": len(ops), "weight_bytes": wb,
+                "sum_linear_ms_per_step": ms, "weight_gbs": wb / ms / 1e6}
+
+    def tp_series(self, steps, warmup):
+        """config 5: gate+up and LM head, sharded along N over all ranks, M=32 and M=8192."""
+        from mimfer_b200.tp import TpLinear
+        out = {"world": self.world}
+        lins = {n: TpLinear(self.weight(n), self.rank, self.world, rt=self.rt) for n in ("gate_up", "lm_head")}
+        for tag, M, st in (("decode_m32", 32, steps), ("prefill_m8192", 8192, max(2, steps // 4))):
+            xs = {n: self.acts(M, SHAPES[n][0]) for n in lins}
+
+            def step():
+                for n, lin in lins.items():
+                    lin.forward(xs[n])
+            ms = self.timed(step, st, warmup)
+            wb = sum(wbytes(*SHAPES[n]) for n in lins)
+            fl = sum(2.0 * M * SHAPES[n][0] * SHAPES[n][1] for n in lins)
+            out[tag] = {"ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "tflops": fl / ms / 1e9}
+            for lin in lins.values():
+                lin._bufs.clear()
+            self.torch.cuda.empty_cache()
+        return out
+
+
+def cpu_baseline(threads=None, target_s=12.0):
+    """The reference CPU kernel (oracle/_ref, else the oracle port) on this
+    host's cores, on a bounded sample of the decode sweep: the first R rows of
+    gate+up and of down at every M of the sweep, R sized by a short probe so
+    the sample takes about target_s seconds.  Same metric as the GPU arm:
+    packed weight bytes processed / time."""
+    import mimfer_b200 as mm
+    from oracle.pyoracle import Oracle, Reference, host_threads
+    threads = threads or host_threads()
+    ref = Reference()
+    kind = "reference" if ref.available else "port"
+    orc = None if ref.available else Oracle()
+
+    def run(x, w):
+        t0 = time.perf_counter()
+        if ref.available:
+            rc, _ = ref.gemm_f4(x, w.payload, w.scales, threads=threads)
+            assert rc == 0
+        else:
+            orc.gemm_f4(x, w.payload, w.scales, 1.0, threads=threads)
+        return time.perf_counter() - t0
+
+    def sweep(rows):
+        dt, nbytes = 0.0, 0
+        for name in ("gate_up", "down"):
+            K, N = SHAPES[name]
+            r = min(rows, N)
+            w = mm.make_weight(r, K, seed=0)
+            for M in DECODE_M:
+                dt += run(mm.make_activations(M, K, seed=1), w)
+                nbytes += wbytes(K, r)
+        return dt, nbytes
+
+    probe_rows = 16 * threads
+    dt, _ = sweep(probe_rows)
+    rows = int(min(5120, max(probe_rows, probe_rows * target_s / max(dt, 1e-6))))
+    dt, nbytes = sweep(rows)
+    return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
+            "sample": f"decode sweep M in {{1,2,4,8,16}} on the first {rows} rows of gate+up and of down, "
+                      f"{dt:.1f} s of CPU time"}
+
+
+def run_b200(args):
+    b = Bench(args)
+    pk = peaks()
+    steps, warmup = args.steps, max(args.warmup, 3)
+    line = {"metric": METRIC, "unit": "GB/s", "n_gpus": b.world, "steps": steps, "warmup": warmup,
+            "higher_is_better": True, "vs_baseline": None, "dtype": "bf16 x nvfp4 -> f32 accumulate",
+            "data": "synthetic"}
+    with Clocks(b.local) as clk:
+        if args.case != "default":
+            res = run_case(b, args.case, steps, warmup)
+            if b.rank == 0:
+                print(json.dumps({"case": args.case, **res}))
+            return
+        if b.world == 1:
+            dec, ops, eng = b.decode_sweep(steps, warmup)
+            line.update(value=dec["weight_gbs"], ms_per_step=dec["ms_per_step"], scaling="weak",
+                        gpu_launches=dec["ops"] * steps,
+                        config={"workload": "decode GEMV sweep M in {1,2,4,8,16} x {gate+up 5120->34816, "
+                                            "down 17408->5120}, 10 ops per step, one CUDA graph",
+                                "l2": "every op reads its own weight copy: 750 MB per step, larger than L2",
+                                "quant": "NVFP4 e2m1 + e4m3/16 + fp32 global scale", "peaks": pk["src"]})
+            line["roofline"] = {"bound": "hbm", "kernel": "f4_stream_kernel",
+                                "achieved": dec["alg_gbs"], "peak": pk["hbm"], "unit": "GB/s",
+                                "frac": dec["alg_gbs"] / pk["hbm"], "of": pk["src"],
+                                "alg_bytes_per_launch": dec["alg_bytes_per_launch"],
+                                "avg_launch_us": dec["avg_launch_us"], "traffic": None}
+            line["e2e"] = b.decode_e2e(ops, max(2, steps // 2), warmup)
+            eng.close()
+            del ops
+            b.torch.cuda.empty_cache()
+            pre = b.prefill_sweep(steps, warmup)
+            pre["roofline"] = {"bound": "tensor", "kernel": "f4_umma_kernel", "achieved": pre["tflops"],
+                               "peak": pk["tensor_sustained"], "peak_burst": pk["tensor_burst"],
+                               "unit": "TFLOP/s", "frac": pre["tflops"] / pk["tensor_sustained"],
+                               "frac_of_burst": pre["tflops"] / pk["tensor_burst"], "of": pk["src"]}
+            line["prefill"] = pre
+            b.torch.cuda.empty_cache()
+            line["decode_step"] = b.decode_step_64(steps, warmup)
+            b.torch.cuda.empty_cache()
+        tp = b.tp_series(steps, warmup)
+        line["tp"] = tp
+        if b.world > 1:
+            d = tp["decode_m32"]
+            line.update(value=d["weight_gbs"], ms_per_step=d["ms_per_step"], scaling="strong",
+                        gpu_launches=2 * steps,
+                        config={"workload": f"tensor-parallel gate+up and LM head (N=151936) split along N "
+                                            f"over {b.world} GPUs at M=32, NCCL all-gather of the output slices",
+                                "l2": "537 MB of weights per step across ranks", "peaks": pk["src"]})
+            line["roofline"] = {"bound": "hbm", "kernel": "f4_stream_kernel", "achieved": d["weight_gbs"],
+                                "peak": pk["hbm"] * b.world, "unit": "GB/s",
+                                "frac": d["weight_gbs"] / (pk["hbm"] * b.world), "of": pk["src"], "traffic": None}
+            line["prefill"] = {"tflops": tp["prefill_m8192"]["tflops"],
+                               "ms_per_step": tp["prefill_m8192"]["ms_per_step"]}
+            line["e2e"] = {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                           "note": "end-to-end host-buffer timing is reported at n_gpus=1"}
+    line["clocks"] = clk.summary()
+    if b.rank == 0:
+        if b.world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(line))
+    if b.world > 1:
+        b.dist.destroy_process_group()
+
+
+def run_case(b, case, steps, warmup):
+    """Single small cases, used for profiling one kernel at a time."""
+    if case == "decode":           # gate+up at M=1 and M=16, two weight copies each
+        res, _, eng = b.decode_sweep(steps, warmup, ms_list=(1, 16), names=("gate_up",))
+        eng.close()
+        return res
+    if case == "decode_down":
+        res, _, eng = b.decode_sweep(steps, warmup, ms_list=(1, 16), names=("down",))
+        eng.close()
+        return res
+    if case == "prefill":          # one 2048 x 5120 x 34816 GEMM
+        return b.prefill_sweep(steps, warmup, ms_list=(2048,), names=("gate_up",))
+    if case == "prefill_small":
+        return b.prefill_sweep(steps, warmup, ms_list=(512,), names=("q",))
+    raise SystemExit(f"unknown case {case}")
+
+
+# --------------------------------------------------------------------------- reference arm
+def run_reference(args):
+    """The reference's own CPU implementation of the path on this host's cores."""
+    rank = int(os.environ.get("RANK", 0))
+    if rank != 0:
+        return
+    base = cpu_baseline(target_s=max(5.0, min(20.0, 4.0 * args.steps)))
+    t0 = time.perf_counter()
+    vals = [base["value"]]
+    for _ in range(max(0, min(args.steps, 3) - 1)):
+        vals.append(cpu_baseline(target_s=5.0)["value"])
+    v = statistics.median(vals)
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": len(vals), "warmup": 1, "ms_per_step": (time.perf_counter() - t0) * 1e3 / max(1, len(vals) - 1)
+            if len(vals) > 1 else None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 x nvfp4 -> f32 accumulate", "data": "synthetic",
+            "config": {"workload": "reference CPU kx_op_gemm_f4 on a bounded sample of the decode workload: "
+                                   + base["sample"]},
+            "cpu_baseline": {**base, "value": v},
+            "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--case", default="default")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -165,10 +165,17 @@ mm_status mm_f4_device_status(unsigned *flags_out);
 unsigned long long mm_f4_launch_count(int reset);
 
 /* Device decode probe: for every (nibble n, scale byte s) writes the fp32
- * bits of the dequantised weight as each kernel family computes it, to two
- * device arrays of 4096 uint32 (index s*16+n): the tensor-core operand path
- * (bf16 operand, rescaled) and the row-warp fp32 path. */
-mm_status mm_f4_decode_probe(uint32_t *out_mma_dev, uint32_t *out_f32_dev);
+ * bits of the dequantised weight as each kernel family computes it, to three
+ * device arrays of 4096 uint32 (index s*16+n): the bf16 tensor-core operand
+ * form (rescaled), the row-warp fp32 form, and the fp16 tensor-core operand
+ * form. */
+mm_status mm_f4_decode_probe(uint32_t *out_bf16_dev, uint32_t *out_f32_dev,
+                             uint32_t *out_f16_dev);
+
+/* Tuning knobs for experiments and tests; defaults are what the benchmark
+ * uses.  No key is defined at present.  Returns the previous value, or -1 for
+ * an unknown key. */
+int mm_f4_tune(int key, int value);
 
 /* ---- timing on the compute stream (events with timing enabled) ----------- */
 mm_status mm_time_begin(void);

@@ -83,6 +83,12 @@ void mm_f4_gscale_clear(void)
 
 void mm_f4_force_variant(int variant) { G.forced_variant = variant; }
 
+int mm_f4_tune(int key, int value)
+{
+    (void)key; (void)value;
+    return -1;
+}
+
 unsigned long long mm_f4_launch_count(int reset)
 {
     unsigned long long n = G.launches;
@@ -318,12 +324,12 @@ mm_status mm_f4_linear_host(const void *x_host, void *x_dev, const void *payload
     return finish_op();
 }
 
-mm_status mm_f4_decode_probe(uint32_t *out_mma_dev, uint32_t *out_f32_dev)
+mm_status mm_f4_decode_probe(uint32_t *out_mma_dev, uint32_t *out_f32_dev, uint32_t *out_f16_dev)
 {
-    MM_REQUIRE(out_mma_dev && out_f32_dev, MM_ERR_STATE);
+    MM_REQUIRE(out_mma_dev && out_f32_dev && out_f16_dev, MM_ERR_STATE);
     MM_CHECK(ensure_ready());
     cudaStream_t cs = (cudaStream_t)mm_cuda_stream_raw(MM_ST_COMPUTE);
-    CK((cudaError_t)mmb_launch_decode_probe(out_mma_dev, out_f32_dev, cs));
+    CK((cudaError_t)mmb_launch_decode_probe(out_mma_dev, out_f32_dev, out_f16_dev, cs));
     G.launches++;
     CK(cudaStreamSynchronize(cs));
     return MM_OK;

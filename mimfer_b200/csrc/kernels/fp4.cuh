@@ -17,6 +17,7 @@
 #pragma once
 #include <cstdint>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 namespace mmb {
 
@@ -84,6 +85,43 @@ __device__ __forceinline__ uint4 unpack8_natural(uint32_t w, uint32_t c)
     r.y = prmt(q[2], q[3], 0x5410u);
     r.z = prmt(q[0], q[1], 0x7632u);
     r.w = prmt(q[2], q[3], 0x7632u);
+    return r;
+}
+
+/* ---- fp16 operand form -------------------------------------------------
+ * cvt.rn.f16x2.e2m1x2 turns one payload byte (two nibbles) into two fp16
+ * values, low nibble in the low half, i.e. already in column order.  e4m3
+ * scales and the e2m1 x e4m3 products (at most 6 significant bits, magnitude
+ * 2^-10 .. 2688) are exact fp16 normals, so one packed fp16 multiply by the
+ * scale entry gives the dequantised weight exactly, with no exponent offset.
+ * Not used by the MMA kernels: tcgen05 kind::f16 wants both operands in one
+ * format and the activations are bf16.  Kept, with its probe, as the verified
+ * building block for an fp16-activation path. */
+__device__ __forceinline__ uint32_t scale_lut_entry_f16(uint32_t b)
+{
+    const __half h = __float2half_rn(e4m3_f32(b));                 /* exact */
+    const uint32_t u = *reinterpret_cast<const uint16_t *>(&h);
+    return u | (u << 16);
+}
+
+__device__ __forceinline__ uint4 unpack8_natural_f16(uint32_t w, uint32_t c)
+{
+    uint4 r;
+    asm("{\n\t"
+        ".reg .b8 b0, b1, b2, b3;\n\t"
+        ".reg .b32 t0, t1, t2, t3;\n\t"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 t0, b0;\n\t"
+        "cvt.rn.f16x2.e2m1x2 t1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 t2, b2;\n\t"
+        "cvt.rn.f16x2.e2m1x2 t3, b3;\n\t"
+        "mul.rn.f16x2 %0, t0, %5;\n\t"
+        "mul.rn.f16x2 %1, t1, %5;\n\t"
+        "mul.rn.f16x2 %2, t2, %5;\n\t"
+        "mul.rn.f16x2 %3, t3, %5;\n\t"
+        "}"
+        : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+        : "r"(w), "r"(c));
     return r;
 }
 

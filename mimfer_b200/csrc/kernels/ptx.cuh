@@ -1,7 +1,7 @@
 /*
  * Thin inline-PTX wrappers for sm_100a: mbarrier, TMA (cp.async.bulk.tensor,
  * never with cluster multicast), tcgen05 (alloc, mma, commit, ld) and the
- * warp-level bf16 MMA.  Every wait is bounded: after about two seconds of
+ * warp-level bf16 MMA.  Every wait is bounded: after about one second of
  * polling it sets MMB_DEV_TIMEOUT in the device status word (passed to the kernel) and returns, so a
  * lost signal ends the kernel with an error instead of hanging the GPU.
  */
@@ -57,18 +57,24 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
-/* Bounded wait.  Returns false (and raises the status bit) on timeout. */
+/* Bounded wait.  Returns false on timeout, after raising MMB_DEV_TIMEOUT in the
+ * status word; once that bit is up every later wait in the grid gives up at
+ * once, so a broken hand-off costs about one second in total, not per wait. */
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned *status)
 {
     if (mbar_try(bar, parity))
         return true;
-    uint64_t t0 = globaltimer_ns();
+    const uint64_t t0 = globaltimer_ns();
     for (uint32_t spin = 1;; spin++) {
         if (mbar_try(bar, parity))
             return true;
-        if ((spin & 63u) == 0 && globaltimer_ns() - t0 > 2000000000ull) {
-            atomicOr(status, MMB_DEV_TIMEOUT);
-            return false;
+        if ((spin & 31u) == 0) {
+            if (*reinterpret_cast<volatile unsigned *>(status) & MMB_DEV_TIMEOUT)
+                return false;
+            if (globaltimer_ns() - t0 > 1000000000ull) {
+                atomicOr(status, MMB_DEV_TIMEOUT);
+                return false;
+            }
         }
     }
 }
@@ -200,7 +206,9 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr)
     d |= static_cast<uint64_t>(2) << 61;                             /* SWIZZLE_128B    */
     return d;
 }
-/* Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major. */
+/* Instruction descriptor for kind::f16: bf16 x bf16 -> fp32, both operands
+ * K-major.  (Both operands must have the same format: fp16 weights against
+ * bf16 activations raise an illegal-instruction fault on B200.) */
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(uint32_t m, uint32_t n)
 {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);

@@ -71,8 +71,9 @@ f4_rowwarp_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ pa
 }
 
 /* index = s * 16 + n.  out_mma: the bf16 operand form, every one of the eight
- * nibble positions of a word must agree, else 0xdeadbeef is written. */
-__global__ void f4_decode_probe_kernel(uint32_t *out_mma, uint32_t *out_f32)
+ * nibble positions of a word must agree, else 0xdeadbeef is written.
+ * out_f16: the fp16 operand form, same rule plus the column order check. */
+__global__ void f4_decode_probe_kernel(uint32_t *out_mma, uint32_t *out_f32, uint32_t *out_f16)
 {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= 4096u)
@@ -92,6 +93,20 @@ __global__ void f4_decode_probe_kernel(uint32_t *out_mma, uint32_t *out_f32)
     same = same && nat.x == q[0] && nat.y == q[0] && nat.z == q[0] && nat.w == q[0];
     const float v = __uint_as_float(first << 16) * 256.0f;
     out_mma[i] = same ? __float_as_uint(v) : 0xdeadbeefu;
+
+    /* fp16 operand form: nibble n in all eight positions, then one position at a time */
+    const uint4 hf = unpack8_natural_f16(n * 0x11111111u, scale_lut_entry_f16(s));
+    const uint32_t h0 = hf.x & 0xffffu;
+    bool same16 = hf.x == (h0 | (h0 << 16)) && hf.y == hf.x && hf.z == hf.x && hf.w == hf.x;
+#pragma unroll
+    for (int pos = 0; pos < 8; pos++) {          /* column order: nibble `pos` lands in slot `pos` */
+        const uint4 one = unpack8_natural_f16(n << (4 * pos), scale_lut_entry_f16(s));
+        const uint32_t regs[4] = { one.x, one.y, one.z, one.w };
+        const uint32_t got = (regs[pos >> 1] >> (16 * (pos & 1))) & 0xffffu;
+        same16 = same16 && got == h0;
+    }
+    const __half hv = *reinterpret_cast<const __half *>(&h0);
+    out_f16[i] = same16 ? __float_as_uint(__half2float(hv)) : 0xdeadbeefu;
 }
 
 } // namespace mmb
@@ -106,9 +121,11 @@ extern "C" int mmb_launch_rowwarp(const mmb_args *a, void *stream)
     return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int mmb_launch_decode_probe(uint32_t *out_mma, uint32_t *out_f32, void *stream)
+extern "C" int mmb_launch_decode_probe(uint32_t *out_mma, uint32_t *out_f32, uint32_t *out_f16,
+                                       void *stream)
 {
-    mmb::f4_decode_probe_kernel<<<16, 256, 0, static_cast<cudaStream_t>(stream)>>>(out_mma, out_f32);
+    mmb::f4_decode_probe_kernel<<<16, 256, 0, static_cast<cudaStream_t>(stream)>>>(out_mma, out_f32,
+                                                                                  out_f16);
     return static_cast<int>(cudaGetLastError());
 }
 

@@ -54,6 +54,7 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
     const uint32_t lut = base + p.stages * STAGE_B;
     const uint32_t bar_full = lut + 1024u;
     const uint32_t bar_empty = bar_full + 8u * p.stages;
+    const uint32_t last_flag = bar_empty + 8u * p.stages;    /* split-K: "this CTA reduces" */
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t row0 = blockIdx.x * MMB_ST_ROWS;
@@ -196,7 +197,6 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
     }
 
     /* split-K: publish this slice, the last CTA of the row block reduces */
-    __shared__ uint32_t s_last;
     float *mine = p.partial + static_cast<size_t>(blockIdx.y) * MPAD * p.N;
 #pragma unroll
     for (int rt = 0; rt < 2; rt++)
@@ -213,10 +213,10 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
     asm volatile("bar.sync 1, 256;" ::: "memory");
     if (tid == 0) {
         const unsigned ticket = atomicAdd(p.counters + blockIdx.x, 1u);
-        s_last = (ticket == p.split_k - 1u) ? 1u : 0u;
+        sts32(last_flag, (ticket == p.split_k - 1u) ? 1u : 0u);
     }
     asm volatile("bar.sync 1, 256;" ::: "memory");
-    if (!s_last)
+    if (!lds32(last_flag))
         return;
     __threadfence();
 #pragma unroll

@@ -192,11 +192,13 @@ class Runtime:
         return ms.value
 
     def decode_probe(self):
-        out = self.torch.zeros((2, 4096), dtype=self.torch.int32, device=self.device)
+        """(bf16 operand form, fp32 form, fp16 operand form), each 4096 fp32 bit patterns."""
+        out = self.torch.zeros((3, 4096), dtype=self.torch.int32, device=self.device)
         self.torch.cuda.synchronize()
-        L.check(self.lib.mm_f4_decode_probe(out[0].data_ptr(), out[1].data_ptr()), "mm_f4_decode_probe")
+        L.check(self.lib.mm_f4_decode_probe(out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr()),
+                "mm_f4_decode_probe")
         a = out.cpu().numpy().view(np.uint32)
-        return a[0], a[1]
+        return a[0], a[1], a[2]
 
 
 class LinearEngine:

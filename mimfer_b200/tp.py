@@ -40,8 +40,11 @@ class TpLinear:
         if M not in self._bufs:
             ns = self.N // self.world
             kw = dict(dtype=like.dtype, device=like.device)
-            self._bufs[M] = (torch.empty((M, ns), **kw), torch.empty((self.world, M, ns), **kw),
-                             torch.empty((M, self.N), **kw))
+            if self.world == 1:
+                self._bufs[M] = (torch.empty((M, ns), **kw), None, None)
+            else:
+                self._bufs[M] = (torch.empty((M, ns), **kw), torch.empty((self.world, M, ns), **kw),
+                                 torch.empty((M, self.N), **kw))
         return self._bufs[M]
 
     def forward(self, x):
@@ -49,6 +52,13 @@ class TpLinear:
         On CUDA everything is enqueued on the runtime's compute stream."""
         M = x.shape[0]
         y_local, gathered, y = self._buffers(M, x)
+        if self.world == 1:                       # nothing to exchange
+            if self.rt is not None and x.is_cuda:
+                with torch.cuda.stream(self.rt.torch_stream()):
+                    self.local_op(x, self.shard, y_local)
+            else:
+                self.local_op(x, self.shard, y_local)
+            return y_local
         if self.rt is not None and x.is_cuda:
             with torch.cuda.stream(self.rt.torch_stream()):
                 self.local_op(x, self.shard, y_local)
@@ -59,9 +69,6 @@ class TpLinear:
         return y
 
     def _gather(self, y_local, gathered, y, M):
-        if self.world == 1:
-            y.copy_(y_local)
-            return
         dist.all_gather_into_tensor(gathered.view(-1), y_local.view(-1), group=self.group)
         if M == 1:
             y.view(-1).copy_(gathered.view(-1))

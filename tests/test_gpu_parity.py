@@ -1,0 +1,252 @@
+"""GPU parity: every kernel family against the CPU oracle, through the C-ABI.
+
+Bar: nibble/scale decode bit-exact; outputs within per-row relative L2 <= 2^-8
+of the oracle after bf16 rounding (conftest.REL_L2_TOL)."""
+import ctypes as C
+import glob
+import os
+
+import numpy as np
+import pytest
+
+import mimfer_b200 as mm
+from mimfer_b200 import V_ROWWARP, V_STREAM, V_UMMA, _lib as L
+from conftest import GOLDEN, REL_L2_TOL, row_rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+def run(rt, x_bits, w, variant=None):
+    if w.dev_payload is None:
+        w.to_device(rt.device)
+    x = rt.to_device_bf16(x_bits)
+    y = rt.gemm_f4(x, w, variant=variant)
+    assert rt.device_status() == 0
+    return rt.from_device_bf16(y)
+
+
+def check(rt, oracle, M, K, N, variant, seed=0, gs=None, sample_rows=None):
+    w = mm.make_weight(N, K, seed=seed)
+    if gs is not None:
+        w.gs = gs
+    x = mm.make_activations(M, K, seed=seed + 1)
+    y = run(rt, x, w, variant)
+    rows = None if sample_rows is None else sorted(set(sample_rows))
+    want = oracle.gemm_f4(x, w.payload, w.scales, w.gs, rows=rows)
+    got = y if rows is None else y[rows]
+    err = row_rel_l2(got, want)
+    assert err <= REL_L2_TOL, f"M={M} K={K} N={N} variant={variant}: rel L2 {err}"
+    return y
+
+
+# ---------------------------------------------------------------- decode
+def test_decode_is_bit_exact(rt, oracle):
+    bf16_form, f32, f16_form = rt.decode_probe()
+    table = oracle.decode_table()
+    assert not (bf16_form == 0xDEADBEEF).any(), "nibble positions of a word disagree"
+    assert not (f16_form == 0xDEADBEEF).any(), "fp16 form: nibble positions or column order disagree"
+    assert np.array_equal(f32, table)
+    assert np.array_equal(bf16_form, table)
+    assert np.array_equal(f16_form, table)
+
+
+def test_decode_matches_reference_fixture(rt):
+    gold = np.load(os.path.join(GOLDEN, "decode_products.npz"))
+    ref = (gold["low_nibble_col0"].astype(np.uint32) << 16).view(np.float32)
+    for form in rt.decode_probe():
+        assert np.array_equal(form.view(np.float32), ref)
+
+
+# ---------------------------------------------------------------- row-warp
+@pytest.mark.parametrize("M,K,N", [(1, 16, 1), (1, 48, 7), (3, 528, 33), (5, 1024, 96), (17, 272, 100),
+                                   (2, 5120, 64), (40, 256, 20)])
+def test_rowwarp(rt, oracle, M, K, N):
+    check(rt, oracle, M, K, N, V_ROWWARP, seed=M + N)
+
+
+# ---------------------------------------------------------------- stream (decode)
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("K,N", [(256, 256), (512, 40), (1024, 600), (5120, 1024)])
+def test_stream_shapes(rt, oracle, M, K, N):
+    check(rt, oracle, M, K, N, V_STREAM, seed=K + N + M)
+
+
+def test_stream_config1(rt, oracle):
+    check(rt, oracle, 1, 5120, 5120, None)
+
+
+@pytest.mark.parametrize("M", [1, 16])
+def test_stream_long_k_split(rt, oracle, M):
+    plan = mm.select_plan(M, 17408, 5120, ws_bytes=rt.lib.mm_f4_workspace_bytes())
+    assert plan.variant == V_STREAM and plan.split_k > 1
+    check(rt, oracle, M, 17408, 5120, None, seed=5)
+
+
+def test_stream_without_workspace(rt, oracle):
+    ws = rt.workspace
+    rt.sync()
+    L.check(rt.lib.mm_f4_workspace_set(None, 0), "clear workspace")
+    try:
+        check(rt, oracle, 4, 4096, 512, V_STREAM, seed=9)
+    finally:
+        L.check(rt.lib.mm_f4_workspace_set(ws.data_ptr(), ws.numel()), "restore workspace")
+
+
+def test_stream_is_deterministic(rt, oracle):
+    w = mm.make_weight(5120, 17408, seed=2).to_device(rt.device)
+    x = mm.make_activations(8, 17408, seed=3)
+    a = run(rt, x, w)
+    for _ in range(3):
+        assert np.array_equal(run(rt, x, w), a)
+
+
+# ---------------------------------------------------------------- umma (prefill)
+@pytest.mark.parametrize("M,K,N", [(128, 256, 128), (256, 256, 256), (33, 512, 136), (300, 1024, 520),
+                                   (512, 2048, 1024), (1000, 768, 264)])
+def test_umma_shapes(rt, oracle, M, K, N):
+    check(rt, oracle, M, K, N, V_UMMA, seed=M + N)
+
+
+@pytest.mark.parametrize("tile", [(256, 256), (256, 128), (128, 256), (128, 128)])
+def test_umma_every_tile_shape(rt, oracle, tile):
+    # shapes chosen so the selector lands on each tile
+    shapes = {(256, 256): (8192, 256, 8192), (256, 128): (512, 512, 5120),
+              (128, 256): (128, 512, 37888), (128, 128): (128, 256, 128)}
+    M, K, N = shapes[tile]
+    plan = mm.select_plan(M, K, N)
+    assert (plan.tile_m, plan.tile_n) == tile, plan.as_dict()
+    rows = [0, 1, 127, 128, M // 2, M - 1] if M > 512 else None
+    check(rt, oracle, M, K, N, V_UMMA, seed=1, sample_rows=rows)
+
+
+def test_umma_prefill_gate_up_sampled(rt, oracle):
+    M, K, N = 2048, 5120, 34816
+    check(rt, oracle, M, K, N, None, seed=0, sample_rows=[0, 255, 256, 1023, 2047])
+
+
+def test_umma_is_deterministic(rt, oracle):
+    w = mm.make_weight(1024, 1024, seed=2).to_device(rt.device)
+    x = mm.make_activations(512, 1024, seed=3)
+    a = run(rt, x, w)
+    assert np.array_equal(run(rt, x, w), a)
+
+
+# ---------------------------------------------------------------- fixtures, edge cases
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLDEN, "seeded_*.npz"))),
+                         ids=lambda p: os.path.basename(p)[:-4])
+def test_seeded_reference_fixtures(rt, path):
+    g = np.load(path)
+    M, K, N = (int(v) for v in os.path.basename(path)[7:-4].split("x"))
+    w = mm.make_weight(N, K, seed=0)
+    w.gs = 1.0                                   # the reference has no global scale
+    x = mm.make_activations(M, K, seed=1)
+    assert row_rel_l2(run(rt, x, w), g["y"]) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("variant", [V_ROWWARP, V_STREAM])
+def test_random_bytes_fixture(rt, variant):
+    """All 256 scale codes: NaN codes decode to 0, negative scales keep their sign."""
+    g = np.load(os.path.join(GOLDEN, "random_bytes.npz"))
+    M, K = g["x"].shape
+    w = mm.NvFp4Weight(g["payload"], g["scales"], 1.0, g["payload"].shape[0], K)
+    assert row_rel_l2(run(rt, g["x"], w, variant), g["y"]) <= REL_L2_TOL
+
+
+def test_random_bytes_umma(rt, oracle):
+    rng = np.random.Generator(np.random.PCG64(5))
+    M, K, N = 130, 512, 264
+    w = mm.NvFp4Weight(rng.integers(0, 256, (N, K // 2), dtype=np.uint8),
+                       rng.integers(0, 256, (N, K // 16), dtype=np.uint8), 1.0, N, K)
+    x = mm.make_activations(M, K, seed=8)
+    want = oracle.gemm_f4(x, w.payload, w.scales, 1.0)
+    assert row_rel_l2(run(rt, x, w, V_UMMA), want) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("gs", [1.0, 0.25, 3.0517578125e-05, 4.0530e-05, 7.0])
+@pytest.mark.parametrize("variant,M", [(V_ROWWARP, 2), (V_STREAM, 2), (V_UMMA, 128)])
+def test_global_scale(rt, oracle, gs, variant, M):
+    check(rt, oracle, M, 512, 256, variant, seed=4, gs=gs)
+
+
+def test_output_canaries(rt, oracle):
+    """Nothing is written outside y[M][N]."""
+    torch = rt.torch
+    for (M, K, N, v) in [(3, 512, 40, V_STREAM), (5, 272, 33, V_ROWWARP), (130, 512, 264, V_UMMA)]:
+        w = mm.make_weight(N, K, seed=1).to_device(rt.device)
+        x = rt.to_device_bf16(mm.make_activations(M, K, seed=2))
+        pad = 4096
+        buf = torch.full((pad + M * N + pad,), 0x7B7B, dtype=torch.int16, device=rt.device)
+        y = buf[pad:pad + M * N].view(torch.bfloat16).view(M, N)
+        rt.gemm_f4(x, w, y, variant=v)
+        assert (buf[:pad] == 0x7B7B).all() and (buf[pad + M * N:] == 0x7B7B).all()
+        want = oracle.gemm_f4(mm.make_activations(M, K, seed=2), w.payload, w.scales, w.gs)
+        assert row_rel_l2(rt.from_device_bf16(y), want) <= REL_L2_TOL
+
+
+def test_error_statuses_on_device(rt):
+    rt.lib.mm_log_set_level(-1)
+    w = mm.make_weight(8, 256, seed=1).to_device(rt.device)
+    x = rt.to_device_bf16(mm.make_activations(1, 256, seed=2))
+    y = rt.torch.empty((1, 8), dtype=rt.torch.bfloat16, device=rt.device)
+    d = rt.op_desc(x, w, y)
+    d.n1 = 24
+    kc = L.MmKcall(C.pointer(d), 1, None)
+    assert rt.lib.mm_kx_invoke(C.byref(kc)) == L.MM_ERR_SHAPE
+    d.n1, d.b = 256, None
+    assert rt.lib.mm_kx_invoke(C.byref(kc)) == L.MM_ERR_STATE
+    rt.lib.mm_log_set_level(1)
+
+
+def test_qkv_routes_to_fp4_kernel(rt, oracle):
+    w = mm.make_weight(512, 512, seed=1).to_device(rt.device)
+    xb = mm.make_activations(2, 512, seed=2)
+    x = rt.to_device_bf16(xb)
+    y = rt.torch.empty((2, 512), dtype=rt.torch.bfloat16, device=rt.device)
+    d = rt.op_desc(x, w, y, op=L.OP_QKV, note=b"qkv")
+    kc = L.MmKcall(C.pointer(d), 1, None)
+    assert rt.lib.mm_kx_invoke(C.byref(kc)) == L.MM_OK
+    assert row_rel_l2(rt.from_device_bf16(y), oracle.gemm_f4(xb, w.payload, w.scales, w.gs)) <= REL_L2_TOL
+
+
+# ---------------------------------------------------------------- engine / graph
+def test_engine_graph_equals_direct_dispatch(rt, oracle):
+    torch = rt.torch
+    shapes = [(5120, 6144), (5120, 1024), (6144, 5120), (5120, 2048), (2048, 5120)]
+    M = 4
+    ws = [mm.make_weight(N, K, seed=i).to_device(rt.device) for i, (K, N) in enumerate(shapes)]
+    xs = [rt.to_device_bf16(mm.make_activations(M, K, seed=50 + i)) for i, (K, N) in enumerate(shapes)]
+    ys = [torch.zeros((M, N), dtype=torch.bfloat16, device=rt.device) for (K, N) in shapes]
+    eng = mm.LinearEngine(rt)
+    for x, w, y in zip(xs, ws, ys):
+        eng.add(x, w, y)
+    eng.launch()                                           # direct dispatch
+    rt.sync()
+    direct = [rt.from_device_bf16(y).copy() for y in ys]
+    for y in ys:
+        y.zero_()
+    torch.cuda.synchronize()
+    eng.capture()
+    for _ in range(2):
+        eng.launch()
+    rt.sync()
+    assert rt.device_status() == 0
+    for i, (y, d) in enumerate(zip(ys, direct)):
+        assert np.array_equal(rt.from_device_bf16(y), d)
+        want = oracle.gemm_f4(mm.make_activations(M, shapes[i][0], seed=50 + i), ws[i].payload,
+                              ws[i].scales, ws[i].gs)
+        assert row_rel_l2(d, want) <= REL_L2_TOL
+    eng.close()
+
+
+def test_host_buffer_call(rt, oracle):
+    torch = rt.torch
+    M, K, N = 4, 1024, 512
+    w = mm.make_weight(N, K, seed=3).to_device(rt.device)
+    xb = mm.make_activations(M, K, seed=4)
+    x_host = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).pin_memory()
+    y_host = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    x_dev = torch.empty((M, K), dtype=torch.bfloat16, device=rt.device)
+    y_dev = torch.empty((M, N), dtype=torch.bfloat16, device=rt.device)
+    rt.linear_host(x_host, x_dev, w, y_dev, y_host)
+    got = y_host.view(torch.int16).numpy().view(np.uint16)
+    assert row_rel_l2(got, oracle.gemm_f4(xb, w.payload, w.scales, w.gs)) <= REL_L2_TOL
