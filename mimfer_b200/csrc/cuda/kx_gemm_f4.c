@@ -212,6 +212,8 @@ mm_status mm_f4_linear(const void *x, const void *payload, const void *scale, fl
                            MMB_ST_ROWS, CU_TENSOR_MAP_SWIZZLE_128B));
         MM_CHECK(encode_2d(a.tm_scale, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, scale, K / 16, N, 16,
                            MMB_ST_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE));
+        MM_CHECK(encode_2d(a.tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, MMB_ST_KSTEP,
+                           a.plan.tile_m, CU_TENSOR_MAP_SWIZZLE_NONE));
         err = mmb_launch_stream(&a, stream);
         break;
     case MM_F4_V_UMMA:

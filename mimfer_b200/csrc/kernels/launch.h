@@ -14,15 +14,17 @@ extern "C" {
 #endif
 
 /* ---- STREAM (decode) geometry ------------------------------------------- */
-#define MMB_ST_ROWS        256u   /* weight rows per CTA (8 warps x 32 rows)   */
+#define MMB_ST_ROWS        256    /* weight rows per CTA (16 warps x 16 rows)  */
 #define MMB_ST_KSTEP       256u   /* weights along K per pipeline stage        */
-#define MMB_ST_CONSUMERS   8u     /* MMA warps; +1 producer warp               */
-#define MMB_ST_THREADS     ((MMB_ST_CONSUMERS + 1u) * 32u)
+#define MMB_ST_CONSUMERS   16     /* MMA warps                                  */
+#define MMB_ST_XFORM_WARPS 4u     /* activation transform warps                 */
+#define MMB_ST_THREADS     ((MMB_ST_CONSUMERS + 1u + MMB_ST_XFORM_WARPS) * 32u)
 #define MMB_ST_PAYLOAD_B   (MMB_ST_ROWS * 128u)            /* SW128 box        */
 #define MMB_ST_SCALE_B     (MMB_ST_ROWS * 16u)
-#define MMB_ST_X_B(mt)     ((mt) * 8u * MMB_ST_KSTEP * 2u)
+#define MMB_ST_X_RAW_B(mt) ((mt) * 8u * MMB_ST_KSTEP * 2u)     /* bytes TMA delivers         */
+#define MMB_ST_X_B(mt)     ((mt) * 5120u)                       /* slot: 8 rows x 576 B, padded */
 #define MMB_ST_STAGE_B(mt) (MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B + MMB_ST_X_B(mt))
-#define MMB_ST_FIXED_B     (1024u /* scale LUT */ + 256u /* barriers */ + 1024u /* align slack */)
+#define MMB_ST_FIXED_B     (2048u /* two scale LUTs */ + 512u /* barriers, flags */ + 1024u /* align slack */)
 
 /* ---- UMMA (prefill) geometry ---------------------------------------------- */
 #define MMB_UM_KBLOCK      64u    /* bf16 elements per smem row (128 B swizzle) */

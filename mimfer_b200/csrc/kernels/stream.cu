@@ -2,26 +2,38 @@
  * STREAM: the decode kernel of the NVFP4 linear op (M <= 32, HBM-bound).
  *
  * One CTA owns 256 weight rows and a contiguous range of 256-wide K steps.
- * A producer warp keeps a ring of stages full: per step one TMA box of packed
- * payload (256 rows x 128 B, 128-byte swizzle), one of block scales
- * (256 rows x 16 B), and the matching slice of the activations, which it
- * re-orders on the way into shared memory (see below).  Eight consumer warps
- * each take 32 rows: 16-byte shared loads of payload, nibble unpack and scale
- * in registers (fp4.cuh), bf16 warp MMAs with the weights as the 16-row
- * operand and up to 32 activation rows as the 8-wide operand, fp32
- * accumulators in registers.  With split-K the partial sums meet in the
- * workspace and the CTA that arrives last adds them in slice order, so the
- * result does not depend on scheduling (no atomics on data; the reference
- * demands order-faithful reductions, include/mimfer/kernels.h:14-15).
+ * One thread keeps a ring of stages full by TMA: per step a box of packed
+ * payload (256 rows x 128 B, 128-byte swizzle), one of block scales (256 rows
+ * x 16 B) and the matching slice of the activations (up to 32 rows x 512 B).
+ * Four transform warps pick the operand format of the step from the
+ * activations and rewrite that slice in place.  Sixteen consumer warps each take 16
+ * rows: 16-byte shared loads of payload, nibble unpack and scale in registers
+ * (fp4.cuh), warp MMAs with the weights as the 16-row operand and the
+ * activation rows as the 8-wide operand, fp32 accumulators in registers.
+ * With split-K the partial sums meet in the workspace and the CTA that
+ * arrives last adds them in slice order, so the result does not depend on
+ * scheduling (no atomics on data; the reference demands order-faithful
+ * reductions, include/mimfer/kernels.h:14-15).
  *
- * Operand order inside a K step.  Lane (g, t) of a consumer warp (g = lane/4,
- * t = lane%4) owns the 64 weights [64t, 64t+64) of each of its rows, as eight
- * 32-bit words of eight nibbles.  A word is unpacked into the pairs (n0,n4)
- * (n1,n5) (n2,n6) (n3,n7) because both halves of such a pair need the same
- * shifts.  The MMA sums over K, so any order works as long as both operands
- * agree: the producer stores each group of eight activations as
- * (x0,x4,x1,x5,x2,x6,x3,x7), at [word][row][t], which also makes the
- * consumers' 16-byte reads conflict-free.
+ * Two operand formats per K step, chosen by the transform warps from the
+ * activations of that step:
+ *
+ *  fp16   when every activation of the slice is zero or has 2^-17 <= |x| < 2^16,
+ *         i.e. converts to fp16 without loss.  Weights go through
+ *         cvt.rn.f16x2.e2m1x2 and one packed fp16 multiply by the scale: about
+ *         one instruction per weight.  Activations are stored in column order.
+ *  bf16   otherwise (tiny, huge or non-finite activations).  Weights take the
+ *         bf16 subnormal construction of fp4.cuh, about two instructions per
+ *         weight, with the pairing (n0,n4)(n1,n5)(n2,n6)(n3,n7); the transform warps
+ *         store each group of eight activations as (x0,x4,x1,x5,x2,x6,x3,x7) to
+ *         match (the MMA sums over K, so any order works if both operands agree).
+ *
+ * Either way the dequantised weight and the activation are exact in the
+ * operand format, so every product is the reference's product and both paths
+ * add into the same fp32 accumulators.
+ *
+ * Lane (g, t) of a consumer warp (g = lane/4, t = lane%4) owns the 64 weights
+ * [64t, 64t+64) of each of its rows per step, as eight 32-bit words.
  *
  * It replaces the one-thread-per-output kernel of the reference
  * (src/kernels/cuda/cx.cu:345-356) for the decode regime.
@@ -42,19 +54,139 @@ struct StreamParams {
     uint32_t        k_steps, split_k, stages;
 };
 
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                              uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+/* 0xffffffff when both bf16 halves of u convert to fp16 exactly. */
+__device__ __forceinline__ uint32_t fp16_exact_mask(uint32_t u)
+{
+    const __nv_bfloat162 a = __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&u));
+    const __nv_bfloat162 hi = __float2bfloat162_rn(65536.0f);
+    const __nv_bfloat162 lo = __float2bfloat162_rn(7.62939453125e-06f);       /* 2^-17 */
+    const __nv_bfloat162 zero = __float2bfloat162_rn(0.0f);
+    return __hlt2_mask(a, hi) & (__hge2_mask(a, lo) | __heq2_mask(a, zero));
+}
+
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t u)
+{
+    const __half2 h = __floats2half2_rn(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+/* Activation slot of a stage: TMA delivers MPAD rows of 512 bytes (256 values)
+ * in column order; the transform warps rewrite it as rows of 576 bytes, with
+ * 16 bytes of padding after every eighth 16-byte chunk.  That is conflict-free
+ * both for the transform warps (a warp covers one row, chunk = lane) and for
+ * the consumers (lane (g, t) reads chunk 8t + word of row g), and gives the
+ * consumers compile-time offsets. */
+__device__ __forceinline__ uint32_t x_slot_offset(uint32_t m, uint32_t c)
+{
+    return m * 576u + (c >> 3) * 144u + (c & 7u) * 16u;
+}
+
+/* One K step of one consumer warp in one operand format (HALF: fp16, else bf16). */
+template <int MT, int RT, int SLOTS, bool HALF>
+__device__ __forceinline__ void consume_step(float (&accs)[SLOTS][RT][MT][4], uint32_t stage,
+                                             uint32_t lut, uint32_t warp, uint32_t g, uint32_t t)
+{
+    /* per-lane bases; everything below is base + compile-time offset */
+    const uint32_t pay = stage + (warp * (16u * RT) + g) * 128u;
+    const uint32_t scl = stage + MMB_ST_PAYLOAD_B + (warp * (16u * RT) + g) * 16u + t * 4u;
+    const uint32_t xs = stage + MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B + g * 576u + t * 144u;
+
+    /* the four scale entries of each of this lane's rows, looked up once */
+    uint32_t cs[RT][2][4];
+#pragma unroll
+    for (int rt = 0; rt < RT; rt++)
+#pragma unroll
+        for (int rr = 0; rr < 2; rr++) {
+            const uint32_t sc4 = lds32(scl + (rt * 16u + rr * 8u) * 16u);
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                cs[rt][rr][j] = lds32(lut + ((sc4 >> (8 * j)) & 255u) * 4u);
+        }
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        uint4 pw[RT][2];
+#pragma unroll
+        for (int rt = 0; rt < RT; rt++)
+#pragma unroll
+            for (int rr = 0; rr < 2; rr++)
+                pw[rt][rr] = lds128(pay + (rt * 16u + rr * 8u) * 128u + (((2u * t + h) ^ g) << 4));
+#pragma unroll
+        for (int wi = 0; wi < 4; wi++) {
+            const uint32_t word = 4u * h + wi;
+            uint4 xb[MT];
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++)
+                xb[mt] = lds128(xs + mt * (8u * 576u) + word * 16u);
+#pragma unroll
+            for (int rt = 0; rt < RT; rt++) {
+                const uint32_t c0 = cs[rt][0][2 * h + (wi >> 1)];
+                const uint32_t c8 = cs[rt][1][2 * h + (wi >> 1)];
+                const uint32_t w0 = wi == 0 ? pw[rt][0].x : wi == 1 ? pw[rt][0].y
+                                  : wi == 2 ? pw[rt][0].z : pw[rt][0].w;
+                const uint32_t w8 = wi == 0 ? pw[rt][1].x : wi == 1 ? pw[rt][1].y
+                                  : wi == 2 ? pw[rt][1].z : pw[rt][1].w;
+                if (HALF) {
+                    const uint4 a0 = unpack8_natural_f16(w0, c0);
+                    const uint4 a8 = unpack8_natural_f16(w8, c8);
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++) {
+                        mma_f16_16816(accs[(2 * wi) % SLOTS][rt][mt], a0.x, a8.x, a0.y, a8.y,
+                                      xb[mt].x, xb[mt].y);
+                        mma_f16_16816(accs[(2 * wi + 1) % SLOTS][rt][mt], a0.z, a8.z, a0.w, a8.w,
+                                      xb[mt].z, xb[mt].w);
+                    }
+                } else {
+                    uint32_t q0[4], q8[4];
+                    unpack8_paired(w0, c0, q0);
+                    unpack8_paired(w8, c8, q8);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {              /* back from the 2^-8 of the bf16 form */
+                        q0[j] = mul_bf16x2(q0[j], 0x43804380u);
+                        q8[j] = mul_bf16x2(q8[j], 0x43804380u);
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++) {
+                        mma_bf16_16816(accs[(2 * wi) % SLOTS][rt][mt], q0[0], q8[0], q0[1], q8[1],
+                                       xb[mt].x, xb[mt].y);
+                        mma_bf16_16816(accs[(2 * wi + 1) % SLOTS][rt][mt], q0[2], q8[2], q0[3], q8[3],
+                                       xb[mt].z, xb[mt].w);
+                    }
+                }
+            }
+        }
+    }
+}
+
 template <int MT>
 __global__ void __launch_bounds__(MMB_ST_THREADS, 1)
 f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
-                 const __grid_constant__ TmaDesc tm_scale, const StreamParams p)
+                 const __grid_constant__ TmaDesc tm_scale, const __grid_constant__ TmaDesc tm_x,
+                 const StreamParams p)
 {
     constexpr uint32_t MPAD = MT * 8;
+    constexpr int RT = MMB_ST_ROWS / (16 * MMB_ST_CONSUMERS);   /* 16-row tiles per consumer warp */
     constexpr uint32_t STAGE_B = MMB_ST_STAGE_B(MT);
+    constexpr uint32_t XFORM_THREADS = MMB_ST_XFORM_WARPS * 32u;
+    constexpr uint32_t ITEMS = MPAD * 32u / XFORM_THREADS;    /* 16-byte chunks per transform thread */
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t lut = base + p.stages * STAGE_B;
-    const uint32_t bar_full = lut + 1024u;
-    const uint32_t bar_empty = bar_full + 8u * p.stages;
-    const uint32_t last_flag = bar_empty + 8u * p.stages;    /* split-K: "this CTA reduces" */
+    const uint32_t lut_bf = base + p.stages * STAGE_B;       /* scale * 2^118, bf16x2 */
+    const uint32_t lut_hf = lut_bf + 1024u;                  /* scale, fp16x2          */
+    const uint32_t bar_raw = lut_hf + 1024u;                 /* [stages] TMA landed      */
+    const uint32_t bar_full = bar_raw + 8u * p.stages;       /* [stages] activations ready */
+    const uint32_t bar_empty = bar_full + 8u * p.stages;     /* [stages] consumers done  */
+    const uint32_t fmt_flag = bar_empty + 8u * p.stages;     /* [stages] 1 = fp16 step  */
+    const uint32_t last_flag = fmt_flag + 4u * p.stages;     /* split-K: "this CTA reduces" */
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t row0 = blockIdx.x * MMB_ST_ROWS;
@@ -64,11 +196,14 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
         static_cast<uint64_t>(p.k_steps) * (blockIdx.y + 1) / p.split_k);
     const uint32_t nsteps = ks_end - ks_begin;
 
-    if (tid < 256u)
-        sts32(lut + tid * 4u, scale_lut_entry(tid));
+    if (tid < 256u) {
+        sts32(lut_bf + tid * 4u, scale_lut_entry(tid));
+        sts32(lut_hf + tid * 4u, scale_lut_entry_f16(tid));
+    }
     if (tid == 0) {
         for (uint32_t s = 0; s < p.stages; s++) {
-            mbar_init(bar_full + 8u * s, 33u);                 /* expect_tx + 32 lanes */
+            mbar_init(bar_raw + 8u * s, 1u);
+            mbar_init(bar_full + 8u * s, XFORM_THREADS);
             mbar_init(bar_empty + 8u * s, MMB_ST_CONSUMERS);
         }
         mbar_fence_init();
@@ -76,35 +211,74 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
     __syncthreads();
 
     if (warp == MMB_ST_CONSUMERS) {
-        /* ------------------------------ producer ------------------------- */
-        const uint32_t t = lane & 3u, w = lane >> 2;          /* chunk = 8t + w */
+        /* ------------------------------ TMA issue ------------------------- */
+        if (lane == 0) {
+            for (uint32_t it = 0; it < nsteps; it++) {
+                const uint32_t s = it % p.stages, round = it / p.stages;
+                const uint32_t stage = base + s * STAGE_B;
+                if (round > 0) {
+                    mbar_wait(bar_empty + 8u * s, (round - 1u) & 1u, p.status);
+                    fence_proxy_async_smem();      /* generic writes of the slot precede the refill */
+                }
+                const uint32_t ks = ks_begin + it;
+                mbar_expect_tx(bar_raw + 8u * s, MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B + MMB_ST_X_RAW_B(MT));
+                tma_load_2d(stage, &tm_payload, static_cast<int>(ks * 128u),
+                            static_cast<int>(row0), bar_raw + 8u * s);
+                tma_load_2d(stage + MMB_ST_PAYLOAD_B, &tm_scale, static_cast<int>(ks * 16u),
+                            static_cast<int>(row0), bar_raw + 8u * s);
+                tma_load_2d(stage + MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B, &tm_x,
+                            static_cast<int>(ks * MMB_ST_KSTEP), 0, bar_raw + 8u * s);
+            }
+        }
+        return;
+    }
+    if (warp > MMB_ST_CONSUMERS) {
+        /* ------------------------------ activation transform --------------- *
+         * TMA delivers the slice as bf16 rows in column order; these warps pick
+         * the operand format of the step and rewrite the slot in place. */
+        const uint32_t xt = tid - (MMB_ST_CONSUMERS + 1u) * 32u;
         for (uint32_t it = 0; it < nsteps; it++) {
             const uint32_t s = it % p.stages, round = it / p.stages;
-            const uint32_t stage = base + s * STAGE_B;
-            if (round > 0)
-                mbar_wait(bar_empty + 8u * s, (round - 1u) & 1u, p.status);
-            const uint32_t ks = ks_begin + it;
-            if (lane == 0) {
-                mbar_expect_tx(bar_full + 8u * s, MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B);
-                tma_load_2d(stage, &tm_payload, static_cast<int>(ks * 128u),
-                            static_cast<int>(row0), bar_full + 8u * s);
-                tma_load_2d(stage + MMB_ST_PAYLOAD_B, &tm_scale, static_cast<int>(ks * 16u),
-                            static_cast<int>(row0), bar_full + 8u * s);
-            }
-            const uint32_t xs = stage + MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B;
-            const uint16_t *xk = p.x + static_cast<size_t>(ks) * MMB_ST_KSTEP + (8u * t + w) * 8u;
+            const uint32_t xs = base + s * STAGE_B + MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B;
+            mbar_wait(bar_raw + 8u * s, round & 1u, p.status);
+            uint4 v[ITEMS];
+            uint32_t ok = 0xffffffffu;
 #pragma unroll
-            for (uint32_t m = 0; m < MPAD; m++) {
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (m < p.M)
-                    v = __ldg(reinterpret_cast<const uint4 *>(xk + static_cast<size_t>(m) * p.K));
-                uint4 o;
-                o.x = prmt(v.x, v.z, 0x5410u);                 /* x0 x4 */
-                o.y = prmt(v.x, v.z, 0x7632u);                 /* x1 x5 */
-                o.z = prmt(v.y, v.w, 0x5410u);                 /* x2 x6 */
-                o.w = prmt(v.y, v.w, 0x7632u);                 /* x3 x7 */
-                sts128(xs + ((w * MPAD + m) * 4u + t) * 16u, o);
+            for (uint32_t i = 0; i < ITEMS; i++) {
+                const uint32_t id = i * XFORM_THREADS + xt;        /* row = id / 32, chunk = lane */
+                v[i] = lds128(xs + id * 16u);
+                ok &= fp16_exact_mask(v[i].x) & fp16_exact_mask(v[i].y) &
+                      fp16_exact_mask(v[i].z) & fp16_exact_mask(v[i].w);
             }
+            /* one decision per step; the barrier also orders every read of the
+             * slot before the first in-place write */
+            uint32_t half_ok;
+            asm volatile(
+                "{\n\t.reg .pred q, r;\n\t"
+                "setp.eq.u32 q, %1, 0xffffffff;\n\t"
+                "bar.red.and.pred r, 2, %2, q;\n\t"
+                "selp.u32 %0, 1, 0, r;\n\t}"
+                : "=r"(half_ok) : "r"(ok), "r"(XFORM_THREADS) : "memory");
+#pragma unroll
+            for (uint32_t i = 0; i < ITEMS; i++) {
+                const uint32_t id = i * XFORM_THREADS + xt;
+                const uint32_t m = id >> 5, c = id & 31u;
+                uint4 o;
+                if (half_ok) {
+                    o.x = bf16x2_to_f16x2(v[i].x);
+                    o.y = bf16x2_to_f16x2(v[i].y);
+                    o.z = bf16x2_to_f16x2(v[i].z);
+                    o.w = bf16x2_to_f16x2(v[i].w);
+                } else {
+                    o.x = prmt(v[i].x, v[i].z, 0x5410u);       /* x0 x4 */
+                    o.y = prmt(v[i].x, v[i].z, 0x7632u);       /* x1 x5 */
+                    o.z = prmt(v[i].y, v[i].w, 0x5410u);       /* x2 x6 */
+                    o.w = prmt(v[i].y, v[i].w, 0x7632u);       /* x3 x7 */
+                }
+                sts128(xs + x_slot_offset(m, c), o);
+            }
+            if (xt == 0)
+                sts32(fmt_flag + 4u * s, half_ok);
             mbar_arrive(bar_full + 8u * s);
         }
         return;
@@ -112,81 +286,55 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
 
     /* --------------------------------- consumers ------------------------- */
     const uint32_t g = lane >> 2, t = lane & 3u;
-    float acc[2][MT][4];
+    /* SLOTS independent accumulator sets per (row tile, activation tile): the
+     * warp MMA has a long dependent-issue latency, so consecutive MMAs must not
+     * chain on one accumulator.  Eight chains per warp whatever MT is. */
+    constexpr int SLOTS = 4 / MT;
+    float accs[SLOTS][RT][MT][4];
 #pragma unroll
-    for (int rt = 0; rt < 2; rt++)
+    for (int sl = 0; sl < SLOTS; sl++)
 #pragma unroll
-        for (int mt = 0; mt < MT; mt++)
+        for (int rt = 0; rt < RT; rt++)
 #pragma unroll
-            for (int i = 0; i < 4; i++) acc[rt][mt][i] = 0.0f;
+            for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) accs[sl][rt][mt][i] = 0.0f;
 
     for (uint32_t it = 0; it < nsteps; it++) {
         const uint32_t s = it % p.stages, round = it / p.stages;
         const uint32_t stage = base + s * STAGE_B;
         mbar_wait(bar_full + 8u * s, round & 1u, p.status);
-        const uint32_t pay = stage, scl = stage + MMB_ST_PAYLOAD_B;
-        const uint32_t xs = scl + MMB_ST_SCALE_B;
-
-        uint32_t scw[2][2];                                    /* 4 scale bytes per row */
-#pragma unroll
-        for (int rt = 0; rt < 2; rt++)
-#pragma unroll
-            for (int rr = 0; rr < 2; rr++) {
-                const uint32_t row = warp * 32u + rt * 16u + rr * 8u + g;
-                scw[rt][rr] = lds32(scl + row * 16u + t * 4u);
-            }
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            uint4 pw[2][2];
-#pragma unroll
-            for (int rt = 0; rt < 2; rt++)
-#pragma unroll
-                for (int rr = 0; rr < 2; rr++) {
-                    const uint32_t row = warp * 32u + rt * 16u + rr * 8u + g;
-                    pw[rt][rr] = lds128(pay + row * 128u + (((2u * t + h) ^ g) << 4));
-                }
-#pragma unroll
-            for (int wi = 0; wi < 4; wi++) {
-                const uint32_t word = 4u * h + wi;
-                uint4 xb[MT];
-#pragma unroll
-                for (int mt = 0; mt < MT; mt++)
-                    xb[mt] = lds128(xs + ((word * MPAD + mt * 8u + g) * 4u + t) * 16u);
-#pragma unroll
-                for (int rt = 0; rt < 2; rt++) {
-                    uint32_t q0[4], q8[4];
-                    const uint32_t sb = 2u * h + (wi >> 1);
-                    const uint32_t c0 = lds32(lut + ((scw[rt][0] >> (8u * sb)) & 255u) * 4u);
-                    const uint32_t c8 = lds32(lut + ((scw[rt][1] >> (8u * sb)) & 255u) * 4u);
-                    const uint32_t w0 = wi == 0 ? pw[rt][0].x : wi == 1 ? pw[rt][0].y
-                                      : wi == 2 ? pw[rt][0].z : pw[rt][0].w;
-                    const uint32_t w8 = wi == 0 ? pw[rt][1].x : wi == 1 ? pw[rt][1].y
-                                      : wi == 2 ? pw[rt][1].z : pw[rt][1].w;
-                    unpack8_paired(w0, c0, q0);
-                    unpack8_paired(w8, c8, q8);
-#pragma unroll
-                    for (int mt = 0; mt < MT; mt++) {
-                        mma_bf16_16816(acc[rt][mt], q0[0], q8[0], q0[1], q8[1], xb[mt].x, xb[mt].y);
-                        mma_bf16_16816(acc[rt][mt], q0[2], q8[2], q0[3], q8[3], xb[mt].z, xb[mt].w);
-                    }
-                }
-            }
-        }
+        if (lds32(fmt_flag + 4u * s) != 0u)
+            consume_step<MT, RT, SLOTS, true>(accs, stage, lut_hf, warp, g, t);
+        else
+            consume_step<MT, RT, SLOTS, false>(accs, stage, lut_bf, warp, g, t);
         __syncwarp();
         if (lane == 0)
             mbar_arrive(bar_empty + 8u * s);
     }
 
     /* --------------------------------- epilogue -------------------------- */
-    const float out_scale = p.gs * 256.0f;          /* undo the 2^-8 of the operand form */
+    const float out_scale = p.gs;
+    float acc[RT][MT][4];                             /* slots added in a fixed order */
+#pragma unroll
+    for (int rt = 0; rt < RT; rt++)
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float v = accs[0][rt][mt][i];
+#pragma unroll
+                for (int sl = 1; sl < SLOTS; sl++) v += accs[sl][rt][mt][i];
+                acc[rt][mt][i] = v;
+            }
     if (p.split_k == 1) {
 #pragma unroll
-        for (int rt = 0; rt < 2; rt++)
+        for (int rt = 0; rt < RT; rt++)
 #pragma unroll
             for (int mt = 0; mt < MT; mt++)
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    const uint32_t n = row0 + warp * 32u + rt * 16u + (i >> 1) * 8u + g;
+                    const uint32_t n = row0 + warp * (16u * RT) + rt * 16u + (i >> 1) * 8u + g;
                     const uint32_t m = mt * 8u + 2u * t + (i & 1);
                     if (n < p.N && m < p.M) {
                         __nv_bfloat16 hv = __float2bfloat16_rn(acc[rt][mt][i] * out_scale);
@@ -199,39 +347,72 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
     /* split-K: publish this slice, the last CTA of the row block reduces */
     float *mine = p.partial + static_cast<size_t>(blockIdx.y) * MPAD * p.N;
 #pragma unroll
-    for (int rt = 0; rt < 2; rt++)
+    for (int rt = 0; rt < RT; rt++)
 #pragma unroll
         for (int mt = 0; mt < MT; mt++)
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const uint32_t n = row0 + warp * 32u + rt * 16u + (i >> 1) * 8u + g;
+                const uint32_t n = row0 + warp * (16u * RT) + rt * 16u + (i >> 1) * 8u + g;
                 const uint32_t m = mt * 8u + 2u * t + (i & 1);
                 if (n < p.N && m < p.M)
                     __stcg(mine + static_cast<size_t>(m) * p.N + n, acc[rt][mt][i]);
             }
     __threadfence();
-    asm volatile("bar.sync 1, 256;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(MMB_ST_CONSUMERS * 32) : "memory");
     if (tid == 0) {
         const unsigned ticket = atomicAdd(p.counters + blockIdx.x, 1u);
         sts32(last_flag, (ticket == p.split_k - 1u) ? 1u : 0u);
     }
-    asm volatile("bar.sync 1, 256;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(MMB_ST_CONSUMERS * 32) : "memory");
     if (!lds32(last_flag))
         return;
     __threadfence();
+    /* Slices are added in ascending order for every output, so the sum does not
+     * depend on which CTA arrived last; the loads of one slice (all outputs of
+     * this thread) are issued together, slices two at a time. */
+    float sum[RT][MT][4];
 #pragma unroll
-    for (int rt = 0; rt < 2; rt++)
+    for (int rt = 0; rt < RT; rt++)
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) sum[rt][mt][i] = 0.0f;
+    for (uint32_t sl = 0; sl < p.split_k; sl += 2u) {
+        float v[2][RT][MT][4];
+#pragma unroll
+        for (int u = 0; u < 2; u++)
+#pragma unroll
+            for (int rt = 0; rt < RT; rt++)
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const uint32_t n = row0 + warp * (16u * RT) + rt * 16u + (i >> 1) * 8u + g;
+                        const uint32_t m = mt * 8u + 2u * t + (i & 1);
+                        v[u][rt][mt][i] = 0.0f;
+                        if (n < p.N && m < p.M && sl + u < p.split_k)
+                            v[u][rt][mt][i] =
+                                __ldcg(p.partial + (static_cast<size_t>(sl + u) * MPAD + m) * p.N + n);
+                    }
+#pragma unroll
+        for (int u = 0; u < 2; u++)
+#pragma unroll
+            for (int rt = 0; rt < RT; rt++)
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) sum[rt][mt][i] += v[u][rt][mt][i];
+    }
+#pragma unroll
+    for (int rt = 0; rt < RT; rt++)
 #pragma unroll
         for (int mt = 0; mt < MT; mt++)
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const uint32_t n = row0 + warp * 32u + rt * 16u + (i >> 1) * 8u + g;
+                const uint32_t n = row0 + warp * (16u * RT) + rt * 16u + (i >> 1) * 8u + g;
                 const uint32_t m = mt * 8u + 2u * t + (i & 1);
                 if (n < p.N && m < p.M) {
-                    float sum = 0.0f;
-                    for (uint32_t sl = 0; sl < p.split_k; sl++)
-                        sum += __ldcg(p.partial + (static_cast<size_t>(sl) * MPAD + m) * p.N + n);
-                    __nv_bfloat16 hv = __float2bfloat16_rn(sum * out_scale);
+                    __nv_bfloat16 hv = __float2bfloat16_rn(sum[rt][mt][i] * out_scale);
                     p.y[static_cast<size_t>(m) * p.N + n] = *reinterpret_cast<uint16_t *>(&hv);
                 }
             }
@@ -254,11 +435,12 @@ static int launch_mt(const mmb_args *a, unsigned *status, cudaStream_t st)
     p.k_steps = a->plan.k_steps;
     p.split_k = a->plan.split_k;
     p.stages = a->plan.stages;
-    TmaDesc tp, ts;
+    TmaDesc tp, ts, tx;
     memcpy(tp.bytes, a->tm_payload, 128);
     memcpy(ts.bytes, a->tm_scale, 128);
+    memcpy(tx.bytes, a->tm_x, 128);
     dim3 grid(a->plan.grid_x, a->plan.grid_y), block(MMB_ST_THREADS);
-    f4_stream_kernel<MT><<<grid, block, a->plan.smem_bytes, st>>>(tp, ts, p);
+    f4_stream_kernel<MT><<<grid, block, a->plan.smem_bytes, st>>>(tp, ts, tx, p);
     return static_cast<int>(cudaGetLastError());
 }
 

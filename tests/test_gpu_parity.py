@@ -92,6 +92,26 @@ def test_stream_without_workspace(rt, oracle):
         L.check(rt.lib.mm_f4_workspace_set(ws.data_ptr(), ws.numel()), "restore workspace")
 
 
+@pytest.mark.parametrize("M", [1, 8, 16, 32])
+def test_stream_activation_range_picks_operand_format(rt, oracle, M):
+    """K steps whose activations do not convert to fp16 exactly (tiny, huge)
+    take the bf16 operand path; both paths share the accumulators."""
+    K, N = 2048, 512
+    w = mm.make_weight(N, K, seed=3)
+    xf = mm.linear.fill_normal(M, K, 4)
+    xf[0, 5] = 3.0e-9            # step 0: below 2^-17
+    xf[M - 1, 700] = 2.5e5       # step 2: above 2^16
+    xf[0, 1300:1310] = 0.0       # zeros are exact in both formats
+    xf[M // 2, 1800] = -1.0e-30  # step 7
+    x = mm.linear.f32_to_bf16(xf)
+    y = run(rt, x, w, V_STREAM)
+    assert row_rel_l2(y, oracle.gemm_f4(x, w.payload, w.scales, w.gs)) <= REL_L2_TOL
+    # all steps out of range
+    x2 = mm.linear.f32_to_bf16(xf * np.float32(1.0e-7))
+    y2 = run(rt, x2, w, V_STREAM)
+    assert row_rel_l2(y2, oracle.gemm_f4(x2, w.payload, w.scales, w.gs)) <= REL_L2_TOL
+
+
 def test_stream_is_deterministic(rt, oracle):
     w = mm.make_weight(5120, 17408, seed=2).to_device(rt.device)
     x = mm.make_activations(8, 17408, seed=3)
