@@ -151,6 +151,32 @@ mm_status mm_f4_linear(const void *x, const void *payload, const void *scale,
                        float gs, void *y, uint32_t M, uint32_t K, uint32_t N,
                        void *stream);
 
+/* No counterpart in the reference.  The decode kernel of mm_f4_linear with its
+ * split-K scratch built in, for callers that cannot hand over a workspace and
+ * may not allocate one: code that runs under mimfer's rule that device memory
+ * is claimed by a few cudaMalloc calls at start-up and never afterwards
+ * (include/mimfer/alloc.h:4-29), or a serving loop that must not touch the
+ * allocator.  Calls no cudaMalloc/cudaFree and no allocating library routine;
+ * x, payload, scale and y are still the caller's (device pointers), `stream`
+ * is a cudaStream_t (NULL = the legacy default stream) and the call does not
+ * synchronise.
+ *  - Scratch is one file-scope device array of 16 KiB + 4 MiB, resident on
+ *    every GPU that loads the library until the process exits.  A shape whose
+ *    split needs more returns MM_ERR_CAPACITY (the log names both numbers);
+ *    shapes the decode kernel cannot take (M > 32, K % 256 != 0, operands not
+ *    16-byte aligned) return MM_ERR_UNSUPPORTED.
+ *  - The first call on each device looks the array's device address up
+ *    (cudaGetSymbolAddress) and sets kernel attributes; make that first call
+ *    outside any stream capture, with the device current.
+ *  - All calls share the array and it keeps the previous call's contents; the
+ *    arrival counters are zeroed on `stream` before each launch.  Two calls of
+ *    one process that overlap on the GPU (issued on different streams) race on
+ *    it: keep the calls on one stream or order them with events.  Separate
+ *    processes have separate copies. */
+mm_status mm_f4_linear_static_ws(const void *x, const void *payload, const void *scale,
+                                 float gs, void *y, uint32_t M, uint32_t K, uint32_t N,
+                                 void *stream);
+
 /* Host-buffer form: copies x (pinned or pageable host memory) to `x_dev`,
  * runs the op on resident device weights, copies y back to `y_host` and
  * synchronises.  This is the call the end-to-end benchmark times. */

@@ -475,3 +475,148 @@ extern "C" int mmb_launch_stream(const mmb_args *a, void *stream)
     default: return static_cast<int>(cudaErrorInvalidValue);
     }
 }
+
+/* ==========================================================================
+ * Decode op with built-in split-K scratch: mm_f4_linear_static_ws
+ *
+ * Same kernel as above, for callers that have no device block to donate as
+ * split-K workspace and must not allocate one: an integrator that lives under
+ * mimfer's start-up-only allocation policy (every byte of device memory is
+ * carved into arenas by a handful of cudaMalloc calls at load and none may
+ * follow), or a token loop that must never take the allocator's lock.  The
+ * partial sums and arrival counters live in the file-scope device array below,
+ * which every GPU that loads this library holds until the process exits.
+ * ========================================================================== */
+#include <cuda.h>
+#include "../core/core.h"
+
+#define MMB_STATIC_WS_BYTES (MMB_WS_COUNTER_B + (4u << 20))   /* 16 KiB counters + 4 MiB partials */
+#define MMB_STATIC_MAX_DEVICES 16
+
+static __device__ __align__(256) unsigned char g_static_ws[MMB_STATIC_WS_BYTES];
+
+namespace {
+
+typedef CUresult (*static_encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                     const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                     const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct StaticWsDevice {
+    bool  ready;
+    void *ws;          /* device address of g_static_ws on this device */
+    int   sm_count;
+};
+StaticWsDevice   g_static_dev[MMB_STATIC_MAX_DEVICES];
+static_encode_fn g_static_encode;
+
+/* Once per device, with that device current: the host-side name g_static_ws is
+ * only a handle, the kernel needs the address cudaGetSymbolAddress returns. */
+mm_status static_ws_setup(int dev)
+{
+    StaticWsDevice &d = g_static_dev[dev];
+    if (d.ready)
+        return MM_OK;
+    void *ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_ws);
+    if (e != cudaSuccess || !ptr) {
+        MM_LOGE("static workspace: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        return MM_ERR_CUDA;
+    }
+    if ((e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess ||
+        (e = static_cast<cudaError_t>(mmb_stream_init())) != cudaSuccess) {
+        MM_LOGE("static workspace: device setup failed: %s", cudaGetErrorString(e));
+        return MM_ERR_CUDA;
+    }
+    if (!g_static_encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr);
+        if (e != cudaSuccess || !fn || qr != cudaDriverEntryPointSuccess) {
+            MM_LOGE("static workspace: cuTensorMapEncodeTiled not available");
+            return MM_ERR_CUDA;
+        }
+        g_static_encode = reinterpret_cast<static_encode_fn>(fn);
+    }
+    d.ws = ptr;
+    d.ready = true;
+    return MM_OK;
+}
+
+bool static_encode(unsigned char out[128], CUtensorMapDataType dt, unsigned esize, const void *base,
+                   uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer,
+                   CUtensorMapSwizzle sw)
+{
+    CUtensorMap map;
+    cuuint64_t dims[2] = { inner, outer }, strides[1] = { inner * esize };
+    cuuint32_t box[2] = { box_inner, box_outer }, estr[2] = { 1, 1 };
+    if (g_static_encode(&map, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    memcpy(out, &map, 128);
+    return true;
+}
+
+} // namespace
+
+extern "C" mm_status mm_f4_linear_static_ws(const void *x, const void *payload, const void *scale,
+                                            float gs, void *y, uint32_t M, uint32_t K, uint32_t N,
+                                            void *stream)
+{
+    if (!x || !payload || !scale || !y)
+        return MM_ERR_STATE;
+    if (M == 0 || N == 0 || K == 0 || K % 16 != 0)
+        return MM_ERR_SHAPE;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MMB_STATIC_MAX_DEVICES)
+        return MM_ERR_CUDA;
+    mm_status st = static_ws_setup(dev);
+    if (st != MM_OK)
+        return st;
+    const StaticWsDevice &d = g_static_dev[dev];
+
+    mmb_args a;
+    memset(&a, 0, sizeof a);
+    a.x = x; a.payload = payload; a.scale = scale; a.y = y;
+    a.gs = gs; a.M = M; a.K = K; a.N = N;
+    a.ws = d.ws;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(payload) |
+                           reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(y) | 256u;
+    /* the split the selector would choose with room to spare ... */
+    mm_f4_shape sh = { M, K, N, static_cast<uint32_t>(d.sm_count),
+                       static_cast<uint32_t>(bits & (~bits + 1u)), static_cast<size_t>(1) << 40 };
+    st = mm_f4_select_variant(&sh, MM_F4_V_STREAM, &a.plan);
+    if (st != MM_OK) {
+        MM_LOGE("mm_f4_linear_static_ws serves the decode kernel only (M <= 32, K %% 256 == 0, "
+                "16-byte aligned operands); M=%u K=%u N=%u: %s", M, K, N, mm_status_str(st));
+        return st;
+    }
+    /* ... must fit the built-in array */
+    if (a.plan.ws_needed > MMB_STATIC_WS_BYTES) {
+        MM_LOGE("mm_f4_linear_static_ws: M=%u K=%u N=%u needs %zu bytes of split-K scratch, the "
+                "built-in array holds %u", M, K, N, a.plan.ws_needed, MMB_STATIC_WS_BYTES);
+        return MM_ERR_CAPACITY;
+    }
+    if (!static_encode(a.tm_payload, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, payload, K / 2, N, 128,
+                       MMB_ST_ROWS, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !static_encode(a.tm_scale, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, scale, K / 16, N, 16,
+                       MMB_ST_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        !static_encode(a.tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, MMB_ST_KSTEP,
+                       a.plan.tile_m, CU_TENSOR_MAP_SWIZZLE_NONE)) {
+        MM_LOGE("mm_f4_linear_static_ws: tensor map encoding failed");
+        return MM_ERR_CUDA;
+    }
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    /* the array keeps what the last call left: the arrival counters must start at zero */
+    if (a.plan.split_k > 1 &&
+        cudaMemsetAsync(d.ws, 0, MMB_WS_COUNTER_B, cs) != cudaSuccess)
+        return MM_ERR_CUDA;
+    const int err = mmb_launch_stream(&a, cs);
+    if (err) {
+        MM_LOGE("mm_f4_linear_static_ws: launch failed: %s",
+                cudaGetErrorString(static_cast<cudaError_t>(err)));
+        return MM_ERR_CUDA;
+    }
+    return MM_OK;
+}
