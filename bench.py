@@ -324,7 +324,7 @@ def cpu_baseline(threads=None, target_s=12.0):
 
     probe_rows = 16 * threads
     dt, _ = sweep(probe_rows)
-    rows = int(min(5120, max(probe_rows, probe_rows * target_s / max(dt, 1e-6))))
+    rows = int(min(34816, max(probe_rows, probe_rows * target_s / max(dt, 1e-6))))
     dt, nbytes = sweep(rows)
     return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
             "sample": f"decode sweep M in {{1,2,4,8,16}} on the first {rows} rows of gate+up and of down, "

@@ -199,8 +199,10 @@ mm_status mm_f4_decode_probe(uint32_t *out_bf16_dev, uint32_t *out_f32_dev,
                              uint32_t *out_f16_dev);
 
 /* Tuning knobs for experiments and tests; defaults are what the benchmark
- * uses.  No key is defined at present.  Returns the previous value, or -1 for
- * an unknown key. */
+ * uses.  key 1: launch kernels with programmatic stream serialization so
+ * that an op's weight prefetch overlaps the tail of the previous kernel in the
+ * stream (1 = on, default).  Returns the previous value, or -1 for an unknown
+ * key. */
 int mm_f4_tune(int key, int value);
 
 /* ---- timing on the compute stream (events with timing enabled) ----------- */

@@ -34,8 +34,9 @@ static struct {
     void      *ws;
     size_t     ws_bytes;
     int        forced_variant;
+    int        pdl;
     unsigned long long launches;
-} G = { .forced_variant = -1 };
+} G = { .forced_variant = -1, .pdl = 1 };
 
 /* global-scale registry: open addressing on the scale base pointer */
 #define GS_SLOTS 4096u
@@ -85,7 +86,11 @@ void mm_f4_force_variant(int variant) { G.forced_variant = variant; }
 
 int mm_f4_tune(int key, int value)
 {
-    (void)key; (void)value;
+    if (key == 1) {
+        int old = G.pdl;
+        G.pdl = value ? 1 : 0;
+        return old;
+    }
     return -1;
 }
 
@@ -193,6 +198,7 @@ mm_status mm_f4_linear(const void *x, const void *payload, const void *scale, fl
     a.x = x; a.payload = payload; a.scale = scale; a.y = y;
     a.gs = gs; a.M = M; a.K = K; a.N = N;
     a.ws = G.ws;
+    a.pdl = G.pdl;
 
     mm_f4_shape sh = { M, K, N, (uint32_t)G.sm_count, min_align(x, payload, scale, y), G.ws_bytes };
     if (sh.ptr_align < 16)

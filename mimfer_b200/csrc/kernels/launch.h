@@ -61,6 +61,7 @@ typedef struct mmb_args {
     uint32_t    M, K, N;
     void       *ws;       /* workspace base or NULL */
     mm_f4_plan  plan;
+    int         pdl;      /* launch with programmatic stream serialization */
     /* 128-byte TMA descriptors, filled by the launcher (opaque here) */
     unsigned char tm_payload[128] __attribute__((aligned(64)));
     unsigned char tm_scale[128] __attribute__((aligned(64)));

@@ -94,6 +94,22 @@ __device__ __forceinline__ void fence_proxy_async_smem()
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+/* ---- programmatic dependent launch ---------------------------------------
+ * A kernel launched with the programmatic-serialization attribute may start
+ * while its predecessor in the stream is still draining.  grid_dep_wait()
+ * blocks until the predecessor has completed and its writes are visible; work
+ * that does not depend on it (weight prefetch) goes before the wait.
+ * grid_dep_launch() tells the scheduler that this CTA no longer minds the
+ * successor's CTAs being placed. */
+__device__ __forceinline__ void grid_dep_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dep_launch()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 /* ---- shared-memory accessors --------------------------------------------- */
 __device__ __forceinline__ uint4 lds128(uint32_t a)
 {

@@ -209,19 +209,35 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
         mbar_fence_init();
     }
     __syncthreads();
+    grid_dep_launch();
 
     if (warp == MMB_ST_CONSUMERS) {
-        /* ------------------------------ TMA issue ------------------------- */
+        /* ------------------------------ TMA issue ------------------------- *
+         * The weights do not depend on the previous kernel in the stream, the
+         * activations may: the first ring of weight boxes is issued before the
+         * grid-dependency wait, the activation boxes after it. */
         if (lane == 0) {
-            for (uint32_t it = 0; it < nsteps; it++) {
-                const uint32_t s = it % p.stages, round = it / p.stages;
-                const uint32_t stage = base + s * STAGE_B;
-                if (round > 0) {
-                    mbar_wait(bar_empty + 8u * s, (round - 1u) & 1u, p.status);
-                    fence_proxy_async_smem();      /* generic writes of the slot precede the refill */
-                }
-                const uint32_t ks = ks_begin + it;
-                mbar_expect_tx(bar_raw + 8u * s, MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B + MMB_ST_X_RAW_B(MT));
+            const uint32_t stage_bytes = MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B + MMB_ST_X_RAW_B(MT);
+            const uint32_t first = nsteps < p.stages ? nsteps : p.stages;
+            for (uint32_t it = 0; it < first; it++) {
+                const uint32_t stage = base + it * STAGE_B, ks = ks_begin + it;
+                mbar_expect_tx(bar_raw + 8u * it, stage_bytes);
+                tma_load_2d(stage, &tm_payload, static_cast<int>(ks * 128u),
+                            static_cast<int>(row0), bar_raw + 8u * it);
+                tma_load_2d(stage + MMB_ST_PAYLOAD_B, &tm_scale, static_cast<int>(ks * 16u),
+                            static_cast<int>(row0), bar_raw + 8u * it);
+            }
+            grid_dep_wait();
+            for (uint32_t it = 0; it < first; it++)
+                tma_load_2d(base + it * STAGE_B + MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B, &tm_x,
+                            static_cast<int>((ks_begin + it) * MMB_ST_KSTEP), 0, bar_raw + 8u * it);
+            uint32_t s = 0, round = 1;                 /* stage index and its use count */
+            for (uint32_t it = first; it < nsteps; it++, s = (s + 1u == p.stages) ? 0u : s + 1u,
+                                                   round += (s == 0u)) {
+                const uint32_t stage = base + s * STAGE_B, ks = ks_begin + it;
+                mbar_wait(bar_empty + 8u * s, (round - 1u) & 1u, p.status);
+                fence_proxy_async_smem();          /* generic writes of the slot precede the refill */
+                mbar_expect_tx(bar_raw + 8u * s, stage_bytes);
                 tma_load_2d(stage, &tm_payload, static_cast<int>(ks * 128u),
                             static_cast<int>(row0), bar_raw + 8u * s);
                 tma_load_2d(stage + MMB_ST_PAYLOAD_B, &tm_scale, static_cast<int>(ks * 16u),
@@ -237,8 +253,9 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
          * TMA delivers the slice as bf16 rows in column order; these warps pick
          * the operand format of the step and rewrite the slot in place. */
         const uint32_t xt = tid - (MMB_ST_CONSUMERS + 1u) * 32u;
-        for (uint32_t it = 0; it < nsteps; it++) {
-            const uint32_t s = it % p.stages, round = it / p.stages;
+        uint32_t s = 0, round = 0;
+        for (uint32_t it = 0; it < nsteps; it++, s = (s + 1u == p.stages) ? 0u : s + 1u,
+                                           round += (s == 0u)) {
             const uint32_t xs = base + s * STAGE_B + MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B;
             mbar_wait(bar_raw + 8u * s, round & 1u, p.status);
             uint4 v[ITEMS];
@@ -300,8 +317,9 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
 #pragma unroll
                 for (int i = 0; i < 4; i++) accs[sl][rt][mt][i] = 0.0f;
 
-    for (uint32_t it = 0; it < nsteps; it++) {
-        const uint32_t s = it % p.stages, round = it / p.stages;
+    uint32_t s = 0, round = 0;
+    for (uint32_t it = 0; it < nsteps; it++, s = (s + 1u == p.stages) ? 0u : s + 1u,
+                                       round += (s == 0u)) {
         const uint32_t stage = base + s * STAGE_B;
         mbar_wait(bar_full + 8u * s, round & 1u, p.status);
         if (lds32(fmt_flag + 4u * s) != 0u)
@@ -439,9 +457,17 @@ static int launch_mt(const mmb_args *a, unsigned *status, cudaStream_t st)
     memcpy(tp.bytes, a->tm_payload, 128);
     memcpy(ts.bytes, a->tm_scale, 128);
     memcpy(tx.bytes, a->tm_x, 128);
-    dim3 grid(a->plan.grid_x, a->plan.grid_y), block(MMB_ST_THREADS);
-    f4_stream_kernel<MT><<<grid, block, a->plan.smem_bytes, st>>>(tp, ts, tx, p);
-    return static_cast<int>(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(a->plan.grid_x, a->plan.grid_y);
+    cfg.blockDim = dim3(MMB_ST_THREADS);
+    cfg.dynamicSmemBytes = a->plan.smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = a->pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, f4_stream_kernel<MT>, tp, ts, tx, p));
 }
 
 } // namespace mmb

@@ -109,8 +109,9 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
     if (warp == 0) {
         /* ------------------------------ TMA producer ---------------------- */
         if (lane == 0) {
-            for (uint32_t kb = 0; kb < KB; kb++) {
-                const uint32_t s = kb % ST, ps = kb % PAY_SLOTS;
+            uint32_t s = 0, round = 0;                 /* A/B stage index and its use count */
+            for (uint32_t kb = 0; kb < KB; kb++, s = (s + 1u == ST) ? 0u : s + 1u, round += (s == 0u)) {
+                const uint32_t ps = kb % PAY_SLOTS;
                 if ((kb & 3u) == 0) {
                     const uint32_t grp = kb >> 2, ss = grp % MMB_UM_SC_SLOTS;
                     if (grp >= MMB_UM_SC_SLOTS)
@@ -124,8 +125,8 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
                 mbar_expect_tx(full_pay + 8u * ps, PAY_B);
                 tma_load_2d(sm_pay + ps * PAY_B, &tm_payload, static_cast<int>(kb * 32u),
                             static_cast<int>(n0), full_pay + 8u * ps);
-                if (kb >= ST)
-                    mbar_wait(empty_ab + 8u * s, ((kb / ST) - 1u) & 1u, p.status);
+                if (round > 0)
+                    mbar_wait(empty_ab + 8u * s, (round - 1u) & 1u, p.status);
                 mbar_expect_tx(full_a + 8u * s, A_B);
                 tma_load_2d(sm_a + s * A_B, &tm_x, static_cast<int>(kb * MMB_UM_KBLOCK),
                             static_cast<int>(m0), full_a + 8u * s);
@@ -134,8 +135,9 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
     } else if (warp == 1) {
         /* ------------------------------ MMA issue -------------------------- */
         if (lane == 0) {
-            for (uint32_t kb = 0; kb < KB; kb++) {
-                const uint32_t s = kb % ST, par = (kb / ST) & 1u;
+            uint32_t s = 0, round = 0;
+            for (uint32_t kb = 0; kb < KB; kb++, s = (s + 1u == ST) ? 0u : s + 1u, round += (s == 0u)) {
+                const uint32_t par = round & 1u;
                 mbar_wait(full_a + 8u * s, par, p.status);
                 mbar_wait(full_b + 8u * s, par, p.status);
                 tc_fence_after();
@@ -155,14 +157,15 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
     } else {
         /* ------------------------------ dequantise -------------------------- */
         const uint32_t td = tid - 64u;                       /* 0..255 */
-        for (uint32_t kb = 0; kb < KB; kb++) {
-            const uint32_t s = kb % ST, ps = kb % PAY_SLOTS;
+        uint32_t s = 0, round = 0;
+        for (uint32_t kb = 0; kb < KB; kb++, s = (s + 1u == ST) ? 0u : s + 1u, round += (s == 0u)) {
+            const uint32_t ps = kb % PAY_SLOTS;
             const uint32_t grp = kb >> 2, ss = grp % MMB_UM_SC_SLOTS, j = kb & 3u;
             if (j == 0)
                 mbar_wait(full_sc + 8u * ss, (grp / MMB_UM_SC_SLOTS) & 1u, p.status);
             mbar_wait(full_pay + 8u * ps, (kb / PAY_SLOTS) & 1u, p.status);
-            if (kb >= ST)
-                mbar_wait(empty_ab + 8u * s, ((kb / ST) - 1u) & 1u, p.status);
+            if (round > 0)
+                mbar_wait(empty_ab + 8u * s, (round - 1u) & 1u, p.status);
             const uint32_t pay = sm_pay + ps * PAY_B, scl = sm_sc + ss * SC_B;
             const uint32_t bt = sm_b + s * B_B;
 #pragma unroll

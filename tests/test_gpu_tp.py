@@ -1,0 +1,62 @@
+"""Tensor-parallel NVFP4 linear on real GPUs: one process per GPU, NCCL
+all-gather of the output slices.  Skipped with fewer than two GPUs."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+from conftest import ROOT, REL_L2_TOL
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, cases, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import mimfer_b200 as mm
+    from mimfer_b200.tp import TpLinear
+    rt = mm.Runtime.get(rank)
+    for i, (M, K, N) in enumerate(cases):
+        w = mm.make_weight(N, K, seed=i)
+        lin = TpLinear(w, rank, world, rt=rt)
+        x = rt.to_device_bf16(mm.make_activations(M, K, seed=100 + i))
+        y = lin.forward(x)
+        rt.sync()
+        assert rt.device_status() == 0
+        np.save(os.path.join(out_dir, f"y{i}_{rank}.npy"), rt.from_device_bf16(y))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gpu_tensor_parallel_matches_oracle(tmp_path, oracle, lib):
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import mimfer_b200 as mm
+    from conftest import row_rel_l2
+    cases = [(1, 1024, 512), (32, 2048, 1024), (300, 512, 1040)]    # decode, decode, prefill kernel
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), cases, str(tmp_path)), nprocs=world, join=True)
+    for i, (M, K, N) in enumerate(cases):
+        w = mm.make_weight(N, K, seed=i)
+        x = mm.make_activations(M, K, seed=100 + i)
+        want = oracle.gemm_f4(x, w.payload, w.scales, w.gs)
+        ys = [np.load(tmp_path / f"y{i}_{r}.npy") for r in range(world)]
+        assert np.array_equal(ys[0], ys[1])                          # every rank holds the full output
+        assert row_rel_l2(ys[0], want) <= REL_L2_TOL
