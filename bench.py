@@ -44,6 +44,10 @@ SHAPES = {  # name: (K, N)
 DECODE_M = (1, 2, 4, 8, 16)
 PREFILL_M = (512, 2048, 8192)
 HBM_FALLBACK_GBS, TENSOR_FALLBACK_TFS = 6650.0, 1590.0
+# dram__bytes_read + dram__bytes_write over algorithmic bytes, from the ncu capture of the decode
+# kernel on gate+up (profiles/stream_kernel_decode_gate_up.md); traffic grows with the weight bytes,
+# so the per-launch figure of the sweep is this ratio times its algorithmic bytes.
+STREAM_TRAFFIC_RATIO = 1.044
 
 
 def wbytes(K, N):
@@ -356,7 +360,9 @@ def run_b200(args):
                                 "achieved": dec["alg_gbs"], "peak": pk["hbm"], "unit": "GB/s",
                                 "frac": dec["alg_gbs"] / pk["hbm"], "of": pk["src"],
                                 "alg_bytes_per_launch": dec["alg_bytes_per_launch"],
-                                "avg_launch_us": dec["avg_launch_us"], "traffic": None}
+                                "avg_launch_us": dec["avg_launch_us"],
+                                "traffic": STREAM_TRAFFIC_RATIO * dec["alg_bytes_per_launch"],
+                                "traffic_src": "ncu capture of gate+up M=1 scaled by algorithmic bytes"}
             line["e2e"] = b.decode_e2e(ops, max(2, steps // 2), warmup)
             eng.close()
             del ops

@@ -75,7 +75,9 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
     const uint32_t tmem_slot = accum_full + 8u;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    const uint32_t n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    /* activation-row tile fastest: the CTAs running together share a few weight
+     * tiles (and all of x) through L2 instead of each streaming the whole weight */
+    const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
     const uint32_t KB = p.k_blocks;
 
     if (tid < 256u)
@@ -105,14 +107,27 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = lds32(tmem_slot);
+    grid_dep_launch();
 
     if (warp == 0) {
-        /* ------------------------------ TMA producer ---------------------- */
+        /* ------------------------------ TMA producer ---------------------- *
+         * Weights do not depend on the previous kernel in the stream, the
+         * activations may: the first payload and scale boxes go out before the
+         * grid-dependency wait, the first activation box after it. */
         if (lane == 0) {
+            const uint32_t pre_pay = KB < PAY_SLOTS ? KB : PAY_SLOTS;
+            for (uint32_t kb = 0; kb < pre_pay; kb++) {
+                mbar_expect_tx(full_pay + 8u * kb, PAY_B);
+                tma_load_2d(sm_pay + kb * PAY_B, &tm_payload, static_cast<int>(kb * 32u),
+                            static_cast<int>(n0), full_pay + 8u * kb);
+            }
+            mbar_expect_tx(full_sc, SC_B);
+            tma_load_2d(sm_sc, &tm_scale, 0, static_cast<int>(n0), full_sc);
+            grid_dep_wait();
             uint32_t s = 0, round = 0;                 /* A/B stage index and its use count */
             for (uint32_t kb = 0; kb < KB; kb++, s = (s + 1u == ST) ? 0u : s + 1u, round += (s == 0u)) {
                 const uint32_t ps = kb % PAY_SLOTS;
-                if ((kb & 3u) == 0) {
+                if ((kb & 3u) == 0 && kb > 0) {
                     const uint32_t grp = kb >> 2, ss = grp % MMB_UM_SC_SLOTS;
                     if (grp >= MMB_UM_SC_SLOTS)
                         mbar_wait(empty_sc + 8u * ss, ((grp / MMB_UM_SC_SLOTS) - 1u) & 1u, p.status);
@@ -120,11 +135,12 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
                     tma_load_2d(sm_sc + ss * SC_B, &tm_scale, static_cast<int>(grp * 16u),
                                 static_cast<int>(n0), full_sc + 8u * ss);
                 }
-                if (kb >= PAY_SLOTS)
+                if (kb >= pre_pay) {
                     mbar_wait(empty_pay + 8u * ps, ((kb / PAY_SLOTS) - 1u) & 1u, p.status);
-                mbar_expect_tx(full_pay + 8u * ps, PAY_B);
-                tma_load_2d(sm_pay + ps * PAY_B, &tm_payload, static_cast<int>(kb * 32u),
-                            static_cast<int>(n0), full_pay + 8u * ps);
+                    mbar_expect_tx(full_pay + 8u * ps, PAY_B);
+                    tma_load_2d(sm_pay + ps * PAY_B, &tm_payload, static_cast<int>(kb * 32u),
+                                static_cast<int>(n0), full_pay + 8u * ps);
+                }
                 if (round > 0)
                     mbar_wait(empty_ab + 8u * s, (round - 1u) & 1u, p.status);
                 mbar_expect_tx(full_a + 8u * s, A_B);
@@ -254,9 +270,17 @@ static int launch_tile(const mmb_args *a, unsigned *status, cudaStream_t st)
     memcpy(tx.bytes, a->tm_x, 128);
     memcpy(tp.bytes, a->tm_payload, 128);
     memcpy(ts.bytes, a->tm_scale, 128);
-    dim3 grid(a->plan.grid_x, a->plan.grid_y), block(MMB_UM_THREADS);
-    f4_umma_kernel<BM, BN><<<grid, block, a->plan.smem_bytes, st>>>(tx, tp, ts, p);
-    return static_cast<int>(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(a->plan.grid_y, a->plan.grid_x);   /* (activation tiles, weight tiles) */
+    cfg.blockDim = dim3(MMB_UM_THREADS);
+    cfg.dynamicSmemBytes = a->plan.smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = a->pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, f4_umma_kernel<BM, BN>, tx, tp, ts, p));
 }
 
 template <int BM, int BN>
