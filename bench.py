@@ -276,20 +276,30 @@ class Bench:
         """config 5: gate+up and LM head, sharded along N over all ranks, M=32 and M=8192."""
         from mimfer_b200.tp import TpLinear
         out = {"world": self.world}
-        lins = {n: TpLinear(self.weight(n), self.rank, self.world, rt=self.rt) for n in ("gate_up", "lm_head")}
-        for tag, M, st in (("decode_m32", 32, steps), ("prefill_m8192", 8192, max(2, steps // 4))):
-            xs = {n: self.acts(M, SHAPES[n][0]) for n in lins}
+        modes = ("gather",) if self.world == 1 else ("fused", "gather")
+        for mode in modes:
+            lins = {n: TpLinear(self.weight(n), self.rank, self.world, rt=self.rt, mode=mode)
+                    for n in ("gate_up", "lm_head")}
+            res = {}
+            for tag, M, st in (("decode_m32", 32, steps), ("prefill_m8192", 8192, max(2, steps // 4))):
+                xs = {n: self.acts(M, SHAPES[n][0]) for n in lins}
 
-            def step():
-                for n, lin in lins.items():
-                    lin.forward(xs[n])
-            ms = self.timed(step, st, warmup)
-            wb = sum(wbytes(*SHAPES[n]) for n in lins)
-            fl = sum(2.0 * M * SHAPES[n][0] * SHAPES[n][1] for n in lins)
-            out[tag] = {"ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "tflops": fl / ms / 1e9}
-            for lin in lins.values():
-                lin._bufs.clear()
-            self.torch.cuda.empty_cache()
+                def step():
+                    for n, lin in lins.items():
+                        lin.forward(xs[n])
+                ms = self.timed(step, st, warmup)
+                wb = sum(wbytes(*SHAPES[n]) for n in lins)
+                fl = sum(2.0 * M * SHAPES[n][0] * SHAPES[n][1] for n in lins)
+                res[tag] = {"ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "tflops": fl / ms / 1e9}
+                for lin in lins.values():
+                    lin._bufs.clear()
+                    lin._symm.clear()
+                self.torch.cuda.empty_cache()
+            out[mode] = res
+            del lins
+        best = modes[0]
+        out["mode"] = best + (" (kernel epilogue stores to peers)" if best == "fused" else " (single GPU)")
+        out.update(out[best])
         return out
 
 

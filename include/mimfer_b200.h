@@ -151,6 +151,20 @@ mm_status mm_f4_linear(const void *x, const void *payload, const void *scale,
                        float gs, void *y, uint32_t M, uint32_t K, uint32_t N,
                        void *stream);
 
+/* Tensor-parallel form (no counterpart in the reference, which is single-GPU).
+ * This rank owns output features [col0, col0 + N_local) of a layer with `ldy`
+ * output features in total; payload/scale point at that row slice.  The
+ * kernel's epilogue stores the slice into all `n_ranks` copies of the full
+ * output y_all[r] ([M][ldy] bf16; y_all[0] is this GPU's own, the others are
+ * peer-mapped device pointers, e.g. from a symmetric-memory rendezvous), so
+ * the exchange rides on the compute kernel as plain peer stores over NVLink.
+ * The caller must run a cross-rank barrier on `stream` after the op before any
+ * rank reads its copy, and must not let a rank start the next write into a
+ * buffer its peers still read.  n_ranks <= 8; col0 and ldy multiples of 8. */
+mm_status mm_f4_linear_tp(const void *x, const void *payload, const void *scale, float gs,
+                          void *const *y_all, uint32_t n_ranks, uint32_t ldy, uint32_t col0,
+                          uint32_t M, uint32_t K, uint32_t N_local, void *stream);
+
 /* No counterpart in the reference.  The decode kernel of mm_f4_linear with its
  * split-K scratch built in, for callers that cannot hand over a workspace and
  * may not allocate one: code that runs under mimfer's rule that device memory

@@ -183,8 +183,9 @@ static uint32_t min_align(const void *a, const void *b, const void *c, const voi
     return (uint32_t)(v & (~v + 1u));
 }
 
-mm_status mm_f4_linear(const void *x, const void *payload, const void *scale, float gs, void *y,
-                       uint32_t M, uint32_t K, uint32_t N, void *stream)
+static mm_status linear_impl(const void *x, const void *payload, const void *scale, float gs,
+                             void *y, void *const *y_dst, uint32_t n_dst, uint32_t ldy,
+                             uint32_t col0, uint32_t M, uint32_t K, uint32_t N, void *stream)
 {
     MM_REQUIRE(x && payload && scale && y, MM_ERR_STATE);
     if (M == 0 || N == 0 || K == 0 || K % 16 != 0)
@@ -199,9 +200,13 @@ mm_status mm_f4_linear(const void *x, const void *payload, const void *scale, fl
     a.gs = gs; a.M = M; a.K = K; a.N = N;
     a.ws = G.ws;
     a.pdl = G.pdl;
+    for (uint32_t d = 0; d < n_dst; d++) a.y_dst[d] = y_dst[d];
+    a.n_dst = n_dst; a.ldy = ldy; a.col0 = col0;
 
     mm_f4_shape sh = { M, K, N, (uint32_t)G.sm_count, min_align(x, payload, scale, y), G.ws_bytes };
-    if (sh.ptr_align < 16)
+    if (n_dst && (col0 % 8u != 0 || ldy % 8u != 0))
+        sh.ptr_align = 8;                  /* 16-byte output vectors need aligned slices */
+    if (sh.ptr_align < 16 && !n_dst)
         return MM_ERR_SHAPE;               /* arena slots are >= 16-byte aligned */
     mm_status st = G.forced_variant >= 0 ? mm_f4_select_variant(&sh, G.forced_variant, &a.plan)
                                          : mm_f4_select(&sh, &a.plan);
@@ -241,6 +246,24 @@ mm_status mm_f4_linear(const void *x, const void *payload, const void *scale, fl
     }
     G.launches++;
     return MM_OK;
+}
+
+mm_status mm_f4_linear(const void *x, const void *payload, const void *scale, float gs, void *y,
+                       uint32_t M, uint32_t K, uint32_t N, void *stream)
+{
+    return linear_impl(x, payload, scale, gs, y, NULL, 0, 0, 0, M, K, N, stream);
+}
+
+mm_status mm_f4_linear_tp(const void *x, const void *payload, const void *scale, float gs,
+                          void *const *y_all, uint32_t n_ranks, uint32_t ldy, uint32_t col0,
+                          uint32_t M, uint32_t K, uint32_t N_local, void *stream)
+{
+    MM_REQUIRE(y_all && n_ranks >= 1 && n_ranks <= MMB_MAX_PEERS, MM_ERR_RANGE);
+    for (uint32_t d = 0; d < n_ranks; d++)
+        MM_REQUIRE(y_all[d] && ((uintptr_t)y_all[d] & 15u) == 0, MM_ERR_STATE);
+    MM_REQUIRE((uint64_t)col0 + N_local <= ldy, MM_ERR_SHAPE);
+    return linear_impl(x, payload, scale, gs, y_all[0], y_all, n_ranks, ldy, col0, M, K, N_local,
+                       stream);
 }
 
 /* Synchronise the compute stream and collect launch/device errors, unless a

@@ -48,6 +48,8 @@ extern "C" {
 #define MMB_WS_COUNTER_B   16384u
 #define MMB_WS_MAX_TILES   (MMB_WS_COUNTER_B / 4u)
 
+#define MMB_MAX_PEERS      8u
+
 /* Device status word bits. */
 #define MMB_DEV_TIMEOUT    1u
 #define MMB_DEV_BADARG     2u
@@ -57,6 +59,11 @@ typedef struct mmb_args {
     const void *payload;  /* u8   [N][K/2]      */
     const void *scale;    /* u8   [N][K/16]     */
     void       *y;        /* bf16 [M][N]        */
+    /* Tensor-parallel output: when n_dst > 0 the result goes to y_dst[0..n_dst-1]
+     * (this GPU's and its peers' copies of the full output) with row pitch ldy
+     * elements and column offset col0, instead of to y. */
+    void       *y_dst[MMB_MAX_PEERS];
+    uint32_t    n_dst, ldy, col0;
     float       gs;
     uint32_t    M, K, N;
     void       *ws;       /* workspace base or NULL */

@@ -19,7 +19,7 @@ constexpr int RW_MB = 4;    /* activation rows per pass */
 __global__ void __launch_bounds__(256)
 f4_rowwarp_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ payload,
                   const uint8_t *__restrict__ scale, uint16_t *__restrict__ y, float gs,
-                  uint32_t M, uint32_t K, uint32_t N)
+                  uint32_t M, uint32_t K, uint32_t N, uint32_t ldy, uint32_t col0)
 {
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t r = blockIdx.x * 8u + warp;
@@ -64,7 +64,7 @@ f4_rowwarp_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ pa
             for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
             if (lane == 0 && m0 + i < M) {
                 __nv_bfloat16 h = __float2bfloat16_rn(v * gs);
-                y[static_cast<size_t>(m0 + i) * N + r] = *reinterpret_cast<uint16_t *>(&h);
+                y[static_cast<size_t>(m0 + i) * ldy + col0 + r] = *reinterpret_cast<uint16_t *>(&h);
             }
         }
     }
@@ -114,10 +114,15 @@ __global__ void f4_decode_probe_kernel(uint32_t *out_mma, uint32_t *out_f32, uin
 extern "C" int mmb_launch_rowwarp(const mmb_args *a, void *stream)
 {
     dim3 grid(a->plan.grid_x, a->plan.grid_y), block(a->plan.threads);
-    mmb::f4_rowwarp_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint16_t *>(a->x), static_cast<const uint8_t *>(a->payload),
-        static_cast<const uint8_t *>(a->scale), static_cast<uint16_t *>(a->y), a->gs, a->M, a->K,
-        a->N);
+    /* tensor parallel: one launch per destination (this kernel is the untuned fallback) */
+    const uint32_t nd = a->n_dst ? a->n_dst : 1u;
+    for (uint32_t d = 0; d < nd; d++) {
+        uint16_t *y = static_cast<uint16_t *>(a->n_dst ? a->y_dst[d] : a->y);
+        mmb::f4_rowwarp_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const uint16_t *>(a->x), static_cast<const uint8_t *>(a->payload),
+            static_cast<const uint8_t *>(a->scale), y, a->gs, a->M, a->K, a->N,
+            a->n_dst ? a->ldy : a->N, a->n_dst ? a->col0 : 0u);
+    }
     return static_cast<int>(cudaGetLastError());
 }
 

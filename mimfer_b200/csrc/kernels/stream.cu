@@ -45,7 +45,8 @@ namespace mmb {
 
 struct StreamParams {
     const uint16_t *x;
-    uint16_t       *y;
+    uint16_t       *y[MMB_MAX_PEERS];   /* destinations: own output, then peers' (tensor parallel) */
+    uint32_t        n_dst, ldy, col0;    /* row pitch and column offset inside each destination */
     float          *partial;     /* workspace + MMB_WS_COUNTER_B, or NULL */
     unsigned       *counters;    /* workspace base, or NULL               */
     unsigned       *status;
@@ -53,6 +54,14 @@ struct StreamParams {
     uint32_t        M, K, N;
     uint32_t        k_steps, split_k, stages;
 };
+
+/* One output element to every destination (one, or all tensor-parallel peers). */
+__device__ __forceinline__ void store_all(const StreamParams &p, uint32_t m, uint32_t n, uint16_t v)
+{
+    const size_t off = static_cast<size_t>(m) * p.ldy + p.col0 + n;
+    for (uint32_t d = 0; d < p.n_dst; d++)
+        p.y[d][off] = v;
+}
 
 __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                               uint32_t a3, uint32_t b0, uint32_t b1)
@@ -356,7 +365,7 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
                     const uint32_t m = mt * 8u + 2u * t + (i & 1);
                     if (n < p.N && m < p.M) {
                         __nv_bfloat16 hv = __float2bfloat16_rn(acc[rt][mt][i] * out_scale);
-                        p.y[static_cast<size_t>(m) * p.N + n] = *reinterpret_cast<uint16_t *>(&hv);
+                        store_all(p, m, n, *reinterpret_cast<uint16_t *>(&hv));
                     }
                 }
         return;
@@ -431,7 +440,7 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
                 const uint32_t m = mt * 8u + 2u * t + (i & 1);
                 if (n < p.N && m < p.M) {
                     __nv_bfloat16 hv = __float2bfloat16_rn(sum[rt][mt][i] * out_scale);
-                    p.y[static_cast<size_t>(m) * p.N + n] = *reinterpret_cast<uint16_t *>(&hv);
+                    store_all(p, m, n, *reinterpret_cast<uint16_t *>(&hv));
                 }
             }
     if (tid == 0)
@@ -443,7 +452,13 @@ static int launch_mt(const mmb_args *a, unsigned *status, cudaStream_t st)
 {
     StreamParams p;
     p.x = static_cast<const uint16_t *>(a->x);
-    p.y = static_cast<uint16_t *>(a->y);
+    if (a->n_dst) {
+        for (uint32_t d = 0; d < a->n_dst; d++) p.y[d] = static_cast<uint16_t *>(a->y_dst[d]);
+        p.n_dst = a->n_dst; p.ldy = a->ldy; p.col0 = a->col0;
+    } else {
+        p.y[0] = static_cast<uint16_t *>(a->y);
+        p.n_dst = 1; p.ldy = a->N; p.col0 = 0;
+    }
     p.counters = static_cast<unsigned *>(a->ws);
     p.partial = a->ws ? reinterpret_cast<float *>(static_cast<unsigned char *>(a->ws) + MMB_WS_COUNTER_B)
                       : nullptr;

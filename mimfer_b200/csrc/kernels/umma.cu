@@ -33,7 +33,8 @@
 namespace mmb {
 
 struct UmmaParams {
-    uint16_t *y;
+    uint16_t *y[MMB_MAX_PEERS];  /* destinations: own output, then peers' (tensor parallel) */
+    uint32_t  n_dst, ldy, col0;   /* row pitch and column offset inside each destination */
     unsigned *status;
     float     gs;
     uint32_t  M, K, N;
@@ -208,43 +209,66 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
             }
         }
 
-        /* ------------------------------ epilogue --------------------------- */
+        /* ------------------------------ epilogue --------------------------- *
+         * Each warp drains pieces of 32 rows x 128 columns: tensor memory ->
+         * registers -> bf16 -> its own staging tile in shared memory (the
+         * operand stages are free once every MMA has completed), then rows go
+         * out as full 256-byte runs, two rows per warp store, once per
+         * destination.  Whole 128-byte lines matter for the peer copies: the
+         * stores cross NVLink as they are issued. */
         mbar_wait(accum_full, 0u, p.status);
         tc_fence_after();
         const float out_scale = p.gs * 256.0f;      /* undo the 2^-8 of the operand form */
         const uint32_t quad = warp & 3u;            /* TMEM lanes this warp may read   */
         const uint32_t pair = (warp - 2u) >> 2;     /* two warps share a quadrant       */
-        constexpr uint32_t CHUNKS = HALVES * (BN / 32);
-        for (uint32_t c = pair; c < CHUNKS; c += 2u) {
-            const uint32_t h = c / (BN / 32), cc = c % (BN / 32);
-            uint32_t r[32];
-            tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + h * BN + cc * 32u, r);
-            tmem_ld_wait();
-            const uint32_t m = m0 + h * 128u + quad * 32u + lane;
-            const uint32_t n = n0 + cc * 32u;
-            if (m < p.M && n < p.N) {
-                uint16_t *dst = p.y + static_cast<size_t>(m) * p.N + n;
-                if (n + 32u <= p.N) {
+        constexpr uint32_t PIECES = HALVES * (BN / 128);
+        constexpr uint32_t PITCH = 272u;            /* 256 B of data + 16 B: conflict-free both ways */
+        const uint32_t stg = sm_a + (warp - 2u) * (32u * PITCH);
+        const bool vec_ok = (p.N % 8u) == 0;
+        for (uint32_t c = pair; c < PIECES; c += 2u) {
+            const uint32_t h = c / (BN / 128), cc = c % (BN / 128);
+            const uint32_t n_base = n0 + cc * 128u;
 #pragma unroll
-                    for (int v = 0; v < 4; v++) {
-                        uint4 o;
-                        o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]) * out_scale,
-                                          __uint_as_float(r[8 * v + 1]) * out_scale);
-                        o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]) * out_scale,
-                                          __uint_as_float(r[8 * v + 3]) * out_scale);
-                        o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]) * out_scale,
-                                          __uint_as_float(r[8 * v + 5]) * out_scale);
-                        o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]) * out_scale,
-                                          __uint_as_float(r[8 * v + 7]) * out_scale);
-                        *reinterpret_cast<uint4 *>(dst + 8 * v) = o;
-                    }
-                } else {
-                    for (uint32_t e = 0; e < 32u && n + e < p.N; e++) {
-                        __nv_bfloat16 hv = __float2bfloat16_rn(__uint_as_float(r[e]) * out_scale);
-                        dst[e] = *reinterpret_cast<uint16_t *>(&hv);
+            for (uint32_t q = 0; q < 4; q++) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + h * BN + cc * 128u + q * 32u, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int v = 0; v < 4; v++) {
+                    uint4 o;
+                    o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]) * out_scale,
+                                      __uint_as_float(r[8 * v + 1]) * out_scale);
+                    o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]) * out_scale,
+                                      __uint_as_float(r[8 * v + 3]) * out_scale);
+                    o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]) * out_scale,
+                                      __uint_as_float(r[8 * v + 5]) * out_scale);
+                    o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]) * out_scale,
+                                      __uint_as_float(r[8 * v + 7]) * out_scale);
+                    sts128(stg + lane * PITCH + q * 64u + v * 16u, o);
+                }
+            }
+            __syncwarp();
+            const uint32_t sub = lane >> 4, col16 = lane & 15u;      /* 2 rows x 16 chunks per store */
+            const uint32_t n = n_base + col16 * 8u;
+#pragma unroll 4
+            for (uint32_t rr = 0; rr < 32u; rr += 2u) {
+                const uint32_t row = rr + sub;
+                const uint32_t m = m0 + h * 128u + quad * 32u + row;
+                if (m < p.M && n < p.N) {
+                    const uint4 o = lds128(stg + row * PITCH + col16 * 16u);
+                    const size_t off = static_cast<size_t>(m) * p.ldy + p.col0 + n;
+                    if (vec_ok) {
+                        for (uint32_t d = 0; d < p.n_dst; d++)
+                            *reinterpret_cast<uint4 *>(p.y[d] + off) = o;
+                    } else {
+                        const uint32_t w4[4] = { o.x, o.y, o.z, o.w };
+                        for (uint32_t e = 0; e < 8u && n + e < p.N; e++)
+                            for (uint32_t d = 0; d < p.n_dst; d++)
+                                p.y[d][off + e] = static_cast<uint16_t>(w4[e >> 1] >> (16u * (e & 1u)));
                     }
                 }
             }
+            __syncwarp();
         }
     }
 
@@ -260,7 +284,13 @@ template <int BM, int BN>
 static int launch_tile(const mmb_args *a, unsigned *status, cudaStream_t st)
 {
     UmmaParams p;
-    p.y = static_cast<uint16_t *>(a->y);
+    if (a->n_dst) {
+        for (uint32_t d = 0; d < a->n_dst; d++) p.y[d] = static_cast<uint16_t *>(a->y_dst[d]);
+        p.n_dst = a->n_dst; p.ldy = a->ldy; p.col0 = a->col0;
+    } else {
+        p.y[0] = static_cast<uint16_t *>(a->y);
+        p.n_dst = 1; p.ldy = a->N; p.col0 = 0;
+    }
     p.status = status;
     p.gs = a->gs;
     p.M = a->M; p.K = a->K; p.N = a->N;

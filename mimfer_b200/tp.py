@@ -6,8 +6,17 @@ tree), so a shard is a contiguous byte range of each buffer and no 16-wide
 scale group is ever split.  Activations are replicated.  Each rank computes
 y[:, shard] with the single-GPU op, then the slices are all-gathered (NCCL over
 NVLink; gloo on CPU in the tests) into [tp][M][N/tp] and laid out as [M][N].
-The reference has no multi-GPU path; this is new surface.
+
+mode="fused" removes the separate exchange: every rank's full output lives in
+symmetric memory, and the kernel's epilogue stores each finished tile into all
+ranks' copies through peer-mapped pointers (plain stores over NVLink, no
+multicast), so the transfer overlaps the remaining tiles; one cross-rank barrier
+on the stream closes the op.  The reference has no multi-GPU path; this is new
+surface.
 """
+import ctypes as C
+
+from . import _lib as L
 import torch
 import torch.distributed as dist
 
@@ -23,8 +32,12 @@ class TpLinear:
     """`local_op(x, w_shard, y_shard)` computes the shard; by default it is the
     CUDA op enqueued on the runtime's compute stream."""
 
-    def __init__(self, weight, rank, world, rt=None, group=None, local_op=None, max_m=None):
+    def __init__(self, weight, rank, world, rt=None, group=None, local_op=None, mode="gather"):
+        if mode not in ("gather", "fused"):
+            raise ValueError(mode)
         self.rank, self.world, self.group, self.rt = rank, world, group, rt
+        self.mode = mode if world > 1 else "gather"
+        self._symm = {}
         self.N, self.K = weight.N, weight.K
         n0, n1 = shard_bounds(weight.N, rank, world)
         self.shard = weight.rows(n0, n1)
@@ -47,9 +60,34 @@ class TpLinear:
                                  torch.empty((M, self.N), **kw))
         return self._bufs[M]
 
+    def _symm_buffers(self, M, like):
+        """Full output in symmetric memory + the pointer table (own copy first)."""
+        if M not in self._symm:
+            import torch.distributed._symmetric_memory as symm_mem
+            y = symm_mem.empty((M, self.N), dtype=like.dtype, device=like.device)
+            hdl = symm_mem.rendezvous(y, self.group if self.group is not None else dist.group.WORLD)
+            order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+            ptrs = (C.c_void_p * self.world)(*[hdl.buffer_ptrs[r] for r in order])
+            self._symm[M] = (y, hdl, ptrs)
+        return self._symm[M]
+
+    def _forward_fused(self, x):
+        M = x.shape[0]
+        y, hdl, ptrs = self._symm_buffers(M, x)
+        n0 = self.rank * (self.N // self.world)
+        w = self.shard
+        with torch.cuda.stream(self.rt.torch_stream()):
+            L.check(self.rt.lib.mm_f4_linear_tp(x.data_ptr(), w.dev_payload.data_ptr(),
+                                                w.dev_scales.data_ptr(), w.gs, ptrs, self.world,
+                                                self.N, n0, M, w.K, w.N, None), "mm_f4_linear_tp")
+            hdl.barrier(channel=0)              # every rank's stores have landed everywhere
+        return y
+
     def forward(self, x):
         """x: [M][K] replicated.  Returns y [M][N], complete on every rank.
         On CUDA everything is enqueued on the runtime's compute stream."""
+        if self.mode == "fused":
+            return self._forward_fused(x)
         M = x.shape[0]
         y_local, gathered, y = self._buffers(M, x)
         if self.world == 1:                       # nothing to exchange

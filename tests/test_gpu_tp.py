@@ -20,7 +20,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, cases, out_dir):
+def _worker(rank, world, port, cases, out_dir, mode):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -33,7 +33,7 @@ def _worker(rank, world, port, cases, out_dir):
     rt = mm.Runtime.get(rank)
     for i, (M, K, N) in enumerate(cases):
         w = mm.make_weight(N, K, seed=i)
-        lin = TpLinear(w, rank, world, rt=rt)
+        lin = TpLinear(w, rank, world, rt=rt, mode=mode)
         x = rt.to_device_bf16(mm.make_activations(M, K, seed=100 + i))
         y = lin.forward(x)
         rt.sync()
@@ -43,7 +43,8 @@ def _worker(rank, world, port, cases, out_dir):
     dist.destroy_process_group()
 
 
-def test_two_gpu_tensor_parallel_matches_oracle(tmp_path, oracle, lib):
+@pytest.mark.parametrize("mode", ["gather", "fused"])
+def test_two_gpu_tensor_parallel_matches_oracle(tmp_path, oracle, lib, mode):
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
@@ -52,7 +53,7 @@ def test_two_gpu_tensor_parallel_matches_oracle(tmp_path, oracle, lib):
     from conftest import row_rel_l2
     cases = [(1, 1024, 512), (32, 2048, 1024), (300, 512, 1040)]    # decode, decode, prefill kernel
     world = 2
-    mp.spawn(_worker, args=(world, _free_port(), cases, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), cases, str(tmp_path), mode), nprocs=world, join=True)
     for i, (M, K, N) in enumerate(cases):
         w = mm.make_weight(N, K, seed=i)
         x = mm.make_activations(M, K, seed=100 + i)
