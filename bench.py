@@ -39,7 +39,7 @@ sys.path.insert(0, ROOT)
 METRIC = "NVFP4 linear: decode GEMV weight GB/s vs HBM peak (prefill GEMM TFLOP/s in 'prefill')"
 SHAPES = {  # name: (K, N)
     "gate_up": (5120, 34816), "down": (17408, 5120), "q": (5120, 6144), "k": (5120, 1024),
-    "v": (5120, 1024), "o": (6144, 5120), "lm_head": (5120, 151936),
+    "v": (5120, 1024), "o": (6144, 5120), "lm_head": (5120, 151936), "qkv": (5120, 8192),
 }
 DECODE_M = (1, 2, 4, 8, 16)
 PREFILL_M = (512, 2048, 8192)
@@ -256,8 +256,7 @@ class Bench:
         eng.close()
         return {"ms_per_step": ms, "tflops": flops / ms / 1e9, "ops": len(ops), "per_op": per}
 
-    def decode_step_64(self, steps, warmup, layers=64, M=16):
-        names = ("q", "k", "v", "o", "gate_up", "down")
+    def decode_step_64(self, steps, warmup, layers=64, M=16, names=("q", "k", "v", "o", "gate_up", "down")):
         base = {n: self.weight(n) for n in names}
         ops, wb = [], 0
         for layer in range(layers):
@@ -271,6 +270,10 @@ class Bench:
         eng.close()
         return {"layers": layers, "M": M, "ops": len(ops), "weight_bytes": wb,
                 "sum_linear_ms_per_step": ms, "weight_gbs": wb / ms / 1e6}
+
+    def _shard_rows(self, name):
+        per = SHAPES[name][1] // self.world
+        return (self.rank * per, (self.rank + 1) * per)
 
     def tp_series(self, steps, warmup):
         """config 5: gate+up and LM head, sharded along N over all ranks, M=32 and M=8192."""
@@ -297,6 +300,22 @@ class Bench:
                 self.torch.cuda.empty_cache()
             out[mode] = res
             del lins
+        # the sharded kernels alone, no exchange: what the GEMM itself scales like
+        shards = {n: self.dev_weight(self.weight(n, rows=self._shard_rows(n))) for n in ("gate_up", "lm_head")}
+        res = {}
+        for tag, M, st in (("decode_m32", 32, steps), ("prefill_m8192", 8192, max(2, steps // 4))):
+            ops = [(self.acts(M, SHAPES[n][0]), w, self.empty(M, w.N)) for n, w in shards.items()]
+
+            def step():
+                for x, w, y in ops:
+                    self.rt.linear_async(x, w, y)
+            ms = self.timed(step, st, warmup)
+            wb = sum(wbytes(*SHAPES[n]) for n in shards)
+            fl = sum(2.0 * M * SHAPES[n][0] * SHAPES[n][1] for n in shards)
+            res[tag] = {"ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "tflops": fl / ms / 1e9}
+            del ops
+            self.torch.cuda.empty_cache()
+        out["local_only"] = res
         best = modes[0]
         out["mode"] = best + (" (kernel epilogue stores to peers)" if best == "fused" else " (single GPU)")
         out.update(out[best])
@@ -347,6 +366,7 @@ def cpu_baseline(threads=None, target_s=12.0):
 
 def run_b200(args):
     b = Bench(args)
+    b.rt.lib.mm_f4_force_variant(args.variant)
     pk = peaks()
     steps, warmup = args.steps, max(args.warmup, 3)
     line = {"metric": METRIC, "unit": "GB/s", "n_gpus": b.world, "steps": steps, "warmup": warmup,
@@ -385,6 +405,10 @@ def run_b200(args):
             line["prefill"] = pre
             b.torch.cuda.empty_cache()
             line["decode_step"] = b.decode_step_64(steps, warmup)
+            b.torch.cuda.empty_cache()
+            # same weights with q, k and v as one fused op (the reference planner's OP_QKV layout)
+            fused = b.decode_step_64(steps, warmup, names=("qkv", "o", "gate_up", "down"))
+            line["decode_step"]["fused_qkv"] = {k: fused[k] for k in ("ops", "sum_linear_ms_per_step", "weight_gbs")}
             b.torch.cuda.empty_cache()
         tp = b.tp_series(steps, warmup)
         line["tp"] = tp
@@ -461,6 +485,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--case", default="default")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--variant", type=int, default=-1,
+                    help="force a kernel variant for every op (experiments; -1 = selector)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -111,7 +111,9 @@ size_t    mm_f4_workspace_bytes(void);
 typedef enum mm_f4_variant {
     MM_F4_V_ROWWARP = 0,  /* any K%16==0: one warp per weight row, shuffles  */
     MM_F4_V_STREAM  = 1,  /* decode: TMA-staged weight stream + warp MMA     */
-    MM_F4_V_UMMA    = 2   /* prefill: tcgen05 kind::f16, TMEM accumulators   */
+    MM_F4_V_UMMA    = 2,  /* prefill: tcgen05 kind::f16, TMEM accumulators   */
+    MM_F4_V_STREAMT = 3   /* decode: TMA-staged weight stream, weights       */
+                          /*   dequantised into tensor memory, tcgen05 MMA   */
 } mm_f4_variant;
 
 typedef struct mm_f4_shape {
@@ -124,7 +126,8 @@ typedef struct mm_f4_shape {
 typedef struct mm_f4_plan {
     int      variant;         /* mm_f4_variant                                */
     uint32_t m_tiles;         /* STREAM: 8-row activation tiles (1, 2 or 4)   */
-    uint32_t tile_m, tile_n;  /* UMMA: CTA tile; STREAM: tile_n = W rows/CTA  */
+    uint32_t tile_m, tile_n;  /* UMMA: CTA tile; STREAM/STREAMT: tile_n = W   */
+                              /*   rows per CTA, tile_m = padded activation rows */
     uint32_t split_k;         /* >= 1                                         */
     uint32_t k_steps;         /* K / 256 (STREAM) or K / 64 (UMMA)            */
     uint32_t stages;          /* smem pipeline depth                          */

@@ -19,7 +19,7 @@ STATUS_NAMES = ["MM_OK", "MM_ERR_NOMEM", "MM_ERR_IO", "MM_ERR_CORRUPT", "MM_ERR_
 
 OP_GEMM_F4, OP_GEMM_BF16, OP_QKV, OP_NOP = 4, 5, 6, 18
 MM_ST_COMPUTE, MM_ST_XFER = 0, 1
-V_ROWWARP, V_STREAM, V_UMMA = 0, 1, 2
+V_ROWWARP, V_STREAM, V_UMMA, V_STREAMT = 0, 1, 2, 3
 
 
 class MmOpDesc(C.Structure):

@@ -20,7 +20,7 @@ NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 
 C_SOURCES = ["core/core.c", "pack/pack.c", "plan/select.c", "engine/engine.c",
              "cuda/rt.c", "cuda/kx_gemm_f4.c"]
-CU_SOURCES = ["kernels/rowwarp.cu", "kernels/stream.cu", "kernels/umma.cu"]
+CU_SOURCES = ["kernels/rowwarp.cu", "kernels/stream.cu", "kernels/streamt.cu", "kernels/umma.cu"]
 HEADERS = ["core/core.h", "kernels/launch.h", "kernels/ptx.cuh", "kernels/fp4.cuh",
            "../../include/mimfer_abi.h", "../../include/mimfer_b200.h"]
 

@@ -18,6 +18,7 @@
 
 int mmb_stream_init(void);
 int mmb_umma_init(void);
+int mmb_streamt_init(void);
 
 /* ------------------------------------------------------------------ state */
 typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
@@ -129,6 +130,7 @@ static mm_status ensure_ready(void)
     G.encode = (encode_fn)fn;
     CK((cudaError_t)mmb_stream_init());
     CK((cudaError_t)mmb_umma_init());
+    CK((cudaError_t)mmb_streamt_init());
     CK((cudaError_t)mmb_status_word(&G.status_dev));
     CK(cudaHostAlloc((void **)&G.status_host, 64, cudaHostAllocDefault));
     *G.status_host = 0;
@@ -226,6 +228,15 @@ static mm_status linear_impl(const void *x, const void *payload, const void *sca
         MM_CHECK(encode_2d(a.tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, MMB_ST_KSTEP,
                            a.plan.tile_m, CU_TENSOR_MAP_SWIZZLE_NONE));
         err = mmb_launch_stream(&a, stream);
+        break;
+    case MM_F4_V_STREAMT:
+        MM_CHECK(encode_2d(a.tm_payload, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, payload, K / 2, N, 128,
+                           MMB_ST_ROWS, CU_TENSOR_MAP_SWIZZLE_128B));
+        MM_CHECK(encode_2d(a.tm_scale, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, scale, K / 16, N, 16,
+                           MMB_ST_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE));
+        MM_CHECK(encode_2d(a.tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, 64,
+                           a.plan.tile_m, CU_TENSOR_MAP_SWIZZLE_128B));
+        err = mmb_launch_streamt(&a, stream);
         break;
     case MM_F4_V_UMMA:
         MM_CHECK(encode_2d(a.tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, MMB_UM_KBLOCK,

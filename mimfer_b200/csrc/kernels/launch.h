@@ -26,6 +26,12 @@ extern "C" {
 #define MMB_ST_STAGE_B(mt) (MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B + MMB_ST_X_B(mt))
 #define MMB_ST_FIXED_B     (2048u /* two scale LUTs */ + 512u /* barriers, flags */ + 1024u /* align slack */)
 
+/* ---- STREAM-T (decode on tcgen05, weights through tensor memory) ------------- */
+#define MMB_STT_DEQ_WARPS   16u    /* thread <-> weight row, 2 tiles x 4 quadrants x 2 K quarters */
+#define MMB_STT_XFORM_WARPS 4u
+#define MMB_STT_THREADS     ((MMB_STT_DEQ_WARPS + 3u + MMB_STT_XFORM_WARPS) * 32u)   /* + TMA, 2 x MMA */
+#define MMB_STT_STAGE_B(npad) (MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B + (npad) * 512u)
+
 /* ---- UMMA (prefill) geometry ---------------------------------------------- */
 #define MMB_UM_KBLOCK      64u    /* bf16 elements per smem row (128 B swizzle) */
 #define MMB_UM_KGROUP      256u   /* weights covered by one scale box (16 B)    */
@@ -80,6 +86,7 @@ typedef struct mmb_args {
 int mmb_launch_rowwarp(const mmb_args *a, void *stream);
 int mmb_launch_stream(const mmb_args *a, void *stream);
 int mmb_launch_umma(const mmb_args *a, void *stream);
+int mmb_launch_streamt(const mmb_args *a, void *stream);
 int mmb_launch_decode_probe(uint32_t *out_mma, uint32_t *out_f32, uint32_t *out_f16, void *stream);
 /* One-time per-process setup (smem opt-in attributes). */
 int mmb_kernels_init(void);

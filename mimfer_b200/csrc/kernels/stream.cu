@@ -205,17 +205,32 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
         static_cast<uint64_t>(p.k_steps) * (blockIdx.y + 1) / p.split_k);
     const uint32_t nsteps = ks_end - ks_begin;
 
-    if (tid < 256u) {
-        sts32(lut_bf + tid * 4u, scale_lut_entry(tid));
-        sts32(lut_hf + tid * 4u, scale_lut_entry_f16(tid));
-    }
-    if (tid == 0) {
+    const uint32_t stage_bytes = MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B + MMB_ST_X_RAW_B(MT);
+    const uint32_t first = nsteps < p.stages ? nsteps : p.stages;   /* steps of the first ring */
+    if (tid == MMB_ST_CONSUMERS * 32u) {
+        /* the issuing thread sets the barriers up itself and starts the weight
+         * stream at once, while the other warps are still building the tables */
+        tma_prefetch_desc(&tm_payload);
+        tma_prefetch_desc(&tm_scale);
+        tma_prefetch_desc(&tm_x);
         for (uint32_t s = 0; s < p.stages; s++) {
             mbar_init(bar_raw + 8u * s, 1u);
             mbar_init(bar_full + 8u * s, XFORM_THREADS);
             mbar_init(bar_empty + 8u * s, MMB_ST_CONSUMERS);
         }
         mbar_fence_init();
+        for (uint32_t it = 0; it < first; it++) {
+            const uint32_t stage = base + it * STAGE_B, ks = ks_begin + it;
+            mbar_expect_tx(bar_raw + 8u * it, stage_bytes);
+            tma_load_2d(stage, &tm_payload, static_cast<int>(ks * 128u),
+                        static_cast<int>(row0), bar_raw + 8u * it);
+            tma_load_2d(stage + MMB_ST_PAYLOAD_B, &tm_scale, static_cast<int>(ks * 16u),
+                        static_cast<int>(row0), bar_raw + 8u * it);
+        }
+    }
+    if (tid < 256u) {
+        sts32(lut_bf + tid * 4u, scale_lut_entry(tid));
+        sts32(lut_hf + tid * 4u, scale_lut_entry_f16(tid));
     }
     __syncthreads();
     grid_dep_launch();
@@ -223,19 +238,10 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
     if (warp == MMB_ST_CONSUMERS) {
         /* ------------------------------ TMA issue ------------------------- *
          * The weights do not depend on the previous kernel in the stream, the
-         * activations may: the first ring of weight boxes is issued before the
-         * grid-dependency wait, the activation boxes after it. */
+         * activations may: the first ring of weight boxes went out in the
+         * prologue, before the grid-dependency wait, the activation boxes
+         * follow it. */
         if (lane == 0) {
-            const uint32_t stage_bytes = MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B + MMB_ST_X_RAW_B(MT);
-            const uint32_t first = nsteps < p.stages ? nsteps : p.stages;
-            for (uint32_t it = 0; it < first; it++) {
-                const uint32_t stage = base + it * STAGE_B, ks = ks_begin + it;
-                mbar_expect_tx(bar_raw + 8u * it, stage_bytes);
-                tma_load_2d(stage, &tm_payload, static_cast<int>(ks * 128u),
-                            static_cast<int>(row0), bar_raw + 8u * it);
-                tma_load_2d(stage + MMB_ST_PAYLOAD_B, &tm_scale, static_cast<int>(ks * 16u),
-                            static_cast<int>(row0), bar_raw + 8u * it);
-            }
             grid_dep_wait();
             for (uint32_t it = 0; it < first; it++)
                 tma_load_2d(base + it * STAGE_B + MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B, &tm_x,

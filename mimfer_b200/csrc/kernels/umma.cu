@@ -80,6 +80,7 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
      * tiles (and all of x) through L2 instead of each streaming the whole weight */
     const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
     const uint32_t KB = p.k_blocks;
+    const uint32_t pre_pay = KB < PAY_SLOTS ? KB : PAY_SLOTS;   /* payload boxes issued in the prologue */
 
     if (tid < 256u)
         sts32(lut + tid * 4u, scale_lut_entry(tid));
@@ -99,6 +100,18 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
         }
         mbar_init(accum_full, 1u);
         mbar_fence_init();
+        /* this thread is also the TMA producer: the first weight boxes go out now,
+         * ahead of the table build, the TMEM allocation and the grid-dependency wait */
+        tma_prefetch_desc(&tm_x);
+        tma_prefetch_desc(&tm_payload);
+        tma_prefetch_desc(&tm_scale);
+        for (uint32_t kb = 0; kb < pre_pay; kb++) {
+            mbar_expect_tx(full_pay + 8u * kb, PAY_B);
+            tma_load_2d(sm_pay + kb * PAY_B, &tm_payload, static_cast<int>(kb * 32u),
+                        static_cast<int>(n0), full_pay + 8u * kb);
+        }
+        mbar_expect_tx(full_sc, SC_B);
+        tma_load_2d(sm_sc, &tm_scale, 0, static_cast<int>(n0), full_sc);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, TMEM_COLS);
@@ -113,17 +126,9 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
     if (warp == 0) {
         /* ------------------------------ TMA producer ---------------------- *
          * Weights do not depend on the previous kernel in the stream, the
-         * activations may: the first payload and scale boxes go out before the
-         * grid-dependency wait, the first activation box after it. */
+         * activations may: the first payload and scale boxes went out in the
+         * prologue, the first activation box follows the grid-dependency wait. */
         if (lane == 0) {
-            const uint32_t pre_pay = KB < PAY_SLOTS ? KB : PAY_SLOTS;
-            for (uint32_t kb = 0; kb < pre_pay; kb++) {
-                mbar_expect_tx(full_pay + 8u * kb, PAY_B);
-                tma_load_2d(sm_pay + kb * PAY_B, &tm_payload, static_cast<int>(kb * 32u),
-                            static_cast<int>(n0), full_pay + 8u * kb);
-            }
-            mbar_expect_tx(full_sc, SC_B);
-            tma_load_2d(sm_sc, &tm_scale, 0, static_cast<int>(n0), full_sc);
             grid_dep_wait();
             uint32_t s = 0, round = 0;                 /* A/B stage index and its use count */
             for (uint32_t kb = 0; kb < KB; kb++, s = (s + 1u == ST) ? 0u : s + 1u, round += (s == 0u)) {

@@ -81,6 +81,37 @@ static mm_status plan_stream(const mm_f4_shape *s, mm_f4_plan *p)
     return MM_OK;
 }
 
+static mm_status plan_streamt(const mm_f4_shape *s, mm_f4_plan *p)
+{
+    /* same decomposition as STREAM; the activation rows are padded to the
+     * tensor-core N extent (16 or 32) instead of to 8-row MMA tiles */
+    mm_status st = plan_stream(s, p);
+    if (st != MM_OK)
+        return st;
+    p->variant = MM_F4_V_STREAMT;
+    p->tile_m = s->M <= 16 ? 16 : 32;
+    p->m_tiles = p->tile_m / 8;
+    p->threads = MMB_STT_THREADS;
+    uint32_t sk = p->split_k;
+    p->ws_needed = 0;
+    while (sk > 1) {
+        size_t need = MMB_WS_COUNTER_B + (size_t)sk * p->tile_m * s->N * 4u;
+        if (need <= s->ws_bytes) { p->ws_needed = need; break; }
+        sk--;
+    }
+    p->split_k = sk;
+    p->grid_y = sk;
+    uint32_t stage = MMB_STT_STAGE_B(p->tile_m);
+    uint32_t stg = (MMB_SMEM_MAX - MMB_ST_FIXED_B) / stage;
+    if (stg > 6) stg = 6;
+    uint32_t per = ceil_div(p->k_steps, sk);
+    if (stg > per) stg = per;
+    if (stg < 1) stg = 1;
+    p->stages = stg;
+    p->smem_bytes = stg * stage + MMB_ST_FIXED_B;
+    return MM_OK;
+}
+
 /* modelled cost of one CTA tile, arbitrary units: MMA time grows with
  * tile_m*tile_n; narrow tiles run the tensor pipe less efficiently because
  * operand traffic per MAC rises. */
@@ -142,6 +173,7 @@ mm_status mm_f4_select_variant(const mm_f4_shape *s, int variant, mm_f4_plan *ou
     case MM_F4_V_ROWWARP: plan_rowwarp(s, out); return MM_OK;
     case MM_F4_V_STREAM:  return plan_stream(s, out);
     case MM_F4_V_UMMA:    return plan_umma(s, out);
+    case MM_F4_V_STREAMT: return plan_streamt(s, out);
     default:              return MM_ERR_RANGE;
     }
 }
