@@ -359,6 +359,9 @@ def cpu_baseline(threads=None, target_s=12.0):
     dt, _ = sweep(probe_rows)
     rows = int(min(34816, max(probe_rows, probe_rows * target_s / max(dt, 1e-6))))
     dt, nbytes = sweep(rows)
+    while dt < 0.8 * target_s:                     # few rows left to add: repeat the sweep instead
+        d2, n2 = sweep(rows)
+        dt, nbytes = dt + d2, nbytes + n2
     return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
             "sample": f"decode sweep M in {{1,2,4,8,16}} on the first {rows} rows of gate+up and of down, "
                       f"{dt:.1f} s of CPU time"}
@@ -439,6 +442,14 @@ def run_case(b, case, steps, warmup):
     """Single small cases, used for profiling one kernel at a time."""
     if case == "decode":           # gate+up at M=1 and M=16, two weight copies each
         res, _, eng = b.decode_sweep(steps, warmup, ms_list=(1, 16), names=("gate_up",))
+        eng.close()
+        return res
+    if case == "decode_m32":       # gate+up at M=32, two weight copies
+        res, _, eng = b.decode_sweep(steps, warmup, ms_list=(32, 32), names=("gate_up",))
+        eng.close()
+        return res
+    if case == "decode_m16":
+        res, _, eng = b.decode_sweep(steps, warmup, ms_list=(16, 16), names=("gate_up", "down"))
         eng.close()
         return res
     if case == "decode_down":

@@ -401,8 +401,8 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
         return;
     __threadfence();
     /* Slices are added in ascending order for every output, so the sum does not
-     * depend on which CTA arrived last; the loads of one slice (all outputs of
-     * this thread) are issued together, slices two at a time. */
+     * depend on which CTA arrived last; the loads of several slices (all
+     * outputs of this thread) are issued together. */
     float sum[RT][MT][4];
 #pragma unroll
     for (int rt = 0; rt < RT; rt++)
@@ -410,10 +410,11 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
         for (int mt = 0; mt < MT; mt++)
 #pragma unroll
             for (int i = 0; i < 4; i++) sum[rt][mt][i] = 0.0f;
-    for (uint32_t sl = 0; sl < p.split_k; sl += 2u) {
-        float v[2][RT][MT][4];
+    constexpr int BATCH = 8 / MT;                 /* slices whose loads are in flight together */
+    for (uint32_t sl = 0; sl < p.split_k; sl += BATCH) {
+        float v[BATCH][RT][MT][4];
 #pragma unroll
-        for (int u = 0; u < 2; u++)
+        for (int u = 0; u < BATCH; u++)
 #pragma unroll
             for (int rt = 0; rt < RT; rt++)
 #pragma unroll
@@ -428,7 +429,7 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
                                 __ldcg(p.partial + (static_cast<size_t>(sl + u) * MPAD + m) * p.N + n);
                     }
 #pragma unroll
-        for (int u = 0; u < 2; u++)
+        for (int u = 0; u < BATCH; u++)
 #pragma unroll
             for (int rt = 0; rt < RT; rt++)
 #pragma unroll

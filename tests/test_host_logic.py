@@ -94,3 +94,15 @@ def test_runtime_refuses_without_gpu(lib):
     with pytest.raises(RuntimeError):
         mimfer_b200.Runtime(0)
     assert lib.mm_cuda_stream_raw(0) is None and lib.mm_cuda_capturing() == 0
+
+
+def test_tensor_parallel_entry_point_validates_arguments(lib):
+    lib.mm_log_set_level(-1)
+    ptrs = (C.c_void_p * 2)(0x1000, 0x2000)
+    bad = (C.c_void_p * 2)(0x1000, 0x2008)              # peer copy not 16-byte aligned
+    assert lib.mm_f4_linear_tp(1, 1, 1, 1.0, None, 2, 512, 0, 1, 256, 256, None) == L.MM_ERR_RANGE
+    assert lib.mm_f4_linear_tp(1, 1, 1, 1.0, ptrs, 9, 512, 0, 1, 256, 256, None) == L.MM_ERR_RANGE
+    assert lib.mm_f4_linear_tp(1, 1, 1, 1.0, bad, 2, 512, 0, 1, 256, 256, None) == L.MM_ERR_STATE
+    assert lib.mm_f4_linear_tp(1, 1, 1, 1.0, ptrs, 2, 512, 384, 1, 256, 256, None) == L.MM_ERR_SHAPE
+    assert lib.mm_f4_linear_tp(1, 1, 1, 1.0, ptrs, 2, 512, 0, 1, 24, 256, None) == L.MM_ERR_SHAPE
+    lib.mm_log_set_level(1)

@@ -2,7 +2,7 @@
 import pytest
 
 import mimfer_b200 as mm
-from mimfer_b200 import V_ROWWARP, V_STREAM, V_UMMA
+from mimfer_b200 import V_ROWWARP, V_STREAM, V_UMMA, V_STREAMT
 
 WS = 64 << 20
 SMEM_MAX = 232448
@@ -61,3 +61,16 @@ def test_errors(lib):
     with pytest.raises(mm.MimferError) as e:
         mm.select_plan(4, 48, 64, variant=V_UMMA)
     assert e.value.status == 7
+
+
+def test_streamt_plan_mirrors_stream_decomposition(lib):
+    for M in (1, 9, 16, 17, 32):
+        a = mm.select_plan(M, 17408, 5120, ws_bytes=WS, variant=V_STREAM)
+        b = mm.select_plan(M, 17408, 5120, ws_bytes=WS, variant=V_STREAMT)
+        assert b.variant == V_STREAMT and b.tile_m == (16 if M <= 16 else 32)
+        assert (b.grid_x, b.k_steps, b.tile_n) == (a.grid_x, a.k_steps, a.tile_n)
+        assert b.split_k >= 1 and b.smem_bytes <= SMEM_MAX and b.threads == 736
+        if b.split_k > 1:
+            assert b.ws_needed == 16384 + b.split_k * b.tile_m * 5120 * 4
+    with pytest.raises(mm.MimferError):
+        mm.select_plan(64, 512, 64, variant=V_STREAMT)
