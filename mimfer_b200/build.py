@@ -27,7 +27,8 @@ HEADERS = ["core/core.h", "kernels/launch.h", "kernels/ptx.cuh", "kernels/fp4.cu
 CFLAGS = ["-std=c11", "-O2", "-fPIC", "-fopenmp", "-Wall", "-Wextra", "-Werror",
           "-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(CUDA_HOME, "include")]
 NVFLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
-           "-Xcompiler", "-fPIC", "-I" + os.path.join(ROOT, "include")]
+           "-Xcompiler", "-fPIC", "-I" + os.path.join(ROOT, "include"),
+           *os.environ.get("MMB_EXTRA_NVFLAGS", "").split()]
 
 
 def _stale(target, deps):

@@ -79,6 +79,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
     }
 }
 
+/* Warp-wide wait with one poller: lane 0 waits, the warp reconverges.  Thirty-two
+ * lanes polling one barrier word cost a few hundred cycles even when the phase
+ * has long completed. */
+__device__ __forceinline__ void mbar_wait_warp(uint32_t bar, uint32_t parity, unsigned *status)
+{
+    if ((threadIdx.x & 31u) == 0)
+        mbar_wait(bar, parity, status);
+    __syncwarp();
+}
+
 /* ---- TMA (2-D tiled loads, completion on an mbarrier) -------------------- */
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const TmaDesc *map, int x, int y,
                                             uint32_t bar)

@@ -272,7 +272,7 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
         for (uint32_t it = 0; it < nsteps; it++, s = (s + 1u == p.stages) ? 0u : s + 1u,
                                            round += (s == 0u)) {
             const uint32_t xs = base + s * STAGE_B + MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B;
-            mbar_wait(bar_raw + 8u * s, round & 1u, p.status);
+            mbar_wait_warp(bar_raw + 8u * s, round & 1u, p.status);
             uint4 v[ITEMS];
             uint32_t ok = 0xffffffffu;
 #pragma unroll
@@ -336,7 +336,7 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
     for (uint32_t it = 0; it < nsteps; it++, s = (s + 1u == p.stages) ? 0u : s + 1u,
                                        round += (s == 0u)) {
         const uint32_t stage = base + s * STAGE_B;
-        mbar_wait(bar_full + 8u * s, round & 1u, p.status);
+        mbar_wait_warp(bar_full + 8u * s, round & 1u, p.status);
         if (lds32(fmt_flag + 4u * s) != 0u)
             consume_step<MT, RT, SLOTS, true>(accs, stage, lut_hf, warp, g, t);
         else

@@ -22,10 +22,10 @@
  * bf16 slice in place), bf16 otherwise; both are exact, both add into the same
  * accumulators.
  *
- * Tensor memory map (512 columns allocated): four accumulators for each of the
- * two 128-row tiles at columns [0, 256) (consecutive MMAs rotate over them, so
- * none waits for the previous one's accumulate); two A slots of 128 columns each
- * (2 tiles x 64 columns = 128 K values per row) at [256, 512).  A slot holds
+ * Tensor memory map (512 columns allocated): two accumulators for each of the
+ * two 128-row tiles at columns [0, 128) (consecutive MMAs alternate between them,
+ * so none waits for the previous one's accumulate); three A slots of 128 columns
+ * each (2 tiles x 64 columns = 128 K values per row) at [128, 512).  A slot holds
  * half a K step.
  *
  * It replaces the one-thread-per-output kernel of the reference
@@ -47,10 +47,11 @@ struct StreamTParams {
     uint32_t  k_steps, split_k, stages;
 };
 
-constexpr uint32_t ST_NACC = 4u;           /* independent accumulators per tile: consecutive MMAs
+constexpr uint32_t ST_NACC = 2u;           /* independent accumulators per tile: consecutive MMAs
                                               never chain on one accumulator; summed in order at the end */
-constexpr uint32_t ST_D_COL = 0u;          /* accumulator a of tile t at (t * ST_NACC + a) * NPAD, <= 256 columns */
-constexpr uint32_t ST_A_COL = 256u;        /* A slot s, tile t at ST_A_COL + s * 128 + t * 64 */
+constexpr uint32_t ST_D_COL = 0u;          /* accumulator a of tile t at (t * ST_NACC + a) * NPAD, <= 128 columns */
+constexpr uint32_t ST_A_COL = 128u;        /* A slot s, tile t at ST_A_COL + s * 128 + t * 64 */
+constexpr uint32_t ST_A_SLOTS = 3u;        /* each holds half a K step for both tiles */
 constexpr uint32_t ST_TMEM_COLS = 512u;
 
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32])
@@ -153,9 +154,9 @@ f4_streamt_kernel(const __grid_constant__ TmaDesc tm_payload,
     const uint32_t bar_raw = lut_hf + 1024u;               /* [stages] TMA landed                 */
     const uint32_t bar_x = bar_raw + 8u * p.stages;        /* [stages] activations converted       */
     const uint32_t bar_empty = bar_x + 8u * p.stages;      /* [stages] MMAs of the stage complete  */
-    const uint32_t a_full = bar_empty + 8u * p.stages;     /* [2] A slot written                   */
-    const uint32_t a_empty = a_full + 16u;                 /* [2] A slot consumed                  */
-    const uint32_t accum_full = a_empty + 16u;
+    const uint32_t a_full = bar_empty + 8u * p.stages;     /* [slots] A slot written               */
+    const uint32_t a_empty = a_full + 8u * ST_A_SLOTS;     /* [slots] A slot consumed              */
+    const uint32_t accum_full = a_empty + 8u * ST_A_SLOTS;
     const uint32_t fmt_flag = accum_full + 8u;             /* [stages] 1 = fp16 step               */
     const uint32_t tmem_slot = fmt_flag + 4u * p.stages;
     const uint32_t last_flag = tmem_slot + 4u;
@@ -185,7 +186,7 @@ f4_streamt_kernel(const __grid_constant__ TmaDesc tm_payload,
             mbar_init(bar_x + 8u * s, XFORM_THREADS);
             mbar_init(bar_empty + 8u * s, 2u);                 /* one commit per issuing thread */
         }
-        for (uint32_t s = 0; s < 2u; s++) {
+        for (uint32_t s = 0; s < ST_A_SLOTS; s++) {
             mbar_init(a_full + 8u * s, MMB_STT_DEQ_WARPS);
             mbar_init(a_empty + 8u * s, 2u);
         }
@@ -247,7 +248,7 @@ f4_streamt_kernel(const __grid_constant__ TmaDesc tm_payload,
             const uint32_t t = warp - (MMB_STT_DEQ_WARPS + 1u);
             const uint32_t d_base = tmem_base + ST_D_COL + t * ST_NACC * NPAD;
             const uint32_t a_base = tmem_base + ST_A_COL + t * 64u;
-            uint32_t s = 0, round = 0, half_idx = 0;
+            uint32_t s = 0, round = 0, half_idx = 0, slot = 0, use = 0;   /* A slot and its use count */
             for (uint32_t it = 0; it < nsteps; it++, s = (s + 1u == p.stages) ? 0u : s + 1u,
                                                round += (s == 0u)) {
                 const uint32_t xs = base + s * STAGE_B + MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B;
@@ -255,9 +256,9 @@ f4_streamt_kernel(const __grid_constant__ TmaDesc tm_payload,
                 const uint32_t idesc = umma_idesc_16(128u, NPAD, lds32(fmt_flag + 4u * s) ? 0u : 1u);
                 const uint64_t bd0 = umma_desc_sw128(xs);
 #pragma unroll
-                for (uint32_t kh = 0; kh < 2u; kh++, half_idx++) {
-                    const uint32_t slot = half_idx & 1u;
-                    mbar_wait(a_full + 8u * slot, (half_idx >> 1) & 1u, p.status);
+                for (uint32_t kh = 0; kh < 2u; kh++, half_idx++,
+                              slot = (slot + 1u == ST_A_SLOTS) ? 0u : slot + 1u, use += (slot == 0u)) {
+                    mbar_wait(a_full + 8u * slot, use & 1u, p.status);
                     tc_fence_after();
                     const uint32_t a_slot = a_base + slot * 128u;
                     const uint32_t fresh = half_idx == 0 ? 0u : 1u;   /* very first use of the accumulators */
@@ -284,7 +285,7 @@ f4_streamt_kernel(const __grid_constant__ TmaDesc tm_payload,
         for (uint32_t it = 0; it < nsteps; it++, s = (s + 1u == p.stages) ? 0u : s + 1u,
                                            round += (s == 0u)) {
             const uint32_t xs = base + s * STAGE_B + MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B;
-            mbar_wait(bar_raw + 8u * s, round & 1u, p.status);
+            mbar_wait_warp(bar_raw + 8u * s, round & 1u, p.status);
             uint4 v[X_ITEMS];
             uint32_t ok = 0xffffffffu;
 #pragma unroll
@@ -321,18 +322,18 @@ f4_streamt_kernel(const __grid_constant__ TmaDesc tm_payload,
         const uint32_t quad = warp & 3u, tile = (warp >> 2) & 1u, kq = warp >> 3;
         const uint32_t row = tile * 128u + quad * 32u + lane;            /* row within the CTA */
         const uint32_t lane_addr = (quad * 32u) << 16;
-        uint32_t s = 0, round = 0, half_idx = 0;
+        uint32_t s = 0, round = 0, slot = 0, use = 0;
         for (uint32_t it = 0; it < nsteps; it++, s = (s + 1u == p.stages) ? 0u : s + 1u,
                                            round += (s == 0u)) {
             const uint32_t stage = base + s * STAGE_B;
-            mbar_wait(bar_raw + 8u * s, round & 1u, p.status);    /* weights and scales landed */
-            mbar_wait(bar_x + 8u * s, round & 1u, p.status);      /* operand format of the step known */
+            mbar_wait_warp(bar_raw + 8u * s, round & 1u, p.status);   /* weights and scales landed */
+            mbar_wait_warp(bar_x + 8u * s, round & 1u, p.status);     /* operand format of the step known */
             const bool half_step = lds32(fmt_flag + 4u * s) != 0u;
             const uint32_t lut = half_step ? lut_hf : lut_bf;
             const uint4 sc16 = lds128(stage + MMB_ST_PAYLOAD_B + row * 16u);
 #pragma unroll
-            for (uint32_t kh = 0; kh < 2u; kh++, half_idx++) {
-                const uint32_t slot = half_idx & 1u;
+            for (uint32_t kh = 0; kh < 2u; kh++,
+                          slot = (slot + 1u == ST_A_SLOTS) ? 0u : slot + 1u, use += (slot == 0u)) {
                 /* 64 weights: K offset kh*128 + kq*64 of the step = payload chunks 4kh+2kq, +1 */
                 const uint32_t c0 = 4u * kh + 2u * kq;
                 const uint4 p0 = lds128(stage + row * 128u + (((c0 + 0u) ^ (row & 7u)) << 4));
@@ -345,8 +346,8 @@ f4_streamt_kernel(const __grid_constant__ TmaDesc tm_payload,
                 uint32_t out[32];
                 if (half_step) dequant64<true>(p0, p1, c, out);
                 else           dequant64<false>(p0, p1, c, out);
-                if (half_idx >= 2u)
-                    mbar_wait(a_empty + 8u * slot, ((half_idx >> 1) - 1u) & 1u, p.status);
+                if (use > 0u)
+                    mbar_wait_warp(a_empty + 8u * slot, (use - 1u) & 1u, p.status);
                 tc_fence_after();
                 tmem_st_32x32(tmem_base + lane_addr + ST_A_COL + slot * 128u + tile * 64u + kq * 32u, out);
                 tmem_st_wait();
@@ -358,7 +359,7 @@ f4_streamt_kernel(const __grid_constant__ TmaDesc tm_payload,
         }
 
         /* ------------------------------ epilogue ------------------------------ */
-        mbar_wait(accum_full, 0u, p.status);
+        mbar_wait_warp(accum_full, 0u, p.status);
         tc_fence_after();
         if (kq == 0) {                                   /* one warp per (tile, lane quadrant) */
             uint32_t acc[NPAD];

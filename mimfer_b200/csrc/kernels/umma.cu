@@ -184,10 +184,10 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
             const uint32_t ps = kb % PAY_SLOTS;
             const uint32_t grp = kb >> 2, ss = grp % MMB_UM_SC_SLOTS, j = kb & 3u;
             if (j == 0)
-                mbar_wait(full_sc + 8u * ss, (grp / MMB_UM_SC_SLOTS) & 1u, p.status);
-            mbar_wait(full_pay + 8u * ps, (kb / PAY_SLOTS) & 1u, p.status);
+                mbar_wait_warp(full_sc + 8u * ss, (grp / MMB_UM_SC_SLOTS) & 1u, p.status);
+            mbar_wait_warp(full_pay + 8u * ps, (kb / PAY_SLOTS) & 1u, p.status);
             if (round > 0)
-                mbar_wait(empty_ab + 8u * s, (round - 1u) & 1u, p.status);
+                mbar_wait_warp(empty_ab + 8u * s, (round - 1u) & 1u, p.status);
             const uint32_t pay = sm_pay + ps * PAY_B, scl = sm_sc + ss * SC_B;
             const uint32_t bt = sm_b + s * B_B;
 #pragma unroll
@@ -221,7 +221,7 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
          * out as full 256-byte runs, two rows per warp store, once per
          * destination.  Whole 128-byte lines matter for the peer copies: the
          * stores cross NVLink as they are issued. */
-        mbar_wait(accum_full, 0u, p.status);
+        mbar_wait_warp(accum_full, 0u, p.status);
         tc_fence_after();
         const float out_scale = p.gs * 256.0f;      /* undo the 2^-8 of the operand form */
         const uint32_t quad = warp & 3u;            /* TMEM lanes this warp may read   */
