@@ -370,6 +370,9 @@ def cpu_baseline(threads=None, target_s=12.0):
 def run_b200(args):
     b = Bench(args)
     b.rt.lib.mm_f4_force_variant(args.variant)
+    for kv in args.tune:
+        k, v = kv.split("=")
+        b.rt.lib.mm_f4_tune(int(k), int(v))
     pk = peaks()
     steps, warmup = args.steps, max(args.warmup, 3)
     line = {"metric": METRIC, "unit": "GB/s", "n_gpus": b.world, "steps": steps, "warmup": warmup,
@@ -496,6 +499,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--case", default="default")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
+                    help="set a library tuning knob (mm_f4_tune), e.g. 2=1; experiments only")
     ap.add_argument("--variant", type=int, default=-1,
                     help="force a kernel variant for every op (experiments; -1 = selector)")
     args = ap.parse_args()

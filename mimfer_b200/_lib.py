@@ -7,7 +7,7 @@ import ctypes as C
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "libmimfer_b200.so")
+LIB_PATH = os.environ.get("MIMFER_B200_LIB", os.path.join(PKG, "libmimfer_b200.so"))
 
 MM_OK = 0
 STATUS_NAMES = ["MM_OK", "MM_ERR_NOMEM", "MM_ERR_IO", "MM_ERR_CORRUPT", "MM_ERR_SHAPE",

@@ -14,7 +14,8 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "build")
-LIB = os.path.join(PKG, "libmimfer_b200.so")
+LIB = os.environ.get("MMB_BUILD_LIB", os.path.join(PKG, "libmimfer_b200.so"))
+OBJ = os.environ.get("MMB_BUILD_OBJ", OBJ)
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 

@@ -79,14 +79,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
     }
 }
 
-/* Warp-wide wait with one poller: lane 0 waits, the warp reconverges.  Thirty-two
- * lanes polling one barrier word cost a few hundred cycles even when the phase
- * has long completed. */
+/* Wait executed by every lane of the calling warp.  (Electing one poller and
+ * re-converging with __syncwarp was measured 3-4 % slower on the decode
+ * kernels: the reconvergence costs more than 32 lanes polling a completed
+ * barrier.) */
 __device__ __forceinline__ void mbar_wait_warp(uint32_t bar, uint32_t parity, unsigned *status)
 {
-    if ((threadIdx.x & 31u) == 0)
-        mbar_wait(bar, parity, status);
-    __syncwarp();
+    mbar_wait(bar, parity, status);
 }
 
 /* ---- TMA (2-D tiled loads, completion on an mbarrier) -------------------- */

@@ -39,7 +39,12 @@ def reference():
 @pytest.fixture(scope="session")
 def rt(lib):
     import mimfer_b200
-    return mimfer_b200.Runtime.get(0)
+    r = mimfer_b200.Runtime.get(0)
+    for kv in os.environ.get("MIMFER_TUNE", "").split(","):      # e.g. MIMFER_TUNE=2=1 for experiments
+        if "=" in kv:
+            k, v = kv.split("=")
+            r.lib.mm_f4_tune(int(k), int(v))
+    return r
 
 
 def bf16_bits_to_f32(bits):
