@@ -215,6 +215,12 @@ unsigned long long mm_f4_launch_count(int reset);
 mm_status mm_f4_decode_probe(uint32_t *out_bf16_dev, uint32_t *out_f32_dev,
                              uint32_t *out_f16_dev);
 
+/* Self test of the bounded device-side waits: launches one thread that waits on
+ * a barrier nothing completes.  The wait must expire (about one second), the
+ * kernel must return, and this call must report MM_ERR_TIMEOUT with
+ * *done_dev == 1; the device stays usable.  done_dev: one device uint32. */
+mm_status mm_f4_wait_selftest(unsigned *done_dev);
+
 /* Tuning knobs for experiments and tests; defaults are what the benchmark
  * uses.  key 1: launch kernels with programmatic stream serialization so
  * that an op's weight prefetch overlaps the tail of the previous kernel in the

@@ -95,6 +95,7 @@ SIGNATURES = {
     "mm_f4_device_status": (C.c_int, [C.POINTER(C.c_uint)]),
     "mm_f4_launch_count": (C.c_ulonglong, [C.c_int]),
     "mm_f4_decode_probe": (C.c_int, [_vp, _vp, _vp]),
+    "mm_f4_wait_selftest": (C.c_int, [_vp]),
     "mm_f4_tune": (C.c_int, [C.c_int, C.c_int]),
     "mm_time_begin": (C.c_int, []),
     "mm_time_end": (C.c_int, [C.POINTER(_f)]),

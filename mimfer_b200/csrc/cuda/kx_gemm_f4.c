@@ -366,6 +366,17 @@ mm_status mm_f4_linear_host(const void *x_host, void *x_dev, const void *payload
     return finish_op();
 }
 
+mm_status mm_f4_wait_selftest(unsigned *done_dev)
+{
+    MM_REQUIRE(done_dev, MM_ERR_STATE);
+    MM_CHECK(ensure_ready());
+    MM_REQUIRE(!mm_cuda_capturing(), MM_ERR_BUSY);
+    cudaStream_t cs = (cudaStream_t)mm_cuda_stream_raw(MM_ST_COMPUTE);
+    CK((cudaError_t)mmb_launch_wait_selftest(G.status_dev, done_dev, cs));
+    G.launches++;
+    return finish_op();                /* MM_ERR_TIMEOUT when the wait gave up as designed */
+}
+
 mm_status mm_f4_decode_probe(uint32_t *out_mma_dev, uint32_t *out_f32_dev, uint32_t *out_f16_dev)
 {
     MM_REQUIRE(out_mma_dev && out_f32_dev && out_f16_dev, MM_ERR_STATE);

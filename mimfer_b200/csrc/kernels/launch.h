@@ -87,6 +87,7 @@ int mmb_launch_rowwarp(const mmb_args *a, void *stream);
 int mmb_launch_stream(const mmb_args *a, void *stream);
 int mmb_launch_umma(const mmb_args *a, void *stream);
 int mmb_launch_streamt(const mmb_args *a, void *stream);
+int mmb_launch_wait_selftest(unsigned *status, unsigned *done, void *stream);
 int mmb_launch_decode_probe(uint32_t *out_mma, uint32_t *out_f32, uint32_t *out_f16, void *stream);
 /* One-time per-process setup (smem opt-in attributes). */
 int mmb_kernels_init(void);

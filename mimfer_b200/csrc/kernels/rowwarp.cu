@@ -109,7 +109,28 @@ __global__ void f4_decode_probe_kernel(uint32_t *out_mma, uint32_t *out_f32, uin
     out_f16[i] = same16 ? __float_as_uint(__half2float(hv)) : 0xdeadbeefu;
 }
 
+/* Bounded-wait self test: one thread waits on an mbarrier that nothing ever
+ * completes.  The wait must give up after its limit, raise MMB_DEV_TIMEOUT in
+ * the status word and let the kernel return normally. */
+__global__ void f4_wait_selftest_kernel(unsigned *status, unsigned *done)
+{
+    __shared__ alignas(8) unsigned long long bar;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mbar_init(b, 1u);
+        mbar_fence_init();
+        const bool ok = mbar_wait(b, 0u, status);       /* never arrives */
+        *done = ok ? 2u : 1u;
+    }
+}
+
 } // namespace mmb
+
+extern "C" int mmb_launch_wait_selftest(unsigned *status, unsigned *done, void *stream)
+{
+    mmb::f4_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, done);
+    return static_cast<int>(cudaGetLastError());
+}
 
 extern "C" int mmb_launch_rowwarp(const mmb_args *a, void *stream)
 {

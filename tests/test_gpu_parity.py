@@ -270,3 +270,18 @@ def test_host_buffer_call(rt, oracle):
     rt.linear_host(x_host, x_dev, w, y_dev, y_host)
     got = y_host.view(torch.int16).numpy().view(np.uint16)
     assert row_rel_l2(got, oracle.gemm_f4(xb, w.payload, w.scales, w.gs)) <= REL_L2_TOL
+
+
+# ---------------------------------------------------------------- failure detection
+def test_bounded_wait_expires_and_device_stays_usable(rt, oracle):
+    """A wait on a barrier that nothing completes gives up after its limit, the
+    kernel returns, the launcher reports MM_ERR_TIMEOUT, and the next op is fine."""
+    done = rt.torch.zeros(1, dtype=rt.torch.int32, device=rt.device)
+    rt.torch.cuda.synchronize()
+    rt.lib.mm_log_set_level(-1)
+    st = rt.lib.mm_f4_wait_selftest(done.data_ptr())
+    rt.lib.mm_log_set_level(1)
+    assert st == L.MM_ERR_TIMEOUT
+    assert int(done.item()) == 1
+    assert rt.device_status() == 0                       # the launcher cleared the word
+    check(rt, oracle, 4, 512, 256, None, seed=3)         # the context is healthy
