@@ -214,29 +214,38 @@ class Bench:
                "avg_launch_us": ms * 1e3 / len(ops)}
         return res, ops, eng
 
-    def decode_e2e(self, ops, steps, warmup):
-        """Same ops through mm_f4_linear_host: pinned host x in, pinned host y out."""
+    def decode_e2e(self, ops, eng, steps, warmup):
+        """The same step through the host-buffer call of the engine: pinned host x
+        in for every op, one graph replay, pinned host y out for every op, one
+        synchronisation (mm_lin_engine_launch_host)."""
         torch = self.torch
-        host = []
-        for x, w, y in ops:
-            host.append((x.cpu().pin_memory(), x, w, y, torch.empty(y.shape, dtype=y.dtype).pin_memory()))
-        h2d = sum(h[0].numel() * 2 for h in host)
-        d2h = sum(h[4].numel() * 2 for h in host)
-
-        def step():
-            for xh, xd, w, yd, yh in host:
-                self.rt.linear_host(xh, xd, w, yd, yh)
+        x_host = [x.cpu().pin_memory() for x, _, _ in ops]
+        y_host = [torch.empty(y.shape, dtype=y.dtype).pin_memory() for _, _, y in ops]
+        h2d = sum(t.numel() * 2 for t in x_host)
+        d2h = sum(t.numel() * 2 for t in y_host)
         for _ in range(max(warmup, 3)):
-            step()
+            eng.launch_host(x_host, y_host)
         self.barrier()
         t0 = time.perf_counter()
         for _ in range(steps):
-            step()
-        self.torch.cuda.synchronize()
+            eng.launch_host(x_host, y_host)
         sec = (time.perf_counter() - t0) / steps
+        # per-op form (mm_f4_linear_host: copy, op, copy, sync for every op), for the record
+        per_op = [(xh, x, w, y, yh) for (x, w, y), xh, yh in zip(ops, x_host, y_host)]
+        for xh, xd, w, yd, yh in per_op:
+            self.rt.linear_host(xh, xd, w, yd, yh)
+        t1 = time.perf_counter()
+        for _ in range(max(2, steps // 4)):
+            for xh, xd, w, yd, yh in per_op:
+                self.rt.linear_host(xh, xd, w, yd, yh)
+        sec_op = (time.perf_counter() - t1) / max(2, steps // 4)
         wb = sum(wbytes(w.K, w.N) for _, w, _ in ops)
         return {"value": wb / sec / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": sec * 1e3,
+                "call": "mm_lin_engine_launch_host: H2D of all activations, one graph replay, "
+                        "D2H of all outputs, one sync",
+                "per_op_sync": {"value": wb / sec_op / 1e9, "ms_per_step": sec_op * 1e3,
+                                "call": "mm_f4_linear_host per op"},
                 "timing": "host wall clock around synchronous calls"}
 
     def prefill_sweep(self, steps, warmup, ms_list=PREFILL_M, names=("gate_up", "down", "q", "k", "v", "o")):
@@ -275,6 +284,57 @@ class Bench:
         per = SHAPES[name][1] // self.world
         return (self.rank * per, (self.rank + 1) * per)
 
+    def tp_e2e(self, steps, warmup, M=32):
+        """The tensor-parallel decode step with host buffers: every rank copies the
+        replicated activations up from pinned memory, runs both sharded linears
+        (fused mode, one closing barrier), and rank 0 reads both full outputs back;
+        one synchronisation per step, host wall clock, max over ranks."""
+        from mimfer_b200.tp import TpLinear
+        torch = self.torch
+        lins = {n: TpLinear(self.weight(n), self.rank, self.world, rt=self.rt, mode="fused")
+                for n in ("gate_up", "lm_head")}
+        xd = {n: self.acts(M, SHAPES[n][0]) for n in lins}
+        xh = {n: xd[n].cpu().pin_memory() for n in lins}
+        yh = {n: torch.empty((M, SHAPES[n][1]), dtype=torch.bfloat16).pin_memory() for n in lins}
+        last = list(lins.values())[-1]
+        stream = self.rt.torch_stream()
+
+        def step():
+            with torch.cuda.stream(stream):
+                for n in lins:
+                    xd[n].copy_(xh[n], non_blocking=True)
+            ys = {n: lin.forward(xd[n], barrier=False) for n, lin in lins.items()}
+            last.barrier()
+            if self.rank == 0:
+                with torch.cuda.stream(stream):
+                    for n in lins:
+                        yh[n].copy_(ys[n], non_blocking=True)
+            self.rt.sync()
+        for _ in range(max(warmup, 3)):
+            step()
+        self.barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        self.barrier()
+        sec = torch.tensor([(time.perf_counter() - t0) / steps], dtype=torch.float64, device=self.dev)
+        self.dist.all_reduce(sec, op=self.dist.ReduceOp.MAX)
+        sec = float(sec.item())
+        status = self.rt.device_status()
+        if status:
+            raise RuntimeError(f"device status 0x{status:x} after the end-to-end region")
+        wb = sum(wbytes(*SHAPES[n]) for n in lins)
+        res = {"value": wb / sec / 1e9, "unit": "GB/s", "ms_per_step": sec * 1e3,
+               "h2d_bytes_per_step": sum(t.numel() * 2 for t in xh.values()) * self.world,
+               "d2h_bytes_per_step": sum(t.numel() * 2 for t in yh.values()),
+               "call": "TpLinear.forward (fused) on host activations, both outputs read back on rank 0",
+               "timing": "host wall clock around a synchronous step, max over ranks"}
+        for lin in lins.values():
+            lin._symm.clear()
+        del lins
+        torch.cuda.empty_cache()
+        return res
+
     def tp_series(self, steps, warmup):
         """config 5: gate+up and LM head, sharded along N over all ranks, M=32 and M=8192."""
         from mimfer_b200.tp import TpLinear
@@ -287,9 +347,12 @@ class Bench:
             for tag, M, st in (("decode_m32", 32, steps), ("prefill_m8192", 8192, max(2, steps // 4))):
                 xs = {n: self.acts(M, SHAPES[n][0]) for n in lins}
 
-                def step():
+                last = list(lins.values())[-1]
+
+                def step():                     # the linears of a step share one closing barrier
                     for n, lin in lins.items():
-                        lin.forward(xs[n])
+                        lin.forward(xs[n], barrier=False)
+                    last.barrier()
                 ms = self.timed(step, st, warmup)
                 wb = sum(wbytes(*SHAPES[n]) for n in lins)
                 fl = sum(2.0 * M * SHAPES[n][0] * SHAPES[n][1] for n in lins)
@@ -300,6 +363,8 @@ class Bench:
                 self.torch.cuda.empty_cache()
             out[mode] = res
             del lins
+        if self.world > 1:
+            out["e2e"] = self.tp_e2e(max(2, steps // 2), warmup)
         # the sharded kernels alone, no exchange: what the GEMM itself scales like
         shards = {n: self.dev_weight(self.weight(n, rows=self._shard_rows(n))) for n in ("gate_up", "lm_head")}
         res = {}
@@ -399,7 +464,7 @@ def run_b200(args):
                                 "avg_launch_us": dec["avg_launch_us"],
                                 "traffic": STREAM_TRAFFIC_RATIO * dec["alg_bytes_per_launch"],
                                 "traffic_src": "ncu capture of gate+up M=1 scaled by algorithmic bytes"}
-            line["e2e"] = b.decode_e2e(ops, max(2, steps // 2), warmup)
+            line["e2e"] = b.decode_e2e(ops, eng, max(2, steps // 2), warmup)
             eng.close()
             del ops
             b.torch.cuda.empty_cache()
@@ -423,15 +488,15 @@ def run_b200(args):
             line.update(value=d["weight_gbs"], ms_per_step=d["ms_per_step"], scaling="strong",
                         gpu_launches=2 * steps,
                         config={"workload": f"tensor-parallel gate+up and LM head (N=151936) split along N "
-                                            f"over {b.world} GPUs at M=32, NCCL all-gather of the output slices",
+                                            f"over {b.world} GPUs at M=32, kernel epilogue stores every output "
+                                            f"tile to all ranks (symmetric memory), one barrier per step",
                                 "l2": "537 MB of weights per step across ranks", "peaks": pk["src"]})
             line["roofline"] = {"bound": "hbm", "kernel": "f4_stream_kernel", "achieved": d["weight_gbs"],
                                 "peak": pk["hbm"] * b.world, "unit": "GB/s",
                                 "frac": d["weight_gbs"] / (pk["hbm"] * b.world), "of": pk["src"], "traffic": None}
             line["prefill"] = {"tflops": tp["prefill_m8192"]["tflops"],
                                "ms_per_step": tp["prefill_m8192"]["ms_per_step"]}
-            line["e2e"] = {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
-                           "note": "end-to-end host-buffer timing is reported at n_gpus=1"}
+            line["e2e"] = tp.pop("e2e")
     line["clocks"] = clk.summary()
     if b.rank == 0:
         if b.world == 1 and not args.no_cpu:

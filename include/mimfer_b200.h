@@ -261,6 +261,16 @@ uint32_t  mm_lin_engine_n_ops(const mm_lin_engine *e);
 mm_status mm_lin_engine_capture(mm_lin_engine *e);
 /* Replay the graph (or dispatch op by op if not captured); no sync. */
 mm_status mm_lin_engine_launch(mm_lin_engine *e);
+/* One step with host buffers, the shape of a serving round in the reference
+ * engine (src/engine/engine.c:233-357: inputs up, one graph launch, results
+ * down, one host sync): for every op i with x_host[i] != NULL the activations
+ * are copied from (pinned) host memory into the op's device operand `a`, the
+ * graph is replayed (or the ops dispatched), every y_host[i] != NULL receives
+ * the op's output, then the compute stream is synchronised and the device
+ * status word checked.  Arrays have mm_lin_engine_n_ops entries; either may be
+ * NULL as a whole. */
+mm_status mm_lin_engine_launch_host(mm_lin_engine *e, const void *const *x_host,
+                                    void *const *y_host);
 void      mm_lin_engine_destroy(mm_lin_engine *e);
 
 #ifdef __cplusplus

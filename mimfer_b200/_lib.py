@@ -109,6 +109,7 @@ SIGNATURES = {
     "mm_lin_engine_n_ops": (_u32, [_vp]),
     "mm_lin_engine_capture": (C.c_int, [_vp]),
     "mm_lin_engine_launch": (C.c_int, [_vp]),
+    "mm_lin_engine_launch_host": (C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
     "mm_lin_engine_destroy": (None, [_vp]),
 }
 

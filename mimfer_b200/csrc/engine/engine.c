@@ -94,6 +94,36 @@ mm_status mm_lin_engine_launch(mm_lin_engine *e)
     return run_ops(e);
 }
 
+mm_status mm_lin_engine_launch_host(mm_lin_engine *e, const void *const *x_host,
+                                    void *const *y_host)
+{
+    MM_REQUIRE(e && e->n_ops > 0, MM_ERR_STATE);
+    MM_REQUIRE(!mm_cuda_capturing(), MM_ERR_BUSY);
+    for (uint32_t i = 0; x_host && i < e->n_ops; i++) {
+        const mm_op_desc *op = &e->ops[i];
+        if (x_host[i] && op->op != OP_NOP)
+            MM_CHECK(mm_h2d_async((void *)(uintptr_t)op->a, x_host[i],
+                                  (size_t)op->n0 * op->n1 * 2u, MM_ST_COMPUTE));
+    }
+    if (e->captured)
+        MM_CHECK(mm_graph_launch(e->graph, MM_ST_COMPUTE));
+    else
+        MM_CHECK(run_ops(e));
+    for (uint32_t i = 0; y_host && i < e->n_ops; i++) {
+        const mm_op_desc *op = &e->ops[i];
+        if (y_host[i] && op->op != OP_NOP)
+            MM_CHECK(mm_d2h_async(y_host[i], op->c, (size_t)op->n0 * op->n2 * 2u, MM_ST_COMPUTE));
+    }
+    MM_CHECK(mm_stream_sync(MM_ST_COMPUTE));
+    unsigned flags = 0;
+    MM_CHECK(mm_f4_device_status(&flags));
+    if (flags) {
+        MM_LOGE("engine: device status 0x%x after step", flags);
+        return (flags & 1u) ? MM_ERR_TIMEOUT : MM_ERR_CUDA;
+    }
+    return MM_OK;
+}
+
 void mm_lin_engine_destroy(mm_lin_engine *e)
 {
     if (!e)

@@ -221,6 +221,14 @@ class LinearEngine:
     def launch(self):
         L.check(self.rt.lib.mm_lin_engine_launch(self.h), "mm_lin_engine_launch")
 
+    def launch_host(self, x_host, y_host):
+        """One step with pinned host tensors: x_host[i] -> op i's activations,
+        op i's output -> y_host[i] (None entries are skipped); synchronises."""
+        n = self.n_ops()
+        xs = (C.c_void_p * n)(*[t.data_ptr() if t is not None else None for t in x_host])
+        ys = (C.c_void_p * n)(*[t.data_ptr() if t is not None else None for t in y_host])
+        L.check(self.rt.lib.mm_lin_engine_launch_host(self.h, xs, ys), "mm_lin_engine_launch_host")
+
     def n_ops(self):
         return self.rt.lib.mm_lin_engine_n_ops(self.h)
 

@@ -71,7 +71,17 @@ class TpLinear:
             self._symm[M] = (y, hdl, ptrs)
         return self._symm[M]
 
-    def _forward_fused(self, x):
+    def barrier(self):
+        """Cross-rank barrier on the compute stream: after it, every rank's copy of
+        every output written since the previous barrier is complete.  Needed once
+        per group of fused forwards issued with barrier=False."""
+        if self.mode != "fused" or not self._symm:
+            return
+        hdl = next(iter(self._symm.values()))[1]
+        with torch.cuda.stream(self.rt.torch_stream()):
+            hdl.barrier(channel=0)
+
+    def _forward_fused(self, x, barrier=True):
         M = x.shape[0]
         y, hdl, ptrs = self._symm_buffers(M, x)
         n0 = self.rank * (self.N // self.world)
@@ -80,14 +90,17 @@ class TpLinear:
             L.check(self.rt.lib.mm_f4_linear_tp(x.data_ptr(), w.dev_payload.data_ptr(),
                                                 w.dev_scales.data_ptr(), w.gs, ptrs, self.world,
                                                 self.N, n0, M, w.K, w.N, None), "mm_f4_linear_tp")
-            hdl.barrier(channel=0)              # every rank's stores have landed everywhere
+            if barrier:
+                hdl.barrier(channel=0)          # every rank's stores have landed everywhere
         return y
 
-    def forward(self, x):
+    def forward(self, x, barrier=True):
         """x: [M][K] replicated.  Returns y [M][N], complete on every rank.
-        On CUDA everything is enqueued on the runtime's compute stream."""
+        On CUDA everything is enqueued on the runtime's compute stream.
+        barrier=False (fused mode) leaves the closing cross-rank barrier to the
+        caller, so several linears of one step can share a single barrier()."""
         if self.mode == "fused":
-            return self._forward_fused(x)
+            return self._forward_fused(x, barrier)
         M = x.shape[0]
         y_local, gathered, y = self._buffers(M, x)
         if self.world == 1:                       # nothing to exchange

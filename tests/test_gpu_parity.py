@@ -258,6 +258,34 @@ def test_engine_graph_equals_direct_dispatch(rt, oracle):
     eng.close()
 
 
+def test_engine_host_step(rt, oracle):
+    """mm_lin_engine_launch_host: host activations in, graph replay, host outputs out."""
+    torch = rt.torch
+    shapes = [(2, 1024, 512), (5, 512, 1000), (1, 2048, 256)]
+    ws = [mm.make_weight(N, K, seed=i).to_device(rt.device) for i, (M, K, N) in enumerate(shapes)]
+    xb = [mm.make_activations(M, K, seed=70 + i) for i, (M, K, N) in enumerate(shapes)]
+    xd = [torch.zeros((M, K), dtype=torch.bfloat16, device=rt.device) for (M, K, N) in shapes]
+    yd = [torch.zeros((M, N), dtype=torch.bfloat16, device=rt.device) for (M, K, N) in shapes]
+    xh = [torch.from_numpy(b.view(np.int16)).view(torch.bfloat16).pin_memory() for b in xb]
+    yh = [torch.zeros((M, N), dtype=torch.bfloat16).pin_memory() for (M, K, N) in shapes]
+    eng = mm.LinearEngine(rt)
+    for x, w, y in zip(xd, ws, yd):
+        eng.add(x, w, y)
+    for captured in (False, True):
+        if captured:
+            eng.capture()
+        for t in yh:
+            t.zero_()
+        eng.launch_host(xh, [yh[0], None, yh[2]])          # None: output stays on the device
+        for i in (0, 2):
+            got = yh[i].view(torch.int16).numpy().view(np.uint16)
+            assert row_rel_l2(got, oracle.gemm_f4(xb[i], ws[i].payload, ws[i].scales, ws[i].gs)) <= REL_L2_TOL
+        assert not yh[1].view(torch.int16).numpy().any()
+        assert row_rel_l2(rt.from_device_bf16(yd[1]),
+                          oracle.gemm_f4(xb[1], ws[1].payload, ws[1].scales, ws[1].gs)) <= REL_L2_TOL
+    eng.close()
+
+
 def test_host_buffer_call(rt, oracle):
     torch = rt.torch
     M, K, N = 4, 1024, 512

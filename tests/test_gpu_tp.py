@@ -35,7 +35,9 @@ def _worker(rank, world, port, cases, out_dir, mode):
         w = mm.make_weight(N, K, seed=i)
         lin = TpLinear(w, rank, world, rt=rt, mode=mode)
         x = rt.to_device_bf16(mm.make_activations(M, K, seed=100 + i))
-        y = lin.forward(x)
+        y = lin.forward(x, barrier=(i % 2 == 0))      # odd cases: barrier issued separately
+        if i % 2:
+            lin.barrier()
         rt.sync()
         assert rt.device_status() == 0
         np.save(os.path.join(out_dir, f"y{i}_{rank}.npy"), rt.from_device_bf16(y))
