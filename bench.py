@@ -280,6 +280,93 @@ class Bench:
         return {"layers": layers, "M": M, "ops": len(ops), "weight_bytes": wb,
                 "sum_linear_ms_per_step": ms, "weight_gbs": wb / ms / 1e6}
 
+    def decode_step_planner(self, steps, warmup, layers=64, M=16):
+        """The 64-layer decode step with the op sequence of the reference planner
+        (src/plan/plan.c:223-247, 386-473): per layer q, k, v, o, gate, up,
+        SILU_MUL, down - gate and up as separate tensors - run as emitted (8 ops
+        per layer) and with the engine's MLP fusion (6 per layer).  down reads the
+        SILU_MUL output."""
+        K, inter = SHAPES["gate_up"][0], SHAPES["gate_up"][1] // 2
+        full = self.weight("gate_up")
+        lin = ("q", "k", "v", "o", "down")
+        base = {n: self.weight(n) for n in lin}
+        x = self.acts(M, K)
+        xo = self.acts(M, SHAPES["o"][0])
+        g, u, h = self.empty(M, inter), self.empty(M, inter), self.empty(M, inter)
+        ys = {n: self.empty(M, SHAPES[n][1]) for n in lin}
+        layer_w, keep, wb = [], [], 0
+        for _ in range(layers):
+            ws = {n: self.dev_weight(base[n]) for n in lin}
+            wg, wu = full.rows(0, inter), full.rows(inter, 2 * inter)
+            keep.append(self.mm.place_weights([wg, wu], self.dev))
+            ws["gate"], ws["up"] = wg, wu
+            layer_w.append(ws)
+            wb += sum(wbytes(*SHAPES[n]) for n in lin) + 2 * wbytes(K, inter)
+        res = {"layers": layers, "M": M, "weight_bytes": wb}
+        for fuse in (False, True):
+            eng = self.mm.LinearEngine(self.rt, max_ops=8 * layers)
+            eng.fuse_mlp(fuse)
+            for ws in layer_w:
+                for n in ("q", "k", "v"):
+                    eng.add(x, ws[n], ys[n])
+                eng.add(xo, ws["o"], ys["o"])
+                eng.add(x, ws["gate"], g, note=b"gate")
+                eng.add(x, ws["up"], u, note=b"up")
+                eng.add_silu_mul(g, u, h)
+                eng.add(h, ws["down"], ys["down"])
+            n_ops = eng.n_ops()
+            eng.launch()
+            self.rt.sync()
+            eng.capture()
+            ms = self.timed(eng.launch, max(2, steps // 2), 3)
+            eng.close()
+            res["fused_mlp" if fuse else "as_emitted"] = {"ops": n_ops, "ms_per_step": ms,
+                                                          "weight_gbs": wb / ms / 1e6}
+        del layer_w, keep
+        self.torch.cuda.empty_cache()
+        return res
+
+    def mlp_front(self, steps, warmup, layers=4):
+        """The MLP front half (gate and up projections 5120 -> 17408 each, then
+        silu(gate) * up) as the reference planner emits it - three ops - against
+        the fused kernel, `layers` weight pairs per step so the weights of a step
+        (100 MB per pair) exceed L2.  Same engine, fusion off and on."""
+        K, inter = SHAPES["gate_up"][0], SHAPES["gate_up"][1] // 2
+        full = self.weight("gate_up")
+        out = {}
+        for tag, M, st in (("decode_m16", 16, steps), ("prefill_m2048", 2048, max(2, steps // 4))):
+            pairs, keep = [], []
+            for _ in range(layers):
+                wg, wu = full.rows(0, inter), full.rows(inter, 2 * inter)
+                keep.append(self.mm.place_weights([wg, wu], self.dev))
+                pairs.append((wg, wu))
+            x = self.acts(M, K)
+            g, u, y = self.empty(M, inter), self.empty(M, inter), self.empty(M, inter)
+            res = {}
+            for fuse in (False, True):
+                eng = self.mm.LinearEngine(self.rt, max_ops=3 * layers)
+                eng.fuse_mlp(fuse)
+                for wg, wu in pairs:
+                    eng.add(x, wg, g, note=b"gate")
+                    eng.add(x, wu, u, note=b"up")
+                    eng.add_silu_mul(g, u, y)
+                n_ops = eng.n_ops()
+                eng.launch()
+                self.rt.sync()
+                eng.capture()
+                ms = self.timed(eng.launch, st, warmup)
+                eng.close()
+                res["fused" if fuse else "three_ops"] = {"ops": n_ops, "ms_per_step": ms}
+            wb = layers * 2 * wbytes(K, inter)
+            fl = layers * 2 * 2.0 * M * K * inter
+            f = res["fused"]["ms_per_step"]
+            res.update(M=M, layers=layers, weight_gbs=wb / f / 1e6, tflops=fl / f / 1e9,
+                       speedup=res["three_ops"]["ms_per_step"] / f)
+            out[tag] = res
+            del pairs, keep
+            self.torch.cuda.empty_cache()
+        return out
+
     def _shard_rows(self, name):
         per = SHAPES[name][1] // self.world
         return (self.rank * per, (self.rank + 1) * per)
@@ -481,6 +568,8 @@ def run_b200(args):
             fused = b.decode_step_64(steps, warmup, names=("qkv", "o", "gate_up", "down"))
             line["decode_step"]["fused_qkv"] = {k: fused[k] for k in ("ops", "sum_linear_ms_per_step", "weight_gbs")}
             b.torch.cuda.empty_cache()
+            line["mlp_front"] = b.mlp_front(steps, warmup)
+            line["decode_step"]["planner_sequence"] = b.decode_step_planner(steps, warmup)
         tp = b.tp_series(steps, warmup)
         line["tp"] = tp
         if b.world > 1:
@@ -520,6 +609,8 @@ def run_case(b, case, steps, warmup):
         res, _, eng = b.decode_sweep(steps, warmup, ms_list=(16, 16), names=("gate_up", "down"))
         eng.close()
         return res
+    if case == "mlp_front":        # gate + up + silu, three ops against the fused kernel
+        return b.mlp_front(steps, warmup)
     if case == "decode_down":
         res, _, eng = b.decode_sweep(steps, warmup, ms_list=(1, 16), names=("down",))
         eng.close()

@@ -14,6 +14,7 @@
  *   mm_op_desc    include/mimfer/plan.h:73-82
  *   mm_kcall      include/mimfer/kernels.h:73-80
  *   mm_wt         include/mimfer/tensor.h:121-126
+ *   mm_dtype      include/mimfer/tensor.h:33-42
  *   mm_stream_id  include/mimfer/cuda_rt.h:32-36
  *
  * tests/test_abi_layout.py compiles this header next to the reference's own
@@ -105,6 +106,17 @@ typedef struct mm_kcall {
     mm_stream_h       stream;           /* passed as 0 and ignored, as in
                                            src/plan/plan.c:121              */
 } mm_kcall;
+
+typedef enum mm_dtype {
+    MM_DT_U8 = 0,
+    MM_DT_I32 = 1,
+    MM_DT_I64 = 2,
+    MM_DT_F32 = 3,
+    MM_DT_BF16 = 4,
+    MM_DT_FP4E2M1 = 5,
+    MM_DT_FP8E4M3 = 6,
+    MM_DT_N = 7
+} mm_dtype;
 
 /* NVFP4 weight view (rows = output features, cols = input features). */
 typedef struct mm_wt {

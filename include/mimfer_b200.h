@@ -45,8 +45,20 @@ mm_status kx_op_gemm_f4(const mm_kcall *kc);
  * bf16 GEMM is outside this library). */
 mm_status kx_op_qkv(const mm_kcall *kc);
 
+/* Replaces kx_op_lmhead in src/kernels/cuda/cx.cu:332-335 the same way: the
+ * operands are a GEMM's (a = x, b = W, c = logits, n0 = M, n1 = K, n2 = N,
+ * src/kernels/cpu/cx.c:187-190); a non-NULL `d` (block scales) makes it the
+ * NVFP4 op, a NULL `d` returns MM_ERR_UNSUPPORTED. */
+mm_status kx_op_lmhead(const mm_kcall *kc);
+
+/* Replaces kx_op_silu_mul in src/kernels/cuda/cx.cu:275-284 (CPU twin
+ * src/kernels/cpu/cx.c:155-167): c[i] = bf16(silu(a[i]) * b[i]) over n0 * n1
+ * bf16 elements.  Served so that the op list of a whole MLP can run here, and
+ * as the unfused form of mm_f4_mlp_gate_up. */
+mm_status kx_op_silu_mul(const mm_kcall *kc);
+
 /* Replaces mm_kx_invoke in src/kernels/kx.c:15-47 for the opcodes this
- * library owns: OP_GEMM_F4, OP_QKV (fp4 form) and OP_NOP.  Same NULL checks
+ * library owns: OP_GEMM_F4, OP_QKV and OP_LMHEAD (fp4 forms), OP_SILU_MUL and OP_NOP.  Same NULL checks
  * (kc, kc->op, kc->e -> MM_ERR_STATE); any other opcode returns
  * MM_ERR_UNSUPPORTED. */
 mm_status mm_kx_invoke(const mm_kcall *kc);
@@ -143,6 +155,9 @@ mm_status mm_f4_select(const mm_f4_shape *s, mm_f4_plan *out);
 /* Force a variant (tests, sweeps); MM_ERR_UNSUPPORTED if the shape cannot run
  * on it. */
 mm_status mm_f4_select_variant(const mm_f4_shape *s, int variant, mm_f4_plan *out);
+/* Plan of the gated pair (mm_f4_mlp_gate_up): s->N = output features.
+ * MM_ERR_UNSUPPORTED when only the unfused three-op form can run the shape. */
+mm_status mm_f4_select_glu(const mm_f4_shape *s, mm_f4_plan *out);
 /* Override for kx_op_gemm_f4: -1 = automatic (default). */
 void      mm_f4_force_variant(int variant);
 
@@ -153,6 +168,28 @@ void      mm_f4_force_variant(int variant);
 mm_status mm_f4_linear(const void *x, const void *payload, const void *scale,
                        float gs, void *y, uint32_t M, uint32_t K, uint32_t N,
                        void *stream);
+
+/* Gated MLP front half in one kernel (no single counterpart in the reference):
+ * replaces the three ops the reference planner emits per layer
+ * (src/plan/plan.c:223-247: OP_GEMM_F4 "gate", OP_GEMM_F4 "up", OP_SILU_MUL)
+ *     y[m][j] = bf16( silu(G) * U ),  G = bf16(x . Wgate[j]),  U = bf16(x . Wup[j]),
+ * i.e. the arithmetic of kx_op_silu_mul (src/kernels/cpu/cx.c:155-167) on the
+ * values the two GEMMs would have stored; the [M][inter] gate and up buffers are
+ * never written.  The two projections are separate NVFP4 tensors ([inter][K/2]
+ * payload, [inter][K/16] scales each) anywhere in device memory, as long as the
+ * payload and the scale tensors lie in the same order (both gate-first or both
+ * up-first) and their distances are multiples of 16 bytes below 2^40 - true for
+ * tensors staged one after the other into one weight arena.  M <= 32 runs the
+ * decode kernel (split-K through the workspace), larger M the tcgen05 kernel.
+ * MM_ERR_UNSUPPORTED if the shape needs the fallback kernel (K % 256 != 0,
+ * unaligned operands) or the layout rule fails: run the three ops then. */
+mm_status mm_f4_mlp_gate_up(const void *x, const void *gate_payload, const void *gate_scale,
+                            float gs_gate, const void *up_payload, const void *up_scale,
+                            float gs_up, void *y, uint32_t M, uint32_t K, uint32_t inter,
+                            void *stream);
+/* y = silu(gate) * up, elementwise on bf16 [n] (src/kernels/cuda/cx.cu:264-273):
+ * the unfused form, enqueued on `stream`. */
+mm_status mm_silu_mul(const void *gate, const void *up, void *y, size_t n, void *stream);
 
 /* Tensor-parallel form (no counterpart in the reference, which is single-GPU).
  * This rank owns output features [col0, col0 + N_local) of a layer with `ldy`
@@ -251,11 +288,61 @@ void mm_bf16_to_f32(const uint16_t *in, float *out, uint64_t n);
 mm_status mm_f4_make_weight(uint32_t N, uint32_t K, uint64_t seed, float std,
                             uint8_t *payload, uint8_t *scales, float *gs_out);
 
+/* ---- NVFP4 tensors in a weights section -----------------------------------
+ * The reference loader walks the tensor index of the artifact's weights
+ * section and stages every tensor into the weight arena
+ * (src/model/tensor_registry.c:372-560; layout in tensor_registry.h:86-120) but
+ * rejects MM_DT_FP4E2M1 entries (tensor_registry.c:468-474).  These calls read
+ * the same index with fp4 entries admitted.  An fp4 entry's bytes are payload
+ * (rows*cols/2), block scales (rows*cols/16) and the fp32 global scale (4),
+ * back to back; cols % 16 == 0.  Errors as in the reference: MM_ERR_CORRUPT
+ * for a bad header, truncated index, wrong nbytes, bytes outside the payload or
+ * a duplicate name; MM_ERR_UNSUPPORTED for any other dtype; MM_ERR_SHAPE for an
+ * fp4 tensor with cols % 16 != 0. */
+typedef struct mm_f4_went {
+    char     name[48];
+    uint32_t rows, cols;
+    uint8_t  dtype;           /* MM_DT_BF16 or MM_DT_FP4E2M1 */
+    uint64_t off, nbytes;     /* within the section payload   */
+} mm_f4_went;
+typedef struct mm_f4_wreg mm_f4_wreg;
+
+/* rows*cols/2 + rows*cols/16 + 4 */
+uint64_t  mm_f4_tensor_bytes(uint32_t rows, uint32_t cols);
+/* Validate the index; ents may be NULL to count only (cap ignored then). */
+mm_status mm_f4_weights_parse(const uint8_t *data, size_t len, mm_f4_went *ents, uint32_t cap,
+                              uint32_t *n_out);
+/* Device bytes the tensors take when bump-placed on 256-byte boundaries. */
+size_t    mm_f4_weights_arena_bytes(const mm_f4_went *ents, uint32_t n);
+/* Copy every tensor into the caller's device block (256-byte aligned, at least
+ * mm_f4_weights_arena_bytes; no allocation here), in index order, an fp4 tensor
+ * as [payload | scales]; register each fp4 tensor's global scale
+ * (mm_f4_gscale_set) and return a name -> view registry.  Copies run on the
+ * transfer stream and are complete on return.  mm_cuda_init first. */
+mm_status mm_f4_weights_stage(const uint8_t *data, size_t len, void *arena_dev, size_t arena_bytes,
+                              mm_f4_wreg **out);
+uint32_t  mm_f4_weights_count(const mm_f4_wreg *r);
+size_t    mm_f4_weights_used(const mm_f4_wreg *r);
+/* The reference's mm_tens_find (include/mimfer/engine.h:86) for this registry:
+ * MM_ERR_RANGE when the name is absent, MM_ERR_UNSUPPORTED when the tensor is of
+ * the other kind. */
+mm_status mm_f4_weights_find(const mm_f4_wreg *r, const char *name, mm_wt *w_out, float *gs_out);
+mm_status mm_f4_weights_find_bf16(const mm_f4_wreg *r, const char *name, const void **data_out,
+                                  uint32_t *rows_out, uint32_t *cols_out);
+void      mm_f4_weights_free(mm_f4_wreg *r);
+
 /* ---- op-list engine (graph-captured sequence of linears) ------------------ */
 typedef struct mm_lin_engine mm_lin_engine;
 mm_status mm_lin_engine_create(mm_lin_engine **out, uint32_t max_ops);
 mm_status mm_lin_engine_add(mm_lin_engine *e, const mm_op_desc *op);
 uint32_t  mm_lin_engine_n_ops(const mm_lin_engine *e);
+/* on != 0: an OP_SILU_MUL added right after the two OP_GEMM_F4 that produce its
+ * operands from the same activations (the MLP front half as the reference
+ * planner emits it, src/plan/plan.c:223-247) replaces the three ops by one
+ * fused kernel (mm_f4_mlp_gate_up) whenever that kernel can take them; the op
+ * count drops by two and the gate/up buffers are no longer written.  Off by
+ * default. */
+mm_status mm_lin_engine_fuse_mlp(mm_lin_engine *e, int on);
 /* Capture all ops into one CUDA graph (reference pattern:
  * src/plan/plan.c:479-507). */
 mm_status mm_lin_engine_capture(mm_lin_engine *e);

@@ -17,7 +17,7 @@ STATUS_NAMES = ["MM_OK", "MM_ERR_NOMEM", "MM_ERR_IO", "MM_ERR_CORRUPT", "MM_ERR_
  MM_ERR_UNSUPPORTED, MM_ERR_RANGE, MM_ERR_STATE, MM_ERR_BUSY, MM_ERR_TIMEOUT,
  MM_ERR_CAPACITY, MM_ERR_EOF) = range(1, 14)
 
-OP_GEMM_F4, OP_GEMM_BF16, OP_QKV, OP_NOP = 4, 5, 6, 18
+OP_LMHEAD, OP_GEMM_F4, OP_GEMM_BF16, OP_QKV, OP_SILU_MUL, OP_NOP = 1, 4, 5, 6, 12, 18
 MM_ST_COMPUTE, MM_ST_XFER = 0, 1
 V_ROWWARP, V_STREAM, V_UMMA, V_STREAMT = 0, 1, 2, 3
 
@@ -31,6 +31,18 @@ class MmOpDesc(C.Structure):
 
 class MmKcall(C.Structure):
     _fields_ = [("op", C.POINTER(MmOpDesc)), ("e", C.c_void_p), ("stream", C.c_void_p)]
+
+
+class MmWt(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("scale", C.c_void_p), ("rows", C.c_uint32), ("cols", C.c_uint32)]
+
+
+class F4Went(C.Structure):
+    _fields_ = [("name", C.c_char * 48), ("rows", C.c_uint32), ("cols", C.c_uint32),
+                ("dtype", C.c_uint8), ("off", C.c_uint64), ("nbytes", C.c_uint64)]
+
+
+MM_DT_BF16, MM_DT_FP4E2M1 = 4, 5
 
 
 class F4Shape(C.Structure):
@@ -86,6 +98,24 @@ SIGNATURES = {
     "mm_f4_workspace_set": (C.c_int, [_vp, _sz]),
     "mm_f4_workspace_bytes": (_sz, []),
     "mm_f4_select": (C.c_int, [C.POINTER(F4Shape), C.POINTER(F4Plan)]),
+    "mm_f4_tensor_bytes": (C.c_uint64, [C.c_uint32, C.c_uint32]),
+    "mm_f4_weights_parse": (C.c_int, [_vp, C.c_size_t, C.POINTER(F4Went), C.c_uint32,
+                                      C.POINTER(C.c_uint32)]),
+    "mm_f4_weights_arena_bytes": (C.c_size_t, [C.POINTER(F4Went), C.c_uint32]),
+    "mm_f4_weights_stage": (C.c_int, [_vp, C.c_size_t, _vp, C.c_size_t, C.POINTER(_vp)]),
+    "mm_f4_weights_count": (C.c_uint32, [_vp]),
+    "mm_f4_weights_used": (C.c_size_t, [_vp]),
+    "mm_f4_weights_find": (C.c_int, [_vp, C.c_char_p, C.POINTER(MmWt), C.POINTER(C.c_float)]),
+    "mm_f4_weights_find_bf16": (C.c_int, [_vp, C.c_char_p, C.POINTER(_vp), C.POINTER(C.c_uint32),
+                                          C.POINTER(C.c_uint32)]),
+    "mm_f4_weights_free": (None, [_vp]),
+    "mm_f4_select_glu": (C.c_int, [C.POINTER(F4Shape), C.POINTER(F4Plan)]),
+    "mm_f4_mlp_gate_up": (C.c_int, [_vp, _vp, _vp, C.c_float, _vp, _vp, C.c_float, _vp,
+                                    C.c_uint32, C.c_uint32, C.c_uint32, _vp]),
+    "mm_silu_mul": (C.c_int, [_vp, _vp, _vp, C.c_size_t, _vp]),
+    "kx_op_lmhead": (C.c_int, [C.POINTER(MmKcall)]),
+    "kx_op_silu_mul": (C.c_int, [C.POINTER(MmKcall)]),
+    "mm_lin_engine_fuse_mlp": (C.c_int, [_vp, C.c_int]),
     "mm_f4_select_variant": (C.c_int, [C.POINTER(F4Shape), C.c_int, C.POINTER(F4Plan)]),
     "mm_f4_force_variant": (None, [C.c_int]),
     "mm_f4_linear": (C.c_int, [_vp, _vp, _vp, _f, _vp, _u32, _u32, _u32, _vp]),

@@ -35,6 +35,15 @@ void mmb_log(int lvl, const char *file, int line, const char *fmt, ...)
         }                                                                \
     } while (0)
 
+/* The gated pair as an op: `op` is the gate projection's OP_GEMM_F4 descriptor
+ * with c = the output of silu(gate) * up, the up projection comes beside it.
+ * Same synchronisation and error behaviour as kx_op_gemm_f4. */
+mm_status mmb_op_mlp_gate_up(const mm_op_desc *op, const void *up_payload, const void *up_scale);
+/* Would mm_f4_mlp_gate_up take these operands?  Host-only check. */
+int mmb_gate_up_fusable(const void *x, const void *gate_payload, const void *gate_scale,
+                        const void *up_payload, const void *up_scale, const void *y,
+                        uint32_t M, uint32_t K, uint32_t inter);
+
 static inline size_t mmb_align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 #ifdef __cplusplus

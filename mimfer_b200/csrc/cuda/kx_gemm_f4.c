@@ -178,6 +178,29 @@ static mm_status encode_2d(unsigned char out[128], CUtensorMapDataType dt, unsig
     return MM_OK;
 }
 
+/* Two equal 2-D tensors `plane_stride` bytes apart as one 3-D map; a box takes
+ * box_outer rows of each. */
+static mm_status encode_pair(unsigned char out[128], const void *base, uint64_t inner, uint64_t outer,
+                             uint64_t plane_stride, uint32_t box_inner, uint32_t box_outer,
+                             CUtensorMapSwizzle sw)
+{
+    CUtensorMap map;
+    cuuint64_t dims[3] = { inner, outer, 2 };
+    cuuint64_t strides[2] = { inner, plane_stride };
+    cuuint32_t box[3] = { box_inner, box_outer, 2 };
+    cuuint32_t estr[3] = { 1, 1, 1 };
+    CUresult r = G.encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, (void *)(uintptr_t)base, dims, strides,
+                          box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        MM_LOGE("cuTensorMapEncodeTiled (pair) failed: %d (inner %llu outer %llu stride %llu)", (int)r,
+                (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)plane_stride);
+        return MM_ERR_CUDA;
+    }
+    memcpy(out, &map, 128);
+    return MM_OK;
+}
+
 /* ------------------------------------------------------------------ launch */
 static uint32_t min_align(const void *a, const void *b, const void *c, const void *d)
 {
@@ -265,6 +288,112 @@ mm_status mm_f4_linear(const void *x, const void *payload, const void *scale, fl
     return linear_impl(x, payload, scale, gs, y, NULL, 0, 0, 0, M, K, N, stream);
 }
 
+/* Layout rule of the gated pair: both tensors of the two projections in the
+ * same address order, 16-byte-multiple distances below 2^40 (TMA strides). */
+static int pair_layout(const void *gate_payload, const void *gate_scale, const void *up_payload,
+                       const void *up_scale, int *gate_first, uint64_t *dpay, uint64_t *dsc)
+{
+    *gate_first = (uintptr_t)gate_payload < (uintptr_t)up_payload;
+    if (*gate_first != ((uintptr_t)gate_scale < (uintptr_t)up_scale))
+        return 0;
+    *dpay = *gate_first ? (uint64_t)((uintptr_t)up_payload - (uintptr_t)gate_payload)
+                        : (uint64_t)((uintptr_t)gate_payload - (uintptr_t)up_payload);
+    *dsc = *gate_first ? (uint64_t)((uintptr_t)up_scale - (uintptr_t)gate_scale)
+                       : (uint64_t)((uintptr_t)gate_scale - (uintptr_t)up_scale);
+    return *dpay != 0 && *dsc != 0 && *dpay % 16 == 0 && *dsc % 16 == 0 && *dpay < (1ull << 40) &&
+           *dsc < (1ull << 40);
+}
+
+int mmb_gate_up_fusable(const void *x, const void *gate_payload, const void *gate_scale,
+                        const void *up_payload, const void *up_scale, const void *y,
+                        uint32_t M, uint32_t K, uint32_t inter)
+{
+    int gate_first;
+    uint64_t dpay, dsc;
+    if (!pair_layout(gate_payload, gate_scale, up_payload, up_scale, &gate_first, &dpay, &dsc))
+        return 0;
+    mm_f4_plan plan;
+    mm_f4_shape sh = { M, K, inter, 148u,
+                       min_align(x, gate_first ? gate_payload : up_payload,
+                                 gate_first ? gate_scale : up_scale, y), (size_t)1 << 40 };
+    return mm_f4_select_glu(&sh, &plan) == MM_OK;
+}
+
+mm_status mm_f4_mlp_gate_up(const void *x, const void *gate_payload, const void *gate_scale,
+                            float gs_gate, const void *up_payload, const void *up_scale,
+                            float gs_up, void *y, uint32_t M, uint32_t K, uint32_t inter,
+                            void *stream)
+{
+    MM_REQUIRE(x && gate_payload && gate_scale && up_payload && up_scale && y, MM_ERR_STATE);
+    if (M == 0 || inter == 0 || K == 0 || K % 16 != 0)
+        return MM_ERR_SHAPE;
+    MM_CHECK(ensure_ready());
+    if (!stream)
+        stream = mm_cuda_stream_raw(MM_ST_COMPUTE);
+    /* plane 0 of the 3-D maps is the lower-addressed projection, in both tensors */
+    int gate_first;
+    uint64_t dpay, dsc;
+    if (!pair_layout(gate_payload, gate_scale, up_payload, up_scale, &gate_first, &dpay, &dsc))
+        return MM_ERR_UNSUPPORTED;
+    const void *pay0 = gate_first ? gate_payload : up_payload;
+    const void *sc0 = gate_first ? gate_scale : up_scale;
+
+    mmb_args a;
+    memset(&a, 0, sizeof a);
+    a.x = x; a.payload = pay0; a.scale = sc0; a.y = y;
+    a.gs = gs_gate; a.gs_up = gs_up;
+    a.glu = 1; a.gate_plane = gate_first ? 0 : 1;
+    a.M = M; a.K = K; a.N = inter;
+    a.ws = G.ws;
+    a.pdl = G.pdl;
+    mm_f4_shape sh = { M, K, inter, (uint32_t)G.sm_count, min_align(x, pay0, sc0, y), G.ws_bytes };
+    mm_status st = mm_f4_select_glu(&sh, &a.plan);
+    if (st != MM_OK)
+        return st;
+    int err = 0;
+    if (a.plan.variant == MM_F4_V_STREAM) {
+        MM_CHECK(encode_pair(a.tm_payload, pay0, K / 2, inter, dpay, 128, MMB_ST_ROWS / 2,
+                             CU_TENSOR_MAP_SWIZZLE_128B));
+        MM_CHECK(encode_pair(a.tm_scale, sc0, K / 16, inter, dsc, 16, MMB_ST_ROWS / 2,
+                             CU_TENSOR_MAP_SWIZZLE_NONE));
+        MM_CHECK(encode_2d(a.tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, MMB_ST_KSTEP,
+                           a.plan.tile_m, CU_TENSOR_MAP_SWIZZLE_NONE));
+        err = mmb_launch_stream(&a, stream);
+    } else {
+        MM_CHECK(encode_2d(a.tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, MMB_UM_KBLOCK,
+                           a.plan.tile_m, CU_TENSOR_MAP_SWIZZLE_128B));
+        MM_CHECK(encode_pair(a.tm_payload, pay0, K / 2, inter, dpay, 32, a.plan.tile_n / 2,
+                             CU_TENSOR_MAP_SWIZZLE_NONE));
+        MM_CHECK(encode_pair(a.tm_scale, sc0, K / 16, inter, dsc, 16, a.plan.tile_n / 2,
+                             CU_TENSOR_MAP_SWIZZLE_NONE));
+        err = mmb_launch_umma(&a, stream);
+    }
+    if (err) {
+        MM_LOGE("cuda: launch (gated pair, variant %d, M %u K %u inter %u): %s", a.plan.variant, M, K,
+                inter, cudaGetErrorString((cudaError_t)err));
+        return MM_ERR_CUDA;
+    }
+    G.launches++;
+    return MM_OK;
+}
+
+mm_status mm_silu_mul(const void *gate, const void *up, void *y, size_t n, void *stream)
+{
+    MM_REQUIRE(gate && up && y, MM_ERR_STATE);
+    if (n == 0)
+        return MM_ERR_SHAPE;
+    MM_CHECK(ensure_ready());
+    if (!stream)
+        stream = mm_cuda_stream_raw(MM_ST_COMPUTE);
+    int err = mmb_launch_silu_mul(gate, up, y, n, stream);
+    if (err) {
+        MM_LOGE("cuda: silu_mul launch: %s", cudaGetErrorString((cudaError_t)err));
+        return MM_ERR_CUDA;
+    }
+    G.launches++;
+    return MM_OK;
+}
+
 mm_status mm_f4_linear_tp(const void *x, const void *payload, const void *scale, float gs,
                           void *const *y_all, uint32_t n_ranks, uint32_t ldy, uint32_t col0,
                           uint32_t M, uint32_t K, uint32_t N_local, void *stream)
@@ -333,9 +462,45 @@ mm_status kx_op_qkv(const mm_kcall *kc)
     return kx_op_gemm_f4(kc);
 }
 
+mm_status mmb_op_mlp_gate_up(const mm_op_desc *op, const void *up_payload, const void *up_scale)
+{
+    MM_REQUIRE(op && op->a && op->b && op->c && op->d && up_payload && up_scale, MM_ERR_STATE);
+    MM_REQUIRE(mm_cuda_stream_raw(MM_ST_COMPUTE) != NULL, MM_ERR_STATE);
+    mm_status st = mm_f4_mlp_gate_up(op->a, op->b, op->d, mm_f4_gscale_get(op->d), up_payload, up_scale,
+                                     mm_f4_gscale_get(up_scale), op->c, op->n0, op->n1, op->n2,
+                                     mm_cuda_stream_raw(MM_ST_COMPUTE));
+    if (st != MM_OK)
+        return st;
+    return finish_op();
+}
+
+/* OP_LMHEAD carries the same operands as a GEMM (src/kernels/cpu/cx.c:187-190
+ * forwards it to the bf16 GEMM); with a scale tensor in `d` it is the NVFP4 op. */
+mm_status kx_op_lmhead(const mm_kcall *kc)
+{
+    MM_REQUIRE(kc && kc->op, MM_ERR_STATE);
+    if (!kc->op->d)
+        return MM_ERR_UNSUPPORTED;     /* bf16 head: not this library's op */
+    return kx_op_gemm_f4(kc);
+}
+
+/* OP_SILU_MUL: a = gate, b = up, c = y, n0 x n1 elements (include/mimfer/kernels.h:87). */
+mm_status kx_op_silu_mul(const mm_kcall *kc)
+{
+    MM_REQUIRE(kc && kc->op, MM_ERR_STATE);
+    const mm_op_desc *op = kc->op;
+    MM_REQUIRE(op->a && op->b && op->c, MM_ERR_STATE);
+    MM_REQUIRE(mm_cuda_stream_raw(MM_ST_COMPUTE) != NULL, MM_ERR_STATE);
+    mm_status st = mm_silu_mul(op->a, op->b, op->c, (size_t)op->n0 * op->n1,
+                               mm_cuda_stream_raw(MM_ST_COMPUTE));
+    if (st != MM_OK)
+        return st;
+    return finish_op();
+}
+
 int kx_cuda_oppref(int op)
 {
-    return op == OP_GEMM_F4 || op == OP_QKV || op == OP_NOP;
+    return op == OP_GEMM_F4 || op == OP_QKV || op == OP_LMHEAD || op == OP_SILU_MUL || op == OP_NOP;
 }
 
 mm_status mm_kx_invoke(const mm_kcall *kc)
@@ -345,6 +510,8 @@ mm_status mm_kx_invoke(const mm_kcall *kc)
     switch (kc->op->op) {
     case OP_GEMM_F4: return kx_op_gemm_f4(kc);
     case OP_QKV:     return kx_op_qkv(kc);
+    case OP_LMHEAD:  return kx_op_lmhead(kc);
+    case OP_SILU_MUL: return kx_op_silu_mul(kc);
     case OP_NOP:     return MM_OK;
     default:
         MM_LOGE("kx: opcode %d is not served by the NVFP4 linear library", kc->op->op);

@@ -14,11 +14,20 @@
 #include <stdlib.h>
 #include <string.h>
 
+/* Engine-private opcode: gate projection, up projection and silu(gate) * up as
+ * one kernel.  The descriptor is the gate GEMM's with c = the SILU_MUL output;
+ * the up projection's tensors sit in the side array. */
+#define MMB_OP_GATE_UP ((mm_op)(OP_N + 1))
+
+typedef struct up_operands { const void *payload, *scale; } up_operands;
+
 struct mm_lin_engine {
-    mm_op_desc *ops;
-    uint32_t    n_ops, max_ops;
-    mm_graph   *graph;
-    int         captured;
+    mm_op_desc  *ops;
+    up_operands *up;            /* [max_ops], used by MMB_OP_GATE_UP entries */
+    uint32_t     n_ops, max_ops;
+    mm_graph    *graph;
+    int          captured;
+    int          fuse_mlp;
 };
 
 mm_status mm_lin_engine_create(mm_lin_engine **out, uint32_t max_ops)
@@ -28,7 +37,10 @@ mm_status mm_lin_engine_create(mm_lin_engine **out, uint32_t max_ops)
     if (!e)
         return MM_ERR_NOMEM;
     e->ops = (mm_op_desc *)calloc(max_ops, sizeof(mm_op_desc));
-    if (!e->ops) {
+    e->up = (up_operands *)calloc(max_ops, sizeof(up_operands));
+    if (!e->ops || !e->up) {
+        free(e->ops);
+        free(e->up);
         free(e);
         return MM_ERR_NOMEM;
     }
@@ -37,19 +49,72 @@ mm_status mm_lin_engine_create(mm_lin_engine **out, uint32_t max_ops)
     return MM_OK;
 }
 
+mm_status mm_lin_engine_fuse_mlp(mm_lin_engine *e, int on)
+{
+    MM_REQUIRE(e, MM_ERR_STATE);
+    MM_REQUIRE(!e->captured, MM_ERR_BUSY);
+    e->fuse_mlp = on ? 1 : 0;
+    return MM_OK;
+}
+
+/* The reference planner's MLP front half (src/plan/plan.c:223-247) is
+ * GEMM_F4 x -> gate, GEMM_F4 x -> up, SILU_MUL (gate, up) -> y.  When the SILU_MUL
+ * arrives and the two ops before it are exactly that pair, and the fused kernel
+ * can take the operands, the three collapse into one MMB_OP_GATE_UP; the gate and
+ * up buffers are then never written. */
+static int try_fuse_mlp(mm_lin_engine *e, const mm_op_desc *silu)
+{
+    if (!e->fuse_mlp || e->n_ops < 2)
+        return 0;
+    mm_op_desc *g = &e->ops[e->n_ops - 2], *u = &e->ops[e->n_ops - 1];
+    if (g->op != OP_GEMM_F4 || u->op != OP_GEMM_F4)
+        return 0;
+    if (g->c == silu->b && u->c == silu->a) {           /* emitted up first */
+        mm_op_desc *t = g; g = u; u = t;
+    }
+    if (g->c != silu->a || u->c != silu->b || g->a != u->a || g->n0 != u->n0 || g->n1 != u->n1 ||
+        g->n2 != u->n2 || silu->n0 != g->n0 || silu->n1 != g->n2)
+        return 0;
+    if (!mmb_gate_up_fusable(g->a, g->b, g->d, u->b, u->d, silu->c, g->n0, g->n1, g->n2))
+        return 0;
+    mm_op_desc f = *g;
+    up_operands upo = { u->b, u->d };
+    f.op = MMB_OP_GATE_UP;
+    f.c = silu->c;
+    memcpy(f.note, "gate+up+silu", 13);
+    e->n_ops -= 2;
+    e->ops[e->n_ops] = f;
+    e->up[e->n_ops] = upo;
+    e->n_ops++;
+    return 1;
+}
+
 mm_status mm_lin_engine_add(mm_lin_engine *e, const mm_op_desc *op)
 {
     MM_REQUIRE(e && op, MM_ERR_STATE);
     MM_REQUIRE(!e->captured, MM_ERR_BUSY);
     MM_REQUIRE(e->n_ops < e->max_ops, MM_ERR_CAPACITY);
     MM_REQUIRE(kx_cuda_oppref(op->op), MM_ERR_UNSUPPORTED);
-    if (op->op != OP_NOP) {
+    if (op->op == OP_SILU_MUL) {
+        MM_REQUIRE(op->a && op->b && op->c, MM_ERR_STATE);
+        if (op->n0 == 0 || op->n1 == 0)
+            return MM_ERR_SHAPE;
+        if (try_fuse_mlp(e, op))
+            return MM_OK;
+    } else if (op->op != OP_NOP) {
         MM_REQUIRE(op->a && op->b && op->c && op->d, MM_ERR_STATE);
         if (op->n0 == 0 || op->n1 == 0 || op->n2 == 0 || op->n1 % 16 != 0)
             return MM_ERR_SHAPE;
     }
     e->ops[e->n_ops++] = *op;
     return MM_OK;
+}
+
+/* bytes of the op's first input and of its output (host-buffer step) */
+static size_t op_in_bytes(const mm_op_desc *op) { return (size_t)op->n0 * op->n1 * 2u; }
+static size_t op_out_bytes(const mm_op_desc *op)
+{
+    return (size_t)op->n0 * (op->op == OP_SILU_MUL ? op->n1 : op->n2) * 2u;
 }
 
 uint32_t mm_lin_engine_n_ops(const mm_lin_engine *e) { return e ? e->n_ops : 0; }
@@ -61,7 +126,9 @@ static mm_status run_ops(mm_lin_engine *e)
     kc.stream = NULL;
     for (uint32_t i = 0; i < e->n_ops; i++) {
         kc.op = &e->ops[i];
-        mm_status st = mm_kx_invoke(&kc);
+        mm_status st = e->ops[i].op == MMB_OP_GATE_UP
+                           ? mmb_op_mlp_gate_up(&e->ops[i], e->up[i].payload, e->up[i].scale)
+                           : mm_kx_invoke(&kc);
         if (st != MM_OK) {
             MM_LOGE("engine: op %u (%s) failed: %s", i, e->ops[i].note, mm_status_str(st));
             return st;
@@ -102,8 +169,7 @@ mm_status mm_lin_engine_launch_host(mm_lin_engine *e, const void *const *x_host,
     for (uint32_t i = 0; x_host && i < e->n_ops; i++) {
         const mm_op_desc *op = &e->ops[i];
         if (x_host[i] && op->op != OP_NOP)
-            MM_CHECK(mm_h2d_async((void *)(uintptr_t)op->a, x_host[i],
-                                  (size_t)op->n0 * op->n1 * 2u, MM_ST_COMPUTE));
+            MM_CHECK(mm_h2d_async((void *)(uintptr_t)op->a, x_host[i], op_in_bytes(op), MM_ST_COMPUTE));
     }
     if (e->captured)
         MM_CHECK(mm_graph_launch(e->graph, MM_ST_COMPUTE));
@@ -112,7 +178,7 @@ mm_status mm_lin_engine_launch_host(mm_lin_engine *e, const void *const *x_host,
     for (uint32_t i = 0; y_host && i < e->n_ops; i++) {
         const mm_op_desc *op = &e->ops[i];
         if (y_host[i] && op->op != OP_NOP)
-            MM_CHECK(mm_d2h_async(y_host[i], op->c, (size_t)op->n0 * op->n2 * 2u, MM_ST_COMPUTE));
+            MM_CHECK(mm_d2h_async(y_host[i], op->c, op_out_bytes(op), MM_ST_COMPUTE));
     }
     MM_CHECK(mm_stream_sync(MM_ST_COMPUTE));
     unsigned flags = 0;
@@ -130,5 +196,6 @@ void mm_lin_engine_destroy(mm_lin_engine *e)
         return;
     mm_graph_destroy(e->graph);
     free(e->ops);
+    free(e->up);
     free(e);
 }

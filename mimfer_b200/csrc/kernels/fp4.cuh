@@ -125,6 +125,44 @@ __device__ __forceinline__ uint4 unpack8_natural_f16(uint32_t w, uint32_t c)
     return r;
 }
 
+/* silu(g) = g / (1 + exp(-g)) with the two special-function-unit approximations
+ * (ex2.approx and rcp.approx, the non-flushing forms: full range, subnormal
+ * results kept, relative error about 2^-22 each).  A few dozen fp32 ulps at the
+ * ends of the range, far below half a bf16 step, so after the bf16 rounding that
+ * follows it the result differs from an expf-and-divide evaluation only on
+ * near-ties.  Limits as the division gives them: +inf -> +inf, -inf -> NaN,
+ * large negative g -> small negative values down to -0. */
+__device__ __forceinline__ float silu_approx(float g)
+{
+    float e, r;
+    asm("ex2.approx.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
+    asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return g * r;
+}
+
+/* Two outputs of silu(gate) * up on the two projections rounded to bf16 first:
+ * the arithmetic of the reference's separate op (src/kernels/cpu/cx.c:155-167)
+ * on the values its two GEMMs would have stored, for kernels that fuse the three
+ * ops.  Returns the packed bf16 pair (first output in the low half). */
+__device__ __forceinline__ uint32_t glu_out_bf16x2(float gate0, float gate1, float up0, float up1,
+                                                   float gate_scale, float up_scale)
+{
+    const __nv_bfloat162 gq = __floats2bfloat162_rn(gate0 * gate_scale, gate1 * gate_scale);
+    const __nv_bfloat162 uq = __floats2bfloat162_rn(up0 * up_scale, up1 * up_scale);
+    const uint32_t gb = *reinterpret_cast<const uint32_t *>(&gq);
+    const uint32_t ub = *reinterpret_cast<const uint32_t *>(&uq);
+    const float y0 = silu_approx(__uint_as_float(gb << 16)) * __uint_as_float(ub << 16);
+    const float y1 = silu_approx(__uint_as_float(gb & 0xffff0000u)) * __uint_as_float(ub & 0xffff0000u);
+    const __nv_bfloat162 o = __floats2bfloat162_rn(y0, y1);
+    return *reinterpret_cast<const uint32_t *>(&o);
+}
+
+__device__ __forceinline__ uint16_t glu_out_bf16(float gate_acc, float up_acc, float gate_scale,
+                                                 float up_scale)
+{
+    return static_cast<uint16_t>(glu_out_bf16x2(gate_acc, 0.0f, up_acc, 0.0f, gate_scale, up_scale) & 0xffffu);
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
 {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

@@ -72,6 +72,14 @@ typedef struct mmb_args {
     uint32_t    n_dst, ldy, col0;
     float       gs;
     uint32_t    M, K, N;
+    /* Gated pair (glu != 0): `payload`/`scale` are the lower-addressed of the gate
+     * and up projections, tm_payload/tm_scale are 3-D maps whose third
+     * coordinate selects the projection (plane 0 = lower address), N counts the
+     * output features (rows of each projection), and the kernel writes
+     * y[m][j] = bf16(silu(bf16(gate)) * bf16(up)) with pitch N.  gate_plane says
+     * which plane is the gate; gs scales the gate, gs_up the up projection. */
+    int         glu, gate_plane;
+    float       gs_up;
     void       *ws;       /* workspace base or NULL */
     mm_f4_plan  plan;
     int         pdl;      /* launch with programmatic stream serialization */
@@ -87,6 +95,7 @@ int mmb_launch_rowwarp(const mmb_args *a, void *stream);
 int mmb_launch_stream(const mmb_args *a, void *stream);
 int mmb_launch_umma(const mmb_args *a, void *stream);
 int mmb_launch_streamt(const mmb_args *a, void *stream);
+int mmb_launch_silu_mul(const void *gate, const void *up, void *y, size_t n, void *stream);
 int mmb_launch_wait_selftest(unsigned *status, unsigned *done, void *stream);
 int mmb_launch_decode_probe(uint32_t *out_mma, uint32_t *out_f32, uint32_t *out_f16, void *stream);
 /* One-time per-process setup (smem opt-in attributes). */

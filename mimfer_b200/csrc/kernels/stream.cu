@@ -53,13 +53,17 @@ struct StreamParams {
     float           gs;
     uint32_t        M, K, N;
     uint32_t        k_steps, split_k, stages;
+    float           gs_up;       /* gated pair: scale of the up projection        */
+    uint32_t        gate_plane;  /* gated pair: which half of the CTA's rows is the gate */
 };
 
 /* One output element to every destination (one, or all tensor-parallel peers). */
 __device__ __forceinline__ void store_all(const StreamParams &p, uint32_t m, uint32_t n, uint16_t v)
 {
     const size_t off = static_cast<size_t>(m) * p.ldy + p.col0 + n;
-    for (uint32_t d = 0; d < p.n_dst; d++)
+    p.y[0][off] = v;
+#pragma unroll 1                       /* kept rolled: this runs once per output, code size matters more */
+    for (uint32_t d = 1; d < p.n_dst; d++)
         p.y[d][off] = v;
 }
 
@@ -176,7 +180,67 @@ __device__ __forceinline__ void consume_step(float (&accs)[SLOTS][RT][MT][4], ui
     }
 }
 
-template <int MT>
+/* The weight boxes of one K step.  Gated pair: one 3-D box brings 128 rows of
+ * each projection, plane 0 first, so the CTA's 256 rows are [plane 0 | plane 1]. */
+template <bool GLU>
+__device__ __forceinline__ void load_weights(uint32_t stage, const TmaDesc *tm_payload,
+                                             const TmaDesc *tm_scale, uint32_t ks, uint32_t row0,
+                                             uint32_t bar)
+{
+    if constexpr (GLU) {
+        tma_load_3d(stage, tm_payload, static_cast<int>(ks * 128u), static_cast<int>(row0), 0, bar);
+        tma_load_3d(stage + MMB_ST_PAYLOAD_B, tm_scale, static_cast<int>(ks * 16u),
+                    static_cast<int>(row0), 0, bar);
+    } else {
+        tma_load_2d(stage, tm_payload, static_cast<int>(ks * 128u), static_cast<int>(row0), bar);
+        tma_load_2d(stage + MMB_ST_PAYLOAD_B, tm_scale, static_cast<int>(ks * 16u),
+                    static_cast<int>(row0), bar);
+    }
+}
+
+/* Gated pair, last step: the warps holding plane 1 hand their sums to the warps
+ * holding plane 0 through shared memory (the ring is idle by then), which apply
+ * the scales, silu(gate) * up and store.  v: final fp32 sums of this thread. */
+template <int MT, int RT>
+__device__ __forceinline__ void glu_store(const StreamParams &p, const float (&v)[RT][MT][4],
+                                          uint32_t xch, uint32_t j0, uint32_t warp, uint32_t g,
+                                          uint32_t t)
+{
+    constexpr uint32_t MPAD = MT * 8, HALF_ROWS = MMB_ST_ROWS / 2;
+    const bool upper = warp * (16u * RT) >= HALF_ROWS;
+    asm volatile("bar.sync 1, %0;" ::"n"(MMB_ST_CONSUMERS * 32) : "memory");   /* every warp left the ring */
+    if (upper) {
+#pragma unroll
+        for (int rt = 0; rt < RT; rt++)
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t lr = warp * (16u * RT) + rt * 16u + (i >> 1) * 8u + g - HALF_ROWS;
+                    const uint32_t m = mt * 8u + 2u * t + (i & 1);
+                    sts32(xch + (lr * MPAD + m) * 4u, __float_as_uint(v[rt][mt][i]));
+                }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(MMB_ST_CONSUMERS * 32) : "memory");
+    if (upper)
+        return;
+#pragma unroll
+    for (int rt = 0; rt < RT; rt++)
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t lr = warp * (16u * RT) + rt * 16u + (i >> 1) * 8u + g;
+                const uint32_t m = mt * 8u + 2u * t + (i & 1);
+                const float other = __uint_as_float(lds32(xch + (lr * MPAD + m) * 4u));
+                const float gate = p.gate_plane ? other : v[rt][mt][i];
+                const float up = p.gate_plane ? v[rt][mt][i] : other;
+                if (j0 + lr < p.N && m < p.M)
+                    store_all(p, m, j0 + lr, glu_out_bf16(gate, up, p.gs, p.gs_up));
+            }
+}
+
+template <int MT, bool GLU>
 __global__ void __launch_bounds__(MMB_ST_THREADS, 1)
 f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
                  const __grid_constant__ TmaDesc tm_scale, const __grid_constant__ TmaDesc tm_x,
@@ -198,7 +262,8 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
     const uint32_t last_flag = fmt_flag + 4u * p.stages;     /* split-K: "this CTA reduces" */
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    const uint32_t row0 = blockIdx.x * MMB_ST_ROWS;
+    /* first weight row of the CTA (of each projection for a gated pair) */
+    const uint32_t row0 = blockIdx.x * (GLU ? MMB_ST_ROWS / 2 : MMB_ST_ROWS);
     const uint32_t ks_begin = static_cast<uint32_t>(
         static_cast<uint64_t>(p.k_steps) * blockIdx.y / p.split_k);
     const uint32_t ks_end = static_cast<uint32_t>(
@@ -222,10 +287,7 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
         for (uint32_t it = 0; it < first; it++) {
             const uint32_t stage = base + it * STAGE_B, ks = ks_begin + it;
             mbar_expect_tx(bar_raw + 8u * it, stage_bytes);
-            tma_load_2d(stage, &tm_payload, static_cast<int>(ks * 128u),
-                        static_cast<int>(row0), bar_raw + 8u * it);
-            tma_load_2d(stage + MMB_ST_PAYLOAD_B, &tm_scale, static_cast<int>(ks * 16u),
-                        static_cast<int>(row0), bar_raw + 8u * it);
+            load_weights<GLU>(stage, &tm_payload, &tm_scale, ks, row0, bar_raw + 8u * it);
         }
     }
     if (tid < 256u) {
@@ -253,10 +315,7 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
                 mbar_wait(bar_empty + 8u * s, (round - 1u) & 1u, p.status);
                 fence_proxy_async_smem();          /* generic writes of the slot precede the refill */
                 mbar_expect_tx(bar_raw + 8u * s, stage_bytes);
-                tma_load_2d(stage, &tm_payload, static_cast<int>(ks * 128u),
-                            static_cast<int>(row0), bar_raw + 8u * s);
-                tma_load_2d(stage + MMB_ST_PAYLOAD_B, &tm_scale, static_cast<int>(ks * 16u),
-                            static_cast<int>(row0), bar_raw + 8u * s);
+                load_weights<GLU>(stage, &tm_payload, &tm_scale, ks, row0, bar_raw + 8u * s);
                 tma_load_2d(stage + MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B, &tm_x,
                             static_cast<int>(ks * MMB_ST_KSTEP), 0, bar_raw + 8u * s);
             }
@@ -361,34 +420,43 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
                 acc[rt][mt][i] = v;
             }
     if (p.split_k == 1) {
+        if constexpr (GLU) {
+            glu_store<MT, RT>(p, acc, base, row0, warp, g, t);
+        } else {
 #pragma unroll
-        for (int rt = 0; rt < RT; rt++)
+            for (int rt = 0; rt < RT; rt++)
 #pragma unroll
-            for (int mt = 0; mt < MT; mt++)
+                for (int mt = 0; mt < MT; mt++)
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const uint32_t n = row0 + warp * (16u * RT) + rt * 16u + (i >> 1) * 8u + g;
-                    const uint32_t m = mt * 8u + 2u * t + (i & 1);
-                    if (n < p.N && m < p.M) {
-                        __nv_bfloat16 hv = __float2bfloat16_rn(acc[rt][mt][i] * out_scale);
-                        store_all(p, m, n, *reinterpret_cast<uint16_t *>(&hv));
+                    for (int i = 0; i < 4; i++) {
+                        const uint32_t n = row0 + warp * (16u * RT) + rt * 16u + (i >> 1) * 8u + g;
+                        const uint32_t m = mt * 8u + 2u * t + (i & 1);
+                        if (n < p.N && m < p.M) {
+                            __nv_bfloat16 hv = __float2bfloat16_rn(acc[rt][mt][i] * out_scale);
+                            store_all(p, m, n, *reinterpret_cast<uint16_t *>(&hv));
+                        }
                     }
-                }
+        }
         return;
     }
 
-    /* split-K: publish this slice, the last CTA of the row block reduces */
-    float *mine = p.partial + static_cast<size_t>(blockIdx.y) * MPAD * p.N;
+    /* split-K: publish this slice, the last CTA of the row block reduces.  The
+     * partials hold one column per weight row of the CTA tiles (pitch = padded
+     * row count for a gated pair, whose tiles interleave the two projections). */
+#define MMB_PCOL(lr) (GLU ? blockIdx.x * MMB_ST_ROWS + (lr) : row0 + (lr))
+#define MMB_PPITCH (GLU ? gridDim.x * MMB_ST_ROWS : p.N)
+#define MMB_ROW_OK(lr) (GLU ? (row0 + ((lr) & (MMB_ST_ROWS / 2 - 1u)) < p.N) : (row0 + (lr) < p.N))
+    float *mine = p.partial + static_cast<size_t>(blockIdx.y) * MPAD * MMB_PPITCH;
 #pragma unroll
     for (int rt = 0; rt < RT; rt++)
 #pragma unroll
         for (int mt = 0; mt < MT; mt++)
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const uint32_t n = row0 + warp * (16u * RT) + rt * 16u + (i >> 1) * 8u + g;
-                const uint32_t m = mt * 8u + 2u * t + (i & 1);
-                if (n < p.N && m < p.M)
-                    __stcg(mine + static_cast<size_t>(m) * p.N + n, acc[rt][mt][i]);
+                const uint32_t lr = warp * (16u * RT) + rt * 16u + (i >> 1) * 8u + g;
+                const uint32_t m = mt * 8u + 2u * t + (i & 1), pc = MMB_PCOL(lr);
+                if (MMB_ROW_OK(lr) && m < p.M)
+                    __stcg(mine + static_cast<size_t>(m) * MMB_PPITCH + pc, acc[rt][mt][i]);
             }
     __threadfence();
     asm volatile("bar.sync 1, %0;" ::"n"(MMB_ST_CONSUMERS * 32) : "memory");
@@ -421,12 +489,12 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
                 for (int mt = 0; mt < MT; mt++)
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
-                        const uint32_t n = row0 + warp * (16u * RT) + rt * 16u + (i >> 1) * 8u + g;
-                        const uint32_t m = mt * 8u + 2u * t + (i & 1);
+                        const uint32_t lr = warp * (16u * RT) + rt * 16u + (i >> 1) * 8u + g;
+                        const uint32_t m = mt * 8u + 2u * t + (i & 1), pc = MMB_PCOL(lr);
                         v[u][rt][mt][i] = 0.0f;
-                        if (n < p.N && m < p.M && sl + u < p.split_k)
-                            v[u][rt][mt][i] =
-                                __ldcg(p.partial + (static_cast<size_t>(sl + u) * MPAD + m) * p.N + n);
+                        if (MMB_ROW_OK(lr) && m < p.M && sl + u < p.split_k)
+                            v[u][rt][mt][i] = __ldcg(p.partial +
+                                (static_cast<size_t>(sl + u) * MPAD + m) * MMB_PPITCH + pc);
                     }
 #pragma unroll
         for (int u = 0; u < BATCH; u++)
@@ -437,24 +505,31 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
 #pragma unroll
                     for (int i = 0; i < 4; i++) sum[rt][mt][i] += v[u][rt][mt][i];
     }
+    if constexpr (GLU) {
+        glu_store<MT, RT>(p, sum, base, row0, warp, g, t);
+    } else {
 #pragma unroll
-    for (int rt = 0; rt < RT; rt++)
+        for (int rt = 0; rt < RT; rt++)
 #pragma unroll
-        for (int mt = 0; mt < MT; mt++)
+            for (int mt = 0; mt < MT; mt++)
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const uint32_t n = row0 + warp * (16u * RT) + rt * 16u + (i >> 1) * 8u + g;
-                const uint32_t m = mt * 8u + 2u * t + (i & 1);
-                if (n < p.N && m < p.M) {
-                    __nv_bfloat16 hv = __float2bfloat16_rn(sum[rt][mt][i] * out_scale);
-                    store_all(p, m, n, *reinterpret_cast<uint16_t *>(&hv));
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t n = row0 + warp * (16u * RT) + rt * 16u + (i >> 1) * 8u + g;
+                    const uint32_t m = mt * 8u + 2u * t + (i & 1);
+                    if (n < p.N && m < p.M) {
+                        __nv_bfloat16 hv = __float2bfloat16_rn(sum[rt][mt][i] * out_scale);
+                        store_all(p, m, n, *reinterpret_cast<uint16_t *>(&hv));
+                    }
                 }
-            }
+    }
     if (tid == 0)
         p.counters[blockIdx.x] = 0u;                /* ready for the next launch */
+#undef MMB_ROW_OK
+#undef MMB_PCOL
+#undef MMB_PPITCH
 }
 
-template <int MT>
+template <int MT, bool GLU>
 static int launch_mt(const mmb_args *a, unsigned *status, cudaStream_t st)
 {
     StreamParams p;
@@ -475,6 +550,8 @@ static int launch_mt(const mmb_args *a, unsigned *status, cudaStream_t st)
     p.k_steps = a->plan.k_steps;
     p.split_k = a->plan.split_k;
     p.stages = a->plan.stages;
+    p.gs_up = a->gs_up;
+    p.gate_plane = a->gate_plane ? 1u : 0u;
     TmaDesc tp, ts, tx;
     memcpy(tp.bytes, a->tm_payload, 128);
     memcpy(ts.bytes, a->tm_scale, 128);
@@ -489,23 +566,26 @@ static int launch_mt(const mmb_args *a, unsigned *status, cudaStream_t st)
     attr[0].val.programmaticStreamSerializationAllowed = a->pdl ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return static_cast<int>(cudaLaunchKernelEx(&cfg, f4_stream_kernel<MT>, tp, ts, tx, p));
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, f4_stream_kernel<MT, GLU>, tp, ts, tx, p));
 }
 
 } // namespace mmb
 
 extern "C" int mmb_stream_init(void)
 {
-    cudaError_t e;
-    e = cudaFuncSetAttribute(mmb::f4_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             MMB_SMEM_MAX);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    e = cudaFuncSetAttribute(mmb::f4_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             MMB_SMEM_MAX);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    e = cudaFuncSetAttribute(mmb::f4_stream_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             MMB_SMEM_MAX);
-    return static_cast<int>(e);
+    const void *kernels[6] = {
+        reinterpret_cast<const void *>(mmb::f4_stream_kernel<1, false>),
+        reinterpret_cast<const void *>(mmb::f4_stream_kernel<2, false>),
+        reinterpret_cast<const void *>(mmb::f4_stream_kernel<4, false>),
+        reinterpret_cast<const void *>(mmb::f4_stream_kernel<1, true>),
+        reinterpret_cast<const void *>(mmb::f4_stream_kernel<2, true>),
+        reinterpret_cast<const void *>(mmb::f4_stream_kernel<4, true>),
+    };
+    for (const void *k : kernels) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, MMB_SMEM_MAX);
+        if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    return 0;
 }
 
 extern "C" int mmb_launch_stream(const mmb_args *a, void *stream)
@@ -516,10 +596,12 @@ extern "C" int mmb_launch_stream(const mmb_args *a, void *stream)
     if (a->plan.split_k > 1 && !a->ws)
         return static_cast<int>(cudaErrorInvalidValue);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (a->glu && a->n_dst)
+        return static_cast<int>(cudaErrorInvalidValue);    /* the gated pair has no peer-store form */
     switch (a->plan.m_tiles) {
-    case 1: return mmb::launch_mt<1>(a, status, st);
-    case 2: return mmb::launch_mt<2>(a, status, st);
-    case 4: return mmb::launch_mt<4>(a, status, st);
+    case 1: return a->glu ? mmb::launch_mt<1, true>(a, status, st) : mmb::launch_mt<1, false>(a, status, st);
+    case 2: return a->glu ? mmb::launch_mt<2, true>(a, status, st) : mmb::launch_mt<2, false>(a, status, st);
+    case 4: return a->glu ? mmb::launch_mt<4, true>(a, status, st) : mmb::launch_mt<4, false>(a, status, st);
     default: return static_cast<int>(cudaErrorInvalidValue);
     }
 }

@@ -40,9 +40,23 @@ struct UmmaParams {
     uint32_t  M, K, N;
     uint32_t  k_blocks;      /* K / 64 */
     uint32_t  stages;
+    float     gs_up;         /* gated pair: scale of the up projection          */
+    uint32_t  gate_plane;    /* gated pair: which half of the weight tile is the gate */
 };
 
-template <int BM, int BN>
+/* One weight box.  Gated pair: a 3-D box brings BN/2 rows of each projection,
+ * plane 0 first, so accumulator columns [0, BN/2) belong to plane 0. */
+template <bool GLU>
+__device__ __forceinline__ void load_w(uint32_t dst, const TmaDesc *map, uint32_t x, uint32_t row,
+                                       uint32_t bar)
+{
+    if constexpr (GLU)
+        tma_load_3d(dst, map, static_cast<int>(x), static_cast<int>(row), 0, bar);
+    else
+        tma_load_2d(dst, map, static_cast<int>(x), static_cast<int>(row), bar);
+}
+
+template <int BM, int BN, bool GLU>
 __global__ void __launch_bounds__(MMB_UM_THREADS, 1)
 f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ TmaDesc tm_payload,
                const __grid_constant__ TmaDesc tm_scale, const UmmaParams p)
@@ -78,7 +92,10 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     /* activation-row tile fastest: the CTAs running together share a few weight
      * tiles (and all of x) through L2 instead of each streaming the whole weight */
-    const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    static_assert(!GLU || BN == 256, "the gated pair runs on 256-row weight tiles");
+    /* n0: first weight row of the tile (of each projection, and the first output
+     * column, for a gated pair) */
+    const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * (GLU ? BN / 2 : BN);
     const uint32_t KB = p.k_blocks;
     const uint32_t pre_pay = KB < PAY_SLOTS ? KB : PAY_SLOTS;   /* payload boxes issued in the prologue */
 
@@ -107,11 +124,10 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
         tma_prefetch_desc(&tm_scale);
         for (uint32_t kb = 0; kb < pre_pay; kb++) {
             mbar_expect_tx(full_pay + 8u * kb, PAY_B);
-            tma_load_2d(sm_pay + kb * PAY_B, &tm_payload, static_cast<int>(kb * 32u),
-                        static_cast<int>(n0), full_pay + 8u * kb);
+            load_w<GLU>(sm_pay + kb * PAY_B, &tm_payload, kb * 32u, n0, full_pay + 8u * kb);
         }
         mbar_expect_tx(full_sc, SC_B);
-        tma_load_2d(sm_sc, &tm_scale, 0, static_cast<int>(n0), full_sc);
+        load_w<GLU>(sm_sc, &tm_scale, 0u, n0, full_sc);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, TMEM_COLS);
@@ -138,14 +154,12 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
                     if (grp >= MMB_UM_SC_SLOTS)
                         mbar_wait(empty_sc + 8u * ss, ((grp / MMB_UM_SC_SLOTS) - 1u) & 1u, p.status);
                     mbar_expect_tx(full_sc + 8u * ss, SC_B);
-                    tma_load_2d(sm_sc + ss * SC_B, &tm_scale, static_cast<int>(grp * 16u),
-                                static_cast<int>(n0), full_sc + 8u * ss);
+                    load_w<GLU>(sm_sc + ss * SC_B, &tm_scale, grp * 16u, n0, full_sc + 8u * ss);
                 }
                 if (kb >= pre_pay) {
                     mbar_wait(empty_pay + 8u * ps, ((kb / PAY_SLOTS) - 1u) & 1u, p.status);
                     mbar_expect_tx(full_pay + 8u * ps, PAY_B);
-                    tma_load_2d(sm_pay + ps * PAY_B, &tm_payload, static_cast<int>(kb * 32u),
-                                static_cast<int>(n0), full_pay + 8u * ps);
+                    load_w<GLU>(sm_pay + ps * PAY_B, &tm_payload, kb * 32u, n0, full_pay + 8u * ps);
                 }
                 if (round > 0)
                     mbar_wait(empty_ab + 8u * s, (round - 1u) & 1u, p.status);
@@ -226,54 +240,110 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
         const float out_scale = p.gs * 256.0f;      /* undo the 2^-8 of the operand form */
         const uint32_t quad = warp & 3u;            /* TMEM lanes this warp may read   */
         const uint32_t pair = (warp - 2u) >> 2;     /* two warps share a quadrant       */
-        constexpr uint32_t PIECES = HALVES * (BN / 128);
-        constexpr uint32_t PITCH = 272u;            /* 256 B of data + 16 B: conflict-free both ways */
-        const uint32_t stg = sm_a + (warp - 2u) * (32u * PITCH);
-        const bool vec_ok = (p.N % 8u) == 0;
-        for (uint32_t c = pair; c < PIECES; c += 2u) {
-            const uint32_t h = c / (BN / 128), cc = c % (BN / 128);
-            const uint32_t n_base = n0 + cc * 128u;
+        if constexpr (GLU) {
+            /* Gated pair: pieces of 32 rows x 64 outputs.  Gate and up sums of an
+             * output sit 128 columns apart in the same lane; silu(gate) * up on
+             * their bf16 roundings, staged, then 128-byte row runs go out, four
+             * rows per warp store. */
+            constexpr uint32_t GPITCH = 144u;       /* 128 B of data + 16 B */
+            const float s_gate = p.gs * 256.0f, s_up = p.gs_up * 256.0f;
+            const uint32_t gstg = sm_a + (warp - 2u) * (32u * GPITCH);
+            const uint32_t gcol = p.gate_plane ? BN / 2 : 0u, ucol = p.gate_plane ? 0u : BN / 2;
+            const bool gvec = (p.N % 8u) == 0;
+            for (uint32_t c = pair; c < HALVES * 2u; c += 2u) {
+                const uint32_t h = c >> 1, cc = c & 1u;
 #pragma unroll
-            for (uint32_t q = 0; q < 4; q++) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + h * BN + cc * 128u + q * 32u, r);
-                tmem_ld_wait();
+                for (uint32_t q = 0; q < 2; q++) {
+                    uint32_t a[32], b[32];
+                    const uint32_t col = tmem_base + ((quad * 32u) << 16) + h * BN + cc * 64u + q * 32u;
+                    tmem_ld_32x32(col + gcol, a);
+                    tmem_ld_32x32(col + ucol, b);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int v = 0; v < 4; v++) {
-                    uint4 o;
-                    o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]) * out_scale,
-                                      __uint_as_float(r[8 * v + 1]) * out_scale);
-                    o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]) * out_scale,
-                                      __uint_as_float(r[8 * v + 3]) * out_scale);
-                    o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]) * out_scale,
-                                      __uint_as_float(r[8 * v + 5]) * out_scale);
-                    o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]) * out_scale,
-                                      __uint_as_float(r[8 * v + 7]) * out_scale);
-                    sts128(stg + lane * PITCH + q * 64u + v * 16u, o);
-                }
-            }
-            __syncwarp();
-            const uint32_t sub = lane >> 4, col16 = lane & 15u;      /* 2 rows x 16 chunks per store */
-            const uint32_t n = n_base + col16 * 8u;
-#pragma unroll 4
-            for (uint32_t rr = 0; rr < 32u; rr += 2u) {
-                const uint32_t row = rr + sub;
-                const uint32_t m = m0 + h * 128u + quad * 32u + row;
-                if (m < p.M && n < p.N) {
-                    const uint4 o = lds128(stg + row * PITCH + col16 * 16u);
-                    const size_t off = static_cast<size_t>(m) * p.ldy + p.col0 + n;
-                    if (vec_ok) {
-                        for (uint32_t d = 0; d < p.n_dst; d++)
-                            *reinterpret_cast<uint4 *>(p.y[d] + off) = o;
-                    } else {
-                        const uint32_t w4[4] = { o.x, o.y, o.z, o.w };
-                        for (uint32_t e = 0; e < 8u && n + e < p.N; e++)
-                            for (uint32_t d = 0; d < p.n_dst; d++)
-                                p.y[d][off + e] = static_cast<uint16_t>(w4[e >> 1] >> (16u * (e & 1u)));
+                    for (int v = 0; v < 4; v++) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++)
+                            w[e] = glu_out_bf16x2(__uint_as_float(a[8 * v + 2 * e]),
+                                                  __uint_as_float(a[8 * v + 2 * e + 1]),
+                                                  __uint_as_float(b[8 * v + 2 * e]),
+                                                  __uint_as_float(b[8 * v + 2 * e + 1]), s_gate, s_up);
+                        sts128(gstg + lane * GPITCH + q * 64u + v * 16u, make_uint4(w[0], w[1], w[2], w[3]));
                     }
                 }
+                __syncwarp();
+                const uint32_t sub = lane >> 3, col8 = lane & 7u;     /* 4 rows x 8 chunks per store */
+                const uint32_t n = n0 + cc * 64u + col8 * 8u;
+#pragma unroll 4
+                for (uint32_t rr = 0; rr < 32u; rr += 4u) {
+                    const uint32_t row = rr + sub;
+                    const uint32_t m = m0 + h * 128u + quad * 32u + row;
+                    if (m < p.M && n < p.N) {
+                        const uint4 o = lds128(gstg + row * GPITCH + col8 * 16u);
+                        const size_t off = static_cast<size_t>(m) * p.ldy + p.col0 + n;
+                        if (gvec) {
+                            for (uint32_t d = 0; d < p.n_dst; d++)
+                                *reinterpret_cast<uint4 *>(p.y[d] + off) = o;
+                        } else {
+                            const uint32_t w4[4] = { o.x, o.y, o.z, o.w };
+                            for (uint32_t e = 0; e < 8u && n + e < p.N; e++)
+                                for (uint32_t d = 0; d < p.n_dst; d++)
+                                    p.y[d][off + e] = static_cast<uint16_t>(w4[e >> 1] >> (16u * (e & 1u)));
+                        }
+                    }
+                }
+                __syncwarp();
             }
-            __syncwarp();
+        } else {
+            constexpr uint32_t PIECES = HALVES * (BN / 128);
+            constexpr uint32_t PITCH = 272u;            /* 256 B of data + 16 B: conflict-free both ways */
+            const uint32_t stg = sm_a + (warp - 2u) * (32u * PITCH);
+            const bool vec_ok = (p.N % 8u) == 0;
+            for (uint32_t c = pair; c < PIECES; c += 2u) {
+                const uint32_t h = c / (BN / 128), cc = c % (BN / 128);
+                const uint32_t n_base = n0 + cc * 128u;
+#pragma unroll
+                for (uint32_t q = 0; q < 4; q++) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + h * BN + cc * 128u + q * 32u, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int v = 0; v < 4; v++) {
+                        uint4 o;
+                        o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]) * out_scale,
+                                          __uint_as_float(r[8 * v + 1]) * out_scale);
+                        o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]) * out_scale,
+                                          __uint_as_float(r[8 * v + 3]) * out_scale);
+                        o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]) * out_scale,
+                                          __uint_as_float(r[8 * v + 5]) * out_scale);
+                        o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]) * out_scale,
+                                          __uint_as_float(r[8 * v + 7]) * out_scale);
+                        sts128(stg + lane * PITCH + q * 64u + v * 16u, o);
+                    }
+                }
+                __syncwarp();
+                const uint32_t sub = lane >> 4, col16 = lane & 15u;      /* 2 rows x 16 chunks per store */
+                const uint32_t n = n_base + col16 * 8u;
+#pragma unroll 4
+                for (uint32_t rr = 0; rr < 32u; rr += 2u) {
+                    const uint32_t row = rr + sub;
+                    const uint32_t m = m0 + h * 128u + quad * 32u + row;
+                    if (m < p.M && n < p.N) {
+                        const uint4 o = lds128(stg + row * PITCH + col16 * 16u);
+                        const size_t off = static_cast<size_t>(m) * p.ldy + p.col0 + n;
+                        if (vec_ok) {
+                            for (uint32_t d = 0; d < p.n_dst; d++)
+                                *reinterpret_cast<uint4 *>(p.y[d] + off) = o;
+                        } else {
+                            const uint32_t w4[4] = { o.x, o.y, o.z, o.w };
+                            for (uint32_t e = 0; e < 8u && n + e < p.N; e++)
+                                for (uint32_t d = 0; d < p.n_dst; d++)
+                                    p.y[d][off + e] = static_cast<uint16_t>(w4[e >> 1] >> (16u * (e & 1u)));
+                        }
+                    }
+                }
+                __syncwarp();
+            }
         }
     }
 
@@ -285,7 +355,7 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
     }
 }
 
-template <int BM, int BN>
+template <int BM, int BN, bool GLU>
 static int launch_tile(const mmb_args *a, unsigned *status, cudaStream_t st)
 {
     UmmaParams p;
@@ -301,6 +371,8 @@ static int launch_tile(const mmb_args *a, unsigned *status, cudaStream_t st)
     p.M = a->M; p.K = a->K; p.N = a->N;
     p.k_blocks = a->plan.k_steps;
     p.stages = a->plan.stages;
+    p.gs_up = a->gs_up;
+    p.gate_plane = a->gate_plane ? 1u : 0u;
     TmaDesc tx, tp, ts;
     memcpy(tx.bytes, a->tm_x, 128);
     memcpy(tp.bytes, a->tm_payload, 128);
@@ -315,13 +387,13 @@ static int launch_tile(const mmb_args *a, unsigned *status, cudaStream_t st)
     attr[0].val.programmaticStreamSerializationAllowed = a->pdl ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return static_cast<int>(cudaLaunchKernelEx(&cfg, f4_umma_kernel<BM, BN>, tx, tp, ts, p));
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, f4_umma_kernel<BM, BN, GLU>, tx, tp, ts, p));
 }
 
-template <int BM, int BN>
+template <int BM, int BN, bool GLU>
 static int set_smem()
 {
-    return static_cast<int>(cudaFuncSetAttribute(f4_umma_kernel<BM, BN>,
+    return static_cast<int>(cudaFuncSetAttribute(f4_umma_kernel<BM, BN, GLU>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  MMB_SMEM_MAX));
 }
@@ -331,10 +403,12 @@ static int set_smem()
 extern "C" int mmb_umma_init(void)
 {
     int e;
-    if ((e = mmb::set_smem<256, 256>())) return e;
-    if ((e = mmb::set_smem<256, 128>())) return e;
-    if ((e = mmb::set_smem<128, 256>())) return e;
-    return mmb::set_smem<128, 128>();
+    if ((e = mmb::set_smem<256, 256, false>())) return e;
+    if ((e = mmb::set_smem<256, 128, false>())) return e;
+    if ((e = mmb::set_smem<128, 256, false>())) return e;
+    if ((e = mmb::set_smem<128, 128, false>())) return e;
+    if ((e = mmb::set_smem<256, 256, true>())) return e;
+    return mmb::set_smem<128, 256, true>();
 }
 
 extern "C" int mmb_launch_umma(const mmb_args *a, void *stream)
@@ -344,9 +418,14 @@ extern "C" int mmb_launch_umma(const mmb_args *a, void *stream)
     if (e) return e;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint32_t bm = a->plan.tile_m, bn = a->plan.tile_n;
-    if (bm == 256 && bn == 256) return mmb::launch_tile<256, 256>(a, status, st);
-    if (bm == 256 && bn == 128) return mmb::launch_tile<256, 128>(a, status, st);
-    if (bm == 128 && bn == 256) return mmb::launch_tile<128, 256>(a, status, st);
-    if (bm == 128 && bn == 128) return mmb::launch_tile<128, 128>(a, status, st);
+    if (a->glu) {
+        if (bm == 256 && bn == 256) return mmb::launch_tile<256, 256, true>(a, status, st);
+        if (bm == 128 && bn == 256) return mmb::launch_tile<128, 256, true>(a, status, st);
+        return static_cast<int>(cudaErrorInvalidValue);
+    }
+    if (bm == 256 && bn == 256) return mmb::launch_tile<256, 256, false>(a, status, st);
+    if (bm == 256 && bn == 128) return mmb::launch_tile<256, 128, false>(a, status, st);
+    if (bm == 128 && bn == 256) return mmb::launch_tile<128, 256, false>(a, status, st);
+    if (bm == 128 && bn == 128) return mmb::launch_tile<128, 128, false>(a, status, st);
     return static_cast<int>(cudaErrorInvalidValue);
 }

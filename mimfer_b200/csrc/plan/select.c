@@ -178,6 +178,45 @@ mm_status mm_f4_select_variant(const mm_f4_shape *s, int variant, mm_f4_plan *ou
     }
 }
 
+/* Gated pair (gate and up projections + silu(gate) * up in one kernel): s->N is
+ * the number of output features, so the kernels stream 2 * N weight rows and a
+ * CTA's 256-row tile is 128 rows of each projection.  Only the TMA kernels have
+ * the fused form; anything else is MM_ERR_UNSUPPORTED and runs as three ops. */
+mm_status mm_f4_select_glu(const mm_f4_shape *s, mm_f4_plan *out)
+{
+    mm_status st = check_shape(s, out);
+    if (st != MM_OK)
+        return st;
+    if (!fast_path_ok(s))
+        return MM_ERR_UNSUPPORTED;
+    mm_f4_shape rows = *s;
+    rows.N = ceil_div(s->N, MMB_ST_ROWS / 2) * MMB_ST_ROWS;      /* weight rows incl. tile padding */
+    if (s->M <= 32)
+        return plan_stream(&rows, out);       /* partials are laid out per 256-row tile */
+    if (s->N % 8 != 0)
+        return MM_ERR_UNSUPPORTED;
+    uint32_t sms = s->sm_count ? s->sm_count : 148;
+    uint32_t gx = rows.N / 256u;
+    uint32_t w256 = ceil_div(ceil_div(s->M, 256) * gx, sms), w128 = ceil_div(ceil_div(s->M, 128) * gx, sms);
+    uint32_t bm = (double)w256 * umma_tile_cost(256, 256) <= (double)w128 * umma_tile_cost(128, 256) * 0.999
+                      ? 256u : 128u;
+    memset(out, 0, sizeof *out);
+    out->variant = MM_F4_V_UMMA;
+    out->tile_m = bm;
+    out->tile_n = 256;
+    out->split_k = 1;
+    out->k_steps = s->K / MMB_UM_KBLOCK;
+    out->grid_x = gx;
+    out->grid_y = ceil_div(s->M, bm);
+    out->grid_z = 1;
+    out->threads = MMB_UM_THREADS;
+    uint32_t stg = 6;
+    while (stg > 2 && MMB_UM_SMEM_B(bm, 256u, stg) > MMB_SMEM_MAX) stg--;
+    out->stages = stg;
+    out->smem_bytes = MMB_UM_SMEM_B(bm, 256u, stg);
+    return out->smem_bytes > MMB_SMEM_MAX ? MM_ERR_UNSUPPORTED : MM_OK;
+}
+
 mm_status mm_f4_select(const mm_f4_shape *s, mm_f4_plan *out)
 {
     mm_status st = check_shape(s, out);

@@ -39,6 +39,31 @@ def _ptr(a):
     return a.ctypes.data_as(C.c_void_p)
 
 
+def place_weights(weights, device="cuda"):
+    """Stage several weights into ONE device block, in order, each tensor as
+    [payload | block scales] on 256-byte boundaries - the way mimfer's weight
+    arena is filled (bump allocation in load order, src/model/tensor_registry.c:532-560).
+    Tensors placed together keep a fixed address order, which the fused
+    gate/up kernel needs.  Returns the block (keep it alive)."""
+    import torch
+    offs, total = [], 0
+    for w in weights:
+        po = total
+        so = po + (w.payload.size + 255) // 256 * 256
+        total = so + (w.scales.size + 255) // 256 * 256
+        offs.append((po, so))
+    host = np.zeros(total, np.uint8)
+    for w, (po, so) in zip(weights, offs):
+        host[po:po + w.payload.size] = w.payload.reshape(-1)
+        host[so:so + w.scales.size] = w.scales.reshape(-1)
+    block = torch.from_numpy(host).to(device)
+    for w, (po, so) in zip(weights, offs):
+        w.dev_payload = block[po:po + w.payload.size].view(w.N, w.K // 2)
+        w.dev_scales = block[so:so + w.scales.size].view(w.N, w.K // 16)
+        L.check(L.lib().mm_f4_gscale_set(w.dev_scales.data_ptr(), w.gs), "mm_f4_gscale_set")
+    return block
+
+
 def pack_weight(W):
     """Quantise fp32 W [N][K] with the library's packer."""
     W = np.ascontiguousarray(W, dtype=np.float32)
@@ -85,10 +110,13 @@ def make_activations(M, K, seed=1, std=1.0):
     return f32_to_bf16(fill_normal(M, K, seed, 0.0, std))
 
 
-def select_plan(M, K, N, sm_count=148, ptr_align=256, ws_bytes=0, variant=None):
+def select_plan(M, K, N, sm_count=148, ptr_align=256, ws_bytes=0, variant=None, glu=False):
+    """glu=True: plan of the fused gate/up kernel, N = output features."""
     shape = L.F4Shape(M, K, N, sm_count, ptr_align, ws_bytes)
     plan = L.F4Plan()
-    if variant is None:
+    if glu:
+        st = L.lib().mm_f4_select_glu(C.byref(shape), C.byref(plan))
+    elif variant is None:
         st = L.lib().mm_f4_select(C.byref(shape), C.byref(plan))
     else:
         st = L.lib().mm_f4_select_variant(C.byref(shape), variant, C.byref(plan))
@@ -176,6 +204,20 @@ class Runtime:
         L.check(self.lib.mm_f4_linear(x.data_ptr(), w.dev_payload.data_ptr(), w.dev_scales.data_ptr(),
                                       w.gs, y.data_ptr(), M, w.K, w.N, None), "mm_f4_linear")
 
+    def mlp_gate_up_async(self, x, w_gate, w_up, y, M=None):
+        """y[M][inter] = silu(x . Wgate^T) * (x . Wup^T) in one kernel (mm_f4_mlp_gate_up);
+        enqueue only."""
+        M = x.shape[0] if M is None else M
+        L.check(self.lib.mm_f4_mlp_gate_up(x.data_ptr(), w_gate.dev_payload.data_ptr(),
+                                           w_gate.dev_scales.data_ptr(), w_gate.gs,
+                                           w_up.dev_payload.data_ptr(), w_up.dev_scales.data_ptr(),
+                                           w_up.gs, y.data_ptr(), M, w_gate.K, w_gate.N, None),
+                "mm_f4_mlp_gate_up")
+
+    def silu_mul_async(self, gate, up, y):
+        L.check(self.lib.mm_silu_mul(gate.data_ptr(), up.data_ptr(), y.data_ptr(), gate.numel(), None),
+                "mm_silu_mul")
+
     def linear_host(self, x_host, x_dev, w, y_dev, y_host):
         """Host buffers in, host buffers out (pinned torch tensors)."""
         M = x_host.shape[0]
@@ -214,6 +256,19 @@ class LinearEngine:
         d = self.rt.op_desc(x, w, y, M, op, note)
         self._keep.append((x, w, y))
         L.check(self.rt.lib.mm_lin_engine_add(self.h, C.byref(d)), "mm_lin_engine_add")
+
+    def add_silu_mul(self, gate, up, y):
+        """OP_SILU_MUL over gate/up [M][inter] (src/plan/plan.c:240-241)."""
+        d = L.MmOpDesc()
+        d.op, d.layer = L.OP_SILU_MUL, -1
+        d.a, d.b, d.c, d.d = gate.data_ptr(), up.data_ptr(), y.data_ptr(), None
+        d.n0, d.n1, d.n2 = gate.shape[0], gate.shape[1], 0
+        d.note = b"silu(gate)*up"
+        self._keep.append((gate, up, y))
+        L.check(self.rt.lib.mm_lin_engine_add(self.h, C.byref(d)), "mm_lin_engine_add")
+
+    def fuse_mlp(self, on=True):
+        L.check(self.rt.lib.mm_lin_engine_fuse_mlp(self.h, int(on)), "mm_lin_engine_fuse_mlp")
 
     def capture(self):
         L.check(self.rt.lib.mm_lin_engine_capture(self.h), "mm_lin_engine_capture")

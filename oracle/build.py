@@ -38,7 +38,7 @@ def build_oracle(force=False):
     src = [os.path.join(HERE, "nvfp4_oracle.c")]
     if not force and _newer(ORACLE_SO, src):
         return ORACLE_SO
-    subprocess.check_call(["gcc", *CFLAGS, *src, "-o", ORACLE_SO])
+    subprocess.check_call(["gcc", *CFLAGS, *src, "-lm", "-o", ORACLE_SO])
     return ORACLE_SO
 
 

@@ -10,6 +10,7 @@
  *                                                         exp 0 -> m/8 * 2^-6, else (1+m/8)*2^(e-7))
  *   orc_wget             include/mimfer/tensor.h:130-139 (low nibble = even column, one scale per
  *                                                         16 columns, row-major by output feature)
+ *   orc_silu_mul         src/kernels/cpu/cx.c:155-167    (silu(gate) * up on bf16, fp32 maths)
  *   orc_bf16_from_f32    include/mimfer/tensor.h:146-152 (RNE by +0x7fff + lsb)
  *   orc_f32_from_bf16    include/mimfer/tensor.h:154-159
  *   orc_gemm_f4          src/kernels/cpu/cx.c:197-216    (fp32 accumulate, k ascending,
@@ -27,6 +28,7 @@
  * keeps floating-point contraction off, so no FMA is formed, as in the
  * reference host build.
  */
+#include <math.h>
 #include <stddef.h>
 #include <stdint.h>
 #include <stdlib.h>
@@ -156,6 +158,19 @@ int orc_gemm_f4_block(const uint16_t *x, const uint8_t *payload, const uint8_t *
         free(w);
     }
     return 0;
+}
+
+/* y[i] = bf16(silu(gate[i]) * up[i]) on bf16 inputs: the reference's SILU_MUL
+ * (src/kernels/cpu/cx.c:155-167): s = g / (1 + expf(-g)) in fp32, one multiply,
+ * one rounding. */
+void orc_silu_mul(const uint16_t *gate, const uint16_t *up, uint16_t *y, size_t n)
+{
+    for (size_t i = 0; i < n; i++) {
+        float g = orc_f32_from_bf16(gate[i]);
+        float s = g / (1.0f + expf(-g));
+        float prod = s * orc_f32_from_bf16(up[i]);
+        y[i] = orc_bf16_from_f32(prod);
+    }
 }
 
 /* Whole op, reference operand order: y[M][N]. */

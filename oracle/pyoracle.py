@@ -39,6 +39,23 @@ class Oracle:
         self.lib.orc_e4m3_decode.argtypes = [C.c_ubyte]
         self.lib.orc_bf16_from_f32.restype = C.c_uint16
         self.lib.orc_bf16_from_f32.argtypes = [C.c_float]
+        self.lib.orc_silu_mul.restype = None
+        self.lib.orc_silu_mul.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]
+
+    def silu_mul(self, gate, up):
+        """bf16 bit patterns in, bf16 bit patterns out, same shape."""
+        gate = np.ascontiguousarray(gate, np.uint16)
+        up = np.ascontiguousarray(up, np.uint16)
+        y = np.empty(gate.shape, np.uint16)
+        self.lib.orc_silu_mul(_p(gate), _p(up), _p(y), gate.size)
+        return y
+
+    def mlp_gate_up(self, x, w_gate, w_up, threads=None):
+        """The MLP front half as the reference planner runs it (src/plan/plan.c:223-247):
+        two GEMMs stored as bf16, then SILU_MUL.  w_*: objects with payload, scales, gs."""
+        g = self.gemm_f4(x, w_gate.payload, w_gate.scales, w_gate.gs, threads=threads)
+        u = self.gemm_f4(x, w_up.payload, w_up.scales, w_up.gs, threads=threads)
+        return self.silu_mul(g, u)
 
     def decode_table(self):
         t = np.empty(4096, np.uint32)
@@ -80,11 +97,20 @@ class Reference:
         if not self.available:
             return
         self.lib = C.CDLL(path)
+        self.lib.ref_silu_mul.restype = C.c_int
+        self.lib.ref_silu_mul.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32]
         for name, extra in (("ref_gemm_f4", []), ("ref_gemm_f4_mt", [C.c_int])):
             fn = getattr(self.lib, name)
             fn.restype = C.c_int
             fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                            C.c_uint32, C.c_uint32, C.c_uint32] + extra
+
+    def silu_mul(self, gate, up):
+        gate = np.ascontiguousarray(gate, np.uint16)
+        up = np.ascontiguousarray(up, np.uint16)
+        y = np.empty(gate.shape, np.uint16)
+        rc = self.lib.ref_silu_mul(_p(gate), _p(up), _p(y), gate.size)
+        return rc, y
 
     def gemm_f4(self, x, payload, scales, threads=1):
         M, K = x.shape

@@ -5,6 +5,7 @@
  * read-only reference tree, into oracle/_ref/libmimfer_ref.so; no reference
  * source is copied into this repository.
  *
+ * ref_silu_mul     one call of the reference kx_op_silu_mul.
  * ref_gemm_f4      one call of the reference kx_op_gemm_f4
  *                  (src/kernels/cpu/cx.c:197-216), single thread, as shipped.
  * ref_gemm_f4_mt   the same function called once per thread on a contiguous
@@ -17,7 +18,23 @@
 #include <string.h>
 #include "mimfer_abi.h"
 
-mm_status kx_op_gemm_f4(const mm_kcall *kc);   /* the reference's symbol */
+mm_status kx_op_gemm_f4(const mm_kcall *kc);   /* the reference's symbols */
+mm_status kx_op_silu_mul(const mm_kcall *kc);
+
+/* One call of the reference kx_op_silu_mul (src/kernels/cpu/cx.c:155-167) over n
+ * bf16 elements. */
+int ref_silu_mul(const uint16_t *gate, const uint16_t *up, uint16_t *y, uint32_t n)
+{
+    mm_op_desc op;
+    mm_kcall kc;
+    memset(&op, 0, sizeof op);
+    op.op = OP_SILU_MUL;
+    op.layer = -1;
+    op.a = gate; op.b = up; op.c = y;
+    op.n0 = 1; op.n1 = n;
+    kc.op = &op; kc.e = NULL; kc.stream = NULL;
+    return (int)kx_op_silu_mul(&kc);
+}
 
 int ref_gemm_f4(const uint16_t *x, const uint8_t *payload, const uint8_t *scale,
                 uint16_t *y, uint32_t M, uint32_t K, uint32_t N)

@@ -9,6 +9,9 @@ oracle/build.py looks for it; the fixtures are committed so the tests do not.
                         high half of a byte; second scale block of a row.
   random_bytes.npz      payload and scale bytes drawn uniformly (all 256 scale
                         codes incl. 0x7f/0xff and negative scales), inputs stored.
+  silu_mul.npz          the reference kx_op_silu_mul (src/kernels/cpu/cx.c:155-167) on
+                        every bf16 bit pattern as the gate against seeded random up
+                        bits (PCG64 seed 5; only the output is stored).
   seeded_<M>x<K>x<N>.npz  weights from the library's packer + generator (seed 0,
                         N(0, 0.02)), activations seed 1 N(0, 1); stores the
                         reference output, the global scale the packer chose and
@@ -72,6 +75,12 @@ def main():
     rc, y = ref.gemm_f4(x, payload, scales)
     assert rc == 0
     np.savez_compressed(os.path.join(HERE, "random_bytes.npz"), x=x, payload=payload, scales=scales, y=y)
+
+    gate = np.arange(65536, dtype=np.uint16)
+    up = np.random.Generator(np.random.PCG64(5)).integers(0, 65536, 65536, dtype=np.uint16)
+    rc, y = ref.silu_mul(gate, up)
+    assert rc == 0
+    np.savez_compressed(os.path.join(HERE, "silu_mul.npz"), y=y)
 
     for (M, K, N) in SEEDED:
         w = mm.make_weight(N, K, seed=0, std=0.02)

@@ -26,13 +26,18 @@ def test_dispatcher_null_checks(lib):
 def test_dispatcher_routes_only_owned_opcodes(lib):
     lib.mm_log_set_level(-1)
     for op in range(19):
-        assert lib.kx_cuda_oppref(op) == (1 if op in (L.OP_GEMM_F4, L.OP_QKV, L.OP_NOP) else 0)
+        owned = (L.OP_GEMM_F4, L.OP_QKV, L.OP_LMHEAD, L.OP_SILU_MUL, L.OP_NOP)
+        assert lib.kx_cuda_oppref(op) == (1 if op in owned else 0)
     kc, _ = kcall(op=L.OP_NOP)
     assert lib.mm_kx_invoke(C.byref(kc)) == L.MM_OK
     kc, _ = kcall(op=L.OP_GEMM_BF16)
     assert lib.mm_kx_invoke(C.byref(kc)) == L.MM_ERR_UNSUPPORTED
     kc, _ = kcall(op=L.OP_QKV, d=None)
     assert lib.mm_kx_invoke(C.byref(kc)) == L.MM_ERR_UNSUPPORTED  # bf16 qkv is not served
+    kc, _ = kcall(op=L.OP_LMHEAD, d=None)
+    assert lib.mm_kx_invoke(C.byref(kc)) == L.MM_ERR_UNSUPPORTED  # nor a bf16 head
+    kc, _ = kcall(op=L.OP_SILU_MUL, a=None)
+    assert lib.mm_kx_invoke(C.byref(kc)) == L.MM_ERR_STATE
     lib.mm_log_set_level(1)
 
 
@@ -106,3 +111,51 @@ def test_tensor_parallel_entry_point_validates_arguments(lib):
     assert lib.mm_f4_linear_tp(1, 1, 1, 1.0, ptrs, 2, 512, 384, 1, 256, 256, None) == L.MM_ERR_SHAPE
     assert lib.mm_f4_linear_tp(1, 1, 1, 1.0, ptrs, 2, 512, 0, 1, 24, 256, None) == L.MM_ERR_SHAPE
     lib.mm_log_set_level(1)
+
+
+def _desc(op, a, b, c, d, n0, n1, n2):
+    desc = L.MmOpDesc()
+    desc.op, desc.layer = op, -1
+    desc.a, desc.b, desc.c, desc.d = a, b, c, d
+    desc.n0, desc.n1, desc.n2 = n0, n1, n2
+    return desc
+
+
+def test_engine_mlp_fusion_is_a_host_decision(lib):
+    """The planner's gate GEMM, up GEMM, SILU_MUL sequence (reference: src/plan/plan.c:223-247)
+    collapses to one op only when asked to and when the fused kernel can take it."""
+    X, G, U, Y = 0x10000, 0x20000, 0x30000, 0x40000
+    PG, SG, PU, SU = 0x100000, 0x200000, 0x300000, 0x400000       # both tensors gate-first
+    M, K, inter = 4, 512, 256
+
+    def build(fuse, up_scale=SU, k=K, up_first=False, other_x=False):
+        h = C.c_void_p()
+        assert lib.mm_lin_engine_create(C.byref(h), 8) == L.MM_OK
+        assert lib.mm_lin_engine_fuse_mlp(h, fuse) == L.MM_OK
+        gate = _desc(L.OP_GEMM_F4, X, PG, G, SG, M, k, inter)
+        up = _desc(L.OP_GEMM_F4, X + (0x1000 if other_x else 0), PU, U, up_scale, M, k, inter)
+        for d in ((up, gate) if up_first else (gate, up)):
+            assert lib.mm_lin_engine_add(h, C.byref(d)) == L.MM_OK
+        silu = _desc(L.OP_SILU_MUL, G, U, Y, None, M, inter, 0)
+        assert lib.mm_lin_engine_add(h, C.byref(silu)) == L.MM_OK
+        n = lib.mm_lin_engine_n_ops(h)
+        lib.mm_lin_engine_destroy(h)
+        return n
+
+    assert build(0) == 3                       # off by default
+    assert build(1) == 1
+    assert build(1, up_first=True) == 1        # emission order does not matter
+    assert build(1, up_scale=0x150000) == 3    # scale tensors in the opposite address order
+    assert build(1, k=272) == 3                # K % 256 != 0: fallback kernel, no fused form
+    assert build(1, other_x=True) == 3         # different activations
+    # a SILU_MUL with nothing to fuse is kept as its own op; bad operands are refused
+    h = C.c_void_p()
+    assert lib.mm_lin_engine_create(C.byref(h), 4) == L.MM_OK
+    lib.mm_lin_engine_fuse_mlp(h, 1)
+    assert lib.mm_lin_engine_add(h, C.byref(_desc(L.OP_SILU_MUL, G, U, Y, None, M, inter, 0))) == L.MM_OK
+    lib.mm_log_set_level(-1)
+    assert lib.mm_lin_engine_add(h, C.byref(_desc(L.OP_SILU_MUL, G, None, Y, None, M, inter, 0))) == L.MM_ERR_STATE
+    assert lib.mm_lin_engine_add(h, C.byref(_desc(L.OP_SILU_MUL, G, U, Y, None, 0, inter, 0))) == L.MM_ERR_SHAPE
+    lib.mm_log_set_level(1)
+    assert lib.mm_lin_engine_n_ops(h) == 1
+    lib.mm_lin_engine_destroy(h)

@@ -38,6 +38,18 @@ def test_decode_products_match_reference_fixture(oracle):
     assert np.array_equal(table.view(np.uint32) & 0xFFFF, np.zeros(4096, np.uint32))
 
 
+def test_silu_mul_fixture(oracle):
+    """SILU_MUL restatement against the reference's own kernel on every bf16 gate value."""
+    gold = np.load(os.path.join(GOLDEN, "silu_mul.npz"))["y"]
+    gate = np.arange(65536, dtype=np.uint16)
+    up = np.random.Generator(np.random.PCG64(5)).integers(0, 65536, 65536, dtype=np.uint16)
+    got = oracle.silu_mul(gate, up)
+    nan = np.isnan(bf16_bits_to_f32(gold))
+    assert np.array_equal(nan, np.isnan(bf16_bits_to_f32(got)))
+    assert np.array_equal(got[~nan], gold[~nan])
+    assert nan.sum() < 2000                                    # NaN/Inf inputs only
+
+
 def test_random_bytes_fixture(oracle):
     g = np.load(os.path.join(GOLDEN, "random_bytes.npz"))
     y = oracle.gemm_f4(g["x"], g["payload"], g["scales"], 1.0)
@@ -89,6 +101,15 @@ def test_global_scale_is_one_multiply_before_rounding(oracle, lib):
     yg = oracle.gemm_f4(x, w.payload, w.scales, float(gs))
     want = mm.linear.f32_to_bf16(acc * gs)
     assert np.array_equal(yg, want)
+
+
+def test_live_reference_silu_mul(oracle, reference):
+    if not reference.available:
+        pytest.skip("compiled reference not present")
+    g = mm.make_activations(1, 5000, seed=12, std=4.0)[0]
+    u = mm.make_activations(1, 5000, seed=13)[0]
+    rc, y = reference.silu_mul(g, u)
+    assert rc == 0 and np.array_equal(y, oracle.silu_mul(g, u))
 
 
 def test_live_reference_when_present(oracle, reference, lib):

@@ -74,3 +74,22 @@ def test_streamt_plan_mirrors_stream_decomposition(lib):
             assert b.ws_needed == 16384 + b.split_k * b.tile_m * 5120 * 4
     with pytest.raises(mm.MimferError):
         mm.select_plan(64, 512, 64, variant=V_STREAMT)
+
+
+def test_gated_pair_plans(lib):
+    """mm_f4_select_glu: N counts output features; a CTA tile is 128 rows of each projection."""
+    p = mm.select_plan(16, 5120, 17408, ws_bytes=WS, glu=True)
+    assert p.variant == V_STREAM and p.grid_x == 17408 // 128 and p.split_k == 1
+    p = mm.select_plan(4, 5120, 1000, ws_bytes=WS, glu=True)          # 8 tiles: K is split
+    assert p.grid_x == 8 and p.split_k > 1
+    assert p.ws_needed == 16384 + p.split_k * p.tile_m * 8 * 256 * 4  # partials per padded tile row
+    for M in (512, 8192):
+        p = mm.select_plan(M, 5120, 17408, glu=True)
+        assert p.variant == V_UMMA and p.tile_n == 256 and p.grid_x == 136
+        assert p.tile_m in (128, 256) and p.grid_y == -(-M // p.tile_m)
+        assert p.smem_bytes <= SMEM_MAX
+    for bad in ((4, 272, 128, 256), (64, 512, 100, 256), (4, 512, 128, 8)):
+        M, K, N, align = bad
+        with pytest.raises(mm.MimferError) as e:
+            mm.select_plan(M, K, N, ptr_align=align, glu=True)
+        assert e.value.status == 7                                    # MM_ERR_UNSUPPORTED
