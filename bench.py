@@ -184,9 +184,10 @@ class Bench:
             raise RuntimeError(f"device status 0x{status:x} after timed region")
         return ms / steps
 
-    def engine(self, ops):
+    def engine(self, ops, overlap=False):
         """ops: list of (x, w_dev, y). Captured into one graph."""
         eng = self.mm.LinearEngine(self.rt, max_ops=len(ops) + 1)
+        eng.overlap(overlap)
         for x, w, y in ops:
             eng.add(x, w, y)
         eng.launch()                  # direct dispatch once: errors surface per op
@@ -207,11 +208,15 @@ class Bench:
                 ops.append((self.acts(M, K), self.dev_weight(hw), self.empty(M, N)))
                 wb += wbytes(K, N)
                 ab += alg_bytes(M, K, N)
-        eng = self.engine(ops)
+        serial = self.engine(ops)
+        ms_serial = self.timed(serial.launch, steps, warmup)
+        serial.close()
+        eng = self.engine(ops, overlap=True)      # independent ops run ahead of their predecessors
         ms = self.timed(eng.launch, steps, warmup)
         res = {"ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "alg_gbs": ab / ms / 1e6,
                "ops": len(ops), "weight_bytes": wb, "alg_bytes_per_launch": ab / len(ops),
-               "avg_launch_us": ms * 1e3 / len(ops)}
+               "avg_launch_us": ms * 1e3 / len(ops), "independent_ops": eng.n_independent(),
+               "serial_order": {"ms_per_step": ms_serial, "weight_gbs": wb / ms_serial / 1e6}}
         return res, ops, eng
 
     def decode_e2e(self, ops, eng, steps, warmup):
@@ -275,10 +280,15 @@ class Bench:
                             self.dev_weight(base[n]), self.empty(M, N) if layer == 0 else ops[names.index(n)][2]))
                 wb += wbytes(K, N)
         eng = self.engine(ops)
+        ms_serial = self.timed(eng.launch, max(2, steps // 2), 3)
+        eng.close()
+        eng = self.engine(ops, overlap=True)
         ms = self.timed(eng.launch, max(2, steps // 2), 3)
+        ind = eng.n_independent()
         eng.close()
         return {"layers": layers, "M": M, "ops": len(ops), "weight_bytes": wb,
-                "sum_linear_ms_per_step": ms, "weight_gbs": wb / ms / 1e6}
+                "sum_linear_ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "independent_ops": ind,
+                "serial_order": {"sum_linear_ms_per_step": ms_serial, "weight_gbs": wb / ms_serial / 1e6}}
 
     def decode_step_planner(self, steps, warmup, layers=64, M=16):
         """The 64-layer decode step with the op sequence of the reference planner
@@ -303,9 +313,11 @@ class Bench:
             layer_w.append(ws)
             wb += sum(wbytes(*SHAPES[n]) for n in lin) + 2 * wbytes(K, inter)
         res = {"layers": layers, "M": M, "weight_bytes": wb}
-        for fuse in (False, True):
+        for fuse, overlap, tag in ((False, False, "as_emitted"), (True, False, "fused_mlp"),
+                                   (True, True, "fused_mlp_overlap")):
             eng = self.mm.LinearEngine(self.rt, max_ops=8 * layers)
             eng.fuse_mlp(fuse)
+            eng.overlap(overlap)
             for ws in layer_w:
                 for n in ("q", "k", "v"):
                     eng.add(x, ws[n], ys[n])
@@ -320,8 +332,7 @@ class Bench:
             eng.capture()
             ms = self.timed(eng.launch, max(2, steps // 2), 3)
             eng.close()
-            res["fused_mlp" if fuse else "as_emitted"] = {"ops": n_ops, "ms_per_step": ms,
-                                                          "weight_gbs": wb / ms / 1e6}
+            res[tag] = {"ops": n_ops, "ms_per_step": ms, "weight_gbs": wb / ms / 1e6}
         del layer_w, keep
         self.torch.cuda.empty_cache()
         return res
@@ -566,7 +577,8 @@ def run_b200(args):
             b.torch.cuda.empty_cache()
             # same weights with q, k and v as one fused op (the reference planner's OP_QKV layout)
             fused = b.decode_step_64(steps, warmup, names=("qkv", "o", "gate_up", "down"))
-            line["decode_step"]["fused_qkv"] = {k: fused[k] for k in ("ops", "sum_linear_ms_per_step", "weight_gbs")}
+            line["decode_step"]["fused_qkv"] = {k: fused[k] for k in ("ops", "sum_linear_ms_per_step", "weight_gbs",
+                                                                      "independent_ops", "serial_order")}
             b.torch.cuda.empty_cache()
             line["mlp_front"] = b.mlp_front(steps, warmup)
             line["decode_step"]["planner_sequence"] = b.decode_step_planner(steps, warmup)

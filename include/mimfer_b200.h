@@ -343,6 +343,18 @@ uint32_t  mm_lin_engine_n_ops(const mm_lin_engine *e);
  * count drops by two and the gate/up buffers are no longer written.  Off by
  * default. */
 mm_status mm_lin_engine_fuse_mlp(mm_lin_engine *e, int on);
+/* on != 0: dependency-aware launch order.  The engine compares the memory every
+ * op reads and writes (activations, outputs, split-K scratch) with the ops still
+ * in flight before it; an op that shares nothing with them is launched so that
+ * it starts while they drain (programmatic dependent launch without the leading
+ * wait) and still completes after them; every other op waits for its
+ * predecessor as before.  Results are identical; only ops served by the decode
+ * kernel run ahead.  Needs a workspace of at least 16 MiB to let split-K ops
+ * overlap (each of four regions serves one op in flight).  Off by default.
+ * mm_lin_engine_n_independent: how many ops of the last dispatch or capture ran
+ * ahead. */
+mm_status mm_lin_engine_overlap(mm_lin_engine *e, int on);
+uint32_t  mm_lin_engine_n_independent(const mm_lin_engine *e);
 /* Capture all ops into one CUDA graph (reference pattern:
  * src/plan/plan.c:479-507). */
 mm_status mm_lin_engine_capture(mm_lin_engine *e);

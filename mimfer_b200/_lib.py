@@ -116,6 +116,8 @@ SIGNATURES = {
     "kx_op_lmhead": (C.c_int, [C.POINTER(MmKcall)]),
     "kx_op_silu_mul": (C.c_int, [C.POINTER(MmKcall)]),
     "mm_lin_engine_fuse_mlp": (C.c_int, [_vp, C.c_int]),
+    "mm_lin_engine_overlap": (C.c_int, [_vp, C.c_int]),
+    "mm_lin_engine_n_independent": (C.c_uint32, [_vp]),
     "mm_f4_select_variant": (C.c_int, [C.POINTER(F4Shape), C.c_int, C.POINTER(F4Plan)]),
     "mm_f4_force_variant": (None, [C.c_int]),
     "mm_f4_linear": (C.c_int, [_vp, _vp, _vp, _f, _vp, _u32, _u32, _u32, _vp]),

@@ -44,6 +44,17 @@ int mmb_gate_up_fusable(const void *x, const void *gate_payload, const void *gat
                         const void *up_payload, const void *up_scale, const void *y,
                         uint32_t M, uint32_t K, uint32_t inter);
 
+/* Engine -> launcher, for the next op only: how to order the launch against its
+ * predecessor (MMB_PDL_* of kernels/launch.h, -1 = the launcher's default) and
+ * which workspace region its split-K scratch lives in. */
+void mmb_next_op_context(int pdl_mode, int ws_region);
+/* Regions the workspace is cut into, so that ops in flight together never share
+ * scratch (1 when the workspace is too small to divide). */
+int mmb_ws_regions(void);
+/* The plan the launcher would pick for this op (glu: the op is a fused gate/up
+ * pair, n2 = output features). */
+mm_status mmb_plan_for_op(const mm_op_desc *op, int glu, mm_f4_plan *out);
+
 static inline size_t mmb_align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 #ifdef __cplusplus

@@ -36,8 +36,42 @@ static struct {
     size_t     ws_bytes;
     int        forced_variant;
     int        pdl;
+    int        next_pdl;         /* per-op override from the engine, -1 = none */
+    int        next_region;
     unsigned long long launches;
-} G = { .forced_variant = -1, .pdl = 1 };
+} G = { .forced_variant = -1, .pdl = 1, .next_pdl = -1 };
+
+/* The workspace is cut into WS_REGIONS equal regions, each with its own arrival
+ * counters, when every region still holds WS_REGION_MIN bytes; an op uses one
+ * region (0 unless the engine says otherwise). */
+#define WS_REGIONS    4
+#define WS_REGION_MIN ((size_t)4 << 20)
+
+int mmb_ws_regions(void)
+{
+    return G.ws && G.ws_bytes / WS_REGIONS >= WS_REGION_MIN ? WS_REGIONS : 1;
+}
+
+static size_t ws_region_bytes(void)
+{
+    return G.ws ? (G.ws_bytes / (size_t)mmb_ws_regions()) & ~(size_t)255 : 0;
+}
+
+void mmb_next_op_context(int pdl_mode, int ws_region)
+{
+    G.next_pdl = pdl_mode;
+    G.next_region = ws_region >= 0 && ws_region < mmb_ws_regions() ? ws_region : 0;
+}
+
+/* Consume the per-op context: launch mode and workspace base of this op. */
+static void take_op_context(int *pdl_out, void **ws_out)
+{
+    int mode = G.next_pdl >= 0 ? G.next_pdl : MMB_PDL_TRIGGER_FIRST;
+    *pdl_out = G.pdl ? mode : MMB_PDL_OFF;
+    *ws_out = G.ws ? (unsigned char *)G.ws + (size_t)G.next_region * ws_region_bytes() : NULL;
+    G.next_pdl = -1;
+    G.next_region = 0;
+}
 
 /* global-scale registry: open addressing on the scale base pointer */
 #define GS_SLOTS 4096u
@@ -148,9 +182,13 @@ mm_status mm_f4_workspace_set(void *dev_ptr, size_t bytes)
         return dev_ptr ? MM_ERR_RANGE : MM_OK;
     }
     MM_REQUIRE(((uintptr_t)dev_ptr & 255u) == 0, MM_ERR_SHAPE);
-    CK(cudaMemsetAsync(dev_ptr, 0, MMB_WS_COUNTER_B, (cudaStream_t)mm_cuda_stream_raw(MM_ST_COMPUTE)));
     G.ws = dev_ptr;
     G.ws_bytes = bytes;
+    /* the arrival counters at the head of every region start at zero (kernels
+     * leave them at zero again) */
+    for (int r = 0; r < mmb_ws_regions(); r++)
+        CK(cudaMemsetAsync((unsigned char *)dev_ptr + (size_t)r * ws_region_bytes(), 0, MMB_WS_COUNTER_B,
+                           (cudaStream_t)mm_cuda_stream_raw(MM_ST_COMPUTE)));
     return MM_OK;
 }
 
@@ -208,6 +246,20 @@ static uint32_t min_align(const void *a, const void *b, const void *c, const voi
     return (uint32_t)(v & (~v + 1u));
 }
 
+/* Plan of a linear op as the launcher runs it (shared with mmb_plan_for_op). */
+static mm_status plan_linear(const void *x, const void *payload, const void *scale, const void *y,
+                             uint32_t n_dst, uint32_t ldy, uint32_t col0, uint32_t M, uint32_t K,
+                             uint32_t N, mm_f4_plan *plan)
+{
+    mm_f4_shape sh = { M, K, N, (uint32_t)G.sm_count, min_align(x, payload, scale, y), ws_region_bytes() };
+    if (n_dst && (col0 % 8u != 0 || ldy % 8u != 0))
+        sh.ptr_align = 8;                  /* 16-byte output vectors need aligned slices */
+    if (sh.ptr_align < 16 && !n_dst)
+        return MM_ERR_SHAPE;               /* arena slots are >= 16-byte aligned */
+    return G.forced_variant >= 0 ? mm_f4_select_variant(&sh, G.forced_variant, plan)
+                                 : mm_f4_select(&sh, plan);
+}
+
 static mm_status linear_impl(const void *x, const void *payload, const void *scale, float gs,
                              void *y, void *const *y_dst, uint32_t n_dst, uint32_t ldy,
                              uint32_t col0, uint32_t M, uint32_t K, uint32_t N, void *stream)
@@ -223,18 +275,11 @@ static mm_status linear_impl(const void *x, const void *payload, const void *sca
     memset(&a, 0, sizeof a);
     a.x = x; a.payload = payload; a.scale = scale; a.y = y;
     a.gs = gs; a.M = M; a.K = K; a.N = N;
-    a.ws = G.ws;
-    a.pdl = G.pdl;
+    take_op_context(&a.pdl, &a.ws);
     for (uint32_t d = 0; d < n_dst; d++) a.y_dst[d] = y_dst[d];
     a.n_dst = n_dst; a.ldy = ldy; a.col0 = col0;
 
-    mm_f4_shape sh = { M, K, N, (uint32_t)G.sm_count, min_align(x, payload, scale, y), G.ws_bytes };
-    if (n_dst && (col0 % 8u != 0 || ldy % 8u != 0))
-        sh.ptr_align = 8;                  /* 16-byte output vectors need aligned slices */
-    if (sh.ptr_align < 16 && !n_dst)
-        return MM_ERR_SHAPE;               /* arena slots are >= 16-byte aligned */
-    mm_status st = G.forced_variant >= 0 ? mm_f4_select_variant(&sh, G.forced_variant, &a.plan)
-                                         : mm_f4_select(&sh, &a.plan);
+    mm_status st = plan_linear(x, payload, scale, y, n_dst, ldy, col0, M, K, N, &a.plan);
     if (st != MM_OK)
         return st;
 
@@ -344,9 +389,8 @@ mm_status mm_f4_mlp_gate_up(const void *x, const void *gate_payload, const void 
     a.gs = gs_gate; a.gs_up = gs_up;
     a.glu = 1; a.gate_plane = gate_first ? 0 : 1;
     a.M = M; a.K = K; a.N = inter;
-    a.ws = G.ws;
-    a.pdl = G.pdl;
-    mm_f4_shape sh = { M, K, inter, (uint32_t)G.sm_count, min_align(x, pay0, sc0, y), G.ws_bytes };
+    take_op_context(&a.pdl, &a.ws);
+    mm_f4_shape sh = { M, K, inter, (uint32_t)G.sm_count, min_align(x, pay0, sc0, y), ws_region_bytes() };
     mm_status st = mm_f4_select_glu(&sh, &a.plan);
     if (st != MM_OK)
         return st;
@@ -460,6 +504,19 @@ mm_status kx_op_qkv(const mm_kcall *kc)
     if (!kc->op->d)
         return MM_ERR_UNSUPPORTED;     /* bf16 fused qkv: not this library's op */
     return kx_op_gemm_f4(kc);
+}
+
+mm_status mmb_plan_for_op(const mm_op_desc *op, int glu, mm_f4_plan *out)
+{
+    MM_REQUIRE(op && out, MM_ERR_STATE);
+    MM_CHECK(ensure_ready());
+    if (glu) {
+        /* the lower-addressed projection decides the alignment; both are placed alike */
+        mm_f4_shape sh = { op->n0, op->n1, op->n2, (uint32_t)G.sm_count,
+                           min_align(op->a, op->b, op->d, op->c), ws_region_bytes() };
+        return mm_f4_select_glu(&sh, out);
+    }
+    return plan_linear(op->a, op->b, op->d, op->c, 0, 0, 0, op->n0, op->n1, op->n2, out);
 }
 
 mm_status mmb_op_mlp_gate_up(const mm_op_desc *op, const void *up_payload, const void *up_scale)

@@ -11,6 +11,7 @@
  * appended unchanged.
  */
 #include "../core/core.h"
+#include "../kernels/launch.h"
 #include <stdlib.h>
 #include <string.h>
 
@@ -28,6 +29,8 @@ struct mm_lin_engine {
     mm_graph    *graph;
     int          captured;
     int          fuse_mlp;
+    int          overlap;
+    uint32_t     n_independent;     /* ops of the last walk launched without a leading wait */
 };
 
 mm_status mm_lin_engine_create(mm_lin_engine **out, uint32_t max_ops)
@@ -119,12 +122,93 @@ static size_t op_out_bytes(const mm_op_desc *op)
 
 uint32_t mm_lin_engine_n_ops(const mm_lin_engine *e) { return e ? e->n_ops : 0; }
 
+mm_status mm_lin_engine_overlap(mm_lin_engine *e, int on)
+{
+    MM_REQUIRE(e, MM_ERR_STATE);
+    MM_REQUIRE(!e->captured, MM_ERR_BUSY);
+    e->overlap = on ? 1 : 0;
+    return MM_OK;
+}
+
+uint32_t mm_lin_engine_n_independent(const mm_lin_engine *e) { return e ? e->n_independent : 0; }
+
+/* ---- which ops may run ahead of their predecessors --------------------------
+ * The reference engine serialises its ops on one stream (src/plan/plan.c:119-130)
+ * although many neighbours do not depend on each other: q, k and v read the same
+ * activations, as do gate and up.  With overlap on, an op that neither reads nor
+ * writes anything a kernel still in flight touches is launched in the
+ * INDEPENDENT form of kernels/launch.h: it starts streaming weights and
+ * activations while its predecessors drain, fills the SMs they leave idle, and
+ * still completes after them.  "In flight" = every op since, and including, the
+ * last op that waited for its predecessor; split-K scratch counts as touched
+ * memory, so ops in flight together use different workspace regions. */
+typedef struct span { uintptr_t lo, hi; } span;
+
+static span mk_span(const void *p, size_t bytes)
+{
+    span s = { (uintptr_t)p, (uintptr_t)p + bytes };
+    return s;
+}
+static int spans_meet(span a, span b) { return a.lo < b.hi && b.lo < a.hi; }
+
+/* reads[0..1] and the write of an op (weights are never written, so they do not count) */
+static void op_spans(const mm_op_desc *op, span reads[2], span *write)
+{
+    size_t in = op_in_bytes(op);
+    reads[0] = mk_span(op->a, in);
+    reads[1] = op->op == OP_SILU_MUL ? mk_span(op->b, in) : mk_span(op->a, 0);
+    *write = mk_span(op->c, op_out_bytes(op));
+}
+
+static int ops_independent(const mm_op_desc *p, const mm_op_desc *q)
+{
+    span pr[2], qr[2], pw, qw;
+    op_spans(p, pr, &pw);
+    op_spans(q, qr, &qw);
+    if (spans_meet(pw, qw))
+        return 0;
+    for (int i = 0; i < 2; i++)
+        if (spans_meet(pw, qr[i]) || spans_meet(qw, pr[i]))
+            return 0;
+    return 1;
+}
+
 static mm_status run_ops(mm_lin_engine *e)
 {
     mm_kcall kc;
     kc.e = (const mm_engine *)e;      /* the dispatcher only tests it for NULL */
     kc.stream = NULL;
+    uint32_t first_in_flight = 0;     /* the last op that waited for its predecessor */
+    unsigned regions_in_flight = 0;   /* workspace regions used since then */
+    int next_region = 0;
+    const int n_regions = e->overlap ? mmb_ws_regions() : 1;
+    e->n_independent = 0;
     for (uint32_t i = 0; i < e->n_ops; i++) {
+        const mm_op_desc *op = &e->ops[i];
+        if (e->overlap && op->op != OP_NOP) {
+            int independent = 0, region = 0, split = 0;
+            if (op->op != OP_SILU_MUL) {
+                mm_f4_plan plan;
+                MM_CHECK(mmb_plan_for_op(op, op->op == MMB_OP_GATE_UP, &plan));
+                split = plan.split_k > 1;
+                region = split ? next_region : 0;
+                independent = i > 0 && plan.variant == MM_F4_V_STREAM &&
+                              !(split && (regions_in_flight & (1u << region)));
+                for (uint32_t j = first_in_flight; independent && j < i; j++)
+                    if (e->ops[j].op != OP_NOP && !ops_independent(op, &e->ops[j]))
+                        independent = 0;
+            }
+            if (!independent) {
+                first_in_flight = i;
+                regions_in_flight = 0;
+            }
+            if (split) {
+                regions_in_flight |= 1u << region;
+                next_region = (region + 1) % n_regions;
+            }
+            e->n_independent += (uint32_t)independent;
+            mmb_next_op_context(independent ? MMB_PDL_INDEPENDENT : MMB_PDL_WAIT_FIRST, region);
+        }
         kc.op = &e->ops[i];
         mm_status st = e->ops[i].op == MMB_OP_GATE_UP
                            ? mmb_op_mlp_gate_up(&e->ops[i], e->up[i].payload, e->up[i].scale)

@@ -56,6 +56,25 @@ extern "C" {
 
 #define MMB_MAX_PEERS      8u
 
+/* Programmatic dependent launch, per op.  C(k) = completion of kernel k of the
+ * stream, T(k) = the moment all its CTAs have triggered their dependents.
+ *   OFF           plain launch: starts after C(prev).
+ *   TRIGGER_FIRST every CTA triggers in its prologue, then waits for C(prev)
+ *                 before the first activation load.  Safe on its own; gives no
+ *                 ordering guarantee to an INDEPENDENT successor.
+ *   WAIT_FIRST    wait for C(prev), then trigger: T(k) >= C(k-1).
+ *   INDEPENDENT   the op touches nothing that any kernel since (and including)
+ *                 the last WAIT_FIRST/OFF kernel reads or writes, workspace
+ *                 included: trigger at once, never wait before loading, wait for
+ *                 C(prev) just before the CTA exits, so completions stay ordered
+ *                 (C(k) >= C(k-1)) and a later waiting kernel still sees
+ *                 everything before it.  Only the decode kernel has this form.
+ * INDEPENDENT must only follow WAIT_FIRST, OFF or INDEPENDENT kernels. */
+#define MMB_PDL_OFF           0
+#define MMB_PDL_TRIGGER_FIRST 1
+#define MMB_PDL_WAIT_FIRST    2
+#define MMB_PDL_INDEPENDENT   3
+
 /* Device status word bits. */
 #define MMB_DEV_TIMEOUT    1u
 #define MMB_DEV_BADARG     2u
@@ -82,7 +101,7 @@ typedef struct mmb_args {
     float       gs_up;
     void       *ws;       /* workspace base or NULL */
     mm_f4_plan  plan;
-    int         pdl;      /* launch with programmatic stream serialization */
+    int         pdl;      /* MMB_PDL_*: how the launch is ordered against its predecessor */
     /* 128-byte TMA descriptors, filled by the launcher (opaque here) */
     unsigned char tm_payload[128] __attribute__((aligned(64)));
     unsigned char tm_scale[128] __attribute__((aligned(64)));

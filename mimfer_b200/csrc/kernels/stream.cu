@@ -53,6 +53,7 @@ struct StreamParams {
     float           gs;
     uint32_t        M, K, N;
     uint32_t        k_steps, split_k, stages;
+    uint32_t        pdl;         /* MMB_PDL_* */
     float           gs_up;       /* gated pair: scale of the up projection        */
     uint32_t        gate_plane;  /* gated pair: which half of the CTA's rows is the gate */
 };
@@ -295,16 +296,24 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
         sts32(lut_hf + tid * 4u, scale_lut_entry_f16(tid));
     }
     __syncthreads();
-    grid_dep_launch();
+    if (p.pdl == MMB_PDL_TRIGGER_FIRST)
+        grid_dep_launch();
 
     if (warp == MMB_ST_CONSUMERS) {
         /* ------------------------------ TMA issue ------------------------- *
          * The weights do not depend on the previous kernel in the stream, the
          * activations may: the first ring of weight boxes went out in the
          * prologue, before the grid-dependency wait, the activation boxes
-         * follow it. */
+         * follow it.  An op known to be independent of everything in flight
+         * skips that wait and makes up for it before the CTA exits (launch.h). */
         if (lane == 0) {
-            grid_dep_wait();
+            if (p.pdl == MMB_PDL_INDEPENDENT) {
+                grid_dep_launch();
+            } else {
+                grid_dep_wait();
+                if (p.pdl == MMB_PDL_WAIT_FIRST)
+                    grid_dep_launch();
+            }
             for (uint32_t it = 0; it < first; it++)
                 tma_load_2d(base + it * STAGE_B + MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B, &tm_x,
                             static_cast<int>((ks_begin + it) * MMB_ST_KSTEP), 0, bar_raw + 8u * it);
@@ -319,6 +328,8 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
                 tma_load_2d(stage + MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B, &tm_x,
                             static_cast<int>(ks * MMB_ST_KSTEP), 0, bar_raw + 8u * s);
             }
+            if (p.pdl == MMB_PDL_INDEPENDENT)
+                grid_dep_wait();                   /* this kernel completes after its predecessor */
         }
         return;
     }
@@ -552,6 +563,7 @@ static int launch_mt(const mmb_args *a, unsigned *status, cudaStream_t st)
     p.stages = a->plan.stages;
     p.gs_up = a->gs_up;
     p.gate_plane = a->gate_plane ? 1u : 0u;
+    p.pdl = static_cast<uint32_t>(a->pdl);
     TmaDesc tp, ts, tx;
     memcpy(tp.bytes, a->tm_payload, 128);
     memcpy(ts.bytes, a->tm_scale, 128);

@@ -480,7 +480,8 @@ static int launch_npad(const mmb_args *a, unsigned *status, cudaStream_t st)
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = a->pdl ? 1 : 0;
+    /* this kernel only has the trigger-first form; any other mode runs as a plain launch */
+    attr[0].val.programmaticStreamSerializationAllowed = a->pdl == MMB_PDL_TRIGGER_FIRST ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return static_cast<int>(cudaLaunchKernelEx(&cfg, f4_streamt_kernel<NPAD>, tp, ts, tx, p));

@@ -40,6 +40,7 @@ struct UmmaParams {
     uint32_t  M, K, N;
     uint32_t  k_blocks;      /* K / 64 */
     uint32_t  stages;
+    uint32_t  pdl;           /* MMB_PDL_* (INDEPENDENT is served as WAIT_FIRST)  */
     float     gs_up;         /* gated pair: scale of the up projection          */
     uint32_t  gate_plane;    /* gated pair: which half of the weight tile is the gate */
 };
@@ -137,7 +138,8 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = lds32(tmem_slot);
-    grid_dep_launch();
+    if (p.pdl == MMB_PDL_TRIGGER_FIRST)
+        grid_dep_launch();
 
     if (warp == 0) {
         /* ------------------------------ TMA producer ---------------------- *
@@ -146,6 +148,8 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
          * prologue, the first activation box follows the grid-dependency wait. */
         if (lane == 0) {
             grid_dep_wait();
+            if (p.pdl >= MMB_PDL_WAIT_FIRST)
+                grid_dep_launch();
             uint32_t s = 0, round = 0;                 /* A/B stage index and its use count */
             for (uint32_t kb = 0; kb < KB; kb++, s = (s + 1u == ST) ? 0u : s + 1u, round += (s == 0u)) {
                 const uint32_t ps = kb % PAY_SLOTS;
@@ -373,6 +377,7 @@ static int launch_tile(const mmb_args *a, unsigned *status, cudaStream_t st)
     p.stages = a->plan.stages;
     p.gs_up = a->gs_up;
     p.gate_plane = a->gate_plane ? 1u : 0u;
+    p.pdl = static_cast<uint32_t>(a->pdl);
     TmaDesc tx, tp, ts;
     memcpy(tx.bytes, a->tm_x, 128);
     memcpy(tp.bytes, a->tm_payload, 128);

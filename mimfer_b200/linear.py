@@ -267,6 +267,13 @@ class LinearEngine:
         self._keep.append((gate, up, y))
         L.check(self.rt.lib.mm_lin_engine_add(self.h, C.byref(d)), "mm_lin_engine_add")
 
+    def overlap(self, on=True):
+        """Dependency-aware launch order (mm_lin_engine_overlap)."""
+        L.check(self.rt.lib.mm_lin_engine_overlap(self.h, int(on)), "mm_lin_engine_overlap")
+
+    def n_independent(self):
+        return self.rt.lib.mm_lin_engine_n_independent(self.h)
+
     def fuse_mlp(self, on=True):
         L.check(self.rt.lib.mm_lin_engine_fuse_mlp(self.h, int(on)), "mm_lin_engine_fuse_mlp")
 
