@@ -234,7 +234,23 @@ class Bench:
         t0 = time.perf_counter()
         for _ in range(steps):
             eng.launch_host(x_host, y_host)
+        sec_unbound = (time.perf_counter() - t0) / steps
+        # the same step with the copies captured into the graph (bound pinned buffers)
+        bound = self.mm.LinearEngine(self.rt, max_ops=len(ops) + 1)
+        bound.overlap(True)
+        for x, w, y in ops:
+            bound.add(x, w, y)
+        bound.upload_group((len(ops) + 1) // 2)
+        bound.bind_host(x_host, y_host)
+        bound.capture()
+        for _ in range(max(warmup, 3)):
+            bound.step_bound()
+        self.barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            bound.step_bound()
         sec = (time.perf_counter() - t0) / steps
+        bound.close()
         # per-op form (mm_f4_linear_host: copy, op, copy, sync for every op), for the record
         per_op = [(xh, x, w, y, yh) for (x, w, y), xh, yh in zip(ops, x_host, y_host)]
         for xh, xd, w, yd, yh in per_op:
@@ -247,8 +263,11 @@ class Bench:
         wb = sum(wbytes(w.K, w.N) for _, w, _ in ops)
         return {"value": wb / sec / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": sec * 1e3,
-                "call": "mm_lin_engine_launch_host: H2D of all activations, one graph replay, "
-                        "D2H of all outputs, one sync",
+                "call": "mm_lin_engine_step_bound: one graph replay that uploads every op's activations "
+                        "from pinned host memory on the transfer stream, runs the ten ops and downloads "
+                        "every output to pinned host memory; one sync",
+                "copies_outside_graph": {"value": wb / sec_unbound / 1e9, "ms_per_step": sec_unbound * 1e3,
+                                         "call": "mm_lin_engine_launch_host"},
                 "per_op_sync": {"value": wb / sec_op / 1e9, "ms_per_step": sec_op * 1e3,
                                 "call": "mm_f4_linear_host per op"},
                 "timing": "host wall clock around synchronous calls"}
@@ -378,6 +397,49 @@ class Bench:
             self.torch.cuda.empty_cache()
         return out
 
+    def decode_parts(self, secs=1.5):
+        """Where a decode launch spends its time: gate+up and down at M = 1 and 16,
+        as shipped and in the kernel's measurement modes (mm_f4_tune key 4: 1 = the
+        weight stream alone, 2 = the arithmetic alone, 4 = split-K without the
+        exchange), each as a short burst (20 graph replays after a pause) and
+        sustained for `secs` seconds with SM clock and board power sampled."""
+        rows = []
+        for name, copies in (("gate_up", 5), ("down", 8)):
+            K, N = SHAPES[name]
+            hw = self.weight(name)
+            ws = [self.dev_weight(hw) for _ in range(copies)]
+            for M in (1, 16):
+                x = self.acts(M, K)
+                ys = [self.empty(M, N) for _ in ws]
+                for mode, tag in ((0, "as shipped"), (1, "weight stream alone"), (2, "arithmetic alone"),
+                                  (4, "no split-K exchange")):
+                    if mode == 4 and name == "gate_up":
+                        continue                      # gate+up runs unsplit
+                    self.rt.lib.mm_f4_tune(4, mode)
+                    eng = self.engine([(x, w, y) for w, y in zip(ws, ys)], overlap=True)
+                    time.sleep(0.3)
+                    burst = self.timed(eng.launch, 20, 3)
+                    with Clocks(self.local) as clk:
+                        t0, n = time.time(), 0
+                        self.rt.sync()
+                        self.rt.time_begin()
+                        while time.time() - t0 < secs:
+                            for _ in range(50):
+                                eng.launch()
+                            self.rt.sync()
+                            n += 50
+                        sustained = self.rt.time_end() / n
+                    eng.close()
+                    self.rt.lib.mm_f4_tune(4, 0)
+                    c = clk.summary()
+                    rows.append({"op": name, "M": M, "mode": tag, "burst_us": round(burst * 1e3 / copies, 2),
+                                 "sustained_us": round(sustained * 1e3 / copies, 2), "sm_mhz": c["sm_mhz"],
+                                 "power_w_max": c["power_w_max"], "reasons": c["reasons"],
+                                 "weight_gbs_burst": round(wbytes(K, N) / (burst / copies) / 1e6)})
+            del ws
+            self.torch.cuda.empty_cache()
+        return {"rows": rows}
+
     def _shard_rows(self, name):
         per = SHAPES[name][1] // self.world
         return (self.rank * per, (self.rank + 1) * per)
@@ -435,7 +497,7 @@ class Bench:
 
     def tp_series(self, steps, warmup):
         """config 5: gate+up and LM head, sharded along N over all ranks, M=32 and M=8192."""
-        from mimfer_b200.tp import TpLinear
+        from mimfer_b200.tp import TpLinear, TpStep
         out = {"world": self.world}
         modes = ("gather",) if self.world == 1 else ("fused", "gather")
         for mode in modes:
@@ -451,10 +513,15 @@ class Bench:
                     for n, lin in lins.items():
                         lin.forward(xs[n], barrier=False)
                     last.barrier()
-                ms = self.timed(step, st, warmup)
+                ms_eager = self.timed(step, st, warmup)
+                # the same step captured once and replayed: one launch per step and rank
+                graph = TpStep(list(lins.values()), [xs[n] for n in lins])
+                ms = self.timed(graph.replay, st, warmup)
+                del graph
                 wb = sum(wbytes(*SHAPES[n]) for n in lins)
                 fl = sum(2.0 * M * SHAPES[n][0] * SHAPES[n][1] for n in lins)
-                res[tag] = {"ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "tflops": fl / ms / 1e9}
+                res[tag] = {"ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "tflops": fl / ms / 1e9,
+                            "issue": "one CUDA graph per rank", "op_by_op_ms_per_step": ms_eager}
                 for lin in lins.values():
                     lin._bufs.clear()
                     lin._symm.clear()
@@ -611,6 +678,13 @@ def run_case(b, case, steps, warmup):
     """Single small cases, used for profiling one kernel at a time."""
     if case == "decode":           # gate+up at M=1 and M=16, two weight copies each
         res, _, eng = b.decode_sweep(steps, warmup, ms_list=(1, 16), names=("gate_up",))
+        eng.close()
+        return res
+    if case == "decode_parts":     # the decode kernel's time split into stream / arithmetic / exchange
+        return b.decode_parts()
+    if case == "e2e":              # the default sweep and its host-buffer step
+        res, ops, eng = b.decode_sweep(steps, warmup)
+        res["e2e"] = b.decode_e2e(ops, eng, max(2, steps // 2), warmup)
         eng.close()
         return res
     if case == "decode_m32":       # gate+up at M=32, two weight copies

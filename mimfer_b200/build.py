@@ -27,10 +27,11 @@ HEADERS = ["core/core.h", "kernels/launch.h", "kernels/ptx.cuh", "kernels/fp4.cu
            "../../include/mimfer_abi.h", "../../include/mimfer_b200.h"]
 
 CFLAGS = ["-std=c11", "-O2", "-fPIC", "-fopenmp", "-Wall", "-Wextra", "-Werror",
-          "-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(CUDA_HOME, "include")]
+          "-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(CUDA_HOME, "include"),
+          *os.environ.get("MMB_EXTRA_DEFS", "").split()]
 NVFLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
            "-Xcompiler", "-fPIC", "-I" + os.path.join(ROOT, "include"),
-           *os.environ.get("MMB_EXTRA_NVFLAGS", "").split()]
+           *os.environ.get("MMB_EXTRA_NVFLAGS", "").split(), *os.environ.get("MMB_EXTRA_DEFS", "").split()]
 
 
 def _stale(target, deps):

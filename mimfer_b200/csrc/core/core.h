@@ -51,6 +51,9 @@ void mmb_next_op_context(int pdl_mode, int ws_region);
 /* Regions the workspace is cut into, so that ops in flight together never share
  * scratch (1 when the workspace is too small to divide). */
 int mmb_ws_regions(void);
+/* Grow the runtime shim's event pool (mm_event_record / mm_event_wait indices)
+ * to at least n events; set-up time only. */
+mm_status mmb_event_pool_reserve(int n);
 /* The plan the launcher would pick for this op (glu: the op is a fused gate/up
  * pair, n2 = output features). */
 mm_status mmb_plan_for_op(const mm_op_desc *op, int glu, mm_f4_plan *out);

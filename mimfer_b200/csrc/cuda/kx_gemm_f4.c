@@ -39,6 +39,8 @@ static struct {
     int        next_pdl;         /* per-op override from the engine, -1 = none */
     int        next_region;
     unsigned long long launches;
+    /* experiment knobs (mm_f4_tune keys 2..4), all 0 in production */
+    uint32_t   st_rows, st_split, st_dbg;
 } G = { .forced_variant = -1, .pdl = 1, .next_pdl = -1 };
 
 /* The workspace is cut into WS_REGIONS equal regions, each with its own arrival
@@ -126,6 +128,9 @@ int mm_f4_tune(int key, int value)
         G.pdl = value ? 1 : 0;
         return old;
     }
+    if (key == 2) { int old = (int)G.st_rows; G.st_rows = (uint32_t)value; return old; }
+    if (key == 3) { int old = (int)G.st_split; G.st_split = (uint32_t)value; return old; }
+    if (key == 4) { int old = (int)G.st_dbg; G.st_dbg = (uint32_t)value; return old; }
     return -1;
 }
 
@@ -256,8 +261,11 @@ static mm_status plan_linear(const void *x, const void *payload, const void *sca
         sh.ptr_align = 8;                  /* 16-byte output vectors need aligned slices */
     if (sh.ptr_align < 16 && !n_dst)
         return MM_ERR_SHAPE;               /* arena slots are >= 16-byte aligned */
-    return G.forced_variant >= 0 ? mm_f4_select_variant(&sh, G.forced_variant, plan)
-                                 : mm_f4_select(&sh, plan);
+    mm_status st = G.forced_variant >= 0 ? mm_f4_select_variant(&sh, G.forced_variant, plan)
+                                         : mm_f4_select(&sh, plan);
+    if (st == MM_OK && plan->variant == MM_F4_V_STREAM && (G.st_rows || G.st_split))
+        st = mmb_plan_stream_with(&sh, G.st_rows, G.st_split, plan);
+    return st;
 }
 
 static mm_status linear_impl(const void *x, const void *payload, const void *scale, float gs,
@@ -290,11 +298,12 @@ static mm_status linear_impl(const void *x, const void *payload, const void *sca
         break;
     case MM_F4_V_STREAM:
         MM_CHECK(encode_2d(a.tm_payload, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, payload, K / 2, N, 128,
-                           MMB_ST_ROWS, CU_TENSOR_MAP_SWIZZLE_128B));
+                           a.plan.tile_n, CU_TENSOR_MAP_SWIZZLE_128B));
         MM_CHECK(encode_2d(a.tm_scale, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, scale, K / 16, N, 16,
-                           MMB_ST_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE));
+                           a.plan.tile_n, CU_TENSOR_MAP_SWIZZLE_NONE));
         MM_CHECK(encode_2d(a.tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, MMB_ST_KSTEP,
                            a.plan.tile_m, CU_TENSOR_MAP_SWIZZLE_NONE));
+        a.dbg = G.st_dbg;
         err = mmb_launch_stream(&a, stream);
         break;
     case MM_F4_V_STREAMT:

@@ -19,6 +19,8 @@
 
 static cudaStream_t g_stream[MM_ST_N];
 static cudaEvent_t  g_t0, g_t1;
+static cudaEvent_t *g_events;             /* ordering events, no timing: MM_N_EVENTS at init */
+static int          g_n_events;
 static int          g_ready, g_capturing, g_device = -1;
 
 #define CK(call)                                                              \
@@ -63,6 +65,37 @@ mm_status mm_cuda_init(int device_ordinal)
     CK(cudaEventCreate(&g_t1));
     g_device = dev;
     g_ready = 1;
+    return mmb_event_pool_reserve(MM_N_EVENTS);
+}
+
+/* Grow the event pool to at least n events (set-up time only). */
+mm_status mmb_event_pool_reserve(int n)
+{
+    MM_REQUIRE(g_ready && n > 0, MM_ERR_STATE);
+    if (n <= g_n_events)
+        return MM_OK;
+    cudaEvent_t *ev = (cudaEvent_t *)realloc(g_events, (size_t)n * sizeof *ev);
+    if (!ev)
+        return MM_ERR_NOMEM;
+    g_events = ev;
+    while (g_n_events < n) {
+        CK(cudaEventCreateWithFlags(&g_events[g_n_events], cudaEventDisableTiming));
+        g_n_events++;
+    }
+    return MM_OK;
+}
+
+mm_status mm_event_record(int ev, mm_stream_id st)
+{
+    MM_REQUIRE(g_ready && ev >= 0 && ev < g_n_events && (int)st >= 0 && st < MM_ST_N, MM_ERR_STATE);
+    CK(cudaEventRecord(g_events[ev], g_stream[st]));
+    return MM_OK;
+}
+
+mm_status mm_event_wait(int ev, mm_stream_id st)
+{
+    MM_REQUIRE(g_ready && ev >= 0 && ev < g_n_events && (int)st >= 0 && st < MM_ST_N, MM_ERR_STATE);
+    CK(cudaStreamWaitEvent(g_stream[st], g_events[ev], 0));
     return MM_OK;
 }
 
@@ -72,6 +105,11 @@ mm_status mm_cuda_shutdown(void)
         return MM_OK;
     cudaEventDestroy(g_t0);
     cudaEventDestroy(g_t1);
+    for (int i = 0; i < g_n_events; i++)
+        cudaEventDestroy(g_events[i]);
+    free(g_events);
+    g_events = NULL;
+    g_n_events = 0;
     cudaStreamDestroy(g_stream[MM_ST_COMPUTE]);
     cudaStreamDestroy(g_stream[MM_ST_XFER]);
     g_ready = 0;

@@ -31,6 +31,11 @@ struct mm_lin_engine {
     int          fuse_mlp;
     int          overlap;
     uint32_t     n_independent;     /* ops of the last walk launched without a leading wait */
+    /* host buffers bound before capture: the copies become nodes of the graph */
+    const void **x_bound;           /* [max_ops] pinned host source of op i's activations, or NULL */
+    void       **y_bound;           /* [max_ops] pinned host destination of op i's output, or NULL  */
+    int          bound, bound_captured;
+    uint32_t     upload_group;      /* ops whose uploads share one event (>= 1) */
 };
 
 mm_status mm_lin_engine_create(mm_lin_engine **out, uint32_t max_ops)
@@ -47,8 +52,37 @@ mm_status mm_lin_engine_create(mm_lin_engine **out, uint32_t max_ops)
         free(e);
         return MM_ERR_NOMEM;
     }
+    e->x_bound = (const void **)calloc(max_ops, sizeof(void *));
+    e->y_bound = (void **)calloc(max_ops, sizeof(void *));
+    if (!e->x_bound || !e->y_bound) {
+        mm_lin_engine_destroy(e);
+        return MM_ERR_NOMEM;
+    }
     e->max_ops = max_ops;
+    e->upload_group = 1;
     *out = e;
+    return MM_OK;
+}
+
+mm_status mm_lin_engine_upload_group(mm_lin_engine *e, uint32_t ops_per_event)
+{
+    MM_REQUIRE(e && ops_per_event >= 1, MM_ERR_STATE);
+    MM_REQUIRE(!e->captured, MM_ERR_BUSY);
+    e->upload_group = ops_per_event;
+    return MM_OK;
+}
+
+mm_status mm_lin_engine_bind_host(mm_lin_engine *e, const void *const *x_host, void *const *y_host)
+{
+    MM_REQUIRE(e && e->n_ops > 0, MM_ERR_STATE);
+    MM_REQUIRE(!e->captured, MM_ERR_BUSY);
+    e->bound = 0;
+    for (uint32_t i = 0; i < e->n_ops; i++) {
+        e->x_bound[i] = x_host ? x_host[i] : NULL;
+        e->y_bound[i] = y_host ? y_host[i] : NULL;
+        if (e->ops[i].op != OP_NOP && (e->x_bound[i] || e->y_bound[i]))
+            e->bound = 1;
+    }
     return MM_OK;
 }
 
@@ -173,8 +207,31 @@ static int ops_independent(const mm_op_desc *p, const mm_op_desc *q)
     return 1;
 }
 
+/* Events of the runtime shim's pool used while capturing a bound step. */
+enum { EV_FORK = 0, EV_Y = 1, EV_JOIN = 2, EV_OP0 = 4 };   /* EV_OP0 + i: op i's upload */
+
 static mm_status run_ops(mm_lin_engine *e)
 {
+    /* Bound host buffers, while capturing: the copies ride on the transfer stream
+     * as nodes of the same graph.  All uploads are enqueued first, none of them
+     * depending on a kernel, so the first op of a group only waits for the
+     * activations of its group and the copy engine works ahead of the kernels; each download follows its kernel
+     * and overlaps the next ones. */
+    const int with_copies = e->bound && mm_cuda_capturing();
+    const uint32_t grp = e->upload_group;
+    if (with_copies) {
+        MM_CHECK(mmb_event_pool_reserve((int)(e->n_ops / grp) + 1 + EV_OP0));
+        MM_CHECK(mm_event_record(EV_FORK, MM_ST_COMPUTE));
+        MM_CHECK(mm_event_wait(EV_FORK, MM_ST_XFER));
+        for (uint32_t i = 0; i < e->n_ops; i++) {
+            const mm_op_desc *op = &e->ops[i];
+            if (e->x_bound[i] && op->op != OP_NOP)
+                MM_CHECK(mm_h2d_async((void *)(uintptr_t)op->a, e->x_bound[i], op_in_bytes(op), MM_ST_XFER));
+            /* one event per group of ops, after the group's last upload */
+            if (i % grp == grp - 1 || i + 1 == e->n_ops)
+                MM_CHECK(mm_event_record(EV_OP0 + (int)(i / grp), MM_ST_XFER));
+        }
+    }
     mm_kcall kc;
     kc.e = (const mm_engine *)e;      /* the dispatcher only tests it for NULL */
     kc.stream = NULL;
@@ -209,6 +266,9 @@ static mm_status run_ops(mm_lin_engine *e)
             e->n_independent += (uint32_t)independent;
             mmb_next_op_context(independent ? MMB_PDL_INDEPENDENT : MMB_PDL_WAIT_FIRST, region);
         }
+        /* the first op of a group waits for the uploads of the whole group */
+        if (with_copies && i % grp == 0)
+            MM_CHECK(mm_event_wait(EV_OP0 + (int)(i / grp), MM_ST_COMPUTE));
         kc.op = &e->ops[i];
         mm_status st = e->ops[i].op == MMB_OP_GATE_UP
                            ? mmb_op_mlp_gate_up(&e->ops[i], e->up[i].payload, e->up[i].scale)
@@ -217,6 +277,15 @@ static mm_status run_ops(mm_lin_engine *e)
             MM_LOGE("engine: op %u (%s) failed: %s", i, e->ops[i].note, mm_status_str(st));
             return st;
         }
+        if (with_copies && e->y_bound[i] && op->op != OP_NOP) {
+            MM_CHECK(mm_event_record(EV_Y, MM_ST_COMPUTE));
+            MM_CHECK(mm_event_wait(EV_Y, MM_ST_XFER));
+            MM_CHECK(mm_d2h_async(e->y_bound[i], op->c, op_out_bytes(op), MM_ST_XFER));
+        }
+    }
+    if (with_copies) {
+        MM_CHECK(mm_event_record(EV_JOIN, MM_ST_XFER));
+        MM_CHECK(mm_event_wait(EV_JOIN, MM_ST_COMPUTE));
     }
     return MM_OK;
 }
@@ -234,7 +303,28 @@ mm_status mm_lin_engine_capture(mm_lin_engine *e)
     if (st2 != MM_OK)
         return st2;
     e->captured = 1;
+    e->bound_captured = e->bound;
     return MM_OK;
+}
+
+static mm_status step_status(void)
+{
+    unsigned flags = 0;
+    MM_CHECK(mm_f4_device_status(&flags));
+    if (flags) {
+        MM_LOGE("engine: device status 0x%x after step", flags);
+        return (flags & 1u) ? MM_ERR_TIMEOUT : MM_ERR_CUDA;
+    }
+    return MM_OK;
+}
+
+mm_status mm_lin_engine_step_bound(mm_lin_engine *e)
+{
+    MM_REQUIRE(e && e->n_ops > 0 && e->captured && e->bound_captured, MM_ERR_STATE);
+    MM_REQUIRE(!mm_cuda_capturing(), MM_ERR_BUSY);
+    MM_CHECK(mm_graph_launch(e->graph, MM_ST_COMPUTE));
+    MM_CHECK(mm_stream_sync(MM_ST_COMPUTE));
+    return step_status();
 }
 
 mm_status mm_lin_engine_launch(mm_lin_engine *e)
@@ -250,6 +340,7 @@ mm_status mm_lin_engine_launch_host(mm_lin_engine *e, const void *const *x_host,
 {
     MM_REQUIRE(e && e->n_ops > 0, MM_ERR_STATE);
     MM_REQUIRE(!mm_cuda_capturing(), MM_ERR_BUSY);
+    MM_REQUIRE(!(e->captured && e->bound_captured), MM_ERR_BUSY);   /* that graph already copies */
     for (uint32_t i = 0; x_host && i < e->n_ops; i++) {
         const mm_op_desc *op = &e->ops[i];
         if (x_host[i] && op->op != OP_NOP)
@@ -265,13 +356,7 @@ mm_status mm_lin_engine_launch_host(mm_lin_engine *e, const void *const *x_host,
             MM_CHECK(mm_d2h_async(y_host[i], op->c, op_out_bytes(op), MM_ST_COMPUTE));
     }
     MM_CHECK(mm_stream_sync(MM_ST_COMPUTE));
-    unsigned flags = 0;
-    MM_CHECK(mm_f4_device_status(&flags));
-    if (flags) {
-        MM_LOGE("engine: device status 0x%x after step", flags);
-        return (flags & 1u) ? MM_ERR_TIMEOUT : MM_ERR_CUDA;
-    }
-    return MM_OK;
+    return step_status();
 }
 
 void mm_lin_engine_destroy(mm_lin_engine *e)
@@ -281,5 +366,7 @@ void mm_lin_engine_destroy(mm_lin_engine *e)
     mm_graph_destroy(e->graph);
     free(e->ops);
     free(e->up);
+    free(e->x_bound);
+    free(e->y_bound);
     free(e);
 }

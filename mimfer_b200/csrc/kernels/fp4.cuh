@@ -104,6 +104,30 @@ __device__ __forceinline__ uint32_t scale_lut_entry_f16(uint32_t b)
     return u | (u << 16);
 }
 
+/* The four e4m3 scales of `sc4` (byte j = scale j) as four fp16x2 registers
+ * (c, c), by cvt.rn.f16x2.e4m3x2 instead of a table in shared memory: every
+ * e4m3 value is an exact fp16, the sign is kept.  The two NaN codes 0x7f and
+ * 0xff must read as 0.0 (include/mimfer/tensor.h:100-101): such bytes are
+ * cleared first, 0x00 converts to +0. */
+__device__ __forceinline__ void scales4_f16(uint32_t sc4, uint32_t (&c)[4])
+{
+    const uint32_t nan = (((sc4 & 0x7f7f7f7fu) + 0x01010101u) & 0x80808080u) >> 7;   /* 1 per NaN byte */
+    if (nan)
+        sc4 &= ~(nan * 0xffu);
+    uint32_t lo, hi;
+    asm("{\n\t"
+        ".reg .b16 a, b;\n\t"
+        "mov.b32 {a, b}, %2;\n\t"
+        "cvt.rn.f16x2.e4m3x2 %0, a;\n\t"
+        "cvt.rn.f16x2.e4m3x2 %1, b;\n\t"
+        "}"
+        : "=r"(lo), "=r"(hi) : "r"(sc4));
+    c[0] = prmt(lo, lo, 0x1010u);
+    c[1] = prmt(lo, lo, 0x3232u);
+    c[2] = prmt(hi, hi, 0x1010u);
+    c[3] = prmt(hi, hi, 0x3232u);
+}
+
 __device__ __forceinline__ uint4 unpack8_natural_f16(uint32_t w, uint32_t c)
 {
     uint4 r;

@@ -17,7 +17,9 @@ extern "C" {
 #define MMB_ST_ROWS        256    /* weight rows per CTA (16 warps x 16 rows)  */
 #define MMB_ST_KSTEP       256u   /* weights along K per pipeline stage        */
 #define MMB_ST_CONSUMERS   16     /* MMA warps                                  */
+#ifndef MMB_ST_XFORM_WARPS
 #define MMB_ST_XFORM_WARPS 4u     /* activation transform warps                 */
+#endif
 #define MMB_ST_THREADS     ((MMB_ST_CONSUMERS + 1u + MMB_ST_XFORM_WARPS) * 32u)
 #define MMB_ST_PAYLOAD_B   (MMB_ST_ROWS * 128u)            /* SW128 box        */
 #define MMB_ST_SCALE_B     (MMB_ST_ROWS * 16u)
@@ -75,6 +77,14 @@ extern "C" {
 #define MMB_PDL_WAIT_FIRST    2
 #define MMB_PDL_INDEPENDENT   3
 
+/* Measurement modes of the decode kernel (mmb_args.dbg, mm_f4_tune key 4;
+ * results are not meaningful with any of them set).  They split a launch time
+ * into its parts: the weight stream alone, the arithmetic alone, the split-K
+ * exchange. */
+#define MMB_DBG_NO_MATH      1u   /* consumers release every stage untouched        */
+#define MMB_DBG_NO_LOADS     2u   /* no TMA traffic and no waits: arithmetic on whatever shared memory holds */
+#define MMB_DBG_NO_EXCHANGE  4u   /* split-K slices store their own sums, no partials, no ticket */
+
 /* Device status word bits. */
 #define MMB_DEV_TIMEOUT    1u
 #define MMB_DEV_BADARG     2u
@@ -102,6 +112,7 @@ typedef struct mmb_args {
     void       *ws;       /* workspace base or NULL */
     mm_f4_plan  plan;
     int         pdl;      /* MMB_PDL_*: how the launch is ordered against its predecessor */
+    uint32_t    dbg;      /* MMB_DBG_* (decode kernel), 0 in production */
     /* 128-byte TMA descriptors, filled by the launcher (opaque here) */
     unsigned char tm_payload[128] __attribute__((aligned(64)));
     unsigned char tm_scale[128] __attribute__((aligned(64)));
@@ -117,6 +128,9 @@ int mmb_launch_streamt(const mmb_args *a, void *stream);
 int mmb_launch_silu_mul(const void *gate, const void *up, void *y, size_t n, void *stream);
 int mmb_launch_wait_selftest(unsigned *status, unsigned *done, void *stream);
 int mmb_launch_decode_probe(uint32_t *out_mma, uint32_t *out_f32, uint32_t *out_f16, void *stream);
+/* STREAM plan with the rows per CTA and the K split given (0 = the selector's
+ * own choice for that number); experiments and the selector's tests. */
+mm_status mmb_plan_stream_with(const mm_f4_shape *s, uint32_t rows, uint32_t split, mm_f4_plan *p);
 /* One-time per-process setup (smem opt-in attributes). */
 int mmb_kernels_init(void);
 /* Address of the device status word. */

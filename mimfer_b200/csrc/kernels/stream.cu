@@ -56,6 +56,8 @@ struct StreamParams {
     uint32_t        pdl;         /* MMB_PDL_* */
     float           gs_up;       /* gated pair: scale of the up projection        */
     uint32_t        gate_plane;  /* gated pair: which half of the CTA's rows is the gate */
+    uint32_t        rows;        /* weight rows per CTA: a multiple of 16, at most MMB_ST_ROWS */
+    uint32_t        dbg;         /* MMB_DBG_*: measurement modes, 0 in production  */
 };
 
 /* One output element to every destination (one, or all tensor-parallel peers). */
@@ -122,9 +124,13 @@ __device__ __forceinline__ void consume_step(float (&accs)[SLOTS][RT][MT][4], ui
 #pragma unroll
         for (int rr = 0; rr < 2; rr++) {
             const uint32_t sc4 = lds32(scl + (rt * 16u + rr * 8u) * 16u);
+            if (HALF) {
+                scales4_f16(sc4, cs[rt][rr]);
+            } else {
 #pragma unroll
-            for (int j = 0; j < 4; j++)
-                cs[rt][rr][j] = lds32(lut + ((sc4 >> (8 * j)) & 255u) * 4u);
+                for (int j = 0; j < 4; j++)
+                    cs[rt][rr][j] = lds32(lut + ((sc4 >> (8 * j)) & 255u) * 4u);
+            }
         }
 #pragma unroll
     for (int h = 0; h < 2; h++) {
@@ -263,15 +269,20 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
     const uint32_t last_flag = fmt_flag + 4u * p.stages;     /* split-K: "this CTA reduces" */
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    /* rows of this CTA and the consumer warps that have some (16 rows each); a
+     * gated pair always takes the full tile, half of it from each projection */
+    const uint32_t rows = GLU ? MMB_ST_ROWS : p.rows;
+    const uint32_t nc = rows >> 4;
     /* first weight row of the CTA (of each projection for a gated pair) */
-    const uint32_t row0 = blockIdx.x * (GLU ? MMB_ST_ROWS / 2 : MMB_ST_ROWS);
+    const uint32_t row0 = blockIdx.x * (GLU ? MMB_ST_ROWS / 2 : rows);
     const uint32_t ks_begin = static_cast<uint32_t>(
         static_cast<uint64_t>(p.k_steps) * blockIdx.y / p.split_k);
     const uint32_t ks_end = static_cast<uint32_t>(
         static_cast<uint64_t>(p.k_steps) * (blockIdx.y + 1) / p.split_k);
     const uint32_t nsteps = ks_end - ks_begin;
 
-    const uint32_t stage_bytes = MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B + MMB_ST_X_RAW_B(MT);
+    const uint32_t stage_bytes = rows * 144u + MMB_ST_X_RAW_B(MT);   /* payload + scales + activations */
+    const bool loads = !(p.dbg & MMB_DBG_NO_LOADS);
     const uint32_t first = nsteps < p.stages ? nsteps : p.stages;   /* steps of the first ring */
     if (tid == MMB_ST_CONSUMERS * 32u) {
         /* the issuing thread sets the barriers up itself and starts the weight
@@ -282,10 +293,10 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
         for (uint32_t s = 0; s < p.stages; s++) {
             mbar_init(bar_raw + 8u * s, 1u);
             mbar_init(bar_full + 8u * s, XFORM_THREADS);
-            mbar_init(bar_empty + 8u * s, MMB_ST_CONSUMERS);
+            mbar_init(bar_empty + 8u * s, nc);
         }
         mbar_fence_init();
-        for (uint32_t it = 0; it < first; it++) {
+        for (uint32_t it = 0; loads && it < first; it++) {
             const uint32_t stage = base + it * STAGE_B, ks = ks_begin + it;
             mbar_expect_tx(bar_raw + 8u * it, stage_bytes);
             load_weights<GLU>(stage, &tm_payload, &tm_scale, ks, row0, bar_raw + 8u * it);
@@ -314,11 +325,11 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
                 if (p.pdl == MMB_PDL_WAIT_FIRST)
                     grid_dep_launch();
             }
-            for (uint32_t it = 0; it < first; it++)
+            for (uint32_t it = 0; loads && it < first; it++)
                 tma_load_2d(base + it * STAGE_B + MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B, &tm_x,
                             static_cast<int>((ks_begin + it) * MMB_ST_KSTEP), 0, bar_raw + 8u * it);
             uint32_t s = 0, round = 1;                 /* stage index and its use count */
-            for (uint32_t it = first; it < nsteps; it++, s = (s + 1u == p.stages) ? 0u : s + 1u,
+            for (uint32_t it = first; loads && it < nsteps; it++, s = (s + 1u == p.stages) ? 0u : s + 1u,
                                                    round += (s == 0u)) {
                 const uint32_t stage = base + s * STAGE_B, ks = ks_begin + it;
                 mbar_wait(bar_empty + 8u * s, (round - 1u) & 1u, p.status);
@@ -339,7 +350,7 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
          * the operand format of the step and rewrite the slot in place. */
         const uint32_t xt = tid - (MMB_ST_CONSUMERS + 1u) * 32u;
         uint32_t s = 0, round = 0;
-        for (uint32_t it = 0; it < nsteps; it++, s = (s + 1u == p.stages) ? 0u : s + 1u,
+        for (uint32_t it = 0; loads && it < nsteps; it++, s = (s + 1u == p.stages) ? 0u : s + 1u,
                                            round += (s == 0u)) {
             const uint32_t xs = base + s * STAGE_B + MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B;
             mbar_wait_warp(bar_raw + 8u * s, round & 1u, p.status);
@@ -387,7 +398,10 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
     }
 
     /* --------------------------------- consumers ------------------------- */
+    if (warp >= nc)
+        return;                                        /* no rows for this warp */
     const uint32_t g = lane >> 2, t = lane & 3u;
+    const uint32_t nct = nc * 32u;                     /* threads at the consumers' named barrier */
     /* SLOTS independent accumulator sets per (row tile, activation tile): the
      * warp MMA has a long dependent-issue latency, so consecutive MMAs must not
      * chain on one accumulator.  Eight chains per warp whatever MT is. */
@@ -406,13 +420,16 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
     for (uint32_t it = 0; it < nsteps; it++, s = (s + 1u == p.stages) ? 0u : s + 1u,
                                        round += (s == 0u)) {
         const uint32_t stage = base + s * STAGE_B;
-        mbar_wait_warp(bar_full + 8u * s, round & 1u, p.status);
-        if (lds32(fmt_flag + 4u * s) != 0u)
-            consume_step<MT, RT, SLOTS, true>(accs, stage, lut_hf, warp, g, t);
-        else
-            consume_step<MT, RT, SLOTS, false>(accs, stage, lut_bf, warp, g, t);
+        if (loads)
+            mbar_wait_warp(bar_full + 8u * s, round & 1u, p.status);
+        if (!(p.dbg & MMB_DBG_NO_MATH)) {
+            if (!loads || lds32(fmt_flag + 4u * s) != 0u)
+                consume_step<MT, RT, SLOTS, true>(accs, stage, lut_hf, warp, g, t);
+            else
+                consume_step<MT, RT, SLOTS, false>(accs, stage, lut_bf, warp, g, t);
+        }
         __syncwarp();
-        if (lane == 0)
+        if (loads && lane == 0)
             mbar_arrive(bar_empty + 8u * s);
     }
 
@@ -430,7 +447,7 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
                 for (int sl = 1; sl < SLOTS; sl++) v += accs[sl][rt][mt][i];
                 acc[rt][mt][i] = v;
             }
-    if (p.split_k == 1) {
+    if (p.split_k == 1 || (p.dbg & MMB_DBG_NO_EXCHANGE)) {
         if constexpr (GLU) {
             glu_store<MT, RT>(p, acc, base, row0, warp, g, t);
         } else {
@@ -469,16 +486,20 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
                 if (MMB_ROW_OK(lr) && m < p.M)
                     __stcg(mine + static_cast<size_t>(m) * MMB_PPITCH + pc, acc[rt][mt][i]);
             }
-    __threadfence();
-    asm volatile("bar.sync 1, %0;" ::"n"(MMB_ST_CONSUMERS * 32) : "memory");
+    /* Every thread's partials are ordered before the ticket by the CTA barrier
+     * and one device-scope fence of the thread that takes the ticket; on the
+     * other side the same thread fences after the ticket and the barrier hands
+     * the visibility on to the CTA (the pattern of a grid-wide barrier). */
+    asm volatile("bar.sync 1, %0;" ::"r"(nct) : "memory");
     if (tid == 0) {
+        __threadfence();
         const unsigned ticket = atomicAdd(p.counters + blockIdx.x, 1u);
+        __threadfence();
         sts32(last_flag, (ticket == p.split_k - 1u) ? 1u : 0u);
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(MMB_ST_CONSUMERS * 32) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"r"(nct) : "memory");
     if (!lds32(last_flag))
         return;
-    __threadfence();
     /* Slices are added in ascending order for every output, so the sum does not
      * depend on which CTA arrived last; the loads of several slices (all
      * outputs of this thread) are issued together. */
@@ -563,6 +584,8 @@ static int launch_mt(const mmb_args *a, unsigned *status, cudaStream_t st)
     p.stages = a->plan.stages;
     p.gs_up = a->gs_up;
     p.gate_plane = a->gate_plane ? 1u : 0u;
+    p.rows = a->plan.tile_n;
+    p.dbg = a->dbg;
     p.pdl = static_cast<uint32_t>(a->pdl);
     TmaDesc tp, ts, tx;
     memcpy(tp.bytes, a->tm_payload, 128);
@@ -610,6 +633,9 @@ extern "C" int mmb_launch_stream(const mmb_args *a, void *stream)
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (a->glu && a->n_dst)
         return static_cast<int>(cudaErrorInvalidValue);    /* the gated pair has no peer-store form */
+    if (a->plan.tile_n == 0 || a->plan.tile_n % 16u != 0 || a->plan.tile_n > MMB_ST_ROWS ||
+        (a->glu && a->plan.tile_n != MMB_ST_ROWS))
+        return static_cast<int>(cudaErrorInvalidValue);
     switch (a->plan.m_tiles) {
     case 1: return a->glu ? mmb::launch_mt<1, true>(a, status, st) : mmb::launch_mt<1, false>(a, status, st);
     case 2: return a->glu ? mmb::launch_mt<2, true>(a, status, st) : mmb::launch_mt<2, false>(a, status, st);
@@ -741,9 +767,9 @@ extern "C" mm_status mm_f4_linear_static_ws(const void *x, const void *payload, 
         return MM_ERR_CAPACITY;
     }
     if (!static_encode(a.tm_payload, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, payload, K / 2, N, 128,
-                       MMB_ST_ROWS, CU_TENSOR_MAP_SWIZZLE_128B) ||
+                       a.plan.tile_n, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !static_encode(a.tm_scale, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, scale, K / 16, N, 16,
-                       MMB_ST_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+                       a.plan.tile_n, CU_TENSOR_MAP_SWIZZLE_NONE) ||
         !static_encode(a.tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, MMB_ST_KSTEP,
                        a.plan.tile_m, CU_TENSOR_MAP_SWIZZLE_NONE)) {
         MM_LOGE("mm_f4_linear_static_ws: tensor map encoding failed");

@@ -21,6 +21,7 @@
 #include <string.h>
 
 static uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
+static mm_status check_shape(const mm_f4_shape *s, mm_f4_plan *out);
 
 static int fast_path_ok(const mm_f4_shape *s)
 {
@@ -40,22 +41,27 @@ static void plan_rowwarp(const mm_f4_shape *s, mm_f4_plan *p)
     if (p->grid_y > 65535) p->grid_y = 65535;
 }
 
-static mm_status plan_stream(const mm_f4_shape *s, mm_f4_plan *p)
+/* STREAM plan with `rows` weight rows per CTA (a multiple of 16, at most
+ * MMB_ST_ROWS) and K cut into `split` slices; split = 0 picks the split that
+ * gives about one CTA per SM. */
+static mm_status plan_stream_with(const mm_f4_shape *s, uint32_t rows, uint32_t split, mm_f4_plan *p)
 {
     if (!fast_path_ok(s) || s->M > 32)
         return MM_ERR_UNSUPPORTED;
+    if (rows == 0 || rows % 16u != 0 || rows > MMB_ST_ROWS)
+        return MM_ERR_RANGE;
     memset(p, 0, sizeof *p);
     p->variant = MM_F4_V_STREAM;
     p->m_tiles = s->M <= 8 ? 1 : (s->M <= 16 ? 2 : 4);
-    p->tile_n = MMB_ST_ROWS;
+    p->tile_n = rows;
     p->tile_m = p->m_tiles * 8;
     p->k_steps = s->K / MMB_ST_KSTEP;
-    p->grid_x = ceil_div(s->N, MMB_ST_ROWS);
+    p->grid_x = ceil_div(s->N, rows);
     p->threads = MMB_ST_THREADS;
 
     /* split K until roughly one CTA per SM, keeping >= 4 steps per slice */
     uint32_t sms = s->sm_count ? s->sm_count : 148;
-    uint32_t sk = sms / p->grid_x;
+    uint32_t sk = split ? split : sms / p->grid_x;
     if (sk < 1) sk = 1;
     uint32_t max_by_steps = p->k_steps / 4 ? p->k_steps / 4 : 1;
     if (sk > max_by_steps) sk = max_by_steps;
@@ -79,6 +85,17 @@ static mm_status plan_stream(const mm_f4_shape *s, mm_f4_plan *p)
     p->stages = st;
     p->smem_bytes = st * stage + MMB_ST_FIXED_B;
     return MM_OK;
+}
+
+static mm_status plan_stream(const mm_f4_shape *s, mm_f4_plan *p)
+{
+    return plan_stream_with(s, MMB_ST_ROWS, 0, p);
+}
+
+mm_status mmb_plan_stream_with(const mm_f4_shape *s, uint32_t rows, uint32_t split, mm_f4_plan *p)
+{
+    mm_status st = check_shape(s, p);
+    return st != MM_OK ? st : plan_stream_with(s, rows ? rows : MMB_ST_ROWS, split, p);
 }
 
 static mm_status plan_streamt(const mm_f4_shape *s, mm_f4_plan *p)

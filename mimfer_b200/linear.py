@@ -291,6 +291,22 @@ class LinearEngine:
         ys = (C.c_void_p * n)(*[t.data_ptr() if t is not None else None for t in y_host])
         L.check(self.rt.lib.mm_lin_engine_launch_host(self.h, xs, ys), "mm_lin_engine_launch_host")
 
+    def bind_host(self, x_host, y_host):
+        """Bind pinned host tensors (None entries are skipped) before capture():
+        the copies become nodes of the captured graph (mm_lin_engine_bind_host)."""
+        n = self.n_ops()
+        xs = (C.c_void_p * n)(*[t.data_ptr() if t is not None else None for t in x_host])
+        ys = (C.c_void_p * n)(*[t.data_ptr() if t is not None else None for t in y_host])
+        self._keep.append((x_host, y_host))
+        L.check(self.rt.lib.mm_lin_engine_bind_host(self.h, xs, ys), "mm_lin_engine_bind_host")
+
+    def upload_group(self, ops_per_event):
+        L.check(self.rt.lib.mm_lin_engine_upload_group(self.h, ops_per_event), "mm_lin_engine_upload_group")
+
+    def step_bound(self):
+        """Replay the graph captured with bound host buffers; synchronises."""
+        L.check(self.rt.lib.mm_lin_engine_step_bound(self.h), "mm_lin_engine_step_bound")
+
     def n_ops(self):
         return self.rt.lib.mm_lin_engine_n_ops(self.h)
 

@@ -286,6 +286,41 @@ def test_engine_host_step(rt, oracle):
     eng.close()
 
 
+@pytest.mark.parametrize("overlap", [False, True])
+def test_engine_bound_host_step(rt, oracle, overlap):
+    """mm_lin_engine_bind_host + mm_lin_engine_step_bound: the uploads and downloads are nodes
+    of the captured graph; refilling the same pinned buffers changes the next step's result."""
+    torch = rt.torch
+    shapes = [(2, 1024, 512), (16, 5120, 768), (5, 512, 1000), (1, 2048, 256)]
+    ws = [mm.make_weight(N, K, seed=i).to_device(rt.device) for i, (M, K, N) in enumerate(shapes)]
+    xd = [torch.zeros((M, K), dtype=torch.bfloat16, device=rt.device) for (M, K, N) in shapes]
+    yd = [torch.zeros((M, N), dtype=torch.bfloat16, device=rt.device) for (M, K, N) in shapes]
+    xh = [torch.zeros((M, K), dtype=torch.bfloat16).pin_memory() for (M, K, N) in shapes]
+    yh = [torch.zeros((M, N), dtype=torch.bfloat16).pin_memory() for (M, K, N) in shapes]
+    eng = mm.LinearEngine(rt)
+    eng.overlap(overlap)
+    for x, w, y in zip(xd, ws, yd):
+        eng.add(x, w, y)
+    eng.bind_host(xh, [yh[0], yh[1], None, yh[3]])          # None: output stays on the device
+    eng.capture()
+    with pytest.raises(mm.MimferError):                     # that graph already carries the copies
+        eng.launch_host(xh, yh)
+    for step in range(2):
+        xb = [mm.make_activations(M, K, seed=90 + 10 * step + i) for i, (M, K, N) in enumerate(shapes)]
+        for t, b in zip(xh, xb):
+            t.copy_(torch.from_numpy(b.view(np.int16)).view(torch.bfloat16))
+        for t in yh:
+            t.zero_()
+        eng.step_bound()
+        for i in (0, 1, 3):
+            got = yh[i].view(torch.int16).numpy().view(np.uint16)
+            assert row_rel_l2(got, oracle.gemm_f4(xb[i], ws[i].payload, ws[i].scales, ws[i].gs)) <= REL_L2_TOL
+        assert not yh[2].view(torch.int16).numpy().any()
+        assert row_rel_l2(rt.from_device_bf16(yd[2]),
+                          oracle.gemm_f4(xb[2], ws[2].payload, ws[2].scales, ws[2].gs)) <= REL_L2_TOL
+    eng.close()
+
+
 def test_host_buffer_call(rt, oracle):
     torch = rt.torch
     M, K, N = 4, 1024, 512

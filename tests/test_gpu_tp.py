@@ -41,6 +41,20 @@ def _worker(rank, world, port, cases, out_dir, mode):
         rt.sync()
         assert rt.device_status() == 0
         np.save(os.path.join(out_dir, f"y{i}_{rank}.npy"), rt.from_device_bf16(y))
+    # the same linears as one captured step: refill the activations in place, replay
+    from mimfer_b200.tp import TpStep
+    M, K, N = cases[1]
+    lins = [TpLinear(mm.make_weight(N, K, seed=40 + j), rank, world, rt=rt, mode=mode) for j in range(2)]
+    xs = [rt.to_device_bf16(mm.make_activations(M, K, seed=1)) for _ in range(2)]
+    step = TpStep(lins, xs)
+    for j in range(2):
+        xs[j].copy_(rt.to_device_bf16(mm.make_activations(M, K, seed=60 + j)))
+    torch.cuda.synchronize()
+    ys = step.replay()
+    rt.sync()
+    assert rt.device_status() == 0
+    for j in range(2):
+        np.save(os.path.join(out_dir, f"g{j}_{rank}.npy"), rt.from_device_bf16(ys[j]))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -63,3 +77,10 @@ def test_two_gpu_tensor_parallel_matches_oracle(tmp_path, oracle, lib, mode):
         ys = [np.load(tmp_path / f"y{i}_{r}.npy") for r in range(world)]
         assert np.array_equal(ys[0], ys[1])                          # every rank holds the full output
         assert row_rel_l2(ys[0], want) <= REL_L2_TOL
+    M, K, N = cases[1]
+    for j in range(2):                                               # the captured step
+        w = mm.make_weight(N, K, seed=40 + j)
+        want = oracle.gemm_f4(mm.make_activations(M, K, seed=60 + j), w.payload, w.scales, w.gs)
+        gs = [np.load(tmp_path / f"g{j}_{r}.npy") for r in range(world)]
+        assert np.array_equal(gs[0], gs[1])
+        assert row_rel_l2(gs[0], want) <= REL_L2_TOL
