@@ -20,8 +20,9 @@
  *
  *  fp16   when every activation of the slice is zero or has 2^-17 <= |x| < 2^16,
  *         i.e. converts to fp16 without loss.  Weights go through
- *         cvt.rn.f16x2.e2m1x2 and one packed fp16 multiply by the scale: about
- *         one instruction per weight.  Activations are stored in column order.
+ *         cvt.rn.f16x2.e2m1x2 and one packed fp16 multiply by the scale (itself
+ *         converted with cvt.rn.f16x2.e4m3x2, no table): about one instruction
+ *         per weight.  Activations are stored in column order.
  *  bf16   otherwise (tiny, huge or non-finite activations).  Weights take the
  *         bf16 subnormal construction of fp4.cuh, about two instructions per
  *         weight, with the pairing (n0,n4)(n1,n5)(n2,n6)(n3,n7); the transform warps
@@ -260,9 +261,8 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
     constexpr uint32_t ITEMS = MPAD * 32u / XFORM_THREADS;    /* 16-byte chunks per transform thread */
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t lut_bf = base + p.stages * STAGE_B;       /* scale * 2^118, bf16x2 */
-    const uint32_t lut_hf = lut_bf + 1024u;                  /* scale, fp16x2          */
-    const uint32_t bar_raw = lut_hf + 1024u;                 /* [stages] TMA landed      */
+    const uint32_t lut_bf = base + p.stages * STAGE_B;       /* scale * 2^118, bf16x2 (bf16 steps) */
+    const uint32_t bar_raw = lut_bf + 2048u;                 /* [stages] TMA landed      */
     const uint32_t bar_full = bar_raw + 8u * p.stages;       /* [stages] activations ready */
     const uint32_t bar_empty = bar_full + 8u * p.stages;     /* [stages] consumers done  */
     const uint32_t fmt_flag = bar_empty + 8u * p.stages;     /* [stages] 1 = fp16 step  */
@@ -302,10 +302,8 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
             load_weights<GLU>(stage, &tm_payload, &tm_scale, ks, row0, bar_raw + 8u * it);
         }
     }
-    if (tid < 256u) {
-        sts32(lut_bf + tid * 4u, scale_lut_entry(tid));
-        sts32(lut_hf + tid * 4u, scale_lut_entry_f16(tid));
-    }
+    if (tid < 256u)
+        sts32(lut_bf + tid * 4u, scale_lut_entry(tid));     /* the fp16 steps convert their scales directly */
     __syncthreads();
     if (p.pdl == MMB_PDL_TRIGGER_FIRST)
         grid_dep_launch();
@@ -424,7 +422,7 @@ f4_stream_kernel(const __grid_constant__ TmaDesc tm_payload,
             mbar_wait_warp(bar_full + 8u * s, round & 1u, p.status);
         if (!(p.dbg & MMB_DBG_NO_MATH)) {
             if (!loads || lds32(fmt_flag + 4u * s) != 0u)
-                consume_step<MT, RT, SLOTS, true>(accs, stage, lut_hf, warp, g, t);
+                consume_step<MT, RT, SLOTS, true>(accs, stage, lut_bf, warp, g, t);
             else
                 consume_step<MT, RT, SLOTS, false>(accs, stage, lut_bf, warp, g, t);
         }

@@ -89,7 +89,15 @@ static mm_status plan_stream_with(const mm_f4_shape *s, uint32_t rows, uint32_t 
 
 static mm_status plan_stream(const mm_f4_shape *s, mm_f4_plan *p)
 {
-    return plan_stream_with(s, MMB_ST_ROWS, 0, p);
+    /* A weight with few rows (k and v projections: N = 1024) cannot fill the SMs
+     * with 256-row tiles even at the deepest K split; half-height tiles double
+     * the CTAs that stream it (measured on B200, N = 1024, K = 5120: 3.1 us
+     * against 3.7 us at M = 1, 3.8 against 4.6 at M = 16; 64-row tiles lose again). */
+    uint32_t sms = s->sm_count ? s->sm_count : 148;
+    uint32_t k_steps = s->K / MMB_ST_KSTEP;
+    uint32_t max_split = k_steps / 4 ? k_steps / 4 : 1;
+    uint32_t rows = ceil_div(s->N, MMB_ST_ROWS) * max_split * 4u < sms ? MMB_ST_ROWS / 2 : MMB_ST_ROWS;
+    return plan_stream_with(s, rows, 0, p);
 }
 
 mm_status mmb_plan_stream_with(const mm_f4_shape *s, uint32_t rows, uint32_t split, mm_f4_plan *p)
@@ -102,7 +110,7 @@ static mm_status plan_streamt(const mm_f4_shape *s, mm_f4_plan *p)
 {
     /* same decomposition as STREAM; the activation rows are padded to the
      * tensor-core N extent (16 or 32) instead of to 8-row MMA tiles */
-    mm_status st = plan_stream(s, p);
+    mm_status st = plan_stream_with(s, MMB_ST_ROWS, 0, p);
     if (st != MM_OK)
         return st;
     p->variant = MM_F4_V_STREAMT;
@@ -209,7 +217,7 @@ mm_status mm_f4_select_glu(const mm_f4_shape *s, mm_f4_plan *out)
     mm_f4_shape rows = *s;
     rows.N = ceil_div(s->N, MMB_ST_ROWS / 2) * MMB_ST_ROWS;      /* weight rows incl. tile padding */
     if (s->M <= 32)
-        return plan_stream(&rows, out);       /* partials are laid out per 256-row tile */
+        return plan_stream_with(&rows, MMB_ST_ROWS, 0, out);       /* partials are laid out per 256-row tile */
     if (s->N % 8 != 0)
         return MM_ERR_UNSUPPORTED;
     uint32_t sms = s->sm_count ? s->sm_count : 148;

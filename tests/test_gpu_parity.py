@@ -82,6 +82,27 @@ def test_stream_long_k_split(rt, oracle, M):
     check(rt, oracle, M, 17408, 5120, None, seed=5)
 
 
+@pytest.mark.parametrize("rows,split", [(256, 1), (240, 0), (128, 3), (48, 0), (16, 2)])
+@pytest.mark.parametrize("M", [1, 16])
+def test_stream_rows_per_cta(rt, oracle, M, rows, split):
+    """The decode kernel with any multiple of 16 weight rows per CTA (idle consumer
+    warps, ragged last tile) and a forced K split: same result as the oracle, and
+    bit-for-bit the 256-row result when the K split is the same."""
+    K, N = 2048, 1000
+    want = check(rt, oracle, M, K, N, V_STREAM, seed=31)
+    base = mm.select_plan(M, K, N, ws_bytes=rt.lib.mm_f4_workspace_bytes(), variant=V_STREAM)
+    assert base.split_k == 2                   # K / 256 = 8 steps, at least 4 per slice
+    rt.lib.mm_f4_tune(2, rows)
+    rt.lib.mm_f4_tune(3, split)
+    try:
+        got = check(rt, oracle, M, K, N, V_STREAM, seed=31)
+    finally:
+        rt.lib.mm_f4_tune(2, 0)
+        rt.lib.mm_f4_tune(3, 0)
+    if split != 1:                             # every other case ends up with two K slices too
+        assert np.array_equal(got, want)
+
+
 def test_stream_without_workspace(rt, oracle):
     ws = rt.workspace
     rt.sync()

@@ -14,11 +14,20 @@ def test_decode_shapes_use_stream_and_fill_the_gpu(lib):
             p = mm.select_plan(M, K, N, ws_bytes=WS)
             assert p.variant == V_STREAM
             assert p.m_tiles * 8 >= M and p.m_tiles in (1, 2, 4)
-            assert p.k_steps == K // 256 and p.grid_x == -(-N // 256)
+            assert p.k_steps == K // 256 and p.tile_n == 256 and p.grid_x == -(-N // 256)
             assert 100 <= p.grid_x * p.grid_y <= 148
             assert p.smem_bytes <= SMEM_MAX and p.stages >= 2
             if p.split_k > 1:
                 assert p.ws_needed <= WS and p.k_steps // p.split_k >= 4
+
+
+def test_small_weights_get_half_height_tiles(lib):
+    """k and v projections (N = 1024): 256-row tiles give 20 CTAs at the deepest split, so
+    the selector halves the tile; bigger weights keep 256 rows."""
+    p = mm.select_plan(16, 5120, 1024, ws_bytes=WS)
+    assert p.variant == V_STREAM and p.tile_n == 128 and p.grid_x == 8 and p.split_k == 5
+    for (K, N) in ((5120, 6144), (5120, 34816), (17408, 5120)):
+        assert mm.select_plan(16, K, N, ws_bytes=WS).tile_n == 256
 
 
 def test_no_workspace_means_no_split(lib):
