@@ -513,15 +513,17 @@ class Bench:
                     for n, lin in lins.items():
                         lin.forward(xs[n], barrier=False)
                     last.barrier()
-                ms_eager = self.timed(step, st, warmup)
-                # the same step captured once and replayed: one launch per step and rank
-                graph = TpStep(list(lins.values()), [xs[n] for n in lins])
-                ms = self.timed(graph.replay, st, warmup)
-                del graph
+                ms_eager = ms = self.timed(step, st, warmup)
+                if mode == "fused" or self.world == 1:
+                    # the same step captured once and replayed: one launch per step and rank
+                    graph = TpStep(list(lins.values()), [xs[n] for n in lins])
+                    ms = self.timed(graph.replay, st, warmup)
+                    del graph
                 wb = sum(wbytes(*SHAPES[n]) for n in lins)
                 fl = sum(2.0 * M * SHAPES[n][0] * SHAPES[n][1] for n in lins)
                 res[tag] = {"ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "tflops": fl / ms / 1e9,
-                            "issue": "one CUDA graph per rank", "op_by_op_ms_per_step": ms_eager}
+                            "issue": "one CUDA graph per rank" if mode == "fused" or self.world == 1
+                                     else "op by op", "op_by_op_ms_per_step": ms_eager}
                 for lin in lins.values():
                     lin._bufs.clear()
                     lin._symm.clear()

@@ -208,6 +208,18 @@ mm_status mm_f4_linear_tp(const void *x, const void *payload, const void *scale,
                           void *const *y_all, uint32_t n_ranks, uint32_t ldy, uint32_t col0,
                           uint32_t M, uint32_t K, uint32_t N_local, void *stream);
 
+/* Cross-rank barrier for the tensor-parallel form (no counterpart in the
+ * reference): one small kernel on `stream` (NULL = the compute stream).
+ * flags_all[r] points at rank r's flag block: 64 bytes of memory every rank can
+ * write (r == rank: this GPU's own block, the others peer-mapped), zeroed once
+ * before the first barrier, indexed by rank.  After the kernel, every store any
+ * rank issued on its stream before its own call of the same barrier is visible
+ * here.  No argument changes between calls, so the call can be captured into a
+ * graph.  A peer that does not arrive within about a second makes the wait give
+ * up with MMB_DEV_TIMEOUT in the device status word (mm_f4_device_status,
+ * MM_ERR_TIMEOUT from the synchronising calls) instead of hanging the GPU. */
+mm_status mm_f4_tp_barrier(void *const *flags_all, uint32_t n_ranks, uint32_t rank, void *stream);
+
 /* No counterpart in the reference.  The decode kernel of mm_f4_linear with its
  * split-K scratch built in, for callers that cannot hand over a workspace and
  * may not allocate one: code that runs under mimfer's rule that device memory

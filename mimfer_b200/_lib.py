@@ -122,6 +122,7 @@ SIGNATURES = {
     "mm_f4_force_variant": (None, [C.c_int]),
     "mm_f4_linear": (C.c_int, [_vp, _vp, _vp, _f, _vp, _u32, _u32, _u32, _vp]),
     "mm_f4_linear_tp": (C.c_int, [_vp, _vp, _vp, _f, C.POINTER(_vp), _u32, _u32, _u32, _u32, _u32, _u32, _vp]),
+    "mm_f4_tp_barrier": (C.c_int, [C.POINTER(_vp), _u32, _u32, _vp]),
     "mm_f4_linear_static_ws": (C.c_int, [_vp, _vp, _vp, _f, _vp, _u32, _u32, _u32, _vp]),
     "mm_f4_linear_host": (C.c_int, [_vp, _vp, _vp, _vp, _f, _vp, _vp, _u32, _u32, _u32]),
     "mm_f4_device_status": (C.c_int, [C.POINTER(C.c_uint)]),

@@ -599,6 +599,23 @@ mm_status mm_f4_linear_host(const void *x_host, void *x_dev, const void *payload
     return finish_op();
 }
 
+mm_status mm_f4_tp_barrier(void *const *flags_all, uint32_t n_ranks, uint32_t rank, void *stream)
+{
+    MM_REQUIRE(flags_all && n_ranks >= 1 && n_ranks <= MMB_MAX_PEERS && rank < n_ranks, MM_ERR_RANGE);
+    for (uint32_t r = 0; r < n_ranks; r++)
+        MM_REQUIRE(flags_all[r] && ((uintptr_t)flags_all[r] & 3u) == 0, MM_ERR_STATE);
+    MM_CHECK(ensure_ready());
+    if (!stream)
+        stream = mm_cuda_stream_raw(MM_ST_COMPUTE);
+    int err = mmb_launch_tp_barrier((unsigned *const *)flags_all, n_ranks, rank, stream);
+    if (err) {
+        MM_LOGE("cuda: tensor-parallel barrier launch: %s", cudaGetErrorString((cudaError_t)err));
+        return MM_ERR_CUDA;
+    }
+    G.launches++;
+    return MM_OK;
+}
+
 mm_status mm_f4_wait_selftest(unsigned *done_dev)
 {
     MM_REQUIRE(done_dev, MM_ERR_STATE);

@@ -58,6 +58,11 @@ extern "C" {
 
 #define MMB_MAX_PEERS      8u
 
+/* Flag block of the cross-rank barrier (mm_f4_tp_barrier): one arrival slot per
+ * peer, then the owner's epoch counter; 64 bytes, zeroed before first use. */
+#define MMB_TPB_EPOCH      MMB_MAX_PEERS
+#define MMB_TPB_WORDS      16u
+
 /* Programmatic dependent launch, per op.  C(k) = completion of kernel k of the
  * stream, T(k) = the moment all its CTAs have triggered their dependents.
  *   OFF           plain launch: starts after C(prev).
@@ -125,6 +130,7 @@ int mmb_launch_rowwarp(const mmb_args *a, void *stream);
 int mmb_launch_stream(const mmb_args *a, void *stream);
 int mmb_launch_umma(const mmb_args *a, void *stream);
 int mmb_launch_streamt(const mmb_args *a, void *stream);
+int mmb_launch_tp_barrier(unsigned *const *flags, uint32_t n_ranks, uint32_t rank, void *stream);
 int mmb_launch_silu_mul(const void *gate, const void *up, void *y, size_t n, void *stream);
 int mmb_launch_wait_selftest(unsigned *status, unsigned *done, void *stream);
 int mmb_launch_decode_probe(uint32_t *out_mma, uint32_t *out_f32, uint32_t *out_f16, void *stream);

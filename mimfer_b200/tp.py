@@ -11,7 +11,7 @@ mode="fused" removes the separate exchange: every rank's full output lives in
 symmetric memory, and the kernel's epilogue stores each finished tile into all
 ranks' copies through peer-mapped pointers (plain stores over NVLink, no
 multicast), so the transfer overlaps the remaining tiles; one cross-rank barrier
-on the stream closes the op.  The reference has no multi-GPU path; this is new
+kernel of this library (bounded wait) on the stream closes the op.  The reference has no multi-GPU path; this is new
 surface.
 """
 import ctypes as C
@@ -26,6 +26,35 @@ def shard_bounds(N, rank, world):
         raise ValueError(f"N={N} is not divisible by the tensor-parallel degree {world}")
     per = N // world
     return rank * per, (rank + 1) * per
+
+
+class TpBarrier:
+    """Cross-rank barrier on the runtime's compute stream (mm_f4_tp_barrier): a
+    64-byte flag block per rank in symmetric memory, one small kernel per call,
+    a bounded wait.  One instance per process group, shared by its linears."""
+
+    _by_group = {}
+
+    def __init__(self, rt, rank, world, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.rt, self.rank, self.world = rt, rank, world
+        g = group if group is not None else dist.group.WORLD
+        self.flags = symm_mem.empty((16,), dtype=torch.int32, device=rt.device)
+        self.flags.zero_()
+        self.hdl = symm_mem.rendezvous(self.flags, g)
+        self.ptrs = (C.c_void_p * world)(*[self.hdl.buffer_ptrs[r] for r in range(world)])
+        torch.cuda.synchronize()
+        dist.barrier(group=group)             # every block is zero before anyone signals
+
+    @classmethod
+    def get(cls, rt, rank, world, group=None):
+        key = id(group) if group is not None else 0
+        if key not in cls._by_group:
+            cls._by_group[key] = cls(rt, rank, world, group)
+        return cls._by_group[key]
+
+    def sync(self):
+        L.check(self.rt.lib.mm_f4_tp_barrier(self.ptrs, self.world, self.rank, None), "mm_f4_tp_barrier")
 
 
 class TpLinear:
@@ -75,23 +104,20 @@ class TpLinear:
         """Cross-rank barrier on the compute stream: after it, every rank's copy of
         every output written since the previous barrier is complete.  Needed once
         per group of fused forwards issued with barrier=False."""
-        if self.mode != "fused" or not self._symm:
+        if self.mode != "fused":
             return
-        hdl = next(iter(self._symm.values()))[1]
-        with torch.cuda.stream(self.rt.torch_stream()):
-            hdl.barrier(channel=0)
+        TpBarrier.get(self.rt, self.rank, self.world, self.group).sync()
 
     def _forward_fused(self, x, barrier=True):
         M = x.shape[0]
         y, hdl, ptrs = self._symm_buffers(M, x)
         n0 = self.rank * (self.N // self.world)
         w = self.shard
-        with torch.cuda.stream(self.rt.torch_stream()):
-            L.check(self.rt.lib.mm_f4_linear_tp(x.data_ptr(), w.dev_payload.data_ptr(),
-                                                w.dev_scales.data_ptr(), w.gs, ptrs, self.world,
-                                                self.N, n0, M, w.K, w.N, None), "mm_f4_linear_tp")
-            if barrier:
-                hdl.barrier(channel=0)          # every rank's stores have landed everywhere
+        L.check(self.rt.lib.mm_f4_linear_tp(x.data_ptr(), w.dev_payload.data_ptr(),
+                                            w.dev_scales.data_ptr(), w.gs, ptrs, self.world,
+                                            self.N, n0, M, w.K, w.N, None), "mm_f4_linear_tp")
+        if barrier:
+            self.barrier()                      # every rank's stores have landed everywhere
         return y
 
     def forward(self, x, barrier=True):
@@ -134,9 +160,10 @@ class TpStep:
     A decode step at tp=8 is a few tens of microseconds of kernel time per
     rank; issued op by op from Python, the launches and the barrier cost more
     than that on the host.  This captures `lins[i].forward(xs[i])` for every
-    i, plus the closing cross-rank barrier (fused mode) or the NCCL all-gathers
-    (gather mode), on the runtime's compute stream and replays them with one
-    launch.  The activations are read from the same device tensors `xs` on
+    i plus the closing cross-rank barrier on the runtime's compute stream and
+    replays them with one launch.  Fused mode only when there is more than one
+    rank (the kernels' peer stores and one barrier kernel; no NCCL call is
+    captured).  The activations are read from the same device tensors `xs` on
     every replay: refill them in place.  Outputs: `self.ys`, complete on every
     rank once the replay has finished."""
 
@@ -147,6 +174,9 @@ class TpStep:
         self.rt = lins[0].rt
         if self.rt is None:
             raise RuntimeError("TpStep needs the CUDA runtime")
+        if any(lin.world > 1 and lin.mode != "fused" for lin in lins):
+            raise NotImplementedError("TpStep captures fused-mode linears; gather mode issues its "
+                                      "NCCL all-gather op by op")
         self.stream = self.rt.torch_stream()
         self._issue()                         # eager once: buffers, symmetric-memory rendezvous
         self.rt.sync()

@@ -369,3 +369,27 @@ def test_bounded_wait_expires_and_device_stays_usable(rt, oracle):
     assert int(done.item()) == 1
     assert rt.device_status() == 0                       # the launcher cleared the word
     check(rt, oracle, 4, 512, 256, None, seed=3)         # the context is healthy
+
+
+def test_tp_barrier_signals_waits_and_gives_up(rt, oracle):
+    """mm_f4_tp_barrier on one GPU, both flag blocks local: with the peer's arrival already
+    written the kernel passes and leaves its own arrival in the peer's block; with no peer it
+    gives up after its limit, raises the timeout bit, and the device stays usable."""
+    import ctypes as C
+    torch = rt.torch
+    blocks = torch.zeros((2, 16), dtype=torch.int32, device=rt.device)
+    ptrs = (C.c_void_p * 2)(blocks[0].data_ptr(), blocks[1].data_ptr())
+    blocks[0, 1] = 1                                       # rank 1 "arrived" at epoch 1
+    torch.cuda.synchronize()
+    L.check(rt.lib.mm_f4_tp_barrier(ptrs, 2, 0, None), "mm_f4_tp_barrier")
+    rt.sync()
+    assert rt.device_status() == 0
+    got = blocks.cpu().numpy()
+    assert got[0, 0] == 1 and got[1, 0] == 1 and got[0, 8] == 1      # own slots and the epoch word
+    # epoch 2: nobody signals for rank 1
+    L.check(rt.lib.mm_f4_tp_barrier(ptrs, 2, 0, None), "mm_f4_tp_barrier")
+    rt.sync()
+    assert rt.device_status() == 1                         # MMB_DEV_TIMEOUT, cleared by the read
+    assert blocks.cpu().numpy()[1, 0] == 2
+    check(rt, oracle, 4, 512, 256, None, seed=3)           # the context is healthy
+    assert rt.lib.mm_f4_tp_barrier(ptrs, 9, 0, None) == L.MM_ERR_RANGE
