@@ -514,7 +514,8 @@ class Bench:
                         lin.forward(xs[n], barrier=False)
                     last.barrier()
                 ms_eager = ms = self.timed(step, st, warmup)
-                if mode == "fused" or self.world == 1:
+                captured = (mode == "fused" or self.world == 1) and M <= 32   # launch cost matters at decode sizes only
+                if captured:
                     # the same step captured once and replayed: one launch per step and rank
                     graph = TpStep(list(lins.values()), [xs[n] for n in lins])
                     ms = self.timed(graph.replay, st, warmup)
@@ -522,8 +523,8 @@ class Bench:
                 wb = sum(wbytes(*SHAPES[n]) for n in lins)
                 fl = sum(2.0 * M * SHAPES[n][0] * SHAPES[n][1] for n in lins)
                 res[tag] = {"ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "tflops": fl / ms / 1e9,
-                            "issue": "one CUDA graph per rank" if mode == "fused" or self.world == 1
-                                     else "op by op", "op_by_op_ms_per_step": ms_eager}
+                            "issue": "one CUDA graph per rank" if captured else "op by op",
+                            "op_by_op_ms_per_step": ms_eager}
                 for lin in lins.values():
                     lin._bufs.clear()
                     lin._symm.clear()
