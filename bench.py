@@ -211,7 +211,7 @@ class Bench:
         serial = self.engine(ops)
         ms_serial = self.timed(serial.launch, steps, warmup)
         serial.close()
-        eng = self.engine(ops, overlap=True)      # independent ops run ahead of their predecessors
+        eng = self.engine(ops, overlap=2)         # independent ops run ahead of their predecessors, on shallower K splits
         ms = self.timed(eng.launch, steps, warmup)
         res = {"ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "alg_gbs": ab / ms / 1e6,
                "ops": len(ops), "weight_bytes": wb, "alg_bytes_per_launch": ab / len(ops),
@@ -237,7 +237,7 @@ class Bench:
         sec_unbound = (time.perf_counter() - t0) / steps
         # the same step with the copies captured into the graph (bound pinned buffers)
         bound = self.mm.LinearEngine(self.rt, max_ops=len(ops) + 1)
-        bound.overlap(True)
+        bound.overlap(2)
         for x, w, y in ops:
             bound.add(x, w, y)
         bound.upload_group((len(ops) + 1) // 2)
@@ -301,7 +301,7 @@ class Bench:
         eng = self.engine(ops)
         ms_serial = self.timed(eng.launch, max(2, steps // 2), 3)
         eng.close()
-        eng = self.engine(ops, overlap=True)
+        eng = self.engine(ops, overlap=2)
         ms = self.timed(eng.launch, max(2, steps // 2), 3)
         ind = eng.n_independent()
         eng.close()
@@ -332,8 +332,8 @@ class Bench:
             layer_w.append(ws)
             wb += sum(wbytes(*SHAPES[n]) for n in lin) + 2 * wbytes(K, inter)
         res = {"layers": layers, "M": M, "weight_bytes": wb}
-        for fuse, overlap, tag in ((False, False, "as_emitted"), (True, False, "fused_mlp"),
-                                   (True, True, "fused_mlp_overlap")):
+        for fuse, overlap, tag in ((False, 0, "as_emitted"), (True, 0, "fused_mlp"),
+                                   (True, 2, "fused_mlp_overlap")):
             eng = self.mm.LinearEngine(self.rt, max_ops=8 * layers)
             eng.fuse_mlp(fuse)
             eng.overlap(overlap)

@@ -366,6 +366,11 @@ mm_status mm_lin_engine_fuse_mlp(mm_lin_engine *e, int on);
  * predecessor as before.  Results are identical; only ops served by the decode
  * kernel run ahead.  Needs a workspace of at least 16 MiB to let split-K ops
  * overlap (each of four regions serves one op in flight).  Off by default.
+ * on == 2 additionally lets an op that runs ahead take fewer, longer K slices
+ * than it would alone (it shares the SMs with its predecessors, so about half
+ * of them is its fair share): faster, still the same bits from run to run,
+ * but no longer the bits of the serial order, because the fp32 partial sums are
+ * cut at other places.
  * mm_lin_engine_n_independent: how many ops of the last dispatch or capture ran
  * ahead. */
 mm_status mm_lin_engine_overlap(mm_lin_engine *e, int on);

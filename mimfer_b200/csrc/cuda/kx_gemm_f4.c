@@ -38,6 +38,7 @@ static struct {
     int        pdl;
     int        next_pdl;         /* per-op override from the engine, -1 = none */
     int        next_region;
+    int        next_shallow;     /* the next op may take the shallower K split of a run-ahead op */
     unsigned long long launches;
     /* experiment knobs (mm_f4_tune keys 2..4), all 0 in production */
     uint32_t   st_rows, st_split, st_dbg;
@@ -59,15 +60,18 @@ static size_t ws_region_bytes(void)
     return G.ws ? (G.ws_bytes / (size_t)mmb_ws_regions()) & ~(size_t)255 : 0;
 }
 
-void mmb_next_op_context(int pdl_mode, int ws_region)
+void mmb_next_op_context(int pdl_mode, int ws_region, int shallow_split)
 {
     G.next_pdl = pdl_mode;
+    G.next_shallow = shallow_split && pdl_mode == MMB_PDL_INDEPENDENT;
     G.next_region = ws_region >= 0 && ws_region < mmb_ws_regions() ? ws_region : 0;
 }
 
 /* Consume the per-op context: launch mode and workspace base of this op. */
-static void take_op_context(int *pdl_out, void **ws_out)
+static void take_op_context(int *pdl_out, void **ws_out, int *shallow_out)
 {
+    *shallow_out = G.next_shallow;
+    G.next_shallow = 0;
     int mode = G.next_pdl >= 0 ? G.next_pdl : MMB_PDL_TRIGGER_FIRST;
     *pdl_out = G.pdl ? mode : MMB_PDL_OFF;
     *ws_out = G.ws ? (unsigned char *)G.ws + (size_t)G.next_region * ws_region_bytes() : NULL;
@@ -254,7 +258,7 @@ static uint32_t min_align(const void *a, const void *b, const void *c, const voi
 /* Plan of a linear op as the launcher runs it (shared with mmb_plan_for_op). */
 static mm_status plan_linear(const void *x, const void *payload, const void *scale, const void *y,
                              uint32_t n_dst, uint32_t ldy, uint32_t col0, uint32_t M, uint32_t K,
-                             uint32_t N, mm_f4_plan *plan)
+                             uint32_t N, int run_ahead, mm_f4_plan *plan)
 {
     mm_f4_shape sh = { M, K, N, (uint32_t)G.sm_count, min_align(x, payload, scale, y), ws_region_bytes() };
     if (n_dst && (col0 % 8u != 0 || ldy % 8u != 0))
@@ -264,7 +268,20 @@ static mm_status plan_linear(const void *x, const void *payload, const void *sca
     mm_status st = G.forced_variant >= 0 ? mm_f4_select_variant(&sh, G.forced_variant, plan)
                                          : mm_f4_select(&sh, plan);
     if (st == MM_OK && plan->variant == MM_F4_V_STREAM && (G.st_rows || G.st_split))
-        st = mmb_plan_stream_with(&sh, G.st_rows, G.st_split, plan);
+        return mmb_plan_stream_with(&sh, G.st_rows, G.st_split, plan);
+    /* An op that runs ahead of its predecessors shares the GPU with them: it is
+     * served best by fewer, longer K slices on about half of the SMs (less
+     * exchange, the fill paid once per more steps) - the other half is busy with
+     * the ops around it.  An op that has the GPU to itself keeps the deepest
+     * split.  Measured on B200, us per op, run-ahead / alone: down at M = 16 with
+     * 3 slices 17.0 / 31.9, with 7 slices 19.9 / 21.4; q with 3 slices 8.2 / 13.8,
+     * with 5 slices 9.9 / 12.9. */
+    if (st == MM_OK && run_ahead && plan->variant == MM_F4_V_STREAM && plan->split_k > 1) {
+        uint32_t s = (uint32_t)(0.45 * (double)sh.sm_count / (double)plan->grid_x + 0.5);
+        if (s < 1) s = 1;
+        if (s < plan->split_k)
+            st = mmb_plan_stream_with(&sh, plan->tile_n, s, plan);
+    }
     return st;
 }
 
@@ -283,11 +300,12 @@ static mm_status linear_impl(const void *x, const void *payload, const void *sca
     memset(&a, 0, sizeof a);
     a.x = x; a.payload = payload; a.scale = scale; a.y = y;
     a.gs = gs; a.M = M; a.K = K; a.N = N;
-    take_op_context(&a.pdl, &a.ws);
+    int shallow = 0;
+    take_op_context(&a.pdl, &a.ws, &shallow);
     for (uint32_t d = 0; d < n_dst; d++) a.y_dst[d] = y_dst[d];
     a.n_dst = n_dst; a.ldy = ldy; a.col0 = col0;
 
-    mm_status st = plan_linear(x, payload, scale, y, n_dst, ldy, col0, M, K, N, &a.plan);
+    mm_status st = plan_linear(x, payload, scale, y, n_dst, ldy, col0, M, K, N, shallow, &a.plan);
     if (st != MM_OK)
         return st;
 
@@ -398,7 +416,9 @@ mm_status mm_f4_mlp_gate_up(const void *x, const void *gate_payload, const void 
     a.gs = gs_gate; a.gs_up = gs_up;
     a.glu = 1; a.gate_plane = gate_first ? 0 : 1;
     a.M = M; a.K = K; a.N = inter;
-    take_op_context(&a.pdl, &a.ws);
+    int shallow = 0;
+    take_op_context(&a.pdl, &a.ws, &shallow);
+    (void)shallow;                         /* the gated pair keeps its split */
     mm_f4_shape sh = { M, K, inter, (uint32_t)G.sm_count, min_align(x, pay0, sc0, y), ws_region_bytes() };
     mm_status st = mm_f4_select_glu(&sh, &a.plan);
     if (st != MM_OK)
@@ -525,7 +545,7 @@ mm_status mmb_plan_for_op(const mm_op_desc *op, int glu, mm_f4_plan *out)
                            min_align(op->a, op->b, op->d, op->c), ws_region_bytes() };
         return mm_f4_select_glu(&sh, out);
     }
-    return plan_linear(op->a, op->b, op->d, op->c, 0, 0, 0, op->n0, op->n1, op->n2, out);
+    return plan_linear(op->a, op->b, op->d, op->c, 0, 0, 0, op->n0, op->n1, op->n2, 0, out);
 }
 
 mm_status mmb_op_mlp_gate_up(const mm_op_desc *op, const void *up_payload, const void *up_scale)

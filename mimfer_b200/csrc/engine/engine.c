@@ -160,7 +160,7 @@ mm_status mm_lin_engine_overlap(mm_lin_engine *e, int on)
 {
     MM_REQUIRE(e, MM_ERR_STATE);
     MM_REQUIRE(!e->captured, MM_ERR_BUSY);
-    e->overlap = on ? 1 : 0;
+    e->overlap = on < 0 ? 0 : (on > 2 ? 2 : on);
     return MM_OK;
 }
 
@@ -264,7 +264,8 @@ static mm_status run_ops(mm_lin_engine *e)
                 next_region = (region + 1) % n_regions;
             }
             e->n_independent += (uint32_t)independent;
-            mmb_next_op_context(independent ? MMB_PDL_INDEPENDENT : MMB_PDL_WAIT_FIRST, region);
+            mmb_next_op_context(independent ? MMB_PDL_INDEPENDENT : MMB_PDL_WAIT_FIRST, region,
+                                e->overlap > 1);
         }
         /* the first op of a group waits for the uploads of the whole group */
         if (with_copies && i % grp == 0)

@@ -268,7 +268,8 @@ class LinearEngine:
         L.check(self.rt.lib.mm_lin_engine_add(self.h, C.byref(d)), "mm_lin_engine_add")
 
     def overlap(self, on=True):
-        """Dependency-aware launch order (mm_lin_engine_overlap)."""
+        """Dependency-aware launch order (mm_lin_engine_overlap): 1 = bits of the serial
+        order, 2 = run-ahead ops may also take a shallower K split."""
         L.check(self.rt.lib.mm_lin_engine_overlap(self.h, int(on)), "mm_lin_engine_overlap")
 
     def n_independent(self):

@@ -99,3 +99,39 @@ def test_many_independent_split_ops_stay_correct(rt, oracle):
     for w, y in zip(ws, ys):
         assert row_rel_l2(rt.from_device_bf16(y), oracle.gemm_f4(xb, w.payload, w.scales, w.gs)) <= REL_L2_TOL
     eng.close()
+
+
+def test_run_ahead_ops_on_shallow_split(rt, oracle):
+    """Overlap level 2: ops that run ahead take fewer K slices.  Same answer within the
+    op's tolerance, the same bits on every replay, and the first op (which waits) keeps
+    the bits of the serial order."""
+    torch = rt.torch
+    M, K, N = 4, 17408, 2048                            # 8 row tiles: 17 slices alone, 8 when running ahead
+    ws = [mm.make_weight(N, K, seed=30 + i) for i in range(3)]
+    ds = [_dev(rt, w) for w in ws]
+    xb = mm.make_activations(M, K, seed=11)
+    x = rt.to_device_bf16(xb)
+    ys = [torch.zeros((M, N), dtype=torch.bfloat16, device=rt.device) for _ in ws]
+    runs = {}
+    for level in (1, 2):
+        eng = mm.LinearEngine(rt)
+        eng.overlap(level)
+        for d, y in zip(ds, ys):
+            eng.add(x, d, y)
+        eng.capture()
+        assert eng.n_independent() == 2
+        got = []
+        for rep in range(2):
+            for y in ys:
+                y.zero_()
+            eng.launch()
+            rt.sync()
+            assert rt.device_status() == 0
+            got.append([rt.from_device_bf16(y) for y in ys])
+        eng.close()
+        for a, b in zip(*got):
+            assert np.array_equal(a, b)                 # run to run
+        for w, y in zip(ws, got[0]):
+            assert row_rel_l2(y, oracle.gemm_f4(xb, w.payload, w.scales, w.gs)) <= REL_L2_TOL
+        runs[level] = got[0]
+    assert np.array_equal(runs[1][0], runs[2][0])       # the op that waits is planned as before
