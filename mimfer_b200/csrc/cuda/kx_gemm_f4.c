@@ -276,7 +276,8 @@ static mm_status plan_linear(const void *x, const void *payload, const void *sca
      * split.  Measured on B200, us per op, run-ahead / alone: down at M = 16 with
      * 3 slices 17.0 / 31.9, with 7 slices 19.9 / 21.4; q with 3 slices 8.2 / 13.8,
      * with 5 slices 9.9 / 12.9. */
-    if (st == MM_OK && run_ahead && plan->variant == MM_F4_V_STREAM && plan->split_k > 1) {
+    if (st == MM_OK && run_ahead && plan->variant == MM_F4_V_STREAM && plan->split_k > 1 &&
+        plan->grid_x <= 24) {              /* measured for 17 to 24 row tiles; a fused qkv (32) lost with 2 slices */
         uint32_t s = (uint32_t)(0.45 * (double)sh.sm_count / (double)plan->grid_x + 0.5);
         if (s < 1) s = 1;
         if (s < plan->split_k)
