@@ -215,7 +215,7 @@ mm_status mm_f4_linear_tp(const void *x, const void *payload, const void *scale,
  * before the first barrier, indexed by rank.  After the kernel, every store any
  * rank issued on its stream before its own call of the same barrier is visible
  * here.  No argument changes between calls, so the call can be captured into a
- * graph.  A peer that does not arrive within about a second makes the wait give
+ * graph.  A peer that does not arrive within about two seconds makes the wait give
  * up with MMB_DEV_TIMEOUT in the device status word (mm_f4_device_status,
  * MM_ERR_TIMEOUT from the synchronising calls) instead of hanging the GPU. */
 mm_status mm_f4_tp_barrier(void *const *flags_all, uint32_t n_ranks, uint32_t rank, void *stream);

@@ -12,10 +12,12 @@
  * is already one barrier ahead does no harm, and the kernel takes no argument
  * that changes between launches: it can sit in a captured graph.
  *
- * The wait is bounded like every other wait of this library: after about one
- * second it raises MMB_DEV_TIMEOUT in the status word and returns, so a rank
- * that never arrives costs its peers a second and an error code, not a hung
- * GPU.  The reference is single-GPU and has no counterpart.
+ * The wait is bounded like every other wait of this library: after about two
+ * seconds it raises MMB_DEV_TIMEOUT in the status word and returns, so a rank
+ * that never arrives costs its peers two seconds and an error code, not a hung
+ * GPU.  Ranks must therefore reach a barrier within that time of each other:
+ * meet on the host first wherever set-up work (loading weights, capturing a
+ * graph) can take longer on one rank than on another.  The reference is single-GPU and has no counterpart.
  */
 #include "ptx.cuh"
 
@@ -48,7 +50,7 @@ __global__ void __launch_bounds__(32, 1) tp_barrier_kernel(const TpBarrierParams
             if ((spin & 63u) == 0) {
                 if (*reinterpret_cast<volatile unsigned *>(p.status) & MMB_DEV_TIMEOUT)
                     break;
-                if (globaltimer_ns() - t0 > 1000000000ull) {
+                if (globaltimer_ns() - t0 > 2000000000ull) {      /* ranks drift more than pipeline stages do */
                     atomicOr(p.status, MMB_DEV_TIMEOUT);
                     break;
                 }

@@ -186,6 +186,9 @@ class TpStep:
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph, stream=self.stream, capture_error_mode="thread_local"):
             self.ys = self._issue()
+        if dist.is_initialized() and lins[0].world > 1:
+            dist.barrier(group=lins[0].group)     # the barrier kernel's wait is bounded: replay together
+        torch.cuda.synchronize()
 
     def _issue(self):
         ys = [lin.forward(x, barrier=False) for lin, x in zip(self.lins, self.xs)]

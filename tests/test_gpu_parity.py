@@ -374,7 +374,7 @@ def test_bounded_wait_expires_and_device_stays_usable(rt, oracle):
 def test_tp_barrier_signals_waits_and_gives_up(rt, oracle):
     """mm_f4_tp_barrier on one GPU, both flag blocks local: with the peer's arrival already
     written the kernel passes and leaves its own arrival in the peer's block; with no peer it
-    gives up after its limit, raises the timeout bit, and the device stays usable."""
+    gives up after its limit (about two seconds), raises the timeout bit, and the device stays usable."""
     import ctypes as C
     torch = rt.torch
     blocks = torch.zeros((2, 16), dtype=torch.int32, device=rt.device)
