@@ -140,7 +140,7 @@ typedef struct mm_f4_shape {
 
 typedef struct mm_f4_plan {
     int      variant;         /* mm_f4_variant                                */
-    uint32_t m_tiles;         /* STREAM: 8-row activation tiles (1, 2 or 4)   */
+    uint32_t m_tiles;         /* STREAM: 8-row activation tiles (1 to 4)      */
     uint32_t tile_m, tile_n;  /* UMMA: CTA tile; STREAM/STREAMT: tile_n = W   */
                               /*   rows per CTA, tile_m = padded activation rows */
     uint32_t split_k;         /* >= 1                                         */

@@ -606,12 +606,14 @@ static int launch_mt(const mmb_args *a, unsigned *status, cudaStream_t st)
 
 extern "C" int mmb_stream_init(void)
 {
-    const void *kernels[6] = {
+    const void *kernels[8] = {
         reinterpret_cast<const void *>(mmb::f4_stream_kernel<1, false>),
         reinterpret_cast<const void *>(mmb::f4_stream_kernel<2, false>),
+        reinterpret_cast<const void *>(mmb::f4_stream_kernel<3, false>),
         reinterpret_cast<const void *>(mmb::f4_stream_kernel<4, false>),
         reinterpret_cast<const void *>(mmb::f4_stream_kernel<1, true>),
         reinterpret_cast<const void *>(mmb::f4_stream_kernel<2, true>),
+        reinterpret_cast<const void *>(mmb::f4_stream_kernel<3, true>),
         reinterpret_cast<const void *>(mmb::f4_stream_kernel<4, true>),
     };
     for (const void *k : kernels) {
@@ -637,6 +639,7 @@ extern "C" int mmb_launch_stream(const mmb_args *a, void *stream)
     switch (a->plan.m_tiles) {
     case 1: return a->glu ? mmb::launch_mt<1, true>(a, status, st) : mmb::launch_mt<1, false>(a, status, st);
     case 2: return a->glu ? mmb::launch_mt<2, true>(a, status, st) : mmb::launch_mt<2, false>(a, status, st);
+    case 3: return a->glu ? mmb::launch_mt<3, true>(a, status, st) : mmb::launch_mt<3, false>(a, status, st);
     case 4: return a->glu ? mmb::launch_mt<4, true>(a, status, st) : mmb::launch_mt<4, false>(a, status, st);
     default: return static_cast<int>(cudaErrorInvalidValue);
     }

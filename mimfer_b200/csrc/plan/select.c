@@ -52,7 +52,7 @@ static mm_status plan_stream_with(const mm_f4_shape *s, uint32_t rows, uint32_t 
         return MM_ERR_RANGE;
     memset(p, 0, sizeof *p);
     p->variant = MM_F4_V_STREAM;
-    p->m_tiles = s->M <= 8 ? 1 : (s->M <= 16 ? 2 : 4);
+    p->m_tiles = (s->M + 7u) / 8u;                /* 8-row activation tiles: 1..4 */
     p->tile_n = rows;
     p->tile_m = p->m_tiles * 8;
     p->k_steps = s->K / MMB_ST_KSTEP;

@@ -13,7 +13,7 @@ def test_decode_shapes_use_stream_and_fill_the_gpu(lib):
         for (K, N) in ((5120, 34816), (17408, 5120), (5120, 5120)):
             p = mm.select_plan(M, K, N, ws_bytes=WS)
             assert p.variant == V_STREAM
-            assert p.m_tiles * 8 >= M and p.m_tiles in (1, 2, 4)
+            assert p.m_tiles == -(-M // 8)
             assert p.k_steps == K // 256 and p.tile_n == 256 and p.grid_x == -(-N // 256)
             assert 100 <= p.grid_x * p.grid_y <= 148
             assert p.smem_bytes <= SMEM_MAX and p.stages >= 2
