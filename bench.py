@@ -264,8 +264,8 @@ class Bench:
         return {"value": wb / sec / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": sec * 1e3,
                 "call": "mm_lin_engine_step_bound: one graph replay that uploads every op's activations "
-                        "from pinned host memory on the transfer stream, runs the ten ops and downloads "
-                        "every output to pinned host memory; one sync",
+                        "from pinned host memory on the transfer stream (one gather kernel per five ops), "
+                        "runs the ten ops and downloads every output to pinned host memory; one sync",
                 "copies_outside_graph": {"value": wb / sec_unbound / 1e9, "ms_per_step": sec_unbound * 1e3,
                                          "call": "mm_lin_engine_launch_host"},
                 "per_op_sync": {"value": wb / sec_op / 1e9, "ms_per_step": sec_op * 1e3,

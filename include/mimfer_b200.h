@@ -407,10 +407,17 @@ mm_status mm_lin_engine_step_bound(mm_lin_engine *e);
  * several microseconds whatever its size and a cross-stream dependency a few
  * more per kernel, so a list of short ops does better with larger groups: the
  * first op of a group waits for the uploads of the whole group, the others for
- * nothing (measured on the ten-op decode sweep: 0.298 ms per step with groups
- * of 1, 0.276 ms with groups of 5, 0.304 ms with one group of 10; the kernels
- * alone take 0.209 ms).  Before capture. */
+ * nothing (measured on the ten-op decode sweep, copy nodes / upload kernel:
+ * 0.325 / 0.290 ms per step with groups of 1, 0.261 / 0.225 ms with groups of 5,
+ * 0.290 / 0.253 ms with one group of 10; the kernels alone take 0.191 ms).
+ * Before capture. */
 mm_status mm_lin_engine_upload_group(mm_lin_engine *e, uint32_t ops_per_event);
+/* on != 0 (default): the uploads of a group go up as ONE kernel that reads the
+ * pinned host buffers over PCIe (they must be mapped for the device, which
+ * cudaHostAlloc memory is, and 16-byte aligned; other buffers and groups of
+ * more than 32 buffers fall back to copy nodes).  on == 0: always copy nodes.
+ * Before capture. */
+mm_status mm_lin_engine_upload_kernel(mm_lin_engine *e, int on);
 void      mm_lin_engine_destroy(mm_lin_engine *e);
 
 #ifdef __cplusplus

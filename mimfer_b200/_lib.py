@@ -146,6 +146,7 @@ SIGNATURES = {
     "mm_lin_engine_bind_host": (C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
     "mm_lin_engine_step_bound": (C.c_int, [_vp]),
     "mm_lin_engine_upload_group": (C.c_int, [_vp, _u32]),
+    "mm_lin_engine_upload_kernel": (C.c_int, [_vp, C.c_int]),
     "mm_event_record": (C.c_int, [C.c_int, C.c_int]),
     "mm_event_wait": (C.c_int, [C.c_int, C.c_int]),
     "mm_lin_engine_destroy": (None, [_vp]),

@@ -36,6 +36,7 @@ struct mm_lin_engine {
     void       **y_bound;           /* [max_ops] pinned host destination of op i's output, or NULL  */
     int          bound, bound_captured;
     uint32_t     upload_group;      /* ops whose uploads share one event (>= 1) */
+    int          upload_kernel;     /* uploads of a group as one kernel instead of copy nodes */
 };
 
 mm_status mm_lin_engine_create(mm_lin_engine **out, uint32_t max_ops)
@@ -60,6 +61,7 @@ mm_status mm_lin_engine_create(mm_lin_engine **out, uint32_t max_ops)
     }
     e->max_ops = max_ops;
     e->upload_group = 1;
+    e->upload_kernel = 1;
     *out = e;
     return MM_OK;
 }
@@ -69,6 +71,14 @@ mm_status mm_lin_engine_upload_group(mm_lin_engine *e, uint32_t ops_per_event)
     MM_REQUIRE(e && ops_per_event >= 1, MM_ERR_STATE);
     MM_REQUIRE(!e->captured, MM_ERR_BUSY);
     e->upload_group = ops_per_event;
+    return MM_OK;
+}
+
+mm_status mm_lin_engine_upload_kernel(mm_lin_engine *e, int on)
+{
+    MM_REQUIRE(e, MM_ERR_STATE);
+    MM_REQUIRE(!e->captured, MM_ERR_BUSY);
+    e->upload_kernel = on ? 1 : 0;
     return MM_OK;
 }
 
@@ -223,13 +233,42 @@ static mm_status run_ops(mm_lin_engine *e)
         MM_CHECK(mmb_event_pool_reserve((int)(e->n_ops / grp) + 1 + EV_OP0));
         MM_CHECK(mm_event_record(EV_FORK, MM_ST_COMPUTE));
         MM_CHECK(mm_event_wait(EV_FORK, MM_ST_XFER));
+        /* a group's uploads go up as one kernel that reads the pinned buffers over
+         * PCIe (kernels/host_gather.cu); buffers it cannot take, and groups larger
+         * than one launch holds, use copy nodes */
+        const void *src[MMB_GATHER_MAX];
+        void *dst[MMB_GATHER_MAX];
+        size_t len[MMB_GATHER_MAX];
+        uint32_t pending = 0, first = 0;
         for (uint32_t i = 0; i < e->n_ops; i++) {
             const mm_op_desc *op = &e->ops[i];
-            if (e->x_bound[i] && op->op != OP_NOP)
-                MM_CHECK(mm_h2d_async((void *)(uintptr_t)op->a, e->x_bound[i], op_in_bytes(op), MM_ST_XFER));
+            if (e->x_bound[i] && op->op != OP_NOP) {
+                if (pending == 0)
+                    first = i;
+                if (pending < MMB_GATHER_MAX) {
+                    src[pending] = e->x_bound[i];
+                    dst[pending] = (void *)(uintptr_t)op->a;
+                    len[pending] = op_in_bytes(op);
+                }
+                pending++;
+            }
             /* one event per group of ops, after the group's last upload */
-            if (i % grp == grp - 1 || i + 1 == e->n_ops)
+            if (i % grp == grp - 1 || i + 1 == e->n_ops) {
+                int rc = pending && pending <= MMB_GATHER_MAX && e->upload_kernel
+                             ? mmb_launch_host_gather(src, dst, len, pending, mm_cuda_stream_raw(MM_ST_XFER))
+                             : -1;
+                if (rc > 0) {
+                    MM_LOGE("engine: upload kernel launch failed (cuda error %d)", rc);
+                    return MM_ERR_CUDA;
+                }
+                if (rc < 0)
+                    for (uint32_t j = first; pending && j <= i; j++)
+                        if (e->x_bound[j] && e->ops[j].op != OP_NOP)
+                            MM_CHECK(mm_h2d_async((void *)(uintptr_t)e->ops[j].a, e->x_bound[j],
+                                                  op_in_bytes(&e->ops[j]), MM_ST_XFER));
+                pending = 0;
                 MM_CHECK(mm_event_record(EV_OP0 + (int)(i / grp), MM_ST_XFER));
+            }
         }
     }
     mm_kcall kc;

@@ -7,6 +7,7 @@
 #ifndef MMB_LAUNCH_H
 #define MMB_LAUNCH_H
 
+#include <stddef.h>
 #include "mimfer_b200.h"
 
 #ifdef __cplusplus
@@ -130,6 +131,10 @@ int mmb_launch_rowwarp(const mmb_args *a, void *stream);
 int mmb_launch_stream(const mmb_args *a, void *stream);
 int mmb_launch_umma(const mmb_args *a, void *stream);
 int mmb_launch_streamt(const mmb_args *a, void *stream);
+/* Buffers one launch of the upload kernel takes (host_gather.cu). */
+#define MMB_GATHER_MAX 32u
+int mmb_launch_host_gather(const void *const *src_host, void *const *dst_dev, const size_t *bytes,
+                           uint32_t n, void *stream);
 int mmb_launch_tp_barrier(unsigned *const *flags, uint32_t n_ranks, uint32_t rank, void *stream);
 int mmb_launch_silu_mul(const void *gate, const void *up, void *y, size_t n, void *stream);
 int mmb_launch_wait_selftest(unsigned *status, unsigned *done, void *stream);

@@ -304,6 +304,9 @@ class LinearEngine:
     def upload_group(self, ops_per_event):
         L.check(self.rt.lib.mm_lin_engine_upload_group(self.h, ops_per_event), "mm_lin_engine_upload_group")
 
+    def upload_kernel(self, on=True):
+        L.check(self.rt.lib.mm_lin_engine_upload_kernel(self.h, int(on)), "mm_lin_engine_upload_kernel")
+
     def step_bound(self):
         """Replay the graph captured with bound host buffers; synchronises."""
         L.check(self.rt.lib.mm_lin_engine_step_bound(self.h), "mm_lin_engine_step_bound")

@@ -307,8 +307,9 @@ def test_engine_host_step(rt, oracle):
     eng.close()
 
 
+@pytest.mark.parametrize("upload_kernel", [True, False])
 @pytest.mark.parametrize("overlap", [False, True])
-def test_engine_bound_host_step(rt, oracle, overlap):
+def test_engine_bound_host_step(rt, oracle, overlap, upload_kernel):
     """mm_lin_engine_bind_host + mm_lin_engine_step_bound: the uploads and downloads are nodes
     of the captured graph; refilling the same pinned buffers changes the next step's result."""
     torch = rt.torch
@@ -322,6 +323,8 @@ def test_engine_bound_host_step(rt, oracle, overlap):
     eng.overlap(overlap)
     for x, w, y in zip(xd, ws, yd):
         eng.add(x, w, y)
+    eng.upload_kernel(upload_kernel)                        # one gather kernel per group, or copy nodes
+    eng.upload_group(3)
     eng.bind_host(xh, [yh[0], yh[1], None, yh[3]])          # None: output stays on the device
     eng.capture()
     with pytest.raises(mm.MimferError):                     # that graph already carries the copies
