@@ -110,6 +110,8 @@ void mm_log_set_level(int level);
  * Unregistered weights use 1.0f, which is bit-for-bit the reference maths. */
 mm_status mm_f4_gscale_set(const void *scale_base, float gs);
 float     mm_f4_gscale_get(const void *scale_base);
+void      mm_f4_gscale_unset(const void *scale_base);   /* back to 1.0f; unknown keys are ignored */
+uint32_t  mm_f4_gscale_room(void);                      /* registrations the table still takes  */
 void      mm_f4_gscale_clear(void);
 
 /* ---- split-K workspace ---------------------------------------------------

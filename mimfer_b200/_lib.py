@@ -94,6 +94,8 @@ SIGNATURES = {
     "mm_status_str": (C.c_char_p, [C.c_int]),
     "mm_f4_gscale_set": (C.c_int, [_vp, _f]),
     "mm_f4_gscale_get": (_f, [_vp]),
+    "mm_f4_gscale_unset": (None, [_vp]),
+    "mm_f4_gscale_room": (C.c_uint32, []),
     "mm_f4_gscale_clear": (None, []),
     "mm_f4_workspace_set": (C.c_int, [_vp, _sz]),
     "mm_f4_workspace_bytes": (_sz, []),

@@ -52,6 +52,8 @@ void mmb_next_op_context(int pdl_mode, int ws_region, int shallow_split);
 /* Regions the workspace is cut into, so that ops in flight together never share
  * scratch (1 when the workspace is too small to divide). */
 int mmb_ws_regions(void);
+/* Drop the launcher's per-device state (runtime shutdown or re-initialisation). */
+void mmb_launcher_reset(void);
 /* Grow the runtime shim's event pool (mm_event_record / mm_event_wait indices)
  * to at least n events; set-up time only. */
 mm_status mmb_event_pool_reserve(int n);

@@ -28,6 +28,7 @@ typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, vo
 
 static struct {
     int        ready;
+    void      *ready_stream;     /* compute stream the set-up below was made for */
     int        sm_count;
     encode_fn  encode;
     unsigned  *status_dev;
@@ -79,10 +80,12 @@ static void take_op_context(int *pdl_out, void **ws_out, int *shallow_out)
     G.next_region = 0;
 }
 
-/* global-scale registry: open addressing on the scale base pointer */
-#define GS_SLOTS 4096u
+/* global-scale registry: open addressing on the scale base pointer, with
+ * tombstones so that an entry can be taken back (a failed staging run) */
+#define GS_SLOTS 8192u                   /* more than the weights loader admits tensors (4096) */
+#define GS_TOMB  ((const void *)(uintptr_t)1)
 static struct { const void *key; float gs; } g_gs[GS_SLOTS];
-static unsigned g_gs_used;
+static unsigned g_gs_used;               /* live entries + tombstones */
 
 static unsigned gs_hash(const void *p)
 {
@@ -93,18 +96,27 @@ static unsigned gs_hash(const void *p)
 
 mm_status mm_f4_gscale_set(const void *scale_base, float gs)
 {
-    MM_REQUIRE(scale_base, MM_ERR_STATE);
+    MM_REQUIRE(scale_base && scale_base != GS_TOMB, MM_ERR_STATE);
     MM_REQUIRE(gs == gs && gs > 0.0f && gs < 3.0e38f, MM_ERR_RANGE);
     unsigned h = gs_hash(scale_base);
+    int free_at = -1;
     for (unsigned i = 0; i < GS_SLOTS; i++, h = (h + 1u) & (GS_SLOTS - 1u)) {
         if (g_gs[h].key == scale_base) { g_gs[h].gs = gs; return MM_OK; }
+        if (g_gs[h].key == GS_TOMB) { if (free_at < 0) free_at = (int)h; continue; }
         if (!g_gs[h].key) {
-            if (g_gs_used + 1u >= GS_SLOTS) return MM_ERR_CAPACITY;
-            g_gs[h].key = scale_base; g_gs[h].gs = gs; g_gs_used++;
-            return MM_OK;
+            if (free_at < 0) {
+                if (g_gs_used + 1u >= GS_SLOTS) return MM_ERR_CAPACITY;
+                free_at = (int)h;
+                g_gs_used++;
+            }
+            break;
         }
     }
-    return MM_ERR_CAPACITY;
+    if (free_at < 0)
+        return MM_ERR_CAPACITY;
+    g_gs[free_at].key = scale_base;
+    g_gs[free_at].gs = gs;
+    return MM_OK;
 }
 
 float mm_f4_gscale_get(const void *scale_base)
@@ -115,6 +127,22 @@ float mm_f4_gscale_get(const void *scale_base)
         if (!g_gs[h].key) break;
     }
     return 1.0f;
+}
+
+void mm_f4_gscale_unset(const void *scale_base)
+{
+    if (!scale_base || scale_base == GS_TOMB)
+        return;
+    unsigned h = gs_hash(scale_base);
+    for (unsigned i = 0; i < GS_SLOTS; i++, h = (h + 1u) & (GS_SLOTS - 1u)) {
+        if (g_gs[h].key == scale_base) { g_gs[h].key = GS_TOMB; return; }
+        if (!g_gs[h].key) return;
+    }
+}
+
+uint32_t mm_f4_gscale_room(void)
+{
+    return GS_SLOTS - 1u - g_gs_used;
 }
 
 void mm_f4_gscale_clear(void)
@@ -155,11 +183,35 @@ unsigned long long mm_f4_launch_count(int reset)
         }                                                                     \
     } while (0)
 
+/* Forget everything that belongs to the device the runtime was initialised on:
+ * status word, workspace, per-device kernel attributes.  Called by the runtime
+ * shim's mm_cuda_shutdown, and by ensure_ready when it finds the runtime on
+ * another compute stream than the one it prepared for (a shutdown followed by
+ * a new mm_cuda_init, possibly on another device, in a runtime that is not the
+ * shim). */
+void mmb_launcher_reset(void)
+{
+    if (G.status_host)
+        cudaFreeHost(G.status_host);
+    G.status_host = NULL;
+    G.status_dev = NULL;
+    G.ws = NULL;
+    G.ws_bytes = 0;
+    G.ready = 0;
+    G.ready_stream = NULL;
+    G.next_pdl = -1;
+    G.next_region = 0;
+    G.next_shallow = 0;
+}
+
 static mm_status ensure_ready(void)
 {
-    if (G.ready)
+    void *cs = mm_cuda_stream_raw(MM_ST_COMPUTE);
+    if (G.ready && cs == G.ready_stream)
         return MM_OK;
-    MM_REQUIRE(mm_cuda_stream_raw(MM_ST_COMPUTE) != NULL, MM_ERR_STATE);   /* mm_cuda_init first */
+    if (G.ready)
+        mmb_launcher_reset();
+    MM_REQUIRE(cs != NULL, MM_ERR_STATE);   /* mm_cuda_init first */
     int dev = 0;
     CK(cudaGetDevice(&dev));
     CK(cudaDeviceGetAttribute(&G.sm_count, cudaDevAttrMultiProcessorCount, dev));
@@ -177,8 +229,9 @@ static mm_status ensure_ready(void)
     CK((cudaError_t)mmb_status_word(&G.status_dev));
     CK(cudaHostAlloc((void **)&G.status_host, 64, cudaHostAllocDefault));
     *G.status_host = 0;
-    CK(cudaMemsetAsync(G.status_dev, 0, sizeof(unsigned), (cudaStream_t)mm_cuda_stream_raw(MM_ST_COMPUTE)));
+    CK(cudaMemsetAsync(G.status_dev, 0, sizeof(unsigned), (cudaStream_t)cs));
     G.ready = 1;
+    G.ready_stream = cs;
     return MM_OK;
 }
 
@@ -261,10 +314,10 @@ static mm_status plan_linear(const void *x, const void *payload, const void *sca
                              uint32_t N, int run_ahead, mm_f4_plan *plan)
 {
     mm_f4_shape sh = { M, K, N, (uint32_t)G.sm_count, min_align(x, payload, scale, y), ws_region_bytes() };
+    if (sh.ptr_align < 16)
+        return MM_ERR_SHAPE;               /* arena slots are >= 16-byte aligned; every kernel loads 16-byte vectors */
     if (n_dst && (col0 % 8u != 0 || ldy % 8u != 0))
-        sh.ptr_align = 8;                  /* 16-byte output vectors need aligned slices */
-    if (sh.ptr_align < 16 && !n_dst)
-        return MM_ERR_SHAPE;               /* arena slots are >= 16-byte aligned */
+        sh.ptr_align = 8;                  /* aligned operands, unaligned output slice: the row-warp kernel */
     mm_status st = G.forced_variant >= 0 ? mm_f4_select_variant(&sh, G.forced_variant, plan)
                                          : mm_f4_select(&sh, plan);
     if (st == MM_OK && plan->variant == MM_F4_V_STREAM && (G.st_rows || G.st_split))
@@ -293,6 +346,8 @@ static mm_status linear_impl(const void *x, const void *payload, const void *sca
     MM_REQUIRE(x && payload && scale && y, MM_ERR_STATE);
     if (M == 0 || N == 0 || K == 0 || K % 16 != 0)
         return MM_ERR_SHAPE;               /* e4m3 group scale spans 16 columns */
+    if (min_align(x, payload, scale, y) < 16)
+        return MM_ERR_SHAPE;               /* refused before anything is launched, in every form of the op */
     MM_CHECK(ensure_ready());
     if (!stream)
         stream = mm_cuda_stream_raw(MM_ST_COMPUTE);

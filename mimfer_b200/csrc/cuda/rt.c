@@ -112,6 +112,7 @@ mm_status mm_cuda_shutdown(void)
     g_n_events = 0;
     cudaStreamDestroy(g_stream[MM_ST_COMPUTE]);
     cudaStreamDestroy(g_stream[MM_ST_XFER]);
+    mmb_launcher_reset();       /* status word, workspace and kernel attributes belong to this device */
     g_ready = 0;
     g_device = -1;
     return MM_OK;

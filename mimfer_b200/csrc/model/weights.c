@@ -206,8 +206,35 @@ mm_status mm_f4_weights_stage(const uint8_t *data, size_t len, void *arena_dev, 
                 st = MM_ERR_CORRUPT;
                 goto fail;
             }
+    /* Everything that can be refused is refused before the first copy or
+     * registration (the reference loader's "no partial state" gate,
+     * src/model/tensor_registry.c:372-560): global scales and the room left in
+     * the scale registry. */
+    uint32_t n_fp4 = 0;
+    for (uint32_t i = 0; i < n; i++) {
+        const mm_f4_went *e = &ents[i];
+        if (e->dtype != MM_DT_FP4E2M1)
+            continue;
+        size_t pb = (size_t)e->rows * e->cols / 2u, sb = (size_t)e->rows * e->cols / 16u;
+        uint32_t bits = rd32(data + e->off + pb + sb);
+        float gs;
+        memcpy(&gs, &bits, 4);
+        if (!(gs > 0.0f && gs < 3.0e38f)) {
+            MM_LOGE("weights: \"%s\": global scale %g is not a positive finite number", e->name, (double)gs);
+            st = MM_ERR_CORRUPT;
+            goto fail;
+        }
+        n_fp4++;
+    }
+    if (n_fp4 > mm_f4_gscale_room()) {
+        MM_LOGE("weights: %u NVFP4 tensors, the global-scale registry has room for %u", n_fp4,
+                mm_f4_gscale_room());
+        st = MM_ERR_CAPACITY;
+        goto fail;
+    }
     uint8_t *base = (uint8_t *)arena_dev;
     size_t at = 0;
+    uint32_t done = 0;                      /* tensors whose scale is registered */
     for (uint32_t i = 0; i < n; i++) {
         const mm_f4_went *e = &ents[i];
         wt_view *v = &views[i];
@@ -221,33 +248,28 @@ mm_status mm_f4_weights_stage(const uint8_t *data, size_t len, void *arena_dev, 
             at += slot(pb) + slot(sb);
             if ((st = mm_h2d_async(pay, src, pb, MM_ST_XFER)) != MM_OK ||
                 (st = mm_h2d_async(scl, src + pb, sb, MM_ST_XFER)) != MM_OK)
-                goto fail;
+                goto unwind;
             uint32_t bits = rd32(src + pb + sb);
             memcpy(&v->gs, &bits, 4);
-            if (!(v->gs > 0.0f && v->gs < 3.0e38f)) {
-                MM_LOGE("weights: \"%s\": global scale %g is not a positive finite number", e->name,
-                        (double)v->gs);
-                st = MM_ERR_CORRUPT;
-                goto fail;
-            }
             v->is_fp4 = 1;
             v->w.data = pay;
             v->w.scale = scl;
             v->w.rows = e->rows;
             v->w.cols = e->cols;
             if ((st = mm_f4_gscale_set(scl, v->gs)) != MM_OK)
-                goto fail;
+                goto unwind;
         } else {
             uint8_t *dst = base + at;
             at += slot((size_t)e->nbytes);
             if ((st = mm_h2d_async(dst, src, (size_t)e->nbytes, MM_ST_XFER)) != MM_OK)
-                goto fail;
+                goto unwind;
             v->data = dst;
             v->bytes = (size_t)e->nbytes;
         }
+        done = i + 1;
     }
     if ((st = mm_stream_sync(MM_ST_XFER)) != MM_OK)
-        goto fail;
+        goto unwind;
     reg->v = views;
     reg->n = n;
     reg->used = at;
@@ -255,6 +277,15 @@ mm_status mm_f4_weights_stage(const uint8_t *data, size_t len, void *arena_dev, 
     MM_LOGI("weights: staged %u tensors (%zu bytes of the arena)", n, at);
     *out = reg;
     return MM_OK;
+unwind:
+    /* copies from `data` may still be in flight and some scales are registered
+     * under arena addresses the caller will reuse: wait, then take them back */
+    (void)mm_stream_sync(MM_ST_XFER);
+    for (uint32_t i = 0; i < done && i < n; i++)
+        if (views[i].is_fp4)
+            mm_f4_gscale_unset(views[i].w.scale);
+    if (done < n && views[done].is_fp4 && views[done].w.scale)
+        mm_f4_gscale_unset(views[done].w.scale);
 fail:
     free(ents);
     free(views);

@@ -159,3 +159,32 @@ def test_engine_mlp_fusion_is_a_host_decision(lib):
     lib.mm_log_set_level(1)
     assert lib.mm_lin_engine_n_ops(h) == 1
     lib.mm_lin_engine_destroy(h)
+
+
+def test_misaligned_operands_are_refused_before_any_launch(lib):
+    """Every form of the op needs 16-byte aligned x, payload, scales and output (all
+    kernels load 16-byte vectors): a sliced activation view two bytes off is
+    MM_ERR_SHAPE, on the tensor-parallel entry point too, and nothing is launched."""
+    lib.mm_log_set_level(-1)
+    before = lib.mm_f4_launch_count(0)
+    ptrs = (C.c_void_p * 2)(0x1000, 0x2000)
+    assert lib.mm_f4_linear_tp(0x10002, 0x20000, 0x30000, 1.0, ptrs, 2, 512, 0, 1, 256, 256, None) == L.MM_ERR_SHAPE
+    assert lib.mm_f4_linear_tp(0x10000, 0x20008, 0x30000, 1.0, ptrs, 2, 512, 0, 1, 256, 256, None) == L.MM_ERR_SHAPE
+    assert lib.mm_f4_linear_tp(0x10000, 0x20000, 0x30004, 1.0, ptrs, 2, 512, 0, 1, 256, 256, None) == L.MM_ERR_SHAPE
+    assert lib.mm_f4_linear(0x10002, 0x20000, 0x30000, 1.0, 0x40000, 1, 256, 256, None) == L.MM_ERR_SHAPE
+    assert lib.mm_f4_launch_count(0) == before
+    lib.mm_log_set_level(1)
+
+
+def test_global_scale_entries_can_be_taken_back(lib):
+    lib.mm_f4_gscale_clear()
+    room = lib.mm_f4_gscale_room()
+    assert room >= 4096                      # at least one registration per tensor the loader admits
+    for i in range(1, 50):
+        assert lib.mm_f4_gscale_set(0x2000 * i, 2.0 * i) == L.MM_OK
+    lib.mm_f4_gscale_unset(0x2000 * 7)
+    assert lib.mm_f4_gscale_get(0x2000 * 7) == 1.0
+    assert lib.mm_f4_gscale_get(0x2000 * 8) == 16.0      # probing runs past the emptied slot
+    assert lib.mm_f4_gscale_set(0x2000 * 7, 5.0) == L.MM_OK and lib.mm_f4_gscale_get(0x2000 * 7) == 5.0
+    assert lib.mm_f4_gscale_room() == room - 49
+    lib.mm_f4_gscale_clear()
