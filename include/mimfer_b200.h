@@ -57,8 +57,18 @@ mm_status kx_op_lmhead(const mm_kcall *kc);
  * as the unfused form of mm_f4_mlp_gate_up. */
 mm_status kx_op_silu_mul(const mm_kcall *kc);
 
+/* Replaces kx_op_add_rmsnorm in src/kernels/cuda/cx.cu:223-260 (CPU twin
+ * src/kernels/cpu/cx.c:132-150): a[m][i] = bf16(a[m][i] + b[m][i]) in place, then
+ * c[m][i] = bf16(a[m][i] * inv * d[i]) with inv = 1 / sqrt(mean(a[m]^2) + eps) over
+ * n0 rows of n1 bf16 values.  The reference planner emits it right behind the o
+ * and down projections (src/plan/plan.c:440-449), so an op list of a whole layer's
+ * linears runs here without leaving the library.  eps is the value registered with
+ * mm_norm_eps_set (the reference reads kc->e->mc.norm_eps; the engine is opaque
+ * here). */
+mm_status kx_op_add_rmsnorm(const mm_kcall *kc);
+
 /* Replaces mm_kx_invoke in src/kernels/kx.c:15-47 for the opcodes this
- * library owns: OP_GEMM_F4, OP_QKV and OP_LMHEAD (fp4 forms), OP_SILU_MUL and OP_NOP.  Same NULL checks
+ * library owns: OP_GEMM_F4, OP_QKV and OP_LMHEAD (fp4 forms), OP_SILU_MUL, OP_ADD_RMSNORM and OP_NOP.  Same NULL checks
  * (kc, kc->op, kc->e -> MM_ERR_STATE); any other opcode returns
  * MM_ERR_UNSUPPORTED. */
 mm_status mm_kx_invoke(const mm_kcall *kc);
@@ -129,8 +139,11 @@ typedef enum mm_f4_variant {
     MM_F4_V_ROWWARP = 0,  /* any K%16==0: one warp per weight row, shuffles  */
     MM_F4_V_STREAM  = 1,  /* decode: TMA-staged weight stream + warp MMA     */
     MM_F4_V_UMMA    = 2,  /* prefill: tcgen05 kind::f16, TMEM accumulators   */
-    MM_F4_V_STREAMT = 3   /* decode: TMA-staged weight stream, weights       */
+    MM_F4_V_STREAMT = 3,  /* decode: TMA-staged weight stream, weights       */
                           /*   dequantised into tensor memory, tcgen05 MMA   */
+    MM_F4_V_MX      = 4   /* decode: block-scaled tcgen05 MMA on the packed  */
+                          /*   payload and its e4m3 scales as they lie in    */
+                          /*   memory; activations as e2m1 digit planes      */
 } mm_f4_variant;
 
 typedef struct mm_f4_shape {
@@ -142,9 +155,11 @@ typedef struct mm_f4_shape {
 
 typedef struct mm_f4_plan {
     int      variant;         /* mm_f4_variant                                */
-    uint32_t m_tiles;         /* STREAM: 8-row activation tiles (1 to 4)      */
-    uint32_t tile_m, tile_n;  /* UMMA: CTA tile; STREAM/STREAMT: tile_n = W   */
-                              /*   rows per CTA, tile_m = padded activation rows */
+    uint32_t m_tiles;         /* STREAM: 8-row activation tiles (1 to 4); MX: */
+                              /*   groups of four activation rows (1 to 8)    */
+    uint32_t tile_m, tile_n;  /* UMMA: CTA tile; STREAM/STREAMT/MX: tile_n =  */
+                              /*   W rows per CTA, tile_m = padded activation */
+                              /*   rows (MX: digit-plane rows, 24 per group)  */
     uint32_t split_k;         /* >= 1                                         */
     uint32_t k_steps;         /* K / 256 (STREAM) or K / 64 (UMMA)            */
     uint32_t stages;          /* smem pipeline depth                          */
@@ -195,6 +210,14 @@ mm_status mm_f4_mlp_gate_up(const void *x, const void *gate_payload, const void 
 /* y = silu(gate) * up, elementwise on bf16 [n] (src/kernels/cuda/cx.cu:264-273):
  * the unfused form, enqueued on `stream`. */
 mm_status mm_silu_mul(const void *gate, const void *up, void *y, size_t n, void *stream);
+
+/* res += delta in place, y = rmsnorm(res) * gain on M rows of H bf16 values
+ * (src/kernels/cuda/cx.cu:223-243), enqueued on `stream`; epsilon as registered
+ * (default 1e-6, the value of the reference's model configurations). */
+mm_status mm_add_rmsnorm(void *res, const void *delta, void *y, const void *gain, uint32_t M, uint32_t H,
+                         void *stream);
+mm_status mm_norm_eps_set(float eps);
+float     mm_norm_eps_get(void);
 
 /* Tensor-parallel form (no counterpart in the reference, which is single-GPU).
  * This rank owns output features [col0, col0 + N_local) of a layer with `ldy`

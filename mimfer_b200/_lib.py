@@ -17,9 +17,9 @@ STATUS_NAMES = ["MM_OK", "MM_ERR_NOMEM", "MM_ERR_IO", "MM_ERR_CORRUPT", "MM_ERR_
  MM_ERR_UNSUPPORTED, MM_ERR_RANGE, MM_ERR_STATE, MM_ERR_BUSY, MM_ERR_TIMEOUT,
  MM_ERR_CAPACITY, MM_ERR_EOF) = range(1, 14)
 
-OP_LMHEAD, OP_GEMM_F4, OP_GEMM_BF16, OP_QKV, OP_SILU_MUL, OP_NOP = 1, 4, 5, 6, 12, 18
+OP_LMHEAD, OP_ADD_RMSNORM, OP_GEMM_F4, OP_GEMM_BF16, OP_QKV, OP_SILU_MUL, OP_NOP = 1, 3, 4, 5, 6, 12, 18
 MM_ST_COMPUTE, MM_ST_XFER = 0, 1
-V_ROWWARP, V_STREAM, V_UMMA, V_STREAMT = 0, 1, 2, 3
+V_ROWWARP, V_STREAM, V_UMMA, V_STREAMT, V_MX = 0, 1, 2, 3, 4
 
 
 class MmOpDesc(C.Structure):
@@ -117,6 +117,10 @@ SIGNATURES = {
     "mm_silu_mul": (C.c_int, [_vp, _vp, _vp, C.c_size_t, _vp]),
     "kx_op_lmhead": (C.c_int, [C.POINTER(MmKcall)]),
     "kx_op_silu_mul": (C.c_int, [C.POINTER(MmKcall)]),
+    "kx_op_add_rmsnorm": (C.c_int, [C.POINTER(MmKcall)]),
+    "mm_add_rmsnorm": (C.c_int, [_vp, _vp, _vp, _vp, _u32, _u32, _vp]),
+    "mm_norm_eps_set": (C.c_int, [_f]),
+    "mm_norm_eps_get": (_f, []),
     "mm_lin_engine_fuse_mlp": (C.c_int, [_vp, C.c_int]),
     "mm_lin_engine_overlap": (C.c_int, [_vp, C.c_int]),
     "mm_lin_engine_n_independent": (C.c_uint32, [_vp]),

@@ -46,9 +46,11 @@ int mmb_gate_up_fusable(const void *x, const void *gate_payload, const void *gat
 
 /* Engine -> launcher, for the next op only: how to order the launch against its
  * predecessor (MMB_PDL_* of kernels/launch.h, -1 = the launcher's default),
- * which workspace region its split-K scratch lives in, and whether an op that
- * runs ahead may take fewer, longer K slices than it would alone. */
-void mmb_next_op_context(int pdl_mode, int ws_region, int shallow_split);
+ * which workspace region its scratch lives in, whether an op that runs ahead
+ * may take fewer, longer K slices than it would alone, and whether it reads the
+ * activations the op before it already turned into digit planes (block-scaled
+ * decode path: the planes are shared instead of made again). */
+void mmb_next_op_context(int pdl_mode, int ws_region, int shallow_split, int share_x);
 /* Regions the workspace is cut into, so that ops in flight together never share
  * scratch (1 when the workspace is too small to divide). */
 int mmb_ws_regions(void);

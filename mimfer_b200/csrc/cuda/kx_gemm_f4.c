@@ -19,6 +19,7 @@
 int mmb_stream_init(void);
 int mmb_umma_init(void);
 int mmb_streamt_init(void);
+int mmb_mx_init(void);
 
 /* ------------------------------------------------------------------ state */
 typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
@@ -40,10 +41,16 @@ static struct {
     int        next_pdl;         /* per-op override from the engine, -1 = none */
     int        next_region;
     int        next_shallow;     /* the next op may take the shallower K split of a run-ahead op */
+    int        next_share_x;     /* the next op reads the activations the op before it sliced */
+    int        use_mx;           /* decode ops take the block-scaled tensor path when they can */
+    /* the digit planes made last: which activations, and where they lie */
+    const void *sliced_x;
+    uint32_t   sliced_M, sliced_K;
+    void      *sliced_ws;
     unsigned long long launches;
     /* experiment knobs (mm_f4_tune keys 2..4), all 0 in production */
     uint32_t   st_rows, st_split, st_dbg;
-} G = { .forced_variant = -1, .pdl = 1, .next_pdl = -1 };
+} G = { .forced_variant = -1, .pdl = 1, .next_pdl = -1, .use_mx = 0 };
 
 /* The workspace is cut into WS_REGIONS equal regions, each with its own arrival
  * counters, when every region still holds WS_REGION_MIN bytes; an op uses one
@@ -61,18 +68,21 @@ static size_t ws_region_bytes(void)
     return G.ws ? (G.ws_bytes / (size_t)mmb_ws_regions()) & ~(size_t)255 : 0;
 }
 
-void mmb_next_op_context(int pdl_mode, int ws_region, int shallow_split)
+void mmb_next_op_context(int pdl_mode, int ws_region, int shallow_split, int share_x)
 {
     G.next_pdl = pdl_mode;
     G.next_shallow = shallow_split && pdl_mode == MMB_PDL_INDEPENDENT;
     G.next_region = ws_region >= 0 && ws_region < mmb_ws_regions() ? ws_region : 0;
+    G.next_share_x = share_x;
 }
 
 /* Consume the per-op context: launch mode and workspace base of this op. */
-static void take_op_context(int *pdl_out, void **ws_out, int *shallow_out)
+static void take_op_context(int *pdl_out, void **ws_out, int *shallow_out, int *share_out)
 {
     *shallow_out = G.next_shallow;
     G.next_shallow = 0;
+    *share_out = G.next_share_x;
+    G.next_share_x = 0;
     int mode = G.next_pdl >= 0 ? G.next_pdl : MMB_PDL_TRIGGER_FIRST;
     *pdl_out = G.pdl ? mode : MMB_PDL_OFF;
     *ws_out = G.ws ? (unsigned char *)G.ws + (size_t)G.next_region * ws_region_bytes() : NULL;
@@ -163,6 +173,7 @@ int mm_f4_tune(int key, int value)
     if (key == 2) { int old = (int)G.st_rows; G.st_rows = (uint32_t)value; return old; }
     if (key == 3) { int old = (int)G.st_split; G.st_split = (uint32_t)value; return old; }
     if (key == 4) { int old = (int)G.st_dbg; G.st_dbg = (uint32_t)value; return old; }
+    if (key == 5) { int old = G.use_mx; G.use_mx = value ? 1 : 0; return old; }
     return -1;
 }
 
@@ -197,6 +208,8 @@ void mmb_launcher_reset(void)
     G.status_dev = NULL;
     G.ws = NULL;
     G.ws_bytes = 0;
+    G.sliced_x = NULL;
+    G.sliced_ws = NULL;
     G.ready = 0;
     G.ready_stream = NULL;
     G.next_pdl = -1;
@@ -226,6 +239,7 @@ static mm_status ensure_ready(void)
     CK((cudaError_t)mmb_stream_init());
     CK((cudaError_t)mmb_umma_init());
     CK((cudaError_t)mmb_streamt_init());
+    CK((cudaError_t)mmb_mx_init());
     CK((cudaError_t)mmb_status_word(&G.status_dev));
     CK(cudaHostAlloc((void **)&G.status_host, 64, cudaHostAllocDefault));
     *G.status_host = 0;
@@ -238,6 +252,8 @@ static mm_status ensure_ready(void)
 mm_status mm_f4_workspace_set(void *dev_ptr, size_t bytes)
 {
     MM_CHECK(ensure_ready());
+    G.sliced_x = NULL;
+    G.sliced_ws = NULL;
     if (!dev_ptr || bytes <= MMB_WS_COUNTER_B) {
         G.ws = NULL;
         G.ws_bytes = 0;
@@ -320,8 +336,15 @@ static mm_status plan_linear(const void *x, const void *payload, const void *sca
         sh.ptr_align = 8;                  /* aligned operands, unaligned output slice: the row-warp kernel */
     mm_status st = G.forced_variant >= 0 ? mm_f4_select_variant(&sh, G.forced_variant, plan)
                                          : mm_f4_select(&sh, plan);
+    if (st == MM_OK && plan->variant == MM_F4_V_STREAM && G.forced_variant < 0 && G.use_mx) {
+        mm_f4_plan mx;                     /* the block-scaled tensor path when its scratch fits the workspace */
+        if (mm_f4_select_variant(&sh, MM_F4_V_MX, &mx) == MM_OK)
+            *plan = mx;
+    }
     if (st == MM_OK && plan->variant == MM_F4_V_STREAM && (G.st_rows || G.st_split))
         return mmb_plan_stream_with(&sh, G.st_rows, G.st_split, plan);
+    if (st == MM_OK && plan->variant == MM_F4_V_MX && (G.st_rows || G.st_split))
+        return mmb_plan_mx_with(&sh, G.st_rows, G.st_split, plan);
     /* An op that runs ahead of its predecessors shares the GPU with them: it is
      * served best by fewer, longer K slices on about half of the SMs (less
      * exchange, the fill paid once per more steps) - the other half is busy with
@@ -329,14 +352,53 @@ static mm_status plan_linear(const void *x, const void *payload, const void *sca
      * split.  Measured on B200, us per op, run-ahead / alone: down at M = 16 with
      * 3 slices 17.0 / 31.9, with 7 slices 19.9 / 21.4; q with 3 slices 8.2 / 13.8,
      * with 5 slices 9.9 / 12.9. */
-    if (st == MM_OK && run_ahead && plan->variant == MM_F4_V_STREAM && plan->split_k > 1 &&
-        plan->grid_x <= 24) {              /* measured for 17 to 24 row tiles; a fused qkv (32) lost with 2 slices */
+    if (st == MM_OK && run_ahead && (plan->variant == MM_F4_V_STREAM || plan->variant == MM_F4_V_MX) &&
+        plan->split_k > 1 && plan->grid_x <= 24) {   /* measured for 17 to 24 row tiles; a fused qkv (32) lost with 2 slices */
         uint32_t s = (uint32_t)(0.45 * (double)sh.sm_count / (double)plan->grid_x + 0.5);
         if (s < 1) s = 1;
         if (s < plan->split_k)
-            st = mmb_plan_stream_with(&sh, plan->tile_n, s, plan);
+            st = plan->variant == MM_F4_V_MX ? mmb_plan_mx_with(&sh, plan->tile_n, s, plan)
+                                             : mmb_plan_stream_with(&sh, plan->tile_n, s, plan);
     }
     return st;
+}
+
+/* The two launches of an op on the block-scaled tensor path: the activations'
+ * digit planes into the op's scratch (skipped when the op in front sliced the
+ * same activations and they are still there), then the linear kernel.  The
+ * weight maps of `a` are encoded by the caller. */
+static mm_status launch_mx_pair(mmb_args *a, int share_x, void *stream)
+{
+    const uint32_t nb = a->plan.tile_m;
+    const int reuse = share_x && G.sliced_ws && G.sliced_x == a->x && G.sliced_M == a->M && G.sliced_K == a->K;
+    a->mx_x_ws = reuse ? G.sliced_ws : (void *)((unsigned char *)a->ws + MMB_WS_COUNTER_B);
+    a->mx_partial_off = MMB_WS_COUNTER_B + MMB_MX_XS_B(nb, a->K);
+    unsigned char *planes = (unsigned char *)a->mx_x_ws + MMB_MX_PLANES_OFF;
+    MM_CHECK(encode_2d(a->tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, planes, a->K / 2, nb, 128, nb,
+                       CU_TENSOR_MAP_SWIZZLE_128B));
+    MM_CHECK(encode_2d(a->tm_sfb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, planes + MMB_MX_PLANES_B(nb, a->K),
+                       a->K / 16, nb, 16, nb, CU_TENSOR_MAP_SWIZZLE_NONE));
+    int err;
+    if (!reuse) {
+        /* an op that slices its own activations waits for its predecessor (they may
+         * be its output, and the scratch may still be read) */
+        if (a->pdl == MMB_PDL_INDEPENDENT)
+            a->pdl = MMB_PDL_WAIT_FIRST;
+        if ((err = mmb_launch_xslice(a, stream)) != 0) {
+            MM_LOGE("cuda: launch (activation slicing, M %u K %u): %s", a->M, a->K,
+                    cudaGetErrorString((cudaError_t)err));
+            return MM_ERR_CUDA;
+        }
+        G.launches++;
+        G.sliced_x = a->x; G.sliced_M = a->M; G.sliced_K = a->K; G.sliced_ws = a->mx_x_ws;
+    }
+    if ((err = mmb_launch_mx(a, stream)) != 0) {
+        MM_LOGE("cuda: launch (variant %d, M %u K %u N %u): %s", a->plan.variant, a->M, a->K, a->N,
+                cudaGetErrorString((cudaError_t)err));
+        return MM_ERR_CUDA;
+    }
+    G.launches++;
+    return MM_OK;
 }
 
 static mm_status linear_impl(const void *x, const void *payload, const void *scale, float gs,
@@ -356,8 +418,8 @@ static mm_status linear_impl(const void *x, const void *payload, const void *sca
     memset(&a, 0, sizeof a);
     a.x = x; a.payload = payload; a.scale = scale; a.y = y;
     a.gs = gs; a.M = M; a.K = K; a.N = N;
-    int shallow = 0;
-    take_op_context(&a.pdl, &a.ws, &shallow);
+    int shallow = 0, share_x = 0;
+    take_op_context(&a.pdl, &a.ws, &shallow, &share_x);
     for (uint32_t d = 0; d < n_dst; d++) a.y_dst[d] = y_dst[d];
     a.n_dst = n_dst; a.ldy = ldy; a.col0 = col0;
 
@@ -380,6 +442,13 @@ static mm_status linear_impl(const void *x, const void *payload, const void *sca
         a.dbg = G.st_dbg;
         err = mmb_launch_stream(&a, stream);
         break;
+    case MM_F4_V_MX:
+        MM_CHECK(encode_2d(a.tm_payload, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, payload, K / 2, N, 128,
+                           a.plan.tile_n, CU_TENSOR_MAP_SWIZZLE_128B));
+        MM_CHECK(encode_2d(a.tm_scale, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, scale, K / 16, N, 16,
+                           a.plan.tile_n, CU_TENSOR_MAP_SWIZZLE_NONE));
+        MM_CHECK(launch_mx_pair(&a, share_x, stream));
+        return MM_OK;
     case MM_F4_V_STREAMT:
         MM_CHECK(encode_2d(a.tm_payload, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, payload, K / 2, N, 128,
                            MMB_ST_ROWS, CU_TENSOR_MAP_SWIZZLE_128B));
@@ -472,14 +541,19 @@ mm_status mm_f4_mlp_gate_up(const void *x, const void *gate_payload, const void 
     a.gs = gs_gate; a.gs_up = gs_up;
     a.glu = 1; a.gate_plane = gate_first ? 0 : 1;
     a.M = M; a.K = K; a.N = inter;
-    int shallow = 0;
-    take_op_context(&a.pdl, &a.ws, &shallow);
+    int shallow = 0, share_x = 0;
+    take_op_context(&a.pdl, &a.ws, &shallow, &share_x);
     (void)shallow;                         /* the gated pair keeps its split */
     mm_f4_shape sh = { M, K, inter, (uint32_t)G.sm_count, min_align(x, pay0, sc0, y), ws_region_bytes() };
-    mm_status st = mm_f4_select_glu(&sh, &a.plan);
+    mm_status st = mmb_select_glu(&sh, G.use_mx, &a.plan);
     if (st != MM_OK)
         return st;
     int err = 0;
+    if (a.plan.variant == MM_F4_V_MX) {
+        MM_CHECK(encode_pair(a.tm_payload, pay0, K / 2, inter, dpay, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B));
+        MM_CHECK(encode_pair(a.tm_scale, sc0, K / 16, inter, dsc, 16, 128, CU_TENSOR_MAP_SWIZZLE_NONE));
+        return launch_mx_pair(&a, share_x, stream);
+    }
     if (a.plan.variant == MM_F4_V_STREAM) {
         MM_CHECK(encode_pair(a.tm_payload, pay0, K / 2, inter, dpay, 128, MMB_ST_ROWS / 2,
                              CU_TENSOR_MAP_SWIZZLE_128B));
@@ -599,7 +673,7 @@ mm_status mmb_plan_for_op(const mm_op_desc *op, int glu, mm_f4_plan *out)
         /* the lower-addressed projection decides the alignment; both are placed alike */
         mm_f4_shape sh = { op->n0, op->n1, op->n2, (uint32_t)G.sm_count,
                            min_align(op->a, op->b, op->d, op->c), ws_region_bytes() };
-        return mm_f4_select_glu(&sh, out);
+        return mmb_select_glu(&sh, G.use_mx, out);
     }
     return plan_linear(op->a, op->b, op->d, op->c, 0, 0, 0, op->n0, op->n1, op->n2, 0, out);
 }
@@ -640,9 +714,61 @@ mm_status kx_op_silu_mul(const mm_kcall *kc)
     return finish_op();
 }
 
+/* Epsilon of the RMSNorm.  The reference reads it from the engine's model
+ * configuration (kc->e->mc.norm_eps, src/kernels/cpu/cx.c:143); the engine is
+ * opaque to this library, so its owner registers the value once. */
+static float g_norm_eps = 1.0e-6f;
+
+mm_status mm_norm_eps_set(float eps)
+{
+    MM_REQUIRE(eps == eps && eps >= 0.0f && eps < 1.0f, MM_ERR_RANGE);
+    g_norm_eps = eps;
+    return MM_OK;
+}
+
+float mm_norm_eps_get(void) { return g_norm_eps; }
+
+mm_status mm_add_rmsnorm(void *res, const void *delta, void *y, const void *gain, uint32_t M, uint32_t H,
+                         void *stream)
+{
+    MM_REQUIRE(res && delta && y && gain, MM_ERR_STATE);
+    if (M == 0 || H == 0)
+        return MM_ERR_SHAPE;
+    MM_CHECK(ensure_ready());
+    if (!stream)
+        stream = mm_cuda_stream_raw(MM_ST_COMPUTE);
+    int pdl = 0, shallow = 0, share = 0;
+    void *ws = NULL;
+    take_op_context(&pdl, &ws, &shallow, &share);
+    int err = mmb_launch_add_rmsnorm(res, delta, y, gain, M, H, g_norm_eps, pdl != MMB_PDL_OFF, stream);
+    if (err) {
+        MM_LOGE("cuda: add_rmsnorm launch: %s", cudaGetErrorString((cudaError_t)err));
+        return MM_ERR_CUDA;
+    }
+    G.sliced_x = NULL;                 /* activations change under the planes made last */
+    G.launches++;
+    return MM_OK;
+}
+
+/* OP_ADD_RMSNORM: a = residual (updated in place), b = delta, c = normalised
+ * output, d = gain, n0 = M rows of n1 values (include/mimfer/kernels.h:87-88). */
+mm_status kx_op_add_rmsnorm(const mm_kcall *kc)
+{
+    MM_REQUIRE(kc && kc->op, MM_ERR_STATE);
+    const mm_op_desc *op = kc->op;
+    MM_REQUIRE(op->a && op->b && op->c && op->d, MM_ERR_STATE);
+    MM_REQUIRE(mm_cuda_stream_raw(MM_ST_COMPUTE) != NULL, MM_ERR_STATE);
+    mm_status st = mm_add_rmsnorm((void *)(uintptr_t)op->a, op->b, op->c, op->d, op->n0, op->n1,
+                                  mm_cuda_stream_raw(MM_ST_COMPUTE));
+    if (st != MM_OK)
+        return st;
+    return finish_op();
+}
+
 int kx_cuda_oppref(int op)
 {
-    return op == OP_GEMM_F4 || op == OP_QKV || op == OP_LMHEAD || op == OP_SILU_MUL || op == OP_NOP;
+    return op == OP_GEMM_F4 || op == OP_QKV || op == OP_LMHEAD || op == OP_SILU_MUL ||
+           op == OP_ADD_RMSNORM || op == OP_NOP;
 }
 
 mm_status mm_kx_invoke(const mm_kcall *kc)
@@ -654,6 +780,7 @@ mm_status mm_kx_invoke(const mm_kcall *kc)
     case OP_QKV:     return kx_op_qkv(kc);
     case OP_LMHEAD:  return kx_op_lmhead(kc);
     case OP_SILU_MUL: return kx_op_silu_mul(kc);
+    case OP_ADD_RMSNORM: return kx_op_add_rmsnorm(kc);
     case OP_NOP:     return MM_OK;
     default:
         MM_LOGE("kx: opcode %d is not served by the NVFP4 linear library", kc->op->op);

@@ -148,6 +148,10 @@ mm_status mm_lin_engine_add(mm_lin_engine *e, const mm_op_desc *op)
             return MM_ERR_SHAPE;
         if (try_fuse_mlp(e, op))
             return MM_OK;
+    } else if (op->op == OP_ADD_RMSNORM) {
+        MM_REQUIRE(op->a && op->b && op->c && op->d, MM_ERR_STATE);
+        if (op->n0 == 0 || op->n1 == 0)
+            return MM_ERR_SHAPE;
     } else if (op->op != OP_NOP) {
         MM_REQUIRE(op->a && op->b && op->c && op->d, MM_ERR_STATE);
         if (op->n0 == 0 || op->n1 == 0 || op->n2 == 0 || op->n1 % 16 != 0)
@@ -161,7 +165,7 @@ mm_status mm_lin_engine_add(mm_lin_engine *e, const mm_op_desc *op)
 static size_t op_in_bytes(const mm_op_desc *op) { return (size_t)op->n0 * op->n1 * 2u; }
 static size_t op_out_bytes(const mm_op_desc *op)
 {
-    return (size_t)op->n0 * (op->op == OP_SILU_MUL ? op->n1 : op->n2) * 2u;
+    return (size_t)op->n0 * (op->op == OP_SILU_MUL || op->op == OP_ADD_RMSNORM ? op->n1 : op->n2) * 2u;
 }
 
 uint32_t mm_lin_engine_n_ops(const mm_lin_engine *e) { return e ? e->n_ops : 0; }
@@ -195,25 +199,27 @@ static span mk_span(const void *p, size_t bytes)
 }
 static int spans_meet(span a, span b) { return a.lo < b.hi && b.lo < a.hi; }
 
-/* reads[0..1] and the write of an op (weights are never written, so they do not count) */
-static void op_spans(const mm_op_desc *op, span reads[2], span *write)
+/* reads[0..1] and writes[0..1] of an op (weights and gains are never written, so
+ * they do not count).  ADD_RMSNORM updates its first operand in place. */
+static void op_spans(const mm_op_desc *op, span reads[2], span writes[2])
 {
     size_t in = op_in_bytes(op);
+    const int two = op->op == OP_SILU_MUL || op->op == OP_ADD_RMSNORM;
     reads[0] = mk_span(op->a, in);
-    reads[1] = op->op == OP_SILU_MUL ? mk_span(op->b, in) : mk_span(op->a, 0);
-    *write = mk_span(op->c, op_out_bytes(op));
+    reads[1] = two ? mk_span(op->b, in) : mk_span(op->a, 0);
+    writes[0] = mk_span(op->c, op_out_bytes(op));
+    writes[1] = op->op == OP_ADD_RMSNORM ? mk_span(op->a, in) : mk_span(op->c, 0);
 }
 
 static int ops_independent(const mm_op_desc *p, const mm_op_desc *q)
 {
-    span pr[2], qr[2], pw, qw;
-    op_spans(p, pr, &pw);
-    op_spans(q, qr, &qw);
-    if (spans_meet(pw, qw))
-        return 0;
+    span pr[2], qr[2], pw[2], qw[2];
+    op_spans(p, pr, pw);
+    op_spans(q, qr, qw);
     for (int i = 0; i < 2; i++)
-        if (spans_meet(pw, qr[i]) || spans_meet(qw, pr[i]))
-            return 0;
+        for (int j = 0; j < 2; j++)
+            if (spans_meet(pw[i], qw[j]) || spans_meet(pw[i], qr[j]) || spans_meet(qw[i], pr[j]))
+                return 0;
     return 1;
 }
 
@@ -279,17 +285,36 @@ static mm_status run_ops(mm_lin_engine *e)
     int next_region = 0;
     const int n_regions = e->overlap ? mmb_ws_regions() : 1;
     e->n_independent = 0;
+    int prev_mx = -1;                 /* index of the op in front when it made digit planes, else -1 */
     for (uint32_t i = 0; i < e->n_ops; i++) {
         const mm_op_desc *op = &e->ops[i];
+        const int linear = op->op != OP_NOP && op->op != OP_SILU_MUL && op->op != OP_ADD_RMSNORM;
+        mm_f4_plan plan;
+        int share = 0;
+        if (linear) {
+            MM_CHECK(mmb_plan_for_op(op, op->op == MMB_OP_GATE_UP, &plan));
+            /* block-scaled decode path: an op that reads the activations the op in
+             * front already turned into digit planes takes those planes (q, k and v;
+             * gate and up), unless that op wrote into them */
+            if (plan.variant == MM_F4_V_MX && prev_mx >= 0) {
+                const mm_op_desc *q = &e->ops[prev_mx];
+                span qr[2], qw[2];
+                op_spans(q, qr, qw);
+                share = q->a == op->a && q->n0 == op->n0 && q->n1 == op->n1 &&
+                        !spans_meet(qw[0], mk_span(op->a, op_in_bytes(op)));
+            }
+            prev_mx = plan.variant == MM_F4_V_MX ? (int)i : -1;
+        } else if (op->op != OP_NOP) {
+            prev_mx = -1;
+        }
         if (e->overlap && op->op != OP_NOP) {
-            int independent = 0, region = 0, split = 0;
-            if (op->op != OP_SILU_MUL) {
-                mm_f4_plan plan;
-                MM_CHECK(mmb_plan_for_op(op, op->op == MMB_OP_GATE_UP, &plan));
-                split = plan.split_k > 1;
-                region = split ? next_region : 0;
-                independent = i > 0 && plan.variant == MM_F4_V_STREAM &&
-                              !(split && (regions_in_flight & (1u << region)));
+            int independent = 0, region = 0, scratch = 0;
+            if (linear) {
+                /* split-K partials and digit planes live in the op's workspace region */
+                scratch = plan.split_k > 1 || plan.variant == MM_F4_V_MX;
+                region = scratch ? next_region : 0;
+                independent = i > 0 && (plan.variant == MM_F4_V_STREAM || (plan.variant == MM_F4_V_MX && share)) &&
+                              !(scratch && (regions_in_flight & (1u << region)));
                 for (uint32_t j = first_in_flight; independent && j < i; j++)
                     if (e->ops[j].op != OP_NOP && !ops_independent(op, &e->ops[j]))
                         independent = 0;
@@ -298,13 +323,15 @@ static mm_status run_ops(mm_lin_engine *e)
                 first_in_flight = i;
                 regions_in_flight = 0;
             }
-            if (split) {
+            if (scratch) {
                 regions_in_flight |= 1u << region;
                 next_region = (region + 1) % n_regions;
             }
             e->n_independent += (uint32_t)independent;
             mmb_next_op_context(independent ? MMB_PDL_INDEPENDENT : MMB_PDL_WAIT_FIRST, region,
-                                e->overlap > 1);
+                                e->overlap > 1, share);
+        } else if (linear) {
+            mmb_next_op_context(-1, 0, 0, share);
         }
         /* the first op of a group waits for the uploads of the whole group */
         if (with_copies && i % grp == 0)

@@ -35,6 +35,22 @@ extern "C" {
 #define MMB_STT_THREADS     ((MMB_STT_DEQ_WARPS + 3u + MMB_STT_XFORM_WARPS) * 32u)   /* + TMA, 2 x MMA */
 #define MMB_STT_STAGE_B(npad) (MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B + (npad) * 512u)
 
+/* ---- MX (decode on the block-scaled tensor path) ---------------------------- */
+#define MMB_MX_PLANES       6      /* signed e2m1 digits per activation                      */
+#define MMB_MX_THREADS      352u   /* TMA, MMA (half 0), 2 x 4 scale-factor warps (four also run the epilogue), MMA (half 1) */
+#define MMB_MX_MAX_NB       192u   /* B rows: 6 x (M padded to a multiple of 4), M <= 32     */
+/* one pipeline stage: payload (rows x 128 B) | digit planes (nb x 128 B) | block scales
+ * (rows x 16 B) | plane scales (nb x 16 B), padded so that every stage starts on a
+ * 1024-byte boundary (128-byte swizzle) */
+#define MMB_MX_STAGE_B(rows, nb) ((((rows) + (nb)) * 144u + 1023u) & ~1023u)
+#define MMB_MX_FIXED_B      (512u /* barriers, flags */ + 1024u /* align slack */)
+/* activation scratch of one op, inside its workspace region after the arrival
+ * counters: row factors (32 rows x 2 floats), digit planes [nb][K/2], plane scales [nb][K/16] */
+#define MMB_MX_ROWSCALE_OFF 0u
+#define MMB_MX_PLANES_OFF   1024u
+#define MMB_MX_PLANES_B(nb, K) ((((size_t)(nb) * ((K) / 2u)) + 1023u) & ~(size_t)1023u)
+#define MMB_MX_XS_B(nb, K)  (MMB_MX_PLANES_OFF + MMB_MX_PLANES_B(nb, K) + ((((size_t)(nb) * ((K) / 16u)) + 1023u) & ~(size_t)1023u))
+
 /* ---- UMMA (prefill) geometry ---------------------------------------------- */
 #define MMB_UM_KBLOCK      64u    /* bf16 elements per smem row (128 B swizzle) */
 #define MMB_UM_KGROUP      256u   /* weights covered by one scale box (16 B)    */
@@ -116,13 +132,19 @@ typedef struct mmb_args {
     int         glu, gate_plane;
     float       gs_up;
     void       *ws;       /* workspace base or NULL */
+    /* MX: activation scratch of this op (inside its own workspace region, or the
+     * region of the op in front when both read the same activations) and where the
+     * split-K partials start inside `ws` */
+    void       *mx_x_ws;
+    size_t      mx_partial_off;
     mm_f4_plan  plan;
     int         pdl;      /* MMB_PDL_*: how the launch is ordered against its predecessor */
     uint32_t    dbg;      /* MMB_DBG_* (decode kernel), 0 in production */
     /* 128-byte TMA descriptors, filled by the launcher (opaque here) */
     unsigned char tm_payload[128] __attribute__((aligned(64)));
     unsigned char tm_scale[128] __attribute__((aligned(64)));
-    unsigned char tm_x[128] __attribute__((aligned(64)));
+    unsigned char tm_x[128] __attribute__((aligned(64)));     /* MX: the digit planes */
+    unsigned char tm_sfb[128] __attribute__((aligned(64)));   /* MX: the planes' block scales */
 } mmb_args;
 
 /* Each returns a cudaError_t value (0 = success) from the launch. `stream`
@@ -131,17 +153,24 @@ int mmb_launch_rowwarp(const mmb_args *a, void *stream);
 int mmb_launch_stream(const mmb_args *a, void *stream);
 int mmb_launch_umma(const mmb_args *a, void *stream);
 int mmb_launch_streamt(const mmb_args *a, void *stream);
+int mmb_launch_xslice(const mmb_args *a, void *stream);     /* activations -> digit planes (a->mx_x_ws) */
+int mmb_launch_mx(const mmb_args *a, void *stream);
 /* Buffers one launch of the upload kernel takes (host_gather.cu). */
 #define MMB_GATHER_MAX 32u
 int mmb_launch_host_gather(const void *const *src_host, void *const *dst_dev, const size_t *bytes,
                            uint32_t n, void *stream);
 int mmb_launch_tp_barrier(unsigned *const *flags, uint32_t n_ranks, uint32_t rank, void *stream);
 int mmb_launch_silu_mul(const void *gate, const void *up, void *y, size_t n, void *stream);
+int mmb_launch_add_rmsnorm(void *res, const void *delta, void *y, const void *gain, uint32_t M, uint32_t H,
+                           float eps, int pdl, void *stream);
 int mmb_launch_wait_selftest(unsigned *status, unsigned *done, void *stream);
 int mmb_launch_decode_probe(uint32_t *out_mma, uint32_t *out_f32, uint32_t *out_f16, void *stream);
 /* STREAM plan with the rows per CTA and the K split given (0 = the selector's
  * own choice for that number); experiments and the selector's tests. */
 mm_status mmb_plan_stream_with(const mm_f4_shape *s, uint32_t rows, uint32_t split, mm_f4_plan *p);
+/* mm_f4_select_glu with the block-scaled decode path allowed or not. */
+mm_status mmb_select_glu(const mm_f4_shape *s, int allow_mx, mm_f4_plan *p);
+mm_status mmb_plan_mx_with(const mm_f4_shape *s, uint32_t rows, uint32_t split, mm_f4_plan *p);
 /* One-time per-process setup (smem opt-in attributes). */
 int mmb_kernels_init(void);
 /* Address of the device status word. */

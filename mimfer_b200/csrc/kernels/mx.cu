@@ -1,0 +1,766 @@
+/*
+ * MX: the decode kernel of the NVFP4 linear op on the block-scaled tensor path
+ * (M <= 32, HBM-bound).
+ *
+ * NVFP4 is the operand format of tcgen05.mma kind::mxf4nvf4: packed e2m1
+ * payload, one e4m3 scale per 16 values.  A TMA box of payload (rows x 128 B,
+ * 128-byte swizzle) is the A operand as it lies in memory, and the matching box
+ * of block scales is its scale-factor tensor once copied into tensor memory.  So
+ * no CUDA core touches a weight: the SM streams boxes and issues MMAs.
+ *
+ * The other operand has to be e2m1 with power-of-two block scales too, and the
+ * reference keeps activations in bf16 (src/kernels/cpu/cx.c:211).  A small
+ * kernel in front (f4_xslice_kernel) rewrites every bf16 activation as a sum
+ * of six signed e2m1 digits on block scales 2^(s_p) * unit, s_p = 1, 3, 6, 9,
+ * 12, 15: digit planes p = 0..5 of every activation row become rows of the B
+ * operand (NB = 6 x padded M rows), the fp32 accumulator columns of the planes of
+ * one activation row are added in the epilogue.  The digit set of e2m1
+ * {0, .5, 1, 1.5, 2, 3, 4, 6} with signs covers every integer up to 149 796
+ * units with six digits (greedy, nearest digit first), i.e. 17 bits below the
+ * largest value of a 16-wide block: a bf16 value is reproduced exactly when it
+ * lies within 2^9 of its block's maximum, smaller ones are rounded at 2^-17 of
+ * that maximum (and never coarser than 2^-19 of the row maximum), which is below
+ * the rounding error of the reference's own fp32 accumulation.  Weights and
+ * block scales are exact, products are exact, sums are fp32.
+ *
+ * Scale bytes the tensor core reads differently from the reference decoder
+ * (include/mimfer/tensor.h:98-118) are rewritten on the way into tensor memory:
+ * 0x7f and 0xff (zero in the reference, NaN as ue4m3) become 0, and a byte with the sign
+ * bit set (the tensor core ignores it) has the bit cleared and the sign bits of
+ * the 16 payload nibbles of its block flipped in shared memory instead.
+ *
+ * Warp roles (11 warps): 0 = TMA producer; 1 and 10 = MMA issue for the first
+ * and the second 128-row half (one thread each; warp 1 owns tensor memory);
+ * 2..9 = scale-factor copies into tensor memory: one warp per lane quadrant (the
+ * data is replicated over the four) and per parity of the K step, so a warp
+ * has two steps' time for its copy; warps 2..5 then run the epilogue.
+ *
+ * It replaces the one-thread-per-output kernel of the reference
+ * (src/kernels/cuda/cx.cu:345-356) for the decode regime.
+ */
+#include "fp4.cuh"
+#include "ptx.cuh"
+
+namespace mmb {
+
+/* ---- tcgen05 pieces this file adds to ptx.cuh -------------------------------- */
+__device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&v)[16])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),
+          "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]),
+          "r"(v[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint32_t (&v)[8])
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]),
+                   "r"(v[6]), "r"(v[7]) : "memory");
+}
+/* one instruction for a whole 64-column slot: a tcgen05.st costs several hundred
+ * cycles whatever its width (measured), so the slot goes out in one */
+__device__ __forceinline__ void tmem_st_x64(uint32_t taddr, const uint32_t (&v)[64])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x64.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,"
+        "%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,"
+        "%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63,%64};"
+        ::"r"(taddr),
+          "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]),
+          "r"(v[32]), "r"(v[33]), "r"(v[34]), "r"(v[35]), "r"(v[36]), "r"(v[37]), "r"(v[38]), "r"(v[39]),
+          "r"(v[40]), "r"(v[41]), "r"(v[42]), "r"(v[43]), "r"(v[44]), "r"(v[45]), "r"(v[46]), "r"(v[47]),
+          "r"(v[48]), "r"(v[49]), "r"(v[50]), "r"(v[51]), "r"(v[52]), "r"(v[53]), "r"(v[54]), "r"(v[55]),
+          "r"(v[56]), "r"(v[57]), "r"(v[58]), "r"(v[59]), "r"(v[60]), "r"(v[61]), "r"(v[62]), "r"(v[63])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait()
+{
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t (&r)[8])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                   "=r"(r[7]) : "r"(taddr) : "memory");
+}
+/* D[tmem] (+)= A[smem] * B[smem]^T on e2m1 operands with one ue4m3 scale per 16
+ * values of K for each row of A and of B (scale factors in tensor memory). */
+__device__ __forceinline__ void umma_mxf4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate, uint32_t sfa, uint32_t sfb)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+}
+/* Instruction descriptor of kind::mxf4nvf4: e2m1 x e2m1 (format code 1 for both
+ * operands), both K-major, N / 8 at bit 17, ue4m3 scales (bit 23 clear),
+ * M / 16 at bit 24 (M = 128), K = 64 per instruction (bit 31 clear). */
+__host__ __device__ constexpr uint32_t umma_idesc_mxf4(uint32_t n)
+{
+    return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | (8u << 24);
+}
+
+/* ==========================================================================
+ * Activation slicing
+ * ========================================================================== */
+struct XsliceParams {
+    const uint16_t *x;          /* bf16 [M][K]                                    */
+    uint8_t        *planes;     /* [NB][K/2] e2m1 nibbles, row = 6 * m + plane     */
+    uint8_t        *sfb;        /* [NB][K/16] ue4m3 powers of two                  */
+    float          *row_scale;  /* [Mpad][2]: two factors whose product is 2^-G(m) */
+    uint32_t        M, K, m_pad;
+    uint32_t        pdl;
+};
+
+__device__ __forceinline__ uint32_t quant_e2m1(float t)
+{
+    /* nearest e2m1 code of t (round to nearest even, saturating); the second
+     * operand is zero, so whichever nibble holds t is found by folding */
+    uint32_t u;
+    asm("{\n\t.reg .b8 q;\n\tcvt.rn.satfinite.e2m1x2.f32 q, %1, %2;\n\tmov.b32 %0, {q, q, q, q};\n\t}"
+        : "=r"(u) : "f"(t), "f"(0.0f));
+    return (u | (u >> 4)) & 15u;
+}
+
+__device__ __forceinline__ float dequant_e2m1(uint32_t code)
+{
+    uint32_t h2;
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\tmov.b32 {b0, b1, b2, b3}, %1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t}" : "=r"(h2) : "r"(code));
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(h2 & 0xffffu)));
+}
+
+/* shift s_p of plane p: its digit v stands for v * 2^(s_p + 1) units */
+__host__ __device__ constexpr int mx_shift(int plane)
+{
+    return plane == 0 ? 0 : 3 * plane - 1;       /* 0, 2, 5, 8, 11, 14 */
+}
+
+/* Thread = four consecutive activations (a quarter of a 16-wide block); a CTA
+ * covers 1024 values of one activation row; grid = (ceil(K / 1024), padded M). */
+__global__ void __launch_bounds__(256)
+f4_xslice_kernel(const XsliceParams p)
+{
+    __shared__ uint32_t s_max[8];
+    const uint32_t m = blockIdx.y, tid = threadIdx.x;
+    const uint32_t blocks = p.K / 16u;
+    grid_dep_launch();                       /* the linear kernel may start fetching weights */
+    if (p.pdl != MMB_PDL_OFF)
+        grid_dep_wait();                     /* x is the previous kernel's output */
+
+    /* this thread's four values, fetched while the row is scanned */
+    const uint32_t quarter = blockIdx.x * 256u + tid;         /* index of the four values in the row */
+    const uint32_t blk = quarter >> 2;
+    uint32_t w0 = 0, w1 = 0;
+    if (blk < blocks && m < p.M) {
+        const uint2 v = __ldcg(reinterpret_cast<const uint2 *>(p.x + static_cast<size_t>(m) * p.K) + quarter);
+        w0 = v.x; w1 = v.y;                  /* written by the kernel in front: not the read-only path */
+    }
+    /* largest magnitude of the row: every CTA of the row scans all of it, eight
+     * 16-byte loads in flight per thread */
+    uint32_t amax = 0;
+    if (m < p.M) {
+        const uint4 *row = reinterpret_cast<const uint4 *>(p.x + static_cast<size_t>(m) * p.K);
+        const uint32_t n8 = p.K / 8u;
+        for (uint32_t base8 = 0; base8 < n8; base8 += 2048u) {
+            uint4 v[8];
+#pragma unroll
+            for (uint32_t j = 0; j < 8u; j++) {
+                const uint32_t i = base8 + j * 256u + tid;
+                v[j] = i < n8 ? __ldcg(row + i) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (uint32_t j = 0; j < 8u; j++) {
+                const uint32_t w[4] = { v[j].x, v[j].y, v[j].z, v[j].w };
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    amax = max(amax, w[q] & 0x7fffu);
+                    amax = max(amax, (w[q] >> 16) & 0x7fffu);
+                }
+            }
+        }
+    }
+    amax = __reduce_max_sync(0xffffffffu, amax);
+    if ((tid & 31u) == 0)
+        s_max[tid >> 5] = amax;
+    __syncthreads();
+    amax = s_max[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) amax = max(amax, s_max[i]);
+
+    /* G = 9 - floor(log2(row maximum)): the largest block's top digit plane gets
+     * the largest power of two a ue4m3 holds */
+    const bool finite = amax < 0x7f80u;
+    int e_max = static_cast<int>(amax >> 7) - 127;           /* exponent field 0: subnormal, below 2^-126 */
+    if ((amax >> 7) == 0)
+        e_max = amax ? (31 - __clz(amax)) - 133 : -126;       /* top bit of the 7-bit fraction x 2^-133 */
+    const int G = 9 - e_max;
+    if (blockIdx.x == 0 && tid == 0) {
+        const int g1 = G >> 1, g2 = G - g1;
+        float f1 = __int_as_float((127 - g1) << 23), f2 = __int_as_float((127 - g2) << 23);
+        if (!finite)
+            f1 = __int_as_float(0x7fc00000);                  /* a row with inf or NaN gives NaN outputs */
+        p.row_scale[2u * m] = f1;
+        p.row_scale[2u * m + 1u] = f2;
+    }
+
+    const bool live = blk < blocks && m < p.M && finite && amax;
+    if (!live)
+        w0 = w1 = 0u;
+    /* largest magnitude of the 16-wide block: the four threads of a block are neighbours */
+    uint32_t bmax = max(max(w0 & 0x7fffu, (w0 >> 16) & 0x7fffu), max(w1 & 0x7fffu, (w1 >> 16) & 0x7fffu));
+    bmax = max(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
+    bmax = max(bmax, __shfl_xor_sync(0xffffffffu, bmax, 2));
+    if (blk >= blocks)
+        return;
+    int e_b = static_cast<int>(bmax >> 7) - 127;
+    if ((bmax >> 7) == 0)
+        e_b = bmax ? (31 - __clz(bmax)) - 133 : -200;
+    const int U = max(e_b - 16, -10 - G);                      /* the block's unit is 2^U */
+    uint32_t codes[MMB_MX_PLANES];
+#pragma unroll
+    for (int q = 0; q < MMB_MX_PLANES; q++) codes[q] = 0u;
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t bits = ((i < 2 ? w0 : w1) >> (16 * (i & 1))) & 0xffffu;
+            const uint32_t ef = (bits >> 7) & 0xffu, mant = bits & 0x7fu;
+            const uint32_t sig = ef ? 128u + mant : mant;
+            const int e = ef ? static_cast<int>(ef) - 127 : -126;
+            const int sh = e - 7 - U;                          /* value = sig * 2^sh units */
+            uint32_t V;
+            if (sh >= 0)
+                V = sig << sh;                                  /* sh <= 9 by the choice of U */
+            else
+                V = sh < -10 ? 0u : (sig + (1u << (-sh - 1))) >> (-sh);
+            float R = static_cast<float>(V);
+            if (bits & 0x8000u)
+                R = -R;
+#pragma unroll
+            for (int q = MMB_MX_PLANES - 1; q >= 0; q--) {
+                const float wgt = __int_as_float((127 + mx_shift(q) + 1) << 23);
+                const float inv = __int_as_float((127 - mx_shift(q) - 1) << 23);
+                const uint32_t code = quant_e2m1(R * inv);
+                R = fmaf(-dequant_e2m1(code), wgt, R);
+                codes[q] |= code << (4 * i);
+            }
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < MMB_MX_PLANES; q++) {
+        const size_t n = static_cast<size_t>(m) * MMB_MX_PLANES + q;
+        *reinterpret_cast<uint16_t *>(p.planes + n * (p.K / 2u) + quarter * 2u) = static_cast<uint16_t>(codes[q]);
+        if ((tid & 3u) == 0) {
+            /* block scale of the plane, stored with the row's 2^G: 2^(U + 1 + s + G) in [2^-9, 2^8] */
+            const int sfe = U + 1 + mx_shift(q) + G;
+            const uint32_t byte = live ? (sfe >= -6 ? static_cast<uint32_t>(sfe + 7) << 3 : 1u << (sfe + 9)) : 0u;
+            p.sfb[n * blocks + blk] = static_cast<uint8_t>(byte);
+        }
+    }
+}
+
+/* ==========================================================================
+ * The linear kernel
+ * ========================================================================== */
+#ifdef MMB_MX_TRACE
+/* build-time option for timing studies: CTA 0 records the SM clock at the hand-offs
+ * of its first 32 K steps */
+__device__ long long g_mx_trace[12 * 32];
+#define MX_TRACE(ev, it) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (it) < 32u) g_mx_trace[(ev) * 32 + (it)] = clock64(); } while (0)
+#else
+#define MX_TRACE(ev, it) do { } while (0)
+#endif
+struct MxParams {
+    uint16_t       *y[MMB_MAX_PEERS];
+    uint32_t        n_dst, ldy, col0;
+    float          *partial;
+    unsigned       *counters;
+    unsigned       *status;
+    const float    *row_scale;
+    float           gs, gs_up;
+    uint32_t        gate_plane;
+    uint32_t        M, K, N;
+    uint32_t        k_steps, split_k, stages;
+    uint32_t        pdl;
+    uint32_t        rows;        /* weight rows per CTA: 256 or 128 (GLU: 256 = 128 of each projection) */
+    uint32_t        nb;          /* B rows: 6 x M padded to a multiple of four                          */
+};
+
+/* tensor memory map (512 columns): accumulators of the two 128-row halves at
+ * 0 and nb; scale-factor slots from 384 on, 64 columns each */
+#define MMB_MX_SF_COL   384u
+#define MMB_MX_SF_SLOT  64u
+#define MMB_MX_SFB_OFF  32u
+
+__device__ __forceinline__ void mx_store_all(const MxParams &p, uint32_t m, uint32_t n, uint16_t v)
+{
+    const size_t off = static_cast<size_t>(m) * p.ldy + p.col0 + n;
+    p.y[0][off] = v;
+#pragma unroll 1
+    for (uint32_t d = 1; d < p.n_dst; d++)
+        p.y[d][off] = v;
+}
+
+/* Sum of the six plane columns of one activation row, smallest plane first. */
+__device__ __forceinline__ float mx_row_sum(const uint32_t (&c)[24], int r)
+{
+    float v = __uint_as_float(c[6 * r]);
+#pragma unroll
+    for (int q = 1; q < MMB_MX_PLANES; q++) v += __uint_as_float(c[6 * r + q]);
+    return v;
+}
+
+template <bool GLU>
+__global__ void __launch_bounds__(MMB_MX_THREADS, 1)
+f4_mx_kernel(const __grid_constant__ TmaDesc tm_payload, const __grid_constant__ TmaDesc tm_scale,
+             const __grid_constant__ TmaDesc tm_planes, const __grid_constant__ TmaDesc tm_sfb,
+             const MxParams p)
+{
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t rows = p.rows, nb = p.nb, halves = rows >> 7;
+    const uint32_t pay_b = rows * 128u, pl_b = nb * 128u, sc_b = rows * 16u, sfb_b = nb * 16u;
+    const uint32_t stage_b = MMB_MX_STAGE_B(rows, nb);
+    const uint32_t o_pl = pay_b, o_sc = pay_b + pl_b, o_sfb = o_sc + sc_b;
+    const uint32_t bars = base + p.stages * stage_b;
+    const uint32_t bar_full = bars;                              /* [stages] TMA landed             */
+    const uint32_t bar_empty = bar_full + 8u * p.stages;         /* [stages] MMAs of the stage done */
+    const uint32_t bar_sf_full = bar_empty + 8u * p.stages;      /* [2] scale factors in tensor memory */
+    const uint32_t bar_accum = bar_sf_full + 16u;
+    const uint32_t tmem_slot = bar_accum + 8u;
+    const uint32_t last_flag = tmem_slot + 4u;
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t row0 = blockIdx.x * (GLU ? 128u : rows);     /* first weight row (of each projection) */
+    const uint32_t ks_begin = static_cast<uint32_t>(static_cast<uint64_t>(p.k_steps) * blockIdx.y / p.split_k);
+    const uint32_t ks_end = static_cast<uint32_t>(static_cast<uint64_t>(p.k_steps) * (blockIdx.y + 1) / p.split_k);
+    const uint32_t nsteps = ks_end - ks_begin;
+    const uint32_t first = nsteps < p.stages ? nsteps : p.stages;
+    const uint32_t stage_tx = pay_b + pl_b + sc_b + sfb_b;
+
+    if (tid == 0) {
+        tma_prefetch_desc(&tm_payload);
+        tma_prefetch_desc(&tm_scale);
+        tma_prefetch_desc(&tm_planes);
+        tma_prefetch_desc(&tm_sfb);
+        for (uint32_t s = 0; s < p.stages; s++) {
+            mbar_init(bar_full + 8u * s, 1u);
+            mbar_init(bar_empty + 8u * s, halves);       /* one commit per issuing thread */
+        }
+        for (uint32_t t = 0; t < 2u; t++)
+            mbar_init(bar_sf_full + 8u * t, 4u);
+        mbar_init(bar_accum, halves);
+        mbar_fence_init();
+        /* the weight boxes of the first ring go out before anything else */
+        for (uint32_t it = 0; it < first; it++) {
+            const uint32_t st = base + it * stage_b, ks = ks_begin + it;
+            mbar_expect_tx(bar_full + 8u * it, stage_tx);
+            if constexpr (GLU) {
+                tma_load_3d(st, &tm_payload, static_cast<int>(ks * 128u), static_cast<int>(row0), 0, bar_full + 8u * it);
+                tma_load_3d(st + o_sc, &tm_scale, static_cast<int>(ks * 16u), static_cast<int>(row0), 0, bar_full + 8u * it);
+            } else {
+                tma_load_2d(st, &tm_payload, static_cast<int>(ks * 128u), static_cast<int>(row0), bar_full + 8u * it);
+                tma_load_2d(st + o_sc, &tm_scale, static_cast<int>(ks * 16u), static_cast<int>(row0), bar_full + 8u * it);
+            }
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512u);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = lds32(tmem_slot);
+    if (p.pdl == MMB_PDL_TRIGGER_FIRST)
+        grid_dep_launch();
+
+    if (warp == 0) {
+        /* ------------------------------ TMA producer ------------------------ */
+        if (lane == 0) {
+            if (p.pdl == MMB_PDL_INDEPENDENT) {
+                grid_dep_launch();
+            } else {
+                grid_dep_wait();                 /* the digit planes come from the kernel in front */
+                if (p.pdl == MMB_PDL_WAIT_FIRST)
+                    grid_dep_launch();
+            }
+            for (uint32_t it = 0; it < first; it++) {
+                const uint32_t st = base + it * stage_b, ks = ks_begin + it;
+                tma_load_2d(st + o_pl, &tm_planes, static_cast<int>(ks * 128u), 0, bar_full + 8u * it);
+                tma_load_2d(st + o_sfb, &tm_sfb, static_cast<int>(ks * 16u), 0, bar_full + 8u * it);
+                MX_TRACE(0, it);
+            }
+            uint32_t s = 0, round = 1;
+            for (uint32_t it = first; it < nsteps; it++, s = (s + 1u == p.stages) ? 0u : s + 1u, round += (s == 0u)) {
+                const uint32_t st = base + s * stage_b, ks = ks_begin + it, bar = bar_full + 8u * s;
+                mbar_wait(bar_empty + 8u * s, (round - 1u) & 1u, p.status);
+                mbar_expect_tx(bar, stage_tx);
+                if constexpr (GLU) {
+                    tma_load_3d(st, &tm_payload, static_cast<int>(ks * 128u), static_cast<int>(row0), 0, bar);
+                    tma_load_3d(st + o_sc, &tm_scale, static_cast<int>(ks * 16u), static_cast<int>(row0), 0, bar);
+                } else {
+                    tma_load_2d(st, &tm_payload, static_cast<int>(ks * 128u), static_cast<int>(row0), bar);
+                    tma_load_2d(st + o_sc, &tm_scale, static_cast<int>(ks * 16u), static_cast<int>(row0), bar);
+                }
+                tma_load_2d(st + o_pl, &tm_planes, static_cast<int>(ks * 128u), 0, bar);
+                tma_load_2d(st + o_sfb, &tm_sfb, static_cast<int>(ks * 16u), 0, bar);
+                MX_TRACE(0, it);
+            }
+            if (p.pdl == MMB_PDL_INDEPENDENT)
+                grid_dep_wait();                 /* this kernel completes after its predecessor */
+        }
+    } else if (warp == 1 || warp == 10) {
+        /* ------------------------------ MMA issue ---------------------------- *
+         * One thread per 128-row half: eight MMAs per K step cost one thread more
+         * issue time than the step's weights take to arrive. */
+        const uint32_t h = warp == 1 ? 0u : 1u;
+        if (lane == 0 && h < halves) {
+            const uint32_t idesc = umma_idesc_mxf4(nb);
+            uint32_t s = 0, round = 0;
+            for (uint32_t it = 0; it < nsteps; it++, s = (s + 1u == p.stages) ? 0u : s + 1u, round += (s == 0u)) {
+                const uint32_t t = it & 1u, st = base + s * stage_b;
+                mbar_wait(bar_full + 8u * s, round & 1u, p.status);
+                if (h == 0) MX_TRACE(1, it);
+                mbar_wait(bar_sf_full + 8u * t, (it >> 1) & 1u, p.status);
+                tc_fence_after();
+                if (h == 0) MX_TRACE(2, it);
+                const uint32_t sf = tmem + MMB_MX_SF_COL + t * MMB_MX_SF_SLOT;
+                const uint64_t ad = umma_desc_sw128(st + h * 16384u), bd = umma_desc_sw128(st + o_pl);
+#pragma unroll
+                for (uint32_t j = 0; j < 4u; j++)       /* 32 bytes along K per slice: + 2 in the address field */
+                    umma_mxf4(tmem + h * nb, ad + 2u * j, bd + 2u * j, idesc, (it | j) ? 1u : 0u,
+                              sf + h * 16u + 4u * j, sf + MMB_MX_SFB_OFF + 8u * j);
+                umma_commit(bar_empty + 8u * s);       /* frees the stage and, two steps on, the scale slot */
+                if (h == 0) MX_TRACE(3, it);
+            }
+            umma_commit(bar_accum);
+        }
+    } else {
+        /* ------------------------------ scale factors ------------------------ *
+         * Lane l of a slot's column c holds the four scale bytes (K = 64) of row
+         * 32 c + l; every lane quadrant holds a copy, so the four warps write the
+         * same values, each into its own quadrant. */
+        const uint32_t quad = warp & 3u;
+        const uint32_t mine_t = (warp - 2u) >> 2;      /* this warp fills slot 0 (even steps) or 1 (odd steps) */
+        const uint32_t tq = tmem + ((quad * 32u) << 16);
+        const uint32_t ncol = (nb + 31u) >> 5;
+        uint32_t s = 0, round = 0;
+        uint32_t s1 = 0, round1 = 0, s2 = 0, round2 = 0;      /* stage and use count of the steps one and two back */
+        for (uint32_t it = 0; it < nsteps; it++, s2 = s1, round2 = round1, s1 = s, round1 = round,
+                                           s = (s + 1u == p.stages) ? 0u : s + 1u, round += (s == 0u)) {
+            const uint32_t t = it & 1u, st = base + s * stage_b;
+            if (t != mine_t)
+                continue;
+            mbar_wait_warp(bar_full + 8u * s, round & 1u, p.status);
+            if (warp == 2u && lane == 0) MX_TRACE(4, it);
+            if (it >= 2u)                        /* the slot is free once the MMAs of step it - 2 are done */
+                mbar_wait_warp(bar_empty + 8u * s2, round2 & 1u, p.status);
+            tc_fence_after();
+            if (warp == 2u && lane == 0) MX_TRACE(5, it);
+            const uint32_t sf = tq + MMB_MX_SF_COL + t * MMB_MX_SF_SLOT;
+            bool patched = false;
+            uint32_t v[64];                      /* the slot: A scales of both halves, then B scales */
+            uint4 qa[8];
+#pragma unroll
+            for (uint32_t i = 0; i < 8u; i++) {
+                qa[i] = make_uint4(0u, 0u, 0u, 0u);
+                if ((i >> 2) < halves)
+                    qa[i] = lds128(st + o_sc + ((i >> 2) * 128u + 32u * (i & 3u) + lane) * 16u);
+            }
+            if (warp == 2u && lane == 0) MX_TRACE(8, it);
+            /* Branch-free on the common path (a lone warp pays dearly for every
+             * branch): 0x7f and 0xff, zero in the reference, are cleared; sign bits
+             * are cleared and collected. */
+            uint32_t negs = 0u;
+#pragma unroll
+            for (uint32_t i = 0; i < 8u; i++) {
+                const uint32_t w[4] = { qa[i].x, qa[i].y, qa[i].z, qa[i].w };
+#pragma unroll
+                for (uint32_t j = 0; j < 4u; j++) {
+                    const uint32_t nan = (((w[j] & 0x7f7f7f7fu) + 0x01010101u) & 0x80808080u) >> 7;
+                    const uint32_t clean = w[j] & ~(nan * 0xffu);
+                    negs |= clean & 0x80808080u;
+                    v[(i >> 2) * 16u + 4u * j + (i & 3u)] = clean & 0x7f7f7f7fu;
+                }
+            }
+            if (__any_sync(0xffffffffu, negs != 0u)) {
+                /* negative block scales (no packer writes them, the reference decodes
+                 * them): flip the signs of the block's 16 weights in shared memory
+                 * instead; one warp does it, every warp has cleared the sign bits */
+                if (quad == 2u && negs) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 8u; i++) {
+                        const uint32_t r = (i >> 2) * 128u + 32u * (i & 3u) + lane;
+                        const uint32_t w[4] = { qa[i].x, qa[i].y, qa[i].z, qa[i].w };
+#pragma unroll
+                        for (uint32_t j = 0; j < 4u; j++) {
+                            const uint32_t nan = (((w[j] & 0x7f7f7f7fu) + 0x01010101u) & 0x80808080u) >> 7;
+                            const uint32_t neg = w[j] & ~(nan * 0xffu) & 0x80808080u;
+                            for (uint32_t b = 0; neg && b < 4u; b++)
+                                if (neg & (0x80u << (8u * b))) {
+                                    const uint32_t o = (4u * j + b) * 8u;
+                                    const uint32_t a = st + r * 128u + ((((o >> 4) ^ (r & 7u)) << 4) | (o & 15u));
+                                    sts32(a, lds32(a) ^ 0x88888888u);
+                                    sts32(a + 4u, lds32(a + 4u) ^ 0x88888888u);
+                                }
+                        }
+                    }
+                }
+                patched = true;
+            }
+            if (warp == 2u && lane == 0) MX_TRACE(9, it);
+#pragma unroll
+            for (uint32_t c = 0; c < 8u; c++) {
+                const uint32_t r = 32u * c + lane;
+                uint4 q = make_uint4(0u, 0u, 0u, 0u);
+                if (c < ncol && r < nb)
+                    q = lds128(st + o_sfb + r * 16u);
+                v[MMB_MX_SFB_OFF + c] = q.x;
+                v[MMB_MX_SFB_OFF + 8u + c] = q.y;
+                v[MMB_MX_SFB_OFF + 16u + c] = q.z;
+                v[MMB_MX_SFB_OFF + 24u + c] = q.w;
+            }
+            if (warp == 2u && lane == 0) MX_TRACE(10, it);
+            tmem_st_x64(sf, v);
+            if (warp == 2u && lane == 0) MX_TRACE(6, it);
+            tmem_st_wait();
+            if (warp == 2u && lane == 0) MX_TRACE(7, it);
+            if (patched)
+                fence_proxy_async_smem();        /* the tensor core reads the rewritten payload */
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(bar_sf_full + 8u * t);
+        }
+
+        /* ------------------------------ epilogue ----------------------------- *
+         * Thread = weight row (lane of tensor memory); four activation rows (24
+         * plane columns) at a time.  One warp per quadrant. */
+        if (mine_t != 0u)
+            goto done;
+        mbar_wait_warp(bar_accum, 0u, p.status);
+        tc_fence_after();
+        grid_dep_wait();                         /* row factors come from the kernel in front */
+        const uint32_t lr = quad * 32u + lane;   /* row within a half */
+        const uint32_t groups = nb / 24u;
+        const bool direct = p.split_k == 1u;
+        const uint32_t pitch = GLU ? gridDim.x * 256u : p.N;   /* partials: one column per weight row of the tiles */
+        float *mine = p.partial + static_cast<size_t>(blockIdx.y) * (groups * 4u) * pitch;
+        for (uint32_t g = 0; g < groups; g++) {
+            uint32_t c0[24], c1[24];
+            tmem_ld_x8(tq + g * 24u, *reinterpret_cast<uint32_t (*)[8]>(&c0[0]));
+            tmem_ld_x8(tq + g * 24u + 8u, *reinterpret_cast<uint32_t (*)[8]>(&c0[8]));
+            tmem_ld_x8(tq + g * 24u + 16u, *reinterpret_cast<uint32_t (*)[8]>(&c0[16]));
+            if (halves == 2u) {
+                tmem_ld_x8(tq + nb + g * 24u, *reinterpret_cast<uint32_t (*)[8]>(&c1[0]));
+                tmem_ld_x8(tq + nb + g * 24u + 8u, *reinterpret_cast<uint32_t (*)[8]>(&c1[8]));
+                tmem_ld_x8(tq + nb + g * 24u + 16u, *reinterpret_cast<uint32_t (*)[8]>(&c1[16]));
+            }
+            tmem_ld_wait();
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+                const uint32_t m = g * 4u + r;
+                if (m >= p.M)
+                    break;
+                const float f1 = __ldcg(p.row_scale + 2u * m), f2 = __ldcg(p.row_scale + 2u * m + 1u);
+                const float a0 = mx_row_sum(c0, r) * f1 * f2;
+                const float a1 = halves == 2u ? mx_row_sum(c1, r) * f1 * f2 : 0.0f;
+                if constexpr (GLU) {
+                    /* half 0 = plane 0 of the pair, half 1 = plane 1; one output per thread */
+                    const uint32_t n = row0 + lr;
+                    if (direct) {
+                        if (n < p.N)
+                            mx_store_all(p, m, n, glu_out_bf16(p.gate_plane ? a1 : a0, p.gate_plane ? a0 : a1,
+                                                               p.gs, p.gs_up));
+                    } else if (n < p.N) {
+                        __stcg(mine + static_cast<size_t>(m) * pitch + blockIdx.x * 256u + lr, a0);
+                        __stcg(mine + static_cast<size_t>(m) * pitch + blockIdx.x * 256u + 128u + lr, a1);
+                    }
+                } else {
+#pragma unroll
+                    for (uint32_t h = 0; h < 2u; h++) {
+                        if (h >= halves)
+                            break;
+                        const uint32_t n = row0 + h * 128u + lr;
+                        const float a = h ? a1 : a0;
+                        if (n >= p.N)
+                            continue;
+                        if (direct) {
+                            __nv_bfloat16 hv = __float2bfloat16_rn(a * p.gs);
+                            mx_store_all(p, m, n, *reinterpret_cast<uint16_t *>(&hv));
+                        } else {
+                            __stcg(mine + static_cast<size_t>(m) * pitch + n, a);
+                        }
+                    }
+                }
+            }
+        }
+        if (!direct) {
+            /* split-K: the CTA of a row tile that arrives last adds the slices in
+             * ascending order (results do not depend on scheduling) */
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (tid == 64u) {
+                __threadfence();
+                const unsigned ticket = atomicAdd(p.counters + blockIdx.x, 1u);
+                __threadfence();
+                sts32(last_flag, (ticket == p.split_k - 1u) ? 1u : 0u);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (lds32(last_flag)) {
+                const size_t slice = static_cast<size_t>(groups * 4u) * pitch;
+                for (uint32_t m = 0; m < p.M; m++) {
+                    float s0 = 0.0f, s1 = 0.0f;
+                    if constexpr (GLU) {
+                        const float *src = p.partial + static_cast<size_t>(m) * pitch + blockIdx.x * 256u + lr;
+                        const bool ok = row0 + lr < p.N;
+                        for (uint32_t sl = 0; ok && sl < p.split_k; sl++) {
+                            s0 += __ldcg(src + sl * slice);
+                            s1 += __ldcg(src + sl * slice + 128u);
+                        }
+                        if (ok)
+                            mx_store_all(p, m, row0 + lr, glu_out_bf16(p.gate_plane ? s1 : s0, p.gate_plane ? s0 : s1,
+                                                                       p.gs, p.gs_up));
+                    } else {
+                        const uint32_t n0 = row0 + lr, n1 = n0 + 128u;
+                        const bool ok0 = n0 < p.N, ok1 = halves == 2u && n1 < p.N;
+                        const float *src = p.partial + static_cast<size_t>(m) * pitch;
+                        for (uint32_t sl = 0; sl < p.split_k; sl++) {
+                            if (ok0) s0 += __ldcg(src + sl * slice + n0);
+                            if (ok1) s1 += __ldcg(src + sl * slice + n1);
+                        }
+                        if (ok0) {
+                            __nv_bfloat16 hv = __float2bfloat16_rn(s0 * p.gs);
+                            mx_store_all(p, m, n0, *reinterpret_cast<uint16_t *>(&hv));
+                        }
+                        if (ok1) {
+                            __nv_bfloat16 hv = __float2bfloat16_rn(s1 * p.gs);
+                            mx_store_all(p, m, n1, *reinterpret_cast<uint16_t *>(&hv));
+                        }
+                    }
+                }
+                if (tid == 64u)
+                    p.counters[blockIdx.x] = 0u;
+            }
+        }
+    }
+
+done:
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512u);
+    }
+}
+
+static void fill_desc(TmaDesc &d, const unsigned char *src) { memcpy(d.bytes, src, 128); }
+
+template <bool GLU>
+static int launch_mx(const mmb_args *a, unsigned *status, cudaStream_t st)
+{
+    MxParams p;
+    if (a->n_dst) {
+        for (uint32_t d = 0; d < a->n_dst; d++) p.y[d] = static_cast<uint16_t *>(a->y_dst[d]);
+        p.n_dst = a->n_dst; p.ldy = a->ldy; p.col0 = a->col0;
+    } else {
+        p.y[0] = static_cast<uint16_t *>(a->y);
+        p.n_dst = 1; p.ldy = a->N; p.col0 = 0;
+    }
+    unsigned char *ws = static_cast<unsigned char *>(a->ws);
+    p.counters = reinterpret_cast<unsigned *>(ws);
+    p.partial = reinterpret_cast<float *>(ws + a->mx_partial_off);
+    p.row_scale = reinterpret_cast<const float *>(static_cast<const unsigned char *>(a->mx_x_ws) + MMB_MX_ROWSCALE_OFF);
+    p.status = status;
+    p.gs = a->gs; p.gs_up = a->gs_up;
+    p.gate_plane = a->gate_plane ? 1u : 0u;
+    p.M = a->M; p.K = a->K; p.N = a->N;
+    p.k_steps = a->plan.k_steps; p.split_k = a->plan.split_k; p.stages = a->plan.stages;
+    p.pdl = static_cast<uint32_t>(a->pdl);
+    p.rows = a->plan.tile_n;
+    p.nb = a->plan.tile_m;
+    TmaDesc tp, ts, tx, tf;
+    fill_desc(tp, a->tm_payload);
+    fill_desc(ts, a->tm_scale);
+    fill_desc(tx, a->tm_x);
+    fill_desc(tf, a->tm_sfb);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(a->plan.grid_x, a->plan.grid_y);
+    cfg.blockDim = dim3(MMB_MX_THREADS);
+    cfg.dynamicSmemBytes = a->plan.smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = a->pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, f4_mx_kernel<GLU>, tp, ts, tx, tf, p));
+}
+
+} // namespace mmb
+
+#ifdef MMB_MX_TRACE
+extern "C" int mmb_mx_trace_read(long long *out)
+{
+    return static_cast<int>(cudaMemcpyFromSymbol(out, mmb::g_mx_trace, sizeof(long long) * 12 * 32));
+}
+#endif
+
+extern "C" int mmb_mx_init(void)
+{
+    cudaError_t e = cudaFuncSetAttribute(mmb::f4_mx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         MMB_SMEM_MAX);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    e = cudaFuncSetAttribute(mmb::f4_mx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MMB_SMEM_MAX);
+    return static_cast<int>(e);
+}
+
+/* Digit planes of the activations into the op's scratch (a->mx_x_ws). */
+extern "C" int mmb_launch_xslice(const mmb_args *a, void *stream)
+{
+    mmb::XsliceParams p;
+    unsigned char *xs = static_cast<unsigned char *>(a->mx_x_ws);
+    const uint32_t m_pad = a->plan.tile_m / MMB_MX_PLANES;
+    p.x = static_cast<const uint16_t *>(a->x);
+    p.row_scale = reinterpret_cast<float *>(xs + MMB_MX_ROWSCALE_OFF);
+    p.planes = xs + MMB_MX_PLANES_OFF;
+    p.sfb = xs + MMB_MX_PLANES_OFF + MMB_MX_PLANES_B(a->plan.tile_m, a->K);
+    p.M = a->M; p.K = a->K; p.m_pad = m_pad;
+    p.pdl = static_cast<uint32_t>(a->pdl);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((a->K / 4u + 255u) / 256u, m_pad);
+    cfg.blockDim = dim3(256);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = a->pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, mmb::f4_xslice_kernel, p));
+}
+
+extern "C" int mmb_launch_mx(const mmb_args *a, void *stream)
+{
+    unsigned *status = nullptr;
+    int e = mmb_status_word(&status);
+    if (e) return e;
+    if (!a->ws || !a->mx_x_ws)
+        return static_cast<int>(cudaErrorInvalidValue);
+    if ((a->plan.tile_n != 256u && a->plan.tile_n != 128u) || (a->glu && a->plan.tile_n != 256u) ||
+        a->plan.tile_m == 0 || a->plan.tile_m % 24u != 0 || a->plan.tile_m > 192u)
+        return static_cast<int>(cudaErrorInvalidValue);
+    if (a->glu && a->n_dst)
+        return static_cast<int>(cudaErrorInvalidValue);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return a->glu ? mmb::launch_mx<true>(a, status, st) : mmb::launch_mx<false>(a, status, st);
+}

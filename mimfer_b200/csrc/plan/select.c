@@ -8,9 +8,15 @@
  * "M<=8: split-K gemv, else dequant + bf16 mma gemm" (include/mimfer/plan.h:51-52).
  * This file is that choice for B200:
  *
- *   STREAM   M <= 32.  HBM-bound.  One CTA streams 256 weight rows through a
- *            TMA pipeline; K is split across CTAs until about one CTA per SM
- *            exists, partials meet in the workspace in a fixed order.
+ *   MX       M <= 32 with a workspace.  HBM-bound.  The block-scaled tensor
+ *            path: payload and block scales are the MMA's operands as they lie
+ *            in memory, the activations are re-expressed as e2m1 digit planes by
+ *            a small kernel in front (scratch in the workspace).  Same tiling as
+ *            STREAM.
+ *   STREAM   M <= 32 without a workspace (or when asked for).  One CTA streams
+ *            256 weight rows through a TMA pipeline and dequantises on the CUDA
+ *            cores; K is split across CTAs until about one CTA per SM exists,
+ *            partials meet in the workspace in a fixed order.
  *   UMMA     M > 32.  tcgen05 tiles of tile_m x tile_n; the tile shape is the
  *            one with the lowest modelled time (waves x per-tile cost).
  *   ROWWARP  anything the two above cannot take (K not a multiple of 256,
@@ -98,6 +104,75 @@ static mm_status plan_stream(const mm_f4_shape *s, mm_f4_plan *p)
     uint32_t max_split = k_steps / 4 ? k_steps / 4 : 1;
     uint32_t rows = ceil_div(s->N, MMB_ST_ROWS) * max_split * 4u < sms ? MMB_ST_ROWS / 2 : MMB_ST_ROWS;
     return plan_stream_with(s, rows, 0, p);
+}
+
+/* MX plan: `rows` weight rows per CTA (256 or 128), K cut into `split` slices
+ * (0 = about one CTA per SM).  Workspace of the op: arrival counters, the
+ * activation scratch (row factors, digit planes, their block scales), split-K
+ * partials.  `glu_rows`: weight rows including tile padding when the op is a
+ * gated pair (partials are laid out per 256-row tile), else 0. */
+static mm_status plan_mx_with(const mm_f4_shape *s, uint32_t rows, uint32_t split, uint32_t glu_rows,
+                              mm_f4_plan *p)
+{
+    if (!fast_path_ok(s) || s->M > 32)
+        return MM_ERR_UNSUPPORTED;
+    if (rows != 256u && rows != 128u)
+        return MM_ERR_RANGE;
+    const uint32_t n_rows = glu_rows ? glu_rows : s->N;
+    memset(p, 0, sizeof *p);
+    p->variant = MM_F4_V_MX;
+    p->m_tiles = (s->M + 3u) / 4u;                 /* groups of four activation rows */
+    p->tile_m = p->m_tiles * 4u * MMB_MX_PLANES;   /* B rows: six digit planes per activation row */
+    p->tile_n = rows;
+    p->k_steps = s->K / MMB_ST_KSTEP;
+    p->grid_x = ceil_div(n_rows, rows);
+    p->threads = MMB_MX_THREADS;
+    const size_t xs = MMB_WS_COUNTER_B + MMB_MX_XS_B(p->tile_m, s->K);
+    if (xs > s->ws_bytes)
+        return MM_ERR_UNSUPPORTED;                 /* no room for the digit planes: the CUDA-core kernel runs */
+
+    uint32_t sms = s->sm_count ? s->sm_count : 148;
+    uint32_t sk = split ? split : sms / p->grid_x;
+    if (sk < 1) sk = 1;
+    uint32_t max_by_steps = p->k_steps / 4 ? p->k_steps / 4 : 1;
+    if (sk > max_by_steps) sk = max_by_steps;
+    if (sk > 32) sk = 32;
+    if (p->grid_x > MMB_WS_MAX_TILES) sk = 1;
+    p->ws_needed = xs;
+    while (sk > 1) {
+        size_t need = xs + (size_t)sk * p->m_tiles * 4u * ((size_t)p->grid_x * rows) * 4u;
+        if (need <= s->ws_bytes) { p->ws_needed = need; break; }
+        sk--;
+    }
+    p->split_k = sk;
+    p->grid_y = sk;
+    p->grid_z = 1;
+    uint32_t stage = MMB_MX_STAGE_B(rows, p->tile_m);
+    uint32_t st = (MMB_SMEM_MAX - MMB_MX_FIXED_B) / stage;
+    if (st > 6) st = 6;
+    uint32_t per = ceil_div(p->k_steps, sk);
+    if (st > per) st = per;
+    if (st < 1) st = 1;
+    p->stages = st;
+    p->smem_bytes = st * stage + MMB_MX_FIXED_B;
+    return MM_OK;
+}
+
+static mm_status plan_mx(const mm_f4_shape *s, mm_f4_plan *p)
+{
+    /* half-height tiles for weights that 256-row tiles cannot spread over the SMs
+     * (the rule of the STREAM plan below) */
+    uint32_t sms = s->sm_count ? s->sm_count : 148;
+    uint32_t k_steps = s->K / MMB_ST_KSTEP;
+    uint32_t max_split = k_steps / 4 ? k_steps / 4 : 1;
+    uint32_t rows = ceil_div(s->N, 256u) * max_split * 4u < sms ? 128u : 256u;
+    return plan_mx_with(s, rows, 0, 0, p);
+}
+
+mm_status mmb_plan_mx_with(const mm_f4_shape *s, uint32_t rows, uint32_t split, mm_f4_plan *p)
+{
+    mm_status st = check_shape(s, p);
+    return st != MM_OK ? st : plan_mx_with(s, rows ? rows : 256u, split, 0, p);
 }
 
 mm_status mmb_plan_stream_with(const mm_f4_shape *s, uint32_t rows, uint32_t split, mm_f4_plan *p)
@@ -199,6 +274,7 @@ mm_status mm_f4_select_variant(const mm_f4_shape *s, int variant, mm_f4_plan *ou
     case MM_F4_V_STREAM:  return plan_stream(s, out);
     case MM_F4_V_UMMA:    return plan_umma(s, out);
     case MM_F4_V_STREAMT: return plan_streamt(s, out);
+    case MM_F4_V_MX:      return plan_mx(s, out);
     default:              return MM_ERR_RANGE;
     }
 }
@@ -209,6 +285,11 @@ mm_status mm_f4_select_variant(const mm_f4_shape *s, int variant, mm_f4_plan *ou
  * the fused form; anything else is MM_ERR_UNSUPPORTED and runs as three ops. */
 mm_status mm_f4_select_glu(const mm_f4_shape *s, mm_f4_plan *out)
 {
+    return mmb_select_glu(s, 0, out);
+}
+
+mm_status mmb_select_glu(const mm_f4_shape *s, int allow_mx, mm_f4_plan *out)
+{
     mm_status st = check_shape(s, out);
     if (st != MM_OK)
         return st;
@@ -216,8 +297,12 @@ mm_status mm_f4_select_glu(const mm_f4_shape *s, mm_f4_plan *out)
         return MM_ERR_UNSUPPORTED;
     mm_f4_shape rows = *s;
     rows.N = ceil_div(s->N, MMB_ST_ROWS / 2) * MMB_ST_ROWS;      /* weight rows incl. tile padding */
-    if (s->M <= 32)
+    if (s->M <= 32) {
+        /* the tile padding only counts rows: the planes' size follows K and M */
+        if (allow_mx && plan_mx_with(s, 256u, 0, rows.N, out) == MM_OK)
+            return MM_OK;
         return plan_stream_with(&rows, MMB_ST_ROWS, 0, out);       /* partials are laid out per 256-row tile */
+    }
     if (s->N % 8 != 0)
         return MM_ERR_UNSUPPORTED;
     uint32_t sms = s->sm_count ? s->sm_count : 148;

@@ -267,6 +267,16 @@ class LinearEngine:
         self._keep.append((gate, up, y))
         L.check(self.rt.lib.mm_lin_engine_add(self.h, C.byref(d)), "mm_lin_engine_add")
 
+    def add_add_rmsnorm(self, res, delta, y, gain):
+        """OP_ADD_RMSNORM: res += delta in place, y = rmsnorm(res) * gain (src/plan/plan.c:446-447)."""
+        d = L.MmOpDesc()
+        d.op, d.layer = L.OP_ADD_RMSNORM, -1
+        d.a, d.b, d.c, d.d = res.data_ptr(), delta.data_ptr(), y.data_ptr(), gain.data_ptr()
+        d.n0, d.n1, d.n2 = res.shape[0], res.shape[1], 0
+        d.note = b"add_rmsnorm"
+        self._keep.append((res, delta, y, gain))
+        L.check(self.rt.lib.mm_lin_engine_add(self.h, C.byref(d)), "mm_lin_engine_add")
+
     def overlap(self, on=True):
         """Dependency-aware launch order (mm_lin_engine_overlap): 1 = bits of the serial
         order, 2 = run-ahead ops may also take a shallower K split."""

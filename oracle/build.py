@@ -5,7 +5,7 @@
   _ref/libmimfer_ref.so   the reference's own CPU kernel, compiled from the
                           sources where they lie in the read-only reference
                           tree (src/kernels/cpu/cx.c + src/core/mimfer.c) plus
-                          oracle/ref_driver.c.  Only built when that tree is
+                          oracle/ref_driver.c and oracle/ref_driver_norm.c.  Only built when that tree is
                           mounted; the prebuilt file is used otherwise.
 
 Run:  python oracle/build.py
@@ -53,7 +53,8 @@ def build_ref(force=False):
         return REF_SO if os.path.exists(REF_SO) else None
     src = [os.path.join(REF, "src", "kernels", "cpu", "cx.c"),
            os.path.join(REF, "src", "core", "mimfer.c"),
-           os.path.join(HERE, "ref_driver.c")]
+           os.path.join(HERE, "ref_driver.c"),
+           os.path.join(HERE, "ref_driver_norm.c")]
     if not force and _newer(REF_SO, src):
         return REF_SO
     os.makedirs(os.path.dirname(REF_SO), exist_ok=True)

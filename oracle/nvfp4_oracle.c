@@ -173,6 +173,38 @@ void orc_silu_mul(const uint16_t *gate, const uint16_t *up, uint16_t *y, size_t 
     }
 }
 
+/* Residual add + RMSNorm, the reference's OP_ADD_RMSNORM
+ * (src/kernels/cpu/cx.c:70-84 and 132-150): per row, res[i] = bf16(res[i] +
+ * delta[i]) in place; ss = sum of squares of the rounded row, fp32, ascending;
+ * inv = 1 / sqrtf(ss / H + eps); y[i] = bf16(res[i] * inv * gain[i]), multiplied
+ * left to right. */
+void orc_add_rmsnorm(uint16_t *res, const uint16_t *delta, uint16_t *y, const uint16_t *gain,
+                     uint32_t M, uint32_t H, float eps)
+{
+    for (uint32_t m = 0; m < M; m++) {
+        uint16_t *rr = res + (size_t)m * H;
+        const uint16_t *dr = delta + (size_t)m * H;
+        uint16_t *yr = y + (size_t)m * H;
+        for (uint32_t i = 0; i < H; i++) {
+            float s = orc_f32_from_bf16(rr[i]) + orc_f32_from_bf16(dr[i]);
+            rr[i] = orc_bf16_from_f32(s);
+        }
+        float ss = 0.0f;
+        for (uint32_t i = 0; i < H; i++) {
+            float v = orc_f32_from_bf16(rr[i]);
+            float sq = v * v;
+            ss += sq;
+        }
+        float mean = ss / (float)H;
+        float inv = 1.0f / sqrtf(mean + eps);
+        for (uint32_t i = 0; i < H; i++) {
+            float t = orc_f32_from_bf16(rr[i]) * inv;
+            float o = t * orc_f32_from_bf16(gain[i]);
+            yr[i] = orc_bf16_from_f32(o);
+        }
+    }
+}
+
 /* Whole op, reference operand order: y[M][N]. */
 int orc_gemm_f4(const uint16_t *x, const uint8_t *payload, const uint8_t *scale,
                 float gs, uint16_t *y, uint32_t M, uint32_t K, uint32_t N, int threads)

@@ -41,6 +41,18 @@ class Oracle:
         self.lib.orc_bf16_from_f32.argtypes = [C.c_float]
         self.lib.orc_silu_mul.restype = None
         self.lib.orc_silu_mul.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]
+        self.lib.orc_add_rmsnorm.restype = None
+        self.lib.orc_add_rmsnorm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                             C.c_uint32, C.c_uint32, C.c_float]
+
+    def add_rmsnorm(self, res, delta, gain, eps):
+        """bf16 bit patterns [M][H], [M][H], [H]; returns (res + delta, normalised output)."""
+        res = np.array(res, np.uint16, copy=True, order="C")
+        delta = np.ascontiguousarray(delta, np.uint16)
+        gain = np.ascontiguousarray(gain, np.uint16)
+        y = np.empty(res.shape, np.uint16)
+        self.lib.orc_add_rmsnorm(_p(res), _p(delta), _p(y), _p(gain), res.shape[0], res.shape[1], eps)
+        return res, y
 
     def silu_mul(self, gate, up):
         """bf16 bit patterns in, bf16 bit patterns out, same shape."""
@@ -99,6 +111,9 @@ class Reference:
         self.lib = C.CDLL(path)
         self.lib.ref_silu_mul.restype = C.c_int
         self.lib.ref_silu_mul.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32]
+        self.lib.ref_add_rmsnorm.restype = C.c_int
+        self.lib.ref_add_rmsnorm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                             C.c_uint32, C.c_uint32, C.c_float]
         for name, extra in (("ref_gemm_f4", []), ("ref_gemm_f4_mt", [C.c_int])):
             fn = getattr(self.lib, name)
             fn.restype = C.c_int
@@ -111,6 +126,14 @@ class Reference:
         y = np.empty(gate.shape, np.uint16)
         rc = self.lib.ref_silu_mul(_p(gate), _p(up), _p(y), gate.size)
         return rc, y
+
+    def add_rmsnorm(self, res, delta, gain, eps):
+        res = np.array(res, np.uint16, copy=True, order="C")
+        delta = np.ascontiguousarray(delta, np.uint16)
+        gain = np.ascontiguousarray(gain, np.uint16)
+        y = np.empty(res.shape, np.uint16)
+        rc = self.lib.ref_add_rmsnorm(_p(res), _p(delta), _p(y), _p(gain), res.shape[0], res.shape[1], eps)
+        return rc, res, y
 
     def gemm_f4(self, x, payload, scales, threads=1):
         M, K = x.shape

@@ -12,6 +12,10 @@ oracle/build.py looks for it; the fixtures are committed so the tests do not.
   silu_mul.npz          the reference kx_op_silu_mul (src/kernels/cpu/cx.c:155-167) on
                         every bf16 bit pattern as the gate against seeded random up
                         bits (PCG64 seed 5; only the output is stored).
+  add_rmsnorm.npz       the reference kx_op_add_rmsnorm (src/kernels/cpu/cx.c:132-150) on
+                        seeded rows: residual N(0, 1) + a few large and tiny values, delta
+                        N(0, 0.5), gain N(1, 0.1), eps 1e-6; hidden sizes 64, 1000 and 5120.
+                        Inputs are regenerated from the seeds, outputs are stored.
   seeded_<M>x<K>x<N>.npz  weights from the library's packer + generator (seed 0,
                         N(0, 0.02)), activations seed 1 N(0, 1); stores the
                         reference output, the global scale the packer chose and
@@ -32,6 +36,20 @@ from oracle.pyoracle import Reference        # noqa: E402
 
 SEEDED = [(1, 256, 64), (3, 512, 40), (5, 1024, 96), (8, 768, 33), (16, 2048, 128),
           (2, 5120, 64), (33, 256, 72)]
+
+
+ADD_RMSNORM_SHAPES = [(1, 64), (3, 1000), (4, 5120)]
+ADD_RMSNORM_EPS = 1.0e-6
+
+
+def add_rmsnorm_inputs(M, H):
+    """Seeded inputs of the add + RMSNorm fixture (bf16 bit patterns)."""
+    res = mm.linear.fill_normal(M, H, 100 + H, 0.0, 1.0)
+    res[0, 1] = 300.0
+    res[M - 1, H // 2] = -2.0e-5
+    delta = mm.linear.fill_normal(M, H, 200 + H, 0.0, 0.5)
+    gain = mm.linear.fill_normal(1, H, 300 + H, 1.0, 0.1)
+    return mm.linear.f32_to_bf16(res), mm.linear.f32_to_bf16(delta), mm.linear.f32_to_bf16(gain)[0]
 
 
 def fnv1a64(a):
@@ -81,6 +99,15 @@ def main():
     rc, y = ref.silu_mul(gate, up)
     assert rc == 0
     np.savez_compressed(os.path.join(HERE, "silu_mul.npz"), y=y)
+
+    norm = {}
+    for (M, H) in ADD_RMSNORM_SHAPES:
+        res, delta, gain = add_rmsnorm_inputs(M, H)
+        rc, res_out, y = ref.add_rmsnorm(res, delta, gain, ADD_RMSNORM_EPS)
+        assert rc == 0
+        norm[f"res_{M}x{H}"] = res_out
+        norm[f"y_{M}x{H}"] = y
+    np.savez_compressed(os.path.join(HERE, "add_rmsnorm.npz"), **norm)
 
     for (M, K, N) in SEEDED:
         w = mm.make_weight(N, K, seed=0, std=0.02)

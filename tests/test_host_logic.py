@@ -26,7 +26,7 @@ def test_dispatcher_null_checks(lib):
 def test_dispatcher_routes_only_owned_opcodes(lib):
     lib.mm_log_set_level(-1)
     for op in range(19):
-        owned = (L.OP_GEMM_F4, L.OP_QKV, L.OP_LMHEAD, L.OP_SILU_MUL, L.OP_NOP)
+        owned = (L.OP_GEMM_F4, L.OP_QKV, L.OP_LMHEAD, L.OP_SILU_MUL, L.OP_ADD_RMSNORM, L.OP_NOP)
         assert lib.kx_cuda_oppref(op) == (1 if op in owned else 0)
     kc, _ = kcall(op=L.OP_NOP)
     assert lib.mm_kx_invoke(C.byref(kc)) == L.MM_OK
@@ -37,6 +37,8 @@ def test_dispatcher_routes_only_owned_opcodes(lib):
     kc, _ = kcall(op=L.OP_LMHEAD, d=None)
     assert lib.mm_kx_invoke(C.byref(kc)) == L.MM_ERR_UNSUPPORTED  # nor a bf16 head
     kc, _ = kcall(op=L.OP_SILU_MUL, a=None)
+    assert lib.mm_kx_invoke(C.byref(kc)) == L.MM_ERR_STATE
+    kc, _ = kcall(op=L.OP_ADD_RMSNORM, d=None)               # no gain tensor
     assert lib.mm_kx_invoke(C.byref(kc)) == L.MM_ERR_STATE
     lib.mm_log_set_level(1)
 

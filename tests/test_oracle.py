@@ -123,3 +123,35 @@ def test_live_reference_when_present(oracle, reference, lib):
         assert np.array_equal(oracle.gemm_f4(x, w.payload, w.scales, 1.0), yr)
         rc, ym = reference.gemm_f4(x, w.payload, w.scales, threads=3)
         assert rc == 0 and np.array_equal(ym, yr)
+
+
+def _golden_norm_inputs():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(GOLDEN, "make_golden.py"))
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    return mg
+
+
+def test_add_rmsnorm_fixture(oracle, lib):
+    """The restatement of OP_ADD_RMSNORM against outputs of the reference's own
+    kx_op_add_rmsnorm (src/kernels/cpu/cx.c:132-150): bit for bit, the in-place sum too."""
+    mg = _golden_norm_inputs()
+    g = np.load(os.path.join(GOLDEN, "add_rmsnorm.npz"))
+    for (M, H) in mg.ADD_RMSNORM_SHAPES:
+        res, delta, gain = mg.add_rmsnorm_inputs(M, H)
+        res_out, y = oracle.add_rmsnorm(res, delta, gain, mg.ADD_RMSNORM_EPS)
+        assert np.array_equal(res_out, g[f"res_{M}x{H}"])
+        assert np.array_equal(y, g[f"y_{M}x{H}"])
+
+
+def test_live_reference_add_rmsnorm(oracle, reference, lib):
+    if not reference.available:
+        pytest.skip("compiled reference not present")
+    res = mm.make_activations(5, 2048, seed=21, std=3.0)
+    delta = mm.make_activations(5, 2048, seed=22)
+    gain = mm.make_activations(1, 2048, seed=23, std=0.3)[0]
+    for eps in (1.0e-6, 1.0e-5, 0.0):
+        rc, r1, y1 = reference.add_rmsnorm(res, delta, gain, eps)
+        r2, y2 = oracle.add_rmsnorm(res, delta, gain, eps)
+        assert rc == 0 and np.array_equal(r1, r2) and np.array_equal(y1, y2)
