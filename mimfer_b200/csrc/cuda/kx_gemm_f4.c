@@ -550,8 +550,10 @@ mm_status mm_f4_mlp_gate_up(const void *x, const void *gate_payload, const void 
         return st;
     int err = 0;
     if (a.plan.variant == MM_F4_V_MX) {
-        MM_CHECK(encode_pair(a.tm_payload, pay0, K / 2, inter, dpay, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B));
-        MM_CHECK(encode_pair(a.tm_scale, sc0, K / 16, inter, dsc, 16, 128, CU_TENSOR_MAP_SWIZZLE_NONE));
+        MM_CHECK(encode_pair(a.tm_payload, pay0, K / 2, inter, dpay, 128, a.plan.tile_n / 2,
+                             CU_TENSOR_MAP_SWIZZLE_128B));
+        MM_CHECK(encode_pair(a.tm_scale, sc0, K / 16, inter, dsc, 16, a.plan.tile_n / 2,
+                             CU_TENSOR_MAP_SWIZZLE_NONE));
         return launch_mx_pair(&a, share_x, stream);
     }
     if (a.plan.variant == MM_F4_V_STREAM) {

@@ -39,10 +39,16 @@ extern "C" {
 #define MMB_MX_PLANES       6      /* signed e2m1 digits per activation                      */
 #define MMB_MX_THREADS      352u   /* TMA, MMA (half 0), 2 x 4 scale-factor warps (four also run the epilogue), MMA (half 1) */
 #define MMB_MX_MAX_NB       192u   /* B rows: 6 x (M padded to a multiple of 4), M <= 32     */
-/* one pipeline stage: payload (rows x 128 B) | digit planes (nb x 128 B) | block scales
- * (rows x 16 B) | plane scales (nb x 16 B), padded so that every stage starts on a
- * 1024-byte boundary (128-byte swizzle) */
-#define MMB_MX_STAGE_B(rows, nb) ((((rows) + (nb)) * 144u + 1023u) & ~1023u)
+/* one pipeline stage: payload (rows x 128 B, padded to 1024) | digit planes (nb x 128 B)
+ * | block scales (rows x 16 B) | plane scales (nb x 16 B), padded so that every stage
+ * and both swizzled tiles start on a 1024-byte boundary.  `rows` is any multiple of 4 up
+ * to 256: the selector sizes the tiles so that the grid fills the SMs. */
+/* An MMA half always reads 128 rows of 128 bytes, valid or not, so the payload area
+ * spans every byte the halves can touch: one half for a plain tile of up to 128
+ * rows, two otherwise (the second half of a gated pair starts at rows / 2). */
+#define MMB_MX_PAY_B(rows, glu)  (((glu) || (rows) > 128u) ? 32768u : 16384u)
+#define MMB_MX_SC_B(rows)   ((((rows) * 16u) + 127u) & ~127u)      /* TMA destinations are 128-byte aligned */
+#define MMB_MX_STAGE_B(rows, nb, glu) ((MMB_MX_PAY_B(rows, glu) + (nb) * 144u + MMB_MX_SC_B(rows) + 1023u) & ~1023u)
 #define MMB_MX_FIXED_B      (512u /* barriers, flags */ + 1024u /* align slack */)
 /* activation scratch of one op, inside its workspace region after the arrival
  * counters: row factors (32 rows x 2 floats), digit planes [nb][K/2], plane scales [nb][K/16] */

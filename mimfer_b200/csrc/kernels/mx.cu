@@ -292,7 +292,7 @@ struct MxParams {
     uint32_t        M, K, N;
     uint32_t        k_steps, split_k, stages;
     uint32_t        pdl;
-    uint32_t        rows;        /* weight rows per CTA: 256 or 128 (GLU: 256 = 128 of each projection) */
+    uint32_t        rows;        /* weight rows per CTA, a multiple of 4 up to 256 (GLU: 2 x rows of each projection) */
     uint32_t        nb;          /* B rows: 6 x M padded to a multiple of four                          */
 };
 
@@ -328,10 +328,17 @@ f4_mx_kernel(const __grid_constant__ TmaDesc tm_payload, const __grid_constant__
 {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t rows = p.rows, nb = p.nb, halves = rows >> 7;
+    /* The tile is two MMA halves of up to 128 weight rows.  Plain op: rows 0..127 and
+     * 128..rows-1 of the box; gated pair: rows/2 rows of each projection, one after
+     * the other.  Rows of a half beyond its count hold whatever the stage held before:
+     * their accumulator lanes are never read, their scale factors are forced to zero. */
+    const uint32_t rows = p.rows, nb = p.nb;
+    const uint32_t halves = GLU ? 2u : (rows > 128u ? 2u : 1u);
+    const uint32_t h1 = GLU ? rows >> 1 : 128u;                 /* first row of the second half */
+    const uint32_t cnt0 = GLU ? rows >> 1 : (rows < 128u ? rows : 128u), cnt1 = rows - cnt0;
     const uint32_t pay_b = rows * 128u, pl_b = nb * 128u, sc_b = rows * 16u, sfb_b = nb * 16u;
-    const uint32_t stage_b = MMB_MX_STAGE_B(rows, nb);
-    const uint32_t o_pl = pay_b, o_sc = pay_b + pl_b, o_sfb = o_sc + sc_b;
+    const uint32_t stage_b = MMB_MX_STAGE_B(rows, nb, GLU);
+    const uint32_t o_pl = MMB_MX_PAY_B(rows, GLU), o_sc = o_pl + pl_b, o_sfb = o_sc + MMB_MX_SC_B(rows);
     const uint32_t bars = base + p.stages * stage_b;
     const uint32_t bar_full = bars;                              /* [stages] TMA landed             */
     const uint32_t bar_empty = bar_full + 8u * p.stages;         /* [stages] MMAs of the stage done */
@@ -339,9 +346,11 @@ f4_mx_kernel(const __grid_constant__ TmaDesc tm_payload, const __grid_constant__
     const uint32_t bar_accum = bar_sf_full + 16u;
     const uint32_t tmem_slot = bar_accum + 8u;
     const uint32_t last_flag = tmem_slot + 4u;
+    const uint32_t rs_smem = last_flag + 4u;                     /* [32][2] row factors 2^-G */
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    const uint32_t row0 = blockIdx.x * (GLU ? 128u : rows);     /* first weight row (of each projection) */
+    if (tid == 0) MX_TRACE(11, 0);
+    const uint32_t row0 = blockIdx.x * (GLU ? rows >> 1 : rows); /* first weight row (of each projection) */
     const uint32_t ks_begin = static_cast<uint32_t>(static_cast<uint64_t>(p.k_steps) * blockIdx.y / p.split_k);
     const uint32_t ks_end = static_cast<uint32_t>(static_cast<uint64_t>(p.k_steps) * (blockIdx.y + 1) / p.split_k);
     const uint32_t nsteps = ks_end - ks_begin;
@@ -436,7 +445,7 @@ f4_mx_kernel(const __grid_constant__ TmaDesc tm_payload, const __grid_constant__
                 tc_fence_after();
                 if (h == 0) MX_TRACE(2, it);
                 const uint32_t sf = tmem + MMB_MX_SF_COL + t * MMB_MX_SF_SLOT;
-                const uint64_t ad = umma_desc_sw128(st + h * 16384u), bd = umma_desc_sw128(st + o_pl);
+                const uint64_t ad = umma_desc_sw128(st + h * h1 * 128u), bd = umma_desc_sw128(st + o_pl);
 #pragma unroll
                 for (uint32_t j = 0; j < 4u; j++)       /* 32 bytes along K per slice: + 2 in the address field */
                     umma_mxf4(tmem + h * nb, ad + 2u * j, bd + 2u * j, idesc, (it | j) ? 1u : 0u,
@@ -464,6 +473,13 @@ f4_mx_kernel(const __grid_constant__ TmaDesc tm_payload, const __grid_constant__
                 continue;
             mbar_wait_warp(bar_full + 8u * s, round & 1u, p.status);
             if (warp == 2u && lane == 0) MX_TRACE(4, it);
+            if (it == 0u && warp == 2u) {
+                /* the planes of step 0 have landed, so the kernel that made them is done:
+                 * its row factors go to shared memory for the epilogue */
+                sts32(rs_smem + 4u * lane, __float_as_uint(lane < 2u * p.M ? __ldcg(p.row_scale + lane) : 0.0f));
+                sts32(rs_smem + 4u * (lane + 32u),
+                      __float_as_uint(lane + 32u < 2u * p.M ? __ldcg(p.row_scale + lane + 32u) : 0.0f));
+            }
             if (it >= 2u)                        /* the slot is free once the MMAs of step it - 2 are done */
                 mbar_wait_warp(bar_empty + 8u * s2, round2 & 1u, p.status);
             tc_fence_after();
@@ -474,9 +490,10 @@ f4_mx_kernel(const __grid_constant__ TmaDesc tm_payload, const __grid_constant__
             uint4 qa[8];
 #pragma unroll
             for (uint32_t i = 0; i < 8u; i++) {
+                const uint32_t in_half = 32u * (i & 3u) + lane;
                 qa[i] = make_uint4(0u, 0u, 0u, 0u);
-                if ((i >> 2) < halves)
-                    qa[i] = lds128(st + o_sc + ((i >> 2) * 128u + 32u * (i & 3u) + lane) * 16u);
+                if (in_half < ((i >> 2) ? cnt1 : cnt0))
+                    qa[i] = lds128(st + o_sc + ((i >> 2) * h1 + in_half) * 16u);
             }
             if (warp == 2u && lane == 0) MX_TRACE(8, it);
             /* Branch-free on the common path (a lone warp pays dearly for every
@@ -501,7 +518,7 @@ f4_mx_kernel(const __grid_constant__ TmaDesc tm_payload, const __grid_constant__
                 if (quad == 2u && negs) {
 #pragma unroll
                     for (uint32_t i = 0; i < 8u; i++) {
-                        const uint32_t r = (i >> 2) * 128u + 32u * (i & 3u) + lane;
+                        const uint32_t r = (i >> 2) * h1 + 32u * (i & 3u) + lane;     /* row of the payload box */
                         const uint32_t w[4] = { qa[i].x, qa[i].y, qa[i].z, qa[i].w };
 #pragma unroll
                         for (uint32_t j = 0; j < 4u; j++) {
@@ -551,7 +568,8 @@ f4_mx_kernel(const __grid_constant__ TmaDesc tm_payload, const __grid_constant__
             goto done;
         mbar_wait_warp(bar_accum, 0u, p.status);
         tc_fence_after();
-        grid_dep_wait();                         /* row factors come from the kernel in front */
+        if (warp == 2u && lane == 0) MX_TRACE(11, 1);
+        asm volatile("bar.sync 1, 128;" ::: "memory");       /* row factors written by warp 2 */
         const uint32_t lr = quad * 32u + lane;   /* row within a half */
         const uint32_t groups = nb / 24u;
         const bool direct = p.split_k == 1u;
@@ -573,17 +591,18 @@ f4_mx_kernel(const __grid_constant__ TmaDesc tm_payload, const __grid_constant__
                 const uint32_t m = g * 4u + r;
                 if (m >= p.M)
                     break;
-                const float f1 = __ldcg(p.row_scale + 2u * m), f2 = __ldcg(p.row_scale + 2u * m + 1u);
+                const float f1 = __uint_as_float(lds32(rs_smem + 8u * m)), f2 = __uint_as_float(lds32(rs_smem + 8u * m + 4u));
                 const float a0 = mx_row_sum(c0, r) * f1 * f2;
                 const float a1 = halves == 2u ? mx_row_sum(c1, r) * f1 * f2 : 0.0f;
                 if constexpr (GLU) {
                     /* half 0 = plane 0 of the pair, half 1 = plane 1; one output per thread */
                     const uint32_t n = row0 + lr;
+                    const bool ok = lr < cnt0 && n < p.N;
                     if (direct) {
-                        if (n < p.N)
+                        if (ok)
                             mx_store_all(p, m, n, glu_out_bf16(p.gate_plane ? a1 : a0, p.gate_plane ? a0 : a1,
                                                                p.gs, p.gs_up));
-                    } else if (n < p.N) {
+                    } else if (ok) {
                         __stcg(mine + static_cast<size_t>(m) * pitch + blockIdx.x * 256u + lr, a0);
                         __stcg(mine + static_cast<size_t>(m) * pitch + blockIdx.x * 256u + 128u + lr, a1);
                     }
@@ -594,7 +613,7 @@ f4_mx_kernel(const __grid_constant__ TmaDesc tm_payload, const __grid_constant__
                             break;
                         const uint32_t n = row0 + h * 128u + lr;
                         const float a = h ? a1 : a0;
-                        if (n >= p.N)
+                        if (lr >= (h ? cnt1 : cnt0) || n >= p.N)
                             continue;
                         if (direct) {
                             __nv_bfloat16 hv = __float2bfloat16_rn(a * p.gs);
@@ -619,33 +638,51 @@ f4_mx_kernel(const __grid_constant__ TmaDesc tm_payload, const __grid_constant__
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (lds32(last_flag)) {
                 const size_t slice = static_cast<size_t>(groups * 4u) * pitch;
-                for (uint32_t m = 0; m < p.M; m++) {
-                    float s0 = 0.0f, s1 = 0.0f;
-                    if constexpr (GLU) {
-                        const float *src = p.partial + static_cast<size_t>(m) * pitch + blockIdx.x * 256u + lr;
-                        const bool ok = row0 + lr < p.N;
-                        for (uint32_t sl = 0; ok && sl < p.split_k; sl++) {
-                            s0 += __ldcg(src + sl * slice);
-                            s1 += __ldcg(src + sl * slice + 128u);
-                        }
-                        if (ok)
-                            mx_store_all(p, m, row0 + lr, glu_out_bf16(p.gate_plane ? s1 : s0, p.gate_plane ? s0 : s1,
-                                                                       p.gs, p.gs_up));
-                    } else {
-                        const uint32_t n0 = row0 + lr, n1 = n0 + 128u;
-                        const bool ok0 = n0 < p.N, ok1 = halves == 2u && n1 < p.N;
-                        const float *src = p.partial + static_cast<size_t>(m) * pitch;
-                        for (uint32_t sl = 0; sl < p.split_k; sl++) {
-                            if (ok0) s0 += __ldcg(src + sl * slice + n0);
-                            if (ok1) s1 += __ldcg(src + sl * slice + n1);
-                        }
-                        if (ok0) {
-                            __nv_bfloat16 hv = __float2bfloat16_rn(s0 * p.gs);
-                            mx_store_all(p, m, n0, *reinterpret_cast<uint16_t *>(&hv));
-                        }
-                        if (ok1) {
-                            __nv_bfloat16 hv = __float2bfloat16_rn(s1 * p.gs);
-                            mx_store_all(p, m, n1, *reinterpret_cast<uint16_t *>(&hv));
+                /* column of this thread's two outputs in a partial row, and whether they exist */
+                const uint32_t col0 = GLU ? blockIdx.x * 256u + lr : row0 + lr, col1 = col0 + 128u;
+                const bool ok0 = lr < cnt0 && row0 + lr < p.N;
+                const bool ok1 = GLU ? ok0 : (lr < cnt1 && row0 + 128u + lr < p.N);
+                /* four activation rows x eight slices x two halves of loads in flight, added
+                 * slice by slice in ascending order */
+                for (uint32_t m0 = 0; m0 < p.M; m0 += 4u) {
+                    float s0[4] = { 0.0f, 0.0f, 0.0f, 0.0f }, s1[4] = { 0.0f, 0.0f, 0.0f, 0.0f };
+                    for (uint32_t sl0 = 0; sl0 < p.split_k; sl0 += 8u) {
+                        float v0[4][8], v1[4][8];
+#pragma unroll
+                        for (uint32_t r = 0; r < 4u; r++)
+#pragma unroll
+                            for (uint32_t u = 0; u < 8u; u++) {
+                                const bool live = m0 + r < p.M && sl0 + u < p.split_k;
+                                const float *src = p.partial + (sl0 + u) * slice + static_cast<size_t>(m0 + r) * pitch;
+                                v0[r][u] = live && ok0 ? __ldcg(src + col0) : 0.0f;
+                                v1[r][u] = live && ok1 ? __ldcg(src + col1) : 0.0f;
+                            }
+#pragma unroll
+                        for (uint32_t r = 0; r < 4u; r++)
+#pragma unroll
+                            for (uint32_t u = 0; u < 8u; u++) {
+                                s0[r] += v0[r][u];
+                                s1[r] += v1[r][u];
+                            }
+                    }
+#pragma unroll
+                    for (uint32_t r = 0; r < 4u; r++) {
+                        const uint32_t m = m0 + r;
+                        if (m >= p.M)
+                            break;
+                        if constexpr (GLU) {
+                            if (ok0)
+                                mx_store_all(p, m, row0 + lr, glu_out_bf16(p.gate_plane ? s1[r] : s0[r],
+                                                                           p.gate_plane ? s0[r] : s1[r], p.gs, p.gs_up));
+                        } else {
+                            if (ok0) {
+                                __nv_bfloat16 hv = __float2bfloat16_rn(s0[r] * p.gs);
+                                mx_store_all(p, m, row0 + lr, *reinterpret_cast<uint16_t *>(&hv));
+                            }
+                            if (ok1) {
+                                __nv_bfloat16 hv = __float2bfloat16_rn(s1[r] * p.gs);
+                                mx_store_all(p, m, row0 + 128u + lr, *reinterpret_cast<uint16_t *>(&hv));
+                            }
                         }
                     }
                 }
@@ -656,8 +693,10 @@ f4_mx_kernel(const __grid_constant__ TmaDesc tm_payload, const __grid_constant__
     }
 
 done:
+    if (warp == 2u && lane == 0) MX_TRACE(11, 2);
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) MX_TRACE(11, 3);
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem, 512u);
@@ -756,8 +795,8 @@ extern "C" int mmb_launch_mx(const mmb_args *a, void *stream)
     if (e) return e;
     if (!a->ws || !a->mx_x_ws)
         return static_cast<int>(cudaErrorInvalidValue);
-    if ((a->plan.tile_n != 256u && a->plan.tile_n != 128u) || (a->glu && a->plan.tile_n != 256u) ||
-        a->plan.tile_m == 0 || a->plan.tile_m % 24u != 0 || a->plan.tile_m > 192u)
+    if (a->plan.tile_n == 0 || a->plan.tile_n > 256u || a->plan.tile_n % (a->glu ? 16u : 4u) != 0 ||
+        a->plan.tile_m == 0 || a->plan.tile_m % 24u != 0 || a->plan.tile_m > MMB_MX_MAX_NB)
         return static_cast<int>(cudaErrorInvalidValue);
     if (a->glu && a->n_dst)
         return static_cast<int>(cudaErrorInvalidValue);

@@ -106,52 +106,69 @@ static mm_status plan_stream(const mm_f4_shape *s, mm_f4_plan *p)
     return plan_stream_with(s, rows, 0, p);
 }
 
-/* MX plan: `rows` weight rows per CTA (256 or 128), K cut into `split` slices
- * (0 = about one CTA per SM).  Workspace of the op: arrival counters, the
- * activation scratch (row factors, digit planes, their block scales), split-K
- * partials.  `glu_rows`: weight rows including tile padding when the op is a
- * gated pair (partials are laid out per 256-row tile), else 0. */
-static mm_status plan_mx_with(const mm_f4_shape *s, uint32_t rows, uint32_t split, uint32_t glu_rows,
-                              mm_f4_plan *p)
+/* MX plan.  `rows` weight rows per CTA (0 = sized here) and K cut into `split`
+ * slices (0 = about one CTA per SM).  The kernel takes any tile height up to 256
+ * rows (two MMA halves of up to 128), so the height is what makes row tiles x K
+ * slices come out at the number of SMs: gate+up runs as 148 tiles of 236 rows
+ * instead of 136 of 256, down as 21 x 7 instead of 20 x 7.  Workspace of the op:
+ * arrival counters, the activation scratch (row factors, digit planes, their
+ * block scales), split-K partials.  `glu`: gated pair, s->N = output features =
+ * rows of each projection; a tile is tile_n / 2 rows of each. */
+static mm_status plan_mx_with(const mm_f4_shape *s, uint32_t rows, uint32_t split, int glu, mm_f4_plan *p)
 {
     if (!fast_path_ok(s) || s->M > 32)
         return MM_ERR_UNSUPPORTED;
-    if (rows != 256u && rows != 128u)
+    const uint32_t unit = glu ? 128u : 256u;       /* largest tile, in rows of one tensor */
+    const uint32_t gran = glu ? 8u : 4u;
+    if (rows && (rows % (glu ? 16u : 4u) != 0 || rows > 256u))
         return MM_ERR_RANGE;
-    const uint32_t n_rows = glu_rows ? glu_rows : s->N;
     memset(p, 0, sizeof *p);
     p->variant = MM_F4_V_MX;
     p->m_tiles = (s->M + 3u) / 4u;                 /* groups of four activation rows */
     p->tile_m = p->m_tiles * 4u * MMB_MX_PLANES;   /* B rows: six digit planes per activation row */
-    p->tile_n = rows;
     p->k_steps = s->K / MMB_ST_KSTEP;
-    p->grid_x = ceil_div(n_rows, rows);
     p->threads = MMB_MX_THREADS;
     const size_t xs = MMB_WS_COUNTER_B + MMB_MX_XS_B(p->tile_m, s->K);
     if (xs > s->ws_bytes)
         return MM_ERR_UNSUPPORTED;                 /* no room for the digit planes: the CUDA-core kernel runs */
 
     uint32_t sms = s->sm_count ? s->sm_count : 148;
-    uint32_t sk = split ? split : sms / p->grid_x;
+    uint32_t per = rows ? (glu ? rows / 2u : rows) : unit;        /* rows of one tensor per tile */
+    uint32_t tiles = ceil_div(s->N, per);
+    uint32_t sk = split ? split : sms / tiles;
     if (sk < 1) sk = 1;
     uint32_t max_by_steps = p->k_steps / 4 ? p->k_steps / 4 : 1;
     if (sk > max_by_steps) sk = max_by_steps;
     if (sk > 32) sk = 32;
-    if (p->grid_x > MMB_WS_MAX_TILES) sk = 1;
+    if (tiles > MMB_WS_MAX_TILES) sk = 1;
+    if (!rows) {
+        /* lower tiles until tiles x slices reaches the SM count (never below 32 rows) */
+        uint32_t want = sms / sk;
+        if (tiles > sms)                            /* several waves: make the last one full too */
+            want = ceil_div(tiles, sms) * sms;
+        if (want > tiles && want <= MMB_WS_MAX_TILES) {
+            per = ceil_div(ceil_div(s->N, want), gran) * gran;
+            if (per < 32u) per = 32u;
+            if (per > unit) per = unit;
+            tiles = ceil_div(s->N, per);
+        }
+    }
+    p->tile_n = glu ? 2u * per : per;
+    p->grid_x = tiles;
     p->ws_needed = xs;
     while (sk > 1) {
-        size_t need = xs + (size_t)sk * p->m_tiles * 4u * ((size_t)p->grid_x * rows) * 4u;
+        size_t need = xs + (size_t)sk * p->m_tiles * 4u * ((size_t)tiles * 256u) * 4u;
         if (need <= s->ws_bytes) { p->ws_needed = need; break; }
         sk--;
     }
     p->split_k = sk;
     p->grid_y = sk;
     p->grid_z = 1;
-    uint32_t stage = MMB_MX_STAGE_B(rows, p->tile_m);
+    uint32_t stage = MMB_MX_STAGE_B(p->tile_n, p->tile_m, glu);
     uint32_t st = (MMB_SMEM_MAX - MMB_MX_FIXED_B) / stage;
     if (st > 6) st = 6;
-    uint32_t per = ceil_div(p->k_steps, sk);
-    if (st > per) st = per;
+    uint32_t steps = ceil_div(p->k_steps, sk);
+    if (st > steps) st = steps;
     if (st < 1) st = 1;
     p->stages = st;
     p->smem_bytes = st * stage + MMB_MX_FIXED_B;
@@ -160,19 +177,13 @@ static mm_status plan_mx_with(const mm_f4_shape *s, uint32_t rows, uint32_t spli
 
 static mm_status plan_mx(const mm_f4_shape *s, mm_f4_plan *p)
 {
-    /* half-height tiles for weights that 256-row tiles cannot spread over the SMs
-     * (the rule of the STREAM plan below) */
-    uint32_t sms = s->sm_count ? s->sm_count : 148;
-    uint32_t k_steps = s->K / MMB_ST_KSTEP;
-    uint32_t max_split = k_steps / 4 ? k_steps / 4 : 1;
-    uint32_t rows = ceil_div(s->N, 256u) * max_split * 4u < sms ? 128u : 256u;
-    return plan_mx_with(s, rows, 0, 0, p);
+    return plan_mx_with(s, 0, 0, 0, p);
 }
 
 mm_status mmb_plan_mx_with(const mm_f4_shape *s, uint32_t rows, uint32_t split, mm_f4_plan *p)
 {
     mm_status st = check_shape(s, p);
-    return st != MM_OK ? st : plan_mx_with(s, rows ? rows : 256u, split, 0, p);
+    return st != MM_OK ? st : plan_mx_with(s, rows, split, 0, p);
 }
 
 mm_status mmb_plan_stream_with(const mm_f4_shape *s, uint32_t rows, uint32_t split, mm_f4_plan *p)
@@ -299,7 +310,7 @@ mm_status mmb_select_glu(const mm_f4_shape *s, int allow_mx, mm_f4_plan *out)
     rows.N = ceil_div(s->N, MMB_ST_ROWS / 2) * MMB_ST_ROWS;      /* weight rows incl. tile padding */
     if (s->M <= 32) {
         /* the tile padding only counts rows: the planes' size follows K and M */
-        if (allow_mx && plan_mx_with(s, 256u, 0, rows.N, out) == MM_OK)
+        if (allow_mx && plan_mx_with(s, 0, 0, 1, out) == MM_OK)
             return MM_OK;
         return plan_stream_with(&rows, MMB_ST_ROWS, 0, out);       /* partials are laid out per 256-row tile */
     }
