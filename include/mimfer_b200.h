@@ -189,6 +189,19 @@ mm_status mm_f4_linear(const void *x, const void *payload, const void *scale,
                        float gs, void *y, uint32_t M, uint32_t K, uint32_t N,
                        void *stream);
 
+/* The activation side of the block-scaled decode kernel (no counterpart in the
+ * reference, which keeps activations in bf16, src/kernels/cpu/cx.c:211).  The tensor
+ * core multiplies e2m1 by e2m1, so the bf16 activations x [M][K] (M <= 32, K a
+ * multiple of 256) are rewritten as six signed e2m1 digit planes per row with
+ * power-of-two block scales, exact for every value within 2^9 of its 16-wide
+ * block's largest and rounded at 2^-17 of that largest below.  mm_f4_linear does
+ * this itself in front of its kernel; an owner of a whole op list does it once per
+ * distinct activation tensor per step, ahead of the ops (the op-list engine does,
+ * in overlap mode, into the upper half of the workspace).  `scratch`: device
+ * memory, 256-byte aligned, mm_f4_xslice_bytes(M, K) bytes. */
+size_t    mm_f4_xslice_bytes(uint32_t M, uint32_t K);
+mm_status mm_f4_xslice(const void *x, uint32_t M, uint32_t K, void *scratch, size_t scratch_bytes, void *stream);
+
 /* Gated MLP front half in one kernel (no single counterpart in the reference):
  * replaces the three ops the reference planner emits per layer
  * (src/plan/plan.c:223-247: OP_GEMM_F4 "gate", OP_GEMM_F4 "up", OP_SILU_MUL)
@@ -400,6 +413,10 @@ mm_status mm_lin_engine_fuse_mlp(mm_lin_engine *e, int on);
  * ahead. */
 mm_status mm_lin_engine_overlap(mm_lin_engine *e, int on);
 uint32_t  mm_lin_engine_n_independent(const mm_lin_engine *e);
+/* Overlap mode, block-scaled decode path: how many distinct activation tensors of
+ * the last dispatch or capture were turned into digit planes ahead of the ops, on
+ * the transfer stream (inputs of the step that no earlier op of the list writes). */
+uint32_t  mm_lin_engine_n_sliced_ahead(const mm_lin_engine *e);
 /* Capture all ops into one CUDA graph (reference pattern:
  * src/plan/plan.c:479-507). */
 mm_status mm_lin_engine_capture(mm_lin_engine *e);

@@ -51,6 +51,13 @@ int mmb_gate_up_fusable(const void *x, const void *gate_payload, const void *gat
  * activations the op before it already turned into digit planes (block-scaled
  * decode path: the planes are shared instead of made again). */
 void mmb_next_op_context(int pdl_mode, int ws_region, int shallow_split, int share_x);
+/* For the next op only: its activations' digit planes already lie at `planes_ws`
+ * (made by mm_f4_xslice into the plane cache), so the op launches no slicing
+ * kernel and waits for none. */
+void mmb_next_op_planes(void *planes_ws);
+/* The part of the workspace set aside for digit planes made ahead of their ops
+ * (NULL / 0 when the workspace is too small to divide). */
+void *mmb_plane_cache(size_t *bytes_out);
 /* Regions the workspace is cut into, so that ops in flight together never share
  * scratch (1 when the workspace is too small to divide). */
 int mmb_ws_regions(void);

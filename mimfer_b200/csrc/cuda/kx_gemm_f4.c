@@ -42,6 +42,7 @@ static struct {
     int        next_region;
     int        next_shallow;     /* the next op may take the shallower K split of a run-ahead op */
     int        next_share_x;     /* the next op reads the activations the op before it sliced */
+    void      *next_planes;      /* the next op's digit planes are already there (plane cache) */
     int        use_mx;           /* decode ops take the block-scaled tensor path when they can */
     /* the digit planes made last: which activations, and where they lie */
     const void *sliced_x;
@@ -60,12 +61,30 @@ static struct {
 
 int mmb_ws_regions(void)
 {
-    return G.ws && G.ws_bytes / WS_REGIONS >= WS_REGION_MIN ? WS_REGIONS : 1;
+    return G.ws && G.ws_bytes / (2 * WS_REGIONS) >= WS_REGION_MIN ? WS_REGIONS : 1;
 }
 
+/* With room to divide, the lower half of the workspace holds the per-op regions
+ * and the upper half is the plane cache: digit planes of activations that are
+ * made once per step, ahead of the ops that read them (engine, overlap mode). */
 static size_t ws_region_bytes(void)
 {
-    return G.ws ? (G.ws_bytes / (size_t)mmb_ws_regions()) & ~(size_t)255 : 0;
+    if (!G.ws)
+        return 0;
+    const int n = mmb_ws_regions();
+    return (n > 1 ? G.ws_bytes / (size_t)(2 * n) : G.ws_bytes) & ~(size_t)1023;
+}
+
+void *mmb_plane_cache(size_t *bytes_out)
+{
+    const int n = mmb_ws_regions();
+    if (n <= 1) {
+        *bytes_out = 0;
+        return NULL;
+    }
+    const size_t lower = (size_t)n * ws_region_bytes();
+    *bytes_out = (G.ws_bytes - lower) & ~(size_t)1023;
+    return (unsigned char *)G.ws + lower;
 }
 
 void mmb_next_op_context(int pdl_mode, int ws_region, int shallow_split, int share_x)
@@ -75,6 +94,8 @@ void mmb_next_op_context(int pdl_mode, int ws_region, int shallow_split, int sha
     G.next_region = ws_region >= 0 && ws_region < mmb_ws_regions() ? ws_region : 0;
     G.next_share_x = share_x;
 }
+
+void mmb_next_op_planes(void *planes_ws) { G.next_planes = planes_ws; }
 
 /* Consume the per-op context: launch mode and workspace base of this op. */
 static void take_op_context(int *pdl_out, void **ws_out, int *shallow_out, int *share_out)
@@ -352,13 +373,12 @@ static mm_status plan_linear(const void *x, const void *payload, const void *sca
      * split.  Measured on B200, us per op, run-ahead / alone: down at M = 16 with
      * 3 slices 17.0 / 31.9, with 7 slices 19.9 / 21.4; q with 3 slices 8.2 / 13.8,
      * with 5 slices 9.9 / 12.9. */
-    if (st == MM_OK && run_ahead && (plan->variant == MM_F4_V_STREAM || plan->variant == MM_F4_V_MX) &&
-        plan->split_k > 1 && plan->grid_x <= 24) {   /* measured for 17 to 24 row tiles; a fused qkv (32) lost with 2 slices */
+    if (st == MM_OK && run_ahead && plan->variant == MM_F4_V_STREAM && plan->split_k > 1 &&
+        plan->grid_x <= 24) {              /* measured for 17 to 24 row tiles; a fused qkv (32) lost with 2 slices */
         uint32_t s = (uint32_t)(0.45 * (double)sh.sm_count / (double)plan->grid_x + 0.5);
         if (s < 1) s = 1;
         if (s < plan->split_k)
-            st = plan->variant == MM_F4_V_MX ? mmb_plan_mx_with(&sh, plan->tile_n, s, plan)
-                                             : mmb_plan_stream_with(&sh, plan->tile_n, s, plan);
+            st = mmb_plan_stream_with(&sh, plan->tile_n, s, plan);
     }
     return st;
 }
@@ -370,8 +390,11 @@ static mm_status plan_linear(const void *x, const void *payload, const void *sca
 static mm_status launch_mx_pair(mmb_args *a, int share_x, void *stream)
 {
     const uint32_t nb = a->plan.tile_m;
-    const int reuse = share_x && G.sliced_ws && G.sliced_x == a->x && G.sliced_M == a->M && G.sliced_K == a->K;
-    a->mx_x_ws = reuse ? G.sliced_ws : (void *)((unsigned char *)a->ws + MMB_WS_COUNTER_B);
+    void *cached = G.next_planes;
+    G.next_planes = NULL;
+    const int reuse = cached != NULL ||
+                      (share_x && G.sliced_ws && G.sliced_x == a->x && G.sliced_M == a->M && G.sliced_K == a->K);
+    a->mx_x_ws = cached ? cached : reuse ? G.sliced_ws : (void *)((unsigned char *)a->ws + MMB_WS_COUNTER_B);
     a->mx_partial_off = MMB_WS_COUNTER_B + MMB_MX_XS_B(nb, a->K);
     unsigned char *planes = (unsigned char *)a->mx_x_ws + MMB_MX_PLANES_OFF;
     MM_CHECK(encode_2d(a->tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, planes, a->K / 2, nb, 128, nb,
@@ -473,6 +496,38 @@ static mm_status linear_impl(const void *x, const void *payload, const void *sca
     if (err) {
         MM_LOGE("cuda: launch (variant %d, M %u K %u N %u): %s", a.plan.variant, M, K, N,
                 cudaGetErrorString((cudaError_t)err));
+        return MM_ERR_CUDA;
+    }
+    G.launches++;
+    return MM_OK;
+}
+
+size_t mm_f4_xslice_bytes(uint32_t M, uint32_t K)
+{
+    if (M == 0 || M > 32 || K == 0 || K % 256 != 0)
+        return 0;
+    return MMB_MX_XS_B(((M + 3u) / 4u) * 4u * MMB_MX_PLANES, K);
+}
+
+mm_status mm_f4_xslice(const void *x, uint32_t M, uint32_t K, void *scratch, size_t scratch_bytes, void *stream)
+{
+    MM_REQUIRE(x && scratch, MM_ERR_STATE);
+    const size_t need = mm_f4_xslice_bytes(M, K);
+    if (!need || ((uintptr_t)x & 15u) || ((uintptr_t)scratch & 255u))
+        return MM_ERR_SHAPE;
+    MM_REQUIRE(scratch_bytes >= need, MM_ERR_CAPACITY);
+    MM_CHECK(ensure_ready());
+    if (!stream)
+        stream = mm_cuda_stream_raw(MM_ST_COMPUTE);
+    mmb_args a;
+    memset(&a, 0, sizeof a);
+    a.x = x; a.M = M; a.K = K;
+    a.plan.tile_m = ((M + 3u) / 4u) * 4u * MMB_MX_PLANES;
+    a.mx_x_ws = scratch;
+    a.pdl = MMB_PDL_OFF;
+    int err = mmb_launch_xslice(&a, stream);
+    if (err) {
+        MM_LOGE("cuda: launch (activation slicing, M %u K %u): %s", M, K, cudaGetErrorString((cudaError_t)err));
         return MM_ERR_CUDA;
     }
     G.launches++;

@@ -35,6 +35,9 @@ struct mm_lin_engine {
     const void **x_bound;           /* [max_ops] pinned host source of op i's activations, or NULL */
     void       **y_bound;           /* [max_ops] pinned host destination of op i's output, or NULL  */
     int          bound, bound_captured;
+    void       **planes;            /* [max_ops] op i's digit planes in the plane cache, or NULL    */
+    int         *plane_ev;          /* [max_ops] event that says they are there (-1: already waited) */
+    uint32_t     n_plane_slots;     /* distinct activation tensors sliced ahead in the last walk    */
     uint32_t     upload_group;      /* ops whose uploads share one event (>= 1) */
     int          upload_kernel;     /* uploads of a group as one kernel instead of copy nodes */
 };
@@ -55,7 +58,9 @@ mm_status mm_lin_engine_create(mm_lin_engine **out, uint32_t max_ops)
     }
     e->x_bound = (const void **)calloc(max_ops, sizeof(void *));
     e->y_bound = (void **)calloc(max_ops, sizeof(void *));
-    if (!e->x_bound || !e->y_bound) {
+    e->planes = (void **)calloc(max_ops, sizeof(void *));
+    e->plane_ev = (int *)calloc(max_ops, sizeof(int));
+    if (!e->x_bound || !e->y_bound || !e->planes || !e->plane_ev) {
         mm_lin_engine_destroy(e);
         return MM_ERR_NOMEM;
     }
@@ -179,6 +184,7 @@ mm_status mm_lin_engine_overlap(mm_lin_engine *e, int on)
 }
 
 uint32_t mm_lin_engine_n_independent(const mm_lin_engine *e) { return e ? e->n_independent : 0; }
+uint32_t mm_lin_engine_n_sliced_ahead(const mm_lin_engine *e) { return e ? e->n_plane_slots : 0; }
 
 /* ---- which ops may run ahead of their predecessors --------------------------
  * The reference engine serialises its ops on one stream (src/plan/plan.c:119-130)
@@ -277,6 +283,82 @@ static mm_status run_ops(mm_lin_engine *e)
             }
         }
     }
+    /* Block-scaled decode path, overlap mode: activations that no earlier op of the
+     * list writes (inputs of the step; the same tensor read by several ops) are
+     * turned into digit planes once, on the transfer stream ahead of the ops, into
+     * the plane cache.  The ops that read them launch no slicing kernel of their
+     * own, wait only for that event, and may run ahead of their predecessors like
+     * any op whose inputs are ready. */
+    enum { MAX_PLANE_SLOTS = 64 };
+    struct { const void *x; uint32_t M, K; void *ws; } slot[MAX_PLANE_SLOTS];
+    uint32_t n_slots = 0;
+    const int ev_x0 = EV_OP0 + (int)(e->n_ops / grp) + 1;
+    for (uint32_t i = 0; i < e->n_ops; i++) {
+        e->planes[i] = NULL;
+        e->plane_ev[i] = -1;
+    }
+    if (e->overlap) {
+        size_t cap = 0, used = 0;
+        unsigned char *cache = (unsigned char *)mmb_plane_cache(&cap);
+        for (uint32_t i = 0; cache && i < e->n_ops; i++) {
+            const mm_op_desc *op = &e->ops[i];
+            if (op->op == OP_NOP || op->op == OP_SILU_MUL || op->op == OP_ADD_RMSNORM)
+                continue;
+            mm_f4_plan plan;
+            MM_CHECK(mmb_plan_for_op(op, op->op == MMB_OP_GATE_UP, &plan));
+            if (plan.variant != MM_F4_V_MX)
+                continue;
+            int external = 1;
+            const span xs = mk_span(op->a, op_in_bytes(op));
+            for (uint32_t j = 0; external && j < i; j++) {
+                span r[2], w[2];
+                if (e->ops[j].op == OP_NOP)
+                    continue;
+                op_spans(&e->ops[j], r, w);
+                if (spans_meet(w[0], xs) || spans_meet(w[1], xs))
+                    external = 0;
+            }
+            if (!external)
+                continue;
+            uint32_t k = 0;
+            while (k < n_slots && !(slot[k].x == op->a && slot[k].M == op->n0 && slot[k].K == op->n1))
+                k++;
+            if (k == n_slots) {
+                const size_t need = (mm_f4_xslice_bytes(op->n0, op->n1) + 1023u) & ~(size_t)1023u;
+                if (n_slots == MAX_PLANE_SLOTS || need == 0 || used + need > cap)
+                    continue;                     /* no room: the op slices for itself */
+                slot[k].x = op->a; slot[k].M = op->n0; slot[k].K = op->n1;
+                slot[k].ws = cache + used;
+                used += need;
+                n_slots++;
+            }
+            e->planes[i] = slot[k].ws;
+            e->plane_ev[i] = ev_x0 + (int)k;
+        }
+    }
+    e->n_plane_slots = n_slots;
+    if (n_slots) {
+        MM_CHECK(mmb_event_pool_reserve(ev_x0 + (int)n_slots));
+        if (!with_copies) {
+            MM_CHECK(mm_event_record(EV_FORK, MM_ST_COMPUTE));
+            MM_CHECK(mm_event_wait(EV_FORK, MM_ST_XFER));
+        }
+        for (uint32_t k = 0; k < n_slots; k++) {
+            MM_CHECK(mm_f4_xslice(slot[k].x, slot[k].M, slot[k].K, slot[k].ws,
+                                  mm_f4_xslice_bytes(slot[k].M, slot[k].K), mm_cuda_stream_raw(MM_ST_XFER)));
+            MM_CHECK(mm_event_record(ev_x0 + (int)k, MM_ST_XFER));
+        }
+        for (uint32_t i = 0; i < e->n_ops; i++) {                /* only a tensor's first reader waits */
+            if (e->plane_ev[i] < 0)
+                continue;
+            int first = 1;
+            for (uint32_t j = 0; j < i; j++)
+                if (e->plane_ev[j] == e->plane_ev[i] || (e->planes[j] == e->planes[i] && e->planes[j]))
+                    first = 0;
+            if (!first)
+                e->plane_ev[i] = -1;
+        }
+    }
     mm_kcall kc;
     kc.e = (const mm_engine *)e;      /* the dispatcher only tests it for NULL */
     kc.stream = NULL;
@@ -313,7 +395,8 @@ static mm_status run_ops(mm_lin_engine *e)
                 /* split-K partials and digit planes live in the op's workspace region */
                 scratch = plan.split_k > 1 || plan.variant == MM_F4_V_MX;
                 region = scratch ? next_region : 0;
-                independent = i > 0 && (plan.variant == MM_F4_V_STREAM || (plan.variant == MM_F4_V_MX && share)) &&
+                independent = i > 0 && (plan.variant == MM_F4_V_STREAM ||
+                                        (plan.variant == MM_F4_V_MX && (share || e->planes[i]))) &&
                               !(scratch && (regions_in_flight & (1u << region)));
                 for (uint32_t j = first_in_flight; independent && j < i; j++)
                     if (e->ops[j].op != OP_NOP && !ops_independent(op, &e->ops[j]))
@@ -336,6 +419,11 @@ static mm_status run_ops(mm_lin_engine *e)
         /* the first op of a group waits for the uploads of the whole group */
         if (with_copies && i % grp == 0)
             MM_CHECK(mm_event_wait(EV_OP0 + (int)(i / grp), MM_ST_COMPUTE));
+        if (e->planes[i]) {
+            if (e->plane_ev[i] >= 0)
+                MM_CHECK(mm_event_wait(e->plane_ev[i], MM_ST_COMPUTE));
+            mmb_next_op_planes(e->planes[i]);
+        }
         kc.op = &e->ops[i];
         mm_status st = e->ops[i].op == MMB_OP_GATE_UP
                            ? mmb_op_mlp_gate_up(&e->ops[i], e->up[i].payload, e->up[i].scale)
@@ -350,7 +438,7 @@ static mm_status run_ops(mm_lin_engine *e)
             MM_CHECK(mm_d2h_async(e->y_bound[i], op->c, op_out_bytes(op), MM_ST_XFER));
         }
     }
-    if (with_copies) {
+    if (with_copies || n_slots) {
         MM_CHECK(mm_event_record(EV_JOIN, MM_ST_XFER));
         MM_CHECK(mm_event_wait(EV_JOIN, MM_ST_COMPUTE));
     }
@@ -435,5 +523,7 @@ void mm_lin_engine_destroy(mm_lin_engine *e)
     free(e->up);
     free(e->x_bound);
     free(e->y_bound);
+    free(e->planes);
+    free(e->plane_ev);
     free(e);
 }

@@ -110,6 +110,31 @@ __host__ __device__ constexpr uint32_t umma_idesc_mxf4(uint32_t n)
     return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | (8u << 24);
 }
 
+#ifdef MMB_MX_TRACE
+/* build-time option for timing studies: a timeline of kernel entries and exits
+ * (global timer, first and last CTA of every launch) */
+__device__ unsigned long long g_tl[4 * 4096];
+__device__ unsigned g_tl_n;
+__device__ __forceinline__ void tl_mark(unsigned kind)
+{
+    const unsigned i = atomicAdd(&g_tl_n, 1u);
+    if (i < 4096u) {
+        g_tl[4 * i] = kind;
+        g_tl[4 * i + 1] = blockIdx.x + 1000u * blockIdx.y;
+        g_tl[4 * i + 2] = globaltimer_ns();
+        g_tl[4 * i + 3] = gridDim.x * gridDim.y;
+    }
+}
+#define TL_MARK(kind) do { if (threadIdx.x == 0 && ((blockIdx.x == 0 && blockIdx.y == 0) || (blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1))) tl_mark(kind); } while (0)
+/* CTA 0 records the SM clock at the hand-offs
+ * of its first 32 K steps */
+__device__ long long g_mx_trace[12 * 32];
+#define MX_TRACE(ev, it) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (it) < 32u) g_mx_trace[(ev) * 32 + (it)] = clock64(); } while (0)
+#else
+#define MX_TRACE(ev, it) do { } while (0)
+#define TL_MARK(kind) do { } while (0)
+#endif
+
 /* ==========================================================================
  * Activation slicing
  * ========================================================================== */
@@ -154,6 +179,7 @@ f4_xslice_kernel(const XsliceParams p)
     __shared__ uint32_t s_max[8];
     const uint32_t m = blockIdx.y, tid = threadIdx.x;
     const uint32_t blocks = p.K / 16u;
+    TL_MARK(1);
     grid_dep_launch();                       /* the linear kernel may start fetching weights */
     if (p.pdl != MMB_PDL_OFF)
         grid_dep_wait();                     /* x is the previous kernel's output */
@@ -267,19 +293,13 @@ f4_xslice_kernel(const XsliceParams p)
             p.sfb[n * blocks + blk] = static_cast<uint8_t>(byte);
         }
     }
+    TL_MARK(2);
 }
 
 /* ==========================================================================
  * The linear kernel
  * ========================================================================== */
-#ifdef MMB_MX_TRACE
-/* build-time option for timing studies: CTA 0 records the SM clock at the hand-offs
- * of its first 32 K steps */
-__device__ long long g_mx_trace[12 * 32];
-#define MX_TRACE(ev, it) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (it) < 32u) g_mx_trace[(ev) * 32 + (it)] = clock64(); } while (0)
-#else
-#define MX_TRACE(ev, it) do { } while (0)
-#endif
+
 struct MxParams {
     uint16_t       *y[MMB_MAX_PEERS];
     uint32_t        n_dst, ldy, col0;
@@ -320,8 +340,11 @@ __device__ __forceinline__ float mx_row_sum(const uint32_t (&c)[24], int r)
     return v;
 }
 
+/* 128 registers per thread: the slicing kernels of the ops behind (256 threads,
+ * 32 registers) must fit on the SM beside this kernel's one CTA, or they wait for
+ * it to leave and then hold up the next linear kernel's CTA on that SM. */
 template <bool GLU>
-__global__ void __launch_bounds__(MMB_MX_THREADS, 1)
+__global__ void __maxnreg__(128)
 f4_mx_kernel(const __grid_constant__ TmaDesc tm_payload, const __grid_constant__ TmaDesc tm_scale,
              const __grid_constant__ TmaDesc tm_planes, const __grid_constant__ TmaDesc tm_sfb,
              const MxParams p)
@@ -350,6 +373,7 @@ f4_mx_kernel(const __grid_constant__ TmaDesc tm_payload, const __grid_constant__
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     if (tid == 0) MX_TRACE(11, 0);
+    TL_MARK(3);
     const uint32_t row0 = blockIdx.x * (GLU ? rows >> 1 : rows); /* first weight row (of each projection) */
     const uint32_t ks_begin = static_cast<uint32_t>(static_cast<uint64_t>(p.k_steps) * blockIdx.y / p.split_k);
     const uint32_t ks_end = static_cast<uint32_t>(static_cast<uint64_t>(p.k_steps) * (blockIdx.y + 1) / p.split_k);
@@ -697,6 +721,7 @@ done:
     tc_fence_before();
     __syncthreads();
     if (tid == 0) MX_TRACE(11, 3);
+    TL_MARK(4);
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem, 512u);
@@ -749,6 +774,13 @@ static int launch_mx(const mmb_args *a, unsigned *status, cudaStream_t st)
 } // namespace mmb
 
 #ifdef MMB_MX_TRACE
+extern "C" int mmb_mx_timeline_read(unsigned long long *out, unsigned *n, int reset)
+{
+    cudaError_t e = cudaMemcpyFromSymbol(n, mmb::g_tl_n, sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out, mmb::g_tl, sizeof(unsigned long long) * 4 * 4096);
+    if (e == cudaSuccess && reset) { unsigned z = 0; e = cudaMemcpyToSymbol(mmb::g_tl_n, &z, sizeof z); }
+    return static_cast<int>(e);
+}
 extern "C" int mmb_mx_trace_read(long long *out)
 {
     return static_cast<int>(cudaMemcpyFromSymbol(out, mmb::g_mx_trace, sizeof(long long) * 12 * 32));
