@@ -417,6 +417,16 @@ uint32_t  mm_lin_engine_n_independent(const mm_lin_engine *e);
  * the last dispatch or capture were turned into digit planes ahead of the ops, on
  * the transfer stream (inputs of the step that no earlier op of the list writes). */
 uint32_t  mm_lin_engine_n_sliced_ahead(const mm_lin_engine *e);
+/* on != 0: group mode.  Runs of consecutive decode linears (M <= 32) that share no
+ * memory with each other - q, k and v of a layer, gate and up, a benchmark's
+ * stand-alone linears - become ONE persistent launch of the block-scaled kernel:
+ * the CTAs walk the ops' work units in turn and the weight stream does not stop
+ * between ops (up to 48 ops per launch; an activation tensor several ops read is
+ * sliced once).  Results are those of the single launches.  Needs a workspace of
+ * at least 32 MiB.  Off by default; before capture.
+ * mm_lin_engine_n_group_launches: group launches of the last dispatch or capture. */
+mm_status mm_lin_engine_group(mm_lin_engine *e, int on);
+uint32_t  mm_lin_engine_n_group_launches(const mm_lin_engine *e);
 /* Capture all ops into one CUDA graph (reference pattern:
  * src/plan/plan.c:479-507). */
 mm_status mm_lin_engine_capture(mm_lin_engine *e);

@@ -125,6 +125,8 @@ SIGNATURES = {
     "mm_lin_engine_overlap": (C.c_int, [_vp, C.c_int]),
     "mm_lin_engine_n_independent": (C.c_uint32, [_vp]),
     "mm_lin_engine_n_sliced_ahead": (C.c_uint32, [_vp]),
+    "mm_lin_engine_group": (C.c_int, [_vp, C.c_int]),
+    "mm_lin_engine_n_group_launches": (C.c_uint32, [_vp]),
     "mm_f4_select_variant": (C.c_int, [C.POINTER(F4Shape), C.c_int, C.POINTER(F4Plan)]),
     "mm_f4_force_variant": (None, [C.c_int]),
     "mm_f4_linear": (C.c_int, [_vp, _vp, _vp, _f, _vp, _u32, _u32, _u32, _vp]),

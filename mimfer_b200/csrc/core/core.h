@@ -58,6 +58,15 @@ void mmb_next_op_planes(void *planes_ws);
 /* The part of the workspace set aside for digit planes made ahead of their ops
  * (NULL / 0 when the workspace is too small to divide). */
 void *mmb_plane_cache(size_t *bytes_out);
+/* A run of mutually independent decode linears as one persistent launch of the
+ * block-scaled kernel.  begin: open a group (launch mode and workspace region as
+ * for a single op); add: MM_OK, MM_ERR_CAPACITY (full: launch and open another)
+ * or MM_ERR_UNSUPPORTED (the op does not run on that kernel); launch: enqueue the
+ * slicing of the group's activations and the kernel, then synchronise like an op. */
+mm_status mmb_group_begin(int pdl_mode, int ws_region);
+mm_status mmb_group_add(const mm_op_desc *op, int glu, const void *up_payload, const void *up_scale);
+mm_status mmb_group_launch(void);
+uint32_t  mmb_group_size(void);
 /* Regions the workspace is cut into, so that ops in flight together never share
  * scratch (1 when the workspace is too small to divide). */
 int mmb_ws_regions(void);

@@ -20,6 +20,7 @@ int mmb_stream_init(void);
 int mmb_umma_init(void);
 int mmb_streamt_init(void);
 int mmb_mx_init(void);
+int mmb_mxg_init(void);
 
 /* ------------------------------------------------------------------ state */
 typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
@@ -261,6 +262,7 @@ static mm_status ensure_ready(void)
     CK((cudaError_t)mmb_umma_init());
     CK((cudaError_t)mmb_streamt_init());
     CK((cudaError_t)mmb_mx_init());
+    CK((cudaError_t)mmb_mxg_init());
     CK((cudaError_t)mmb_status_word(&G.status_dev));
     CK(cudaHostAlloc((void **)&G.status_host, 64, cudaHostAllocDefault));
     *G.status_host = 0;
@@ -652,6 +654,148 @@ mm_status mm_silu_mul(const void *gate, const void *up, void *y, size_t n, void 
     }
     G.launches++;
     return MM_OK;
+}
+
+static mm_status finish_op(void);
+
+/* ------------------------------------------------------------- group launch
+ * A run of decode linears that are independent of each other, as one persistent
+ * launch of the block-scaled kernel (kernels/mxg.cu).  The engine opens a group,
+ * adds ops while they fit, and launches it.  Scratch: arrival counters and
+ * split-K partials of every op from one workspace region, digit planes from the
+ * plane cache (an activation tensor several ops read is sliced once). */
+static struct {
+    int       active;
+    mmb_group g;
+    size_t    part_used, cache_used;
+    uint32_t  counters_used;
+    unsigned char *region;
+} GR;
+
+mm_status mmb_group_begin(int pdl_mode, int ws_region)
+{
+    MM_CHECK(ensure_ready());
+    MM_REQUIRE(G.ws && mmb_ws_regions() > 1, MM_ERR_STATE);
+    memset(&GR.g, 0, sizeof GR.g);
+    GR.active = 1;
+    GR.g.pdl = G.pdl ? (pdl_mode >= 0 ? pdl_mode : MMB_PDL_TRIGGER_FIRST) : MMB_PDL_OFF;
+    GR.g.acc_bufs = 2;
+    const int r = ws_region >= 0 && ws_region < mmb_ws_regions() ? ws_region : 0;
+    GR.region = (unsigned char *)G.ws + (size_t)r * ws_region_bytes();
+    GR.part_used = MMB_WS_COUNTER_B;
+    GR.counters_used = 0;
+    GR.cache_used = 0;
+    return MM_OK;
+}
+
+uint32_t mmb_group_size(void) { return GR.active ? GR.g.n_ops : 0; }
+
+/* MM_ERR_CAPACITY: the group is full (launch it and open another);
+ * MM_ERR_UNSUPPORTED: this op does not run on the block-scaled kernel. */
+mm_status mmb_group_add(const mm_op_desc *op, int glu, const void *up_payload, const void *up_scale)
+{
+    MM_REQUIRE(GR.active && op, MM_ERR_STATE);
+    if (GR.g.n_ops == MMB_MXG_MAX_OPS)
+        return MM_ERR_CAPACITY;
+    const uint32_t M = op->n0, K = op->n1, N = op->n2;
+    const void *pay0 = op->b, *sc0 = op->d;
+    int gate_first = 1;
+    uint64_t dpay = 0, dsc = 0;
+    mm_f4_plan plan;
+    mm_f4_shape sh = { M, K, N, (uint32_t)G.sm_count, min_align(op->a, op->b, op->d, op->c), ws_region_bytes() };
+    if (sh.ptr_align < 16 || M == 0 || K == 0 || N == 0 || K % 16 != 0)
+        return MM_ERR_SHAPE;
+    if (glu) {
+        if (!pair_layout(op->b, op->d, up_payload, up_scale, &gate_first, &dpay, &dsc))
+            return MM_ERR_UNSUPPORTED;
+        pay0 = gate_first ? op->b : up_payload;
+        sc0 = gate_first ? op->d : up_scale;
+        sh.ptr_align = min_align(op->a, pay0, sc0, op->c);
+        if (mmb_select_glu(&sh, 1, &plan) != MM_OK || plan.variant != MM_F4_V_MX)
+            return MM_ERR_UNSUPPORTED;
+    } else if (mm_f4_select_variant(&sh, MM_F4_V_MX, &plan) != MM_OK) {
+        return MM_ERR_UNSUPPORTED;
+    }
+    const uint32_t nb = plan.tile_m;
+    const size_t xs = MMB_MX_XS_B(nb, K);
+    const size_t pb = plan.split_k > 1 ? (plan.ws_needed - MMB_WS_COUNTER_B - xs + 255u) & ~(size_t)255 : 0;
+    if (GR.part_used + pb > ws_region_bytes() ||
+        (plan.split_k > 1 && GR.counters_used + plan.grid_x > MMB_WS_MAX_TILES))
+        return MM_ERR_CAPACITY;
+    /* digit planes: shared with an op of the group that reads the same activations */
+    mmb_gop *g = &GR.g.op[GR.g.n_ops];
+    memset(g, 0, sizeof *g);
+    for (uint32_t i = 0; i < GR.g.n_ops; i++)
+        if (GR.g.op[i].x == op->a && GR.g.op[i].M == M && GR.g.op[i].K == K)
+            g->x_ws = GR.g.op[i].x_ws;
+    if (!g->x_ws) {
+        size_t cap = 0;
+        unsigned char *cache = (unsigned char *)mmb_plane_cache(&cap);
+        const size_t need = (xs + 1023u) & ~(size_t)1023u;
+        if (!cache || GR.cache_used + need > cap)
+            return MM_ERR_CAPACITY;
+        g->x_ws = cache + GR.cache_used;
+        g->slice_here = 1;
+        GR.cache_used += need;
+    }
+    const uint32_t stage = MMB_MX_STAGE_B(plan.tile_n, nb, glu);
+    g->x = op->a; g->y = op->c;
+    g->gs = mm_f4_gscale_get(op->d);
+    g->gs_up = glu ? mm_f4_gscale_get(up_scale) : 0.0f;
+    g->glu = glu; g->gate_plane = glu ? (gate_first ? 0 : 1) : 0;
+    g->M = M; g->K = K; g->N = N;
+    g->rows = plan.tile_n; g->nb = nb; g->k_steps = plan.k_steps; g->split_k = plan.split_k;
+    g->tiles = plan.grid_x; g->unit0 = GR.g.n_units;
+    if (plan.split_k > 1) {
+        g->counters = GR.region + (size_t)GR.counters_used * 4u;
+        g->partial = GR.region + GR.part_used;
+        GR.counters_used += plan.grid_x;
+        GR.part_used += pb;
+    }
+    if (glu) {
+        MM_CHECK(encode_pair(g->tm_payload, pay0, K / 2, N, dpay, 128, plan.tile_n / 2, CU_TENSOR_MAP_SWIZZLE_128B));
+        MM_CHECK(encode_pair(g->tm_scale, sc0, K / 16, N, dsc, 16, plan.tile_n / 2, CU_TENSOR_MAP_SWIZZLE_NONE));
+    } else {
+        MM_CHECK(encode_2d(g->tm_payload, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pay0, K / 2, N, 128, plan.tile_n,
+                           CU_TENSOR_MAP_SWIZZLE_128B));
+        MM_CHECK(encode_2d(g->tm_scale, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, sc0, K / 16, N, 16, plan.tile_n,
+                           CU_TENSOR_MAP_SWIZZLE_NONE));
+    }
+    unsigned char *planes = (unsigned char *)g->x_ws + MMB_MX_PLANES_OFF;
+    MM_CHECK(encode_2d(g->tm_planes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, planes, K / 2, nb, 128, nb,
+                       CU_TENSOR_MAP_SWIZZLE_128B));
+    MM_CHECK(encode_2d(g->tm_sfb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, planes + MMB_MX_PLANES_B(nb, K), K / 16, nb, 16,
+                       nb, CU_TENSOR_MAP_SWIZZLE_NONE));
+    if (stage > GR.g.stage_b) GR.g.stage_b = stage;
+    if (nb > 96u) GR.g.acc_bufs = 1;
+    GR.g.n_units += plan.grid_x * plan.split_k;
+    GR.g.n_ops++;
+    return MM_OK;
+}
+
+mm_status mmb_group_launch(void)
+{
+    MM_REQUIRE(GR.active, MM_ERR_STATE);
+    GR.active = 0;
+    if (GR.g.n_ops == 0)
+        return MM_OK;
+    uint32_t st = (MMB_SMEM_MAX - MMB_MXG_FIXED_B) / GR.g.stage_b;
+    if (st > 6) st = 6;
+    if (st < 2) st = 2;
+    GR.g.stages = st;
+    GR.g.smem_bytes = st * GR.g.stage_b + MMB_MXG_FIXED_B;
+    GR.g.grid = GR.g.n_units < (uint32_t)G.sm_count ? GR.g.n_units : (uint32_t)G.sm_count;
+    uint32_t sliced = 0;
+    for (uint32_t i = 0; i < GR.g.n_ops; i++) sliced += GR.g.op[i].slice_here ? 1u : 0u;
+    int err = mmb_launch_mxg(&GR.g, mm_cuda_stream_raw(MM_ST_COMPUTE));
+    if (err) {
+        MM_LOGE("cuda: group launch (%u ops, %u units): %s", GR.g.n_ops, GR.g.n_units,
+                cudaGetErrorString((cudaError_t)err));
+        return MM_ERR_CUDA;
+    }
+    G.launches += 1u + (sliced ? 1u : 0u);
+    G.sliced_x = NULL;
+    return finish_op();
 }
 
 mm_status mm_f4_linear_tp(const void *x, const void *payload, const void *scale, float gs,

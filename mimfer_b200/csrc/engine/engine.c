@@ -30,6 +30,8 @@ struct mm_lin_engine {
     int          captured;
     int          fuse_mlp;
     int          overlap;
+    int          group;             /* runs of independent decode linears as one persistent launch */
+    uint32_t     n_group_launches;  /* group launches of the last walk */
     uint32_t     n_independent;     /* ops of the last walk launched without a leading wait */
     /* host buffers bound before capture: the copies become nodes of the graph */
     const void **x_bound;           /* [max_ops] pinned host source of op i's activations, or NULL */
@@ -186,6 +188,16 @@ mm_status mm_lin_engine_overlap(mm_lin_engine *e, int on)
 uint32_t mm_lin_engine_n_independent(const mm_lin_engine *e) { return e ? e->n_independent : 0; }
 uint32_t mm_lin_engine_n_sliced_ahead(const mm_lin_engine *e) { return e ? e->n_plane_slots : 0; }
 
+mm_status mm_lin_engine_group(mm_lin_engine *e, int on)
+{
+    MM_REQUIRE(e, MM_ERR_STATE);
+    MM_REQUIRE(!e->captured, MM_ERR_BUSY);
+    e->group = on ? 1 : 0;
+    return MM_OK;
+}
+
+uint32_t mm_lin_engine_n_group_launches(const mm_lin_engine *e) { return e ? e->n_group_launches : 0; }
+
 /* ---- which ops may run ahead of their predecessors --------------------------
  * The reference engine serialises its ops on one stream (src/plan/plan.c:119-130)
  * although many neighbours do not depend on each other: q, k and v read the same
@@ -231,6 +243,30 @@ static int ops_independent(const mm_op_desc *p, const mm_op_desc *q)
 
 /* Events of the runtime shim's pool used while capturing a bound step. */
 enum { EV_FORK = 0, EV_Y = 1, EV_JOIN = 2, EV_OP0 = 4 };   /* EV_OP0 + i: op i's upload */
+
+/* Launch the open group (ops [first, end) that joined it).  With bound host
+ * buffers the group waits for the uploads of all its ops and every output goes
+ * down after the launch. */
+static mm_status engine_close_group(mm_lin_engine *e, uint32_t first, uint32_t end, int with_copies, uint32_t grp)
+{
+    if (mmb_group_size() == 0)
+        return mmb_group_launch();
+    if (with_copies)
+        for (uint32_t k = first / grp; k <= (end - 1) / grp; k++)
+            MM_CHECK(mm_event_wait(EV_OP0 + (int)k, MM_ST_COMPUTE));
+    MM_CHECK(mmb_group_launch());
+    e->n_group_launches++;
+    if (with_copies) {
+        MM_CHECK(mm_event_record(EV_Y, MM_ST_COMPUTE));
+        MM_CHECK(mm_event_wait(EV_Y, MM_ST_XFER));
+        for (uint32_t i = first; i < end; i++) {
+            const mm_op_desc *op = &e->ops[i];
+            if (e->y_bound[i] && op->op != OP_NOP)
+                MM_CHECK(mm_d2h_async(e->y_bound[i], op->c, op_out_bytes(op), MM_ST_XFER));
+        }
+    }
+    return MM_OK;
+}
 
 static mm_status run_ops(mm_lin_engine *e)
 {
@@ -297,7 +333,7 @@ static mm_status run_ops(mm_lin_engine *e)
         e->planes[i] = NULL;
         e->plane_ev[i] = -1;
     }
-    if (e->overlap) {
+    if (e->overlap && !(e->group && mmb_ws_regions() > 1)) {
         size_t cap = 0, used = 0;
         unsigned char *cache = (unsigned char *)mmb_plane_cache(&cap);
         for (uint32_t i = 0; cache && i < e->n_ops; i++) {
@@ -368,9 +404,58 @@ static mm_status run_ops(mm_lin_engine *e)
     const int n_regions = e->overlap ? mmb_ws_regions() : 1;
     e->n_independent = 0;
     int prev_mx = -1;                 /* index of the op in front when it made digit planes, else -1 */
+    uint32_t group_first = 0;         /* first op of the open group */
+    int group_open = 0, group_region = 0;
+    e->n_group_launches = 0;
     for (uint32_t i = 0; i < e->n_ops; i++) {
         const mm_op_desc *op = &e->ops[i];
         const int linear = op->op != OP_NOP && op->op != OP_SILU_MUL && op->op != OP_ADD_RMSNORM;
+        if (e->group && mmb_ws_regions() > 1) {
+            /* Group mode: an op joins the open group when it runs on the block-scaled
+             * kernel and shares no memory with the group's ops; anything else closes
+             * the group (one persistent launch for all its ops) first. */
+            int joined = 0;
+            if (linear) {
+                int indep = 1;
+                for (uint32_t j = group_first; group_open && indep && j < i; j++)
+                    if (e->ops[j].op != OP_NOP && !ops_independent(op, &e->ops[j]))
+                        indep = 0;
+                for (int attempt = 0; attempt < 2 && !joined; attempt++) {
+                    if (!group_open) {
+                        MM_CHECK(mmb_group_begin(MMB_PDL_WAIT_FIRST, group_region));
+                        group_region = (group_region + 1) % mmb_ws_regions();
+                        group_open = 1;
+                        group_first = i;
+                        indep = 1;
+                    }
+                    mm_status gs = indep ? mmb_group_add(op, op->op == MMB_OP_GATE_UP, e->up[i].payload, e->up[i].scale)
+                                         : MM_ERR_CAPACITY;
+                    if (gs == MM_OK) {
+                        joined = 1;
+                    } else if (gs == MM_ERR_CAPACITY && mmb_group_size() > 0) {
+                        MM_CHECK(engine_close_group(e, group_first, i, with_copies, grp));
+                        group_open = 0;
+                    } else if (gs == MM_ERR_UNSUPPORTED || gs == MM_ERR_CAPACITY) {
+                        break;                      /* not a block-scaled op: dispatched on its own below */
+                    } else {
+                        return gs;
+                    }
+                }
+            }
+            if (joined) {
+                if (i > group_first)
+                    e->n_independent++;
+                if (i + 1 == e->n_ops) {
+                    MM_CHECK(engine_close_group(e, group_first, i + 1, with_copies, grp));
+                    group_open = 0;
+                }
+                continue;
+            }
+            if (group_open && op->op != OP_NOP) {
+                MM_CHECK(engine_close_group(e, group_first, i, with_copies, grp));
+                group_open = 0;
+            }
+        }
         mm_f4_plan plan;
         int share = 0;
         if (linear) {
@@ -438,6 +523,8 @@ static mm_status run_ops(mm_lin_engine *e)
             MM_CHECK(mm_d2h_async(e->y_bound[i], op->c, op_out_bytes(op), MM_ST_XFER));
         }
     }
+    if (group_open)
+        MM_CHECK(engine_close_group(e, group_first, e->n_ops, with_copies, grp));
     if (with_copies || n_slots) {
         MM_CHECK(mm_event_record(EV_JOIN, MM_ST_XFER));
         MM_CHECK(mm_event_wait(EV_JOIN, MM_ST_COMPUTE));

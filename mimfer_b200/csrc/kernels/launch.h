@@ -57,6 +57,12 @@ extern "C" {
 #define MMB_MX_PLANES_B(nb, K) ((((size_t)(nb) * ((K) / 2u)) + 1023u) & ~(size_t)1023u)
 #define MMB_MX_XS_B(nb, K)  (MMB_MX_PLANES_OFF + MMB_MX_PLANES_B(nb, K) + ((((size_t)(nb) * ((K) / 16u)) + 1023u) & ~(size_t)1023u))
 
+/* ---- MXG (a group of independent decode linears in one persistent launch) ------- */
+#define MMB_MXG_THREADS     480u   /* TMA, 2 x MMA, 8 x scale copy, 4 x epilogue                       */
+#define MMB_MXG_MAX_OPS     48u    /* the op list travels in the kernel's parameter space (32 KB)      */
+#define MMB_MXG_ACC_STRIDE  192u   /* tensor-memory columns between the two accumulator buffers        */
+#define MMB_MXG_FIXED_B     (512u + 1024u)
+
 /* ---- UMMA (prefill) geometry ---------------------------------------------- */
 #define MMB_UM_KBLOCK      64u    /* bf16 elements per smem row (128 B swizzle) */
 #define MMB_UM_KGROUP      256u   /* weights covered by one scale box (16 B)    */
@@ -152,6 +158,32 @@ typedef struct mmb_args {
     unsigned char tm_x[128] __attribute__((aligned(64)));     /* MX: the digit planes */
     unsigned char tm_sfb[128] __attribute__((aligned(64)));   /* MX: the planes' block scales */
 } mmb_args;
+
+/* One op of a group launch, and the group (host side; mxg.cu turns it into the
+ * kernel's parameter block). */
+typedef struct mmb_gop {
+    const void *x;            /* bf16 [M][K] */
+    void       *y;            /* bf16 [M][N] */
+    void       *x_ws;         /* activation scratch (row factors, digit planes, plane scales) */
+    int         slice_here;   /* this op is the first of the group to read x: slice it        */
+    void       *partial, *counters;
+    float       gs, gs_up;
+    int         glu, gate_plane;
+    uint32_t    M, K, N;
+    uint32_t    rows, nb, k_steps, split_k, tiles, unit0;
+    unsigned char tm_payload[128] __attribute__((aligned(64)));
+    unsigned char tm_scale[128] __attribute__((aligned(64)));
+    unsigned char tm_planes[128] __attribute__((aligned(64)));
+    unsigned char tm_sfb[128] __attribute__((aligned(64)));
+} mmb_gop;
+
+typedef struct mmb_group {
+    uint32_t n_ops, n_units, stages, acc_bufs, stage_b, smem_bytes, grid;
+    int      pdl;
+    mmb_gop  op[MMB_MXG_MAX_OPS];
+} mmb_group;
+
+int mmb_launch_mxg(const mmb_group *g, void *stream);
 
 /* Each returns a cudaError_t value (0 = success) from the launch. `stream`
  * is a cudaStream_t. */

@@ -1,0 +1,572 @@
+/*
+ * MXG: a group of independent NVFP4 decode linears in ONE persistent launch on
+ * the block-scaled tensor path (the kernel of mx.cu turned into a work loop).
+ *
+ * A decode step is hundreds of short linears (3 to 100 MB of weights each).
+ * Launched one by one, each pays its own launch, pipeline fill, tail and split-K
+ * exchange, and the weight stream stops between them.  Here the ops the
+ * engine has shown to be independent of each other (q, k and v of a layer; gate
+ * and up; in a benchmark of stand-alone linears, all of them) are cut into work
+ * units (op, row tile, K slice) that the CTAs, one per SM, take in round-robin
+ * order.  The TMA producer of a CTA runs ahead across unit and op borders, so
+ * the weight stream never stops; the accumulators are double-buffered in tensor
+ * memory (M <= 16), so a unit's epilogue overlaps the next unit's MMAs.
+ *
+ * The op list travels in the kernel's parameter space (up to 48 ops, 30 KB):
+ * tensor maps there are usable by TMA as they are, nothing is uploaded.
+ *
+ * Per-op arithmetic, scale clean-up, epilogue and split-K exchange are those of
+ * mx.cu; results are bit-identical to the single-op launches.
+ *
+ * Warp roles (15 warps): 0 = TMA producer; 1 and 10 = MMA issue (first / second
+ * 128-row half); 2..9 = scale-factor copies into tensor memory (lane quadrant x
+ * parity of the K step); 11..14 = epilogue (one per lane quadrant).
+ *
+ * It replaces a run of launches of the reference's one-thread-per-output kernel
+ * (src/kernels/cuda/cx.cu:345-376), one per linear of the op walk
+ * (src/plan/plan.c:119-138).
+ */
+#include "fp4.cuh"
+#include "ptx.cuh"
+#include "mx.cuh"
+
+namespace mmb {
+
+struct __align__(128) MxgOp {
+    TmaDesc         tm_payload, tm_scale, tm_planes, tm_sfb;
+    uint16_t       *y;
+    const float    *row_scale;
+    float          *partial;
+    unsigned       *counters;
+    float           gs, gs_up;
+    uint32_t        M, N;
+    uint32_t        rows, nb, k_steps, split_k, tiles, unit0;
+    uint32_t        glu, gate_plane;
+    uint32_t        pad[12];
+};
+static_assert(sizeof(MxgOp) == 640, "MxgOp layout");
+
+struct __align__(128) MxgGroup {
+    uint32_t  n_ops, n_units, stages, acc_bufs;
+    uint32_t  stage_b, pdl;
+    unsigned *status;
+    uint32_t  pad[24];
+    MxgOp     ops[MMB_MXG_MAX_OPS];
+};
+static_assert(sizeof(MxgGroup) <= 32764, "kernel parameter space");
+
+/* The units of one CTA, in order: global unit g = blockIdx.x, + gridDim.x, ... */
+struct UnitWalk {
+    uint32_t g, op;
+    __device__ __forceinline__ void start() { g = blockIdx.x; op = 0; }
+    __device__ __forceinline__ bool valid(const MxgGroup &grp)
+    {
+        if (g >= grp.n_units)
+            return false;
+        while (op + 1u < grp.n_ops && g >= grp.ops[op + 1u].unit0) op++;
+        return true;
+    }
+    __device__ __forceinline__ void next() { g += gridDim.x; }
+};
+
+struct UnitGeom {
+    uint32_t tile, slice, ks_begin, nsteps;
+    uint32_t rows, nb, halves, h1, cnt0, cnt1, row0;
+    uint32_t o_pl, o_sc, o_sfb, tx;
+    bool glu;
+};
+
+__device__ __forceinline__ UnitGeom unit_geom(const MxgOp &o, uint32_t g)
+{
+    UnitGeom u;
+    const uint32_t v = g - o.unit0;
+    u.tile = v / o.split_k;
+    u.slice = v - u.tile * o.split_k;
+    u.ks_begin = static_cast<uint32_t>(static_cast<uint64_t>(o.k_steps) * u.slice / o.split_k);
+    u.nsteps = static_cast<uint32_t>(static_cast<uint64_t>(o.k_steps) * (u.slice + 1u) / o.split_k) - u.ks_begin;
+    u.glu = o.glu != 0u;
+    u.rows = o.rows; u.nb = o.nb;
+    u.halves = u.glu ? 2u : (u.rows > 128u ? 2u : 1u);
+    u.h1 = u.glu ? u.rows >> 1 : 128u;
+    u.cnt0 = u.glu ? u.rows >> 1 : (u.rows < 128u ? u.rows : 128u);
+    u.cnt1 = u.rows - u.cnt0;
+    u.row0 = u.tile * (u.glu ? u.rows >> 1 : u.rows);
+    u.o_pl = (u.glu || u.rows > 128u) ? 32768u : 16384u;
+    u.o_sc = u.o_pl + u.nb * 128u;
+    u.o_sfb = u.o_sc + ((u.rows * 16u + 127u) & ~127u);
+    u.tx = u.rows * 144u + u.nb * 144u;
+    return u;
+}
+
+__device__ __forceinline__ void mxg_load_weights(const MxgOp &o, const UnitGeom &u, uint32_t st, uint32_t ks,
+                                                 uint32_t bar)
+{
+    if (u.glu) {
+        tma_load_3d(st, &o.tm_payload, static_cast<int>(ks * 128u), static_cast<int>(u.row0), 0, bar);
+        tma_load_3d(st + u.o_sc, &o.tm_scale, static_cast<int>(ks * 16u), static_cast<int>(u.row0), 0, bar);
+    } else {
+        tma_load_2d(st, &o.tm_payload, static_cast<int>(ks * 128u), static_cast<int>(u.row0), bar);
+        tma_load_2d(st + u.o_sc, &o.tm_scale, static_cast<int>(ks * 16u), static_cast<int>(u.row0), bar);
+    }
+}
+__device__ __forceinline__ void mxg_load_planes(const MxgOp &o, const UnitGeom &u, uint32_t st, uint32_t ks,
+                                                uint32_t bar)
+{
+    tma_load_2d(st + u.o_pl, &o.tm_planes, static_cast<int>(ks * 128u), 0, bar);
+    tma_load_2d(st + u.o_sfb, &o.tm_sfb, static_cast<int>(ks * 16u), 0, bar);
+}
+
+__global__ void __maxnreg__(128)
+f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
+{
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t ST = grp.stages, stage_b = grp.stage_b, AB = grp.acc_bufs;
+    const uint32_t bars = base + ST * stage_b;
+    const uint32_t bar_full = bars;                       /* [ST] TMA landed                       */
+    const uint32_t bar_empty = bar_full + 8u * ST;        /* [ST] both MMA threads past the stage  */
+    const uint32_t bar_sf_full = bar_empty + 8u * ST;     /* [2]  scale factors in tensor memory   */
+    const uint32_t bar_acc_full = bar_sf_full + 16u;      /* [2]  a unit's MMAs done               */
+    const uint32_t bar_acc_empty = bar_acc_full + 16u;    /* [2]  its accumulators read            */
+    const uint32_t tmem_slot = bar_acc_empty + 16u;
+    const uint32_t last_flag = tmem_slot + 4u;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < ST; s++) {
+            mbar_init(bar_full + 8u * s, 1u);
+            mbar_init(bar_empty + 8u * s, 2u);
+        }
+        for (uint32_t t = 0; t < 2u; t++) {
+            mbar_init(bar_sf_full + 8u * t, 4u);
+            mbar_init(bar_acc_full + 8u * t, 2u);
+            mbar_init(bar_acc_empty + 8u * t, 4u);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512u);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = lds32(tmem_slot);
+
+    if (warp == 0) {
+        /* ------------------------------ TMA producer -------------------------- *
+         * The weights of the first ring go out before the grid-dependency wait, the
+         * digit planes (made by the kernel in front) after it; from then on a step's
+         * four boxes go out together as soon as its stage is free. */
+        if (lane == 0) {
+            UnitWalk w;
+            uint32_t s = 0, issued = 0;
+            w.start();
+            while (issued < ST && w.valid(grp)) {
+                const MxgOp &o = grp.ops[w.op];
+                const UnitGeom u = unit_geom(o, w.g);
+                uint32_t it = 0;
+                for (; it < u.nsteps && issued < ST; it++, issued++, s++) {
+                    mbar_expect_tx(bar_full + 8u * s, u.tx);
+                    mxg_load_weights(o, u, base + s * stage_b, u.ks_begin + it, bar_full + 8u * s);
+                }
+                if (it == u.nsteps)
+                    w.next();
+                else
+                    break;
+            }
+            if (grp.pdl != MMB_PDL_OFF)
+                grid_dep_launch();
+            grid_dep_wait();
+            /* second walk over the same steps for the planes, then on */
+            w.start();
+            s = 0;
+            uint32_t round = 0, gstep = 0;
+            while (w.valid(grp)) {
+                const MxgOp &o = grp.ops[w.op];
+                const UnitGeom u = unit_geom(o, w.g);
+                for (uint32_t it = 0; it < u.nsteps; it++, gstep++, s = (s + 1u == ST) ? 0u : s + 1u, round += (s == 0u)) {
+                    const uint32_t st = base + s * stage_b, bar = bar_full + 8u * s;
+                    if (gstep >= ST) {
+                        mbar_wait(bar_empty + 8u * s, (round - 1u) & 1u, grp.status);
+                        mbar_expect_tx(bar, u.tx);
+                        mxg_load_weights(o, u, st, u.ks_begin + it, bar);
+                    }
+                    mxg_load_planes(o, u, st, u.ks_begin + it, bar);
+                }
+                w.next();
+            }
+        }
+    } else if (warp == 1 || warp == 10) {
+        /* ------------------------------ MMA issue ------------------------------ */
+        const uint32_t h = warp == 1 ? 0u : 1u;
+        if (lane == 0) {
+            UnitWalk w;
+            uint32_t s = 0, round = 0, gstep = 0, j = 0;
+            for (w.start(); w.valid(grp); w.next(), j++) {
+                const MxgOp &o = grp.ops[w.op];
+                const UnitGeom u = unit_geom(o, w.g);
+                const uint32_t buf = AB == 2u ? (j & 1u) : 0u, use = j / AB;
+                if (use >= 1u)                       /* the epilogue has drained this buffer's previous unit */
+                    mbar_wait(bar_acc_empty + 8u * buf, (use - 1u) & 1u, grp.status);
+                tc_fence_after();
+                const uint32_t idesc = umma_idesc_mxf4(u.nb);
+                const uint32_t d = tmem + buf * MMB_MXG_ACC_STRIDE + h * u.nb;
+                for (uint32_t it = 0; it < u.nsteps; it++, gstep++, s = (s + 1u == ST) ? 0u : s + 1u, round += (s == 0u)) {
+                    const uint32_t t = gstep & 1u, st = base + s * stage_b;
+                    mbar_wait(bar_full + 8u * s, round & 1u, grp.status);
+                    if (h < u.halves) {
+                        mbar_wait(bar_sf_full + 8u * t, (gstep >> 1) & 1u, grp.status);
+                        tc_fence_after();
+                        const uint32_t sf = tmem + MMB_MX_SF_COL + t * MMB_MX_SF_SLOT;
+                        const uint64_t ad = umma_desc_sw128(st + h * u.h1 * 128u), bd = umma_desc_sw128(st + u.o_pl);
+#pragma unroll
+                        for (uint32_t q = 0; q < 4u; q++)
+                            umma_mxf4(d, ad + 2u * q, bd + 2u * q, idesc, (it | q) ? 1u : 0u,
+                                      sf + h * 16u + 4u * q, sf + MMB_MX_SFB_OFF + 8u * q);
+                    }
+                    umma_commit(bar_empty + 8u * s);
+                }
+                umma_commit(bar_acc_full + 8u * buf);
+            }
+        }
+    } else if (warp < 10) {
+        /* ------------------------------ scale factors --------------------------- */
+        const uint32_t quad = warp & 3u;
+        const uint32_t mine_t = (warp - 2u) >> 2;
+        const uint32_t tq = tmem + ((quad * 32u) << 16);
+        UnitWalk w;
+        uint32_t s = 0, round = 0, gstep = 0;
+        uint32_t s1 = 0, round1 = 0, s2 = 0, round2 = 0;
+        for (w.start(); w.valid(grp); w.next()) {
+            const MxgOp &o = grp.ops[w.op];
+            const UnitGeom u = unit_geom(o, w.g);
+            const uint32_t ncol = (u.nb + 31u) >> 5;
+            for (uint32_t it = 0; it < u.nsteps; it++, gstep++, s2 = s1, round2 = round1, s1 = s, round1 = round,
+                                                s = (s + 1u == ST) ? 0u : s + 1u, round += (s == 0u)) {
+                const uint32_t t = gstep & 1u, st = base + s * stage_b;
+                if (t != mine_t)
+                    continue;
+                mbar_wait_warp(bar_full + 8u * s, round & 1u, grp.status);
+                if (gstep >= 2u)
+                    mbar_wait_warp(bar_empty + 8u * s2, round2 & 1u, grp.status);
+                tc_fence_after();
+                const uint32_t sf = tq + MMB_MX_SF_COL + t * MMB_MX_SF_SLOT;
+                bool patched = false;
+                uint32_t v[64];
+                uint4 qa[8];
+#pragma unroll
+                for (uint32_t i = 0; i < 8u; i++) {
+                    const uint32_t in_half = 32u * (i & 3u) + lane;
+                    qa[i] = make_uint4(0u, 0u, 0u, 0u);
+                    if (in_half < ((i >> 2) ? u.cnt1 : u.cnt0))
+                        qa[i] = lds128(st + u.o_sc + ((i >> 2) * u.h1 + in_half) * 16u);
+                }
+                uint32_t negs = 0u;
+#pragma unroll
+                for (uint32_t i = 0; i < 8u; i++) {
+                    const uint32_t wv[4] = { qa[i].x, qa[i].y, qa[i].z, qa[i].w };
+#pragma unroll
+                    for (uint32_t q = 0; q < 4u; q++) {
+                        const uint32_t nan = (((wv[q] & 0x7f7f7f7fu) + 0x01010101u) & 0x80808080u) >> 7;
+                        const uint32_t clean = wv[q] & ~(nan * 0xffu);
+                        negs |= clean & 0x80808080u;
+                        v[(i >> 2) * 16u + 4u * q + (i & 3u)] = clean & 0x7f7f7f7fu;
+                    }
+                }
+                if (__any_sync(0xffffffffu, negs != 0u)) {
+                    if (quad == 2u && negs) {
+#pragma unroll
+                        for (uint32_t i = 0; i < 8u; i++) {
+                            const uint32_t r = (i >> 2) * u.h1 + 32u * (i & 3u) + lane;
+                            const uint32_t wv[4] = { qa[i].x, qa[i].y, qa[i].z, qa[i].w };
+#pragma unroll
+                            for (uint32_t q = 0; q < 4u; q++) {
+                                const uint32_t nan = (((wv[q] & 0x7f7f7f7fu) + 0x01010101u) & 0x80808080u) >> 7;
+                                const uint32_t neg = wv[q] & ~(nan * 0xffu) & 0x80808080u;
+                                for (uint32_t b = 0; neg && b < 4u; b++)
+                                    if (neg & (0x80u << (8u * b))) {
+                                        const uint32_t off = (4u * q + b) * 8u;
+                                        const uint32_t a = st + r * 128u + ((((off >> 4) ^ (r & 7u)) << 4) | (off & 15u));
+                                        sts32(a, lds32(a) ^ 0x88888888u);
+                                        sts32(a + 4u, lds32(a + 4u) ^ 0x88888888u);
+                                    }
+                            }
+                        }
+                    }
+                    patched = true;
+                }
+#pragma unroll
+                for (uint32_t c = 0; c < 8u; c++) {
+                    const uint32_t r = 32u * c + lane;
+                    uint4 q = make_uint4(0u, 0u, 0u, 0u);
+                    if (c < ncol && r < u.nb)
+                        q = lds128(st + u.o_sfb + r * 16u);
+                    v[MMB_MX_SFB_OFF + c] = q.x;
+                    v[MMB_MX_SFB_OFF + 8u + c] = q.y;
+                    v[MMB_MX_SFB_OFF + 16u + c] = q.z;
+                    v[MMB_MX_SFB_OFF + 24u + c] = q.w;
+                }
+                tmem_st_x64(sf, v);
+                tmem_st_wait();
+                if (patched)
+                    fence_proxy_async_smem();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(bar_sf_full + 8u * t);
+            }
+        }
+    } else {
+        /* ------------------------------ epilogue -------------------------------- *
+         * Thread = weight row; a unit's accumulators are read while the MMA threads
+         * fill the other buffer with the next unit. */
+        const uint32_t quad = warp & 3u;
+        const uint32_t tq = tmem + ((quad * 32u) << 16);
+        const uint32_t lr = quad * 32u + lane;
+        const uint32_t etid = tid - 11u * 32u;             /* 0..127 */
+        grid_dep_wait();                                    /* row factors come from the kernel in front */
+        UnitWalk w;
+        uint32_t j = 0;
+        for (w.start(); w.valid(grp); w.next(), j++) {
+            const MxgOp &o = grp.ops[w.op];
+            const UnitGeom u = unit_geom(o, w.g);
+            const uint32_t buf = AB == 2u ? (j & 1u) : 0u, use = j / AB;
+            const uint32_t groups = u.nb / 24u;
+            const bool direct = o.split_k == 1u;
+            const uint32_t pitch = u.glu ? o.tiles * 256u : o.N;
+            /* row factors: lane l holds entries l and l + 32 of the [32][2] table */
+            const float ra = lane < 2u * o.M ? __ldcg(o.row_scale + lane) : 0.0f;
+            const float rb = lane + 32u < 2u * o.M ? __ldcg(o.row_scale + lane + 32u) : 0.0f;
+            mbar_wait_warp(bar_acc_full + 8u * buf, use & 1u, grp.status);
+            tc_fence_after();
+            const uint32_t d0 = tq + buf * MMB_MXG_ACC_STRIDE;
+            float *mine = o.partial + static_cast<size_t>(u.slice) * (groups * 4u) * pitch;
+            for (uint32_t g4 = 0; g4 < groups; g4++) {
+                uint32_t c0[24], c1[24];
+                tmem_ld_x8(d0 + g4 * 24u, *reinterpret_cast<uint32_t (*)[8]>(&c0[0]));
+                tmem_ld_x8(d0 + g4 * 24u + 8u, *reinterpret_cast<uint32_t (*)[8]>(&c0[8]));
+                tmem_ld_x8(d0 + g4 * 24u + 16u, *reinterpret_cast<uint32_t (*)[8]>(&c0[16]));
+                if (u.halves == 2u) {
+                    tmem_ld_x8(d0 + u.nb + g4 * 24u, *reinterpret_cast<uint32_t (*)[8]>(&c1[0]));
+                    tmem_ld_x8(d0 + u.nb + g4 * 24u + 8u, *reinterpret_cast<uint32_t (*)[8]>(&c1[8]));
+                    tmem_ld_x8(d0 + u.nb + g4 * 24u + 16u, *reinterpret_cast<uint32_t (*)[8]>(&c1[16]));
+                }
+                tmem_ld_wait();
+#pragma unroll
+                for (int r = 0; r < 4; r++) {
+                    const uint32_t m = g4 * 4u + r;            /* warp-uniform */
+                    if (m >= o.M)
+                        break;
+                    const uint32_t e = 2u * m;
+                    const float f1 = e < 32u ? __shfl_sync(0xffffffffu, ra, e) : __shfl_sync(0xffffffffu, rb, e - 32u);
+                    const float f2 = e + 1u < 32u ? __shfl_sync(0xffffffffu, ra, e + 1u)
+                                                  : __shfl_sync(0xffffffffu, rb, e - 31u);
+                    const float a0 = mx_row_sum(c0, r) * f1 * f2;
+                    const float a1 = u.halves == 2u ? mx_row_sum(c1, r) * f1 * f2 : 0.0f;
+                    if (u.glu) {
+                        const uint32_t n = u.row0 + lr;
+                        const bool ok = lr < u.cnt0 && n < o.N;
+                        if (direct) {
+                            if (ok)
+                                o.y[static_cast<size_t>(m) * o.N + n] =
+                                    glu_out_bf16(o.gate_plane ? a1 : a0, o.gate_plane ? a0 : a1, o.gs, o.gs_up);
+                        } else if (ok) {
+                            __stcg(mine + static_cast<size_t>(m) * pitch + u.tile * 256u + lr, a0);
+                            __stcg(mine + static_cast<size_t>(m) * pitch + u.tile * 256u + 128u + lr, a1);
+                        }
+                    } else {
+#pragma unroll
+                        for (uint32_t hh = 0; hh < 2u; hh++) {
+                            if (hh >= u.halves)
+                                break;
+                            const uint32_t n = u.row0 + hh * 128u + lr;
+                            const float a = hh ? a1 : a0;
+                            if (lr >= (hh ? u.cnt1 : u.cnt0) || n >= o.N)
+                                continue;
+                            if (direct) {
+                                __nv_bfloat16 hv = __float2bfloat16_rn(a * o.gs);
+                                o.y[static_cast<size_t>(m) * o.N + n] = *reinterpret_cast<uint16_t *>(&hv);
+                            } else {
+                                __stcg(mine + static_cast<size_t>(m) * pitch + n, a);
+                            }
+                        }
+                    }
+                }
+            }
+            /* the accumulators are in registers or stored: the buffer may be refilled */
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(bar_acc_empty + 8u * buf);
+            if (!direct) {
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (etid == 0u) {
+                    __threadfence();
+                    const unsigned ticket = atomicAdd(o.counters + u.tile, 1u);
+                    __threadfence();
+                    sts32(last_flag, (ticket == o.split_k - 1u) ? 1u : 0u);
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (lds32(last_flag)) {
+                    const size_t slice = static_cast<size_t>(groups * 4u) * pitch;
+                    const uint32_t col0 = u.glu ? u.tile * 256u + lr : u.row0 + lr, col1 = col0 + 128u;
+                    const bool ok0 = lr < u.cnt0 && u.row0 + lr < o.N;
+                    const bool ok1 = u.glu ? ok0 : (lr < u.cnt1 && u.row0 + 128u + lr < o.N);
+                    for (uint32_t m0 = 0; m0 < o.M; m0 += 4u) {
+                        float s0[4] = { 0.0f, 0.0f, 0.0f, 0.0f }, s1[4] = { 0.0f, 0.0f, 0.0f, 0.0f };
+                        for (uint32_t sl0 = 0; sl0 < o.split_k; sl0 += 4u) {
+                            float v0[4][4], v1[4][4];
+#pragma unroll
+                            for (uint32_t r = 0; r < 4u; r++)
+#pragma unroll
+                                for (uint32_t q = 0; q < 4u; q++) {
+                                    const bool live = m0 + r < o.M && sl0 + q < o.split_k;
+                                    const float *src = o.partial + (sl0 + q) * slice + static_cast<size_t>(m0 + r) * pitch;
+                                    v0[r][q] = live && ok0 ? __ldcg(src + col0) : 0.0f;
+                                    v1[r][q] = live && ok1 ? __ldcg(src + col1) : 0.0f;
+                                }
+#pragma unroll
+                            for (uint32_t r = 0; r < 4u; r++)
+#pragma unroll
+                                for (uint32_t q = 0; q < 4u; q++) {
+                                    s0[r] += v0[r][q];
+                                    s1[r] += v1[r][q];
+                                }
+                        }
+#pragma unroll
+                        for (uint32_t r = 0; r < 4u; r++) {
+                            const uint32_t m = m0 + r;
+                            if (m >= o.M)
+                                break;
+                            if (u.glu) {
+                                if (ok0)
+                                    o.y[static_cast<size_t>(m) * o.N + u.row0 + lr] =
+                                        glu_out_bf16(o.gate_plane ? s1[r] : s0[r], o.gate_plane ? s0[r] : s1[r],
+                                                     o.gs, o.gs_up);
+                            } else {
+                                if (ok0) {
+                                    __nv_bfloat16 hv = __float2bfloat16_rn(s0[r] * o.gs);
+                                    o.y[static_cast<size_t>(m) * o.N + u.row0 + lr] = *reinterpret_cast<uint16_t *>(&hv);
+                                }
+                                if (ok1) {
+                                    __nv_bfloat16 hv = __float2bfloat16_rn(s1[r] * o.gs);
+                                    o.y[static_cast<size_t>(m) * o.N + u.row0 + 128u + lr] =
+                                        *reinterpret_cast<uint16_t *>(&hv);
+                                }
+                            }
+                        }
+                    }
+                    if (etid == 0u)
+                        o.counters[u.tile] = 0u;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");     /* last_flag is reused by the next unit */
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512u);
+    }
+}
+
+/* Digit planes of every distinct activation tensor of a group, one launch:
+ * blockIdx.z picks the tensor. */
+struct XsliceItem {
+    const uint16_t *x;
+    uint8_t        *scratch;
+    uint32_t        M, K, m_pad, nb;
+};
+struct XsliceGroup {
+    uint32_t   n, pdl;
+    XsliceItem item[MMB_MXG_MAX_OPS];
+};
+
+__global__ void __launch_bounds__(256)
+f4_xslice_group_kernel(const __grid_constant__ XsliceGroup g)
+{
+    grid_dep_launch();
+    if (g.pdl != MMB_PDL_OFF)
+        grid_dep_wait();
+    const XsliceItem &it = g.item[blockIdx.z];
+    if (blockIdx.y >= it.m_pad || blockIdx.x * 1024u >= it.K)
+        return;
+    uint8_t *planes = it.scratch + MMB_MX_PLANES_OFF;
+    xslice_cta(it.x, planes, planes + MMB_MX_PLANES_B(it.nb, it.K),
+               reinterpret_cast<float *>(it.scratch + MMB_MX_ROWSCALE_OFF), it.M, it.K, blockIdx.y, blockIdx.x);
+}
+} // namespace mmb
+
+extern "C" int mmb_mxg_init(void)
+{
+    return static_cast<int>(cudaFuncSetAttribute(mmb::f4_mxg_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 MMB_SMEM_MAX));
+}
+
+extern "C" int mmb_launch_mxg(const mmb_group *hg, void *stream)
+{
+    static mmb::MxgGroup grp;            /* built in place: 30 KB is too much for the stack of a small thread */
+    static mmb::XsliceGroup xs;
+    unsigned *status = nullptr;
+    int e = mmb_status_word(&status);
+    if (e) return e;
+    if (hg->n_ops == 0 || hg->n_ops > MMB_MXG_MAX_OPS)
+        return static_cast<int>(cudaErrorInvalidValue);
+    memset(&grp, 0, sizeof grp);
+    memset(&xs, 0, sizeof xs);
+    grp.n_ops = hg->n_ops; grp.n_units = hg->n_units; grp.stages = hg->stages; grp.acc_bufs = hg->acc_bufs;
+    grp.stage_b = hg->stage_b; grp.pdl = static_cast<uint32_t>(hg->pdl); grp.status = status;
+    uint32_t max_m = 0, max_kx = 0;
+    for (uint32_t i = 0; i < hg->n_ops; i++) {
+        const mmb_gop &s = hg->op[i];
+        mmb::MxgOp &d = grp.ops[i];
+        memcpy(d.tm_payload.bytes, s.tm_payload, 128);
+        memcpy(d.tm_scale.bytes, s.tm_scale, 128);
+        memcpy(d.tm_planes.bytes, s.tm_planes, 128);
+        memcpy(d.tm_sfb.bytes, s.tm_sfb, 128);
+        d.y = static_cast<uint16_t *>(s.y);
+        d.row_scale = reinterpret_cast<const float *>(static_cast<const unsigned char *>(s.x_ws) + MMB_MX_ROWSCALE_OFF);
+        d.partial = static_cast<float *>(s.partial);
+        d.counters = static_cast<unsigned *>(s.counters);
+        d.gs = s.gs; d.gs_up = s.gs_up;
+        d.M = s.M; d.N = s.N;
+        d.rows = s.rows; d.nb = s.nb; d.k_steps = s.k_steps; d.split_k = s.split_k; d.tiles = s.tiles;
+        d.unit0 = s.unit0;
+        d.glu = s.glu ? 1u : 0u; d.gate_plane = s.gate_plane ? 1u : 0u;
+        if (s.slice_here) {
+            mmb::XsliceItem &it = xs.item[xs.n++];
+            it.x = static_cast<const uint16_t *>(s.x);
+            it.scratch = static_cast<uint8_t *>(s.x_ws);
+            it.M = s.M; it.K = s.K; it.nb = s.nb; it.m_pad = s.nb / MMB_MX_PLANES;
+            if (it.m_pad > max_m) max_m = it.m_pad;
+            if ((s.K + 1023u) / 1024u > max_kx) max_kx = (s.K + 1023u) / 1024u;
+        }
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = hg->pdl ? 1 : 0;
+    if (xs.n) {
+        xs.pdl = static_cast<uint32_t>(hg->pdl);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(max_kx, max_m, xs.n);
+        cfg.blockDim = dim3(256);
+        cfg.stream = st;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t err = cudaLaunchKernelEx(&cfg, mmb::f4_xslice_group_kernel, xs);
+        if (err != cudaSuccess)
+            return static_cast<int>(err);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(hg->grid);
+    cfg.blockDim = dim3(MMB_MXG_THREADS);
+    cfg.dynamicSmemBytes = hg->smem_bytes;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, mmb::f4_mxg_kernel, grp));
+}

@@ -282,6 +282,13 @@ class LinearEngine:
         order, 2 = run-ahead ops may also take a shallower K split."""
         L.check(self.rt.lib.mm_lin_engine_overlap(self.h, int(on)), "mm_lin_engine_overlap")
 
+    def group(self, on=True):
+        """Runs of independent decode linears as one persistent launch (mm_lin_engine_group)."""
+        L.check(self.rt.lib.mm_lin_engine_group(self.h, int(on)), "mm_lin_engine_group")
+
+    def n_group_launches(self):
+        return self.rt.lib.mm_lin_engine_n_group_launches(self.h)
+
     def n_independent(self):
         return self.rt.lib.mm_lin_engine_n_independent(self.h)
 
