@@ -139,8 +139,6 @@ typedef enum mm_f4_variant {
     MM_F4_V_ROWWARP = 0,  /* any K%16==0: one warp per weight row, shuffles  */
     MM_F4_V_STREAM  = 1,  /* decode: TMA-staged weight stream + warp MMA     */
     MM_F4_V_UMMA    = 2,  /* prefill: tcgen05 kind::f16, TMEM accumulators   */
-    MM_F4_V_STREAMT = 3,  /* decode: TMA-staged weight stream, weights       */
-                          /*   dequantised into tensor memory, tcgen05 MMA   */
     MM_F4_V_MX      = 4   /* decode: block-scaled tcgen05 MMA on the packed  */
                           /*   payload and its e4m3 scales as they lie in    */
                           /*   memory; activations as e2m1 digit planes      */
@@ -157,7 +155,7 @@ typedef struct mm_f4_plan {
     int      variant;         /* mm_f4_variant                                */
     uint32_t m_tiles;         /* STREAM: 8-row activation tiles (1 to 4); MX: */
                               /*   groups of four activation rows (1 to 8)    */
-    uint32_t tile_m, tile_n;  /* UMMA: CTA tile; STREAM/STREAMT/MX: tile_n =  */
+    uint32_t tile_m, tile_n;  /* UMMA: CTA tile; STREAM/MX: tile_n =  */
                               /*   W rows per CTA, tile_m = padded activation */
                               /*   rows (MX: digit-plane rows, 24 per group)  */
     uint32_t split_k;         /* >= 1                                         */
@@ -193,12 +191,22 @@ mm_status mm_f4_linear(const void *x, const void *payload, const void *scale,
  * reference, which keeps activations in bf16, src/kernels/cpu/cx.c:211).  The tensor
  * core multiplies e2m1 by e2m1, so the bf16 activations x [M][K] (M <= 32, K a
  * multiple of 256) are rewritten as six signed e2m1 digit planes per row with
- * power-of-two block scales, exact for every value within 2^9 of its 16-wide
- * block's largest and rounded at 2^-17 of that largest below.  mm_f4_linear does
+ * power-of-two block scales.  A 16-wide block's unit is 2^-16 of its largest
+ * magnitude's power of two (2^-19 of the row's, if that is larger): every value
+ * that is a multiple of the unit is kept exactly - all values within 2^9 of the
+ * block's largest - and the rest is rounded to the nearest multiple.  mm_f4_linear does
  * this itself in front of its kernel; an owner of a whole op list does it once per
  * distinct activation tensor per step, ahead of the ops (the op-list engine does,
  * in overlap mode, into the upper half of the workspace).  `scratch`: device
- * memory, 256-byte aligned, mm_f4_xslice_bytes(M, K) bytes. */
+ * memory, 256-byte aligned, mm_f4_xslice_bytes(M, K) bytes.  Its layout, with
+ * R = 6 * (M rounded up to a multiple of 4) plane rows:
+ *   byte 0       float f[2 * m], f[2 * m + 1]: row m's value = (sum of its planes) * f1 * f2
+ *   byte 1024    scratch of the two-pass slicing of an op group
+ *   byte 16384   planes  [R][K / 2]   row 6 * m + p = digit plane p of activation row m,
+ *                                     e2m1 codes, low nibble = even column
+ *   then         scales  [R][K / 16]  one ue4m3 byte (a power of two) per 16-wide block
+ * x[m][k] ~= f1 * f2 * sum over p of e2m1(planes[6m+p][k]) * ue4m3(scales[6m+p][k/16]);
+ * rows m >= M are zero. */
 size_t    mm_f4_xslice_bytes(uint32_t M, uint32_t K);
 mm_status mm_f4_xslice(const void *x, uint32_t M, uint32_t K, void *scratch, size_t scratch_bytes, void *stream);
 
@@ -279,10 +287,17 @@ mm_status mm_f4_tp_barrier(void *const *flags_all, uint32_t n_ranks, uint32_t ra
  *    arrival counters are zeroed on `stream` before each launch.  Two calls of
  *    one process that overlap on the GPU (issued on different streams) race on
  *    it: keep the calls on one stream or order them with events.  Separate
- *    processes have separate copies. */
+ *    processes have separate copies.
+ *  - A device-side wait that gave up (the kernel's waits are bounded) raises a
+ *    bit in the device status word and the output is then not valid.  A caller
+ *    that uses the runtime shim reads it with mm_f4_device_status; one that does
+ *    not reads it with mm_f4_device_status_on(stream, &flags), which synchronises
+ *    the caller's own stream, returns the bits (1 = a wait timed out) and clears
+ *    them.  Check it wherever the stream is synchronised anyway. */
 mm_status mm_f4_linear_static_ws(const void *x, const void *payload, const void *scale,
                                  float gs, void *y, uint32_t M, uint32_t K, uint32_t N,
                                  void *stream);
+mm_status mm_f4_device_status_on(void *stream, unsigned *flags_out);
 
 /* Host-buffer form: copies x (pinned or pageable host memory) to `x_dev`,
  * runs the op on resident device weights, copies y back to `y_host` and
@@ -311,11 +326,16 @@ mm_status mm_f4_decode_probe(uint32_t *out_bf16_dev, uint32_t *out_f32_dev,
  * *done_dev == 1; the device stays usable.  done_dev: one device uint32. */
 mm_status mm_f4_wait_selftest(unsigned *done_dev);
 
-/* Tuning knobs for experiments and tests; defaults are what the benchmark
- * uses.  key 1: launch kernels with programmatic stream serialization so
- * that an op's weight prefetch overlaps the tail of the previous kernel in the
- * stream (1 = on, default).  Returns the previous value, or -1 for an unknown
- * key. */
+/* Knobs for tests and sweeps; the defaults are what the benchmark uses.
+ * Returns the previous value, or -1 for an unknown key.
+ *   key 1  programmatic dependent launch: an op's weight prefetch overlaps the
+ *          tail of the kernel in front of it in the stream (1 = on, default)
+ *   key 2  weight rows per CTA of the decode kernels (0 = the planner's choice)
+ *   key 3  K slices of the decode kernels (0 = the planner's choice)
+ *   key 5  decode ops on the block-scaled tensor kernel (1, default) or on the
+ *          CUDA-core streaming kernel (0)
+ * Key 4 (measurement modes that skip loads, arithmetic or the split-K exchange)
+ * exists only in a library built with -DMMB_MEASURE_MODES. */
 int mm_f4_tune(int key, int value);
 
 /* ---- timing on the compute stream (events with timing enabled) ----------- */

@@ -6,11 +6,11 @@ tests and the benchmark.  PyTorch is used only to own device memory and for
 torch.distributed.
 """
 from ._lib import (lib, check, MimferError, MmOpDesc, MmKcall, F4Shape, F4Plan,
-                   OP_GEMM_F4, OP_QKV, OP_LMHEAD, OP_SILU_MUL, OP_ADD_RMSNORM, OP_NOP, V_ROWWARP, V_STREAM, V_UMMA, V_STREAMT, V_MX)
+                   OP_GEMM_F4, OP_QKV, OP_LMHEAD, OP_SILU_MUL, OP_ADD_RMSNORM, OP_NOP, V_ROWWARP, V_STREAM, V_UMMA, V_MX)
 from .linear import (NvFp4Weight, make_weight, pack_weight, make_activations, select_plan,
                      place_weights, Runtime, LinearEngine, weight_bytes)
 
 __all__ = ["lib", "check", "MimferError", "MmOpDesc", "MmKcall", "F4Shape", "F4Plan",
-           "OP_GEMM_F4", "OP_QKV", "OP_LMHEAD", "OP_SILU_MUL", "OP_ADD_RMSNORM", "OP_NOP", "V_ROWWARP", "V_STREAM", "V_UMMA", "V_STREAMT", "V_MX",
+           "OP_GEMM_F4", "OP_QKV", "OP_LMHEAD", "OP_SILU_MUL", "OP_ADD_RMSNORM", "OP_NOP", "V_ROWWARP", "V_STREAM", "V_UMMA", "V_MX",
            "NvFp4Weight", "make_weight", "pack_weight", "make_activations", "select_plan", "place_weights",
            "Runtime", "LinearEngine", "weight_bytes"]

@@ -19,7 +19,7 @@ STATUS_NAMES = ["MM_OK", "MM_ERR_NOMEM", "MM_ERR_IO", "MM_ERR_CORRUPT", "MM_ERR_
 
 OP_LMHEAD, OP_ADD_RMSNORM, OP_GEMM_F4, OP_GEMM_BF16, OP_QKV, OP_SILU_MUL, OP_NOP = 1, 3, 4, 5, 6, 12, 18
 MM_ST_COMPUTE, MM_ST_XFER = 0, 1
-V_ROWWARP, V_STREAM, V_UMMA, V_STREAMT, V_MX = 0, 1, 2, 3, 4
+V_ROWWARP, V_STREAM, V_UMMA, V_MX = 0, 1, 2, 4
 
 
 class MmOpDesc(C.Structure):
@@ -130,6 +130,7 @@ SIGNATURES = {
     "mm_f4_select_variant": (C.c_int, [C.POINTER(F4Shape), C.c_int, C.POINTER(F4Plan)]),
     "mm_f4_force_variant": (None, [C.c_int]),
     "mm_f4_linear": (C.c_int, [_vp, _vp, _vp, _f, _vp, _u32, _u32, _u32, _vp]),
+    "mm_f4_device_status_on": (C.c_int, [_vp, C.POINTER(C.c_uint)]),
     "mm_f4_xslice_bytes": (_sz, [_u32, _u32]),
     "mm_f4_xslice": (C.c_int, [_vp, _u32, _u32, _vp, _sz, _vp]),
     "mm_f4_linear_tp": (C.c_int, [_vp, _vp, _vp, _f, C.POINTER(_vp), _u32, _u32, _u32, _u32, _u32, _u32, _vp]),

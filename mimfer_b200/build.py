@@ -21,7 +21,7 @@ NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 
 C_SOURCES = ["core/core.c", "pack/pack.c", "plan/select.c", "engine/engine.c", "model/weights.c",
              "cuda/rt.c", "cuda/kx_gemm_f4.c"]
-CU_SOURCES = ["kernels/rowwarp.cu", "kernels/stream.cu", "kernels/streamt.cu", "kernels/mx.cu", "kernels/mxg.cu", "kernels/umma.cu",
+CU_SOURCES = ["kernels/rowwarp.cu", "kernels/stream.cu", "kernels/mx.cu", "kernels/mxg.cu", "kernels/umma.cu",
               "kernels/silu_mul.cu", "kernels/add_rmsnorm.cu", "kernels/tp_barrier.cu", "kernels/host_gather.cu"]
 HEADERS = ["core/core.h", "kernels/launch.h", "kernels/ptx.cuh", "kernels/fp4.cuh", "kernels/mx.cuh",
            "../../include/mimfer_abi.h", "../../include/mimfer_b200.h"]

@@ -18,7 +18,6 @@
 
 int mmb_stream_init(void);
 int mmb_umma_init(void);
-int mmb_streamt_init(void);
 int mmb_mx_init(void);
 int mmb_mxg_init(void);
 
@@ -52,7 +51,7 @@ static struct {
     unsigned long long launches;
     /* experiment knobs (mm_f4_tune keys 2..4), all 0 in production */
     uint32_t   st_rows, st_split, st_dbg;
-} G = { .forced_variant = -1, .pdl = 1, .next_pdl = -1, .use_mx = 0 };
+} G = { .forced_variant = -1, .pdl = 1, .next_pdl = -1, .use_mx = 1 };
 
 /* The workspace is cut into WS_REGIONS equal regions, each with its own arrival
  * counters, when every region still holds WS_REGION_MIN bytes; an op uses one
@@ -194,7 +193,9 @@ int mm_f4_tune(int key, int value)
     }
     if (key == 2) { int old = (int)G.st_rows; G.st_rows = (uint32_t)value; return old; }
     if (key == 3) { int old = (int)G.st_split; G.st_split = (uint32_t)value; return old; }
+#ifdef MMB_MEASURE_MODES
     if (key == 4) { int old = (int)G.st_dbg; G.st_dbg = (uint32_t)value; return old; }
+#endif
     if (key == 5) { int old = G.use_mx; G.use_mx = value ? 1 : 0; return old; }
     return -1;
 }
@@ -260,7 +261,6 @@ static mm_status ensure_ready(void)
     G.encode = (encode_fn)fn;
     CK((cudaError_t)mmb_stream_init());
     CK((cudaError_t)mmb_umma_init());
-    CK((cudaError_t)mmb_streamt_init());
     CK((cudaError_t)mmb_mx_init());
     CK((cudaError_t)mmb_mxg_init());
     CK((cudaError_t)mmb_status_word(&G.status_dev));
@@ -359,11 +359,8 @@ static mm_status plan_linear(const void *x, const void *payload, const void *sca
         sh.ptr_align = 8;                  /* aligned operands, unaligned output slice: the row-warp kernel */
     mm_status st = G.forced_variant >= 0 ? mm_f4_select_variant(&sh, G.forced_variant, plan)
                                          : mm_f4_select(&sh, plan);
-    if (st == MM_OK && plan->variant == MM_F4_V_STREAM && G.forced_variant < 0 && G.use_mx) {
-        mm_f4_plan mx;                     /* the block-scaled tensor path when its scratch fits the workspace */
-        if (mm_f4_select_variant(&sh, MM_F4_V_MX, &mx) == MM_OK)
-            *plan = mx;
-    }
+    if (st == MM_OK && plan->variant == MM_F4_V_MX && G.forced_variant < 0 && !G.use_mx)
+        st = mm_f4_select_variant(&sh, MM_F4_V_STREAM, plan);     /* tuning key 5 = 0: the CUDA-core kernel */
     if (st == MM_OK && plan->variant == MM_F4_V_STREAM && (G.st_rows || G.st_split))
         return mmb_plan_stream_with(&sh, G.st_rows, G.st_split, plan);
     if (st == MM_OK && plan->variant == MM_F4_V_MX && (G.st_rows || G.st_split))
@@ -474,15 +471,6 @@ static mm_status linear_impl(const void *x, const void *payload, const void *sca
                            a.plan.tile_n, CU_TENSOR_MAP_SWIZZLE_NONE));
         MM_CHECK(launch_mx_pair(&a, share_x, stream));
         return MM_OK;
-    case MM_F4_V_STREAMT:
-        MM_CHECK(encode_2d(a.tm_payload, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, payload, K / 2, N, 128,
-                           MMB_ST_ROWS, CU_TENSOR_MAP_SWIZZLE_128B));
-        MM_CHECK(encode_2d(a.tm_scale, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, scale, K / 16, N, 16,
-                           MMB_ST_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE));
-        MM_CHECK(encode_2d(a.tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, 64,
-                           a.plan.tile_m, CU_TENSOR_MAP_SWIZZLE_128B));
-        err = mmb_launch_streamt(&a, stream);
-        break;
     case MM_F4_V_UMMA:
         MM_CHECK(encode_2d(a.tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, MMB_UM_KBLOCK,
                            a.plan.tile_m, CU_TENSOR_MAP_SWIZZLE_128B));
@@ -664,136 +652,227 @@ static mm_status finish_op(void);
  * adds ops while they fit, and launches it.  Scratch: arrival counters and
  * split-K partials of every op from one workspace region, digit planes from the
  * plane cache (an activation tensor several ops read is sliced once). */
+typedef struct gr_item {
+    mm_op_desc  op;
+    int         glu, gate_first;
+    const void *pay0, *sc0;          /* the lower-addressed projection of a gated pair, else b and d */
+    const void *up_scale;
+    uint64_t    dpay, dsc;
+    uint32_t    align;
+    uint32_t    split;               /* K slices chosen at launch */
+} gr_item;
+
 static struct {
     int       active;
-    mmb_group g;
-    size_t    part_used, cache_used;
-    uint32_t  counters_used;
+    int       pdl;
+    uint32_t  n;
+    gr_item   item[MMB_MXG_MAX_OPS];
+    size_t    part_bound, cache_used;    /* upper bounds kept while ops are added */
+    uint32_t  counters_bound;
     unsigned char *region;
+    mmb_group g;                         /* filled at launch */
 } GR;
 
 mm_status mmb_group_begin(int pdl_mode, int ws_region)
 {
     MM_CHECK(ensure_ready());
     MM_REQUIRE(G.ws && mmb_ws_regions() > 1, MM_ERR_STATE);
-    memset(&GR.g, 0, sizeof GR.g);
     GR.active = 1;
-    GR.g.pdl = G.pdl ? (pdl_mode >= 0 ? pdl_mode : MMB_PDL_TRIGGER_FIRST) : MMB_PDL_OFF;
-    GR.g.acc_bufs = 2;
+    GR.n = 0;
+    GR.pdl = G.pdl ? (pdl_mode >= 0 ? pdl_mode : MMB_PDL_TRIGGER_FIRST) : MMB_PDL_OFF;
     const int r = ws_region >= 0 && ws_region < mmb_ws_regions() ? ws_region : 0;
     GR.region = (unsigned char *)G.ws + (size_t)r * ws_region_bytes();
-    GR.part_used = MMB_WS_COUNTER_B;
-    GR.counters_used = 0;
+    GR.part_bound = MMB_WS_COUNTER_B;
+    GR.counters_bound = 0;
     GR.cache_used = 0;
     return MM_OK;
 }
 
-uint32_t mmb_group_size(void) { return GR.active ? GR.g.n_ops : 0; }
+uint32_t mmb_group_size(void) { return GR.active ? GR.n : 0; }
+
+static size_t gr_partial_bytes(const mm_f4_plan *p, uint32_t K)
+{
+    if (p->split_k <= 1)
+        return 0;
+    return (p->ws_needed - MMB_WS_COUNTER_B - MMB_MX_XS_B(p->tile_m, K) + 255u) & ~(size_t)255;
+}
+
+static mm_status gr_plan(const gr_item *it, uint32_t split, mm_f4_plan *plan)
+{
+    mm_f4_shape sh = { it->op.n0, it->op.n1, it->op.n2, (uint32_t)G.sm_count, it->align, ws_region_bytes() };
+    return mmb_plan_mx_group(&sh, it->glu, split, plan);
+}
 
 /* MM_ERR_CAPACITY: the group is full (launch it and open another);
  * MM_ERR_UNSUPPORTED: this op does not run on the block-scaled kernel. */
 mm_status mmb_group_add(const mm_op_desc *op, int glu, const void *up_payload, const void *up_scale)
 {
     MM_REQUIRE(GR.active && op, MM_ERR_STATE);
-    if (GR.g.n_ops == MMB_MXG_MAX_OPS)
+    if (GR.n == MMB_MXG_MAX_OPS)
         return MM_ERR_CAPACITY;
-    const uint32_t M = op->n0, K = op->n1, N = op->n2;
-    const void *pay0 = op->b, *sc0 = op->d;
-    int gate_first = 1;
-    uint64_t dpay = 0, dsc = 0;
-    mm_f4_plan plan;
-    mm_f4_shape sh = { M, K, N, (uint32_t)G.sm_count, min_align(op->a, op->b, op->d, op->c), ws_region_bytes() };
-    if (sh.ptr_align < 16 || M == 0 || K == 0 || N == 0 || K % 16 != 0)
+    gr_item it;
+    memset(&it, 0, sizeof it);
+    it.op = *op;
+    it.glu = glu;
+    it.pay0 = op->b; it.sc0 = op->d; it.gate_first = 1;
+    it.up_scale = up_scale;
+    it.align = min_align(op->a, op->b, op->d, op->c);
+    if (it.align < 16 || op->n0 == 0 || op->n1 == 0 || op->n2 == 0 || op->n1 % 16 != 0)
         return MM_ERR_SHAPE;
     if (glu) {
-        if (!pair_layout(op->b, op->d, up_payload, up_scale, &gate_first, &dpay, &dsc))
+        if (!pair_layout(op->b, op->d, up_payload, up_scale, &it.gate_first, &it.dpay, &it.dsc))
             return MM_ERR_UNSUPPORTED;
-        pay0 = gate_first ? op->b : up_payload;
-        sc0 = gate_first ? op->d : up_scale;
-        sh.ptr_align = min_align(op->a, pay0, sc0, op->c);
-        if (mmb_select_glu(&sh, 1, &plan) != MM_OK || plan.variant != MM_F4_V_MX)
-            return MM_ERR_UNSUPPORTED;
-    } else if (mm_f4_select_variant(&sh, MM_F4_V_MX, &plan) != MM_OK) {
-        return MM_ERR_UNSUPPORTED;
+        it.pay0 = it.gate_first ? op->b : up_payload;
+        it.sc0 = it.gate_first ? op->d : up_scale;
+        it.align = min_align(op->a, it.pay0, it.sc0, op->c);
     }
-    const uint32_t nb = plan.tile_m;
-    const size_t xs = MMB_MX_XS_B(nb, K);
-    const size_t pb = plan.split_k > 1 ? (plan.ws_needed - MMB_WS_COUNTER_B - xs + 255u) & ~(size_t)255 : 0;
-    if (GR.part_used + pb > ws_region_bytes() ||
-        (plan.split_k > 1 && GR.counters_used + plan.grid_x > MMB_WS_MAX_TILES))
+    mm_f4_plan plan;
+    if (gr_plan(&it, 0, &plan) != MM_OK || plan.variant != MM_F4_V_MX)
+        return MM_ERR_UNSUPPORTED;
+    const size_t pb = gr_partial_bytes(&plan, op->n1);
+    if (GR.part_bound + pb > ws_region_bytes() || GR.counters_bound + plan.grid_x > MMB_WS_MAX_TILES)
         return MM_ERR_CAPACITY;
-    /* digit planes: shared with an op of the group that reads the same activations */
-    mmb_gop *g = &GR.g.op[GR.g.n_ops];
-    memset(g, 0, sizeof *g);
-    for (uint32_t i = 0; i < GR.g.n_ops; i++)
-        if (GR.g.op[i].x == op->a && GR.g.op[i].M == M && GR.g.op[i].K == K)
-            g->x_ws = GR.g.op[i].x_ws;
-    if (!g->x_ws) {
+    int shared = 0;
+    for (uint32_t i = 0; i < GR.n; i++)
+        if (GR.item[i].op.a == op->a && GR.item[i].op.n0 == op->n0 && GR.item[i].op.n1 == op->n1)
+            shared = 1;
+    if (!shared) {
         size_t cap = 0;
-        unsigned char *cache = (unsigned char *)mmb_plane_cache(&cap);
-        const size_t need = (xs + 1023u) & ~(size_t)1023u;
-        if (!cache || GR.cache_used + need > cap)
+        const size_t need = (MMB_MX_XS_B(plan.tile_m, op->n1) + 1023u) & ~(size_t)1023u;
+        if (!mmb_plane_cache(&cap) || GR.cache_used + need > cap)
             return MM_ERR_CAPACITY;
-        g->x_ws = cache + GR.cache_used;
-        g->slice_here = 1;
         GR.cache_used += need;
     }
-    const uint32_t stage = MMB_MX_STAGE_B(plan.tile_n, nb, glu);
-    g->x = op->a; g->y = op->c;
-    g->gs = mm_f4_gscale_get(op->d);
-    g->gs_up = glu ? mm_f4_gscale_get(up_scale) : 0.0f;
-    g->glu = glu; g->gate_plane = glu ? (gate_first ? 0 : 1) : 0;
-    g->M = M; g->K = K; g->N = N;
-    g->rows = plan.tile_n; g->nb = nb; g->k_steps = plan.k_steps; g->split_k = plan.split_k;
-    g->tiles = plan.grid_x; g->unit0 = GR.g.n_units;
-    if (plan.split_k > 1) {
-        g->counters = GR.region + (size_t)GR.counters_used * 4u;
-        g->partial = GR.region + GR.part_used;
-        GR.counters_used += plan.grid_x;
-        GR.part_used += pb;
-    }
-    if (glu) {
-        MM_CHECK(encode_pair(g->tm_payload, pay0, K / 2, N, dpay, 128, plan.tile_n / 2, CU_TENSOR_MAP_SWIZZLE_128B));
-        MM_CHECK(encode_pair(g->tm_scale, sc0, K / 16, N, dsc, 16, plan.tile_n / 2, CU_TENSOR_MAP_SWIZZLE_NONE));
-    } else {
-        MM_CHECK(encode_2d(g->tm_payload, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pay0, K / 2, N, 128, plan.tile_n,
-                           CU_TENSOR_MAP_SWIZZLE_128B));
-        MM_CHECK(encode_2d(g->tm_scale, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, sc0, K / 16, N, 16, plan.tile_n,
-                           CU_TENSOR_MAP_SWIZZLE_NONE));
-    }
-    unsigned char *planes = (unsigned char *)g->x_ws + MMB_MX_PLANES_OFF;
-    MM_CHECK(encode_2d(g->tm_planes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, planes, K / 2, nb, 128, nb,
-                       CU_TENSOR_MAP_SWIZZLE_128B));
-    MM_CHECK(encode_2d(g->tm_sfb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, planes + MMB_MX_PLANES_B(nb, K), K / 16, nb, 16,
-                       nb, CU_TENSOR_MAP_SWIZZLE_NONE));
-    if (stage > GR.g.stage_b) GR.g.stage_b = stage;
-    if (nb > 96u) GR.g.acc_bufs = 1;
-    GR.g.n_units += plan.grid_x * plan.split_k;
-    GR.g.n_ops++;
+    GR.part_bound += pb;
+    GR.counters_bound += plan.grid_x;
+    GR.item[GR.n++] = it;
     return MM_OK;
+}
+
+/* Bytes of weights the busiest CTA streams when the units go round-robin over
+ * `ctas` CTAs (the kernel's assignment), given every op's plan. */
+static double gr_makespan(const mm_f4_plan *plans, uint32_t n, uint32_t ctas)
+{
+    static double load[1024];
+    if (ctas > 1024u) ctas = 1024u;
+    for (uint32_t c = 0; c < ctas; c++) load[c] = 0.0;
+    uint32_t g = 0;
+    for (uint32_t i = 0; i < n; i++) {
+        const double unit = (double)plans[i].tile_n * 144.0 * (double)plans[i].k_steps / (double)plans[i].split_k;
+        const uint32_t units = plans[i].grid_x * plans[i].split_k;
+        for (uint32_t u = 0; u < units; u++, g++)
+            load[g % ctas] += unit + 40000.0;      /* a unit costs about a microsecond beside its bytes */
+    }
+    double worst = 0.0;
+    for (uint32_t c = 0; c < ctas; c++)
+        if (load[c] > worst) worst = load[c];
+    return worst;
 }
 
 mm_status mmb_group_launch(void)
 {
     MM_REQUIRE(GR.active, MM_ERR_STATE);
     GR.active = 0;
-    if (GR.g.n_ops == 0)
+    if (GR.n == 0)
         return MM_OK;
-    uint32_t st = (MMB_SMEM_MAX - MMB_MXG_FIXED_B) / GR.g.stage_b;
+    /* plans: units of up to about 768 KiB; then, from the last op backwards, a
+     * finer K split is kept wherever it shortens the busiest CTA's share */
+    static mm_f4_plan plans[MMB_MXG_MAX_OPS];
+    for (uint32_t i = 0; i < GR.n; i++)
+        MM_CHECK(gr_plan(&GR.item[i], 0, &plans[i]));
+    double best = gr_makespan(plans, GR.n, (uint32_t)G.sm_count);
+    for (uint32_t k = GR.n; k-- > 0;)
+        for (uint32_t extra = 1; extra <= 2u; extra++) {
+            mm_f4_plan trial;
+            if (gr_plan(&GR.item[k], plans[k].split_k + extra, &trial) != MM_OK ||
+                trial.split_k <= plans[k].split_k)
+                continue;
+            const mm_f4_plan keep = plans[k];
+            const size_t grow = gr_partial_bytes(&trial, GR.item[k].op.n1) - gr_partial_bytes(&keep, GR.item[k].op.n1);
+            if (GR.part_bound + grow > ws_region_bytes() || trial.grid_x != keep.grid_x)
+                continue;                        /* every op's tile counters are already reserved */
+            plans[k] = trial;
+            const double t = gr_makespan(plans, GR.n, (uint32_t)G.sm_count);
+            if (t < best * 0.985) {
+                best = t;
+                GR.part_bound += grow;
+            } else {
+                plans[k] = keep;
+            }
+        }
+
+    mmb_group *gg = &GR.g;
+    memset(gg, 0, sizeof *gg);
+    gg->pdl = GR.pdl;
+    gg->acc_bufs = 2;
+    size_t part_used = MMB_WS_COUNTER_B, cache_used = 0, cap = 0;
+    uint32_t counters_used = 0, sliced = 0;
+    unsigned char *cache = (unsigned char *)mmb_plane_cache(&cap);
+    for (uint32_t i = 0; i < GR.n; i++) {
+        const gr_item *it = &GR.item[i];
+        const mm_f4_plan *plan = &plans[i];
+        const uint32_t M = it->op.n0, K = it->op.n1, N = it->op.n2, nb = plan->tile_m;
+        mmb_gop *g = &gg->op[i];
+        for (uint32_t j = 0; j < i; j++)
+            if (gg->op[j].x == it->op.a && gg->op[j].M == M && gg->op[j].K == K)
+                g->x_ws = gg->op[j].x_ws;
+        if (!g->x_ws) {
+            g->x_ws = cache + cache_used;
+            g->slice_here = 1;
+            cache_used += (MMB_MX_XS_B(nb, K) + 1023u) & ~(size_t)1023u;
+            sliced++;
+        }
+        g->x = it->op.a; g->y = it->op.c;
+        g->gs = mm_f4_gscale_get(it->op.d);
+        g->gs_up = it->glu ? mm_f4_gscale_get(it->up_scale) : 0.0f;
+        g->glu = it->glu; g->gate_plane = it->glu ? (it->gate_first ? 0 : 1) : 0;
+        g->M = M; g->K = K; g->N = N;
+        g->rows = plan->tile_n; g->nb = nb; g->k_steps = plan->k_steps; g->split_k = plan->split_k;
+        g->tiles = plan->grid_x; g->unit0 = gg->n_units;
+        if (plan->split_k > 1) {
+            const size_t pb = gr_partial_bytes(plan, K);
+            MM_REQUIRE(part_used + pb <= ws_region_bytes() && counters_used + plan->grid_x <= MMB_WS_MAX_TILES &&
+                       cache_used <= cap, MM_ERR_CAPACITY);
+            g->counters = GR.region + (size_t)counters_used * 4u;
+            g->partial = GR.region + part_used;
+            counters_used += plan->grid_x;
+            part_used += pb;
+        }
+        if (it->glu) {
+            MM_CHECK(encode_pair(g->tm_payload, it->pay0, K / 2, N, it->dpay, 128, plan->tile_n / 2,
+                                 CU_TENSOR_MAP_SWIZZLE_128B));
+            MM_CHECK(encode_pair(g->tm_scale, it->sc0, K / 16, N, it->dsc, 16, plan->tile_n / 2,
+                                 CU_TENSOR_MAP_SWIZZLE_NONE));
+        } else {
+            MM_CHECK(encode_2d(g->tm_payload, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, it->pay0, K / 2, N, 128,
+                               plan->tile_n, CU_TENSOR_MAP_SWIZZLE_128B));
+            MM_CHECK(encode_2d(g->tm_scale, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, it->sc0, K / 16, N, 16,
+                               plan->tile_n, CU_TENSOR_MAP_SWIZZLE_NONE));
+        }
+        unsigned char *planes = (unsigned char *)g->x_ws + MMB_MX_PLANES_OFF;
+        MM_CHECK(encode_2d(g->tm_planes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, planes, K / 2, nb, 128, nb,
+                           CU_TENSOR_MAP_SWIZZLE_128B));
+        MM_CHECK(encode_2d(g->tm_sfb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, planes + MMB_MX_PLANES_B(nb, K), K / 16,
+                           nb, 16, nb, CU_TENSOR_MAP_SWIZZLE_NONE));
+        const uint32_t stage = MMB_MX_STAGE_B(plan->tile_n, nb, it->glu);
+        if (stage > gg->stage_b) gg->stage_b = stage;
+        if (nb > 96u) gg->acc_bufs = 1;
+        gg->n_units += plan->grid_x * plan->split_k;
+    }
+    gg->n_ops = GR.n;
+    uint32_t st = (MMB_SMEM_MAX - MMB_MXG_FIXED_B) / gg->stage_b;
     if (st > 6) st = 6;
     if (st < 2) st = 2;
-    GR.g.stages = st;
-    GR.g.smem_bytes = st * GR.g.stage_b + MMB_MXG_FIXED_B;
-    GR.g.grid = GR.g.n_units < (uint32_t)G.sm_count ? GR.g.n_units : (uint32_t)G.sm_count;
-    uint32_t sliced = 0;
-    for (uint32_t i = 0; i < GR.g.n_ops; i++) sliced += GR.g.op[i].slice_here ? 1u : 0u;
-    int err = mmb_launch_mxg(&GR.g, mm_cuda_stream_raw(MM_ST_COMPUTE));
+    gg->stages = st;
+    gg->smem_bytes = st * gg->stage_b + MMB_MXG_FIXED_B;
+    gg->grid = gg->n_units < (uint32_t)G.sm_count ? gg->n_units : (uint32_t)G.sm_count;
+    int err = mmb_launch_mxg(gg, mm_cuda_stream_raw(MM_ST_COMPUTE));
     if (err) {
-        MM_LOGE("cuda: group launch (%u ops, %u units): %s", GR.g.n_ops, GR.g.n_units,
+        MM_LOGE("cuda: group launch (%u ops, %u units): %s", gg->n_ops, gg->n_units,
                 cudaGetErrorString((cudaError_t)err));
         return MM_ERR_CUDA;
     }
-    G.launches += 1u + (sliced ? 1u : 0u);
+    G.launches += 1u + (sliced ? 2u : 0u);
     G.sliced_x = NULL;
     return finish_op();
 }

@@ -69,6 +69,7 @@ mm_status mm_lin_engine_create(mm_lin_engine **out, uint32_t max_ops)
     e->max_ops = max_ops;
     e->upload_group = 1;
     e->upload_kernel = 1;
+    e->group = 1;
     *out = e;
     return MM_OK;
 }

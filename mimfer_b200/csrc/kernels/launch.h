@@ -27,13 +27,8 @@ extern "C" {
 #define MMB_ST_X_RAW_B(mt) ((mt) * 8u * MMB_ST_KSTEP * 2u)     /* bytes TMA delivers         */
 #define MMB_ST_X_B(mt)     ((mt) * 5120u)                       /* slot: 8 rows x 576 B, padded */
 #define MMB_ST_STAGE_B(mt) (MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B + MMB_ST_X_B(mt))
-#define MMB_ST_FIXED_B     (2048u /* two scale LUTs */ + 512u /* barriers, flags */ + 1024u /* align slack */)
+#define MMB_ST_FIXED_B     (2048u /* scale LUT */ + 512u /* barriers, flags */ + 1024u /* align slack */)
 
-/* ---- STREAM-T (decode on tcgen05, weights through tensor memory) ------------- */
-#define MMB_STT_DEQ_WARPS   16u    /* thread <-> weight row, 2 tiles x 4 quadrants x 2 K quarters */
-#define MMB_STT_XFORM_WARPS 4u
-#define MMB_STT_THREADS     ((MMB_STT_DEQ_WARPS + 3u + MMB_STT_XFORM_WARPS) * 32u)   /* + TMA, 2 x MMA */
-#define MMB_STT_STAGE_B(npad) (MMB_ST_PAYLOAD_B + MMB_ST_SCALE_B + (npad) * 512u)
 
 /* ---- MX (decode on the block-scaled tensor path) ---------------------------- */
 #define MMB_MX_PLANES       6      /* signed e2m1 digits per activation                      */
@@ -51,9 +46,12 @@ extern "C" {
 #define MMB_MX_STAGE_B(rows, nb, glu) ((MMB_MX_PAY_B(rows, glu) + (nb) * 144u + MMB_MX_SC_B(rows) + 1023u) & ~1023u)
 #define MMB_MX_FIXED_B      (512u /* barriers, flags */ + 1024u /* align slack */)
 /* activation scratch of one op, inside its workspace region after the arrival
- * counters: row factors (32 rows x 2 floats), digit planes [nb][K/2], plane scales [nb][K/16] */
+ * counters: row factors (32 rows x 2 floats), chunk maxima, digit planes [nb][K/2],
+ * plane scales [nb][K/16] */
 #define MMB_MX_ROWSCALE_OFF 0u
-#define MMB_MX_PLANES_OFF   1024u
+#define MMB_MX_CHUNKMAX_OFF 1024u  /* [32 rows][64] largest magnitude of every 1024-value chunk (group slicing) */
+#define MMB_MX_MAX_CHUNKS   64u
+#define MMB_MX_PLANES_OFF   16384u
 #define MMB_MX_PLANES_B(nb, K) ((((size_t)(nb) * ((K) / 2u)) + 1023u) & ~(size_t)1023u)
 #define MMB_MX_XS_B(nb, K)  (MMB_MX_PLANES_OFF + MMB_MX_PLANES_B(nb, K) + ((((size_t)(nb) * ((K) / 16u)) + 1023u) & ~(size_t)1023u))
 
@@ -111,13 +109,20 @@ extern "C" {
 #define MMB_PDL_WAIT_FIRST    2
 #define MMB_PDL_INDEPENDENT   3
 
-/* Measurement modes of the decode kernel (mmb_args.dbg, mm_f4_tune key 4;
- * results are not meaningful with any of them set).  They split a launch time
- * into its parts: the weight stream alone, the arithmetic alone, the split-K
- * exchange. */
+/* Measurement modes of the streaming decode kernel (mmb_args.dbg, mm_f4_tune
+ * key 4).  They split a launch time into its parts: the weight stream alone,
+ * the arithmetic alone, the split-K exchange; results are not meaningful with
+ * any of them set.  Only a build with -DMMB_MEASURE_MODES has them: in the
+ * shipped library the bits read as zero and key 4 is an unknown key. */
+#ifdef MMB_MEASURE_MODES
 #define MMB_DBG_NO_MATH      1u   /* consumers release every stage untouched        */
 #define MMB_DBG_NO_LOADS     2u   /* no TMA traffic and no waits: arithmetic on whatever shared memory holds */
 #define MMB_DBG_NO_EXCHANGE  4u   /* split-K slices store their own sums, no partials, no ticket */
+#else
+#define MMB_DBG_NO_MATH      0u
+#define MMB_DBG_NO_LOADS     0u
+#define MMB_DBG_NO_EXCHANGE  0u
+#endif
 
 /* Device status word bits. */
 #define MMB_DEV_TIMEOUT    1u
@@ -190,7 +195,6 @@ int mmb_launch_mxg(const mmb_group *g, void *stream);
 int mmb_launch_rowwarp(const mmb_args *a, void *stream);
 int mmb_launch_stream(const mmb_args *a, void *stream);
 int mmb_launch_umma(const mmb_args *a, void *stream);
-int mmb_launch_streamt(const mmb_args *a, void *stream);
 int mmb_launch_xslice(const mmb_args *a, void *stream);     /* activations -> digit planes (a->mx_x_ws) */
 int mmb_launch_mx(const mmb_args *a, void *stream);
 /* Buffers one launch of the upload kernel takes (host_gather.cu). */
@@ -208,6 +212,7 @@ int mmb_launch_decode_probe(uint32_t *out_mma, uint32_t *out_f32, uint32_t *out_
 mm_status mmb_plan_stream_with(const mm_f4_shape *s, uint32_t rows, uint32_t split, mm_f4_plan *p);
 /* mm_f4_select_glu with the block-scaled decode path allowed or not. */
 mm_status mmb_select_glu(const mm_f4_shape *s, int allow_mx, mm_f4_plan *p);
+mm_status mmb_plan_mx_group(const mm_f4_shape *s, int glu, uint32_t split_k, mm_f4_plan *p);
 mm_status mmb_plan_mx_with(const mm_f4_shape *s, uint32_t rows, uint32_t split, mm_f4_plan *p);
 /* One-time per-process setup (smem opt-in attributes). */
 int mmb_kernels_init(void);

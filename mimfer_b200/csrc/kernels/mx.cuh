@@ -103,8 +103,33 @@ __host__ __device__ constexpr int mx_shift(int plane)
 
 /* Thread = four consecutive activations (a quarter of a 16-wide block); one CTA of
  * 256 threads covers 1024 values of activation row m, starting at 1024 * cta_x. */
+/* Largest magnitude (bf16 bits without the sign) of the 1024 values of row m that
+ * start at 1024 * cta_x: the first pass of the two-pass slicing of a group. */
+__device__ __forceinline__ void xamax_cta(const uint16_t *x, uint32_t *chunk_max, uint32_t M, uint32_t K,
+                                          uint32_t m, uint32_t cta_x)
+{
+    __shared__ uint32_t s_cm[8];
+    const uint32_t tid = threadIdx.x, quarter = cta_x * 256u + tid;
+    uint32_t a = 0;
+    if (quarter < K / 4u && m < M) {
+        const uint2 v = __ldcg(reinterpret_cast<const uint2 *>(x + static_cast<size_t>(m) * K) + quarter);
+        a = max(max(v.x & 0x7fffu, (v.x >> 16) & 0x7fffu), max(v.y & 0x7fffu, (v.y >> 16) & 0x7fffu));
+    }
+    a = __reduce_max_sync(0xffffffffu, a);
+    if ((tid & 31u) == 0)
+        s_cm[tid >> 5] = a;
+    __syncthreads();
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 1; i < 8; i++) a = max(a, s_cm[i]);
+        chunk_max[m * MMB_MX_MAX_CHUNKS + cta_x] = a;
+    }
+}
+
+/* chunk_max: the row's chunk maxima from xamax_cta (NULL: this CTA scans the row itself). */
 __device__ __forceinline__ void xslice_cta(const uint16_t *x, uint8_t *planes, uint8_t *sfb, float *row_scale,
-                                           uint32_t M, uint32_t K, uint32_t m, uint32_t cta_x)
+                                           uint32_t M, uint32_t K, uint32_t m, uint32_t cta_x,
+                                           const uint32_t *chunk_max = nullptr)
 {
     __shared__ uint32_t s_max[8];
     const uint32_t tid = threadIdx.x;
@@ -121,7 +146,10 @@ __device__ __forceinline__ void xslice_cta(const uint16_t *x, uint8_t *planes, u
     /* largest magnitude of the row: every CTA of the row scans all of it, eight
      * 16-byte loads in flight per thread */
     uint32_t amax = 0;
-    if (m < M) {
+    if (chunk_max) {
+        if (m < M && tid < (K + 1023u) / 1024u)
+            amax = __ldcg(chunk_max + m * MMB_MX_MAX_CHUNKS + tid);
+    } else if (m < M) {
         const uint4 *row = reinterpret_cast<const uint4 *>(x + static_cast<size_t>(m) * K);
         const uint32_t n8 = K / 8u;
         for (uint32_t base8 = 0; base8 < n8; base8 += 2048u) {

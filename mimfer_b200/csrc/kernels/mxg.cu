@@ -485,6 +485,21 @@ struct XsliceGroup {
     XsliceItem item[MMB_MXG_MAX_OPS];
 };
 
+/* Two passes, so that a row is read twice and not once per chunk: chunk maxima,
+ * then the slicing with the row maximum taken from them. */
+__global__ void __launch_bounds__(256)
+f4_xamax_group_kernel(const __grid_constant__ XsliceGroup g)
+{
+    grid_dep_launch();
+    if (g.pdl != MMB_PDL_OFF)
+        grid_dep_wait();                     /* the activations are the previous kernel's output */
+    const XsliceItem &it = g.item[blockIdx.z];
+    if (blockIdx.y >= it.m_pad || blockIdx.x * 1024u >= it.K)
+        return;
+    xamax_cta(it.x, reinterpret_cast<uint32_t *>(it.scratch + MMB_MX_CHUNKMAX_OFF), it.M, it.K, blockIdx.y,
+              blockIdx.x);
+}
+
 __global__ void __launch_bounds__(256)
 f4_xslice_group_kernel(const __grid_constant__ XsliceGroup g)
 {
@@ -495,8 +510,10 @@ f4_xslice_group_kernel(const __grid_constant__ XsliceGroup g)
     if (blockIdx.y >= it.m_pad || blockIdx.x * 1024u >= it.K)
         return;
     uint8_t *planes = it.scratch + MMB_MX_PLANES_OFF;
+    const bool two_pass = (it.K + 1023u) / 1024u <= MMB_MX_MAX_CHUNKS;
     xslice_cta(it.x, planes, planes + MMB_MX_PLANES_B(it.nb, it.K),
-               reinterpret_cast<float *>(it.scratch + MMB_MX_ROWSCALE_OFF), it.M, it.K, blockIdx.y, blockIdx.x);
+               reinterpret_cast<float *>(it.scratch + MMB_MX_ROWSCALE_OFF), it.M, it.K, blockIdx.y, blockIdx.x,
+               two_pass ? reinterpret_cast<const uint32_t *>(it.scratch + MMB_MX_CHUNKMAX_OFF) : nullptr);
 }
 } // namespace mmb
 
@@ -557,7 +574,9 @@ extern "C" int mmb_launch_mxg(const mmb_group *hg, void *stream)
         cfg.stream = st;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        cudaError_t err = cudaLaunchKernelEx(&cfg, mmb::f4_xslice_group_kernel, xs);
+        cudaError_t err = cudaLaunchKernelEx(&cfg, mmb::f4_xamax_group_kernel, xs);
+        if (err == cudaSuccess)
+            err = cudaLaunchKernelEx(&cfg, mmb::f4_xslice_group_kernel, xs);
         if (err != cudaSuccess)
             return static_cast<int>(err);
     }

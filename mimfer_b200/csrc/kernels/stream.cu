@@ -789,3 +789,25 @@ extern "C" mm_status mm_f4_linear_static_ws(const void *x, const void *payload, 
     }
     return MM_OK;
 }
+
+/* Status word of the device, read on the caller's stream: for users of
+ * mm_f4_linear_static_ws that run without the runtime shim.  Synchronises
+ * `stream`, returns the MMB_DEV_* bits in *flags_out and clears them. */
+extern "C" mm_status mm_f4_device_status_on(void *stream, unsigned *flags_out)
+{
+    if (!flags_out)
+        return MM_ERR_STATE;
+    unsigned *word = nullptr;
+    if (mmb_status_word(&word) != 0 || !word)
+        return MM_ERR_CUDA;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    unsigned v = 0;
+    /* pageable destination: the copy has landed when the call returns */
+    if (cudaMemcpyAsync(&v, word, sizeof v, cudaMemcpyDeviceToHost, cs) != cudaSuccess ||
+        cudaStreamSynchronize(cs) != cudaSuccess)
+        return MM_ERR_CUDA;
+    if (v && (cudaMemsetAsync(word, 0, sizeof v, cs) != cudaSuccess || cudaStreamSynchronize(cs) != cudaSuccess))
+        return MM_ERR_CUDA;
+    *flags_out = v;
+    return MM_OK;
+}

@@ -180,6 +180,35 @@ static mm_status plan_mx(const mm_f4_shape *s, mm_f4_plan *p)
     return plan_mx_with(s, 0, 0, 0, p);
 }
 
+/* MX plan of an op inside a group launch.  The CTAs take the work units of all
+ * the group's ops in turn, so an op need not fill the SMs by itself: what counts
+ * is that a unit is large enough to amortise its hand-over (accumulator switch,
+ * epilogue, split-K exchange) and small enough for the tail of the group to stay
+ * balanced.  Tiles of the full height, evened out over the rows; K is cut only
+ * where a unit would exceed about 768 KiB of weights (split_k = 0), or as the
+ * caller says. */
+mm_status mmb_plan_mx_group(const mm_f4_shape *s, int glu, uint32_t split_k, mm_f4_plan *p)
+{
+    mm_status st = check_shape(s, p);
+    if (st != MM_OK)
+        return st;
+    const uint32_t unit = glu ? 128u : 256u, gran = glu ? 8u : 4u;
+    uint32_t tiles = ceil_div(s->N, unit);
+    uint32_t per = ceil_div(ceil_div(s->N, tiles), gran) * gran;
+    if (per > unit) per = unit;
+    const uint32_t rows = glu ? 2u * per : per;
+    const uint32_t k_steps = s->K / MMB_ST_KSTEP;
+    uint32_t max_steps = (768u << 10) / (rows * 144u);
+    if (max_steps < 4u) max_steps = 4u;
+    uint32_t split = k_steps ? ceil_div(k_steps, max_steps) : 1u;
+    if (split_k)                                    /* the caller's own K split */
+        split = split_k;
+    if (split > 32u) split = 32u;
+    if (split < 1u) split = 1u;
+    st = plan_mx_with(s, rows, split, glu, p);
+    return st;
+}
+
 mm_status mmb_plan_mx_with(const mm_f4_shape *s, uint32_t rows, uint32_t split, mm_f4_plan *p)
 {
     mm_status st = check_shape(s, p);
@@ -190,37 +219,6 @@ mm_status mmb_plan_stream_with(const mm_f4_shape *s, uint32_t rows, uint32_t spl
 {
     mm_status st = check_shape(s, p);
     return st != MM_OK ? st : plan_stream_with(s, rows ? rows : MMB_ST_ROWS, split, p);
-}
-
-static mm_status plan_streamt(const mm_f4_shape *s, mm_f4_plan *p)
-{
-    /* same decomposition as STREAM; the activation rows are padded to the
-     * tensor-core N extent (16 or 32) instead of to 8-row MMA tiles */
-    mm_status st = plan_stream_with(s, MMB_ST_ROWS, 0, p);
-    if (st != MM_OK)
-        return st;
-    p->variant = MM_F4_V_STREAMT;
-    p->tile_m = s->M <= 16 ? 16 : 32;
-    p->m_tiles = p->tile_m / 8;
-    p->threads = MMB_STT_THREADS;
-    uint32_t sk = p->split_k;
-    p->ws_needed = 0;
-    while (sk > 1) {
-        size_t need = MMB_WS_COUNTER_B + (size_t)sk * p->tile_m * s->N * 4u;
-        if (need <= s->ws_bytes) { p->ws_needed = need; break; }
-        sk--;
-    }
-    p->split_k = sk;
-    p->grid_y = sk;
-    uint32_t stage = MMB_STT_STAGE_B(p->tile_m);
-    uint32_t stg = (MMB_SMEM_MAX - MMB_ST_FIXED_B) / stage;
-    if (stg > 6) stg = 6;
-    uint32_t per = ceil_div(p->k_steps, sk);
-    if (stg > per) stg = per;
-    if (stg < 1) stg = 1;
-    p->stages = stg;
-    p->smem_bytes = stg * stage + MMB_ST_FIXED_B;
-    return MM_OK;
 }
 
 /* modelled cost of one CTA tile, arbitrary units: MMA time grows with
@@ -284,7 +282,6 @@ mm_status mm_f4_select_variant(const mm_f4_shape *s, int variant, mm_f4_plan *ou
     case MM_F4_V_ROWWARP: plan_rowwarp(s, out); return MM_OK;
     case MM_F4_V_STREAM:  return plan_stream(s, out);
     case MM_F4_V_UMMA:    return plan_umma(s, out);
-    case MM_F4_V_STREAMT: return plan_streamt(s, out);
     case MM_F4_V_MX:      return plan_mx(s, out);
     default:              return MM_ERR_RANGE;
     }
@@ -296,7 +293,7 @@ mm_status mm_f4_select_variant(const mm_f4_shape *s, int variant, mm_f4_plan *ou
  * the fused form; anything else is MM_ERR_UNSUPPORTED and runs as three ops. */
 mm_status mm_f4_select_glu(const mm_f4_shape *s, mm_f4_plan *out)
 {
-    return mmb_select_glu(s, 0, out);
+    return mmb_select_glu(s, 1, out);
 }
 
 mm_status mmb_select_glu(const mm_f4_shape *s, int allow_mx, mm_f4_plan *out)
@@ -343,7 +340,9 @@ mm_status mm_f4_select(const mm_f4_shape *s, mm_f4_plan *out)
     mm_status st = check_shape(s, out);
     if (st != MM_OK)
         return st;
-    if (s->M <= 32 && plan_stream(s, out) == MM_OK)
+    /* decode: the block-scaled tensor kernel when the digit planes of the
+     * activations fit the workspace, else the CUDA-core streaming kernel */
+    if (s->M <= 32 && (plan_mx(s, out) == MM_OK || plan_stream(s, out) == MM_OK))
         return MM_OK;
     if (s->M > 32 && plan_umma(s, out) == MM_OK)
         return MM_OK;

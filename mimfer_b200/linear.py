@@ -129,7 +129,7 @@ class Runtime:
 
     _instance = None
 
-    def __init__(self, device=0, workspace_bytes=64 << 20):
+    def __init__(self, device=0, workspace_bytes=256 << 20):
         import torch
         if not torch.cuda.is_available():
             raise RuntimeError("mimfer_b200 needs a CUDA device (sm_100a); there is no CPU path")

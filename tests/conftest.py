@@ -47,6 +47,15 @@ def rt(lib):
     return r
 
 
+@pytest.fixture
+def stream_kernel(rt):
+    """Decode ops on the CUDA-core streaming kernel for the duration of a test (the
+    block-scaled tensor kernel is the default)."""
+    rt.lib.mm_f4_tune(5, 0)
+    yield rt
+    rt.lib.mm_f4_tune(5, 1)
+
+
 def bf16_bits_to_f32(bits):
     return (np.ascontiguousarray(bits).astype(np.uint32) << 16).view(np.float32)
 

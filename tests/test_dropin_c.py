@@ -33,10 +33,13 @@ def test_links_against_unmodified_reference_headers(lib, tmp_path):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("M,K,N", [(1, 5120, 512), (16, 17408, 1024), (300, 512, 264), (3, 48, 9)])
-def test_c_host_matches_python_path(rt, lib, tmp_path, M, K, N):
+def test_c_host_matches_python_path_and_oracle(rt, lib, oracle, tmp_path, M, K, N):
     import mimfer_b200 as mm
+    from conftest import REL_L2_TOL, row_rel_l2
     exe = _build(tmp_path, ["-I" + os.path.join(ROOT, "include")])
     out = subprocess.check_output([exe, str(M), str(K), str(N)], timeout=300).decode().split()[-1]
     w = mm.make_weight(N, K, seed=0).to_device(rt.device)
-    y = rt.from_device_bf16(rt.gemm_f4(rt.to_device_bf16(mm.make_activations(M, K, seed=1)), w))
-    assert int(out, 16) == fnv1a64(np.ascontiguousarray(y))
+    xb = mm.make_activations(M, K, seed=1)
+    y = rt.from_device_bf16(rt.gemm_f4(rt.to_device_bf16(xb), w))
+    assert int(out, 16) == fnv1a64(np.ascontiguousarray(y))          # the C host's output, bit for bit
+    assert row_rel_l2(y, oracle.gemm_f4(xb, w.payload, w.scales, w.gs)) <= REL_L2_TOL

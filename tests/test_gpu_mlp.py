@@ -32,12 +32,22 @@ DECODE = [(1, 1024, 384), (5, 2048, 200), (8, 5120, 128), (16, 1024, 1000), (17,
 
 @pytest.mark.parametrize("M,K,inter", DECODE)
 @pytest.mark.parametrize("order", ["gate_first", "up_first"])
-def test_gate_up_decode(rt, oracle, M, K, inter, order):
+@pytest.mark.parametrize("kernel", ["block_scaled", "streaming"])
+def test_gate_up_decode(rt, oracle, M, K, inter, order, kernel):
+    rt.lib.mm_f4_tune(5, 1 if kernel == "block_scaled" else 0)
+    try:
+        _gate_up_decode(rt, oracle, M, K, inter, order, L.V_MX if kernel == "block_scaled" else L.V_STREAM)
+    finally:
+        rt.lib.mm_f4_tune(5, 1)
+
+
+def _gate_up_decode(rt, oracle, M, K, inter, order, variant):
     wg, wu, keep = _pair(rt, K, inter, seed=M + inter, order=order)
     xb = mm.make_activations(M, K, seed=3)
     x = rt.to_device_bf16(xb)
     y = rt.torch.full((M, inter), 7.0, dtype=rt.torch.bfloat16, device=rt.device)
-    assert mm.select_plan(M, K, inter, ws_bytes=64 << 20, glu=True).variant == L.V_STREAM
+    if variant == L.V_MX:                                   # the selector's default for a decode pair
+        assert mm.select_plan(M, K, inter, ws_bytes=rt.lib.mm_f4_workspace_bytes() // 8, glu=True).variant == variant
     rt.mlp_gate_up_async(x, wg, wu, y)
     rt.sync()
     assert rt.device_status() == 0
@@ -72,12 +82,14 @@ def test_gate_up_prefill(rt, oracle, M, K, inter):
     assert _exact_fraction(got, ref) > 0.9
 
 
-def test_gate_up_matches_three_ops_on_device(rt):
-    """Fused kernel against the same library's gate GEMM, up GEMM and SILU_MUL."""
+def test_gate_up_matches_three_ops_on_device(rt, oracle):
+    """Fused kernel against the same library's gate GEMM, up GEMM and SILU_MUL, and both
+    against the oracle's three ops."""
     torch = rt.torch
     for (M, K, inter) in [(4, 5120, 1024), (96, 1024, 512)]:
         wg, wu, keep = _pair(rt, K, inter, seed=11)
-        x = rt.to_device_bf16(mm.make_activations(M, K, seed=5))
+        xb = mm.make_activations(M, K, seed=5)
+        x = rt.to_device_bf16(xb)
         g = torch.empty((M, inter), dtype=torch.bfloat16, device=rt.device)
         u = torch.empty_like(g)
         y3 = torch.empty_like(g)
@@ -87,9 +99,13 @@ def test_gate_up_matches_three_ops_on_device(rt):
         rt.silu_mul_async(g, u, y3)
         rt.mlp_gate_up_async(x, wg, wu, y1)
         rt.sync()
+        assert rt.device_status() == 0
         a, b = rt.from_device_bf16(y1), rt.from_device_bf16(y3)
-        assert _exact_fraction(a, b) > 0.999          # same sums, same epilogue arithmetic
+        assert _exact_fraction(a, b) > 0.99           # same epilogue arithmetic; K slices may differ
         assert row_rel_l2(a, b) <= 2.0 ** -10
+        want = oracle.mlp_gate_up(xb, wg, wu)
+        assert row_rel_l2(a, want) <= REL_L2_TOL and row_rel_l2(b, want) <= REL_L2_TOL
+        assert _exact_fraction(a, want) > 0.9
 
 
 def test_gate_up_rejects_what_it_cannot_fuse(rt):

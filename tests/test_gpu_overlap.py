@@ -1,10 +1,13 @@
 """Dependency-aware launch order of the op-list engine (mm_lin_engine_overlap):
 independent ops run ahead of their predecessors, dependent ones wait; results
-are those of the serial order."""
+are those of the serial order.  This is the engine with group launches off; the
+run-ahead form of the streaming kernel is tested with that kernel selected, the
+plane cache with the block-scaled one."""
 import numpy as np
 import pytest
 
 import mimfer_b200 as mm
+from mimfer_b200 import _lib as L
 from conftest import REL_L2_TOL, row_rel_l2
 
 pytestmark = pytest.mark.gpu
@@ -14,10 +17,11 @@ def _dev(rt, w):
     return mm.NvFp4Weight(w.payload, w.scales, w.gs, w.N, w.K).to_device(rt.device)
 
 
-def test_chain_with_dependent_and_independent_ops(rt, oracle):
+def test_chain_with_dependent_and_independent_ops(stream_kernel, oracle):
     """q, k, v read the same x (independent); o reads q's output (dependent);
     two split-K ops in a row take different workspace regions; a third reuse of a
     buffer forces a wait."""
+    rt = stream_kernel
     torch = rt.torch
     M, K = 4, 1024
     wq, wk, wv = (mm.make_weight(n, K, seed=s) for n, s in ((1024, 1), (256, 2), (256, 3)))
@@ -34,6 +38,7 @@ def test_chain_with_dependent_and_independent_ops(rt, oracle):
     def build(overlap):
         eng = mm.LinearEngine(rt)
         eng.overlap(overlap)
+        eng.group(False)
         eng.add(x, dq, yq)          # 0 first op: waits
         eng.add(x, dk, yk)          # 1 independent
         eng.add(x, dv, yv)          # 2 independent
@@ -77,8 +82,9 @@ def test_chain_with_dependent_and_independent_ops(rt, oracle):
         assert np.array_equal(outs[(False, True)][n], outs[(True, True)][n]), n
 
 
-def test_many_independent_split_ops_stay_correct(rt, oracle):
+def test_many_independent_split_ops_stay_correct(stream_kernel, oracle):
     """More split-K ops in a row than workspace regions, replayed many times."""
+    rt = stream_kernel
     torch = rt.torch
     M, K, N = 8, 8192, 512
     ws = [mm.make_weight(N, K, seed=20 + i) for i in range(6)]
@@ -88,6 +94,7 @@ def test_many_independent_split_ops_stay_correct(rt, oracle):
     ys = [torch.zeros((M, N), dtype=torch.bfloat16, device=rt.device) for _ in ws]
     eng = mm.LinearEngine(rt)
     eng.overlap(True)
+    eng.group(False)
     for d, y in zip(ds, ys):
         eng.add(x, d, y)
     eng.capture()
@@ -101,10 +108,11 @@ def test_many_independent_split_ops_stay_correct(rt, oracle):
     eng.close()
 
 
-def test_run_ahead_ops_on_shallow_split(rt, oracle):
+def test_run_ahead_ops_on_shallow_split(stream_kernel, oracle):
     """Overlap level 2: ops that run ahead take fewer K slices.  Same answer within the
     op's tolerance, the same bits on every replay, and the first op (which waits) keeps
     the bits of the serial order."""
+    rt = stream_kernel
     torch = rt.torch
     M, K, N = 4, 17408, 2048                            # 8 row tiles: 17 slices alone, 8 when running ahead
     ws = [mm.make_weight(N, K, seed=30 + i) for i in range(3)]
@@ -116,6 +124,7 @@ def test_run_ahead_ops_on_shallow_split(rt, oracle):
     for level in (1, 2):
         eng = mm.LinearEngine(rt)
         eng.overlap(level)
+        eng.group(False)
         for d, y in zip(ds, ys):
             eng.add(x, d, y)
         eng.capture()
@@ -135,3 +144,34 @@ def test_run_ahead_ops_on_shallow_split(rt, oracle):
             assert row_rel_l2(y, oracle.gemm_f4(xb, w.payload, w.scales, w.gs)) <= REL_L2_TOL
         runs[level] = got[0]
     assert np.array_equal(runs[1][0], runs[2][0])       # the op that waits is planned as before
+
+
+def test_plane_cache_with_the_block_scaled_kernel(rt, oracle):
+    """Overlap mode without group launches: activations that no op of the list writes are
+    turned into digit planes once, ahead of the ops; q, k and v share one set, the op that
+    reads q's output slices for itself."""
+    torch = rt.torch
+    M, K = 4, 1024
+    wq, wk, wv = (mm.make_weight(n, K, seed=s) for n, s in ((1024, 1), (256, 2), (256, 3)))
+    wo = mm.make_weight(512, 1024, seed=4)
+    dq, dk, dv, do = (_dev(rt, w) for w in (wq, wk, wv, wo))
+    xb = mm.make_activations(M, K, seed=7)
+    x = rt.to_device_bf16(xb)
+    bf = dict(dtype=torch.bfloat16, device=rt.device)
+    yq, yk, yv, yo = (torch.zeros((M, n), **bf) for n in (1024, 256, 256, 512))
+    eng = mm.LinearEngine(rt)
+    eng.overlap(2)
+    eng.group(False)
+    for a, w, y in ((x, dq, yq), (x, dk, yk), (x, dv, yv), (yq, do, yo)):
+        eng.add(a, w, y)
+    eng.capture()
+    assert rt.lib.mm_lin_engine_n_sliced_ahead(eng.h) == 1
+    for _ in range(3):
+        eng.launch()
+    rt.sync()
+    assert rt.device_status() == 0
+    for w, y in ((wq, yq), (wk, yk), (wv, yv)):
+        assert row_rel_l2(rt.from_device_bf16(y), oracle.gemm_f4(xb, w.payload, w.scales, w.gs)) <= REL_L2_TOL
+    q = rt.from_device_bf16(yq)
+    assert row_rel_l2(rt.from_device_bf16(yo), oracle.gemm_f4(q, wo.payload, wo.scales, wo.gs)) <= REL_L2_TOL
+    eng.close()

@@ -77,9 +77,9 @@ def test_stream_config1(rt, oracle):
 
 @pytest.mark.parametrize("M", [1, 16])
 def test_stream_long_k_split(rt, oracle, M):
-    plan = mm.select_plan(M, 17408, 5120, ws_bytes=rt.lib.mm_f4_workspace_bytes())
+    plan = mm.select_plan(M, 17408, 5120, ws_bytes=rt.lib.mm_f4_workspace_bytes(), variant=V_STREAM)
     assert plan.variant == V_STREAM and plan.split_k > 1
-    check(rt, oracle, M, 17408, 5120, None, seed=5)
+    check(rt, oracle, M, 17408, 5120, V_STREAM, seed=5)
 
 
 @pytest.mark.parametrize("rows,split", [(256, 1), (240, 0), (128, 3), (48, 0), (16, 2)])

@@ -2,16 +2,40 @@
 import pytest
 
 import mimfer_b200 as mm
-from mimfer_b200 import V_ROWWARP, V_STREAM, V_UMMA, V_STREAMT
+from mimfer_b200 import V_ROWWARP, V_STREAM, V_UMMA, V_MX
 
 WS = 64 << 20
 SMEM_MAX = 232448
 
 
-def test_decode_shapes_use_stream_and_fill_the_gpu(lib):
-    for M in (1, 2, 4, 8, 16):
+def test_decode_shapes_use_the_block_scaled_kernel_and_fill_the_gpu(lib):
+    for M in (1, 2, 4, 8, 16, 32):
         for (K, N) in ((5120, 34816), (17408, 5120), (5120, 5120)):
             p = mm.select_plan(M, K, N, ws_bytes=WS)
+            assert p.variant == V_MX and p.threads == 352
+            assert p.m_tiles == -(-M // 4) and p.tile_m == 6 * 4 * p.m_tiles      # six digit planes per row
+            assert p.k_steps == K // 256 and 32 <= p.tile_n <= 256 and p.tile_n % 4 == 0
+            assert p.grid_x == -(-N // p.tile_n) and p.grid_y == p.split_k
+            assert 100 <= p.grid_x * p.grid_y <= 148 or p.grid_x > 148
+            assert p.smem_bytes <= SMEM_MAX and p.stages >= 2
+            assert p.ws_needed <= WS
+            if p.split_k > 1:
+                assert p.k_steps // p.split_k >= 4
+
+
+def test_block_scaled_tiles_even_out_over_the_sms(lib):
+    """gate+up (34816 rows) runs as 148 tiles of 236 rows, not 136 of 256; down (5120
+    rows) as 21 tiles x 7 K slices."""
+    p = mm.select_plan(1, 5120, 34816, ws_bytes=WS)
+    assert (p.tile_n, p.grid_x, p.split_k) == (236, 148, 1)
+    p = mm.select_plan(16, 17408, 5120, ws_bytes=WS)
+    assert (p.grid_x, p.split_k) == (21, 7) and p.tile_n * 21 >= 5120
+
+
+def test_stream_kernel_when_asked_or_when_the_planes_do_not_fit(lib):
+    for M in (1, 2, 4, 8, 16):
+        for (K, N) in ((5120, 34816), (17408, 5120), (5120, 5120)):
+            p = mm.select_plan(M, K, N, ws_bytes=WS, variant=V_STREAM)
             assert p.variant == V_STREAM
             assert p.m_tiles == -(-M // 8)
             assert p.k_steps == K // 256 and p.tile_n == 256 and p.grid_x == -(-N // 256)
@@ -19,15 +43,22 @@ def test_decode_shapes_use_stream_and_fill_the_gpu(lib):
             assert p.smem_bytes <= SMEM_MAX and p.stages >= 2
             if p.split_k > 1:
                 assert p.ws_needed <= WS and p.k_steps // p.split_k >= 4
+    # no workspace: no room for digit planes, so the selector itself falls back
+    assert mm.select_plan(16, 17408, 5120, ws_bytes=0).variant == V_STREAM
+    with pytest.raises(mm.MimferError) as e:
+        mm.select_plan(16, 17408, 5120, ws_bytes=0, variant=V_MX)
+    assert e.value.status == 7
+    with pytest.raises(mm.MimferError):
+        mm.select_plan(33, 512, 256, ws_bytes=WS, variant=V_MX)        # more than 32 activation rows
 
 
 def test_small_weights_get_half_height_tiles(lib):
-    """k and v projections (N = 1024): 256-row tiles give 20 CTAs at the deepest split, so
-    the selector halves the tile; bigger weights keep 256 rows."""
-    p = mm.select_plan(16, 5120, 1024, ws_bytes=WS)
+    """k and v projections (N = 1024) on the streaming kernel: 256-row tiles give 20 CTAs at
+    the deepest split, so the selector halves the tile; bigger weights keep 256 rows."""
+    p = mm.select_plan(16, 5120, 1024, ws_bytes=WS, variant=V_STREAM)
     assert p.variant == V_STREAM and p.tile_n == 128 and p.grid_x == 8 and p.split_k == 5
     for (K, N) in ((5120, 6144), (5120, 34816), (17408, 5120)):
-        assert mm.select_plan(16, K, N, ws_bytes=WS).tile_n == 256
+        assert mm.select_plan(16, K, N, ws_bytes=WS, variant=V_STREAM).tile_n == 256
 
 
 def test_no_workspace_means_no_split(lib):
@@ -70,28 +101,20 @@ def test_errors(lib):
     with pytest.raises(mm.MimferError) as e:
         mm.select_plan(4, 48, 64, variant=V_UMMA)
     assert e.value.status == 7
-
-
-def test_streamt_plan_mirrors_stream_decomposition(lib):
-    for M in (1, 9, 16, 17, 32):
-        a = mm.select_plan(M, 17408, 5120, ws_bytes=WS, variant=V_STREAM)
-        b = mm.select_plan(M, 17408, 5120, ws_bytes=WS, variant=V_STREAMT)
-        assert b.variant == V_STREAMT and b.tile_m == (16 if M <= 16 else 32)
-        assert (b.grid_x, b.k_steps, b.tile_n) == (a.grid_x, a.k_steps, a.tile_n)
-        assert b.split_k >= 1 and b.smem_bytes <= SMEM_MAX and b.threads == 736
-        if b.split_k > 1:
-            assert b.ws_needed == 16384 + b.split_k * b.tile_m * 5120 * 4
-    with pytest.raises(mm.MimferError):
-        mm.select_plan(64, 512, 64, variant=V_STREAMT)
+    with pytest.raises(mm.MimferError) as e:
+        mm.select_plan(4, 512, 64, variant=3)                    # no such variant
+    assert e.value.status != 0
 
 
 def test_gated_pair_plans(lib):
     """mm_f4_select_glu: N counts output features; a CTA tile is 128 rows of each projection."""
     p = mm.select_plan(16, 5120, 17408, ws_bytes=WS, glu=True)
-    assert p.variant == V_STREAM and p.grid_x == 17408 // 128 and p.split_k == 1
-    p = mm.select_plan(4, 5120, 1000, ws_bytes=WS, glu=True)          # 8 tiles: K is split
-    assert p.grid_x == 8 and p.split_k > 1
-    assert p.ws_needed == 16384 + p.split_k * p.tile_m * 8 * 256 * 4  # partials per padded tile row
+    assert p.variant == V_MX and p.split_k == 1
+    assert p.tile_n % 16 == 0 and p.grid_x == -(-17408 // (p.tile_n // 2)) and 136 <= p.grid_x <= 148
+    p = mm.select_plan(4, 5120, 1000, ws_bytes=WS, glu=True)          # few tiles: K is split
+    assert p.variant == V_MX and p.split_k > 1 and p.ws_needed <= WS
+    p = mm.select_plan(4, 5120, 1000, ws_bytes=0, glu=True)           # no room for digit planes
+    assert p.variant == V_STREAM and p.grid_x == 8
     for M in (512, 8192):
         p = mm.select_plan(M, 5120, 17408, glu=True)
         assert p.variant == V_UMMA and p.tile_n == 256 and p.grid_x == 136
