@@ -7,8 +7,10 @@ One "step" is one pass of the hot path over one batch of synthetic input:
 
   N = 1   the decode sweep: M in {1,2,4,8,16} on gate+up (K=5120 -> N=34816) and
           down (K=17408 -> N=5120); ten ops, each on its own copy of the weights
-          (750 MB per step, larger than L2), replayed as one captured graph.
-          value = packed weight bytes (payload + block scales) / time, GB/s.
+          (750 MB per step, larger than L2), replayed as one captured graph (the
+          engine runs the ten independent ops as one persistent group launch).
+          value = packed weight bytes (payload + block scales) / time, GB/s: the
+          median of REPEATS timed regions of --steps steps each, min and max beside it.
   N > 1   tensor-parallel linears: gate+up and the LM head (K=5120 -> N=151936),
           split along N, at M=32, each followed by the all-gather of the output
           slices (NCCL over NVLink).  value = whole-weight bytes / time, GB/s.
@@ -44,10 +46,11 @@ SHAPES = {  # name: (K, N)
 DECODE_M = (1, 2, 4, 8, 16)
 PREFILL_M = (512, 2048, 8192)
 HBM_FALLBACK_GBS, TENSOR_FALLBACK_TFS = 6650.0, 1590.0
-# dram__bytes_read + dram__bytes_write over algorithmic bytes, from the ncu capture of the decode
-# kernel on gate+up (profiles/stream_kernel_decode_gate_up.md); traffic grows with the weight bytes,
-# so the per-launch figure of the sweep is this ratio times its algorithmic bytes.
-STREAM_TRAFFIC_RATIO = 1.044
+REPEATS = 7          # timed regions per headline number
+# dram__bytes_read + dram__bytes_write over algorithmic bytes, from an ncu capture of the group
+# kernel on two gate+up ops at M=1 and M=16; traffic grows with the weight bytes, so the
+# per-launch figure of the sweep is this ratio times its algorithmic bytes.
+GROUP_TRAFFIC_RATIO = 1.02
 
 
 def wbytes(K, N):
@@ -164,30 +167,41 @@ class Bench:
             self.dist.barrier()
         self.torch.cuda.synchronize()
 
-    def timed(self, fn, steps, warmup):
-        """ms per step: events on the compute stream, max over ranks."""
+    def timed(self, fn, steps, warmup, repeats=1, stats=None):
+        """ms per step: events on the compute stream, max over ranks.  With repeats > 1 the
+        timed region of `steps` steps runs that many times and the median is returned;
+        `stats` (a dict) receives median, min and max."""
         for _ in range(max(warmup, 3)):
             fn()
-        self.rt.sync()
-        self.barrier()
-        self.rt.time_begin()
-        for _ in range(steps):
-            fn()
-        ms = self.rt.time_end()
-        self.barrier()
-        if self.world > 1:
-            t = self.torch.tensor([ms], device=self.dev)
-            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
-            ms = float(t.item())
+        vals = []
+        for _ in range(max(1, repeats)):
+            self.rt.sync()
+            self.barrier()
+            self.rt.time_begin()
+            for _ in range(steps):
+                fn()
+            ms = self.rt.time_end()
+            self.barrier()
+            if self.world > 1:
+                t = self.torch.tensor([ms], device=self.dev)
+                self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+                ms = float(t.item())
+            vals.append(ms / steps)
         status = self.rt.device_status()
         if status:
             raise RuntimeError(f"device status 0x{status:x} after timed region")
-        return ms / steps
+        med = statistics.median(vals)
+        if stats is not None:
+            stats.update(median=med, min=min(vals), max=max(vals), regions=len(vals), steps_per_region=steps)
+        return med
 
-    def engine(self, ops, overlap=False):
-        """ops: list of (x, w_dev, y). Captured into one graph."""
+    def engine(self, ops, overlap=False, group=True):
+        """ops: list of (x, w_dev, y). Captured into one graph.  group: independent decode
+        ops as persistent group launches (the engine's default); off, with `overlap`, the
+        op-by-op forms."""
         eng = self.mm.LinearEngine(self.rt, max_ops=len(ops) + 1)
         eng.overlap(overlap)
+        eng.group(group)
         for x, w, y in ops:
             eng.add(x, w, y)
         eng.launch()                  # direct dispatch once: errors surface per op
@@ -199,7 +213,8 @@ class Bench:
         return self.torch.empty((M, N), dtype=self.torch.bfloat16, device=self.dev)
 
     # -- workloads -------------------------------------------------------------
-    def decode_sweep(self, steps, warmup, ms_list=DECODE_M, names=("gate_up", "down")):
+    def decode_sweep(self, steps, warmup, ms_list=DECODE_M, names=("gate_up", "down"), per_op=False,
+                     repeats=REPEATS, other_orders=True):
         ops, wb, ab = [], 0, 0
         for name in names:
             K, N = SHAPES[name]
@@ -208,15 +223,47 @@ class Bench:
                 ops.append((self.acts(M, K), self.dev_weight(hw), self.empty(M, N)))
                 wb += wbytes(K, N)
                 ab += alg_bytes(M, K, N)
-        serial = self.engine(ops)
-        ms_serial = self.timed(serial.launch, steps, warmup)
-        serial.close()
-        eng = self.engine(ops, overlap=2)         # independent ops run ahead of their predecessors, on shallower K splits
-        ms = self.timed(eng.launch, steps, warmup)
+        pk = peaks()["hbm"]
+        ms_serial = ms_ahead = float("nan")
+        if other_orders:
+            serial = self.engine(ops, group=False)          # op by op in list order, one kernel each
+            ms_serial = self.timed(serial.launch, steps, warmup, repeats=3)
+            serial.close()
+            ahead = self.engine(ops, overlap=2, group=False)  # op by op, independent ops run ahead
+            ms_ahead = self.timed(ahead.launch, steps, warmup, repeats=3)
+            ahead.close()
+        table = []
+        if per_op:
+            # one (op, M) at a time: as many ops of that shape as the sweep holds weight copies
+            # of it (5 x 100 MB or 5 x 50 MB per step: larger than L2), one group launch
+            for name in names:
+                K, N = SHAPES[name]
+                same = [o for o in ops if (o[1].K, o[1].N) == (K, N)]
+                for M in ms_list:
+                    x = self.acts(M, K)
+                    grp = [(x, w, self.empty(M, N)) for _, w, _ in same]
+                    e = self.engine(grp)
+                    ms1 = self.timed(e.launch, steps, warmup, repeats=3) / len(grp)
+                    e.close()
+                    table.append({"op": name, "M": M, "us": round(ms1 * 1e3, 2),
+                                  "weight_gbs": round(wbytes(K, N) / ms1 / 1e6),
+                                  "frac": round(alg_bytes(M, K, N) / ms1 / 1e6 / pk, 3)})
+        self.rt.lib.mm_f4_launch_count(1)
+        eng = self.engine(ops)                            # the default: one persistent group launch
+        per_capture = int(self.rt.lib.mm_f4_launch_count(1)) // 2      # issued once directly, once captured
+        st = {}
+        ms = self.timed(eng.launch, steps, warmup, repeats=repeats, stats=st)
         res = {"ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "alg_gbs": ab / ms / 1e6,
-               "ops": len(ops), "weight_bytes": wb, "alg_bytes_per_launch": ab / len(ops),
-               "avg_launch_us": ms * 1e3 / len(ops), "independent_ops": eng.n_independent(),
-               "serial_order": {"ms_per_step": ms_serial, "weight_gbs": wb / ms_serial / 1e6}}
+               "ms_per_step_min": st["min"], "ms_per_step_max": st["max"], "timed_regions": st["regions"],
+               "weight_gbs_min": wb / st["max"] / 1e6, "weight_gbs_max": wb / st["min"] / 1e6,
+               "ops": len(ops), "weight_bytes": wb, "alg_bytes": ab, "group_launches": eng.n_group_launches(),
+               "kernel_launches_per_step": per_capture,
+               "serial_order": {"ms_per_step": ms_serial, "weight_gbs": wb / ms_serial / 1e6,
+                                "what": "one kernel pair per op, in list order"},
+               "run_ahead": {"ms_per_step": ms_ahead, "weight_gbs": wb / ms_ahead / 1e6,
+                             "what": "one kernel per op, independent ops launched ahead of their predecessors"}}
+        if table:
+            res["per_op"] = table
         return res, ops, eng
 
     def decode_e2e(self, ops, eng, steps, warmup):
@@ -237,7 +284,6 @@ class Bench:
         sec_unbound = (time.perf_counter() - t0) / steps
         # the same step with the copies captured into the graph (bound pinned buffers)
         bound = self.mm.LinearEngine(self.rt, max_ops=len(ops) + 1)
-        bound.overlap(2)
         for x, w, y in ops:
             bound.add(x, w, y)
         bound.upload_group((len(ops) + 1) // 2)
@@ -265,7 +311,8 @@ class Bench:
                 "d2h_bytes_per_step": d2h, "ms_per_step": sec * 1e3,
                 "call": "mm_lin_engine_step_bound: one graph replay that uploads every op's activations "
                         "from pinned host memory on the transfer stream (one gather kernel per five ops), "
-                        "runs the ten ops and downloads every output to pinned host memory; one sync",
+                        "runs the ten ops as one group launch and downloads every output to pinned host "
+                        "memory; one sync",
                 "copies_outside_graph": {"value": wb / sec_unbound / 1e9, "ms_per_step": sec_unbound * 1e3,
                                          "call": "mm_lin_engine_launch_host"},
                 "per_op_sync": {"value": wb / sec_op / 1e9, "ms_per_step": sec_op * 1e3,
@@ -295,19 +342,31 @@ class Bench:
         for layer in range(layers):
             for n in names:
                 K, N = SHAPES[n]
+                # every op has its own weights and its own output: 384 independent linears
                 ops.append((self.acts(M, K) if layer == 0 else ops[names.index(n)][0],
-                            self.dev_weight(base[n]), self.empty(M, N) if layer == 0 else ops[names.index(n)][2]))
+                            self.dev_weight(base[n]), self.empty(M, N)))
                 wb += wbytes(K, N)
-        eng = self.engine(ops)
+        eng = self.engine(ops, group=False)
         ms_serial = self.timed(eng.launch, max(2, steps // 2), 3)
         eng.close()
-        eng = self.engine(ops, overlap=2)
-        ms = self.timed(eng.launch, max(2, steps // 2), 3)
+        eng = self.engine(ops, overlap=2, group=False)
+        ms_ahead = self.timed(eng.launch, max(2, steps // 2), 3)
         ind = eng.n_independent()
         eng.close()
+        self.rt.lib.mm_f4_launch_count(1)
+        eng = self.engine(ops)
+        launches = int(self.rt.lib.mm_f4_launch_count(1)) // 2
+        st = {}
+        ms = self.timed(eng.launch, max(2, steps // 2), 3, repeats=5, stats=st)
+        groups = eng.n_group_launches()
+        eng.close()
         return {"layers": layers, "M": M, "ops": len(ops), "weight_bytes": wb,
-                "sum_linear_ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "independent_ops": ind,
-                "serial_order": {"sum_linear_ms_per_step": ms_serial, "weight_gbs": wb / ms_serial / 1e6}}
+                "sum_linear_ms_per_step": ms, "weight_gbs": wb / ms / 1e6,
+                "ms_min": st["min"], "ms_max": st["max"], "timed_regions": st["regions"],
+                "group_launches": groups, "kernel_launches_per_step": launches,
+                "serial_order": {"sum_linear_ms_per_step": ms_serial, "weight_gbs": wb / ms_serial / 1e6},
+                "run_ahead": {"sum_linear_ms_per_step": ms_ahead, "weight_gbs": wb / ms_ahead / 1e6,
+                              "independent_ops": ind}}
 
     def decode_step_planner(self, steps, warmup, layers=64, M=16):
         """The 64-layer decode step with the op sequence of the reference planner
@@ -332,11 +391,12 @@ class Bench:
             layer_w.append(ws)
             wb += sum(wbytes(*SHAPES[n]) for n in lin) + 2 * wbytes(K, inter)
         res = {"layers": layers, "M": M, "weight_bytes": wb}
-        for fuse, overlap, tag in ((False, 0, "as_emitted"), (True, 0, "fused_mlp"),
-                                   (True, 2, "fused_mlp_overlap")):
+        for fuse, overlap, group, tag in ((False, 0, False, "as_emitted"), (True, 0, False, "fused_mlp"),
+                                          (True, 2, False, "fused_mlp_overlap"), (True, 0, True, "fused_mlp_groups")):
             eng = self.mm.LinearEngine(self.rt, max_ops=8 * layers)
             eng.fuse_mlp(fuse)
             eng.overlap(overlap)
+            eng.group(group)
             for ws in layer_w:
                 for n in ("q", "k", "v"):
                     eng.add(x, ws[n], ys[n])
@@ -350,8 +410,9 @@ class Bench:
             self.rt.sync()
             eng.capture()
             ms = self.timed(eng.launch, max(2, steps // 2), 3)
+            groups = eng.n_group_launches()
             eng.close()
-            res[tag] = {"ops": n_ops, "ms_per_step": ms, "weight_gbs": wb / ms / 1e6}
+            res[tag] = {"ops": n_ops, "ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "group_launches": groups}
         del layer_w, keep
         self.torch.cuda.empty_cache()
         return res
@@ -403,6 +464,9 @@ class Bench:
         weight stream alone, 2 = the arithmetic alone, 4 = split-K without the
         exchange), each as a short burst (20 graph replays after a pause) and
         sustained for `secs` seconds with SM clock and board power sampled."""
+        if self.rt.lib.mm_f4_tune(4, 0) == -1:
+            raise SystemExit("decode_parts needs a library built with MMB_EXTRA_DEFS=-DMMB_MEASURE_MODES")
+        self.rt.lib.mm_f4_tune(5, 0)                  # the modes belong to the streaming kernel
         rows = []
         for name, copies in (("gate_up", 5), ("down", 8)):
             K, N = SHAPES[name]
@@ -416,7 +480,7 @@ class Bench:
                     if mode == 4 and name == "gate_up":
                         continue                      # gate+up runs unsplit
                     self.rt.lib.mm_f4_tune(4, mode)
-                    eng = self.engine([(x, w, y) for w, y in zip(ws, ys)], overlap=True)
+                    eng = self.engine([(x, w, y) for w, y in zip(ws, ys)], overlap=True, group=False)
                     time.sleep(0.3)
                     burst = self.timed(eng.launch, 20, 3)
                     with Clocks(self.local) as clk:
@@ -438,6 +502,7 @@ class Bench:
                                  "weight_gbs_burst": round(wbytes(K, N) / (burst / copies) / 1e6)})
             del ws
             self.torch.cuda.empty_cache()
+        self.rt.lib.mm_f4_tune(5, 1)
         return {"rows": rows}
 
     def _shard_rows(self, name):
@@ -495,6 +560,42 @@ class Bench:
         torch.cuda.empty_cache()
         return res
 
+    def tp_parity(self, lins, xs, M):
+        """The outputs of one more tensor-parallel step against the CPU oracle (checker only):
+        every rank's copy of both full outputs, on column windows inside and across the shard
+        edges, sampled rows at prefill size.  Worst per-row relative L2 over ranks and windows."""
+        from oracle.pyoracle import Oracle
+        orc = Oracle()
+        ys = {n: lin.forward(xs[n], barrier=False) for n, lin in lins.items()}
+        list(lins.values())[-1].barrier()
+        self.rt.sync()
+        self.barrier()
+        rows = None if M <= 32 else sorted({0, 255, M // 2, M - 1})
+        worst = 0.0
+        for n, lin in lins.items():
+            hw = self.weight(n)
+            xb = self.rt.from_device_bf16(xs[n])
+            ns = SHAPES[n][1] // self.world
+            edges = sorted({0, ns * (self.world // 2), ns * (self.world - 1)})
+            y = ys[n]
+            for e in edges:
+                a = max(0, e - 128)
+                b = a + 256
+                got = self.rt.from_device_bf16(y[:, a:b].contiguous() if rows is None
+                                               else y[rows][:, a:b].contiguous())
+                want = orc.gemm_f4(xb, hw.payload, hw.scales, hw.gs, rows=rows, n_begin=a, n_end=b)
+                g = (got.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+                r = (want.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+                den = np.sqrt((r ** 2).sum(axis=1))
+                err = float((np.sqrt(((g - r) ** 2).sum(axis=1)) / np.where(den == 0, 1.0, den)).max())
+                worst = max(worst, err)
+        t = self.torch.tensor([worst], dtype=self.torch.float64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        worst = float(t.item())
+        return {"max_row_rel_l2": worst, "tolerance": 2.0 ** -8, "ok": worst <= 2.0 ** -8,
+                "checked": "every rank's outputs, 256-column windows at shard edges, against the CPU oracle"}
+
     def tp_series(self, steps, warmup):
         """config 5: gate+up and LM head, sharded along N over all ranks, M=32 and M=8192."""
         from mimfer_b200.tp import TpLinear, TpStep
@@ -525,6 +626,8 @@ class Bench:
                 res[tag] = {"ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "tflops": fl / ms / 1e9,
                             "issue": "one CUDA graph per rank" if captured else "op by op",
                             "op_by_op_ms_per_step": ms_eager}
+                if mode == modes[0]:
+                    res[tag]["parity"] = self.tp_parity(lins, xs, M)
                 for lin in lins.values():
                     lin._bufs.clear()
                     lin._symm.clear()
@@ -549,6 +652,31 @@ class Bench:
             del ops
             self.torch.cuda.empty_cache()
         out["local_only"] = res
+        # like-for-like efficiency: the same two linears unsharded on one GPU, timed in this run
+        # (at one rank that is the series itself)
+        if self.world > 1:
+            whole = {n: self.dev_weight(self.weight(n)) for n in ("gate_up", "lm_head")}
+            one = {}
+            for tag, M, st in (("decode_m32", 32, steps), ("prefill_m8192", 8192, max(2, steps // 4))):
+                ops = [(self.acts(M, SHAPES[n][0]), w, self.empty(M, w.N)) for n, w in whole.items()]
+                if M <= 32:
+                    eng = self.engine(ops)
+                    one[tag] = self.timed(eng.launch, st, warmup)
+                    eng.close()
+                else:
+                    def step():
+                        for x, w, y in ops:
+                            self.rt.linear_async(x, w, y)
+                    one[tag] = self.timed(step, st, warmup)
+                del ops
+                self.torch.cuda.empty_cache()
+            del whole
+            self.torch.cuda.empty_cache()
+        else:
+            one = {tag: out[modes[0]][tag]["ms_per_step"] for tag in ("decode_m32", "prefill_m8192")}
+        out["one_gpu_ms_per_step"] = one
+        out["efficiency"] = {tag: one[tag] / (self.world * out[modes[0]][tag]["ms_per_step"])
+                             for tag in ("decode_m32", "prefill_m8192")}
         best = modes[0]
         out["mode"] = best + (" (kernel epilogue stores to peers)" if best == "fused" else " (single GPU)")
         out.update(out[best])
@@ -560,21 +688,31 @@ def cpu_baseline(threads=None, target_s=12.0):
     host's cores, on a bounded sample of the decode sweep: the first R rows of
     gate+up and of down at every M of the sweep, R sized by a short probe so
     the sample takes about target_s seconds.  Same metric as the GPU arm:
-    packed weight bytes processed / time."""
-    import mimfer_b200 as mm
+    packed weight bytes processed / time.  Inputs come from the host-only
+    generator beside the checkers (numpy; the same packing recipe), so this leg
+    loads nothing of the product library."""
+    from oracle import inputs
     from oracle.pyoracle import Oracle, Reference, host_threads
     threads = threads or host_threads()
     ref = Reference()
     kind = "reference" if ref.available else "port"
     orc = None if ref.available else Oracle()
+    cache = {}
 
-    def run(x, w):
+    def weights(name, rows):
+        if cache.get(name, (0,))[0] < rows:
+            K = SHAPES[name][0]
+            cache[name] = (rows, *inputs.make_weight(rows, K, seed=0)[:2])
+        _, payload, scales = cache[name]
+        return payload[:rows], scales[:rows]
+
+    def run(x, payload, scales):
         t0 = time.perf_counter()
         if ref.available:
-            rc, _ = ref.gemm_f4(x, w.payload, w.scales, threads=threads)
+            rc, _ = ref.gemm_f4(x, payload, scales, threads=threads)
             assert rc == 0
         else:
-            orc.gemm_f4(x, w.payload, w.scales, 1.0, threads=threads)
+            orc.gemm_f4(x, payload, scales, 1.0, threads=threads)
         return time.perf_counter() - t0
 
     def sweep(rows):
@@ -582,20 +720,21 @@ def cpu_baseline(threads=None, target_s=12.0):
         for name in ("gate_up", "down"):
             K, N = SHAPES[name]
             r = min(rows, N)
-            w = mm.make_weight(r, K, seed=0)
+            payload, scales = weights(name, r)
             for M in DECODE_M:
-                dt += run(mm.make_activations(M, K, seed=1), w)
+                dt += run(inputs.make_activations(M, K, seed=1), payload, scales)
                 nbytes += wbytes(K, r)
         return dt, nbytes
 
     probe_rows = 16 * threads
     dt, _ = sweep(probe_rows)
     rows = int(min(34816, max(probe_rows, probe_rows * target_s / max(dt, 1e-6))))
-    dt, nbytes = sweep(rows)
+    dt, nbytes, passes = *sweep(rows), 1
     while dt < 0.8 * target_s:                     # few rows left to add: repeat the sweep instead
         d2, n2 = sweep(rows)
-        dt, nbytes = dt + d2, nbytes + n2
+        dt, nbytes, passes = dt + d2, nbytes + n2, passes + 1
     return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
+            "seconds": dt, "passes": passes,
             "sample": f"decode sweep M in {{1,2,4,8,16}} on the first {rows} rows of gate+up and of down, "
                       f"{dt:.1f} s of CPU time"}
 
@@ -618,20 +757,29 @@ def run_b200(args):
                 print(json.dumps({"case": args.case, **res}))
             return
         if b.world == 1:
-            dec, ops, eng = b.decode_sweep(steps, warmup)
-            line.update(value=dec["weight_gbs"], ms_per_step=dec["ms_per_step"], scaling="weak",
-                        gpu_launches=dec["ops"] * steps,
+            dec, ops, eng = b.decode_sweep(steps, warmup, per_op=True)
+            line.update(value=dec["weight_gbs"], ms_per_step=dec["ms_per_step"], scaling="strong",
+                        value_min=dec["weight_gbs_min"], value_max=dec["weight_gbs_max"],
+                        timed_regions=dec["timed_regions"],
+                        gpu_launches=dec["kernel_launches_per_step"] * steps,
                         config={"workload": "decode GEMV sweep M in {1,2,4,8,16} x {gate+up 5120->34816, "
-                                            "down 17408->5120}, 10 ops per step, one CUDA graph",
+                                            "down 17408->5120}, 10 ops per step, one CUDA graph: two slicing "
+                                            "kernels and one persistent group launch of the block-scaled kernel",
                                 "l2": "every op reads its own weight copy: 750 MB per step, larger than L2",
+                                "timing": f"median of {dec['timed_regions']} timed regions of {steps} steps",
                                 "quant": "NVFP4 e2m1 + e4m3/16 + fp32 global scale", "peaks": pk["src"]})
-            line["roofline"] = {"bound": "hbm", "kernel": "f4_stream_kernel",
+            line["decode_sweep"] = {k: dec[k] for k in ("ops", "weight_bytes", "alg_bytes", "group_launches",
+                                                        "kernel_launches_per_step", "ms_per_step_min",
+                                                        "ms_per_step_max", "serial_order", "run_ahead", "per_op")}
+            line["roofline"] = {"bound": "hbm", "kernel": "f4_mxg_kernel",
                                 "achieved": dec["alg_gbs"], "peak": pk["hbm"], "unit": "GB/s",
                                 "frac": dec["alg_gbs"] / pk["hbm"], "of": pk["src"],
-                                "alg_bytes_per_launch": dec["alg_bytes_per_launch"],
-                                "avg_launch_us": dec["avg_launch_us"],
-                                "traffic": STREAM_TRAFFIC_RATIO * dec["alg_bytes_per_launch"],
-                                "traffic_src": "ncu capture of gate+up M=1 scaled by algorithmic bytes"}
+                                "alg_bytes_per_launch": dec["alg_bytes"],
+                                "launch_us": dec["ms_per_step"] * 1e3,
+                                "launch_includes": "the step's two slicing kernels (activations to digit planes)",
+                                "traffic": GROUP_TRAFFIC_RATIO * dec["alg_bytes"],
+                                "traffic_src": "ncu capture of a group launch on two gate+up ops, "
+                                               "scaled by algorithmic bytes"}
             line["e2e"] = b.decode_e2e(ops, eng, max(2, steps // 2), warmup)
             eng.close()
             del ops
@@ -648,7 +796,7 @@ def run_b200(args):
             # same weights with q, k and v as one fused op (the reference planner's OP_QKV layout)
             fused = b.decode_step_64(steps, warmup, names=("qkv", "o", "gate_up", "down"))
             line["decode_step"]["fused_qkv"] = {k: fused[k] for k in ("ops", "sum_linear_ms_per_step", "weight_gbs",
-                                                                      "independent_ops", "serial_order")}
+                                                                      "group_launches", "serial_order", "run_ahead")}
             b.torch.cuda.empty_cache()
             line["mlp_front"] = b.mlp_front(steps, warmup)
             line["decode_step"]["planner_sequence"] = b.decode_step_planner(steps, warmup)
@@ -662,7 +810,7 @@ def run_b200(args):
                                             f"over {b.world} GPUs at M=32, kernel epilogue stores every output "
                                             f"tile to all ranks (symmetric memory), one barrier per step",
                                 "l2": "537 MB of weights per step across ranks", "peaks": pk["src"]})
-            line["roofline"] = {"bound": "hbm", "kernel": "f4_stream_kernel", "achieved": d["weight_gbs"],
+            line["roofline"] = {"bound": "hbm", "kernel": "f4_mx_kernel", "achieved": d["weight_gbs"],
                                 "peak": pk["hbm"] * b.world, "unit": "GB/s",
                                 "frac": d["weight_gbs"] / (pk["hbm"] * b.world), "of": pk["src"], "traffic": None}
             line["prefill"] = {"tflops": tp["prefill_m8192"]["tflops"],
@@ -681,6 +829,14 @@ def run_case(b, case, steps, warmup):
     """Single small cases, used for profiling one kernel at a time."""
     if case == "decode":           # gate+up at M=1 and M=16, two weight copies each
         res, _, eng = b.decode_sweep(steps, warmup, ms_list=(1, 16), names=("gate_up",))
+        eng.close()
+        return res
+    if case == "group":            # one group launch: gate+up and down at M=1 and M=16 (300 MB of weights)
+        res, _, eng = b.decode_sweep(steps, warmup, ms_list=(1, 16), repeats=1, other_orders=False)
+        eng.close()
+        return res
+    if case == "sweep":            # the headline workload alone: the ten-op sweep as one group launch
+        res, _, eng = b.decode_sweep(steps, warmup, repeats=1, other_orders=False)
         eng.close()
         return res
     if case == "decode_parts":     # the decode kernel's time split into stream / arithmetic / exchange
@@ -715,19 +871,25 @@ def run_case(b, case, steps, warmup):
 
 # --------------------------------------------------------------------------- reference arm
 def run_reference(args):
-    """The reference's own CPU implementation of the path on this host's cores."""
+    """The reference's own CPU implementation of the path on this host's cores.  A step is
+    one pass over the bounded sample; --warmup passes are untimed, the median of --steps
+    (at most 5) timed passes is the value."""
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
         return
-    base = cpu_baseline(target_s=max(5.0, min(20.0, 4.0 * args.steps)))
-    t0 = time.perf_counter()
-    vals = [base["value"]]
-    for _ in range(max(0, min(args.steps, 3) - 1)):
-        vals.append(cpu_baseline(target_s=5.0)["value"])
+    steps = max(1, min(args.steps, 5))
+    per = max(4.0, min(12.0, 40.0 / steps))
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_baseline(target_s=2.0)                   # builds the checker, warms the thread pool
+    runs = [cpu_baseline(target_s=per) for _ in range(steps)]
+    vals = [r["value"] for r in runs]
     v = statistics.median(vals)
+    base = runs[vals.index(sorted(vals)[len(vals) // 2])]
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "GB/s", "n_gpus": args.gpus,
-            "steps": len(vals), "warmup": 1, "ms_per_step": (time.perf_counter() - t0) * 1e3 / max(1, len(vals) - 1)
-            if len(vals) > 1 else None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "steps": steps, "warmup": max(1, min(args.warmup, 2)),
+            "ms_per_step": statistics.median(r["seconds"] / r["passes"] for r in runs) * 1e3,
+            "value_min": min(vals), "value_max": max(vals),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16 x nvfp4 -> f32 accumulate", "data": "synthetic",
             "config": {"workload": "reference CPU kx_op_gemm_f4 on a bounded sample of the decode workload: "
                                    + base["sample"]},

@@ -487,8 +487,9 @@ mm_status mm_lin_engine_upload_group(mm_lin_engine *e, uint32_t ops_per_event);
 /* on != 0 (default): the uploads of a group go up as ONE kernel that reads the
  * pinned host buffers over PCIe (they must be mapped for the device, which
  * cudaHostAlloc memory is, and 16-byte aligned; other buffers and groups of
- * more than 32 buffers fall back to copy nodes).  on == 0: always copy nodes.
- * Before capture. */
+ * more than 32 buffers fall back to copy nodes), and the outputs of a group
+ * launch go down the same way: one kernel that writes the pinned host buffers.
+ * on == 0: always copy nodes.  Before capture. */
 mm_status mm_lin_engine_upload_kernel(mm_lin_engine *e, int on);
 void      mm_lin_engine_destroy(mm_lin_engine *e);
 

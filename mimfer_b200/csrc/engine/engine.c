@@ -260,10 +260,33 @@ static mm_status engine_close_group(mm_lin_engine *e, uint32_t first, uint32_t e
     if (with_copies) {
         MM_CHECK(mm_event_record(EV_Y, MM_ST_COMPUTE));
         MM_CHECK(mm_event_wait(EV_Y, MM_ST_XFER));
-        for (uint32_t i = first; i < end; i++) {
-            const mm_op_desc *op = &e->ops[i];
-            if (e->y_bound[i] && op->op != OP_NOP)
-                MM_CHECK(mm_d2h_async(e->y_bound[i], op->c, op_out_bytes(op), MM_ST_XFER));
+        /* the group's outputs go down as one kernel per MMB_GATHER_MAX buffers that
+         * writes the pinned host buffers itself; what it cannot take uses copy nodes */
+        const void *src[MMB_GATHER_MAX];
+        void *dst[MMB_GATHER_MAX];
+        size_t len[MMB_GATHER_MAX];
+        uint32_t pending = 0;
+        for (uint32_t i = first; i <= end; i++) {
+            const mm_op_desc *op = i < end ? &e->ops[i] : NULL;
+            if (op && e->y_bound[i] && op->op != OP_NOP) {
+                src[pending] = op->c;
+                dst[pending] = e->y_bound[i];
+                len[pending] = op_out_bytes(op);
+                pending++;
+            }
+            if (pending == MMB_GATHER_MAX || (i == end && pending)) {
+                int rc = e->upload_kernel
+                             ? mmb_launch_host_scatter(src, dst, len, pending, mm_cuda_stream_raw(MM_ST_XFER))
+                             : -1;
+                if (rc > 0) {
+                    MM_LOGE("engine: download kernel launch failed (cuda error %d)", rc);
+                    return MM_ERR_CUDA;
+                }
+                if (rc < 0)
+                    for (uint32_t j = 0; j < pending; j++)
+                        MM_CHECK(mm_d2h_async(dst[j], src[j], len[j], MM_ST_XFER));
+                pending = 0;
+            }
         }
     }
     return MM_OK;

@@ -40,10 +40,10 @@ __global__ void __launch_bounds__(256) host_gather_kernel(const __grid_constant_
 } // namespace mmb
 
 /* Returns 0 when the kernel was enqueued for all n buffers, -1 when some buffer
- * cannot be read by the device this way (nothing enqueued: use copies), else a
- * cudaError_t. */
-extern "C" int mmb_launch_host_gather(const void *const *src_host, void *const *dst_dev,
-                                      const size_t *bytes, uint32_t n, void *stream)
+ * cannot be reached by the device this way (nothing enqueued: use copies), else
+ * a cudaError_t.  to_host: the host side is the destination (download). */
+static int launch_copy_list(const void *const *src, void *const *dst, const size_t *bytes, uint32_t n,
+                            bool to_host, void *stream)
 {
     if (n == 0)
         return 0;
@@ -54,21 +54,36 @@ extern "C" int mmb_launch_host_gather(const void *const *src_host, void *const *
     uint32_t longest = 0;
     for (uint32_t i = 0; i < n; i++) {
         void *dptr = nullptr;
-        if ((reinterpret_cast<uintptr_t>(src_host[i]) & 15u) || (reinterpret_cast<uintptr_t>(dst_dev[i]) & 15u) ||
+        void *host = to_host ? dst[i] : const_cast<void *>(src[i]);
+        if ((reinterpret_cast<uintptr_t>(src[i]) & 15u) || (reinterpret_cast<uintptr_t>(dst[i]) & 15u) ||
             (bytes[i] & 15u) || bytes[i] > (static_cast<size_t>(1) << 35))
             return -1;
-        if (cudaHostGetDevicePointer(&dptr, const_cast<void *>(src_host[i]), 0) != cudaSuccess || !dptr) {
+        if (cudaHostGetDevicePointer(&dptr, host, 0) != cudaSuccess || !dptr) {
             (void)cudaGetLastError();
             return -1;
         }
-        l.src[i] = static_cast<const uint4 *>(dptr);
-        l.dst[i] = static_cast<uint4 *>(dst_dev[i]);
+        l.src[i] = static_cast<const uint4 *>(to_host ? src[i] : dptr);
+        l.dst[i] = static_cast<uint4 *>(to_host ? dptr : dst[i]);
         l.n16[i] = static_cast<uint32_t>(bytes[i] >> 4);
         if (l.n16[i] > longest) longest = l.n16[i];
     }
     uint32_t bx = (longest + 255u) / 256u;
-    if (bx > 16u) bx = 16u;                    /* 4096 loads of 16 bytes in flight per buffer */
+    if (bx > 16u) bx = 16u;                    /* 4096 transfers of 16 bytes in flight per buffer */
     if (bx < 1u) bx = 1u;
     mmb::host_gather_kernel<<<dim3(bx, n), 256, 0, static_cast<cudaStream_t>(stream)>>>(l);
     return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mmb_launch_host_gather(const void *const *src_host, void *const *dst_dev,
+                                      const size_t *bytes, uint32_t n, void *stream)
+{
+    return launch_copy_list(src_host, dst_dev, bytes, n, false, stream);
+}
+
+/* The other direction: the step's outputs written into pinned host buffers by one
+ * kernel (posted writes over PCIe) instead of one copy node per output. */
+extern "C" int mmb_launch_host_scatter(const void *const *src_dev, void *const *dst_host,
+                                       const size_t *bytes, uint32_t n, void *stream)
+{
+    return launch_copy_list(src_dev, dst_host, bytes, n, true, stream);
 }

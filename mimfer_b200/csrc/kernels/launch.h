@@ -201,6 +201,8 @@ int mmb_launch_mx(const mmb_args *a, void *stream);
 #define MMB_GATHER_MAX 32u
 int mmb_launch_host_gather(const void *const *src_host, void *const *dst_dev, const size_t *bytes,
                            uint32_t n, void *stream);
+int mmb_launch_host_scatter(const void *const *src_dev, void *const *dst_host, const size_t *bytes,
+                            uint32_t n, void *stream);
 int mmb_launch_tp_barrier(unsigned *const *flags, uint32_t n_ranks, uint32_t rank, void *stream);
 int mmb_launch_silu_mul(const void *gate, const void *up, void *y, size_t n, void *stream);
 int mmb_launch_add_rmsnorm(void *res, const void *delta, void *y, const void *gain, uint32_t M, uint32_t H,

@@ -11,10 +11,20 @@ mode="fused" removes the separate exchange: every rank's full output lives in
 symmetric memory, and the kernel's epilogue stores each finished tile into all
 ranks' copies through peer-mapped pointers (plain stores over NVLink, no
 multicast), so the transfer overlaps the remaining tiles; one cross-rank barrier
-kernel of this library (bounded wait) on the stream closes the op.  The reference has no multi-GPU path; this is new
-surface.
+kernel of this library (a bounded device-side spin on flags in symmetric memory)
+on the stream closes the op.  The full outputs are double-buffered: call i of a
+linear writes buffer i % 2 on every rank, so a rank that runs ahead into the next
+step never overwrites an output a slower rank is still reading - it cannot reach
+the step after that before the slower rank has arrived at the barrier in between,
+which that rank enqueues after its reads.  The reference has no multi-GPU path;
+this is new surface.
 """
 import ctypes as C
+import os
+
+# The kernels store to peers with plain stores: the symmetric buffers need no NVLink
+# multicast binding, and a rank that dies while bound to one disturbs the other GPUs.
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 from . import _lib as L
 import torch
@@ -90,15 +100,22 @@ class TpLinear:
         return self._bufs[M]
 
     def _symm_buffers(self, M, like):
-        """Full output in symmetric memory + the pointer table (own copy first)."""
+        """Full output in symmetric memory + the pointer table (own copy first): two
+        sets per M, taken in turn by successive calls (every rank makes the same calls)."""
         if M not in self._symm:
             import torch.distributed._symmetric_memory as symm_mem
-            y = symm_mem.empty((M, self.N), dtype=like.dtype, device=like.device)
-            hdl = symm_mem.rendezvous(y, self.group if self.group is not None else dist.group.WORLD)
-            order = [self.rank] + [r for r in range(self.world) if r != self.rank]
-            ptrs = (C.c_void_p * self.world)(*[hdl.buffer_ptrs[r] for r in order])
-            self._symm[M] = (y, hdl, ptrs)
-        return self._symm[M]
+            sets = []
+            for _ in range(2):
+                y = symm_mem.empty((M, self.N), dtype=like.dtype, device=like.device)
+                hdl = symm_mem.rendezvous(y, self.group if self.group is not None else dist.group.WORLD)
+                order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+                ptrs = (C.c_void_p * self.world)(*[hdl.buffer_ptrs[r] for r in order])
+                sets.append((y, hdl, ptrs))
+            self._symm[M] = [sets, 0]
+        entry = self._symm[M]
+        chosen = entry[0][entry[1] % 2]
+        entry[1] += 1
+        return chosen
 
     def barrier(self):
         """Cross-rank barrier on the compute stream: after it, every rank's copy of
@@ -163,9 +180,11 @@ class TpStep:
     i plus the closing cross-rank barrier on the runtime's compute stream and
     replays them with one launch.  Fused mode only when there is more than one
     rank (the kernels' peer stores and one barrier kernel; no NCCL call is
-    captured).  The activations are read from the same device tensors `xs` on
-    every replay: refill them in place.  Outputs: `self.ys`, complete on every
-    rank once the replay has finished."""
+    captured).  Two graphs are captured, one per set of output buffers, and
+    replayed in turn, so that consecutive steps never write the same buffers.
+    The activations are read from the same device tensors `xs` on every replay:
+    refill them in place.  Outputs: what replay() returns, complete on every
+    rank once the replay has finished and valid until the replay after the next."""
 
     def __init__(self, lins, xs):
         if len(lins) != len(xs) or not lins:
@@ -183,9 +202,14 @@ class TpStep:
         if dist.is_initialized() and lins[0].world > 1:
             dist.barrier(group=lins[0].group)
         torch.cuda.synchronize()
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, stream=self.stream, capture_error_mode="thread_local"):
-            self.ys = self._issue()
+        self.graphs, self.outs, self.n_replays = [], [], 0
+        for _ in range(2):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=self.stream, capture_error_mode="thread_local"):
+                ys = self._issue()
+            self.graphs.append(g)
+            self.outs.append(ys)
+        self.ys = self.outs[0]
         if dist.is_initialized() and lins[0].world > 1:
             dist.barrier(group=lins[0].group)     # the barrier kernel's wait is bounded: replay together
         torch.cuda.synchronize()
@@ -196,6 +220,9 @@ class TpStep:
         return ys
 
     def replay(self):
+        k = self.n_replays % 2
+        self.n_replays += 1
         with torch.cuda.stream(self.stream):
-            self.graph.replay()
+            self.graphs[k].replay()
+        self.ys = self.outs[k]
         return self.ys

@@ -78,3 +78,21 @@ def test_generator_statistics_and_row_independence(lib):
     assert abs(a.mean()) < 0.01 and abs(a.std() - 1.0) < 0.01
     b = fill_normal(32, 4096, 9, 0.0, 1.0)
     assert np.array_equal(a[:32], b)                           # rows do not depend on the row count
+
+
+def test_host_only_packer_of_the_cpu_arm_matches(lib):
+    """oracle/inputs.py (numpy, used where the product library must not be loaded) packs
+    the same bytes as mm_f4_pack, ties and zero blocks included, and rounds to bf16 alike."""
+    from oracle import inputs
+    rng = np.random.Generator(np.random.PCG64(3))
+    W = rng.standard_normal((96, 512), dtype=np.float32) * np.float32(0.02)
+    W[3, :32] = 0.0
+    W[5, 7] = 0.3
+    W[9, 16:32] = np.float32(0.02) * np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0,
+                                               -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -6.0], np.float32)
+    payload, scales, gs = inputs.pack(W)
+    w = mm.pack_weight(W)
+    assert np.array_equal(payload, w.payload) and np.array_equal(scales, w.scales) and gs == w.gs
+    x = rng.standard_normal((8, 256), dtype=np.float32) * np.float32(3.0)
+    x[0, :4] = [1.00390625, 1.01171875, -1.00390625, 3.0e-40]          # ties and a subnormal
+    assert np.array_equal(inputs.bf16_bits(x), mm.linear.f32_to_bf16(x))
