@@ -80,12 +80,13 @@ class Clocks:
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.proc, self.path = index, None, None
+        self.index, self.proc, self.path, self.t0 = index, None, None, None
 
     def __enter__(self):
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
+            self.t0 = time.time()
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
                  "--format=csv,noheader,nounits", "-lms", "200"],
@@ -101,6 +102,19 @@ class Clocks:
                 self.proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
+
+    def samples(self):
+        """(seconds since the sampler started, SM MHz, board W) per 200 ms sample."""
+        out = []
+        if not self.path or not os.path.exists(self.path):
+            return out
+        for i, line in enumerate(open(self.path)):
+            f = [x.strip() for x in line.split(",")]
+            try:
+                out.append((0.2 * i, float(f[0]), float(f[2])))
+            except (ValueError, IndexError):
+                continue
+        return out
 
     def summary(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "power_w_max": None, "samples": 0}
@@ -505,6 +519,44 @@ class Bench:
         self.rt.lib.mm_f4_tune(5, 1)
         return {"rows": rows}
 
+    def decode_sustained(self, secs=4.0, chunk=50):
+        """The decode sweep replayed for `secs` seconds in chunks of `chunk` steps, each chunk
+        timed with CUDA events, SM clock and board power sampled every 200 ms beside it: step
+        time binned by the clock the chunk ran at.  Shows whether the time follows the clock
+        (an SM-side bound), the power cap, or neither (memory-side)."""
+        _, ops, eng = self.decode_sweep(5, 3, repeats=1, other_orders=False)
+        wb = sum(wbytes(w.K, w.N) for _, w, _ in ops)
+        torch = self.torch
+        stream = self.rt.torch_stream()
+        marks, stamps = [], []
+        with Clocks(self.local) as clk:
+            t0 = time.time()
+            with torch.cuda.stream(stream):
+                while time.time() - t0 < secs:
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(stream)
+                    for _ in range(chunk):
+                        eng.launch()
+                    b.record(stream)
+                    b.synchronize()
+                    marks.append(a.elapsed_time(b) / chunk)
+                    stamps.append(time.time() - t0)
+        samples = clk.samples()          # (seconds since start, sm MHz, watts)
+        eng.close()
+        bins = {}
+        for t, ms in zip(stamps, marks):
+            near = min(samples, key=lambda q: abs(q[0] - t)) if samples else (0.0, 0.0, 0.0)
+            key = int(round(near[1] / 30.0) * 30)
+            bins.setdefault(key, []).append((ms, near[2]))
+        rows = [{"sm_mhz": k, "chunks": len(v), "us_per_step": round(statistics.median(m for m, _ in v) * 1e3, 2),
+                 "weight_gbs": round(wb / statistics.median(m for m, _ in v) / 1e6),
+                 "us_x_ghz": round(statistics.median(m for m, _ in v) * k, 1),
+                 "board_w": round(statistics.median(w for _, w in v))} for k, v in sorted(bins.items())]
+        return {"seconds": secs, "chunk_steps": chunk, "chunks": len(marks),
+                "us_per_step_median": round(statistics.median(marks) * 1e3, 2),
+                "us_per_step_first": round(marks[0] * 1e3, 2), "us_per_step_last": round(marks[-1] * 1e3, 2),
+                "by_clock": rows, "reasons": clk.summary()["reasons"]}
+
     def _shard_rows(self, name):
         per = SHAPES[name][1] // self.world
         return (self.rank * per, (self.rank + 1) * per)
@@ -839,6 +891,8 @@ def run_case(b, case, steps, warmup):
         res, _, eng = b.decode_sweep(steps, warmup, repeats=1, other_orders=False)
         eng.close()
         return res
+    if case == "sustained":        # the sweep for four seconds, step time binned by SM clock
+        return b.decode_sustained()
     if case == "decode_parts":     # the decode kernel's time split into stream / arithmetic / exchange
         return b.decode_parts()
     if case == "e2e":              # the default sweep and its host-buffer step

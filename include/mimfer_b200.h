@@ -334,6 +334,10 @@ mm_status mm_f4_wait_selftest(unsigned *done_dev);
  *   key 3  K slices of the decode kernels (0 = the planner's choice)
  *   key 5  decode ops on the block-scaled tensor kernel (1, default) or on the
  *          CUDA-core streaming kernel (0)
+ *   key 6  cap on the pipeline stages of a group launch (0 = as many as fit, default)
+ *   key 7  group launches carry a persisting L2 access-policy window over the digit
+ *          planes of their activations (0 = off, default; sets the context's persisting
+ *          L2 carve-out to 32 MiB on first use)
  * Key 4 (measurement modes that skip loads, arithmetic or the split-K exchange)
  * exists only in a library built with -DMMB_MEASURE_MODES. */
 int mm_f4_tune(int key, int value);

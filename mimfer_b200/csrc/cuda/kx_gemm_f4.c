@@ -44,6 +44,9 @@ static struct {
     int        next_share_x;     /* the next op reads the activations the op before it sliced */
     void      *next_planes;      /* the next op's digit planes are already there (plane cache) */
     int        use_mx;           /* decode ops take the block-scaled tensor path when they can */
+    uint32_t   mx_stages;        /* cap on the pipeline depth of a group launch (0 = what fits) */
+    int        l2_window;        /* group launches carry a persisting L2 window over the workspace */
+    int        l2_limit_set;
     /* the digit planes made last: which activations, and where they lie */
     const void *sliced_x;
     uint32_t   sliced_M, sliced_K;
@@ -197,6 +200,8 @@ int mm_f4_tune(int key, int value)
     if (key == 4) { int old = (int)G.st_dbg; G.st_dbg = (uint32_t)value; return old; }
 #endif
     if (key == 5) { int old = G.use_mx; G.use_mx = value ? 1 : 0; return old; }
+    if (key == 6) { int old = (int)G.mx_stages; G.mx_stages = (uint32_t)value; return old; }
+    if (key == 7) { int old = G.l2_window; G.l2_window = value ? 1 : 0; return old; }
     return -1;
 }
 
@@ -238,6 +243,7 @@ void mmb_launcher_reset(void)
     G.next_pdl = -1;
     G.next_region = 0;
     G.next_shallow = 0;
+    G.l2_limit_set = 0;
 }
 
 static mm_status ensure_ready(void)
@@ -862,17 +868,39 @@ mm_status mmb_group_launch(void)
     gg->n_ops = GR.n;
     uint32_t st = (MMB_SMEM_MAX - MMB_MXG_FIXED_B) / gg->stage_b;
     if (st > 6) st = 6;
+    if (G.mx_stages && st > G.mx_stages) st = G.mx_stages;
     if (st < 2) st = 2;
     gg->stages = st;
     gg->smem_bytes = st * gg->stage_b + MMB_MXG_FIXED_B;
     gg->grid = gg->n_units < (uint32_t)G.sm_count ? gg->n_units : (uint32_t)G.sm_count;
-    int err = mmb_launch_mxg(gg, mm_cuda_stream_raw(MM_ST_COMPUTE));
+    if (G.l2_window && G.ws) {
+        /* window over the plane cache half of the workspace + this group's region */
+        int dev = 0, max_win = 0, max_persist = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&max_win, cudaDevAttrMaxAccessPolicyWindowSize, dev);
+        cudaDeviceGetAttribute(&max_persist, cudaDevAttrMaxPersistingL2CacheSize, dev);
+        size_t want = cache_used + 4096u;
+        if (want > (size_t)max_win) want = (size_t)max_win;
+        if (!G.l2_limit_set && max_persist > 0) {
+            size_t lim = (size_t)max_persist < ((size_t)32 << 20) ? (size_t)max_persist : ((size_t)32 << 20);
+            if (cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, lim) == cudaSuccess)
+                G.l2_limit_set = 1;
+            else
+                (void)cudaGetLastError();
+        }
+        if (G.l2_limit_set && want) {
+            gg->l2_base = cache;
+            gg->l2_bytes = want;
+        }
+    }
+    uint32_t kernels = 0;
+    int err = mmb_launch_mxg(gg, mm_cuda_stream_raw(MM_ST_COMPUTE), &kernels);
     if (err) {
         MM_LOGE("cuda: group launch (%u ops, %u units): %s", gg->n_ops, gg->n_units,
                 cudaGetErrorString((cudaError_t)err));
         return MM_ERR_CUDA;
     }
-    G.launches += 1u + (sliced ? 2u : 0u);
+    G.launches += kernels;
     G.sliced_x = NULL;
     return finish_op();
 }

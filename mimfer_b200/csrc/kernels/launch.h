@@ -185,10 +185,12 @@ typedef struct mmb_gop {
 typedef struct mmb_group {
     uint32_t n_ops, n_units, stages, acc_bufs, stage_b, smem_bytes, grid;
     int      pdl;
+    void    *l2_base;        /* persisting L2 access window over the scratch (planes, partials); NULL = none */
+    size_t   l2_bytes;
     mmb_gop  op[MMB_MXG_MAX_OPS];
 } mmb_group;
 
-int mmb_launch_mxg(const mmb_group *g, void *stream);
+int mmb_launch_mxg(const mmb_group *g, void *stream, uint32_t *kernels_launched);
 
 /* Each returns a cudaError_t value (0 = success) from the launch. `stream`
  * is a cudaStream_t. */

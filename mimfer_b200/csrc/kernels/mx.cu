@@ -580,8 +580,15 @@ extern "C" int mmb_mx_init(void)
 }
 
 /* Digit planes of the activations into the op's scratch (a->mx_x_ws). */
+extern "C" int mmb_launch_xslice_rows(const void *x, void *scratch, uint32_t M, uint32_t K, uint32_t nb, int pdl,
+                                      void *stream);
+
 extern "C" int mmb_launch_xslice(const mmb_args *a, void *stream)
 {
+    /* rows up to 32768 long: one pass over the activations, a cluster per row */
+    const int rc = mmb_launch_xslice_rows(a->x, a->mx_x_ws, a->M, a->K, a->plan.tile_m, a->pdl, stream);
+    if (rc >= 0)
+        return rc;
     mmb::XsliceParams p;
     unsigned char *xs = static_cast<unsigned char *>(a->mx_x_ws);
     const uint32_t m_pad = a->plan.tile_m / MMB_MX_PLANES;

@@ -249,5 +249,93 @@ __device__ __forceinline__ void xslice_cta(const uint16_t *x, uint8_t *planes, u
     }
 }
 
+/* ---- one thread per 16-wide block ----------------------------------------------
+ * The slicing of xslice_cta with a whole block in one thread: no shuffles, two
+ * 16-byte loads, one 8-byte store per plane.  Row exponent and liveness come from
+ * the caller (row_amax: largest magnitude of the row as bf16 bits without sign). */
+struct RowFrame {
+    int  G;          /* 9 - floor(log2(row maximum)) */
+    bool finite;     /* no inf or NaN in the row */
+    bool any;        /* the row has a non-zero value */
+};
+
+__device__ __forceinline__ RowFrame row_frame(uint32_t row_amax)
+{
+    RowFrame f;
+    f.finite = row_amax < 0x7f80u;
+    f.any = row_amax != 0u;
+    int e_max = static_cast<int>(row_amax >> 7) - 127;
+    if ((row_amax >> 7) == 0)
+        e_max = row_amax ? (31 - __clz(row_amax)) - 133 : -126;
+    f.G = 9 - e_max;
+    return f;
+}
+
+__device__ __forceinline__ void row_factors(const RowFrame &f, float *row_scale, uint32_t m)
+{
+    const int g1 = f.G >> 1, g2 = f.G - g1;
+    float f1 = __int_as_float((127 - g1) << 23), f2 = __int_as_float((127 - g2) << 23);
+    if (!f.finite)
+        f1 = __int_as_float(0x7fc00000);                      /* a row with inf or NaN gives NaN outputs */
+    row_scale[2u * m] = f1;
+    row_scale[2u * m + 1u] = f2;
+}
+
+/* w[8]: the block's sixteen bf16 values, two per word; plane row n0 = 6 * m. */
+__device__ __forceinline__ void xslice_block(const uint32_t (&w)[8], const RowFrame &f, bool live, uint8_t *planes,
+                                             uint8_t *sfb, uint32_t K, uint32_t m, uint32_t blk)
+{
+    uint32_t bmax = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+        bmax = max(bmax, max(w[i] & 0x7fffu, (w[i] >> 16) & 0x7fffu));
+    live = live && f.finite && f.any;
+    int e_b = static_cast<int>(bmax >> 7) - 127;
+    if ((bmax >> 7) == 0)
+        e_b = bmax ? (31 - __clz(bmax)) - 133 : -200;
+    const int U = max(e_b - 16, -10 - f.G);
+    float R[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const uint32_t bits = live ? (w[i >> 1] >> (16 * (i & 1))) & 0xffffu : 0u;
+        const uint32_t ef = (bits >> 7) & 0xffu, mant = bits & 0x7fu;
+        const uint32_t sig = ef ? 128u + mant : mant;
+        const int e = ef ? static_cast<int>(ef) - 127 : -126;
+        const int sh = e - 7 - U;
+        uint32_t V;
+        if (sh >= 0)
+            V = sig << sh;
+        else
+            V = sh < -10 ? 0u : (sig + (1u << (-sh - 1))) >> (-sh);
+        const float r = static_cast<float>(V);
+        R[i] = (bits & 0x8000u) ? -r : r;
+    }
+    const uint32_t blocks = K / 16u;
+#pragma unroll
+    for (int q = MMB_MX_PLANES - 1; q >= 0; q--) {
+        const float wgt = __int_as_float((127 + mx_shift(q) + 1) << 23);
+        const float inv = __int_as_float((127 - mx_shift(q) - 1) << 23);
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            /* a byte of the plane: high nibble = odd column, low nibble = even column */
+            uint32_t byte, h2;
+            asm("{\n\t.reg .b8 q;\n\tcvt.rn.satfinite.e2m1x2.f32 q, %1, %2;\n\tmov.b32 %0, {q, q, q, q};\n\t}"
+                : "=r"(byte) : "f"(R[2 * j + 1] * inv), "f"(R[2 * j] * inv));
+            byte &= 0xffu;
+            asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\tmov.b32 {b0, b1, b2, b3}, %1;\n\t"
+                "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t}" : "=r"(h2) : "r"(byte));
+            const __half2 d = *reinterpret_cast<const __half2 *>(&h2);
+            R[2 * j] = fmaf(-__low2float(d), wgt, R[2 * j]);
+            R[2 * j + 1] = fmaf(-__high2float(d), wgt, R[2 * j + 1]);
+            if (j < 4) lo |= byte << (8 * j); else hi |= byte << (8 * (j - 4));
+        }
+        const size_t n = static_cast<size_t>(m) * MMB_MX_PLANES + q;
+        *reinterpret_cast<uint2 *>(planes + n * (K / 2u) + static_cast<size_t>(blk) * 8u) = make_uint2(lo, hi);
+        const int sfe = U + 1 + mx_shift(q) + f.G;
+        const uint32_t byte = live ? (sfe >= -6 ? static_cast<uint32_t>(sfe + 7) << 3 : 1u << (sfe + 9)) : 0u;
+        sfb[n * blocks + blk] = static_cast<uint8_t>(byte);
+    }
+}
 
 } // namespace mmb

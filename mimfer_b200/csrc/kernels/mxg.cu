@@ -28,6 +28,7 @@
  */
 #include "fp4.cuh"
 #include "ptx.cuh"
+#include <cooperative_groups.h>
 #include "mx.cuh"
 
 namespace mmb {
@@ -483,6 +484,7 @@ struct XsliceItem {
 struct XsliceGroup {
     uint32_t   n, pdl;
     XsliceItem item[MMB_MXG_MAX_OPS];
+    uint32_t   row0[MMB_MXG_MAX_OPS + 1];      /* first padded row of each tensor in the launch; [n] = all rows */
 };
 
 /* Two passes, so that a row is read twice and not once per chunk: chunk maxima,
@@ -515,6 +517,66 @@ f4_xslice_group_kernel(const __grid_constant__ XsliceGroup g)
                reinterpret_cast<float *>(it.scratch + MMB_MX_ROWSCALE_OFF), it.M, it.K, blockIdx.y, blockIdx.x,
                two_pass ? reinterpret_cast<const uint32_t *>(it.scratch + MMB_MX_CHUNKMAX_OFF) : nullptr);
 }
+
+/* One launch, one pass over the activations: a cluster of eight CTAs per (padded)
+ * activation row, 4096 values per CTA, one 16-wide block per thread.  Each CTA
+ * leaves the largest magnitude of its part in its shared memory; after a cluster
+ * barrier every CTA reads the eight values through distributed shared memory and
+ * slices its blocks.  Rows up to 32768 long; longer ones take the two-pass kernels. */
+#define MMB_XS_CLUSTER 8u
+#define MMB_XS_CTA_VALUES 4096u
+
+__global__ void __cluster_dims__(MMB_XS_CLUSTER, 1, 1) __launch_bounds__(256)
+f4_xslice_cluster_kernel(const __grid_constant__ XsliceGroup g)
+{
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ uint32_t s_warp[8];
+    __shared__ uint32_t s_part;                  /* this CTA's maximum, read by the whole cluster */
+    grid_dep_launch();
+    if (g.pdl != MMB_PDL_OFF)
+        grid_dep_wait();                         /* the activations are the previous kernel's output */
+    const uint32_t row = blockIdx.x / MMB_XS_CLUSTER, part = blockIdx.x % MMB_XS_CLUSTER;
+    uint32_t i = 0;
+    while (i + 1u < g.n && row >= g.row0[i + 1u]) i++;
+    const XsliceItem &it = g.item[i];
+    const uint32_t m = row - g.row0[i], tid = threadIdx.x;
+    const uint32_t blk = part * (MMB_XS_CTA_VALUES / 16u) + tid, blocks = it.K / 16u;
+    const bool in_row = blk < blocks, loaded = in_row && m < it.M;
+    uint32_t w[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) w[j] = 0u;
+    if (loaded) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(it.x + static_cast<size_t>(m) * it.K) + 2u * blk;
+        const uint4 a = __ldcg(src), b = __ldcg(src + 1);
+        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+    }
+    uint32_t amax = 0;
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+        amax = max(amax, max(w[j] & 0x7fffu, (w[j] >> 16) & 0x7fffu));
+    amax = __reduce_max_sync(0xffffffffu, amax);
+    if ((tid & 31u) == 0)
+        s_warp[tid >> 5] = amax;
+    __syncthreads();
+    if (tid == 0) {
+#pragma unroll
+        for (int j = 1; j < 8; j++) amax = max(amax, s_warp[j]);
+        s_part = amax;
+    }
+    cluster.sync();                              /* every part's maximum is in place */
+    uint32_t row_amax = 0;
+#pragma unroll
+    for (uint32_t r = 0; r < MMB_XS_CLUSTER; r++)
+        row_amax = max(row_amax, *cluster.map_shared_rank(&s_part, r));
+    cluster.sync();                              /* nobody leaves while its shared memory is still read */
+    const RowFrame f = row_frame(row_amax);
+    uint8_t *planes = it.scratch + MMB_MX_PLANES_OFF;
+    if (part == 0 && tid == 0 && m < it.M)
+        row_factors(f, reinterpret_cast<float *>(it.scratch + MMB_MX_ROWSCALE_OFF), m);
+    if (in_row)
+        xslice_block(w, f, loaded, planes, planes + MMB_MX_PLANES_B(it.nb, it.K), it.K, m, blk);
+}
 } // namespace mmb
 
 extern "C" int mmb_mxg_init(void)
@@ -523,8 +585,36 @@ extern "C" int mmb_mxg_init(void)
                                                  MMB_SMEM_MAX));
 }
 
-extern "C" int mmb_launch_mxg(const mmb_group *hg, void *stream)
+/* Digit planes of one activation tensor with the cluster kernel; -1 when the rows
+ * are too long for it (the caller then uses its own kernel). */
+extern "C" int mmb_launch_xslice_rows(const void *x, void *scratch, uint32_t M, uint32_t K, uint32_t nb, int pdl,
+                                      void *stream)
 {
+    if (K > MMB_XS_CLUSTER * MMB_XS_CTA_VALUES)
+        return -1;
+    static mmb::XsliceGroup xs;
+    memset(&xs, 0, sizeof xs);
+    xs.n = 1;
+    xs.pdl = static_cast<uint32_t>(pdl);
+    xs.item[0].x = static_cast<const uint16_t *>(x);
+    xs.item[0].scratch = static_cast<uint8_t *>(scratch);
+    xs.item[0].M = M; xs.item[0].K = K; xs.item[0].nb = nb; xs.item[0].m_pad = nb / MMB_MX_PLANES;
+    xs.row0[1] = xs.item[0].m_pad;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(xs.row0[1] * MMB_XS_CLUSTER);
+    cfg.blockDim = dim3(256);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, mmb::f4_xslice_cluster_kernel, xs));
+}
+
+extern "C" int mmb_launch_mxg(const mmb_group *hg, void *stream, uint32_t *kernels_launched)
+{
+    uint32_t launched = 0;
     static mmb::MxgGroup grp;            /* built in place: 30 KB is too much for the stack of a small thread */
     static mmb::XsliceGroup xs;
     unsigned *status = nullptr;
@@ -536,7 +626,7 @@ extern "C" int mmb_launch_mxg(const mmb_group *hg, void *stream)
     memset(&xs, 0, sizeof xs);
     grp.n_ops = hg->n_ops; grp.n_units = hg->n_units; grp.stages = hg->stages; grp.acc_bufs = hg->acc_bufs;
     grp.stage_b = hg->stage_b; grp.pdl = static_cast<uint32_t>(hg->pdl); grp.status = status;
-    uint32_t max_m = 0, max_kx = 0;
+    uint32_t max_m = 0, max_kx = 0, max_k = 0;
     for (uint32_t i = 0; i < hg->n_ops; i++) {
         const mmb_gop &s = hg->op[i];
         mmb::MxgOp &d = grp.ops[i];
@@ -554,12 +644,15 @@ extern "C" int mmb_launch_mxg(const mmb_group *hg, void *stream)
         d.unit0 = s.unit0;
         d.glu = s.glu ? 1u : 0u; d.gate_plane = s.gate_plane ? 1u : 0u;
         if (s.slice_here) {
-            mmb::XsliceItem &it = xs.item[xs.n++];
+            mmb::XsliceItem &it = xs.item[xs.n];
             it.x = static_cast<const uint16_t *>(s.x);
             it.scratch = static_cast<uint8_t *>(s.x_ws);
             it.M = s.M; it.K = s.K; it.nb = s.nb; it.m_pad = s.nb / MMB_MX_PLANES;
+            xs.row0[xs.n + 1u] = xs.row0[xs.n] + it.m_pad;
+            xs.n++;
             if (it.m_pad > max_m) max_m = it.m_pad;
             if ((s.K + 1023u) / 1024u > max_kx) max_kx = (s.K + 1023u) / 1024u;
+            if (s.K > max_k) max_k = s.K;
         }
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -569,14 +662,22 @@ extern "C" int mmb_launch_mxg(const mmb_group *hg, void *stream)
     if (xs.n) {
         xs.pdl = static_cast<uint32_t>(hg->pdl);
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(max_kx, max_m, xs.n);
         cfg.blockDim = dim3(256);
         cfg.stream = st;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        cudaError_t err = cudaLaunchKernelEx(&cfg, mmb::f4_xamax_group_kernel, xs);
-        if (err == cudaSuccess)
-            err = cudaLaunchKernelEx(&cfg, mmb::f4_xslice_group_kernel, xs);
+        cudaError_t err;
+        if (max_k <= MMB_XS_CLUSTER * MMB_XS_CTA_VALUES) {
+            cfg.gridDim = dim3(xs.row0[xs.n] * MMB_XS_CLUSTER);
+            err = cudaLaunchKernelEx(&cfg, mmb::f4_xslice_cluster_kernel, xs);
+            launched = 1;
+        } else {
+            cfg.gridDim = dim3(max_kx, max_m, xs.n);
+            err = cudaLaunchKernelEx(&cfg, mmb::f4_xamax_group_kernel, xs);
+            if (err == cudaSuccess)
+                err = cudaLaunchKernelEx(&cfg, mmb::f4_xslice_group_kernel, xs);
+            launched = 2;
+        }
         if (err != cudaSuccess)
             return static_cast<int>(err);
     }
@@ -585,7 +686,23 @@ extern "C" int mmb_launch_mxg(const mmb_group *hg, void *stream)
     cfg.blockDim = dim3(MMB_MXG_THREADS);
     cfg.dynamicSmemBytes = hg->smem_bytes;
     cfg.stream = st;
-    cfg.attrs = attr;
+    cudaLaunchAttribute gattr[2];
+    gattr[0] = attr[0];
+    cfg.attrs = gattr;
     cfg.numAttrs = 1;
+    if (hg->l2_base && hg->l2_bytes) {
+        /* the scratch every tile re-reads (digit planes, split-K partials) is kept in L2 in
+         * preference to the weights, which stream through once (the reference commits such
+         * windows with its graphs, src/cuda/cuda_rt.c:163-181) */
+        gattr[1].id = cudaLaunchAttributeAccessPolicyWindow;
+        gattr[1].val.accessPolicyWindow.base_ptr = hg->l2_base;
+        gattr[1].val.accessPolicyWindow.num_bytes = hg->l2_bytes;
+        gattr[1].val.accessPolicyWindow.hitRatio = 1.0f;
+        gattr[1].val.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
+        gattr[1].val.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
+        cfg.numAttrs = 2;
+    }
+    if (kernels_launched)
+        *kernels_launched = launched + 1u;
     return static_cast<int>(cudaLaunchKernelEx(&cfg, mmb::f4_mxg_kernel, grp));
 }
