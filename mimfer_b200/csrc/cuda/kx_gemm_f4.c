@@ -1073,6 +1073,9 @@ mm_status kx_op_add_rmsnorm(const mm_kcall *kc)
     return finish_op();
 }
 
+/* Inside the mimfer tree the dispatcher (src/kernels/kx.c) and the op preference
+ * table (src/kernels/cuda/cx.cu) are mimfer's own: build with -DMMB_NO_DISPATCHER. */
+#ifndef MMB_NO_DISPATCHER
 int kx_cuda_oppref(int op)
 {
     return op == OP_GEMM_F4 || op == OP_QKV || op == OP_LMHEAD || op == OP_SILU_MUL ||
@@ -1095,6 +1098,7 @@ mm_status mm_kx_invoke(const mm_kcall *kc)
         return MM_ERR_UNSUPPORTED;
     }
 }
+#endif /* MMB_NO_DISPATCHER */
 
 mm_status mm_f4_linear_host(const void *x_host, void *x_dev, const void *payload_dev,
                             const void *scale_dev, float gs, void *y_dev, void *y_host,
