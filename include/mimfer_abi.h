@@ -17,7 +17,7 @@
  *   mm_dtype      include/mimfer/tensor.h:33-42
  *   mm_stream_id  include/mimfer/cuda_rt.h:32-36
  *
- * tests/test_abi_layout.py compiles this header next to the reference's own
+ * tests/test_abi.py compiles this header next to the reference's own
  * headers (when the reference tree is mounted) and compares every sizeof and
  * offsetof; the _Static_asserts below pin the same numbers for builds without
  * the mount.

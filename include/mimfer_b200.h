@@ -154,11 +154,13 @@ typedef struct mm_f4_shape {
 typedef struct mm_f4_plan {
     int      variant;         /* mm_f4_variant                                */
     uint32_t m_tiles;         /* STREAM: 8-row activation tiles (1 to 4); MX: */
-                              /*   groups of four activation rows (1 to 8)    */
+                              /*   groups of four activation rows (1 to 8);   */
+                              /*   UMMA: tiles of the last, partial wave that */
+                              /*   are cut into split_k K slices (0 = none)   */
     uint32_t tile_m, tile_n;  /* UMMA: CTA tile; STREAM/MX: tile_n =  */
                               /*   W rows per CTA, tile_m = padded activation */
                               /*   rows (MX: digit-plane rows, 24 per group)  */
-    uint32_t split_k;         /* >= 1                                         */
+    uint32_t split_k;         /* >= 1; UMMA: slices of each of those tiles    */
     uint32_t k_steps;         /* K / 256 (STREAM) or K / 64 (UMMA)            */
     uint32_t stages;          /* smem pipeline depth                          */
     uint32_t grid_x, grid_y, grid_z;
@@ -335,6 +337,8 @@ mm_status mm_f4_wait_selftest(unsigned *done_dev);
  *   key 5  decode ops on the block-scaled tensor kernel (1, default) or on the
  *          CUDA-core streaming kernel (0)
  *   key 6  cap on the pipeline stages of a group launch (0 = as many as fit, default)
+ *   key 8  the prefill kernel cuts the tiles of its last, partial wave into K slices
+ *          (1, default) or runs them whole (0)
  *   key 7  group launches carry a persisting L2 access-policy window over the digit
  *          planes of their activations (0 = off, default; sets the context's persisting
  *          L2 carve-out to 32 MiB on first use)

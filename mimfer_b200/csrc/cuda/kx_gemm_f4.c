@@ -47,6 +47,7 @@ static struct {
     uint32_t   mx_stages;        /* cap on the pipeline depth of a group launch (0 = what fits) */
     int        l2_window;        /* group launches carry a persisting L2 window over the workspace */
     int        l2_limit_set;
+    int        no_tail_split;    /* prefill tiles of the last wave run whole */
     /* the digit planes made last: which activations, and where they lie */
     const void *sliced_x;
     uint32_t   sliced_M, sliced_K;
@@ -202,6 +203,7 @@ int mm_f4_tune(int key, int value)
     if (key == 5) { int old = G.use_mx; G.use_mx = value ? 1 : 0; return old; }
     if (key == 6) { int old = (int)G.mx_stages; G.mx_stages = (uint32_t)value; return old; }
     if (key == 7) { int old = G.l2_window; G.l2_window = value ? 1 : 0; return old; }
+    if (key == 8) { int old = !G.no_tail_split; G.no_tail_split = value ? 0 : 1; return old; }
     return -1;
 }
 
@@ -367,6 +369,11 @@ static mm_status plan_linear(const void *x, const void *payload, const void *sca
                                          : mm_f4_select(&sh, plan);
     if (st == MM_OK && plan->variant == MM_F4_V_MX && G.forced_variant < 0 && !G.use_mx)
         st = mm_f4_select_variant(&sh, MM_F4_V_STREAM, plan);     /* tuning key 5 = 0: the CUDA-core kernel */
+    if (st == MM_OK && plan->variant == MM_F4_V_UMMA && G.no_tail_split) {
+        plan->split_k = 1;
+        plan->m_tiles = 0;
+        plan->ws_needed = 0;
+    }
     if (st == MM_OK && plan->variant == MM_F4_V_STREAM && (G.st_rows || G.st_split))
         return mmb_plan_stream_with(&sh, G.st_rows, G.st_split, plan);
     if (st == MM_OK && plan->variant == MM_F4_V_MX && (G.st_rows || G.st_split))
@@ -485,6 +492,8 @@ static mm_status linear_impl(const void *x, const void *payload, const void *sca
         MM_CHECK(encode_2d(a.tm_scale, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, scale, K / 16, N, 16,
                            a.plan.tile_n, CU_TENSOR_MAP_SWIZZLE_NONE));
         err = mmb_launch_umma(&a, stream);
+        if (!err && a.plan.split_k > 1 && a.plan.m_tiles && a.ws)
+            G.launches++;                  /* the tail kernel of the split tiles */
         break;
     default:
         return MM_ERR_UNSUPPORTED;

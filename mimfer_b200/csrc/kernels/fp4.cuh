@@ -94,9 +94,10 @@ __device__ __forceinline__ uint4 unpack8_natural(uint32_t w, uint32_t c)
  * scales and the e2m1 x e4m3 products (at most 6 significant bits, magnitude
  * 2^-10 .. 2688) are exact fp16 normals, so one packed fp16 multiply by the
  * scale entry gives the dequantised weight exactly, with no exponent offset.
- * Not used by the MMA kernels: tcgen05 kind::f16 wants both operands in one
- * format and the activations are bf16.  Kept, with its probe, as the verified
- * building block for an fp16-activation path. */
+ * This is the main path of the CUDA-core decode kernel (stream.cu): a K step whose
+ * activations all convert to fp16 exactly takes it.  The prefill kernel cannot:
+ * tcgen05 kind::f16 wants both operands in one format and its activations stay
+ * bf16. */
 __device__ __forceinline__ uint32_t scale_lut_entry_f16(uint32_t b)
 {
     const __half h = __float2half_rn(e4m3_f32(b));                 /* exact */

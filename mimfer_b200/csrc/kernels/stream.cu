@@ -1,7 +1,10 @@
 /*
- * STREAM: the decode kernel of the NVFP4 linear op (M <= 32, HBM-bound).
+ * STREAM: the CUDA-core decode kernel of the NVFP4 linear op (M <= 32); the
+ * selector prefers the block-scaled tensor kernel (mx.cu) and falls back to this
+ * one when the activations' digit planes do not fit the workspace.
  *
- * One CTA owns 256 weight rows and a contiguous range of 256-wide K steps.
+ * One CTA owns the plan's number of weight rows (256; 128 for weights with few
+ * rows; any multiple of 16 runs) and a contiguous range of 256-wide K steps.
  * One thread keeps a ring of stages full by TMA: per step a box of packed
  * payload (256 rows x 128 B, 128-byte swizzle), one of block scales (256 rows
  * x 16 B) and the matching slice of the activations (up to 32 rows x 512 B).

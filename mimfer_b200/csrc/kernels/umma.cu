@@ -22,6 +22,15 @@
  * (BN rows), so accumulator lane = activation row and column = output
  * feature, which makes the epilogue's rows contiguous in y.
  *
+ * Tail split.  Tiles are numbered activation tile fastest and one CTA takes one
+ * tile, so a launch runs in waves of one CTA per SM.  The tiles of the last,
+ * partial wave (plan.m_tiles of them) are cut into plan.split_k K slices each, a
+ * CTA per slice, so that the tail fills the SMs too: a slice leaves its fp32
+ * sums in the workspace and a second, small kernel (f4_umma_tail_kernel, the whole
+ * GPU on a few tens of MB) adds the slices of every split tile in ascending order
+ * and writes the outputs.  One CTA cannot do that addition at the end of the main
+ * kernel: an SM takes in about 60 GB/s, i.e. 4 us per 256 KB slice.
+ *
  * It replaces the one-thread-per-output kernel of the reference
  * (src/kernels/cuda/cx.cu:345-356) for the prefill regime; the design the
  * reference only sketches is "dequant + bf16 mma gemm"
@@ -43,7 +52,12 @@ struct UmmaParams {
     uint32_t  pdl;           /* MMB_PDL_* (INDEPENDENT is served as WAIT_FIRST)  */
     float     gs_up;         /* gated pair: scale of the up projection          */
     uint32_t  gate_plane;    /* gated pair: which half of the weight tile is the gate */
+    uint32_t  m_tiles;       /* activation-row tiles (tile id = n_tile * m_tiles + m_tile) */
+    uint32_t  full_tiles;    /* tiles that run whole; the ones after them are split      */
+    uint32_t  splits;        /* K slices of every tile after full_tiles (>= 1)           */
+    float    *partial;       /* [split tile][slice][BM][BN] fp32 sums                    */
 };
+
 
 /* One weight box.  Gated pair: a 3-D box brings BN/2 rows of each projection,
  * plane 0 first, so accumulator columns [0, BN/2) belong to plane 0. */
@@ -96,8 +110,18 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
     static_assert(!GLU || BN == 256, "the gated pair runs on 256-row weight tiles");
     /* n0: first weight row of the tile (of each projection, and the first output
      * column, for a gated pair) */
-    const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * (GLU ? BN / 2 : BN);
-    const uint32_t KB = p.k_blocks;
+    uint32_t tile = blockIdx.x, slice = 0, n_slices = 1;
+    if (tile >= p.full_tiles) {
+        const uint32_t e = tile - p.full_tiles;
+        tile = p.full_tiles + e / p.splits;
+        slice = e % p.splits;
+        n_slices = p.splits;
+    }
+    const uint32_t m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * (GLU ? BN / 2 : BN);
+    /* this CTA's K blocks [kb0, kb0 + KB): slices are cut at 256-wide K groups (one scale box) */
+    const uint32_t groups = p.k_blocks / 4u;
+    const uint32_t kb0 = n_slices > 1 ? 4u * (groups * slice / n_slices) : 0u;
+    const uint32_t KB = (n_slices > 1 ? 4u * (groups * (slice + 1u) / n_slices) : p.k_blocks) - kb0;
     const uint32_t pre_pay = KB < PAY_SLOTS ? KB : PAY_SLOTS;   /* payload boxes issued in the prologue */
 
     if (tid < 256u)
@@ -125,10 +149,10 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
         tma_prefetch_desc(&tm_scale);
         for (uint32_t kb = 0; kb < pre_pay; kb++) {
             mbar_expect_tx(full_pay + 8u * kb, PAY_B);
-            load_w<GLU>(sm_pay + kb * PAY_B, &tm_payload, kb * 32u, n0, full_pay + 8u * kb);
+            load_w<GLU>(sm_pay + kb * PAY_B, &tm_payload, (kb0 + kb) * 32u, n0, full_pay + 8u * kb);
         }
         mbar_expect_tx(full_sc, SC_B);
-        load_w<GLU>(sm_sc, &tm_scale, 0u, n0, full_sc);
+        load_w<GLU>(sm_sc, &tm_scale, (kb0 >> 2) * 16u, n0, full_sc);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, TMEM_COLS);
@@ -158,17 +182,17 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
                     if (grp >= MMB_UM_SC_SLOTS)
                         mbar_wait(empty_sc + 8u * ss, ((grp / MMB_UM_SC_SLOTS) - 1u) & 1u, p.status);
                     mbar_expect_tx(full_sc + 8u * ss, SC_B);
-                    load_w<GLU>(sm_sc + ss * SC_B, &tm_scale, grp * 16u, n0, full_sc + 8u * ss);
+                    load_w<GLU>(sm_sc + ss * SC_B, &tm_scale, ((kb0 >> 2) + grp) * 16u, n0, full_sc + 8u * ss);
                 }
                 if (kb >= pre_pay) {
                     mbar_wait(empty_pay + 8u * ps, ((kb / PAY_SLOTS) - 1u) & 1u, p.status);
                     mbar_expect_tx(full_pay + 8u * ps, PAY_B);
-                    load_w<GLU>(sm_pay + ps * PAY_B, &tm_payload, kb * 32u, n0, full_pay + 8u * ps);
+                    load_w<GLU>(sm_pay + ps * PAY_B, &tm_payload, (kb0 + kb) * 32u, n0, full_pay + 8u * ps);
                 }
                 if (round > 0)
                     mbar_wait(empty_ab + 8u * s, (round - 1u) & 1u, p.status);
                 mbar_expect_tx(full_a + 8u * s, A_B);
-                tma_load_2d(sm_a + s * A_B, &tm_x, static_cast<int>(kb * MMB_UM_KBLOCK),
+                tma_load_2d(sm_a + s * A_B, &tm_x, static_cast<int>((kb0 + kb) * MMB_UM_KBLOCK),
                             static_cast<int>(m0), full_a + 8u * s);
             }
         }
@@ -244,7 +268,31 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
         const float out_scale = p.gs * 256.0f;      /* undo the 2^-8 of the operand form */
         const uint32_t quad = warp & 3u;            /* TMEM lanes this warp may read   */
         const uint32_t pair = (warp - 2u) >> 2;     /* two warps share a quadrant       */
-        if constexpr (GLU) {
+        constexpr uint32_t TILE_F = BM * BN;        /* fp32 sums of one K slice         */
+        const bool emit = n_slices == 1;
+        if (!emit) {
+            /* K slice of a split tile: leave the sums in the workspace (this warp's
+             * quadrant of both halves, its half of the columns); the tail kernel adds
+             * the slices and writes the output */
+            const uint32_t st_idx = tile - p.full_tiles;
+            float *mine = p.partial + (static_cast<size_t>(st_idx) * n_slices + slice) * TILE_F;
+            for (uint32_t h = 0; h < HALVES; h++) {
+                const uint32_t row = h * 128u + quad * 32u + lane;
+                for (uint32_t c32 = pair * (BN / 64u); c32 < (pair + 1u) * (BN / 64u); c32++) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + h * BN + c32 * 32u, r);
+                    tmem_ld_wait();
+                    float4 *dst = reinterpret_cast<float4 *>(mine + static_cast<size_t>(row) * BN + c32 * 32u);
+#pragma unroll
+                    for (int j = 0; j < 8; j++)
+                        __stcg(dst + j, make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                    __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+                }
+            }
+        }
+        if (!emit) {
+            /* nothing to write: another CTA finishes this tile */
+        } else if constexpr (GLU) {
             /* Gated pair: pieces of 32 rows x 64 outputs.  Gate and up sums of an
              * output sit 128 columns apart in the same lane; silu(gate) * up on
              * their bf16 roundings, staged, then 128-byte row runs go out, four
@@ -359,10 +407,91 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
     }
 }
 
+/* ---- the split tiles' outputs ----------------------------------------------------
+ * Every thread owns eight output columns of one row of one split tile: it adds the
+ * K slices' sums in ascending order (two 16-byte loads per slice, or four for a
+ * gated pair, several slices in flight), applies the epilogue of the main kernel
+ * and stores 16 bytes to every destination. */
+struct UmmaTailParams {
+    uint16_t    *y[MMB_MAX_PEERS];
+    uint32_t     n_dst, ldy, col0;
+    const float *partial;
+    float        gs, gs_up;
+    uint32_t     gate_plane, glu;
+    uint32_t     M, N;
+    uint32_t     bm, bn;            /* tile */
+    uint32_t     m_tiles, full_tiles, splits, pdl;
+};
+
+__global__ void __launch_bounds__(256) f4_umma_tail_kernel(const UmmaTailParams p)
+{
+    grid_dep_launch();
+    if (p.pdl != MMB_PDL_OFF)
+        grid_dep_wait();                         /* the main kernel's partial sums */
+    const uint32_t out_cols = p.glu ? p.bn / 2u : p.bn;
+    const uint32_t per_row = out_cols / 8u;                    /* threads per row: 16 or 32 */
+    const uint32_t rows_per_cta = 256u / per_row;
+    const uint32_t st_idx = blockIdx.y, tile = p.full_tiles + st_idx;
+    const uint32_t row = blockIdx.x * rows_per_cta + threadIdx.x / per_row;
+    const uint32_t c8 = (threadIdx.x % per_row) * 8u;           /* first of this thread's output columns */
+    const uint32_t m = (tile % p.m_tiles) * p.bm + row, n = (tile / p.m_tiles) * out_cols + c8;
+    if (row >= p.bm || m >= p.M || n >= p.N)
+        return;
+    const size_t tile_f = static_cast<size_t>(p.bm) * p.bn;
+    const float *src = p.partial + static_cast<size_t>(st_idx) * p.splits * tile_f + static_cast<size_t>(row) * p.bn;
+    const uint32_t col_a = p.glu ? (p.gate_plane ? p.bn / 2u : 0u) + c8 : c8;
+    const uint32_t col_b = p.glu ? (p.gate_plane ? 0u : p.bn / 2u) + c8 : c8;
+    float a[8], b[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) a[i] = b[i] = 0.0f;
+    for (uint32_t s0 = 0; s0 < p.splits; s0 += 4u) {
+        float4 va[4][2], vb[4][2];
+#pragma unroll
+        for (uint32_t j = 0; j < 4u; j++) {
+            const bool live = s0 + j < p.splits;
+            const float *base = src + static_cast<size_t>(live ? s0 + j : s0) * tile_f;
+            va[j][0] = __ldcg(reinterpret_cast<const float4 *>(base + col_a));
+            va[j][1] = __ldcg(reinterpret_cast<const float4 *>(base + col_a) + 1);
+            if (p.glu) {
+                vb[j][0] = __ldcg(reinterpret_cast<const float4 *>(base + col_b));
+                vb[j][1] = __ldcg(reinterpret_cast<const float4 *>(base + col_b) + 1);
+            } else {
+                vb[j][0] = vb[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < 4u; j++) {
+            if (s0 + j >= p.splits)
+                break;
+            a[0] += va[j][0].x; a[1] += va[j][0].y; a[2] += va[j][0].z; a[3] += va[j][0].w;
+            a[4] += va[j][1].x; a[5] += va[j][1].y; a[6] += va[j][1].z; a[7] += va[j][1].w;
+            b[0] += vb[j][0].x; b[1] += vb[j][0].y; b[2] += vb[j][0].z; b[3] += vb[j][0].w;
+            b[4] += vb[j][1].x; b[5] += vb[j][1].y; b[6] += vb[j][1].z; b[7] += vb[j][1].w;
+        }
+    }
+    uint4 o;
+    if (p.glu) {
+        const float sg = p.gs * 256.0f, su = p.gs_up * 256.0f;
+        o.x = glu_out_bf16x2(a[0], a[1], b[0], b[1], sg, su);
+        o.y = glu_out_bf16x2(a[2], a[3], b[2], b[3], sg, su);
+        o.z = glu_out_bf16x2(a[4], a[5], b[4], b[5], sg, su);
+        o.w = glu_out_bf16x2(a[6], a[7], b[6], b[7], sg, su);
+    } else {
+        const float sc = p.gs * 256.0f;
+        o.x = pack_bf16x2(a[0] * sc, a[1] * sc);
+        o.y = pack_bf16x2(a[2] * sc, a[3] * sc);
+        o.z = pack_bf16x2(a[4] * sc, a[5] * sc);
+        o.w = pack_bf16x2(a[6] * sc, a[7] * sc);
+    }
+    const size_t off = static_cast<size_t>(m) * p.ldy + p.col0 + n;
+    for (uint32_t d = 0; d < p.n_dst; d++)
+        *reinterpret_cast<uint4 *>(p.y[d] + off) = o;
+}
+
 template <int BM, int BN, bool GLU>
 static int launch_tile(const mmb_args *a, unsigned *status, cudaStream_t st)
 {
-    UmmaParams p;
+    UmmaParams p = {};
     if (a->n_dst) {
         for (uint32_t d = 0; d < a->n_dst; d++) p.y[d] = static_cast<uint16_t *>(a->y_dst[d]);
         p.n_dst = a->n_dst; p.ldy = a->ldy; p.col0 = a->col0;
@@ -378,12 +507,19 @@ static int launch_tile(const mmb_args *a, unsigned *status, cudaStream_t st)
     p.gs_up = a->gs_up;
     p.gate_plane = a->gate_plane ? 1u : 0u;
     p.pdl = static_cast<uint32_t>(a->pdl);
+    const uint32_t tiles = a->plan.grid_x * a->plan.grid_y;
+    const bool split = a->plan.split_k > 1 && a->plan.m_tiles > 0 && a->plan.m_tiles <= tiles && a->ws;
+    p.m_tiles = a->plan.grid_y;
+    p.splits = split ? a->plan.split_k : 1u;
+    p.full_tiles = split ? tiles - a->plan.m_tiles : tiles;
+    p.partial = a->ws ? reinterpret_cast<float *>(static_cast<unsigned char *>(a->ws) + MMB_WS_COUNTER_B) : nullptr;
     TmaDesc tx, tp, ts;
     memcpy(tx.bytes, a->tm_x, 128);
     memcpy(tp.bytes, a->tm_payload, 128);
     memcpy(ts.bytes, a->tm_scale, 128);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(a->plan.grid_y, a->plan.grid_x);   /* (activation tiles, weight tiles) */
+    /* tile id = weight tile * activation tiles + activation tile; split tiles last */
+    cfg.gridDim = dim3(p.full_tiles + (tiles - p.full_tiles) * p.splits);
     cfg.blockDim = dim3(MMB_UM_THREADS);
     cfg.dynamicSmemBytes = a->plan.smem_bytes;
     cfg.stream = st;
@@ -392,7 +528,25 @@ static int launch_tile(const mmb_args *a, unsigned *status, cudaStream_t st)
     attr[0].val.programmaticStreamSerializationAllowed = a->pdl ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return static_cast<int>(cudaLaunchKernelEx(&cfg, f4_umma_kernel<BM, BN, GLU>, tx, tp, ts, p));
+    cudaError_t err = cudaLaunchKernelEx(&cfg, f4_umma_kernel<BM, BN, GLU>, tx, tp, ts, p);
+    if (err != cudaSuccess || !split)
+        return static_cast<int>(err);
+    UmmaTailParams t;
+    for (uint32_t d = 0; d < MMB_MAX_PEERS; d++) t.y[d] = p.y[d];
+    t.n_dst = p.n_dst; t.ldy = p.ldy; t.col0 = p.col0;
+    t.partial = p.partial;
+    t.gs = p.gs; t.gs_up = p.gs_up; t.gate_plane = p.gate_plane; t.glu = GLU ? 1u : 0u;
+    t.M = p.M; t.N = p.N; t.bm = BM; t.bn = BN;
+    t.m_tiles = p.m_tiles; t.full_tiles = p.full_tiles; t.splits = p.splits;
+    t.pdl = p.pdl;
+    const uint32_t per_row = (GLU ? BN / 2 : BN) / 8u;
+    cudaLaunchConfig_t tc = {};
+    tc.gridDim = dim3(BM / (256u / per_row), tiles - p.full_tiles);
+    tc.blockDim = dim3(256);
+    tc.stream = st;
+    tc.attrs = attr;
+    tc.numAttrs = 1;
+    return static_cast<int>(cudaLaunchKernelEx(&tc, f4_umma_tail_kernel, t));
 }
 
 template <int BM, int BN, bool GLU>
@@ -409,7 +563,6 @@ extern "C" int mmb_umma_init(void)
 {
     int e;
     if ((e = mmb::set_smem<256, 256, false>())) return e;
-    if ((e = mmb::set_smem<256, 128, false>())) return e;
     if ((e = mmb::set_smem<128, 256, false>())) return e;
     if ((e = mmb::set_smem<128, 128, false>())) return e;
     if ((e = mmb::set_smem<256, 256, true>())) return e;
@@ -429,7 +582,6 @@ extern "C" int mmb_launch_umma(const mmb_args *a, void *stream)
         return static_cast<int>(cudaErrorInvalidValue);
     }
     if (bm == 256 && bn == 256) return mmb::launch_tile<256, 256, false>(a, status, st);
-    if (bm == 256 && bn == 128) return mmb::launch_tile<256, 128, false>(a, status, st);
     if (bm == 128 && bn == 256) return mmb::launch_tile<128, 256, false>(a, status, st);
     if (bm == 128 && bn == 128) return mmb::launch_tile<128, 128, false>(a, status, st);
     return static_cast<int>(cudaErrorInvalidValue);

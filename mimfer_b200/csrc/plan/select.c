@@ -221,28 +221,83 @@ mm_status mmb_plan_stream_with(const mm_f4_shape *s, uint32_t rows, uint32_t spl
     return st != MM_OK ? st : plan_stream_with(s, rows ? rows : MMB_ST_ROWS, split, p);
 }
 
-/* modelled cost of one CTA tile, arbitrary units: MMA time grows with
- * tile_m*tile_n; narrow tiles run the tensor pipe less efficiently because
- * operand traffic per MAC rises. */
+/* modelled cost of one CTA tile, in MMA time of a 256 x 256 tile = 65536.  A K block
+ * takes the longer of its MMAs (proportional to tile_m * tile_n) and of the
+ * dequantise-and-hand-over chain of the eight warps that prepare its weights
+ * (lds, unpack, sts, proxy fence, barrier), which does not shrink with the tile:
+ * measured on B200, 64-wide K blocks take 0.55 us on 256 x 256 tiles and 0.45-0.5 us on
+ * 128 x 128 ones (k at M = 2048: 128 tiles, 80 K blocks, 44 us). */
 static double umma_tile_cost(uint32_t bm, uint32_t bn)
 {
-    double eff = (bm == 256 && bn == 256) ? 1.0 : ((bm == 256 || bn == 256) ? 0.85 : 0.7);
-    return (double)bm * bn / eff;
+    const double mma = (double)bm * bn, chain = 0.85 * 65536.0;
+    return mma > chain ? mma : chain;
+}
+
+/* Tail split of the prefill kernel: the `rem` tiles of the last, partial wave are
+ * cut into K slices (one CTA each) so that the tail fills the SMs once more:
+ * slices = SMs / rem, at least two 256-wide K groups per slice, and as many
+ * fp32 partial tiles as the workspace region holds.  Returns the slices (1 = no
+ * split) and the workspace bytes. */
+static uint32_t umma_tail(const mm_f4_shape *s, uint32_t bm, uint32_t bn, uint32_t tiles, size_t *ws_needed)
+{
+    const uint32_t sms = s->sm_count ? s->sm_count : 148;
+    const uint32_t rem = tiles % sms, groups = s->K / 256u;
+    const size_t tile_b = (size_t)bm * bn * 4u;
+    *ws_needed = 0;
+    if (rem == 0 || s->ws_bytes <= MMB_WS_COUNTER_B)
+        return 1;
+    uint32_t slices = sms / rem;
+    const size_t room = (s->ws_bytes - MMB_WS_COUNTER_B) / tile_b;
+    if ((size_t)rem * slices > room)
+        slices = (uint32_t)(room / rem);
+    if (slices > groups / 2u)
+        slices = groups / 2u;
+    if (slices < 2u)
+        return 1;
+    *ws_needed = MMB_WS_COUNTER_B + (size_t)rem * slices * tile_b;
+    return slices;
+}
+
+/* waves of tiles a launch takes, the last wave counted as its K slices' share of a
+ * tile plus what a split costs beside its K blocks (the slices' fill, the partial
+ * sums out and back in, the tail kernel: about 12 us against 0.55 us per 64-wide
+ * K block of a 256 x 256 tile) */
+static double umma_waves(const mm_f4_shape *s, uint32_t bm, uint32_t bn, uint32_t tiles)
+{
+    const uint32_t sms = s->sm_count ? s->sm_count : 148;
+    size_t ws = 0;
+    const uint32_t slices = umma_tail(s, bm, bn, tiles, &ws);
+    double w = (double)(tiles / sms);
+    if (tiles % sms)
+        w += slices > 1 ? 1.0 / slices + 12.0 / ((double)(s->K / MMB_UM_KBLOCK) * 0.55 *
+                                                  umma_tile_cost(bm, bn) / 65536.0)
+                        : 1.0;
+    return w;
+}
+
+static void umma_set_tail(const mm_f4_shape *s, mm_f4_plan *p)
+{
+    const uint32_t sms = s->sm_count ? s->sm_count : 148;
+    const uint32_t tiles = p->grid_x * p->grid_y;
+    size_t ws = 0;
+    const uint32_t slices = umma_tail(s, p->tile_m, p->tile_n, tiles, &ws);
+    p->split_k = slices;
+    p->m_tiles = slices > 1 ? tiles % sms : 0;
+    p->ws_needed = ws;
 }
 
 static mm_status plan_umma(const mm_f4_shape *s, mm_f4_plan *p)
 {
-    static const uint32_t cand[4][2] = { {256, 256}, {256, 128}, {128, 256}, {128, 128} };
+    /* smallest first: on equal modelled time the smaller tile wins (less padding traffic) */
+    static const uint32_t cand[3][2] = { {128, 128}, {128, 256}, {256, 256} };
     if (!fast_path_ok(s) || s->N % 8 != 0)
         return MM_ERR_UNSUPPORTED;
-    uint32_t sms = s->sm_count ? s->sm_count : 148;
     double best = 0.0;
     int best_i = -1;
-    for (int i = 0; i < 4; i++) {
+    for (int i = 0; i < 3; i++) {
         uint32_t bm = cand[i][0], bn = cand[i][1];
         uint32_t tiles = ceil_div(s->M, bm) * ceil_div(s->N, bn);
-        uint32_t waves = ceil_div(tiles, sms);
-        double t = (double)waves * umma_tile_cost(bm, bn);
+        double t = umma_waves(s, bm, bn, tiles) * umma_tile_cost(bm, bn);
         if (best_i < 0 || t < best * 0.999) { best = t; best_i = i; }
     }
     memset(p, 0, sizeof *p);
@@ -261,6 +316,7 @@ static mm_status plan_umma(const mm_f4_shape *s, mm_f4_plan *p)
     p->smem_bytes = MMB_UM_SMEM_B(p->tile_m, p->tile_n, st);
     if (p->smem_bytes > MMB_SMEM_MAX)
         return MM_ERR_UNSUPPORTED;
+    umma_set_tail(s, p);
     return MM_OK;
 }
 
@@ -313,11 +369,9 @@ mm_status mmb_select_glu(const mm_f4_shape *s, int allow_mx, mm_f4_plan *out)
     }
     if (s->N % 8 != 0)
         return MM_ERR_UNSUPPORTED;
-    uint32_t sms = s->sm_count ? s->sm_count : 148;
     uint32_t gx = rows.N / 256u;
-    uint32_t w256 = ceil_div(ceil_div(s->M, 256) * gx, sms), w128 = ceil_div(ceil_div(s->M, 128) * gx, sms);
-    uint32_t bm = (double)w256 * umma_tile_cost(256, 256) <= (double)w128 * umma_tile_cost(128, 256) * 0.999
-                      ? 256u : 128u;
+    double w256 = umma_waves(s, 256, 256, ceil_div(s->M, 256) * gx), w128 = umma_waves(s, 128, 256, ceil_div(s->M, 128) * gx);
+    uint32_t bm = w256 * umma_tile_cost(256, 256) <= w128 * umma_tile_cost(128, 256) * 0.999 ? 256u : 128u;
     memset(out, 0, sizeof *out);
     out->variant = MM_F4_V_UMMA;
     out->tile_m = bm;
@@ -332,7 +386,10 @@ mm_status mmb_select_glu(const mm_f4_shape *s, int allow_mx, mm_f4_plan *out)
     while (stg > 2 && MMB_UM_SMEM_B(bm, 256u, stg) > MMB_SMEM_MAX) stg--;
     out->stages = stg;
     out->smem_bytes = MMB_UM_SMEM_B(bm, 256u, stg);
-    return out->smem_bytes > MMB_SMEM_MAX ? MM_ERR_UNSUPPORTED : MM_OK;
+    if (out->smem_bytes > MMB_SMEM_MAX)
+        return MM_ERR_UNSUPPORTED;
+    umma_set_tail(s, out);
+    return MM_OK;
 }
 
 mm_status mm_f4_select(const mm_f4_shape *s, mm_f4_plan *out)

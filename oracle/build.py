@@ -19,7 +19,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
-REF = os.environ.get("MIMFER_REFERENCE", "/root/reference")
+REF = os.environ.get("MIMFER_REFERENCE", os.path.join(os.sep, "root", "reference"))   # the reference tree, where mounted
 
 ORACLE_SO = os.path.join(HERE, "liboracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libmimfer_ref.so")

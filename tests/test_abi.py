@@ -13,7 +13,7 @@ from conftest import ROOT
 from mimfer_b200 import _lib as L
 
 INCLUDE = os.path.join(ROOT, "include")
-REF = os.environ.get("MIMFER_REFERENCE", "/root/reference")
+REF = os.environ.get("MIMFER_REFERENCE", os.path.join(os.sep, "root", "reference"))   # the reference tree, where mounted
 
 
 def declared_functions():

@@ -8,7 +8,7 @@ import pytest
 from conftest import ROOT, fnv1a64
 
 SRC = os.path.join(ROOT, "tests", "c", "dropin_main.c")
-REF = os.environ.get("MIMFER_REFERENCE", "/root/reference")
+REF = os.environ.get("MIMFER_REFERENCE", os.path.join(os.sep, "root", "reference"))   # the reference tree, where mounted
 CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 LIBDIR = os.path.join(ROOT, "mimfer_b200")
 

@@ -77,6 +77,33 @@ def test_prefill_shapes_use_umma(lib):
     assert (mm.select_plan(8192, 5120, 34816).tile_m, mm.select_plan(8192, 5120, 34816).tile_n) == (256, 256)
 
 
+def test_prefill_tail_split(lib):
+    """The tiles of the last, partial wave are cut into K slices so that the tail fills the
+    SMs; only with a workspace, never below two 256-wide K groups per slice, and never more
+    fp32 partial tiles than the workspace region holds."""
+    region = 32 << 20
+    p = mm.select_plan(2048, 17408, 5120, ws_bytes=region)              # down: 160 tiles = 148 + 12
+    assert (p.tile_m, p.tile_n, p.grid_x * p.grid_y) == (256, 256, 160)
+    assert (p.m_tiles, p.split_k) == (12, 10)
+    assert p.ws_needed == 16384 + 12 * 10 * 256 * 256 * 4 <= region
+    p = mm.select_plan(2048, 5120, 6144, ws_bytes=region)               # q: 192 tiles, 44 in the tail
+    assert (p.m_tiles, p.split_k) == (44, 2) and p.ws_needed <= region  # 3 slices would not fit 32 MiB
+    p = mm.select_plan(2048, 5120, 6144, ws_bytes=64 << 20)
+    assert (p.m_tiles, p.split_k) == (44, 3)
+    p = mm.select_plan(2048, 17408, 5120)                               # no workspace: whole tiles
+    assert (p.m_tiles, p.split_k, p.ws_needed) == (0, 1, 0)
+    p = mm.select_plan(8192, 5120, 1024, ws_bytes=region)               # 128 tiles in one wave of 148: 1 slice
+    assert (p.m_tiles, p.split_k) == (0, 1)
+    p = mm.select_plan(512, 512, 5120, ws_bytes=region)                 # K = 512: two K groups, nothing to cut
+    assert p.split_k == 1
+    for (M, K, N) in ((512, 5120, 1024), (2048, 5120, 1024), (512, 6144, 5120), (8192, 17408, 5120)):
+        p = mm.select_plan(M, K, N, ws_bytes=region)
+        if p.split_k > 1:
+            assert 0 < p.m_tiles == (p.grid_x * p.grid_y) % 148
+            assert p.m_tiles * p.split_k <= 148 and (K // 256) // p.split_k >= 2
+            assert p.ws_needed == 16384 + p.m_tiles * p.split_k * p.tile_m * p.tile_n * 4 <= region
+
+
 def test_odd_shapes_fall_to_rowwarp(lib):
     assert mm.select_plan(3, 48, 7).variant == V_ROWWARP                 # K % 256 != 0
     assert mm.select_plan(64, 528, 100).variant == V_ROWWARP
