@@ -469,7 +469,10 @@ static mm_status run_ops(mm_lin_engine *e)
             if (joined) {
                 if (i > group_first)
                     e->n_independent++;
-                if (i + 1 == e->n_ops) {
+                /* with bound host buffers a launch ends where an upload group ends: its
+                 * outputs go down, and the next launch's activations come up, while the
+                 * neighbouring launch computes */
+                if (i + 1 == e->n_ops || (with_copies && (i + 1) % grp == 0)) {
                     MM_CHECK(engine_close_group(e, group_first, i + 1, with_copies, grp));
                     group_open = 0;
                 }
