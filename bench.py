@@ -917,6 +917,8 @@ def run_case(b, case, steps, warmup):
         return res
     if case == "decode_layers":    # two layers of the 64-layer decode step (12 ops)
         return b.decode_step_64(steps, warmup, layers=2)
+    if case == "decode_layers8":   # eight layers (48 ops: one group launch)
+        return b.decode_step_64(steps, warmup, layers=8)
     if case == "prefill":          # one 2048 x 5120 x 34816 GEMM
         return b.prefill_sweep(steps, warmup, ms_list=(2048,), names=("gate_up",))
     if case == "prefill_small":

@@ -48,6 +48,7 @@ static struct {
     int        l2_window;        /* group launches carry a persisting L2 window over the workspace */
     int        l2_limit_set;
     int        no_tail_split;    /* prefill tiles of the last wave run whole */
+    int        group_sort;       /* ops of a group launch ordered by activation rows, most first */
     /* the digit planes made last: which activations, and where they lie */
     const void *sliced_x;
     uint32_t   sliced_M, sliced_K;
@@ -55,7 +56,7 @@ static struct {
     unsigned long long launches;
     /* experiment knobs (mm_f4_tune keys 2..4), all 0 in production */
     uint32_t   st_rows, st_split, st_dbg;
-} G = { .forced_variant = -1, .pdl = 1, .next_pdl = -1, .use_mx = 1 };
+} G = { .forced_variant = -1, .pdl = 1, .next_pdl = -1, .use_mx = 1, .group_sort = 1 };
 
 /* The workspace is cut into WS_REGIONS equal regions, each with its own arrival
  * counters, when every region still holds WS_REGION_MIN bytes; an op uses one
@@ -203,6 +204,7 @@ int mm_f4_tune(int key, int value)
     if (key == 5) { int old = G.use_mx; G.use_mx = value ? 1 : 0; return old; }
     if (key == 6) { int old = (int)G.mx_stages; G.mx_stages = (uint32_t)value; return old; }
     if (key == 7) { int old = G.l2_window; G.l2_window = value ? 1 : 0; return old; }
+    if (key == 9) { int old = G.group_sort; G.group_sort = value ? 1 : 0; return old; }
     if (key == 8) { int old = !G.no_tail_split; G.no_tail_split = value ? 0 : 1; return old; }
     return -1;
 }
@@ -793,6 +795,21 @@ mm_status mmb_group_launch(void)
     /* plans: units of up to about 768 KiB; then, from the last op backwards, a
      * finer K split is kept wherever it shortens the busiest CTA's share */
     static mm_f4_plan plans[MMB_MXG_MAX_OPS];
+    /* the ops of a group are independent: the ones with many activation rows (whose units
+     * take longest per byte, and whose split-K exchange is largest) go first, so that the
+     * launch ends on short units (insertion sort, stable).  Measured on the ten-op decode
+     * sweep: 137.8 us per step against 148.0 in list order; ordering equal-M ops by size as
+     * well changed nothing. */
+    if (G.group_sort)
+        for (uint32_t i = 1; i < GR.n; i++) {
+            const gr_item it = GR.item[i];
+            uint32_t j = i;
+            while (j > 0 && GR.item[j - 1].op.n0 < it.op.n0) {
+                GR.item[j] = GR.item[j - 1];
+                j--;
+            }
+            GR.item[j] = it;
+        }
     for (uint32_t i = 0; i < GR.n; i++)
         MM_CHECK(gr_plan(&GR.item[i], 0, &plans[i]));
     double best = gr_makespan(plans, GR.n, (uint32_t)G.sm_count);
