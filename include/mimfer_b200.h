@@ -489,9 +489,11 @@ mm_status mm_lin_engine_step_bound(mm_lin_engine *e);
  * several microseconds whatever its size and a cross-stream dependency a few
  * more per kernel, so a list of short ops does better with larger groups: the
  * first op of a group waits for the uploads of the whole group, the others for
- * nothing (measured on the ten-op decode sweep, copy nodes / upload kernel:
- * 0.325 / 0.290 ms per step with groups of 1, 0.261 / 0.225 ms with groups of 5,
- * 0.290 / 0.253 ms with one group of 10; the kernels alone take 0.191 ms).
+ * nothing.  With group launches on, a launch ends where an upload group ends, so
+ * that one launch's downloads and the next one's uploads overlap the kernels
+ * between them (measured on the ten-op decode sweep, whose kernels alone take
+ * 0.138 ms: 0.282 ms per step with one group of 10, 0.250 with groups of 5,
+ * 0.229 with groups of 4, 0.242 with groups of 3, 0.273 with groups of 2).
  * Before capture. */
 mm_status mm_lin_engine_upload_group(mm_lin_engine *e, uint32_t ops_per_event);
 /* on != 0 (default): the uploads of a group go up as ONE kernel that reads the
