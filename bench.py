@@ -921,6 +921,8 @@ def run_case(b, case, steps, warmup):
         return b.decode_step_64(steps, warmup, layers=8)
     if case == "prefill":          # one 2048 x 5120 x 34816 GEMM
         return b.prefill_sweep(steps, warmup, ms_list=(2048,), names=("gate_up",))
+    if case == "prefill_tail":     # down at M=2048: 148 whole tiles + 12 tiles in 10 K slices + the tail kernel
+        return b.prefill_sweep(steps, warmup, ms_list=(2048,), names=("down",))
     if case == "prefill_small":
         return b.prefill_sweep(steps, warmup, ms_list=(512,), names=("q",))
     raise SystemExit(f"unknown case {case}")
