@@ -337,6 +337,8 @@ mm_status mm_f4_wait_selftest(unsigned *done_dev);
  *   key 5  decode ops on the block-scaled tensor kernel (1, default) or on the
  *          CUDA-core streaming kernel (0)
  *   key 6  cap on the pipeline stages of a group launch (0 = as many as fit, default)
+ *   key 10 the work units of a group launch are handed out as its CTAs ask for them
+ *          (1, default) or dealt round-robin in advance (0)
  *   key 9  the ops of a group launch run in order of activation rows, most first
  *          (1, default), or in list order (0)
  *   key 8  the prefill kernel cuts the tiles of its last, partial wave into K slices

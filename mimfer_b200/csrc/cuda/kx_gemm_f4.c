@@ -49,6 +49,7 @@ static struct {
     int        l2_limit_set;
     int        no_tail_split;    /* prefill tiles of the last wave run whole */
     int        group_sort;       /* ops of a group launch ordered by activation rows, most first */
+    int        static_units;     /* group launch: unit u on CTA u mod grid instead of handed out as CTAs ask */
     /* the digit planes made last: which activations, and where they lie */
     const void *sliced_x;
     uint32_t   sliced_M, sliced_K;
@@ -204,6 +205,7 @@ int mm_f4_tune(int key, int value)
     if (key == 5) { int old = G.use_mx; G.use_mx = value ? 1 : 0; return old; }
     if (key == 6) { int old = (int)G.mx_stages; G.mx_stages = (uint32_t)value; return old; }
     if (key == 7) { int old = G.l2_window; G.l2_window = value ? 1 : 0; return old; }
+    if (key == 10) { int old = !G.static_units; G.static_units = value ? 0 : 1; return old; }
     if (key == 9) { int old = G.group_sort; G.group_sort = value ? 1 : 0; return old; }
     if (key == 8) { int old = !G.no_tail_split; G.no_tail_split = value ? 0 : 1; return old; }
     return -1;
@@ -747,7 +749,7 @@ mm_status mmb_group_add(const mm_op_desc *op, int glu, const void *up_payload, c
     if (gr_plan(&it, 0, &plan) != MM_OK || plan.variant != MM_F4_V_MX)
         return MM_ERR_UNSUPPORTED;
     const size_t pb = gr_partial_bytes(&plan, op->n1);
-    if (GR.part_bound + pb > ws_region_bytes() || GR.counters_bound + plan.grid_x > MMB_WS_MAX_TILES)
+    if (GR.part_bound + pb > ws_region_bytes() || GR.counters_bound + plan.grid_x > MMB_WS_MAX_TILES - 2u)
         return MM_ERR_CAPACITY;
     int shared = 0;
     for (uint32_t i = 0; i < GR.n; i++)
@@ -813,6 +815,35 @@ mm_status mmb_group_launch(void)
     for (uint32_t i = 0; i < GR.n; i++)
         MM_CHECK(gr_plan(&GR.item[i], 0, &plans[i]));
     double best = gr_makespan(plans, GR.n, (uint32_t)G.sm_count);
+    /* a short launch (fewer than three units per SM) has no long round-robin to even
+     * things out: every op's K split is searched outright, twice over the ops, for the
+     * shortest share of the busiest CTA (down alone: 20 tiles x 7 slices on 148 SMs
+     * instead of 20 x 4) */
+    uint32_t units = 0;
+    for (uint32_t i = 0; i < GR.n; i++)
+        units += plans[i].grid_x * plans[i].split_k;
+    if (units < 3u * (uint32_t)G.sm_count)
+        for (int pass = 0; pass < 2; pass++)
+            for (uint32_t k = 0; k < GR.n; k++)
+                for (uint32_t sk = 1; sk <= 16u; sk++) {
+                    mm_f4_plan trial;
+                    if (gr_plan(&GR.item[k], sk, &trial) != MM_OK || trial.split_k != sk ||
+                        trial.split_k == plans[k].split_k || trial.grid_x != plans[k].grid_x)
+                        continue;
+                    const mm_f4_plan keep = plans[k];
+                    const size_t was = gr_partial_bytes(&keep, GR.item[k].op.n1),
+                                 now = gr_partial_bytes(&trial, GR.item[k].op.n1);
+                    if (now > was && GR.part_bound + (now - was) > ws_region_bytes())
+                        continue;
+                    plans[k] = trial;
+                    const double t = gr_makespan(plans, GR.n, (uint32_t)G.sm_count);
+                    if (t < best * 0.985) {
+                        best = t;
+                        GR.part_bound = GR.part_bound + now - was;
+                    } else {
+                        plans[k] = keep;
+                    }
+                }
     for (uint32_t k = GR.n; k-- > 0;)
         for (uint32_t extra = 1; extra <= 2u; extra++) {
             mm_f4_plan trial;
@@ -863,7 +894,7 @@ mm_status mmb_group_launch(void)
         g->tiles = plan->grid_x; g->unit0 = gg->n_units;
         if (plan->split_k > 1) {
             const size_t pb = gr_partial_bytes(plan, K);
-            MM_REQUIRE(part_used + pb <= ws_region_bytes() && counters_used + plan->grid_x <= MMB_WS_MAX_TILES &&
+            MM_REQUIRE(part_used + pb <= ws_region_bytes() && counters_used + plan->grid_x <= MMB_WS_MAX_TILES - 2u &&
                        cache_used <= cap, MM_ERR_CAPACITY);
             g->counters = GR.region + (size_t)counters_used * 4u;
             g->partial = GR.region + part_used;
@@ -919,6 +950,8 @@ mm_status mmb_group_launch(void)
             gg->l2_bytes = want;
         }
     }
+    /* the last two words of the region's counter block: the units handed out, the CTAs done */
+    gg->sched = G.static_units ? NULL : (void *)(GR.region + (size_t)(MMB_WS_MAX_TILES - 2u) * 4u);
     uint32_t kernels = 0;
     int err = mmb_launch_mxg(gg, mm_cuda_stream_raw(MM_ST_COMPUTE), &kernels);
     if (err) {

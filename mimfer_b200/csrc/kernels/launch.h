@@ -185,6 +185,7 @@ typedef struct mmb_gop {
 typedef struct mmb_group {
     uint32_t n_ops, n_units, stages, acc_bufs, stage_b, smem_bytes, grid;
     int      pdl;
+    void    *sched;          /* two zeroed words in the workspace: units are handed out as CTAs ask (NULL: round-robin) */
     void    *l2_base;        /* persisting L2 access window over the scratch (planes, partials); NULL = none */
     size_t   l2_bytes;
     mmb_gop  op[MMB_MXG_MAX_OPS];

@@ -51,23 +51,50 @@ struct __align__(128) MxgGroup {
     uint32_t  n_ops, n_units, stages, acc_bufs;
     uint32_t  stage_b, pdl;
     unsigned *status;
-    uint32_t  pad[24];
+    unsigned *sched;         /* [0] units handed out beyond the first of every CTA, [1] CTAs that took
+                              * their last; both zero between launches.  NULL: unit u goes to CTA u mod grid */
+    uint32_t  pad[22];
     MxgOp     ops[MMB_MXG_MAX_OPS];
 };
 static_assert(sizeof(MxgGroup) <= 32764, "kernel parameter space");
 
-/* The units of one CTA, in order: global unit g = blockIdx.x, + gridDim.x, ... */
+/* The units of one CTA, in order.  The producer thread decides them (the first is
+ * blockIdx.x, the following ones come from a counter all CTAs share, so a CTA takes a
+ * new unit whenever it is ready for one) and hands the numbers to the other warps
+ * through a small queue in shared memory: slot j mod 8 holds the CTA's j-th unit, a
+ * number >= n_units ends the walk.  Fourteen readers per slot: two MMA threads, eight
+ * scale-copy warps, four epilogue warps. */
+#define MMB_MXG_QUEUE   8u
+#define MMB_MXG_READERS 14u
 struct UnitWalk {
-    uint32_t g, op;
-    __device__ __forceinline__ void start() { g = blockIdx.x; op = 0; }
+    uint32_t g, op, j;
+    uint32_t q_ids, q_full, q_empty;
+    unsigned *status;
+    __device__ __forceinline__ void start(uint32_t ids, uint32_t full, uint32_t empty, unsigned *st)
+    {
+        q_ids = ids; q_full = full; q_empty = empty; status = st;
+        g = 0; op = 0; j = 0;
+    }
+    /* by one thread (WARP = false) or by every lane of a warp */
+    template <bool WARP>
     __device__ __forceinline__ bool valid(const MxgGroup &grp)
     {
-        if (g >= grp.n_units)
+        const uint32_t slot = j % MMB_MXG_QUEUE;
+        bool ok = mbar_wait(q_full + 8u * slot, (j / MMB_MXG_QUEUE) & 1u, status);
+        g = lds32(q_ids + 4u * slot);
+        if (WARP) {
+            ok = __all_sync(0xffffffffu, ok);
+            if ((threadIdx.x & 31u) == 0)
+                mbar_arrive(q_empty + 8u * slot);
+        } else {
+            mbar_arrive(q_empty + 8u * slot);
+        }
+        if (!ok || g >= grp.n_units)
             return false;
         while (op + 1u < grp.n_ops && g >= grp.ops[op + 1u].unit0) op++;
         return true;
     }
-    __device__ __forceinline__ void next() { g += gridDim.x; }
+    __device__ __forceinline__ void next() { j++; }
 };
 
 struct UnitGeom {
@@ -131,6 +158,9 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
     const uint32_t bar_acc_empty = bar_acc_full + 16u;    /* [2]  its accumulators read            */
     const uint32_t tmem_slot = bar_acc_empty + 16u;
     const uint32_t last_flag = tmem_slot + 4u;
+    const uint32_t q_full = tmem_slot + 8u;                /* [8] a unit number is in the slot      */
+    const uint32_t q_empty = q_full + 8u * MMB_MXG_QUEUE;  /* [8] all its readers have taken it     */
+    const uint32_t q_ids = q_empty + 8u * MMB_MXG_QUEUE;   /* [8] unit numbers                      */
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
 
     if (tid == 0) {
@@ -142,6 +172,10 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
             mbar_init(bar_sf_full + 8u * t, 4u);
             mbar_init(bar_acc_full + 8u * t, 2u);
             mbar_init(bar_acc_empty + 8u * t, 4u);
+        }
+        for (uint32_t q = 0; q < MMB_MXG_QUEUE; q++) {
+            mbar_init(q_full + 8u * q, 1u);
+            mbar_init(q_empty + 8u * q, MMB_MXG_READERS);
         }
         mbar_fence_init();
     }
@@ -160,42 +194,57 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
          * digit planes (made by the kernel in front) after it; from then on a step's
          * four boxes go out together as soon as its stage is free. */
         if (lane == 0) {
-            UnitWalk w;
-            uint32_t s = 0, issued = 0;
-            w.start();
-            while (issued < ST && w.valid(grp)) {
-                const MxgOp &o = grp.ops[w.op];
-                const UnitGeom u = unit_geom(o, w.g);
-                uint32_t it = 0;
-                for (; it < u.nsteps && issued < ST; it++, issued++, s++) {
-                    mbar_expect_tx(bar_full + 8u * s, u.tx);
-                    mxg_load_weights(o, u, base + s * stage_b, u.ks_begin + it, bar_full + 8u * s);
-                }
-                if (it == u.nsteps)
-                    w.next();
-                else
-                    break;
+            uint32_t pushed = 0;
+            auto push = [&](uint32_t id) {
+                const uint32_t slot = pushed % MMB_MXG_QUEUE;
+                if (pushed >= MMB_MXG_QUEUE)
+                    mbar_wait(q_empty + 8u * slot, ((pushed / MMB_MXG_QUEUE) - 1u) & 1u, grp.status);
+                sts32(q_ids + 4u * slot, id);
+                mbar_arrive(q_full + 8u * slot);
+                pushed++;
+            };
+            uint32_t g = blockIdx.x, op = 0;                /* the grid never exceeds the units */
+            push(g);
+            while (op + 1u < grp.n_ops && g >= grp.ops[op + 1u].unit0) op++;
+            UnitGeom u = unit_geom(grp.ops[op], g);
+            const uint32_t first = u.nsteps < ST ? u.nsteps : ST;
+            for (uint32_t it = 0; it < first; it++) {
+                mbar_expect_tx(bar_full + 8u * it, u.tx);
+                mxg_load_weights(grp.ops[op], u, base + it * stage_b, u.ks_begin + it, bar_full + 8u * it);
             }
             if (grp.pdl != MMB_PDL_OFF)
                 grid_dep_launch();
-            grid_dep_wait();
-            /* second walk over the same steps for the planes, then on */
-            w.start();
-            s = 0;
-            uint32_t round = 0, gstep = 0;
-            while (w.valid(grp)) {
-                const MxgOp &o = grp.ops[w.op];
-                const UnitGeom u = unit_geom(o, w.g);
+            grid_dep_wait();                                /* also: the launch in front has reset the counter */
+            uint32_t s = 0, round = 0, gstep = 0;
+            for (;;) {
+                /* the number of the unit after this one, asked for now and needed at its end */
+                const uint32_t next = grp.sched ? gridDim.x + atomicAdd(grp.sched, 1u) : g + gridDim.x;
+                const MxgOp &o = grp.ops[op];
                 for (uint32_t it = 0; it < u.nsteps; it++, gstep++, s = (s + 1u == ST) ? 0u : s + 1u, round += (s == 0u)) {
                     const uint32_t st = base + s * stage_b, bar = bar_full + 8u * s;
-                    if (gstep >= ST) {
-                        mbar_wait(bar_empty + 8u * s, (round - 1u) & 1u, grp.status);
+                    if (gstep >= first) {
+                        if (round > 0u)
+                            mbar_wait(bar_empty + 8u * s, (round - 1u) & 1u, grp.status);
                         mbar_expect_tx(bar, u.tx);
                         mxg_load_weights(o, u, st, u.ks_begin + it, bar);
                     }
                     mxg_load_planes(o, u, st, u.ks_begin + it, bar);
                 }
-                w.next();
+                push(next);
+                if (next >= grp.n_units)
+                    break;
+                g = next;
+                while (op + 1u < grp.n_ops && g >= grp.ops[op + 1u].unit0) op++;
+                u = unit_geom(grp.ops[op], g);
+            }
+            if (grp.sched) {
+                /* the CTA that is last to have taken its last number puts the counters back */
+                __threadfence();
+                if (atomicAdd(grp.sched + 1, 1u) == gridDim.x - 1u) {
+                    grp.sched[0] = 0u;
+                    grp.sched[1] = 0u;
+                    __threadfence();
+                }
             }
         }
     } else if (warp == 1 || warp == 10) {
@@ -204,7 +253,7 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
         if (lane == 0) {
             UnitWalk w;
             uint32_t s = 0, round = 0, gstep = 0, j = 0;
-            for (w.start(); w.valid(grp); w.next(), j++) {
+            for (w.start(q_ids, q_full, q_empty, grp.status); w.valid<false>(grp); w.next(), j++) {
                 const MxgOp &o = grp.ops[w.op];
                 const UnitGeom u = unit_geom(o, w.g);
                 const uint32_t buf = AB == 2u ? (j & 1u) : 0u, use = j / AB;
@@ -239,7 +288,7 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
         UnitWalk w;
         uint32_t s = 0, round = 0, gstep = 0;
         uint32_t s1 = 0, round1 = 0, s2 = 0, round2 = 0;
-        for (w.start(); w.valid(grp); w.next()) {
+        for (w.start(q_ids, q_full, q_empty, grp.status); w.valid<true>(grp); w.next()) {
             const MxgOp &o = grp.ops[w.op];
             const UnitGeom u = unit_geom(o, w.g);
             const uint32_t ncol = (u.nb + 31u) >> 5;
@@ -329,7 +378,7 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
         grid_dep_wait();                                    /* row factors come from the kernel in front */
         UnitWalk w;
         uint32_t j = 0;
-        for (w.start(); w.valid(grp); w.next(), j++) {
+        for (w.start(q_ids, q_full, q_empty, grp.status); w.valid<true>(grp); w.next(), j++) {
             const MxgOp &o = grp.ops[w.op];
             const UnitGeom u = unit_geom(o, w.g);
             const uint32_t buf = AB == 2u ? (j & 1u) : 0u, use = j / AB;
@@ -626,6 +675,7 @@ extern "C" int mmb_launch_mxg(const mmb_group *hg, void *stream, uint32_t *kerne
     memset(&xs, 0, sizeof xs);
     grp.n_ops = hg->n_ops; grp.n_units = hg->n_units; grp.stages = hg->stages; grp.acc_bufs = hg->acc_bufs;
     grp.stage_b = hg->stage_b; grp.pdl = static_cast<uint32_t>(hg->pdl); grp.status = status;
+    grp.sched = static_cast<unsigned *>(hg->sched);
     uint32_t max_m = 0, max_kx = 0, max_k = 0;
     for (uint32_t i = 0; i < hg->n_ops; i++) {
         const mmb_gop &s = hg->op[i];
