@@ -768,8 +768,12 @@ mm_status mmb_group_add(const mm_op_desc *op, int glu, const void *up_payload, c
     return MM_OK;
 }
 
-/* Bytes of weights the busiest CTA streams when the units go round-robin over
- * `ctas` CTAs (the kernel's assignment), given every op's plan. */
+/* Bytes of weights the busiest CTA streams when the units are dealt in turn over
+ * `ctas` CTAs, given every op's plan: the planner's model of a launch.  (The kernel
+ * hands units out as CTAs ask, which only evens things out further; a model that
+ * did the same and counted the digit planes' bytes chose far too many K slices for
+ * short launches, 58 us instead of 37 for the two-op down launch, because it does
+ * not see what a slice costs in the split-K exchange.) */
 static double gr_makespan(const mm_f4_plan *plans, uint32_t n, uint32_t ctas)
 {
     static double load[1024];
@@ -815,7 +819,7 @@ mm_status mmb_group_launch(void)
     for (uint32_t i = 0; i < GR.n; i++)
         MM_CHECK(gr_plan(&GR.item[i], 0, &plans[i]));
     double best = gr_makespan(plans, GR.n, (uint32_t)G.sm_count);
-    /* a short launch (fewer than three units per SM) has no long round-robin to even
+    /* a short launch (fewer than three units per SM) has no long run of units to even
      * things out: every op's K split is searched outright, twice over the ops, for the
      * shortest share of the busiest CTA (down alone: 20 tiles x 7 slices on 148 SMs
      * instead of 20 x 4) */

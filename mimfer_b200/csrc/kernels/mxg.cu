@@ -7,8 +7,8 @@
  * exchange, and the weight stream stops between them.  Here the ops the
  * engine has shown to be independent of each other (q, k and v of a layer; gate
  * and up; in a benchmark of stand-alone linears, all of them) are cut into work
- * units (op, row tile, K slice) that the CTAs, one per SM, take in round-robin
- * order.  The TMA producer of a CTA runs ahead across unit and op borders, so
+ * units (op, row tile, K slice) that the CTAs, one per SM, take one after the
+ * other from a shared counter, each when it is ready for one.  The TMA producer of a CTA runs ahead across unit and op borders, so
  * the weight stream never stops; the accumulators are double-buffered in tensor
  * memory (M <= 16), so a unit's epilogue overlaps the next unit's MMAs.
  *
