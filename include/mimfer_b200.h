@@ -420,6 +420,13 @@ void      mm_f4_weights_free(mm_f4_wreg *r);
 typedef struct mm_lin_engine mm_lin_engine;
 mm_status mm_lin_engine_create(mm_lin_engine **out, uint32_t max_ops);
 mm_status mm_lin_engine_add(mm_lin_engine *e, const mm_op_desc *op);
+/* Tensor-parallel form of an OP_GEMM_F4 (no counterpart in the reference): op->n2 output
+ * features are this rank's shard of a wider output; the kernel stores them at column
+ * `col0` of every rank's [M][ldy] copy of it, y_all[0] == op->c being this rank's own
+ * (peer-mapped pointers for the others, as for mm_f4_linear_tp).  Such ops join group
+ * launches like any decode op; close a step with mm_f4_tp_barrier. */
+mm_status mm_lin_engine_add_tp(mm_lin_engine *e, const mm_op_desc *op, void *const *y_all, uint32_t n_ranks,
+                               uint32_t ldy, uint32_t col0);
 uint32_t  mm_lin_engine_n_ops(const mm_lin_engine *e);
 /* on != 0: an OP_SILU_MUL added right after the two OP_GEMM_F4 that produce its
  * operands from the same activations (the MLP front half as the reference

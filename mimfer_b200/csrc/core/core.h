@@ -65,6 +65,8 @@ void *mmb_plane_cache(size_t *bytes_out);
  * slicing of the group's activations and the kernel, then synchronise like an op. */
 mm_status mmb_group_begin(int pdl_mode, int ws_region);
 mm_status mmb_group_add(const mm_op_desc *op, int glu, const void *up_payload, const void *up_scale);
+mm_status mmb_group_add_tp(const mm_op_desc *op, void *const *y_all, uint32_t n_ranks, uint32_t ldy, uint32_t col0);
+mm_status mmb_op_linear_tp(const mm_op_desc *op, void *const *y_all, uint32_t n_ranks, uint32_t ldy, uint32_t col0);
 mm_status mmb_group_launch(void);
 uint32_t  mmb_group_size(void);
 /* Regions the workspace is cut into, so that ops in flight together never share

@@ -679,6 +679,8 @@ typedef struct gr_item {
     uint64_t    dpay, dsc;
     uint32_t    align;
     uint32_t    split;               /* K slices chosen at launch */
+    void       *y_dst[MMB_MAX_PEERS];/* tensor parallel: every rank's copy of the full output */
+    uint32_t    n_dst, ldy, col0;
 } gr_item;
 
 static struct {
@@ -722,9 +724,29 @@ static mm_status gr_plan(const gr_item *it, uint32_t split, mm_f4_plan *plan)
     return mmb_plan_mx_group(&sh, it->glu, split, plan);
 }
 
+static mm_status group_add(const mm_op_desc *op, int glu, const void *up_payload, const void *up_scale,
+                           void *const *y_all, uint32_t n_ranks, uint32_t ldy, uint32_t col0);
+
 /* MM_ERR_CAPACITY: the group is full (launch it and open another);
  * MM_ERR_UNSUPPORTED: this op does not run on the block-scaled kernel. */
 mm_status mmb_group_add(const mm_op_desc *op, int glu, const void *up_payload, const void *up_scale)
+{
+    return group_add(op, glu, up_payload, up_scale, NULL, 0, 0, 0);
+}
+
+/* The tensor-parallel form of a plain linear: op->n2 output features (this rank's
+ * shard) stored at column col0 of every rank's [M][ldy] output, op->c = y_all[0]. */
+mm_status mmb_group_add_tp(const mm_op_desc *op, void *const *y_all, uint32_t n_ranks, uint32_t ldy, uint32_t col0)
+{
+    MM_REQUIRE(op && y_all && n_ranks >= 1 && n_ranks <= MMB_MAX_PEERS, MM_ERR_RANGE);
+    for (uint32_t d = 0; d < n_ranks; d++)
+        MM_REQUIRE(y_all[d] && ((uintptr_t)y_all[d] & 15u) == 0, MM_ERR_STATE);
+    MM_REQUIRE((uint64_t)col0 + op->n2 <= ldy, MM_ERR_SHAPE);
+    return group_add(op, 0, NULL, NULL, y_all, n_ranks, ldy, col0);
+}
+
+static mm_status group_add(const mm_op_desc *op, int glu, const void *up_payload, const void *up_scale,
+                           void *const *y_all, uint32_t n_ranks, uint32_t ldy, uint32_t col0)
 {
     MM_REQUIRE(GR.active && op, MM_ERR_STATE);
     if (GR.n == MMB_MXG_MAX_OPS)
@@ -736,6 +758,8 @@ mm_status mmb_group_add(const mm_op_desc *op, int glu, const void *up_payload, c
     it.pay0 = op->b; it.sc0 = op->d; it.gate_first = 1;
     it.up_scale = up_scale;
     it.align = min_align(op->a, op->b, op->d, op->c);
+    it.n_dst = n_ranks; it.ldy = ldy; it.col0 = col0;
+    for (uint32_t d = 0; d < n_ranks; d++) it.y_dst[d] = y_all[d];
     if (it.align < 16 || op->n0 == 0 || op->n1 == 0 || op->n2 == 0 || op->n1 % 16 != 0)
         return MM_ERR_SHAPE;
     if (glu) {
@@ -890,6 +914,8 @@ mm_status mmb_group_launch(void)
             sliced++;
         }
         g->x = it->op.a; g->y = it->op.c;
+        g->n_dst = it->n_dst; g->ldy = it->ldy; g->col0 = it->col0;
+        for (uint32_t d = 0; d < it->n_dst; d++) g->y_dst[d] = it->y_dst[d];
         g->gs = mm_f4_gscale_get(it->op.d);
         g->gs_up = it->glu ? mm_f4_gscale_get(it->up_scale) : 0.0f;
         g->glu = it->glu; g->gate_plane = it->glu ? (it->gate_first ? 0 : 1) : 0;
@@ -900,7 +926,7 @@ mm_status mmb_group_launch(void)
             const size_t pb = gr_partial_bytes(plan, K);
             MM_REQUIRE(part_used + pb <= ws_region_bytes() && counters_used + plan->grid_x <= MMB_WS_MAX_TILES - 2u &&
                        cache_used <= cap, MM_ERR_CAPACITY);
-            g->counters = GR.region + (size_t)counters_used * 4u;
+            g->counters_idx = counters_used;
             g->partial = GR.region + part_used;
             counters_used += plan->grid_x;
             part_used += pb;
@@ -955,6 +981,7 @@ mm_status mmb_group_launch(void)
         }
     }
     /* the last two words of the region's counter block: the units handed out, the CTAs done */
+    gg->counters = GR.region;
     gg->sched = G.static_units ? NULL : (void *)(GR.region + (size_t)(MMB_WS_MAX_TILES - 2u) * 4u);
     uint32_t kernels = 0;
     int err = mmb_launch_mxg(gg, mm_cuda_stream_raw(MM_ST_COMPUTE), &kernels);
@@ -1047,6 +1074,18 @@ mm_status mmb_plan_for_op(const mm_op_desc *op, int glu, mm_f4_plan *out)
         return mmb_select_glu(&sh, G.use_mx, out);
     }
     return plan_linear(op->a, op->b, op->d, op->c, 0, 0, 0, op->n0, op->n1, op->n2, 0, out);
+}
+
+/* a tensor-parallel linear of an op list that runs on its own (not in a group launch) */
+mm_status mmb_op_linear_tp(const mm_op_desc *op, void *const *y_all, uint32_t n_ranks, uint32_t ldy, uint32_t col0)
+{
+    MM_REQUIRE(op && op->a && op->b && op->c && op->d, MM_ERR_STATE);
+    MM_REQUIRE(mm_cuda_stream_raw(MM_ST_COMPUTE) != NULL, MM_ERR_STATE);
+    mm_status st = mm_f4_linear_tp(op->a, op->b, op->d, mm_f4_gscale_get(op->d), y_all, n_ranks, ldy, col0,
+                                   op->n0, op->n1, op->n2, mm_cuda_stream_raw(MM_ST_COMPUTE));
+    if (st != MM_OK)
+        return st;
+    return finish_op();
 }
 
 mm_status mmb_op_mlp_gate_up(const mm_op_desc *op, const void *up_payload, const void *up_scale)

@@ -21,10 +21,13 @@
 #define MMB_OP_GATE_UP ((mm_op)(OP_N + 1))
 
 typedef struct up_operands { const void *payload, *scale; } up_operands;
+/* tensor-parallel linear: every rank's copy of the full output, its row pitch, this op's first column */
+typedef struct tp_dst { void *y[8]; uint32_t n, ldy, col0; } tp_dst;
 
 struct mm_lin_engine {
     mm_op_desc  *ops;
     up_operands *up;            /* [max_ops], used by MMB_OP_GATE_UP entries */
+    tp_dst      *tp;            /* [max_ops], n > 0 for ops added with mm_lin_engine_add_tp */
     uint32_t     n_ops, max_ops;
     mm_graph    *graph;
     int          captured;
@@ -52,9 +55,11 @@ mm_status mm_lin_engine_create(mm_lin_engine **out, uint32_t max_ops)
         return MM_ERR_NOMEM;
     e->ops = (mm_op_desc *)calloc(max_ops, sizeof(mm_op_desc));
     e->up = (up_operands *)calloc(max_ops, sizeof(up_operands));
-    if (!e->ops || !e->up) {
+    e->tp = (tp_dst *)calloc(max_ops, sizeof(tp_dst));
+    if (!e->ops || !e->up || !e->tp) {
         free(e->ops);
         free(e->up);
+        free(e->tp);
         free(e);
         return MM_ERR_NOMEM;
     }
@@ -165,11 +170,34 @@ mm_status mm_lin_engine_add(mm_lin_engine *e, const mm_op_desc *op)
         if (op->n0 == 0 || op->n1 == 0 || op->n2 == 0 || op->n1 % 16 != 0)
             return MM_ERR_SHAPE;
     }
+    memset(&e->tp[e->n_ops], 0, sizeof(tp_dst));
     e->ops[e->n_ops++] = *op;
     return MM_OK;
 }
 
 /* bytes of the op's first input and of its output (host-buffer step) */
+/* A linear whose n2 output features are this rank's shard of a wider output: the kernel
+ * stores them at column col0 of every rank's [M][ldy] copy (y_all[0] = op->c, this rank's).
+ * Inside a group launch, or as mm_f4_linear_tp when it runs on its own. */
+mm_status mm_lin_engine_add_tp(mm_lin_engine *e, const mm_op_desc *op, void *const *y_all, uint32_t n_ranks,
+                               uint32_t ldy, uint32_t col0)
+{
+    MM_REQUIRE(e && op && y_all, MM_ERR_STATE);
+    MM_REQUIRE(n_ranks >= 1 && n_ranks <= 8, MM_ERR_RANGE);
+    MM_REQUIRE(op->op == OP_GEMM_F4 && y_all[0] == op->c, MM_ERR_STATE);
+    MM_REQUIRE((uint64_t)col0 + op->n2 <= ldy, MM_ERR_SHAPE);
+    for (uint32_t d = 0; d < n_ranks; d++)
+        MM_REQUIRE(y_all[d] && ((uintptr_t)y_all[d] & 15u) == 0, MM_ERR_STATE);
+    const uint32_t at = e->n_ops;
+    MM_CHECK(mm_lin_engine_add(e, op));
+    if (e->n_ops != at + 1u)
+        return MM_ERR_STATE;
+    tp_dst *t = &e->tp[at];
+    for (uint32_t d = 0; d < n_ranks; d++) t->y[d] = y_all[d];
+    t->n = n_ranks; t->ldy = ldy; t->col0 = col0;
+    return MM_OK;
+}
+
 static size_t op_in_bytes(const mm_op_desc *op) { return (size_t)op->n0 * op->n1 * 2u; }
 static size_t op_out_bytes(const mm_op_desc *op)
 {
@@ -220,21 +248,23 @@ static int spans_meet(span a, span b) { return a.lo < b.hi && b.lo < a.hi; }
 
 /* reads[0..1] and writes[0..1] of an op (weights and gains are never written, so
  * they do not count).  ADD_RMSNORM updates its first operand in place. */
-static void op_spans(const mm_op_desc *op, span reads[2], span writes[2])
+static void op_spans(const mm_lin_engine *e, const mm_op_desc *op, span reads[2], span writes[2])
 {
     size_t in = op_in_bytes(op);
     const int two = op->op == OP_SILU_MUL || op->op == OP_ADD_RMSNORM;
     reads[0] = mk_span(op->a, in);
     reads[1] = two ? mk_span(op->b, in) : mk_span(op->a, 0);
     writes[0] = mk_span(op->c, op_out_bytes(op));
+    if (op >= e->ops && op < e->ops + e->n_ops && e->tp[op - e->ops].n)      /* a column slice of [M][ldy] */
+        writes[0] = mk_span(op->c, (size_t)op->n0 * e->tp[op - e->ops].ldy * 2u);
     writes[1] = op->op == OP_ADD_RMSNORM ? mk_span(op->a, in) : mk_span(op->c, 0);
 }
 
-static int ops_independent(const mm_op_desc *p, const mm_op_desc *q)
+static int ops_independent(const mm_lin_engine *e, const mm_op_desc *p, const mm_op_desc *q)
 {
     span pr[2], qr[2], pw[2], qw[2];
-    op_spans(p, pr, pw);
-    op_spans(q, qr, qw);
+    op_spans(e, p, pr, pw);
+    op_spans(e, q, qr, qw);
     for (int i = 0; i < 2; i++)
         for (int j = 0; j < 2; j++)
             if (spans_meet(pw[i], qw[j]) || spans_meet(pw[i], qr[j]) || spans_meet(qw[i], pr[j]))
@@ -374,7 +404,7 @@ static mm_status run_ops(mm_lin_engine *e)
                 span r[2], w[2];
                 if (e->ops[j].op == OP_NOP)
                     continue;
-                op_spans(&e->ops[j], r, w);
+                op_spans(e, &e->ops[j], r, w);
                 if (spans_meet(w[0], xs) || spans_meet(w[1], xs))
                     external = 0;
             }
@@ -442,7 +472,7 @@ static mm_status run_ops(mm_lin_engine *e)
             if (linear) {
                 int indep = 1;
                 for (uint32_t j = group_first; group_open && indep && j < i; j++)
-                    if (e->ops[j].op != OP_NOP && !ops_independent(op, &e->ops[j]))
+                    if (e->ops[j].op != OP_NOP && !ops_independent(e, op, &e->ops[j]))
                         indep = 0;
                 for (int attempt = 0; attempt < 2 && !joined; attempt++) {
                     if (!group_open) {
@@ -452,8 +482,10 @@ static mm_status run_ops(mm_lin_engine *e)
                         group_first = i;
                         indep = 1;
                     }
-                    mm_status gs = indep ? mmb_group_add(op, op->op == MMB_OP_GATE_UP, e->up[i].payload, e->up[i].scale)
-                                         : MM_ERR_CAPACITY;
+                    mm_status gs = !indep ? MM_ERR_CAPACITY
+                                   : e->tp[i].n ? mmb_group_add_tp(op, e->tp[i].y, e->tp[i].n, e->tp[i].ldy, e->tp[i].col0)
+                                                : mmb_group_add(op, op->op == MMB_OP_GATE_UP, e->up[i].payload,
+                                                                e->up[i].scale);
                     if (gs == MM_OK) {
                         joined = 1;
                     } else if (gs == MM_ERR_CAPACITY && mmb_group_size() > 0) {
@@ -493,7 +525,7 @@ static mm_status run_ops(mm_lin_engine *e)
             if (plan.variant == MM_F4_V_MX && prev_mx >= 0) {
                 const mm_op_desc *q = &e->ops[prev_mx];
                 span qr[2], qw[2];
-                op_spans(q, qr, qw);
+                op_spans(e, q, qr, qw);
                 share = q->a == op->a && q->n0 == op->n0 && q->n1 == op->n1 &&
                         !spans_meet(qw[0], mk_span(op->a, op_in_bytes(op)));
             }
@@ -511,7 +543,7 @@ static mm_status run_ops(mm_lin_engine *e)
                                         (plan.variant == MM_F4_V_MX && (share || e->planes[i]))) &&
                               !(scratch && (regions_in_flight & (1u << region)));
                 for (uint32_t j = first_in_flight; independent && j < i; j++)
-                    if (e->ops[j].op != OP_NOP && !ops_independent(op, &e->ops[j]))
+                    if (e->ops[j].op != OP_NOP && !ops_independent(e, op, &e->ops[j]))
                         independent = 0;
             }
             if (!independent) {
@@ -539,7 +571,8 @@ static mm_status run_ops(mm_lin_engine *e)
         kc.op = &e->ops[i];
         mm_status st = e->ops[i].op == MMB_OP_GATE_UP
                            ? mmb_op_mlp_gate_up(&e->ops[i], e->up[i].payload, e->up[i].scale)
-                           : mm_kx_invoke(&kc);
+                       : e->tp[i].n ? mmb_op_linear_tp(&e->ops[i], e->tp[i].y, e->tp[i].n, e->tp[i].ldy, e->tp[i].col0)
+                                    : mm_kx_invoke(&kc);
         if (st != MM_OK) {
             MM_LOGE("engine: op %u (%s) failed: %s", i, e->ops[i].note, mm_status_str(st));
             return st;
@@ -635,6 +668,7 @@ void mm_lin_engine_destroy(mm_lin_engine *e)
     mm_graph_destroy(e->graph);
     free(e->ops);
     free(e->up);
+    free(e->tp);
     free(e->x_bound);
     free(e->y_bound);
     free(e->planes);

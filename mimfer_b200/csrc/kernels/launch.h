@@ -171,7 +171,10 @@ typedef struct mmb_gop {
     void       *y;            /* bf16 [M][N] */
     void       *x_ws;         /* activation scratch (row factors, digit planes, plane scales) */
     int         slice_here;   /* this op is the first of the group to read x: slice it        */
-    void       *partial, *counters;
+    void       *y_dst[MMB_MAX_PEERS]; /* tensor parallel: every rank's copy of the full output (n_dst > 0) */
+    uint32_t    n_dst, ldy, col0;     /* ... its row pitch, and this op's first column in it */
+    void       *partial;
+    uint32_t    counters_idx;         /* first arrival counter of the op (mmb_group.counters) */
     float       gs, gs_up;
     int         glu, gate_plane;
     uint32_t    M, K, N;
@@ -185,6 +188,7 @@ typedef struct mmb_gop {
 typedef struct mmb_group {
     uint32_t n_ops, n_units, stages, acc_bufs, stage_b, smem_bytes, grid;
     int      pdl;
+    void    *counters;       /* arrival counters of the region */
     void    *sched;          /* two zeroed words in the workspace: units are handed out as CTAs ask (NULL: round-robin) */
     void    *l2_base;        /* persisting L2 access window over the scratch (planes, partials); NULL = none */
     size_t   l2_bytes;

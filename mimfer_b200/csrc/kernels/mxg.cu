@@ -35,15 +35,17 @@ namespace mmb {
 
 struct __align__(128) MxgOp {
     TmaDesc         tm_payload, tm_scale, tm_planes, tm_sfb;
-    uint16_t       *y;
+    uint16_t       *y[MMB_MAX_PEERS];    /* destinations: own output, then the peers' (tensor parallel) */
     const float    *row_scale;
     float          *partial;
-    unsigned       *counters;
     float           gs, gs_up;
-    uint32_t        M, N;
-    uint32_t        rows, nb, k_steps, split_k, tiles, unit0;
-    uint32_t        glu, gate_plane;
-    uint32_t        pad[12];
+    uint32_t        M, N;                /* N: output features of this op (its shard's) */
+    uint32_t        k_steps, tiles, unit0;
+    uint32_t        counters_idx;        /* first arrival counter of the op in MxgGroup::counters */
+    uint32_t        ldy, col0;           /* row pitch and column offset inside every destination */
+    uint16_t        rows, nb, split_k;
+    uint8_t         flags;               /* 1: gated pair, 2: the second plane of a tile is the gate */
+    uint8_t         n_dst;
 };
 static_assert(sizeof(MxgOp) == 640, "MxgOp layout");
 
@@ -53,7 +55,8 @@ struct __align__(128) MxgGroup {
     unsigned *status;
     unsigned *sched;         /* [0] units handed out beyond the first of every CTA, [1] CTAs that took
                               * their last; both zero between launches.  NULL: unit u goes to CTA u mod grid */
-    uint32_t  pad[22];
+    unsigned *counters;      /* arrival counters of the split tiles, zero between launches */
+    uint32_t  pad[20];
     MxgOp     ops[MMB_MXG_MAX_OPS];
 };
 static_assert(sizeof(MxgGroup) <= 32764, "kernel parameter space");
@@ -112,7 +115,7 @@ __device__ __forceinline__ UnitGeom unit_geom(const MxgOp &o, uint32_t g)
     u.slice = v - u.tile * o.split_k;
     u.ks_begin = static_cast<uint32_t>(static_cast<uint64_t>(o.k_steps) * u.slice / o.split_k);
     u.nsteps = static_cast<uint32_t>(static_cast<uint64_t>(o.k_steps) * (u.slice + 1u) / o.split_k) - u.ks_begin;
-    u.glu = o.glu != 0u;
+    u.glu = (o.flags & 1u) != 0u;
     u.rows = o.rows; u.nb = o.nb;
     u.halves = u.glu ? 2u : (u.rows > 128u ? 2u : 1u);
     u.h1 = u.glu ? u.rows >> 1 : 128u;
@@ -124,6 +127,14 @@ __device__ __forceinline__ UnitGeom unit_geom(const MxgOp &o, uint32_t g)
     u.o_sfb = u.o_sc + ((u.rows * 16u + 127u) & ~127u);
     u.tx = u.rows * 144u + u.nb * 144u;
     return u;
+}
+
+/* one bf16 to every destination of the op */
+__device__ __forceinline__ void mxg_store(const MxgOp &o, size_t off, uint16_t v)
+{
+    o.y[0][off] = v;
+    for (uint32_t d = 1; d < o.n_dst; d++)
+        o.y[d][off] = v;
 }
 
 __device__ __forceinline__ void mxg_load_weights(const MxgOp &o, const UnitGeom &u, uint32_t st, uint32_t ks,
@@ -384,6 +395,7 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
             const uint32_t buf = AB == 2u ? (j & 1u) : 0u, use = j / AB;
             const uint32_t groups = u.nb / 24u;
             const bool direct = o.split_k == 1u;
+            const bool gate_second = (o.flags & 2u) != 0u;
             const uint32_t pitch = u.glu ? o.tiles * 256u : o.N;
             /* row factors: lane l holds entries l and l + 32 of the [32][2] table */
             const float ra = lane < 2u * o.M ? __ldcg(o.row_scale + lane) : 0.0f;
@@ -419,8 +431,8 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
                         const bool ok = lr < u.cnt0 && n < o.N;
                         if (direct) {
                             if (ok)
-                                o.y[static_cast<size_t>(m) * o.N + n] =
-                                    glu_out_bf16(o.gate_plane ? a1 : a0, o.gate_plane ? a0 : a1, o.gs, o.gs_up);
+                                mxg_store(o, static_cast<size_t>(m) * o.ldy + o.col0 + n,
+                                    glu_out_bf16(gate_second ? a1 : a0, gate_second ? a0 : a1, o.gs, o.gs_up));
                         } else if (ok) {
                             __stcg(mine + static_cast<size_t>(m) * pitch + u.tile * 256u + lr, a0);
                             __stcg(mine + static_cast<size_t>(m) * pitch + u.tile * 256u + 128u + lr, a1);
@@ -436,7 +448,7 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
                                 continue;
                             if (direct) {
                                 __nv_bfloat16 hv = __float2bfloat16_rn(a * o.gs);
-                                o.y[static_cast<size_t>(m) * o.N + n] = *reinterpret_cast<uint16_t *>(&hv);
+                                mxg_store(o, static_cast<size_t>(m) * o.ldy + o.col0 + n, *reinterpret_cast<uint16_t *>(&hv));
                             } else {
                                 __stcg(mine + static_cast<size_t>(m) * pitch + n, a);
                             }
@@ -453,7 +465,7 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (etid == 0u) {
                     __threadfence();
-                    const unsigned ticket = atomicAdd(o.counters + u.tile, 1u);
+                    const unsigned ticket = atomicAdd(grp.counters + o.counters_idx + u.tile, 1u);
                     __threadfence();
                     sts32(last_flag, (ticket == o.split_k - 1u) ? 1u : 0u);
                 }
@@ -491,24 +503,25 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
                                 break;
                             if (u.glu) {
                                 if (ok0)
-                                    o.y[static_cast<size_t>(m) * o.N + u.row0 + lr] =
-                                        glu_out_bf16(o.gate_plane ? s1[r] : s0[r], o.gate_plane ? s0[r] : s1[r],
-                                                     o.gs, o.gs_up);
+                                    mxg_store(o, static_cast<size_t>(m) * o.ldy + o.col0 + u.row0 + lr,
+                                              glu_out_bf16(gate_second ? s1[r] : s0[r], gate_second ? s0[r] : s1[r],
+                                                           o.gs, o.gs_up));
                             } else {
                                 if (ok0) {
                                     __nv_bfloat16 hv = __float2bfloat16_rn(s0[r] * o.gs);
-                                    o.y[static_cast<size_t>(m) * o.N + u.row0 + lr] = *reinterpret_cast<uint16_t *>(&hv);
+                                    mxg_store(o, static_cast<size_t>(m) * o.ldy + o.col0 + u.row0 + lr,
+                                              *reinterpret_cast<uint16_t *>(&hv));
                                 }
                                 if (ok1) {
                                     __nv_bfloat16 hv = __float2bfloat16_rn(s1[r] * o.gs);
-                                    o.y[static_cast<size_t>(m) * o.N + u.row0 + 128u + lr] =
-                                        *reinterpret_cast<uint16_t *>(&hv);
+                                    mxg_store(o, static_cast<size_t>(m) * o.ldy + o.col0 + u.row0 + 128u + lr,
+                                              *reinterpret_cast<uint16_t *>(&hv));
                                 }
                             }
                         }
                     }
                     if (etid == 0u)
-                        o.counters[u.tile] = 0u;
+                        grp.counters[o.counters_idx + u.tile] = 0u;
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");     /* last_flag is reused by the next unit */
             }
@@ -676,6 +689,7 @@ extern "C" int mmb_launch_mxg(const mmb_group *hg, void *stream, uint32_t *kerne
     grp.n_ops = hg->n_ops; grp.n_units = hg->n_units; grp.stages = hg->stages; grp.acc_bufs = hg->acc_bufs;
     grp.stage_b = hg->stage_b; grp.pdl = static_cast<uint32_t>(hg->pdl); grp.status = status;
     grp.sched = static_cast<unsigned *>(hg->sched);
+    grp.counters = static_cast<unsigned *>(hg->counters);
     uint32_t max_m = 0, max_kx = 0, max_k = 0;
     for (uint32_t i = 0; i < hg->n_ops; i++) {
         const mmb_gop &s = hg->op[i];
@@ -684,15 +698,21 @@ extern "C" int mmb_launch_mxg(const mmb_group *hg, void *stream, uint32_t *kerne
         memcpy(d.tm_scale.bytes, s.tm_scale, 128);
         memcpy(d.tm_planes.bytes, s.tm_planes, 128);
         memcpy(d.tm_sfb.bytes, s.tm_sfb, 128);
-        d.y = static_cast<uint16_t *>(s.y);
+        d.y[0] = static_cast<uint16_t *>(s.y);
+        d.n_dst = 1; d.ldy = s.N; d.col0 = 0;
+        if (s.n_dst) {
+            for (uint32_t k = 0; k < s.n_dst && k < MMB_MAX_PEERS; k++) d.y[k] = static_cast<uint16_t *>(s.y_dst[k]);
+            d.n_dst = static_cast<uint8_t>(s.n_dst); d.ldy = s.ldy; d.col0 = s.col0;
+        }
         d.row_scale = reinterpret_cast<const float *>(static_cast<const unsigned char *>(s.x_ws) + MMB_MX_ROWSCALE_OFF);
         d.partial = static_cast<float *>(s.partial);
-        d.counters = static_cast<unsigned *>(s.counters);
+        d.counters_idx = s.counters_idx;
         d.gs = s.gs; d.gs_up = s.gs_up;
         d.M = s.M; d.N = s.N;
-        d.rows = s.rows; d.nb = s.nb; d.k_steps = s.k_steps; d.split_k = s.split_k; d.tiles = s.tiles;
+        d.rows = static_cast<uint16_t>(s.rows); d.nb = static_cast<uint16_t>(s.nb); d.k_steps = s.k_steps;
+        d.split_k = static_cast<uint16_t>(s.split_k); d.tiles = s.tiles;
         d.unit0 = s.unit0;
-        d.glu = s.glu ? 1u : 0u; d.gate_plane = s.gate_plane ? 1u : 0u;
+        d.flags = static_cast<uint8_t>((s.glu ? 1u : 0u) | (s.gate_plane ? 2u : 0u));
         if (s.slice_here) {
             mmb::XsliceItem &it = xs.item[xs.n];
             it.x = static_cast<const uint16_t *>(s.x);

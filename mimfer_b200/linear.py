@@ -257,6 +257,15 @@ class LinearEngine:
         self._keep.append((x, w, y))
         L.check(self.rt.lib.mm_lin_engine_add(self.h, C.byref(d)), "mm_lin_engine_add")
 
+    def add_tp(self, x, w_shard, y_full, ptrs, n_ranks, col0):
+        """A tensor-parallel linear: w_shard's output features go to columns
+        [col0, col0 + w_shard.N) of every rank's copy of y_full ([M][ldy]); ptrs: ctypes array
+        of the n_ranks base pointers, this rank's own (y_full) first."""
+        d = self.rt.op_desc(x, w_shard, y_full, None, L.OP_GEMM_F4, b"gemm_f4_tp")
+        self._keep.append((x, w_shard, y_full, ptrs))
+        L.check(self.rt.lib.mm_lin_engine_add_tp(self.h, C.byref(d), ptrs, n_ranks, y_full.shape[1], col0),
+                "mm_lin_engine_add_tp")
+
     def add_silu_mul(self, gate, up, y):
         """OP_SILU_MUL over gate/up [M][inter] (src/plan/plan.c:240-241)."""
         d = L.MmOpDesc()

@@ -226,3 +226,68 @@ class TpStep:
             self.graphs[k].replay()
         self.ys = self.outs[k]
         return self.ys
+
+
+class TpGroupStep:
+    """Several tensor-parallel DECODE linears of one step as one group launch per rank.
+
+    Every linear is sharded along N like TpLinear; the rank's shards go into the
+    op-list engine with mm_lin_engine_add_tp, so the whole step is one slicing kernel
+    and one persistent launch of the block-scaled kernel whose epilogue stores every
+    output tile into all ranks' copies, followed by the library's barrier kernel.
+    Outputs are double-buffered like TpLinear's: two engines, captured once each,
+    replayed in turn.  The activations are read from the same device tensors `xs` on
+    every replay: refill them in place."""
+
+    def __init__(self, weights, xs, rank, world, rt, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        from .linear import LinearEngine
+        if len(weights) != len(xs) or not weights:
+            raise ValueError("one activation tensor per linear")
+        self.rank, self.world, self.rt, self.group = rank, world, rt, group
+        self.xs = list(xs)
+        self.shards, self.col0 = [], []
+        for w in weights:
+            n0, n1 = shard_bounds(w.N, rank, world)
+            self.shards.append(w.rows(n0, n1).to_device(rt.device))
+            self.col0.append(n0)
+        g = group if group is not None else (dist.group.WORLD if world > 1 else None)
+        self.outs, self.engines, self._keep = [], [], []
+        for _ in range(2):
+            ys, eng = [], LinearEngine(rt, max_ops=len(weights) + 1)
+            for w, x, sh, c0 in zip(weights, self.xs, self.shards, self.col0):
+                M = x.shape[0]
+                if world > 1:
+                    y = symm_mem.empty((M, w.N), dtype=x.dtype, device=x.device)
+                    hdl = symm_mem.rendezvous(y, g)
+                    order = [rank] + [r for r in range(world) if r != rank]
+                    ptrs = (C.c_void_p * world)(*[hdl.buffer_ptrs[r] for r in order])
+                    self._keep.append(hdl)
+                else:
+                    y = torch.empty((M, w.N), dtype=x.dtype, device=x.device)
+                    ptrs = (C.c_void_p * 1)(y.data_ptr())
+                eng.add_tp(x, sh, y, ptrs, world, c0)
+                ys.append(y)
+            eng.launch()                          # direct dispatch once: errors surface per op
+            rt.sync()
+            eng.capture()
+            self.outs.append(ys)
+            self.engines.append(eng)
+        self.barrier = TpBarrier.get(rt, rank, world, group) if world > 1 else None
+        if world > 1:
+            dist.barrier(group=group)             # every rank holds its buffers before anyone stores
+        torch.cuda.synchronize()
+        self.n_replays = 0
+
+    def replay(self):
+        k = self.n_replays % 2
+        self.n_replays += 1
+        self.engines[k].launch()
+        if self.barrier is not None:
+            self.barrier.sync()
+        return self.outs[k]
+
+    def close(self):
+        for e in self.engines:
+            e.close()
+        self.engines, self.outs, self._keep = [], [], []

@@ -343,3 +343,38 @@ def test_more_ops_than_one_launch_holds(rt, oracle):
             assert row_rel_l2(rt.from_device_bf16(ys[i]), oracle.gemm_f4(xb[i], w.payload, w.scales, w.gs)) <= REL_L2_TOL
     finally:
         eng.close()
+
+
+def test_group_launch_of_tensor_parallel_ops(rt, oracle):
+    """mm_lin_engine_add_tp: three linears, each the second of two N-shards, every output tile
+    stored at its column offset into two full-width buffers (what two ranks would hold), all
+    in one group launch; the other shard's columns stay untouched."""
+    torch = rt.torch
+    shapes = [(4, 1024, 1200), (16, 2048, 512), (1, 5120, 2048)]
+    ws = [mm.make_weight(N, K, seed=70 + i) for i, (M, K, N) in enumerate(shapes)]
+    xb = [mm.make_activations(M, K, seed=80 + i) for i, (M, K, N) in enumerate(shapes)]
+    xs = [rt.to_device_bf16(v) for v in xb]
+    shards = [w.rows(w.N // 2, w.N).to_device(rt.device) for w in ws]
+    outs = [[torch.zeros((M, N), dtype=torch.bfloat16, device=rt.device) for _ in range(2)] for (M, K, N) in shapes]
+    torch.cuda.synchronize()
+    eng = mm.LinearEngine(rt, max_ops=8)
+    try:
+        keep = []
+        for x, sh, (a, b), w in zip(xs, shards, outs, ws):
+            ptrs = (C.c_void_p * 2)(a.data_ptr(), b.data_ptr())
+            keep.append(ptrs)
+            eng.add_tp(x, sh, a, ptrs, 2, w.N // 2)
+        eng.capture()
+        for _ in range(2):
+            eng.launch()
+        rt.sync()
+        assert rt.device_status() == 0 and eng.n_group_launches() == 1
+        for i, w in enumerate(ws):
+            a, b = rt.from_device_bf16(outs[i][0]), rt.from_device_bf16(outs[i][1])
+            assert np.array_equal(a, b)
+            h = w.N // 2
+            assert not a[:, :h].any()
+            want = oracle.gemm_f4(xb[i], w.payload, w.scales, w.gs, n_begin=h, n_end=w.N)
+            assert row_rel_l2(a[:, h:], want) <= REL_L2_TOL, shapes[i]
+    finally:
+        eng.close()
