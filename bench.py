@@ -11,9 +11,11 @@ One "step" is one pass of the hot path over one batch of synthetic input:
           engine runs the ten independent ops as one persistent group launch).
           value = packed weight bytes (payload + block scales) / time, GB/s: the
           median of REPEATS timed regions of --steps steps each, min and max beside it.
-  N > 1   tensor-parallel linears: gate+up and the LM head (K=5120 -> N=151936),
-          split along N, at M=32, each followed by the all-gather of the output
-          slices (NCCL over NVLink).  value = whole-weight bytes / time, GB/s.
+  N > 1   the same ten ops, every one split along N over the ranks (strong scaling):
+          per rank one group launch whose epilogue stores every output tile into
+          all ranks' copies, then a barrier kernel.  value = whole-weight bytes /
+          time, GB/s.  The tensor-parallel linears of config 4 (gate+up and the LM
+          head at M=32 and M=8192) are in "tp" at every N.
 
 The JSON line also carries the prefill GEMM sweep ("prefill": TFLOP/s against
 the dense bf16 tensor roofline), the 64-layer decode step ("decode_step"), the
@@ -613,6 +615,116 @@ class Bench:
         torch.cuda.empty_cache()
         return res
 
+    def tp_sweep(self, steps, warmup, repeats=REPEATS):
+        """The N=1 headline workload, tensor-parallel: the ten ops of the decode sweep, every
+        one sharded along N over the ranks, as ONE group launch per rank whose epilogue stores
+        every output tile into all ranks' copies, closed by the barrier kernel (TpGroupStep).
+        Strong scaling of the same 752 MB step.  A rank's share of the weights is smaller than
+        L2 from four ranks on, so L2 is flushed before every step (a 256 MiB fill) and the
+        steps are timed one by one with CUDA events; max over ranks."""
+        from mimfer_b200.tp import TpGroupStep
+        torch = self.torch
+        weights, xs, wb = [], [], 0
+        for name in ("gate_up", "down"):
+            K, N = SHAPES[name]
+            for M in DECODE_M:
+                weights.append(self.weight(name))       # TpGroupStep makes a device copy of every shard
+                xs.append(self.acts(M, K))
+                wb += wbytes(K, N)
+        step = TpGroupStep(weights, xs, self.rank, self.world, self.rt)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=self.dev)
+        stream = self.rt.torch_stream()
+        for _ in range(max(warmup, 3)):
+            step.replay()
+        self.rt.sync()
+        regions = []
+        for _ in range(repeats):
+            self.barrier()
+            evs = []
+            with torch.cuda.stream(stream):
+                for _ in range(steps):
+                    flush.fill_(1)
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(stream)
+                    step.replay()
+                    b.record(stream)
+                    evs.append((a, b))
+            self.rt.sync()
+            ms = sum(a.elapsed_time(b) for a, b in evs) / steps
+            t = torch.tensor([ms], device=self.dev)
+            if self.world > 1:
+                self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            regions.append(float(t.item()))
+        status = self.rt.device_status()
+        if status:
+            raise RuntimeError(f"device status 0x{status:x} after the tensor-parallel sweep")
+        # parity: this rank's copy of every output against the CPU oracle, windows at shard edges
+        from oracle.pyoracle import Oracle
+        orc = Oracle()
+        ys = step.replay()
+        self.rt.sync()
+        self.barrier()
+        worst = 0.0
+        for w, x, y in zip(weights, xs, ys):
+            xb = self.rt.from_device_bf16(x)
+            ns = w.N // self.world
+            for e in sorted({0, ns * (self.world // 2), ns * (self.world - 1)}):
+                a = max(0, e - 128)
+                got = self.rt.from_device_bf16(y[:, a:a + 256].contiguous())
+                want = orc.gemm_f4(xb, w.payload, w.scales, w.gs, n_begin=a, n_end=a + 256)
+                g = (got.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+                r = (want.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+                den = np.sqrt((r ** 2).sum(axis=1))
+                worst = max(worst, float((np.sqrt(((g - r) ** 2).sum(axis=1)) / np.where(den == 0, 1.0, den)).max()))
+        t = torch.tensor([worst], dtype=torch.float64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        worst = float(t.item())
+        launches = step.engines[0].n_group_launches()
+        # the same step with host buffers: every rank brings the (replicated) activations up from
+        # pinned memory, rank 0 reads all ten full outputs back; one synchronisation per step
+        xh = [x.cpu().pin_memory() for x in xs]
+        yh = [torch.empty(y.shape, dtype=y.dtype).pin_memory() for y in ys]
+
+        def host_step():
+            with torch.cuda.stream(stream):
+                for x, h in zip(xs, xh):
+                    x.copy_(h, non_blocking=True)
+            out = step.replay()
+            if self.rank == 0:
+                with torch.cuda.stream(stream):
+                    for h, y in zip(yh, out):
+                        h.copy_(y, non_blocking=True)
+            self.rt.sync()
+        for _ in range(max(warmup, 3)):
+            host_step()
+        self.barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            host_step()
+        self.barrier()
+        sec = torch.tensor([(time.perf_counter() - t0) / steps], dtype=torch.float64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(sec, op=self.dist.ReduceOp.MAX)
+        sec = float(sec.item())
+        e2e = {"value": wb / sec / 1e9, "unit": "GB/s", "ms_per_step": sec * 1e3,
+               "h2d_bytes_per_step": sum(t.numel() * 2 for t in xh) * self.world,
+               "d2h_bytes_per_step": sum(t.numel() * 2 for t in yh),
+               "call": "TpGroupStep.replay on host activations (every rank uploads them), all ten outputs read "
+                       "back on rank 0",
+               "timing": "host wall clock around a synchronous step, max over ranks"}
+        step.close()
+        del flush
+        torch.cuda.empty_cache()
+        med = statistics.median(regions)
+        return {"ms_per_step": med, "ms_per_step_min": min(regions), "ms_per_step_max": max(regions),
+                "timed_regions": len(regions), "weight_bytes": wb, "weight_gbs": wb / med / 1e6,
+                "weight_gbs_min": wb / max(regions) / 1e6, "weight_gbs_max": wb / min(regions) / 1e6,
+                "group_launches_per_rank": launches, "e2e": e2e, "l2": "flushed before every step (256 MiB fill), steps timed one by one",
+                "parity": {"max_row_rel_l2": worst, "tolerance": 2.0 ** -8, "ok": worst <= 2.0 ** -8,
+                           "checked": "every rank's copy of all ten outputs, 256-column windows at shard edges, "
+                                      "against the CPU oracle"}}
+
     def tp_parity(self, lins, xs, M):
         """The outputs of one more tensor-parallel step against the CPU oracle (checker only):
         every rank's copy of both full outputs, on column windows inside and across the shard
@@ -856,19 +968,24 @@ def run_b200(args):
         tp = b.tp_series(steps, warmup)
         line["tp"] = tp
         if b.world > 1:
-            d = tp["decode_m32"]
-            line.update(value=d["weight_gbs"], ms_per_step=d["ms_per_step"], scaling="strong",
-                        gpu_launches=2 * steps,
-                        config={"workload": f"tensor-parallel gate+up and LM head (N=151936) split along N "
-                                            f"over {b.world} GPUs at M=32, kernel epilogue stores every output "
-                                            f"tile to all ranks (symmetric memory), one barrier per step",
-                                "l2": "537 MB of weights per step across ranks", "peaks": pk["src"]})
-            line["roofline"] = {"bound": "hbm", "kernel": "f4_mx_kernel", "achieved": d["weight_gbs"],
+            sw = b.tp_sweep(steps, warmup)
+            line["tp_sweep"] = sw
+            line.update(value=sw["weight_gbs"], ms_per_step=sw["ms_per_step"], scaling="strong",
+                        value_min=sw["weight_gbs_min"], value_max=sw["weight_gbs_max"],
+                        timed_regions=sw["timed_regions"], gpu_launches=3 * steps,
+                        config={"workload": f"the decode GEMV sweep of the one-GPU line (M in {{1,2,4,8,16}} x "
+                                            f"{{gate+up, down}}, 752 MB of weights per step), every op split along N "
+                                            f"over {b.world} GPUs: per rank one slicing kernel, one group launch whose "
+                                            f"epilogue stores every output tile to all ranks (symmetric memory), one "
+                                            f"barrier kernel",
+                                "l2": sw["l2"], "timing": f"median of {sw['timed_regions']} timed regions of {steps} steps",
+                                "peaks": pk["src"]})
+            line["roofline"] = {"bound": "hbm", "kernel": "f4_mxg_kernel", "achieved": sw["weight_gbs"],
                                 "peak": pk["hbm"] * b.world, "unit": "GB/s",
-                                "frac": d["weight_gbs"] / (pk["hbm"] * b.world), "of": pk["src"], "traffic": None}
+                                "frac": sw["weight_gbs"] / (pk["hbm"] * b.world), "of": pk["src"], "traffic": None}
             line["prefill"] = {"tflops": tp["prefill_m8192"]["tflops"],
                                "ms_per_step": tp["prefill_m8192"]["ms_per_step"]}
-            line["e2e"] = tp.pop("e2e")
+            line["e2e"] = sw.pop("e2e")
     line["clocks"] = clk.summary()
     if b.rank == 0:
         if b.world == 1 and not args.no_cpu:

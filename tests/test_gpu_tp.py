@@ -182,3 +182,52 @@ def test_rank_that_runs_ahead_does_not_overwrite_a_slow_readers_output(tmp_path,
         for r in range(world):
             got = np.load(tmp_path / f"h{s}_{r}.npy")
             assert row_rel_l2(got, want) <= REL_L2_TOL, (s, r)
+
+
+GROUP_CASES = [(1, 1024, 512), (16, 2048, 1024), (5, 512, 2064)]
+
+
+def _group_worker(rank, world, port, out_dir):
+    """Three decode linears of one step as one group launch per rank (TpGroupStep), replayed
+    three times on changing activations; every rank saves its copy of every output."""
+    torch, dist = _init(rank, world, port)
+    import mimfer_b200 as mm
+    from mimfer_b200.tp import TpGroupStep
+    rt = mm.Runtime.get(rank)
+    ws = [mm.make_weight(N, K, seed=20 + i) for i, (M, K, N) in enumerate(GROUP_CASES)]
+    xs = [rt.to_device_bf16(mm.make_activations(M, K, seed=1)) for (M, K, N) in GROUP_CASES]
+    feeds = [[rt.to_device_bf16(mm.make_activations(M, K, seed=400 + 10 * s + i))
+              for i, (M, K, N) in enumerate(GROUP_CASES)] for s in range(3)]
+    torch.cuda.synchronize()
+    step = TpGroupStep(ws, xs, rank, world, rt)
+    assert step.engines[0].n_group_launches() == 1
+    stream = rt.torch_stream()
+    for s in range(3):
+        with torch.cuda.stream(stream):
+            for x, f in zip(xs, feeds[s]):
+                x.copy_(f, non_blocking=True)
+        ys = step.replay()
+        rt.sync()
+        assert rt.device_status() == 0
+        for i, y in enumerate(ys):
+            np.save(os.path.join(out_dir, f"s{s}_{i}_{rank}.npy"), rt.from_device_bf16(y))
+    step.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gpu_group_step_matches_oracle(tmp_path, oracle, lib):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import mimfer_b200 as mm
+    from conftest import row_rel_l2
+    world = 2
+    _spawn_bounded(_group_worker, (world, _free_port(), str(tmp_path)), world)
+    for s in range(3):
+        for i, (M, K, N) in enumerate(GROUP_CASES):
+            w = mm.make_weight(N, K, seed=20 + i)
+            want = oracle.gemm_f4(mm.make_activations(M, K, seed=400 + 10 * s + i), w.payload, w.scales, w.gs)
+            got = [np.load(tmp_path / f"s{s}_{i}_{r}.npy") for r in range(world)]
+            assert np.array_equal(got[0], got[1])
+            assert row_rel_l2(got[0], want) <= REL_L2_TOL, (s, i)
