@@ -1038,6 +1038,16 @@ def run_case(b, case, steps, warmup):
         return b.decode_step_64(steps, warmup, layers=8)
     if case == "prefill":          # one 2048 x 5120 x 34816 GEMM
         return b.prefill_sweep(steps, warmup, ms_list=(2048,), names=("gate_up",))
+    if case == "chain_down":       # eight down ops at M=16 that write the same output: eight dependent launches
+        K, N = SHAPES["down"]
+        x, y = b.acts(16, K), b.empty(16, N)
+        ops = [(x, b.dev_weight(b.weight("down")), y) for _ in range(8)]
+        eng = b.engine(ops, group=os.environ.get("MMB_CHAIN_GROUP", "1") != "0")
+        ms = b.timed(eng.launch, steps, warmup, repeats=3)
+        groups = eng.n_group_launches()
+        eng.close()
+        return {"ms_per_step": ms, "us_per_op": ms * 1e3 / 8, "group_launches": groups,
+                "weight_gbs": 8 * wbytes(K, N) / ms / 1e6}
     if case == "prefill_tail":     # down at M=2048: 148 whole tiles + 12 tiles in 10 K slices + the tail kernel
         return b.prefill_sweep(steps, warmup, ms_list=(2048,), names=("down",))
     if case == "prefill_small":

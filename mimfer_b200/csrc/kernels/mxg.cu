@@ -57,9 +57,19 @@ struct __align__(128) MxgGroup {
                               * their last; both zero between launches.  NULL: unit u goes to CTA u mod grid */
     unsigned *counters;      /* arrival counters of the split tiles, zero between launches */
     uint32_t  pad[20];
-    MxgOp     ops[MMB_MXG_MAX_OPS];
 };
-static_assert(sizeof(MxgGroup) <= 32764, "kernel parameter space");
+static_assert(sizeof(MxgGroup) == 128, "MxgGroup layout");
+
+/* The kernel's parameter block: the header and as many op descriptors as the launch
+ * needs, in four sizes (0.8, 2.6, 7.8 and 30.8 KB).  A launch costs with the size of
+ * its parameters: a one-op launch with the 48-op block took 8 to 13 us longer than the
+ * single-op kernel on the same op. */
+template <int NOPS>
+struct __align__(128) MxgParams {
+    MxgGroup grp;
+    MxgOp    ops[NOPS];
+};
+static_assert(sizeof(MxgParams<MMB_MXG_MAX_OPS>) <= 32764, "kernel parameter space");
 
 /* The units of one CTA, in order.  The producer thread decides them (the first is
  * blockIdx.x, the following ones come from a counter all CTAs share, so a CTA takes a
@@ -80,7 +90,7 @@ struct UnitWalk {
     }
     /* by one thread (WARP = false) or by every lane of a warp */
     template <bool WARP>
-    __device__ __forceinline__ bool valid(const MxgGroup &grp)
+    __device__ __forceinline__ bool valid(const MxgGroup &grp, const MxgOp *ops)
     {
         const uint32_t slot = j % MMB_MXG_QUEUE;
         bool ok = mbar_wait(q_full + 8u * slot, (j / MMB_MXG_QUEUE) & 1u, status);
@@ -94,7 +104,7 @@ struct UnitWalk {
         }
         if (!ok || g >= grp.n_units)
             return false;
-        while (op + 1u < grp.n_ops && g >= grp.ops[op + 1u].unit0) op++;
+        while (op + 1u < grp.n_ops && g >= ops[op + 1u].unit0) op++;
         return true;
     }
     __device__ __forceinline__ void next() { j++; }
@@ -155,9 +165,12 @@ __device__ __forceinline__ void mxg_load_planes(const MxgOp &o, const UnitGeom &
     tma_load_2d(st + u.o_sfb, &o.tm_sfb, static_cast<int>(ks * 16u), 0, bar);
 }
 
+template <int NOPS>
 __global__ void __maxnreg__(128)
-f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
+f4_mxg_kernel(const __grid_constant__ MxgParams<NOPS> prm)
 {
+    const MxgGroup &grp = prm.grp;
+    const MxgOp *ops = prm.ops;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t ST = grp.stages, stage_b = grp.stage_b, AB = grp.acc_bufs;
@@ -216,12 +229,12 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
             };
             uint32_t g = blockIdx.x, op = 0;                /* the grid never exceeds the units */
             push(g);
-            while (op + 1u < grp.n_ops && g >= grp.ops[op + 1u].unit0) op++;
-            UnitGeom u = unit_geom(grp.ops[op], g);
+            while (op + 1u < grp.n_ops && g >= ops[op + 1u].unit0) op++;
+            UnitGeom u = unit_geom(ops[op], g);
             const uint32_t first = u.nsteps < ST ? u.nsteps : ST;
             for (uint32_t it = 0; it < first; it++) {
                 mbar_expect_tx(bar_full + 8u * it, u.tx);
-                mxg_load_weights(grp.ops[op], u, base + it * stage_b, u.ks_begin + it, bar_full + 8u * it);
+                mxg_load_weights(ops[op], u, base + it * stage_b, u.ks_begin + it, bar_full + 8u * it);
             }
             if (grp.pdl != MMB_PDL_OFF)
                 grid_dep_launch();
@@ -230,7 +243,7 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
             for (;;) {
                 /* the number of the unit after this one, asked for now and needed at its end */
                 const uint32_t next = grp.sched ? gridDim.x + atomicAdd(grp.sched, 1u) : g + gridDim.x;
-                const MxgOp &o = grp.ops[op];
+                const MxgOp &o = ops[op];
                 for (uint32_t it = 0; it < u.nsteps; it++, gstep++, s = (s + 1u == ST) ? 0u : s + 1u, round += (s == 0u)) {
                     const uint32_t st = base + s * stage_b, bar = bar_full + 8u * s;
                     if (gstep >= first) {
@@ -245,8 +258,8 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
                 if (next >= grp.n_units)
                     break;
                 g = next;
-                while (op + 1u < grp.n_ops && g >= grp.ops[op + 1u].unit0) op++;
-                u = unit_geom(grp.ops[op], g);
+                while (op + 1u < grp.n_ops && g >= ops[op + 1u].unit0) op++;
+                u = unit_geom(ops[op], g);
             }
             if (grp.sched) {
                 /* the CTA that is last to have taken its last number puts the counters back */
@@ -264,8 +277,8 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
         if (lane == 0) {
             UnitWalk w;
             uint32_t s = 0, round = 0, gstep = 0, j = 0;
-            for (w.start(q_ids, q_full, q_empty, grp.status); w.valid<false>(grp); w.next(), j++) {
-                const MxgOp &o = grp.ops[w.op];
+            for (w.start(q_ids, q_full, q_empty, grp.status); w.valid<false>(grp, ops); w.next(), j++) {
+                const MxgOp &o = ops[w.op];
                 const UnitGeom u = unit_geom(o, w.g);
                 const uint32_t buf = AB == 2u ? (j & 1u) : 0u, use = j / AB;
                 if (use >= 1u)                       /* the epilogue has drained this buffer's previous unit */
@@ -299,8 +312,8 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
         UnitWalk w;
         uint32_t s = 0, round = 0, gstep = 0;
         uint32_t s1 = 0, round1 = 0, s2 = 0, round2 = 0;
-        for (w.start(q_ids, q_full, q_empty, grp.status); w.valid<true>(grp); w.next()) {
-            const MxgOp &o = grp.ops[w.op];
+        for (w.start(q_ids, q_full, q_empty, grp.status); w.valid<true>(grp, ops); w.next()) {
+            const MxgOp &o = ops[w.op];
             const UnitGeom u = unit_geom(o, w.g);
             const uint32_t ncol = (u.nb + 31u) >> 5;
             for (uint32_t it = 0; it < u.nsteps; it++, gstep++, s2 = s1, round2 = round1, s1 = s, round1 = round,
@@ -389,8 +402,8 @@ f4_mxg_kernel(const __grid_constant__ MxgGroup grp)
         grid_dep_wait();                                    /* row factors come from the kernel in front */
         UnitWalk w;
         uint32_t j = 0;
-        for (w.start(q_ids, q_full, q_empty, grp.status); w.valid<true>(grp); w.next(), j++) {
-            const MxgOp &o = grp.ops[w.op];
+        for (w.start(q_ids, q_full, q_empty, grp.status); w.valid<true>(grp, ops); w.next(), j++) {
+            const MxgOp &o = ops[w.op];
             const UnitGeom u = unit_geom(o, w.g);
             const uint32_t buf = AB == 2u ? (j & 1u) : 0u, use = j / AB;
             const uint32_t groups = u.nb / 24u;
@@ -643,8 +656,15 @@ f4_xslice_cluster_kernel(const __grid_constant__ XsliceGroup g)
 
 extern "C" int mmb_mxg_init(void)
 {
-    return static_cast<int>(cudaFuncSetAttribute(mmb::f4_mxg_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 MMB_SMEM_MAX));
+    cudaError_t e = cudaFuncSetAttribute(mmb::f4_mxg_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, MMB_SMEM_MAX);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(mmb::f4_mxg_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, MMB_SMEM_MAX);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(mmb::f4_mxg_kernel<12>, cudaFuncAttributeMaxDynamicSharedMemorySize, MMB_SMEM_MAX);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(mmb::f4_mxg_kernel<MMB_MXG_MAX_OPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 MMB_SMEM_MAX);
+    return static_cast<int>(e);
 }
 
 /* Digit planes of one activation tensor with the cluster kernel; -1 when the rows
@@ -677,14 +697,15 @@ extern "C" int mmb_launch_xslice_rows(const void *x, void *scratch, uint32_t M, 
 extern "C" int mmb_launch_mxg(const mmb_group *hg, void *stream, uint32_t *kernels_launched)
 {
     uint32_t launched = 0;
-    static mmb::MxgGroup grp;            /* built in place: 30 KB is too much for the stack of a small thread */
+    static mmb::MxgParams<MMB_MXG_MAX_OPS> prm;   /* built in place: 30 KB is too much for the stack of a small thread */
+    mmb::MxgGroup &grp = prm.grp;
     static mmb::XsliceGroup xs;
     unsigned *status = nullptr;
     int e = mmb_status_word(&status);
     if (e) return e;
     if (hg->n_ops == 0 || hg->n_ops > MMB_MXG_MAX_OPS)
         return static_cast<int>(cudaErrorInvalidValue);
-    memset(&grp, 0, sizeof grp);
+    memset(&prm, 0, sizeof prm);
     memset(&xs, 0, sizeof xs);
     grp.n_ops = hg->n_ops; grp.n_units = hg->n_units; grp.stages = hg->stages; grp.acc_bufs = hg->acc_bufs;
     grp.stage_b = hg->stage_b; grp.pdl = static_cast<uint32_t>(hg->pdl); grp.status = status;
@@ -693,7 +714,7 @@ extern "C" int mmb_launch_mxg(const mmb_group *hg, void *stream, uint32_t *kerne
     uint32_t max_m = 0, max_kx = 0, max_k = 0;
     for (uint32_t i = 0; i < hg->n_ops; i++) {
         const mmb_gop &s = hg->op[i];
-        mmb::MxgOp &d = grp.ops[i];
+        mmb::MxgOp &d = prm.ops[i];
         memcpy(d.tm_payload.bytes, s.tm_payload, 128);
         memcpy(d.tm_scale.bytes, s.tm_scale, 128);
         memcpy(d.tm_planes.bytes, s.tm_planes, 128);
@@ -774,5 +795,15 @@ extern "C" int mmb_launch_mxg(const mmb_group *hg, void *stream, uint32_t *kerne
     }
     if (kernels_launched)
         *kernels_launched = launched + 1u;
-    return static_cast<int>(cudaLaunchKernelEx(&cfg, mmb::f4_mxg_kernel, grp));
+    /* the smallest parameter block that holds the ops (its leading bytes are the larger one's) */
+    if (hg->n_ops <= 1u)
+        return static_cast<int>(cudaLaunchKernelEx(&cfg, mmb::f4_mxg_kernel<1>,
+                                                   *reinterpret_cast<const mmb::MxgParams<1> *>(&prm)));
+    if (hg->n_ops <= 4u)
+        return static_cast<int>(cudaLaunchKernelEx(&cfg, mmb::f4_mxg_kernel<4>,
+                                                   *reinterpret_cast<const mmb::MxgParams<4> *>(&prm)));
+    if (hg->n_ops <= 12u)
+        return static_cast<int>(cudaLaunchKernelEx(&cfg, mmb::f4_mxg_kernel<12>,
+                                                   *reinterpret_cast<const mmb::MxgParams<12> *>(&prm)));
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, mmb::f4_mxg_kernel<MMB_MXG_MAX_OPS>, prm));
 }
