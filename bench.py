@@ -763,7 +763,7 @@ class Bench:
 
     def tp_series(self, steps, warmup):
         """config 5: gate+up and LM head, sharded along N over all ranks, M=32 and M=8192."""
-        from mimfer_b200.tp import TpLinear, TpStep
+        from mimfer_b200.tp import TpGroupStep, TpLinear, TpStep
         out = {"world": self.world}
         modes = ("gather",) if self.world == 1 else ("fused", "gather")
         for mode in modes:
@@ -781,16 +781,25 @@ class Bench:
                     last.barrier()
                 ms_eager = ms = self.timed(step, st, warmup)
                 captured = (mode == "fused" or self.world == 1) and M <= 32   # launch cost matters at decode sizes only
+                ms_two = None
                 if captured:
                     # the same step captured once and replayed: one launch per step and rank
                     graph = TpStep(list(lins.values()), [xs[n] for n in lins])
-                    ms = self.timed(graph.replay, st, warmup)
+                    ms_two = ms = self.timed(graph.replay, st, warmup)
                     del graph
+                    # ... and as one group launch per rank instead of a kernel pair per linear
+                    gstep = TpGroupStep([self.weight(n) for n in lins], [xs[n] for n in lins], self.rank,
+                                        self.world, self.rt)
+                    ms = self.timed(gstep.replay, st, warmup)
+                    gstep.close()
+                    del gstep
                 wb = sum(wbytes(*SHAPES[n]) for n in lins)
                 fl = sum(2.0 * M * SHAPES[n][0] * SHAPES[n][1] for n in lins)
                 res[tag] = {"ms_per_step": ms, "weight_gbs": wb / ms / 1e6, "tflops": fl / ms / 1e9,
-                            "issue": "one CUDA graph per rank" if captured else "op by op",
+                            "issue": "one group launch + barrier per rank, captured" if captured else "op by op",
                             "op_by_op_ms_per_step": ms_eager}
+                if ms_two is not None:
+                    res[tag]["kernel_pair_per_linear_ms_per_step"] = ms_two
                 if mode == modes[0]:
                     res[tag]["parity"] = self.tp_parity(lins, xs, M)
                 for lin in lins.values():
