@@ -93,6 +93,30 @@ def test_engine_validates_descriptors(lib):
     lib.mm_log_set_level(1)
 
 
+def test_engine_tensor_parallel_ops_validate_their_destinations(lib):
+    """mm_lin_engine_add_tp: the op's own output is the first destination, the shard's
+    columns fit the row pitch, at most eight aligned destinations; a refused op is not added."""
+    lib.mm_log_set_level(-1)
+    h = C.c_void_p()
+    assert lib.mm_lin_engine_create(C.byref(h), 4) == L.MM_OK
+    _, op = kcall(a=0x10000, b=0x20000, c=0x50000, d=0x30000, M=4, K=512, N=256)
+    own, peer = op.c, 0x70000
+    ptrs = (C.c_void_p * 2)(own, peer)
+    assert lib.mm_lin_engine_add_tp(h, C.byref(op), ptrs, 2, 512, 256) == L.MM_OK
+    assert lib.mm_lin_engine_add_tp(h, C.byref(op), ptrs, 2, 512, 264) == L.MM_ERR_SHAPE      # 264 + 256 > 512
+    assert lib.mm_lin_engine_add_tp(h, C.byref(op), ptrs, 9, 4096, 0) == L.MM_ERR_RANGE
+    assert lib.mm_lin_engine_add_tp(h, C.byref(op), ptrs, 0, 4096, 0) == L.MM_ERR_RANGE
+    swapped = (C.c_void_p * 2)(peer, own)
+    assert lib.mm_lin_engine_add_tp(h, C.byref(op), swapped, 2, 512, 0) == L.MM_ERR_STATE     # own copy first
+    odd = (C.c_void_p * 2)(own, peer + 2)
+    assert lib.mm_lin_engine_add_tp(h, C.byref(op), odd, 2, 512, 0) == L.MM_ERR_STATE
+    _, silu = kcall(op=L.OP_SILU_MUL)
+    assert lib.mm_lin_engine_add_tp(h, C.byref(silu), ptrs, 2, 512, 0) == L.MM_ERR_STATE
+    assert lib.mm_lin_engine_n_ops(h) == 1
+    lib.mm_lin_engine_destroy(h)
+    lib.mm_log_set_level(1)
+
+
 def test_runtime_refuses_without_gpu(lib):
     import torch
     if torch.cuda.is_available():
