@@ -52,7 +52,7 @@ REPEATS = 7          # timed regions per headline number
 # dram__bytes_read + dram__bytes_write over algorithmic bytes, from an ncu capture of the group
 # kernel on two gate+up ops at M=1 and M=16; traffic grows with the weight bytes, so the
 # per-launch figure of the sweep is this ratio times its algorithmic bytes.
-GROUP_TRAFFIC_RATIO = 1.02
+GROUP_TRAFFIC_RATIO = 1.03
 
 
 def wbytes(K, N):
