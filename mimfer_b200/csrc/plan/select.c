@@ -221,12 +221,11 @@ mm_status mmb_plan_stream_with(const mm_f4_shape *s, uint32_t rows, uint32_t spl
     return st != MM_OK ? st : plan_stream_with(s, rows ? rows : MMB_ST_ROWS, split, p);
 }
 
-/* modelled cost of one CTA tile, in MMA time of a 256 x 256 tile = 65536.  A K block
- * takes the longer of its MMAs (proportional to tile_m * tile_n) and of the
- * dequantise-and-hand-over chain of the eight warps that prepare its weights
- * (lds, unpack, sts, proxy fence, barrier), which does not shrink with the tile:
- * measured on B200, 64-wide K blocks take 0.55 us on 256 x 256 tiles and 0.45-0.5 us on
- * 128 x 128 ones (k at M = 2048: 128 tiles, 80 K blocks, 44 us). */
+/* modelled cost of one CTA tile, in MMA time of a 256 x 256 tile = 65536.  A K block's
+ * time does not shrink with the tile below about 0.85 of a 256 x 256 tile's: measured
+ * on B200, 64-wide K blocks take 0.55 us on 256 x 256 tiles and 0.45-0.5 us on 128 x 128
+ * ones (k at M = 2048: 128 tiles, 80 K blocks, 44 us), whether four or eight warps
+ * prepare a block's weights. */
 static double umma_tile_cost(uint32_t bm, uint32_t bn)
 {
     const double mma = (double)bm * bn, chain = 0.85 * 65536.0;
