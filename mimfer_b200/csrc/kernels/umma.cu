@@ -12,7 +12,8 @@
  *               packed payload (BN rows x 32 B per 64-wide K block) and block
  *               scales (BN rows x 16 B per 256-wide K group).
  *   warp 1      owns tensor memory; one lane issues the MMAs and commits.
- *   warps 2-9   dequantise: 16-byte shared load of 32 nibbles, unpack + scale
+ *   warps 2-9   dequantise (two groups of four warps, alternate K blocks): 16-byte
+ *               shared load of 32 nibbles, unpack + scale
  *               in registers (fp4.cuh), 16-byte stores into the K-major
  *               swizzled B tile, fence.proxy.async, mbarrier hand-off to warp 1.
  *               After the K loop the same warps drain tensor memory:
