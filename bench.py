@@ -1059,6 +1059,8 @@ def run_case(b, case, steps, warmup):
                 "weight_gbs": 8 * wbytes(K, N) / ms / 1e6}
     if case == "prefill_tail":     # down at M=2048: 148 whole tiles + 12 tiles in 10 K slices + the tail kernel
         return b.prefill_sweep(steps, warmup, ms_list=(2048,), names=("down",))
+    if case == "prefill_kv":       # k at M=2048: 32 tiles, all of them split
+        return b.prefill_sweep(steps, warmup, ms_list=(2048,), names=("k",))
     if case == "prefill_small":
         return b.prefill_sweep(steps, warmup, ms_list=(512,), names=("q",))
     raise SystemExit(f"unknown case {case}")

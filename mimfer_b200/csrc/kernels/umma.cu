@@ -56,7 +56,7 @@ struct UmmaParams {
     uint32_t  m_tiles;       /* activation-row tiles (tile id = n_tile * m_tiles + m_tile) */
     uint32_t  full_tiles;    /* tiles that run whole; the ones after them are split      */
     uint32_t  splits;        /* K slices of every tile after full_tiles (>= 1)           */
-    float    *partial;       /* [split tile][slice][BM][BN] fp32 sums                    */
+    float    *partial;       /* [split tile][slice][half][32-column chunk][4-column group][128 rows][4] fp32 sums */
 };
 
 
@@ -283,17 +283,19 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
              * the slices and writes the output */
             const uint32_t st_idx = tile - p.full_tiles;
             float *mine = p.partial + (static_cast<size_t>(st_idx) * n_slices + slice) * TILE_F;
+            /* layout of a slice: [half][32-column chunk][group of 4 columns][128 rows] float4, i.e.
+             * the order tensor memory is read in: a warp's store is 512 contiguous bytes */
             for (uint32_t h = 0; h < HALVES; h++) {
-                const uint32_t row = h * 128u + quad * 32u + lane;
                 for (uint32_t c32 = pair * (BN / 64u); c32 < (pair + 1u) * (BN / 64u); c32++) {
                     uint32_t r[32];
                     tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + h * BN + c32 * 32u, r);
                     tmem_ld_wait();
-                    float4 *dst = reinterpret_cast<float4 *>(mine + static_cast<size_t>(row) * BN + c32 * 32u);
+                    float4 *dst = reinterpret_cast<float4 *>(mine) +
+                                  static_cast<size_t>(h * (BN / 32u) + c32) * 8u * 128u + quad * 32u + lane;
 #pragma unroll
                     for (int j = 0; j < 8; j++)
-                        __stcg(dst + j, make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                                    __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+                        __stcg(dst + j * 128, make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                          __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
                 }
             }
         }
@@ -415,10 +417,11 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
 }
 
 /* ---- the split tiles' outputs ----------------------------------------------------
- * Every thread owns eight output columns of one row of one split tile: it adds the
- * K slices' sums in ascending order (two 16-byte loads per slice, or four for a
- * gated pair, several slices in flight), applies the epilogue of the main kernel
- * and stores 16 bytes to every destination. */
+ * One CTA per (split tile, 128-row half, 32 output columns).  A thread owns 16 columns of
+ * one row: it adds the K slices' sums in ascending order (four 16-byte loads per slice,
+ * lanes along the rows, which is how the slices were stored), applies the epilogue of the
+ * main kernel and puts its 32 bytes into a shared tile; the tile then goes out as 64-byte
+ * row runs to every destination. */
 struct UmmaTailParams {
     uint16_t    *y[MMB_MAX_PEERS];
     uint32_t     n_dst, ldy, col0;
@@ -432,67 +435,73 @@ struct UmmaTailParams {
 
 __global__ void __launch_bounds__(256) f4_umma_tail_kernel(const UmmaTailParams p)
 {
+    __shared__ __align__(16) uint16_t tile_s[128][40];         /* 32 columns + 8 of padding per row */
     grid_dep_launch();
     if (p.pdl != MMB_PDL_OFF)
         grid_dep_wait();                         /* the main kernel's partial sums */
-    const uint32_t out_cols = p.glu ? p.bn / 2u : p.bn;
-    const uint32_t per_row = out_cols / 8u;                    /* threads per row: 16 or 32 */
-    const uint32_t rows_per_cta = 256u / per_row;
+    const uint32_t chunks = p.bn / 32u;                        /* 32-column chunks of the accumulators */
+    const uint32_t out_chunks = p.glu ? chunks / 2u : chunks;
+    const uint32_t h = blockIdx.x / out_chunks, oc = blockIdx.x % out_chunks;
     const uint32_t st_idx = blockIdx.y, tile = p.full_tiles + st_idx;
-    const uint32_t row = blockIdx.x * rows_per_cta + threadIdx.x / per_row;
-    const uint32_t c8 = (threadIdx.x % per_row) * 8u;           /* first of this thread's output columns */
-    const uint32_t m = (tile % p.m_tiles) * p.bm + row, n = (tile / p.m_tiles) * out_cols + c8;
-    if (row >= p.bm || m >= p.M || n >= p.N)
-        return;
-    const size_t tile_f = static_cast<size_t>(p.bm) * p.bn;
-    const float *src = p.partial + static_cast<size_t>(st_idx) * p.splits * tile_f + static_cast<size_t>(row) * p.bn;
-    const uint32_t col_a = p.glu ? (p.gate_plane ? p.bn / 2u : 0u) + c8 : c8;
-    const uint32_t col_b = p.glu ? (p.gate_plane ? 0u : p.bn / 2u) + c8 : c8;
-    float a[8], b[8];
+    const uint32_t row = threadIdx.x & 127u, jh = threadIdx.x >> 7;      /* row of the half; columns 16 * jh .. + 15 */
+    const size_t slice_f4 = static_cast<size_t>(p.bm) * p.bn / 4u;
+    const float4 *base = reinterpret_cast<const float4 *>(p.partial) + static_cast<size_t>(st_idx) * p.splits * slice_f4;
+    /* chunk of the first operand (the only one, or the gate's) and of the up projection */
+    const uint32_t gate_off = p.glu && p.gate_plane ? chunks / 2u : 0u, up_off = p.glu && !p.gate_plane ? chunks / 2u : 0u;
+    const size_t ia = (static_cast<size_t>(h * chunks + gate_off + oc) * 8u + jh * 4u) * 128u + row;
+    const size_t ib = (static_cast<size_t>(h * chunks + up_off + oc) * 8u + jh * 4u) * 128u + row;
+    float a[16], b[16];
 #pragma unroll
-    for (int i = 0; i < 8; i++) a[i] = b[i] = 0.0f;
-    for (uint32_t s0 = 0; s0 < p.splits; s0 += 4u) {
-        float4 va[4][2], vb[4][2];
+    for (int i = 0; i < 16; i++) a[i] = b[i] = 0.0f;
+    for (uint32_t s0 = 0; s0 < p.splits; s0 += 2u) {
+        float4 va[2][4], vb[2][4];
 #pragma unroll
-        for (uint32_t j = 0; j < 4u; j++) {
-            const bool live = s0 + j < p.splits;
-            const float *base = src + static_cast<size_t>(live ? s0 + j : s0) * tile_f;
-            va[j][0] = __ldcg(reinterpret_cast<const float4 *>(base + col_a));
-            va[j][1] = __ldcg(reinterpret_cast<const float4 *>(base + col_a) + 1);
-            if (p.glu) {
-                vb[j][0] = __ldcg(reinterpret_cast<const float4 *>(base + col_b));
-                vb[j][1] = __ldcg(reinterpret_cast<const float4 *>(base + col_b) + 1);
-            } else {
-                vb[j][0] = vb[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t j = 0; j < 2u; j++) {
+            const float4 *sl = base + static_cast<size_t>(s0 + j < p.splits ? s0 + j : s0) * slice_f4;
+#pragma unroll
+            for (uint32_t q = 0; q < 4u; q++) {
+                va[j][q] = __ldcg(sl + ia + q * 128u);
+                vb[j][q] = p.glu ? __ldcg(sl + ib + q * 128u) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
 #pragma unroll
-        for (uint32_t j = 0; j < 4u; j++) {
+        for (uint32_t j = 0; j < 2u; j++) {
             if (s0 + j >= p.splits)
                 break;
-            a[0] += va[j][0].x; a[1] += va[j][0].y; a[2] += va[j][0].z; a[3] += va[j][0].w;
-            a[4] += va[j][1].x; a[5] += va[j][1].y; a[6] += va[j][1].z; a[7] += va[j][1].w;
-            b[0] += vb[j][0].x; b[1] += vb[j][0].y; b[2] += vb[j][0].z; b[3] += vb[j][0].w;
-            b[4] += vb[j][1].x; b[5] += vb[j][1].y; b[6] += vb[j][1].z; b[7] += vb[j][1].w;
+#pragma unroll
+            for (uint32_t q = 0; q < 4u; q++) {
+                a[4 * q] += va[j][q].x; a[4 * q + 1] += va[j][q].y; a[4 * q + 2] += va[j][q].z; a[4 * q + 3] += va[j][q].w;
+                b[4 * q] += vb[j][q].x; b[4 * q + 1] += vb[j][q].y; b[4 * q + 2] += vb[j][q].z; b[4 * q + 3] += vb[j][q].w;
+            }
         }
     }
-    uint4 o;
+    uint32_t o[8];
     if (p.glu) {
         const float sg = p.gs * 256.0f, su = p.gs_up * 256.0f;
-        o.x = glu_out_bf16x2(a[0], a[1], b[0], b[1], sg, su);
-        o.y = glu_out_bf16x2(a[2], a[3], b[2], b[3], sg, su);
-        o.z = glu_out_bf16x2(a[4], a[5], b[4], b[5], sg, su);
-        o.w = glu_out_bf16x2(a[6], a[7], b[6], b[7], sg, su);
+#pragma unroll
+        for (int i = 0; i < 8; i++) o[i] = glu_out_bf16x2(a[2 * i], a[2 * i + 1], b[2 * i], b[2 * i + 1], sg, su);
     } else {
         const float sc = p.gs * 256.0f;
-        o.x = pack_bf16x2(a[0] * sc, a[1] * sc);
-        o.y = pack_bf16x2(a[2] * sc, a[3] * sc);
-        o.z = pack_bf16x2(a[4] * sc, a[5] * sc);
-        o.w = pack_bf16x2(a[6] * sc, a[7] * sc);
+#pragma unroll
+        for (int i = 0; i < 8; i++) o[i] = pack_bf16x2(a[2 * i] * sc, a[2 * i + 1] * sc);
     }
-    const size_t off = static_cast<size_t>(m) * p.ldy + p.col0 + n;
-    for (uint32_t d = 0; d < p.n_dst; d++)
-        *reinterpret_cast<uint4 *>(p.y[d] + off) = o;
+    *reinterpret_cast<uint4 *>(&tile_s[row][jh * 16u]) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4 *>(&tile_s[row][jh * 16u + 8u]) = make_uint4(o[4], o[5], o[6], o[7]);
+    __syncthreads();
+    /* 128 rows x 64 bytes: four threads per row, two rows of the tile per thread */
+    const uint32_t m0 = (tile % p.m_tiles) * p.bm + h * 128u;
+    const uint32_t n0 = (tile / p.m_tiles) * (out_chunks * 32u) + oc * 32u;
+#pragma unroll
+    for (uint32_t k = 0; k < 2u; k++) {
+        const uint32_t idx = threadIdx.x + k * 256u, r = idx >> 2, piece = idx & 3u;
+        const uint32_t m = m0 + r, n = n0 + piece * 8u;
+        if (m >= p.M || n >= p.N)
+            continue;
+        const uint4 v = *reinterpret_cast<const uint4 *>(&tile_s[r][piece * 8u]);
+        const size_t off = static_cast<size_t>(m) * p.ldy + p.col0 + n;
+        for (uint32_t d = 0; d < p.n_dst; d++)
+            *reinterpret_cast<uint4 *>(p.y[d] + off) = v;
+    }
 }
 
 template <int BM, int BN, bool GLU>
@@ -546,9 +555,8 @@ static int launch_tile(const mmb_args *a, unsigned *status, cudaStream_t st)
     t.M = p.M; t.N = p.N; t.bm = BM; t.bn = BN;
     t.m_tiles = p.m_tiles; t.full_tiles = p.full_tiles; t.splits = p.splits;
     t.pdl = p.pdl;
-    const uint32_t per_row = (GLU ? BN / 2 : BN) / 8u;
     cudaLaunchConfig_t tc = {};
-    tc.gridDim = dim3(BM / (256u / per_row), tiles - p.full_tiles);
+    tc.gridDim = dim3((BM / 128u) * ((GLU ? BN / 2 : BN) / 32u), tiles - p.full_tiles);
     tc.blockDim = dim3(256);
     tc.stream = st;
     tc.attrs = attr;
