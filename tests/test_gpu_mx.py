@@ -378,3 +378,50 @@ def test_group_launch_of_tensor_parallel_ops(rt, oracle):
             assert row_rel_l2(a[:, h:], want) <= REL_L2_TOL, shapes[i]
     finally:
         eng.close()
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_groups(rt, oracle, seed):
+    """Seeded random groups: 1 to 14 ops of random decode shapes (ragged N, K from 256 to 8192,
+    M from 1 to 32, some sharing activations), captured and replayed twice, every output
+    against the oracle.  Exercises the planner's K-split search, the unit hand-out and the
+    split-K exchange on launches of very different lengths."""
+    torch = rt.torch
+    rng = np.random.Generator(np.random.PCG64(1000 + seed))
+    n_ops = int(rng.integers(1, 15))
+    ws, xb, xs, ys, shapes = [], [], [], [], []
+    for i in range(n_ops):
+        M = int(rng.choice([1, 2, 3, 4, 7, 8, 16, 17, 32]))
+        K = 256 * int(rng.choice([1, 2, 4, 8, 20, 32]))
+        N = int(rng.choice([8, 40, 136, 256, 600, 1000, 1024, 2048, 3000]))
+        if i and rng.random() < 0.3 and shapes[-1][1] == K:      # reads the activations of the op in front
+            M = shapes[-1][0]
+            xb.append(xb[-1])
+            xs.append(xs[-1])
+        else:
+            xb.append(mm.make_activations(M, K, seed=int(rng.integers(1 << 30))))
+            xs.append(rt.to_device_bf16(xb[-1]))
+        shapes.append((M, K, N))
+        ws.append(mm.make_weight(N, K, seed=int(rng.integers(1 << 30))).to_device(rt.device))
+        ys.append(torch.zeros((M, N), dtype=torch.bfloat16, device=rt.device))
+    torch.cuda.synchronize()
+    eng = mm.LinearEngine(rt, max_ops=16)
+    try:
+        for x, w, y in zip(xs, ws, ys):
+            eng.add(x, w, y)
+        eng.capture()
+        first = None
+        for _ in range(2):
+            eng.launch()
+            rt.sync()
+            assert rt.device_status() == 0
+            got = [rt.from_device_bf16(y) for y in ys]
+            if first is not None:
+                assert all(np.array_equal(a, b) for a, b in zip(first, got))       # replays give the same bits
+            first = got
+        assert eng.n_group_launches() >= 1
+        for i, w in enumerate(ws):
+            want = oracle.gemm_f4(xb[i], w.payload, w.scales, w.gs)
+            assert row_rel_l2(first[i], want) <= REL_L2_TOL, (seed, i, shapes[i])
+    finally:
+        eng.close()
