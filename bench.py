@@ -619,9 +619,11 @@ class Bench:
         """The N=1 headline workload, tensor-parallel: the ten ops of the decode sweep, every
         one sharded along N over the ranks, as ONE group launch per rank whose epilogue stores
         every output tile into all ranks' copies, closed by the barrier kernel (TpGroupStep).
-        Strong scaling of the same 752 MB step.  A rank's share of the weights is smaller than
-        L2 from four ranks on, so L2 is flushed before every step (a 256 MiB fill) and the
-        steps are timed one by one with CUDA events; max over ranks."""
+        Strong scaling of the same 752 MB step.  While a rank's share of the weights is at
+        least twice the 126 MB L2 (two ranks: 376 MB) the steps run back to back like the
+        one-GPU sweep; below that (four ranks: 188 MB, eight: 94 MB) L2 is flushed before every
+        step (a 256 MiB fill) and the steps are timed one by one with CUDA events.  Max over
+        ranks either way; MMB_TP_SWEEP_FLUSH=0/1 forces one form."""
         from mimfer_b200.tp import TpGroupStep
         torch = self.torch
         weights, xs, wb = [], [], 0
@@ -634,6 +636,9 @@ class Bench:
         step = TpGroupStep(weights, xs, self.rank, self.world, self.rt)
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=self.dev)
         stream = self.rt.torch_stream()
+        do_flush = wb // self.world < 2 * (126 << 20)
+        if os.environ.get("MMB_TP_SWEEP_FLUSH") in ("0", "1"):
+            do_flush = os.environ["MMB_TP_SWEEP_FLUSH"] == "1"
         for _ in range(max(warmup, 3)):
             step.replay()
         self.rt.sync()
@@ -642,11 +647,19 @@ class Bench:
             self.barrier()
             evs = []
             with torch.cuda.stream(stream):
-                for _ in range(steps):
-                    flush.fill_(1)
+                if do_flush:
+                    for _ in range(steps):
+                        flush.fill_(1)
+                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        a.record(stream)
+                        step.replay()
+                        b.record(stream)
+                        evs.append((a, b))
+                else:
                     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     a.record(stream)
-                    step.replay()
+                    for _ in range(steps):
+                        step.replay()
                     b.record(stream)
                     evs.append((a, b))
             self.rt.sync()
@@ -720,7 +733,9 @@ class Bench:
         return {"ms_per_step": med, "ms_per_step_min": min(regions), "ms_per_step_max": max(regions),
                 "timed_regions": len(regions), "weight_bytes": wb, "weight_gbs": wb / med / 1e6,
                 "weight_gbs_min": wb / max(regions) / 1e6, "weight_gbs_max": wb / min(regions) / 1e6,
-                "group_launches_per_rank": launches, "e2e": e2e, "l2": "flushed before every step (256 MiB fill), steps timed one by one",
+                "group_launches_per_rank": launches, "e2e": e2e,
+                "l2": "flushed before every step (256 MiB fill), steps timed one by one" if do_flush
+                      else f"every rank reads {wb // self.world >> 20} MB of weights per step, more than twice L2; steps back to back",
                 "parity": {"max_row_rel_l2": worst, "tolerance": 2.0 ** -8, "ok": worst <= 2.0 ** -8,
                            "checked": "every rank's copy of all ten outputs, 256-column windows at shard edges, "
                                       "against the CPU oracle"}}

@@ -182,6 +182,19 @@ def test_umma_tail_split_matches_whole_tiles(rt, oracle, M, K, N):
     assert row_rel_l2(a, b) <= REL_L2_TOL / 4          # two roundings of different fp32 sums
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_umma_random_shapes(rt, oracle, seed):
+    """Seeded random prefill shapes (ragged M and N, short and long K, tail split or not),
+    sampled rows against the oracle."""
+    rng = np.random.Generator(np.random.PCG64(500 + seed))
+    M = int(rng.choice([33, 100, 129, 300, 700, 1500, 3000]))
+    K = 256 * int(rng.choice([1, 2, 4, 12, 20, 32]))
+    N = 8 * int(rng.integers(1, 700))
+    assert mm.select_plan(M, K, N, ws_bytes=rt.lib.mm_f4_workspace_bytes() // 8).variant == V_UMMA
+    rows = sorted(set([0, M - 1, M // 2] + [int(v) for v in rng.integers(0, M, 5)]))
+    check(rt, oracle, M, K, N, None, seed=seed, sample_rows=rows)
+
+
 def test_umma_prefill_gate_up_sampled(rt, oracle):
     M, K, N = 2048, 5120, 34816
     check(rt, oracle, M, K, N, None, seed=0, sample_rows=[0, 255, 256, 1023, 2047])
