@@ -100,6 +100,12 @@ mm_status mm_lin_engine_bind_host(mm_lin_engine *e, const void *const *x_host, v
     MM_REQUIRE(e && e->n_ops > 0, MM_ERR_STATE);
     MM_REQUIRE(!e->captured, MM_ERR_BUSY);
     e->bound = 0;
+    /* the output of a tensor-parallel op is a column slice of a wider buffer, completed by
+     * the other ranks: it has no host destination of its own (read the full buffer after
+     * the step's barrier) */
+    for (uint32_t i = 0; y_host && i < e->n_ops; i++)
+        if (e->tp[i].n && y_host[i])
+            return MM_ERR_UNSUPPORTED;
     for (uint32_t i = 0; i < e->n_ops; i++) {
         e->x_bound[i] = x_host ? x_host[i] : NULL;
         e->y_bound[i] = y_host ? y_host[i] : NULL;
