@@ -649,6 +649,9 @@ mm_status mm_lin_engine_launch_host(mm_lin_engine *e, const void *const *x_host,
     MM_REQUIRE(e && e->n_ops > 0, MM_ERR_STATE);
     MM_REQUIRE(!mm_cuda_capturing(), MM_ERR_BUSY);
     MM_REQUIRE(!(e->captured && e->bound_captured), MM_ERR_BUSY);   /* that graph already copies */
+    for (uint32_t i = 0; y_host && i < e->n_ops; i++)
+        if (e->tp[i].n && y_host[i])
+            return MM_ERR_UNSUPPORTED;                                 /* a column slice of a wider buffer */
     for (uint32_t i = 0; x_host && i < e->n_ops; i++) {
         const mm_op_desc *op = &e->ops[i];
         if (x_host[i] && op->op != OP_NOP)
