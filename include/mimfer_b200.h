@@ -424,7 +424,9 @@ mm_status mm_lin_engine_add(mm_lin_engine *e, const mm_op_desc *op);
  * features are this rank's shard of a wider output; the kernel stores them at column
  * `col0` of every rank's [M][ldy] copy of it, y_all[0] == op->c being this rank's own
  * (peer-mapped pointers for the others, as for mm_f4_linear_tp).  Such ops join group
- * launches like any decode op; close a step with mm_f4_tp_barrier. */
+ * launches like any decode op; close a step with mm_f4_tp_barrier.  Such an op takes no
+ * host output buffer (mm_lin_engine_bind_host and mm_lin_engine_launch_host refuse one):
+ * its output is a column slice of a buffer the other ranks complete. */
 mm_status mm_lin_engine_add_tp(mm_lin_engine *e, const mm_op_desc *op, void *const *y_all, uint32_t n_ranks,
                                uint32_t ldy, uint32_t col0);
 uint32_t  mm_lin_engine_n_ops(const mm_lin_engine *e);
@@ -456,13 +458,16 @@ uint32_t  mm_lin_engine_n_independent(const mm_lin_engine *e);
  * the last dispatch or capture were turned into digit planes ahead of the ops, on
  * the transfer stream (inputs of the step that no earlier op of the list writes). */
 uint32_t  mm_lin_engine_n_sliced_ahead(const mm_lin_engine *e);
-/* on != 0: group mode.  Runs of consecutive decode linears (M <= 32) that share no
- * memory with each other - q, k and v of a layer, gate and up, a benchmark's
- * stand-alone linears - become ONE persistent launch of the block-scaled kernel:
- * the CTAs walk the ops' work units in turn and the weight stream does not stop
- * between ops (up to 48 ops per launch; an activation tensor several ops read is
- * sliced once).  Results are those of the single launches.  Needs a workspace of
- * at least 32 MiB.  Off by default; before capture.
+/* on != 0 (the default): group mode.  Runs of consecutive decode linears (M <= 32)
+ * that share no memory with each other - q, k and v of a layer, gate and up, a
+ * benchmark's stand-alone linears - become ONE persistent launch of the
+ * block-scaled kernel: the CTAs take the ops' work units one after the other from
+ * a shared counter and the weight stream does not stop between ops (up to 48 ops
+ * per launch; an activation tensor several ops read is sliced once; inside a launch
+ * the ops run in order of activation rows, most first).  Results are those of the
+ * single launches up to the places where K is cut.  Needs a workspace of at least
+ * 32 MiB; without one, and for ops the block-scaled kernel does not take, the ops
+ * are dispatched one by one.  Before capture.
  * mm_lin_engine_n_group_launches: group launches of the last dispatch or capture. */
 mm_status mm_lin_engine_group(mm_lin_engine *e, int on);
 uint32_t  mm_lin_engine_n_group_launches(const mm_lin_engine *e);
