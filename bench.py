@@ -780,12 +780,14 @@ class Bench:
         """config 5: gate+up and LM head, sharded along N over all ranks, M=32 and M=8192."""
         from mimfer_b200.tp import TpGroupStep, TpLinear, TpStep
         out = {"world": self.world}
-        modes = ("gather",) if self.world == 1 else ("fused", "gather")
+        modes = ("gather",) if self.world == 1 else ("fused", "push", "gather")
         for mode in modes:
             lins = {n: TpLinear(self.weight(n), self.rank, self.world, rt=self.rt, mode=mode)
                     for n in ("gate_up", "lm_head")}
             res = {}
             for tag, M, st in (("decode_m32", 32, steps), ("prefill_m8192", 8192, max(2, steps // 4))):
+                if mode == "push" and M <= 32:      # the copy engines' form is for prefill-size outputs
+                    continue
                 xs = {n: self.acts(M, SHAPES[n][0]) for n in lins}
 
                 last = list(lins.values())[-1]
@@ -815,7 +817,7 @@ class Bench:
                             "op_by_op_ms_per_step": ms_eager}
                 if ms_two is not None:
                     res[tag]["kernel_pair_per_linear_ms_per_step"] = ms_two
-                if mode == modes[0]:
+                if mode in ("fused", "push") or self.world == 1:
                     res[tag]["parity"] = self.tp_parity(lins, xs, M)
                 for lin in lins.values():
                     lin._bufs.clear()
@@ -864,11 +866,19 @@ class Bench:
         else:
             one = {tag: out[modes[0]][tag]["ms_per_step"] for tag in ("decode_m32", "prefill_m8192")}
         out["one_gpu_ms_per_step"] = one
-        out["efficiency"] = {tag: one[tag] / (self.world * out[modes[0]][tag]["ms_per_step"])
-                             for tag in ("decode_m32", "prefill_m8192")}
         best = modes[0]
         out["mode"] = best + (" (kernel epilogue stores to peers)" if best == "fused" else " (single GPU)")
         out.update(out[best])
+        if "push" in out:
+            # prefill: the exchange by the epilogue's stores or by the copy engines, whichever is faster here
+            out["prefill_exchange"] = {"epilogue_stores_ms": out["fused"]["prefill_m8192"]["ms_per_step"],
+                                       "copy_engines_ms": out["push"]["prefill_m8192"]["ms_per_step"]}
+            if out["push"]["prefill_m8192"]["ms_per_step"] < out["fused"]["prefill_m8192"]["ms_per_step"]:
+                out["prefill_m8192"] = dict(out["push"]["prefill_m8192"],
+                                            issue="row chunks; each chunk's slice pushed to the peers by the copy "
+                                                  "engines while the next chunk is multiplied")
+        out["efficiency"] = {tag: one[tag] / (self.world * out[tag]["ms_per_step"])
+                             for tag in ("decode_m32", "prefill_m8192")}
         return out
 
 

@@ -268,6 +268,21 @@ mm_status mm_f4_linear_tp(const void *x, const void *payload, const void *scale,
  * MM_ERR_TIMEOUT from the synchronising calls) instead of hanging the GPU. */
 mm_status mm_f4_tp_barrier(void *const *flags_all, uint32_t n_ranks, uint32_t rank, void *stream);
 
+/* The exchange by the copy engines instead of the epilogue's stores (no counterpart in
+ * the reference).  A rank runs mm_f4_linear_tp with n_ranks = 1 (its own copy only), on
+ * the whole activations or on a chunk of rows, and then pushes what that call wrote:
+ * columns [col0, col0 + cols) of rows [row0, row0 + rows) of y_all[0] go to the same
+ * place in y_all[1 .. n_ranks - 1], one two-dimensional copy per peer, each on a side
+ * stream of its own that waits for the compute stream's work up to this call.  The
+ * compute stream itself goes on, so the next chunk's GEMM runs while the copy engines
+ * drain this one over NVLink.  mm_f4_tp_push_join makes the compute stream wait for every
+ * push since the last join; call it before mm_f4_tp_barrier.  ldy, col0 and cols are
+ * multiples of 8 (16-byte rows); MM_ERR_SHAPE otherwise.  Inside a stream capture the
+ * side streams join the capture, and the join must come before the capture ends. */
+mm_status mm_f4_tp_push(void *const *y_all, uint32_t n_ranks, uint32_t ldy, uint32_t col0, uint32_t cols,
+                        uint32_t row0, uint32_t rows);
+mm_status mm_f4_tp_push_join(void);
+
 /* No counterpart in the reference.  The decode kernel of mm_f4_linear with its
  * split-K scratch built in, for callers that cannot hand over a workspace and
  * may not allocate one: code that runs under mimfer's rule that device memory

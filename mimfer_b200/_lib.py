@@ -130,6 +130,8 @@ SIGNATURES = {
     "mm_f4_select_variant": (C.c_int, [C.POINTER(F4Shape), C.c_int, C.POINTER(F4Plan)]),
     "mm_f4_force_variant": (None, [C.c_int]),
     "mm_f4_linear": (C.c_int, [_vp, _vp, _vp, _f, _vp, _u32, _u32, _u32, _vp]),
+    "mm_f4_tp_push": (C.c_int, [C.POINTER(C.c_void_p), _u32, _u32, _u32, _u32, _u32, _u32]),
+    "mm_f4_tp_push_join": (C.c_int, []),
     "mm_lin_engine_add_tp": (C.c_int, [_vp, C.POINTER(MmOpDesc), C.POINTER(C.c_void_p), _u32, _u32, _u32]),
     "mm_f4_device_status_on": (C.c_int, [_vp, C.POINTER(C.c_uint)]),
     "mm_f4_xslice_bytes": (_sz, [_u32, _u32]),

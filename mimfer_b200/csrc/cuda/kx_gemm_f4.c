@@ -1233,6 +1233,61 @@ mm_status mm_f4_tp_barrier(void *const *flags_all, uint32_t n_ranks, uint32_t ra
     return MM_OK;
 }
 
+/* The exchange of a tensor-parallel linear by the copy engines.  A prefill-size output
+ * slice is hundreds of megabytes per rank: stored from the kernel's epilogue it holds the
+ * SM until NVLink has taken it; pushed by the copy engines it leaves while the next row
+ * chunk is multiplied.  One side stream and one event per peer, made on first use. */
+static struct {
+    cudaStream_t side[MMB_MAX_PEERS];
+    cudaEvent_t  done[MMB_MAX_PEERS], ready;
+    unsigned     made, pending;         /* bit d: stream d exists / carries copies since the last join */
+} TP;
+
+mm_status mm_f4_tp_push(void *const *y_all, uint32_t n_ranks, uint32_t ldy, uint32_t col0, uint32_t cols,
+                        uint32_t row0, uint32_t rows)
+{
+    MM_REQUIRE(y_all && n_ranks >= 1 && n_ranks <= MMB_MAX_PEERS, MM_ERR_RANGE);
+    MM_REQUIRE(cols && rows && (uint64_t)col0 + cols <= ldy, MM_ERR_SHAPE);
+    MM_REQUIRE(ldy % 8u == 0 && col0 % 8u == 0 && cols % 8u == 0, MM_ERR_SHAPE);
+    for (uint32_t d = 0; d < n_ranks; d++)
+        MM_REQUIRE(y_all[d] && ((uintptr_t)y_all[d] & 15u) == 0, MM_ERR_STATE);
+    MM_CHECK(ensure_ready());
+    if (n_ranks == 1)
+        return MM_OK;
+    cudaStream_t cs = (cudaStream_t)mm_cuda_stream_raw(MM_ST_COMPUTE);
+    if (!TP.ready)
+        CK(cudaEventCreateWithFlags(&TP.ready, cudaEventDisableTiming));
+    CK(cudaEventRecord(TP.ready, cs));                       /* the slice is complete in the own copy */
+    const size_t pitch = (size_t)ldy * 2u;
+    const size_t off = (size_t)row0 * pitch + (size_t)col0 * 2u;
+    for (uint32_t d = 1; d < n_ranks; d++) {
+        if (!(TP.made & (1u << d))) {
+            CK(cudaStreamCreateWithFlags(&TP.side[d], cudaStreamNonBlocking));
+            CK(cudaEventCreateWithFlags(&TP.done[d], cudaEventDisableTiming));
+            TP.made |= 1u << d;
+        }
+        CK(cudaStreamWaitEvent(TP.side[d], TP.ready, 0));
+        CK(cudaMemcpy2DAsync((unsigned char *)y_all[d] + off, pitch, (const unsigned char *)y_all[0] + off, pitch,
+                             (size_t)cols * 2u, rows, cudaMemcpyDefault, TP.side[d]));
+        TP.pending |= 1u << d;
+    }
+    return MM_OK;
+}
+
+mm_status mm_f4_tp_push_join(void)
+{
+    MM_CHECK(ensure_ready());
+    cudaStream_t cs = (cudaStream_t)mm_cuda_stream_raw(MM_ST_COMPUTE);
+    for (uint32_t d = 1; d < MMB_MAX_PEERS; d++) {
+        if (!(TP.pending & (1u << d)))
+            continue;
+        CK(cudaEventRecord(TP.done[d], TP.side[d]));
+        CK(cudaStreamWaitEvent(cs, TP.done[d], 0));
+    }
+    TP.pending = 0;
+    return MM_OK;
+}
+
 mm_status mm_f4_wait_selftest(unsigned *done_dev)
 {
     MM_REQUIRE(done_dev, MM_ERR_STATE);

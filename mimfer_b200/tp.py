@@ -16,8 +16,14 @@ on the stream closes the op.  The full outputs are double-buffered: call i of a
 linear writes buffer i % 2 on every rank, so a rank that runs ahead into the next
 step never overwrites an output a slower rank is still reading - it cannot reach
 the step after that before the slower rank has arrived at the barrier in between,
-which that rank enqueues after its reads.  The reference has no multi-GPU path;
-this is new surface.
+which that rank enqueues after its reads.
+
+mode="push" is for prefill sizes, where a rank's output slice is hundreds of
+megabytes: the kernel stores into the rank's own copy only, chunk of rows by chunk
+of rows, and the copy engines push every finished chunk to the peers
+(mm_f4_tp_push) while the SMs multiply the next one; a join and the same barrier
+kernel close the op.  Stored from the epilogue, the same bytes hold every SM until
+NVLink has taken them.  The reference has no multi-GPU path; this is new surface.
 """
 import ctypes as C
 import os
@@ -36,6 +42,22 @@ def shard_bounds(N, rank, world):
         raise ValueError(f"N={N} is not divisible by the tensor-parallel degree {world}")
     per = N // world
     return rank * per, (rank + 1) * per
+
+
+def push_chunks(M, rows):
+    """(row0, rows) of the chunks of a pushed linear: `rows` at a time, the tail halved
+    chunk by chunk down to 256 rows (a tile's height) so the last push is a short one."""
+    out, r0 = [], 0
+    while M - r0 > rows:
+        out.append((r0, rows))
+        r0 += rows
+    left = M - r0
+    while left > 512 and left % 512 == 0:
+        out.append((r0, left // 2))
+        r0 += left // 2
+        left -= left // 2
+    out.append((r0, left))
+    return out
 
 
 class TpBarrier:
@@ -71,10 +93,13 @@ class TpLinear:
     """`local_op(x, w_shard, y_shard)` computes the shard; by default it is the
     CUDA op enqueued on the runtime's compute stream."""
 
-    def __init__(self, weight, rank, world, rt=None, group=None, local_op=None, mode="gather"):
-        if mode not in ("gather", "fused"):
+    def __init__(self, weight, rank, world, rt=None, group=None, local_op=None, mode="gather", push_rows=1024):
+        if mode not in ("gather", "fused", "push"):
             raise ValueError(mode)
+        if push_rows <= 0:
+            raise ValueError("push_rows")
         self.rank, self.world, self.group, self.rt = rank, world, group, rt
+        self.push_rows = push_rows
         self.mode = mode if world > 1 else "gather"
         self._symm = {}
         self.N, self.K = weight.N, weight.K
@@ -121,8 +146,10 @@ class TpLinear:
         """Cross-rank barrier on the compute stream: after it, every rank's copy of
         every output written since the previous barrier is complete.  Needed once
         per group of fused forwards issued with barrier=False."""
-        if self.mode != "fused":
+        if self.mode not in ("fused", "push"):
             return
+        if self.mode == "push":                 # the copy engines' work joins the compute stream first
+            L.check(self.rt.lib.mm_f4_tp_push_join(), "mm_f4_tp_push_join")
         TpBarrier.get(self.rt, self.rank, self.world, self.group).sync()
 
     def _forward_fused(self, x, barrier=True):
@@ -137,6 +164,27 @@ class TpLinear:
             self.barrier()                      # every rank's stores have landed everywhere
         return y
 
+    def _forward_push(self, x, barrier=True):
+        """Row chunks of push_rows: the chunk's GEMM into the own copy, then its push to the
+        peers; the compute stream never waits for a push before the closing join.  The last
+        chunks are halved down to 256 rows so that little of the exchange is left when the
+        multiplying ends."""
+        M = x.shape[0]
+        y, hdl, ptrs = self._symm_buffers(M, x)
+        ns = self.N // self.world
+        n0 = self.rank * ns
+        w, K = self.shard, self.shard.K
+        own = (C.c_void_p * 1)()
+        for r0, rows in push_chunks(M, self.push_rows):
+            own[0] = ptrs[0] + r0 * self.N * 2
+            L.check(self.rt.lib.mm_f4_linear_tp(x.data_ptr() + r0 * K * 2, w.dev_payload.data_ptr(),
+                                                w.dev_scales.data_ptr(), w.gs, own, 1, self.N, n0, rows, K, w.N,
+                                                None), "mm_f4_linear_tp")
+            L.check(self.rt.lib.mm_f4_tp_push(ptrs, self.world, self.N, n0, ns, r0, rows), "mm_f4_tp_push")
+        if barrier:
+            self.barrier()
+        return y
+
     def forward(self, x, barrier=True):
         """x: [M][K] replicated.  Returns y [M][N], complete on every rank.
         On CUDA everything is enqueued on the runtime's compute stream.
@@ -144,6 +192,8 @@ class TpLinear:
         caller, so several linears of one step can share a single barrier()."""
         if self.mode == "fused":
             return self._forward_fused(x, barrier)
+        if self.mode == "push":
+            return self._forward_push(x, barrier)
         M = x.shape[0]
         y_local, gathered, y = self._buffers(M, x)
         if self.world == 1:                       # nothing to exchange

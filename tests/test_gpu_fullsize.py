@@ -147,3 +147,38 @@ def test_tensor_parallel_shards_on_one_gpu(rt, oracle, name, world, M):
             want = oracle.gemm_f4(xb, w.payload, w.scales, w.gs, rows=rows, n_begin=a, n_end=b)
             got = (y0 if rows is None else y0[rows])[:, a:b]
             assert row_rel_l2(got, want) <= REL_L2_TOL, (r, a, b)
+
+
+def test_push_of_row_chunks_on_one_gpu(rt, oracle):
+    """The copy engines' form of the exchange with both "ranks" on one GPU: rank 1 of 2 runs its
+    shard chunk of rows by chunk of rows into its own full-width output (mm_f4_linear_tp with
+    one destination) and pushes every chunk to the other output (mm_f4_tp_push).  After the join
+    the other output holds the shard's columns and nothing else."""
+    from mimfer_b200.tp import push_chunks
+    torch = rt.torch
+    w = weight(rt, "gate_up")
+    K, N = SHAPES["gate_up"]
+    M, world, r = 1280, 2, 1
+    ns = N // world
+    xb = mm.make_activations(M, K, seed=1)
+    x = rt.to_device_bf16(xb)
+    outs = [torch.zeros((M, N), dtype=torch.bfloat16, device=rt.device) for _ in range(2)]
+    ptrs = (C.c_void_p * 2)(outs[0].data_ptr(), outs[1].data_ptr())
+    own = (C.c_void_p * 1)()
+    torch.cuda.synchronize()
+    pay, sc = w.dev_payload[r * ns:(r + 1) * ns], w.dev_scales[r * ns:(r + 1) * ns]
+    for r0, rows in push_chunks(M, 512):
+        own[0] = outs[0].data_ptr() + r0 * N * 2
+        L.check(rt.lib.mm_f4_linear_tp(x.data_ptr() + r0 * K * 2, pay.data_ptr(), sc.data_ptr(), w.gs, own, 1,
+                                       N, r * ns, rows, K, ns, None), "mm_f4_linear_tp")
+        L.check(rt.lib.mm_f4_tp_push(ptrs, 2, N, r * ns, ns, r0, rows), "mm_f4_tp_push")
+    L.check(rt.lib.mm_f4_tp_push_join(), "mm_f4_tp_push_join")
+    rt.sync()
+    assert rt.device_status() == 0
+    y0, y1 = rt.from_device_bf16(outs[0]), rt.from_device_bf16(outs[1])
+    assert np.array_equal(y0, y1)
+    assert not y1[:, :r * ns].any()                        # the other rank's columns stay untouched
+    rows = [0, 255, 511, 512, 1023, 1024, M - 1]           # both sides of every chunk edge
+    for (a, b) in ((r * ns, r * ns + 256), (N - 256, N)):
+        want = oracle.gemm_f4(xb, w.payload, w.scales, w.gs, rows=rows, n_begin=a, n_end=b)
+        assert row_rel_l2(y1[rows][:, a:b], want) <= REL_L2_TOL, (a, b)

@@ -46,7 +46,7 @@ def _worker(rank, world, port, cases, out_dir, mode):
     rt = mm.Runtime.get(rank)
     for i, (M, K, N) in enumerate(cases):
         w = mm.make_weight(N, K, seed=i)
-        lin = TpLinear(w, rank, world, rt=rt, mode=mode)
+        lin = TpLinear(w, rank, world, rt=rt, mode=mode, push_rows=128)   # push mode: several row chunks
         x = rt.to_device_bf16(mm.make_activations(M, K, seed=100 + i))
         y = lin.forward(x, barrier=(i % 2 == 0))      # odd cases: barrier issued separately
         if i % 2:
@@ -104,7 +104,7 @@ def _spawn_bounded(fn, args, world, limit_s=150, grace_s=90):
             pytest.fail(f"ranks still running after {limit_s} s")
 
 
-@pytest.mark.parametrize("mode", ["gather", "fused"])
+@pytest.mark.parametrize("mode", ["gather", "fused", "push"])
 def test_two_gpu_tensor_parallel_matches_oracle(tmp_path, oracle, lib, mode):
     import torch
     import torch.multiprocessing as mp
@@ -112,7 +112,8 @@ def test_two_gpu_tensor_parallel_matches_oracle(tmp_path, oracle, lib, mode):
         pytest.skip("needs two GPUs")
     import mimfer_b200 as mm
     from conftest import row_rel_l2
-    cases = [(1, 1024, 512), (32, 2048, 1024), (300, 512, 1040)]    # decode, decode, prefill kernel
+    # decode, decode, prefill kernel, prefill in several row chunks (push mode: 128 rows each, ragged tail)
+    cases = [(1, 1024, 512), (32, 2048, 1024), (300, 512, 1040), (1100, 256, 4112)]
     world = 2
     _spawn_bounded(_worker, (world, _free_port(), cases, str(tmp_path), mode), world)
     for i, (M, K, N) in enumerate(cases):

@@ -214,3 +214,19 @@ def test_global_scale_entries_can_be_taken_back(lib):
     assert lib.mm_f4_gscale_set(0x2000 * 7, 5.0) == L.MM_OK and lib.mm_f4_gscale_get(0x2000 * 7) == 5.0
     assert lib.mm_f4_gscale_room() == room - 49
     lib.mm_f4_gscale_clear()
+
+
+def test_tensor_parallel_push_validates_arguments(lib):
+    """mm_f4_tp_push: at most eight aligned copies, the slice inside the row pitch, 16-byte rows."""
+    lib.mm_log_set_level(-1)
+    ptrs = (C.c_void_p * 2)(0x1000, 0x2000)
+    bad = (C.c_void_p * 2)(0x1000, 0x2008)
+    assert lib.mm_f4_tp_push(None, 2, 512, 0, 256, 0, 4) == L.MM_ERR_RANGE
+    assert lib.mm_f4_tp_push(ptrs, 9, 512, 0, 256, 0, 4) == L.MM_ERR_RANGE
+    assert lib.mm_f4_tp_push(ptrs, 2, 512, 384, 256, 0, 4) == L.MM_ERR_SHAPE      # 384 + 256 > 512
+    assert lib.mm_f4_tp_push(ptrs, 2, 512, 0, 0, 0, 4) == L.MM_ERR_SHAPE
+    assert lib.mm_f4_tp_push(ptrs, 2, 512, 0, 256, 0, 0) == L.MM_ERR_SHAPE
+    assert lib.mm_f4_tp_push(ptrs, 2, 512, 4, 256, 0, 4) == L.MM_ERR_SHAPE        # rows of the slice not 16-byte aligned
+    assert lib.mm_f4_tp_push(ptrs, 2, 516, 0, 256, 0, 4) == L.MM_ERR_SHAPE
+    assert lib.mm_f4_tp_push(bad, 2, 512, 0, 256, 0, 4) == L.MM_ERR_STATE
+    lib.mm_log_set_level(1)
