@@ -954,6 +954,8 @@ def run_b200(args):
             res = run_case(b, args.case, steps, warmup)
             if b.rank == 0:
                 print(json.dumps({"case": args.case, **res}))
+            if b.world > 1:
+                b.dist.destroy_process_group()
             return
         if b.world == 1:
             dec, ops, eng = b.decode_sweep(steps, warmup, per_op=True)
@@ -1086,6 +1088,8 @@ def run_case(b, case, steps, warmup):
         return b.prefill_sweep(steps, warmup, ms_list=(2048,), names=("down",))
     if case == "prefill_kv":       # k at M=2048: 32 tiles, all of them split
         return b.prefill_sweep(steps, warmup, ms_list=(2048,), names=("k",))
+    if case == "tp":               # the tensor-parallel series alone (any number of ranks)
+        return b.tp_series(steps, warmup)
     if case == "prefill_small":
         return b.prefill_sweep(steps, warmup, ms_list=(512,), names=("q",))
     raise SystemExit(f"unknown case {case}")
