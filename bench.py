@@ -964,8 +964,8 @@ def run_b200(args):
                         timed_regions=dec["timed_regions"],
                         gpu_launches=dec["kernel_launches_per_step"] * steps,
                         config={"workload": "decode GEMV sweep M in {1,2,4,8,16} x {gate+up 5120->34816, "
-                                            "down 17408->5120}, 10 ops per step, one CUDA graph: two slicing "
-                                            "kernels and one persistent group launch of the block-scaled kernel",
+                                            "down 17408->5120}, 10 ops per step, one CUDA graph: one slicing "
+                                            "kernel and one persistent group launch of the block-scaled kernel",
                                 "l2": "every op reads its own weight copy: 750 MB per step, larger than L2",
                                 "timing": f"median of {dec['timed_regions']} timed regions of {steps} steps",
                                 "quant": "NVFP4 e2m1 + e4m3/16 + fp32 global scale", "peaks": pk["src"]})
@@ -977,7 +977,7 @@ def run_b200(args):
                                 "frac": dec["alg_gbs"] / pk["hbm"], "of": pk["src"],
                                 "alg_bytes_per_launch": dec["alg_bytes"],
                                 "launch_us": dec["ms_per_step"] * 1e3,
-                                "launch_includes": "the step's two slicing kernels (activations to digit planes)",
+                                "launch_includes": "the step's slicing kernel (activations to digit planes)",
                                 "traffic": GROUP_TRAFFIC_RATIO * dec["alg_bytes"],
                                 "traffic_src": "ncu capture of a group launch on two gate+up ops, "
                                                "scaled by algorithmic bytes"}

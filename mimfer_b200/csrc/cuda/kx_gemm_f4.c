@@ -228,8 +228,32 @@ unsigned long long mm_f4_launch_count(int reset)
         }                                                                     \
     } while (0)
 
+/* The exchange of a tensor-parallel linear by the copy engines.  A prefill-size output
+ * slice is hundreds of megabytes per rank: stored from the kernel's epilogue it holds the
+ * SM until NVLink has taken it; pushed by the copy engines it leaves while the next row
+ * chunk is multiplied.  One side stream and one event per peer, made on first use. */
+static struct {
+    cudaStream_t side[MMB_MAX_PEERS];
+    cudaEvent_t  done[MMB_MAX_PEERS], ready;
+    unsigned     made, pending;         /* bit d: stream d exists / carries copies since the last join */
+} TP;
+
+static void tp_push_reset(void)
+{
+    for (uint32_t d = 0; d < MMB_MAX_PEERS; d++) {
+        if (TP.made & (1u << d)) {
+            cudaStreamDestroy(TP.side[d]);
+            cudaEventDestroy(TP.done[d]);
+        }
+    }
+    if (TP.ready)
+        cudaEventDestroy(TP.ready);
+    memset(&TP, 0, sizeof TP);
+}
+
 /* Forget everything that belongs to the device the runtime was initialised on:
- * status word, workspace, per-device kernel attributes.  Called by the runtime
+ * status word, workspace, per-device kernel attributes, the side streams of the
+ * tensor-parallel pushes.  Called by the runtime
  * shim's mm_cuda_shutdown, and by ensure_ready when it finds the runtime on
  * another compute stream than the one it prepared for (a shutdown followed by
  * a new mm_cuda_init, possibly on another device, in a runtime that is not the
@@ -250,6 +274,7 @@ void mmb_launcher_reset(void)
     G.next_region = 0;
     G.next_shallow = 0;
     G.l2_limit_set = 0;
+    tp_push_reset();
 }
 
 static mm_status ensure_ready(void)
@@ -1232,16 +1257,6 @@ mm_status mm_f4_tp_barrier(void *const *flags_all, uint32_t n_ranks, uint32_t ra
     G.launches++;
     return MM_OK;
 }
-
-/* The exchange of a tensor-parallel linear by the copy engines.  A prefill-size output
- * slice is hundreds of megabytes per rank: stored from the kernel's epilogue it holds the
- * SM until NVLink has taken it; pushed by the copy engines it leaves while the next row
- * chunk is multiplied.  One side stream and one event per peer, made on first use. */
-static struct {
-    cudaStream_t side[MMB_MAX_PEERS];
-    cudaEvent_t  done[MMB_MAX_PEERS], ready;
-    unsigned     made, pending;         /* bit d: stream d exists / carries copies since the last join */
-} TP;
 
 mm_status mm_f4_tp_push(void *const *y_all, uint32_t n_ranks, uint32_t ldy, uint32_t col0, uint32_t cols,
                         uint32_t row0, uint32_t rows)
