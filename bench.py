@@ -1088,6 +1088,8 @@ def run_case(b, case, steps, warmup):
         return b.prefill_sweep(steps, warmup, ms_list=(2048,), names=("down",))
     if case == "prefill_kv":       # k at M=2048: 32 tiles, all of them split
         return b.prefill_sweep(steps, warmup, ms_list=(2048,), names=("k",))
+    if case == "planner_layers8":  # eight layers in the reference planner's op order, with their dependencies
+        return b.decode_step_planner(steps, warmup, layers=8)
     if case == "tp":               # the tensor-parallel series alone (any number of ranks)
         return b.tp_series(steps, warmup)
     if case == "prefill_small":

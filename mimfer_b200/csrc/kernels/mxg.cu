@@ -33,6 +33,31 @@
 
 namespace mmb {
 
+/* Time stamps of a launch, measurement builds only (-DMMB_MEASURE_MODES): per launch a
+ * row of sixteen globaltimer values, minima and maxima over the CTAs.  [0]/[5] first/last
+ * CTA entered, [1]/[2] first/last CTA past its grid-dependency wait, [3]/[6] first unit's
+ * MMAs done in the first/last CTA, [7] last MMAs of all, [8]/[4] first/last epilogue warp
+ * done, [9] last producer done, [10] first stage landed.  Slicing kernel: [3]/[6] loads
+ * done, [7]/[9] last CTA past the first/second cluster barrier, [11] last thread 0 has sliced
+ * its block, [10]/[4] first/last CTA done. */
+#ifdef MMB_MEASURE_MODES
+#define MMB_TRACE_SLOTS 1024u
+__device__ unsigned long long g_trace[MMB_TRACE_SLOTS][16];
+__device__ __forceinline__ void trace_min(uint32_t slot1, uint32_t k)
+{
+    if (slot1) atomicMin(&g_trace[slot1 - 1u][k], static_cast<unsigned long long>(globaltimer_ns()));
+}
+__device__ __forceinline__ void trace_max(uint32_t slot1, uint32_t k)
+{
+    if (slot1) atomicMax(&g_trace[slot1 - 1u][k], static_cast<unsigned long long>(globaltimer_ns()));
+}
+#define MMB_TRACE_MIN(slot1, k) trace_min(slot1, k)
+#define MMB_TRACE_MAX(slot1, k) trace_max(slot1, k)
+#else
+#define MMB_TRACE_MIN(slot1, k) ((void)0)
+#define MMB_TRACE_MAX(slot1, k) ((void)0)
+#endif
+
 struct __align__(128) MxgOp {
     TmaDesc         tm_payload, tm_scale, tm_planes, tm_sfb;
     uint16_t       *y[MMB_MAX_PEERS];    /* destinations: own output, then the peers' (tensor parallel) */
@@ -56,7 +81,8 @@ struct __align__(128) MxgGroup {
     unsigned *sched;         /* [0] units handed out beyond the first of every CTA, [1] CTAs that took
                               * their last; both zero between launches.  NULL: unit u goes to CTA u mod grid */
     unsigned *counters;      /* arrival counters of the split tiles, zero between launches */
-    uint32_t  pad[20];
+    uint32_t  trace_slot;    /* measurement builds: 1 + the launch's row of time stamps, 0 = none */
+    uint32_t  pad[19];
 };
 static_assert(sizeof(MxgGroup) == 128, "MxgGroup layout");
 
@@ -188,6 +214,8 @@ f4_mxg_kernel(const __grid_constant__ MxgParams<NOPS> prm)
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
 
     if (tid == 0) {
+        MMB_TRACE_MIN(grp.trace_slot, 0);
+        MMB_TRACE_MAX(grp.trace_slot, 5);
         for (uint32_t s = 0; s < ST; s++) {
             mbar_init(bar_full + 8u * s, 1u);
             mbar_init(bar_empty + 8u * s, 2u);
@@ -239,6 +267,8 @@ f4_mxg_kernel(const __grid_constant__ MxgParams<NOPS> prm)
             if (grp.pdl != MMB_PDL_OFF)
                 grid_dep_launch();
             grid_dep_wait();                                /* also: the launch in front has reset the counter */
+            MMB_TRACE_MIN(grp.trace_slot, 1);
+            MMB_TRACE_MAX(grp.trace_slot, 2);
             uint32_t s = 0, round = 0, gstep = 0;
             for (;;) {
                 /* the number of the unit after this one, asked for now and needed at its end */
@@ -261,6 +291,7 @@ f4_mxg_kernel(const __grid_constant__ MxgParams<NOPS> prm)
                 while (op + 1u < grp.n_ops && g >= ops[op + 1u].unit0) op++;
                 u = unit_geom(ops[op], g);
             }
+            MMB_TRACE_MAX(grp.trace_slot, 9);
             if (grp.sched) {
                 /* the CTA that is last to have taken its last number puts the counters back */
                 __threadfence();
@@ -289,6 +320,8 @@ f4_mxg_kernel(const __grid_constant__ MxgParams<NOPS> prm)
                 for (uint32_t it = 0; it < u.nsteps; it++, gstep++, s = (s + 1u == ST) ? 0u : s + 1u, round += (s == 0u)) {
                     const uint32_t t = gstep & 1u, st = base + s * stage_b;
                     mbar_wait(bar_full + 8u * s, round & 1u, grp.status);
+                    if (gstep == 0u && h == 0u)
+                        MMB_TRACE_MIN(grp.trace_slot, 10);
                     if (h < u.halves) {
                         mbar_wait(bar_sf_full + 8u * t, (gstep >> 1) & 1u, grp.status);
                         tc_fence_after();
@@ -415,6 +448,13 @@ f4_mxg_kernel(const __grid_constant__ MxgParams<NOPS> prm)
             const float rb = lane + 32u < 2u * o.M ? __ldcg(o.row_scale + lane + 32u) : 0.0f;
             mbar_wait_warp(bar_acc_full + 8u * buf, use & 1u, grp.status);
             tc_fence_after();
+            if (etid == 0u) {
+                if (j == 0u) {
+                    MMB_TRACE_MIN(grp.trace_slot, 3);
+                    MMB_TRACE_MAX(grp.trace_slot, 6);
+                }
+                MMB_TRACE_MAX(grp.trace_slot, 7);
+            }
             const uint32_t d0 = tq + buf * MMB_MXG_ACC_STRIDE;
             float *mine = o.partial + static_cast<size_t>(u.slice) * (groups * 4u) * pitch;
             for (uint32_t g4 = 0; g4 < groups; g4++) {
@@ -477,58 +517,135 @@ f4_mxg_kernel(const __grid_constant__ MxgParams<NOPS> prm)
             if (!direct) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (etid == 0u) {
-                    __threadfence();
-                    const unsigned ticket = atomicAdd(grp.counters + o.counters_idx + u.tile, 1u);
-                    __threadfence();
+                    /* release: the partial sums of all 128 threads (ordered before by the barrier);
+                     * acquire: the other slices' sums, for the one that arrives last */
+                    unsigned ticket;
+                    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;"
+                                 : "=r"(ticket) : "l"(grp.counters + o.counters_idx + u.tile) : "memory");
                     sts32(last_flag, (ticket == o.split_k - 1u) ? 1u : 0u);
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (lds32(last_flag)) {
                     const size_t slice = static_cast<size_t>(groups * 4u) * pitch;
-                    const uint32_t col0 = u.glu ? u.tile * 256u + lr : u.row0 + lr, col1 = col0 + 128u;
-                    const bool ok0 = lr < u.cnt0 && u.row0 + lr < o.N;
-                    const bool ok1 = u.glu ? ok0 : (lr < u.cnt1 && u.row0 + 128u + lr < o.N);
-                    for (uint32_t m0 = 0; m0 < o.M; m0 += 4u) {
-                        float s0[4] = { 0.0f, 0.0f, 0.0f, 0.0f }, s1[4] = { 0.0f, 0.0f, 0.0f, 0.0f };
-                        for (uint32_t sl0 = 0; sl0 < o.split_k; sl0 += 4u) {
-                            float v0[4][4], v1[4][4];
+                    /* The last slice to arrive adds the tile's partial sums, slice by slice in
+                     * ascending order (the same sums from run to run, and the single-op kernel's).
+                     * Four columns per thread and up to sixteen 16-byte loads in flight: with one
+                     * column per thread the sums of a 16-row tile in eight slices were eight
+                     * dependent round trips to L2, 13 us at the end of every short launch. */
+                    bool vec = ((pitch | o.N | o.ldy | o.col0 | u.row0 | u.cnt0 | u.cnt1) & 3u) == 0u;
+                    for (uint32_t d = 0; d < o.n_dst; d++)
+                        vec = vec && (reinterpret_cast<uintptr_t>(o.y[d]) & 7u) == 0u;
+                    if (vec && !u.glu) {
+                        const uint32_t cq = etid & 63u, rg = etid >> 6;
+                        const uint32_t col = u.row0 + 4u * cq;
+                        const bool ok = 4u * cq < u.rows && col < o.N;
+                        for (uint32_t m = rg; ok && m < o.M; m += 4u) {
+                            float4 sum[2] = { make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f) };
+                            const bool two = m + 2u < o.M;
+                            for (uint32_t sl0 = 0; sl0 < o.split_k; sl0 += 8u) {
+                                float4 v[2][8];
 #pragma unroll
-                            for (uint32_t r = 0; r < 4u; r++)
-#pragma unroll
-                                for (uint32_t q = 0; q < 4u; q++) {
-                                    const bool live = m0 + r < o.M && sl0 + q < o.split_k;
-                                    const float *src = o.partial + (sl0 + q) * slice + static_cast<size_t>(m0 + r) * pitch;
-                                    v0[r][q] = live && ok0 ? __ldcg(src + col0) : 0.0f;
-                                    v1[r][q] = live && ok1 ? __ldcg(src + col1) : 0.0f;
+                                for (uint32_t q = 0; q < 8u; q++) {
+                                    const float *src = o.partial + (sl0 + q) * slice + static_cast<size_t>(m) * pitch + col;
+                                    const bool live = sl0 + q < o.split_k;
+                                    v[0][q] = live ? __ldcg(reinterpret_cast<const float4 *>(src)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                                    v[1][q] = live && two ? __ldcg(reinterpret_cast<const float4 *>(src + 2u * pitch))
+                                                          : make_float4(0.f, 0.f, 0.f, 0.f);
                                 }
 #pragma unroll
-                            for (uint32_t r = 0; r < 4u; r++)
+                                for (uint32_t q = 0; q < 8u; q++)
 #pragma unroll
-                                for (uint32_t q = 0; q < 4u; q++) {
-                                    s0[r] += v0[r][q];
-                                    s1[r] += v1[r][q];
-                                }
+                                    for (uint32_t r = 0; r < 2u; r++) {
+                                        sum[r].x += v[r][q].x; sum[r].y += v[r][q].y;
+                                        sum[r].z += v[r][q].z; sum[r].w += v[r][q].w;
+                                    }
+                            }
+                            for (uint32_t r = 0; r < (two ? 2u : 1u); r++) {
+                                const uint2 out = make_uint2(pack_bf16x2(sum[r].x * o.gs, sum[r].y * o.gs),
+                                                             pack_bf16x2(sum[r].z * o.gs, sum[r].w * o.gs));
+                                const size_t off = static_cast<size_t>(m + 2u * r) * o.ldy + o.col0 + col;
+                                for (uint32_t d = 0; d < o.n_dst; d++)
+                                    *reinterpret_cast<uint2 *>(o.y[d] + off) = out;
+                            }
                         }
+                    } else if (vec) {
+                        /* gated pair: columns [0, 128) of the tile's partial sums are one projection,
+                         * [128, 256) the other; 32 column groups x 4 row groups */
+                        const uint32_t cq = etid & 31u, rg = etid >> 5;
+                        const uint32_t lc = 4u * cq;
+                        const bool ok = lc < u.cnt0 && u.row0 + lc < o.N;
+                        for (uint32_t m = rg; ok && m < o.M; m += 4u) {
+                            float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
+                            for (uint32_t sl0 = 0; sl0 < o.split_k; sl0 += 8u) {
+                                float4 v0[8], v1[8];
 #pragma unroll
-                        for (uint32_t r = 0; r < 4u; r++) {
-                            const uint32_t m = m0 + r;
-                            if (m >= o.M)
-                                break;
-                            if (u.glu) {
-                                if (ok0)
-                                    mxg_store(o, static_cast<size_t>(m) * o.ldy + o.col0 + u.row0 + lr,
-                                              glu_out_bf16(gate_second ? s1[r] : s0[r], gate_second ? s0[r] : s1[r],
-                                                           o.gs, o.gs_up));
-                            } else {
-                                if (ok0) {
-                                    __nv_bfloat16 hv = __float2bfloat16_rn(s0[r] * o.gs);
-                                    mxg_store(o, static_cast<size_t>(m) * o.ldy + o.col0 + u.row0 + lr,
-                                              *reinterpret_cast<uint16_t *>(&hv));
+                                for (uint32_t q = 0; q < 8u; q++) {
+                                    const float *src = o.partial + (sl0 + q) * slice + static_cast<size_t>(m) * pitch +
+                                                       u.tile * 256u + lc;
+                                    const bool live = sl0 + q < o.split_k;
+                                    v0[q] = live ? __ldcg(reinterpret_cast<const float4 *>(src)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                                    v1[q] = live ? __ldcg(reinterpret_cast<const float4 *>(src + 128u))
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
                                 }
-                                if (ok1) {
-                                    __nv_bfloat16 hv = __float2bfloat16_rn(s1[r] * o.gs);
-                                    mxg_store(o, static_cast<size_t>(m) * o.ldy + o.col0 + u.row0 + 128u + lr,
-                                              *reinterpret_cast<uint16_t *>(&hv));
+#pragma unroll
+                                for (uint32_t q = 0; q < 8u; q++) {
+                                    s0.x += v0[q].x; s0.y += v0[q].y; s0.z += v0[q].z; s0.w += v0[q].w;
+                                    s1.x += v1[q].x; s1.y += v1[q].y; s1.z += v1[q].z; s1.w += v1[q].w;
+                                }
+                            }
+                            const float4 gt = gate_second ? s1 : s0, up = gate_second ? s0 : s1;
+                            const uint2 out = make_uint2(glu_out_bf16x2(gt.x, gt.y, up.x, up.y, o.gs, o.gs_up),
+                                                         glu_out_bf16x2(gt.z, gt.w, up.z, up.w, o.gs, o.gs_up));
+                            const size_t off = static_cast<size_t>(m) * o.ldy + o.col0 + u.row0 + lc;
+                            for (uint32_t d = 0; d < o.n_dst; d++)
+                                *reinterpret_cast<uint2 *>(o.y[d] + off) = out;
+                        }
+                    } else {
+                        const uint32_t col0 = u.glu ? u.tile * 256u + lr : u.row0 + lr, col1 = col0 + 128u;
+                        const bool ok0 = lr < u.cnt0 && u.row0 + lr < o.N;
+                        const bool ok1 = u.glu ? ok0 : (lr < u.cnt1 && u.row0 + 128u + lr < o.N);
+                        for (uint32_t m0 = 0; m0 < o.M; m0 += 4u) {
+                            float s0[4] = { 0.0f, 0.0f, 0.0f, 0.0f }, s1[4] = { 0.0f, 0.0f, 0.0f, 0.0f };
+                            for (uint32_t sl0 = 0; sl0 < o.split_k; sl0 += 4u) {
+                                float v0[4][4], v1[4][4];
+    #pragma unroll
+                                for (uint32_t r = 0; r < 4u; r++)
+    #pragma unroll
+                                    for (uint32_t q = 0; q < 4u; q++) {
+                                        const bool live = m0 + r < o.M && sl0 + q < o.split_k;
+                                        const float *src = o.partial + (sl0 + q) * slice + static_cast<size_t>(m0 + r) * pitch;
+                                        v0[r][q] = live && ok0 ? __ldcg(src + col0) : 0.0f;
+                                        v1[r][q] = live && ok1 ? __ldcg(src + col1) : 0.0f;
+                                    }
+    #pragma unroll
+                                for (uint32_t r = 0; r < 4u; r++)
+    #pragma unroll
+                                    for (uint32_t q = 0; q < 4u; q++) {
+                                        s0[r] += v0[r][q];
+                                        s1[r] += v1[r][q];
+                                    }
+                            }
+    #pragma unroll
+                            for (uint32_t r = 0; r < 4u; r++) {
+                                const uint32_t m = m0 + r;
+                                if (m >= o.M)
+                                    break;
+                                if (u.glu) {
+                                    if (ok0)
+                                        mxg_store(o, static_cast<size_t>(m) * o.ldy + o.col0 + u.row0 + lr,
+                                                  glu_out_bf16(gate_second ? s1[r] : s0[r], gate_second ? s0[r] : s1[r],
+                                                               o.gs, o.gs_up));
+                                } else {
+                                    if (ok0) {
+                                        __nv_bfloat16 hv = __float2bfloat16_rn(s0[r] * o.gs);
+                                        mxg_store(o, static_cast<size_t>(m) * o.ldy + o.col0 + u.row0 + lr,
+                                                  *reinterpret_cast<uint16_t *>(&hv));
+                                    }
+                                    if (ok1) {
+                                        __nv_bfloat16 hv = __float2bfloat16_rn(s1[r] * o.gs);
+                                        mxg_store(o, static_cast<size_t>(m) * o.ldy + o.col0 + u.row0 + 128u + lr,
+                                                  *reinterpret_cast<uint16_t *>(&hv));
+                                    }
                                 }
                             }
                         }
@@ -538,6 +655,10 @@ f4_mxg_kernel(const __grid_constant__ MxgParams<NOPS> prm)
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");     /* last_flag is reused by the next unit */
             }
+        }
+        if (lane == 0u) {
+            MMB_TRACE_MAX(grp.trace_slot, 4);
+            MMB_TRACE_MIN(grp.trace_slot, 8);
         }
     }
 
@@ -558,6 +679,9 @@ struct XsliceItem {
 };
 struct XsliceGroup {
     uint32_t   n, pdl;
+#ifdef MMB_MEASURE_MODES
+    uint32_t   trace_slot;
+#endif
     XsliceItem item[MMB_MXG_MAX_OPS];
     uint32_t   row0[MMB_MXG_MAX_OPS + 1];      /* first padded row of each tensor in the launch; [n] = all rows */
 };
@@ -608,9 +732,21 @@ f4_xslice_cluster_kernel(const __grid_constant__ XsliceGroup g)
     cg::cluster_group cluster = cg::this_cluster();
     __shared__ uint32_t s_warp[8];
     __shared__ uint32_t s_part;                  /* this CTA's maximum, read by the whole cluster */
+#ifdef MMB_MEASURE_MODES
+    if (threadIdx.x == 0) {
+        MMB_TRACE_MIN(g.trace_slot, 0);
+        MMB_TRACE_MAX(g.trace_slot, 5);
+    }
+#endif
     grid_dep_launch();
     if (g.pdl != MMB_PDL_OFF)
         grid_dep_wait();                         /* the activations are the previous kernel's output */
+#ifdef MMB_MEASURE_MODES
+    if (threadIdx.x == 0) {
+        MMB_TRACE_MIN(g.trace_slot, 1);
+        MMB_TRACE_MAX(g.trace_slot, 2);
+    }
+#endif
     const uint32_t row = blockIdx.x / MMB_XS_CLUSTER, part = blockIdx.x % MMB_XS_CLUSTER;
     uint32_t i = 0;
     while (i + 1u < g.n && row >= g.row0[i + 1u]) i++;
@@ -638,21 +774,70 @@ f4_xslice_cluster_kernel(const __grid_constant__ XsliceGroup g)
 #pragma unroll
         for (int j = 1; j < 8; j++) amax = max(amax, s_warp[j]);
         s_part = amax;
+#ifdef MMB_MEASURE_MODES
+        MMB_TRACE_MIN(g.trace_slot, 3);
+        MMB_TRACE_MAX(g.trace_slot, 6);
+#endif
     }
     cluster.sync();                              /* every part's maximum is in place */
+#ifdef MMB_MEASURE_MODES
+    if (tid == 0)
+        MMB_TRACE_MAX(g.trace_slot, 7);
+#endif
     uint32_t row_amax = 0;
 #pragma unroll
     for (uint32_t r = 0; r < MMB_XS_CLUSTER; r++)
         row_amax = max(row_amax, *cluster.map_shared_rank(&s_part, r));
     cluster.sync();                              /* nobody leaves while its shared memory is still read */
+#ifdef MMB_MEASURE_MODES
+    if (tid == 0)
+        MMB_TRACE_MAX(g.trace_slot, 9);
+#endif
     const RowFrame f = row_frame(row_amax);
     uint8_t *planes = it.scratch + MMB_MX_PLANES_OFF;
     if (part == 0 && tid == 0 && m < it.M)
         row_factors(f, reinterpret_cast<float *>(it.scratch + MMB_MX_ROWSCALE_OFF), m);
     if (in_row)
         xslice_block(w, f, loaded, planes, planes + MMB_MX_PLANES_B(it.nb, it.K), it.K, m, blk);
+#ifdef MMB_MEASURE_MODES
+    if (threadIdx.x == 0)
+        MMB_TRACE_MAX(g.trace_slot, 11);         /* thread 0's own block sliced */
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        MMB_TRACE_MAX(g.trace_slot, 4);
+        MMB_TRACE_MIN(g.trace_slot, 10);
+    }
+#endif
 }
 } // namespace mmb
+
+#ifdef MMB_MEASURE_MODES
+static uint32_t g_trace_next;       /* rows handed out since the last reset */
+/* All rows back to "nothing recorded": minima at the largest value, maxima at zero. */
+extern "C" int mmb_trace_reset(void)
+{
+    static unsigned long long init[MMB_TRACE_SLOTS][16];
+    for (uint32_t i = 0; i < MMB_TRACE_SLOTS; i++)
+        for (uint32_t k = 0; k < 16u; k++)
+            init[i][k] = (k == 0u || k == 1u || k == 3u || k == 8u || k == 10u) ? ~0ull : 0ull;
+    g_trace_next = 0;
+    return static_cast<int>(cudaMemcpyToSymbol(mmb::g_trace, init, sizeof init));
+}
+/* Minima and maxima are kept across replays of a captured launch: reset the values, keep the rows. */
+extern "C" int mmb_trace_clear(void)
+{
+    const uint32_t keep = g_trace_next;
+    const int e = mmb_trace_reset();
+    g_trace_next = keep;
+    return e;
+}
+extern "C" int mmb_trace_read(unsigned long long *out, uint32_t *rows_out)
+{
+    *rows_out = g_trace_next;
+    return static_cast<int>(cudaMemcpyFromSymbol(out, mmb::g_trace, sizeof(unsigned long long) * 16u * MMB_TRACE_SLOTS));
+}
+static uint32_t trace_take(void) { return g_trace_next < MMB_TRACE_SLOTS ? ++g_trace_next : 0u; }
+#endif
 
 extern "C" int mmb_mxg_init(void)
 {
@@ -678,6 +863,9 @@ extern "C" int mmb_launch_xslice_rows(const void *x, void *scratch, uint32_t M, 
     memset(&xs, 0, sizeof xs);
     xs.n = 1;
     xs.pdl = static_cast<uint32_t>(pdl);
+#ifdef MMB_MEASURE_MODES
+    xs.trace_slot = trace_take();
+#endif
     xs.item[0].x = static_cast<const uint16_t *>(x);
     xs.item[0].scratch = static_cast<uint8_t *>(scratch);
     xs.item[0].M = M; xs.item[0].K = K; xs.item[0].nb = nb; xs.item[0].m_pad = nb / MMB_MX_PLANES;
@@ -752,6 +940,9 @@ extern "C" int mmb_launch_mxg(const mmb_group *hg, void *stream, uint32_t *kerne
     attr[0].val.programmaticStreamSerializationAllowed = hg->pdl ? 1 : 0;
     if (xs.n) {
         xs.pdl = static_cast<uint32_t>(hg->pdl);
+#ifdef MMB_MEASURE_MODES
+        xs.trace_slot = trace_take();
+#endif
         cudaLaunchConfig_t cfg = {};
         cfg.blockDim = dim3(256);
         cfg.stream = st;
@@ -793,6 +984,9 @@ extern "C" int mmb_launch_mxg(const mmb_group *hg, void *stream, uint32_t *kerne
         gattr[1].val.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
         cfg.numAttrs = 2;
     }
+#ifdef MMB_MEASURE_MODES
+    grp.trace_slot = trace_take();
+#endif
     if (kernels_launched)
         *kernels_launched = launched + 1u;
     /* the smallest parameter block that holds the ops (its leading bytes are the larger one's) */
