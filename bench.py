@@ -560,6 +560,82 @@ class Bench:
                 "us_per_step_first": round(marks[0] * 1e3, 2), "us_per_step_last": round(marks[-1] * 1e3, 2),
                 "by_clock": rows, "reasons": clk.summary()["reasons"]}
 
+    def chain_timeline(self, M=16):
+        """Where the time of dependent launches goes: globaltimer stamps taken inside the
+        slicing kernel and the group kernel of every launch of one captured step (first and last
+        CTA in, past the grid-dependency wait, MMAs done, epilogues done).  Needs a library
+        built with -DMMB_MEASURE_MODES (MIMFER_B200_LIB points at it); two workloads: four down
+        ops that write the same output, and three layers in the reference planner's order."""
+        import ctypes as C
+        from mimfer_b200 import _lib as L
+        raw = C.CDLL(L.LIB_PATH)
+        if not hasattr(raw, "mmb_trace_read"):
+            raise SystemExit("chain_timeline needs a build with -DMMB_MEASURE_MODES")
+        raw.mmb_trace_read.argtypes = [C.c_void_p, C.POINTER(C.c_uint32)]
+        names = {"slice": ("in_first", "dep_first", "dep_last", "loads_first", "done_last", "in_last", "loads_last",
+                           "sync1_last", None, "sync2_last", "done_first", "sliced_last"),
+                 "group": ("in_first", "dep_first", "dep_last", "unit1_mma_first", "done_last", "in_last",
+                           "unit1_mma_last", "mma_last", "done_first", "producer_last", "stage1_first", None)}
+
+        def run(eng):
+            eng.launch()
+            self.rt.sync()
+            eng.capture()
+            for _ in range(5):
+                eng.launch()
+            self.rt.sync()
+            assert raw.mmb_trace_clear() == 0
+            eng.launch()
+            self.rt.sync()
+            buf = np.zeros((1024, 16), dtype=np.uint64)
+            n = C.c_uint32()
+            assert raw.mmb_trace_read(buf.ctypes.data, C.byref(n)) == 0
+            rows = [buf[i] for i in range(n.value) if buf[i][4] != 0]
+            t0 = min(int(r[0]) for r in rows)
+            out = []
+            for r in rows:
+                kind = "group" if int(r[15]) == 1 else "slice"
+                rec = {"kernel": kind}
+                for k, name in enumerate(names[kind]):
+                    if name and int(r[k]) not in (0, 2 ** 64 - 1):
+                        rec[name] = round((int(r[k]) - t0) / 1e3, 2)
+                out.append(rec)
+            ms = self.timed(eng.launch, 20, 3)
+            groups = eng.n_group_launches()
+            eng.close()
+            return {"us_per_step": ms * 1e3, "group_launches": groups, "launches_us_from_first_entry": out}
+
+        assert raw.mmb_trace_reset() == 0
+        K, N = SHAPES["down"]
+        x, y = self.acts(M, K), self.empty(M, N)
+        eng = self.mm.LinearEngine(self.rt, max_ops=8)
+        for _ in range(4):
+            eng.add(x, self.dev_weight(self.weight("down")), y)
+        res = {"four_downs_one_output": run(eng)}
+        assert raw.mmb_trace_reset() == 0
+        K, inter = SHAPES["gate_up"][0], SHAPES["gate_up"][1] // 2
+        full = self.weight("gate_up")
+        lin = ("q", "k", "v", "o", "down")
+        xx, xo = self.acts(M, K), self.acts(M, SHAPES["o"][0])
+        g, u, h = self.empty(M, inter), self.empty(M, inter), self.empty(M, inter)
+        ys = {n: self.empty(M, SHAPES[n][1]) for n in lin}
+        keep = []
+        eng = self.mm.LinearEngine(self.rt, max_ops=32)
+        eng.fuse_mlp(True)
+        for _ in range(3):
+            ws = {n: self.dev_weight(self.weight(n)) for n in lin}
+            wg, wu = full.rows(0, inter), full.rows(inter, 2 * inter)
+            keep.append((ws, self.mm.place_weights([wg, wu], self.dev)))
+            for n in ("q", "k", "v"):
+                eng.add(xx, ws[n], ys[n])
+            eng.add(xo, ws["o"], ys["o"])
+            eng.add(xx, wg, g, note=b"gate")
+            eng.add(xx, wu, u, note=b"up")
+            eng.add_silu_mul(g, u, h)
+            eng.add(h, ws["down"], ys["down"])
+        res["planner_order_three_layers"] = run(eng)
+        return res
+
     def _shard_rows(self, name):
         per = SHAPES[name][1] // self.world
         return (self.rank * per, (self.rank + 1) * per)
@@ -1088,6 +1164,8 @@ def run_case(b, case, steps, warmup):
         return b.prefill_sweep(steps, warmup, ms_list=(2048,), names=("down",))
     if case == "prefill_kv":       # k at M=2048: 32 tiles, all of them split
         return b.prefill_sweep(steps, warmup, ms_list=(2048,), names=("k",))
+    if case == "chain_timeline":   # measurement build only: time stamps inside dependent launches
+        return b.chain_timeline()
     if case == "planner_layers8":  # eight layers in the reference planner's op order, with their dependencies
         return b.decode_step_planner(steps, warmup, layers=8)
     if case == "tp":               # the tensor-parallel series alone (any number of ranks)

@@ -39,7 +39,7 @@ namespace mmb {
  * MMAs done in the first/last CTA, [7] last MMAs of all, [8]/[4] first/last epilogue warp
  * done, [9] last producer done, [10] first stage landed.  Slicing kernel: [3]/[6] loads
  * done, [7]/[9] last CTA past the first/second cluster barrier, [11] last thread 0 has sliced
- * its block, [10]/[4] first/last CTA done. */
+ * its block, [10]/[4] first/last CTA done.  [15]: 1 = group kernel, 2 = slicing kernel. */
 #ifdef MMB_MEASURE_MODES
 #define MMB_TRACE_SLOTS 1024u
 __device__ unsigned long long g_trace[MMB_TRACE_SLOTS][16];
@@ -53,9 +53,11 @@ __device__ __forceinline__ void trace_max(uint32_t slot1, uint32_t k)
 }
 #define MMB_TRACE_MIN(slot1, k) trace_min(slot1, k)
 #define MMB_TRACE_MAX(slot1, k) trace_max(slot1, k)
+#define MMB_TRACE_KIND(slot1, v) do { if (slot1) g_trace[(slot1) - 1u][15] = (v); } while (0)
 #else
 #define MMB_TRACE_MIN(slot1, k) ((void)0)
 #define MMB_TRACE_MAX(slot1, k) ((void)0)
+#define MMB_TRACE_KIND(slot1, v) ((void)0)
 #endif
 
 struct __align__(128) MxgOp {
@@ -216,6 +218,7 @@ f4_mxg_kernel(const __grid_constant__ MxgParams<NOPS> prm)
     if (tid == 0) {
         MMB_TRACE_MIN(grp.trace_slot, 0);
         MMB_TRACE_MAX(grp.trace_slot, 5);
+        MMB_TRACE_KIND(grp.trace_slot, 1ull);
         for (uint32_t s = 0; s < ST; s++) {
             mbar_init(bar_full + 8u * s, 1u);
             mbar_init(bar_empty + 8u * s, 2u);
@@ -306,6 +309,10 @@ f4_mxg_kernel(const __grid_constant__ MxgParams<NOPS> prm)
         /* ------------------------------ MMA issue ------------------------------ */
         const uint32_t h = warp == 1 ? 0u : 1u;
         if (lane == 0) {
+            /* nothing to issue before the kernel in front is done (the digit planes are its
+             * output): wait for that in hardware instead of polling the first stage's barrier,
+             * which took issue slots from the slicing CTA that shares the SM meanwhile */
+            grid_dep_wait();
             UnitWalk w;
             uint32_t s = 0, round = 0, gstep = 0, j = 0;
             for (w.start(q_ids, q_full, q_empty, grp.status); w.valid<false>(grp, ops); w.next(), j++) {
@@ -342,6 +349,7 @@ f4_mxg_kernel(const __grid_constant__ MxgParams<NOPS> prm)
         const uint32_t quad = warp & 3u;
         const uint32_t mine_t = (warp - 2u) >> 2;
         const uint32_t tq = tmem + ((quad * 32u) << 16);
+        grid_dep_wait();                                    /* as the MMA threads: no polling before the planes can exist */
         UnitWalk w;
         uint32_t s = 0, round = 0, gstep = 0;
         uint32_t s1 = 0, round1 = 0, s2 = 0, round2 = 0;
@@ -719,9 +727,9 @@ f4_xslice_group_kernel(const __grid_constant__ XsliceGroup g)
 
 /* One launch, one pass over the activations: a cluster of eight CTAs per (padded)
  * activation row, 4096 values per CTA, one 16-wide block per thread.  Each CTA
- * leaves the largest magnitude of its part in its shared memory; after a cluster
- * barrier every CTA reads the eight values through distributed shared memory and
- * slices its blocks.  Rows up to 32768 long; longer ones take the two-pass kernels. */
+ * writes the largest magnitude of its part into the shared memory of all eight
+ * (distributed shared memory); after a cluster barrier every CTA has the eight values
+ * and slices its blocks.  Rows up to 32768 long; longer ones take the two-pass kernels. */
 #define MMB_XS_CLUSTER 8u
 #define MMB_XS_CTA_VALUES 4096u
 
@@ -731,11 +739,12 @@ f4_xslice_cluster_kernel(const __grid_constant__ XsliceGroup g)
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     __shared__ uint32_t s_warp[8];
-    __shared__ uint32_t s_part;                  /* this CTA's maximum, read by the whole cluster */
+    __shared__ uint32_t s_all[MMB_XS_CLUSTER];   /* the maxima of the row's eight parts, written by their CTAs */
 #ifdef MMB_MEASURE_MODES
     if (threadIdx.x == 0) {
         MMB_TRACE_MIN(g.trace_slot, 0);
         MMB_TRACE_MAX(g.trace_slot, 5);
+        MMB_TRACE_KIND(g.trace_slot, 2ull);
     }
 #endif
     grid_dep_launch();
@@ -770,29 +779,31 @@ f4_xslice_cluster_kernel(const __grid_constant__ XsliceGroup g)
     if ((tid & 31u) == 0)
         s_warp[tid >> 5] = amax;
     __syncthreads();
-    if (tid == 0) {
+    /* every CTA writes its maximum into all eight CTAs' shared memory; after one cluster
+     * barrier each reads its own copy (remote loads and a second barrier, so that nobody
+     * left while still being read, took 5 us of a chained launch's 12) */
+    if (tid < MMB_XS_CLUSTER) {
 #pragma unroll
-        for (int j = 1; j < 8; j++) amax = max(amax, s_warp[j]);
-        s_part = amax;
+        for (int j = 0; j < 8; j++) amax = max(amax, s_warp[j]);
+        *cluster.map_shared_rank(&s_all[part], tid) = amax;
+    }
 #ifdef MMB_MEASURE_MODES
+    if (tid == 0) {
         MMB_TRACE_MIN(g.trace_slot, 3);
         MMB_TRACE_MAX(g.trace_slot, 6);
-#endif
     }
+#endif
     cluster.sync();                              /* every part's maximum is in place */
 #ifdef MMB_MEASURE_MODES
-    if (tid == 0)
+    if (tid == 0) {
         MMB_TRACE_MAX(g.trace_slot, 7);
+        MMB_TRACE_MAX(g.trace_slot, 9);
+    }
 #endif
     uint32_t row_amax = 0;
 #pragma unroll
     for (uint32_t r = 0; r < MMB_XS_CLUSTER; r++)
-        row_amax = max(row_amax, *cluster.map_shared_rank(&s_part, r));
-    cluster.sync();                              /* nobody leaves while its shared memory is still read */
-#ifdef MMB_MEASURE_MODES
-    if (tid == 0)
-        MMB_TRACE_MAX(g.trace_slot, 9);
-#endif
+        row_amax = max(row_amax, s_all[r]);
     const RowFrame f = row_frame(row_amax);
     uint8_t *planes = it.scratch + MMB_MX_PLANES_OFF;
     if (part == 0 && tid == 0 && m < it.M)
