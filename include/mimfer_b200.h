@@ -354,6 +354,10 @@ mm_status mm_f4_wait_selftest(unsigned *done_dev);
  *   key 6  cap on the pipeline stages of a group launch (0 = as many as fit, default)
  *   key 10 the work units of a group launch are handed out as its CTAs ask for them
  *          (1, default) or dealt round-robin in advance (0)
+ *   key 11 copy streams per peer of mm_f4_tp_push (0 = about eight over all peers, default)
+ *   key 12 tensor-parallel prefill launches start the CTAs of their first wave spread over
+ *          this many percent of the time NVLink needs for one wave's tiles (100, default;
+ *          0 = all together; at most 400)
  *   key 9  the ops of a group launch run in order of activation rows, most first
  *          (1, default), or in list order (0)
  *   key 8  the prefill kernel cuts the tiles of its last, partial wave into K slices

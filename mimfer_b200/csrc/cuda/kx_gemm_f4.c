@@ -14,6 +14,8 @@
 #include "../kernels/launch.h"
 #include <cuda.h>
 #include <cuda_runtime_api.h>
+#include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 int mmb_stream_init(void);
@@ -55,9 +57,11 @@ static struct {
     uint32_t   sliced_M, sliced_K;
     void      *sliced_ws;
     unsigned long long launches;
+    uint32_t tp_stagger;    /* mm_f4_tune key 12: spread of the first wave of a tensor-parallel prefill launch, percent of a wave's NVLink time */
+    uint32_t tp_lanes;      /* mm_f4_tune key 11: copy streams per peer of mm_f4_tp_push, 0 = by the number of peers */
     /* experiment knobs (mm_f4_tune keys 2..4), all 0 in production */
     uint32_t   st_rows, st_split, st_dbg;
-} G = { .forced_variant = -1, .pdl = 1, .next_pdl = -1, .use_mx = 1, .group_sort = 1 };
+} G = { .forced_variant = -1, .pdl = 1, .next_pdl = -1, .use_mx = 1, .group_sort = 1, .tp_stagger = 100 };
 
 /* The workspace is cut into WS_REGIONS equal regions, each with its own arrival
  * counters, when every region still holds WS_REGION_MIN bytes; an op uses one
@@ -206,6 +210,8 @@ int mm_f4_tune(int key, int value)
     if (key == 6) { int old = (int)G.mx_stages; G.mx_stages = (uint32_t)value; return old; }
     if (key == 7) { int old = G.l2_window; G.l2_window = value ? 1 : 0; return old; }
     if (key == 10) { int old = !G.static_units; G.static_units = value ? 0 : 1; return old; }
+    if (key == 12) { int old = (int)G.tp_stagger; G.tp_stagger = value > 0 ? (uint32_t)(value > 400 ? 400 : value) : 0u; return old; }
+    if (key == 11) { int old = (int)G.tp_lanes; G.tp_lanes = value > 0 ? (uint32_t)value : 0u; return old; }
     if (key == 9) { int old = G.group_sort; G.group_sort = value ? 1 : 0; return old; }
     if (key == 8) { int old = !G.no_tail_split; G.no_tail_split = value ? 0 : 1; return old; }
     return -1;
@@ -232,20 +238,21 @@ unsigned long long mm_f4_launch_count(int reset)
  * slice is hundreds of megabytes per rank: stored from the kernel's epilogue it holds the
  * SM until NVLink has taken it; pushed by the copy engines it leaves while the next row
  * chunk is multiplied.  One side stream and one event per peer, made on first use. */
+#define TP_LANES 8u                     /* copy streams per peer at most */
 static struct {
-    cudaStream_t side[MMB_MAX_PEERS];
-    cudaEvent_t  done[MMB_MAX_PEERS], ready;
-    unsigned     made, pending;         /* bit d: stream d exists / carries copies since the last join */
+    cudaStream_t side[MMB_MAX_PEERS][TP_LANES];
+    cudaEvent_t  done[MMB_MAX_PEERS][TP_LANES], ready;
+    uint8_t      made[MMB_MAX_PEERS][TP_LANES], pending[MMB_MAX_PEERS][TP_LANES];
 } TP;
 
 static void tp_push_reset(void)
 {
-    for (uint32_t d = 0; d < MMB_MAX_PEERS; d++) {
-        if (TP.made & (1u << d)) {
-            cudaStreamDestroy(TP.side[d]);
-            cudaEventDestroy(TP.done[d]);
-        }
-    }
+    for (uint32_t d = 0; d < MMB_MAX_PEERS; d++)
+        for (uint32_t l = 0; l < TP_LANES; l++)
+            if (TP.made[d][l]) {
+                cudaStreamDestroy(TP.side[d][l]);
+                cudaEventDestroy(TP.done[d][l]);
+            }
     if (TP.ready)
         cudaEventDestroy(TP.ready);
     memset(&TP, 0, sizeof TP);
@@ -487,9 +494,20 @@ static mm_status linear_impl(const void *x, const void *payload, const void *sca
     for (uint32_t d = 0; d < n_dst; d++) a.y_dst[d] = y_dst[d];
     a.n_dst = n_dst; a.ldy = ldy; a.col0 = col0;
 
+
     mm_status st = plan_linear(x, payload, scale, y, n_dst, ldy, col0, M, K, N, shallow, &a.plan);
     if (st != MM_OK)
         return st;
+    if (n_dst > 1 && a.plan.variant == MM_F4_V_UMMA && G.tp_stagger) {
+        /* the time NVLink (about 750 bytes per ns) needs for one wave's tiles to the peers */
+        const uint32_t tiles = a.plan.grid_x * a.plan.grid_y;
+        const uint32_t ctas = tiles < (uint32_t)G.sm_count ? tiles : (uint32_t)G.sm_count;
+        const double wave_b = (double)a.plan.tile_m * (double)a.plan.tile_n * 2.0 * (double)(n_dst - 1u) * (double)ctas;
+        double ns = wave_b / 750.0 * (double)G.tp_stagger / 100.0;
+        if (ns > 400000.0) ns = 400000.0;
+        a.stagger_ns = tiles > ctas ? (uint32_t)ns : 0u;     /* a single wave gains nothing from it */
+        a.stagger_ctas = ctas;
+    }
 
     int err = 0;
     switch (a.plan.variant) {
@@ -920,6 +938,29 @@ mm_status mmb_group_launch(void)
             }
         }
 
+    /* among ops of equal activation rows the ones cut along K go first: their last slices
+     * end in the exchange (partial sums, ticket, the last arrival's additions: about 9 us),
+     * which then runs under the whole units of the other ops instead of after everything */
+    if (G.group_sort)
+        for (uint32_t i = 1; i < GR.n; i++) {
+            const gr_item it = GR.item[i];
+            const mm_f4_plan pl = plans[i];
+            uint32_t j = i;
+            while (j > 0 && GR.item[j - 1].op.n0 == it.op.n0 && plans[j - 1].split_k <= 1u && pl.split_k > 1u) {
+                GR.item[j] = GR.item[j - 1];
+                plans[j] = plans[j - 1];
+                j--;
+            }
+            GR.item[j] = it;
+            plans[j] = pl;
+        }
+#ifdef MMB_MEASURE_MODES
+    if (getenv("MMB_PRINT_PLANS"))
+        for (uint32_t i = 0; i < GR.n; i++)
+            fprintf(stderr, "group op %u: M=%u K=%u N=%u glu=%d rows=%u tiles=%u split=%u k_steps=%u\n", i,
+                    GR.item[i].op.n0, GR.item[i].op.n1, GR.item[i].op.n2, GR.item[i].glu, plans[i].tile_n,
+                    plans[i].grid_x, plans[i].split_k, plans[i].k_steps);
+#endif
     mmb_group *gg = &GR.g;
     memset(gg, 0, sizeof *gg);
     gg->pdl = GR.pdl;
@@ -1276,19 +1317,28 @@ mm_status mm_f4_tp_push(void *const *y_all, uint32_t n_ranks, uint32_t ldy, uint
     if (!TP.ready)
         CK(cudaEventCreateWithFlags(&TP.ready, cudaEventDisableTiming));
     CK(cudaEventRecord(TP.ready, cs));                       /* the slice is complete in the own copy */
+    /* One copy engine moves a strided slice at a fraction of what NVLink carries (three
+     * streams, one per peer of four ranks, reached 370 GB/s together): every peer gets
+     * several streams, about eight over all peers, and a push is cut into as many runs of
+     * rows. */
+    uint32_t lanes = G.tp_lanes ? G.tp_lanes : (TP_LANES + n_ranks - 2u) / (n_ranks - 1u);
+    if (lanes > TP_LANES) lanes = TP_LANES;
+    if (lanes > rows / 64u) lanes = rows / 64u ? rows / 64u : 1u;
     const size_t pitch = (size_t)ldy * 2u;
-    const size_t off = (size_t)row0 * pitch + (size_t)col0 * 2u;
-    for (uint32_t d = 1; d < n_ranks; d++) {
-        if (!(TP.made & (1u << d))) {
-            CK(cudaStreamCreateWithFlags(&TP.side[d], cudaStreamNonBlocking));
-            CK(cudaEventCreateWithFlags(&TP.done[d], cudaEventDisableTiming));
-            TP.made |= 1u << d;
+    for (uint32_t d = 1; d < n_ranks; d++)
+        for (uint32_t l = 0; l < lanes; l++) {
+            const uint32_t r0 = (uint32_t)((uint64_t)rows * l / lanes), r1 = (uint32_t)((uint64_t)rows * (l + 1u) / lanes);
+            const size_t off = (size_t)(row0 + r0) * pitch + (size_t)col0 * 2u;
+            if (!TP.made[d][l]) {
+                CK(cudaStreamCreateWithFlags(&TP.side[d][l], cudaStreamNonBlocking));
+                CK(cudaEventCreateWithFlags(&TP.done[d][l], cudaEventDisableTiming));
+                TP.made[d][l] = 1;
+            }
+            CK(cudaStreamWaitEvent(TP.side[d][l], TP.ready, 0));
+            CK(cudaMemcpy2DAsync((unsigned char *)y_all[d] + off, pitch, (const unsigned char *)y_all[0] + off, pitch,
+                                 (size_t)cols * 2u, r1 - r0, cudaMemcpyDefault, TP.side[d][l]));
+            TP.pending[d][l] = 1;
         }
-        CK(cudaStreamWaitEvent(TP.side[d], TP.ready, 0));
-        CK(cudaMemcpy2DAsync((unsigned char *)y_all[d] + off, pitch, (const unsigned char *)y_all[0] + off, pitch,
-                             (size_t)cols * 2u, rows, cudaMemcpyDefault, TP.side[d]));
-        TP.pending |= 1u << d;
-    }
     return MM_OK;
 }
 
@@ -1296,13 +1346,14 @@ mm_status mm_f4_tp_push_join(void)
 {
     MM_CHECK(ensure_ready());
     cudaStream_t cs = (cudaStream_t)mm_cuda_stream_raw(MM_ST_COMPUTE);
-    for (uint32_t d = 1; d < MMB_MAX_PEERS; d++) {
-        if (!(TP.pending & (1u << d)))
-            continue;
-        CK(cudaEventRecord(TP.done[d], TP.side[d]));
-        CK(cudaStreamWaitEvent(cs, TP.done[d], 0));
-    }
-    TP.pending = 0;
+    for (uint32_t d = 1; d < MMB_MAX_PEERS; d++)
+        for (uint32_t l = 0; l < TP_LANES; l++) {
+            if (!TP.pending[d][l])
+                continue;
+            CK(cudaEventRecord(TP.done[d][l], TP.side[d][l]));
+            CK(cudaStreamWaitEvent(cs, TP.done[d][l], 0));
+            TP.pending[d][l] = 0;
+        }
     return MM_OK;
 }
 

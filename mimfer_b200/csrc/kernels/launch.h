@@ -138,6 +138,9 @@ typedef struct mmb_args {
      * elements and column offset col0, instead of to y. */
     void       *y_dst[MMB_MAX_PEERS];
     uint32_t    n_dst, ldy, col0;
+    /* Prefill, tensor parallel: CTA i of the first `stagger_ctas` starts i / stagger_ctas
+     * of stagger_ns late (0 = all together), see umma.cu. */
+    uint32_t    stagger_ns, stagger_ctas;
     float       gs;
     uint32_t    M, K, N;
     /* Gated pair (glu != 0): `payload`/`scale` are the lower-addressed of the gate

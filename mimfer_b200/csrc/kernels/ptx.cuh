@@ -107,6 +107,20 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const TmaDesc *map, in
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
         : "memory");
 }
+/* ---- bulk copies shared -> global (no tensor map): 16-byte aligned both sides, a
+ * multiple of 16 bytes; completion is tracked per thread in bulk groups ---------------- */
+__device__ __forceinline__ void bulk_store(void *dst, uint32_t src, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 ::"l"(reinterpret_cast<uint64_t>(dst)), "r"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+/* all but the newest `KEEP` groups of this thread have read their shared-memory source */
+template <int KEEP>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(KEEP) : "memory"); }
+/* every group of this thread is complete (the data is written) */
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void tma_prefetch_desc(const TmaDesc *map)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");

@@ -57,6 +57,7 @@ struct UmmaParams {
     uint32_t  full_tiles;    /* tiles that run whole; the ones after them are split      */
     uint32_t  splits;        /* K slices of every tile after full_tiles (>= 1)           */
     float    *partial;       /* [split tile][slice][half][32-column chunk][4-column group][128 rows][4] fp32 sums */
+    uint32_t  stagger_ns, stagger_ctas;   /* tensor parallel: CTA i < stagger_ctas starts i / stagger_ctas of stagger_ns late */
 };
 
 
@@ -106,6 +107,21 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
     const uint32_t tmem_slot = accum_full + 8u;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    /* Tensor parallel: the epilogues store every tile to all ranks, and NVLink takes a
+     * wave's tiles more slowly than the SMs make them.  CTAs that start together reach
+     * their epilogues together, share the link evenly, leave together and start the next
+     * tiles together: the link idles during every main loop and the SMs during every
+     * epilogue.  The first wave therefore starts spread over the time the link needs for
+     * one wave's tiles; later CTAs inherit the spread, and some CTAs are always storing. */
+    if (p.stagger_ns && blockIdx.x < p.stagger_ctas) {
+        if (tid == 0) {
+            const uint64_t t0 = globaltimer_ns();
+            const uint64_t late = static_cast<uint64_t>(p.stagger_ns) * blockIdx.x / p.stagger_ctas;
+            while (globaltimer_ns() - t0 < late)
+                __nanosleep(500);
+        }
+        __syncthreads();
+    }
     /* activation-row tile fastest: the CTAs running together share a few weight
      * tiles (and all of x) through L2 instead of each streaming the whole weight */
     static_assert(!GLU || BN == 256, "the gated pair runs on 256-row weight tiles");
@@ -356,41 +372,64 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
                 __syncwarp();
             }
         } else {
-            constexpr uint32_t PIECES = HALVES * (BN / 128);
-            constexpr uint32_t PITCH = 272u;            /* 256 B of data + 16 B: conflict-free both ways */
+            /* One piece per warp: 32 rows of one 128-row half, and as many columns as make
+             * the two warps of a quadrant equal (all BN columns when the tile has two halves).
+             * A row of a piece leaves as one run of up to 512 bytes: measured on four GPUs, all
+             * storing to all, NVLink carried tiles written in 256-byte runs at 568 GB/s per GPU
+             * and in 512-byte runs at 617. */
+            constexpr uint32_t CG = HALVES == 2 ? 1u : 2u;         /* column groups of a tile */
+            constexpr uint32_t W = BN / CG;                        /* columns of a piece: 256, 128 or 64 */
+            constexpr uint32_t PITCH = W * 2u + 16u;               /* + 16 B: conflict-free both ways */
+            static_assert(MMB_UM_DEQ_WARPS * 32u * PITCH <= 2u * (A_B + B_B) + PAY_SLOTS * PAY_B,
+                          "the staging tiles lie in the operand stages (at least two) and the payload slots");
             const uint32_t stg = sm_a + (warp - 2u) * (32u * PITCH);
             const bool vec_ok = (p.N % 8u) == 0;
-            for (uint32_t c = pair; c < PIECES; c += 2u) {
-                const uint32_t h = c / (BN / 128), cc = c % (BN / 128);
-                const uint32_t n_base = n0 + cc * 128u;
+            /* Tensor parallel: every lane hands its finished row to the bulk-copy engine, once
+             * per destination (plain stores to the peers and the engine ended at the same time:
+             * the link is the limit, not the way the SM feeds it). */
+            const bool bulk = p.n_dst > 1u && vec_ok && ((p.ldy | p.col0) & 7u) == 0u;
+            const uint32_t h = pair / CG, cc = pair % CG;
+            const uint32_t n_base = n0 + cc * W;
 #pragma unroll
-                for (uint32_t q = 0; q < 4; q++) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + h * BN + cc * 128u + q * 32u, r);
-                    tmem_ld_wait();
+            for (uint32_t q = 0; q < W / 32u; q++) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + h * BN + cc * W + q * 32u, r);
+                tmem_ld_wait();
 #pragma unroll
-                    for (int v = 0; v < 4; v++) {
-                        uint4 o;
-                        o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]) * out_scale,
-                                          __uint_as_float(r[8 * v + 1]) * out_scale);
-                        o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]) * out_scale,
-                                          __uint_as_float(r[8 * v + 3]) * out_scale);
-                        o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]) * out_scale,
-                                          __uint_as_float(r[8 * v + 5]) * out_scale);
-                        o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]) * out_scale,
-                                          __uint_as_float(r[8 * v + 7]) * out_scale);
-                        sts128(stg + lane * PITCH + q * 64u + v * 16u, o);
-                    }
+                for (int v = 0; v < 4; v++) {
+                    uint4 o;
+                    o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]) * out_scale,
+                                      __uint_as_float(r[8 * v + 1]) * out_scale);
+                    o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]) * out_scale,
+                                      __uint_as_float(r[8 * v + 3]) * out_scale);
+                    o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]) * out_scale,
+                                      __uint_as_float(r[8 * v + 5]) * out_scale);
+                    o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]) * out_scale,
+                                      __uint_as_float(r[8 * v + 7]) * out_scale);
+                    sts128(stg + lane * PITCH + q * 64u + v * 16u, o);
                 }
+            }
+            if (bulk) {
+                fence_proxy_async_smem();                    /* the row this lane wrote, for the copy engine */
+                const uint32_t m = m0 + h * 128u + quad * 32u + lane;
+                const uint32_t cols = n_base < p.N ? (p.N - n_base < W ? p.N - n_base : W) : 0u;
+                if (m < p.M && cols) {
+                    const size_t off = static_cast<size_t>(m) * p.ldy + p.col0 + n_base;
+                    for (uint32_t d = 0; d < p.n_dst; d++)
+                        bulk_store(p.y[d] + off, stg + lane * PITCH, cols * 2u);
+                }
+                bulk_commit();
+            } else {
                 __syncwarp();
-                const uint32_t sub = lane >> 4, col16 = lane & 15u;      /* 2 rows x 16 chunks per store */
-                const uint32_t n = n_base + col16 * 8u;
+                constexpr uint32_t PER_ROW = W / 8u;             /* 16-byte chunks of a row: 32, 16 or 8 lanes */
+                const uint32_t sub = lane / PER_ROW, chunk = lane % PER_ROW;
+                const uint32_t n = n_base + chunk * 8u;
 #pragma unroll 4
-                for (uint32_t rr = 0; rr < 32u; rr += 2u) {
+                for (uint32_t rr = 0; rr < 32u; rr += 32u / PER_ROW) {
                     const uint32_t row = rr + sub;
                     const uint32_t m = m0 + h * 128u + quad * 32u + row;
                     if (m < p.M && n < p.N) {
-                        const uint4 o = lds128(stg + row * PITCH + col16 * 16u);
+                        const uint4 o = lds128(stg + row * PITCH + chunk * 16u);
                         const size_t off = static_cast<size_t>(m) * p.ldy + p.col0 + n;
                         if (vec_ok) {
                             for (uint32_t d = 0; d < p.n_dst; d++)
@@ -403,8 +442,9 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
                         }
                     }
                 }
-                __syncwarp();
             }
+            if (bulk)
+                bulk_wait_all();                             /* before the CTA gives up its shared memory */
         }
     }
 
@@ -523,6 +563,8 @@ static int launch_tile(const mmb_args *a, unsigned *status, cudaStream_t st)
     p.gs_up = a->gs_up;
     p.gate_plane = a->gate_plane ? 1u : 0u;
     p.pdl = static_cast<uint32_t>(a->pdl);
+    p.stagger_ns = a->stagger_ns;
+    p.stagger_ctas = a->stagger_ctas;
     const uint32_t tiles = a->plan.grid_x * a->plan.grid_y;
     const bool split = a->plan.split_k > 1 && a->plan.m_tiles > 0 && a->plan.m_tiles <= tiles && a->ws;
     p.m_tiles = a->plan.grid_y;
