@@ -938,22 +938,6 @@ mm_status mmb_group_launch(void)
             }
         }
 
-    /* among ops of equal activation rows the ones cut along K go first: their last slices
-     * end in the exchange (partial sums, ticket, the last arrival's additions: about 9 us),
-     * which then runs under the whole units of the other ops instead of after everything */
-    if (G.group_sort)
-        for (uint32_t i = 1; i < GR.n; i++) {
-            const gr_item it = GR.item[i];
-            const mm_f4_plan pl = plans[i];
-            uint32_t j = i;
-            while (j > 0 && GR.item[j - 1].op.n0 == it.op.n0 && plans[j - 1].split_k <= 1u && pl.split_k > 1u) {
-                GR.item[j] = GR.item[j - 1];
-                plans[j] = plans[j - 1];
-                j--;
-            }
-            GR.item[j] = it;
-            plans[j] = pl;
-        }
 #ifdef MMB_MEASURE_MODES
     if (getenv("MMB_PRINT_PLANS"))
         for (uint32_t i = 0; i < GR.n; i++)

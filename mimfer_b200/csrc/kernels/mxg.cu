@@ -309,10 +309,6 @@ f4_mxg_kernel(const __grid_constant__ MxgParams<NOPS> prm)
         /* ------------------------------ MMA issue ------------------------------ */
         const uint32_t h = warp == 1 ? 0u : 1u;
         if (lane == 0) {
-            /* nothing to issue before the kernel in front is done (the digit planes are its
-             * output): wait for that in hardware instead of polling the first stage's barrier,
-             * which took issue slots from the slicing CTA that shares the SM meanwhile */
-            grid_dep_wait();
             UnitWalk w;
             uint32_t s = 0, round = 0, gstep = 0, j = 0;
             for (w.start(q_ids, q_full, q_empty, grp.status); w.valid<false>(grp, ops); w.next(), j++) {
@@ -349,7 +345,6 @@ f4_mxg_kernel(const __grid_constant__ MxgParams<NOPS> prm)
         const uint32_t quad = warp & 3u;
         const uint32_t mine_t = (warp - 2u) >> 2;
         const uint32_t tq = tmem + ((quad * 32u) << 16);
-        grid_dep_wait();                                    /* as the MMA threads: no polling before the planes can exist */
         UnitWalk w;
         uint32_t s = 0, round = 0, gstep = 0;
         uint32_t s1 = 0, round1 = 0, s2 = 0, round2 = 0;
@@ -725,11 +720,21 @@ f4_xslice_group_kernel(const __grid_constant__ XsliceGroup g)
                two_pass ? reinterpret_cast<const uint32_t *>(it.scratch + MMB_MX_CHUNKMAX_OFF) : nullptr);
 }
 
+__device__ __forceinline__ uint32_t xslice_trace_slot(const XsliceGroup &g)
+{
+#ifdef MMB_MEASURE_MODES
+    return g.trace_slot;
+#else
+    (void)g;
+    return 0u;
+#endif
+}
+
 /* One launch, one pass over the activations: a cluster of eight CTAs per (padded)
  * activation row, 4096 values per CTA, one 16-wide block per thread.  Each CTA
- * writes the largest magnitude of its part into the shared memory of all eight
- * (distributed shared memory); after a cluster barrier every CTA has the eight values
- * and slices its blocks.  Rows up to 32768 long; longer ones take the two-pass kernels. */
+ * leaves the largest magnitude of its part in its shared memory; after a cluster
+ * barrier every CTA reads the eight values through distributed shared memory and
+ * slices its blocks.  Rows up to 32768 long; longer ones take the two-pass kernels. */
 #define MMB_XS_CLUSTER 8u
 #define MMB_XS_CTA_VALUES 4096u
 
@@ -739,23 +744,20 @@ f4_xslice_cluster_kernel(const __grid_constant__ XsliceGroup g)
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     __shared__ uint32_t s_warp[8];
-    __shared__ uint32_t s_all[MMB_XS_CLUSTER];   /* the maxima of the row's eight parts, written by their CTAs */
-#ifdef MMB_MEASURE_MODES
+    __shared__ uint32_t s_part;                  /* this CTA's maximum, read by the whole cluster */
+    const uint32_t slot = xslice_trace_slot(g);
     if (threadIdx.x == 0) {
-        MMB_TRACE_MIN(g.trace_slot, 0);
-        MMB_TRACE_MAX(g.trace_slot, 5);
-        MMB_TRACE_KIND(g.trace_slot, 2ull);
+        MMB_TRACE_MIN(slot, 0);
+        MMB_TRACE_MAX(slot, 5);
+        MMB_TRACE_KIND(slot, 2ull);
     }
-#endif
     grid_dep_launch();
     if (g.pdl != MMB_PDL_OFF)
         grid_dep_wait();                         /* the activations are the previous kernel's output */
-#ifdef MMB_MEASURE_MODES
     if (threadIdx.x == 0) {
-        MMB_TRACE_MIN(g.trace_slot, 1);
-        MMB_TRACE_MAX(g.trace_slot, 2);
+        MMB_TRACE_MIN(slot, 1);
+        MMB_TRACE_MAX(slot, 2);
     }
-#endif
     const uint32_t row = blockIdx.x / MMB_XS_CLUSTER, part = blockIdx.x % MMB_XS_CLUSTER;
     uint32_t i = 0;
     while (i + 1u < g.n && row >= g.row0[i + 1u]) i++;
@@ -779,31 +781,26 @@ f4_xslice_cluster_kernel(const __grid_constant__ XsliceGroup g)
     if ((tid & 31u) == 0)
         s_warp[tid >> 5] = amax;
     __syncthreads();
-    /* every CTA writes its maximum into all eight CTAs' shared memory; after one cluster
-     * barrier each reads its own copy (remote loads and a second barrier, so that nobody
-     * left while still being read, took 5 us of a chained launch's 12) */
-    if (tid < MMB_XS_CLUSTER) {
+    if (tid == 0) {
 #pragma unroll
-        for (int j = 0; j < 8; j++) amax = max(amax, s_warp[j]);
-        *cluster.map_shared_rank(&s_all[part], tid) = amax;
+        for (int j = 1; j < 8; j++) amax = max(amax, s_warp[j]);
+        s_part = amax;
+        MMB_TRACE_MIN(slot, 3);
+        MMB_TRACE_MAX(slot, 6);
     }
-#ifdef MMB_MEASURE_MODES
-    if (tid == 0) {
-        MMB_TRACE_MIN(g.trace_slot, 3);
-        MMB_TRACE_MAX(g.trace_slot, 6);
-    }
-#endif
     cluster.sync();                              /* every part's maximum is in place */
-#ifdef MMB_MEASURE_MODES
-    if (tid == 0) {
-        MMB_TRACE_MAX(g.trace_slot, 7);
-        MMB_TRACE_MAX(g.trace_slot, 9);
-    }
-#endif
+    if (tid == 0)
+        MMB_TRACE_MAX(slot, 7);
     uint32_t row_amax = 0;
 #pragma unroll
     for (uint32_t r = 0; r < MMB_XS_CLUSTER; r++)
-        row_amax = max(row_amax, s_all[r]);
+        row_amax = max(row_amax, *cluster.map_shared_rank(&s_part, r));
+    /* nobody leaves while its shared memory is still read.  (Writing the maxima into all
+     * eight CTAs' shared memory instead, with one barrier, made this kernel 1.7 us shorter
+     * and the steps that run it between dependent group launches 3 to 5 % longer.) */
+    cluster.sync();
+    if (tid == 0)
+        MMB_TRACE_MAX(slot, 9);
     const RowFrame f = row_frame(row_amax);
     uint8_t *planes = it.scratch + MMB_MX_PLANES_OFF;
     if (part == 0 && tid == 0 && m < it.M)
@@ -811,12 +808,12 @@ f4_xslice_cluster_kernel(const __grid_constant__ XsliceGroup g)
     if (in_row)
         xslice_block(w, f, loaded, planes, planes + MMB_MX_PLANES_B(it.nb, it.K), it.K, m, blk);
 #ifdef MMB_MEASURE_MODES
-    if (threadIdx.x == 0)
-        MMB_TRACE_MAX(g.trace_slot, 11);         /* thread 0's own block sliced */
+    if (tid == 0)
+        MMB_TRACE_MAX(slot, 11);                 /* thread 0's own block sliced */
     __syncthreads();
-    if (threadIdx.x == 0) {
-        MMB_TRACE_MAX(g.trace_slot, 4);
-        MMB_TRACE_MIN(g.trace_slot, 10);
+    if (tid == 0) {
+        MMB_TRACE_MAX(slot, 4);
+        MMB_TRACE_MIN(slot, 10);
     }
 #endif
 }
