@@ -21,7 +21,15 @@ The JSON line also carries the prefill GEMM sweep ("prefill": TFLOP/s against
 the dense bf16 tensor roofline), the 64-layer decode step ("decode_step"), the
 like-for-like tensor-parallel series at every N ("tp"), the end-to-end number
 through the host-buffer C-ABI call ("e2e"), the roofline of the dominant
-kernel and the reference CPU kernel timed on this host ("cpu_baseline").
+kernel and the reference CPU kernel timed on this host ("cpu_baseline").  In "tp"
+the prefill exchange is timed in both forms the library has (the epilogue's peer
+stores, the copy engines) and the faster one is the figure ("prefill_exchange").
+
+--case NAME runs one workload alone and prints its own line: single kernels for
+profiling (decode, group, sweep, prefill, prefill_tail, ...), "tp" (the
+tensor-parallel series at any number of ranks), "planner_layers8" (eight layers
+in the reference planner's op order) and "chain_timeline" (time stamps from inside
+dependent launches; needs a library built with -DMMB_MEASURE_MODES).
 
 Synthetic data: weights N(0, 0.02) seed 0 packed by the library's packer,
 activations N(0, 1) seed 1 rounded to bf16.

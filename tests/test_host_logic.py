@@ -230,3 +230,15 @@ def test_tensor_parallel_push_validates_arguments(lib):
     assert lib.mm_f4_tp_push(ptrs, 2, 516, 0, 256, 0, 4) == L.MM_ERR_SHAPE
     assert lib.mm_f4_tp_push(bad, 2, 512, 0, 256, 0, 4) == L.MM_ERR_STATE
     lib.mm_log_set_level(1)
+
+
+def test_tune_keys_of_the_tensor_parallel_forms(lib):
+    """mm_f4_tune returns the previous value: copy streams per peer (key 11, 0 = automatic) and
+    the spread of a tensor-parallel prefill launch's first wave in percent (key 12, default 100,
+    capped at 400); an unknown key is refused."""
+    assert lib.mm_f4_tune(11, 4) == 0
+    assert lib.mm_f4_tune(11, 0) == 4
+    assert lib.mm_f4_tune(12, 0) == 100
+    assert lib.mm_f4_tune(12, 1000) == 0
+    assert lib.mm_f4_tune(12, 100) == 400
+    assert lib.mm_f4_tune(99, 1) == -1

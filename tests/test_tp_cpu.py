@@ -67,3 +67,27 @@ def test_shard_bounds():
     assert [shard_bounds(34816, r, 4) for r in range(4)] == [(0, 8704), (8704, 17408), (17408, 26112), (26112, 34816)]
     with pytest.raises(ValueError):
         shard_bounds(100, 0, 8)
+
+
+def test_push_chunks_cover_the_rows_once_and_end_on_a_short_chunk():
+    """Row chunks of the copy-engine form of the exchange: every row once, in order, chunks of
+    the asked size, the last whole chunk halved so that little is left to push at the end."""
+    from mimfer_b200.tp import push_chunks
+    for M in (1, 32, 300, 512, 1024, 1100, 2048, 8192):
+        for rows in (128, 512, 1024):
+            chunks = push_chunks(M, rows)
+            assert chunks[0][0] == 0 and sum(n for _, n in chunks) == M
+            assert all(a + n == b for (a, n), (b, _) in zip(chunks, chunks[1:]))
+            assert all(0 < n <= rows for _, n in chunks)
+    assert push_chunks(8192, 1024)[-2:] == [(7168, 512), (7680, 512)]
+    assert push_chunks(1100, 128)[-1] == (1024, 76)
+
+
+def test_tensor_parallel_modes_are_checked():
+    import mimfer_b200 as mm
+    from mimfer_b200.tp import TpLinear
+    w = mm.make_weight(64, 64, seed=0)
+    with pytest.raises(ValueError):
+        TpLinear(w, 0, 1, local_op=lambda x, s, y: None, mode="scatter")
+    with pytest.raises(ValueError):
+        TpLinear(w, 0, 1, local_op=lambda x, s, y: None, mode="push", push_rows=0)
