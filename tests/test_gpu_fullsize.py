@@ -182,3 +182,47 @@ def test_push_of_row_chunks_on_one_gpu(rt, oracle):
     for (a, b) in ((r * ns, r * ns + 256), (N - 256, N)):
         want = oracle.gemm_f4(xb, w.payload, w.scales, w.gs, rows=rows, n_begin=a, n_end=b)
         assert row_rel_l2(y1[rows][:, a:b], want) <= REL_L2_TOL, (a, b)
+
+
+@pytest.mark.parametrize("world,r", [(8, 3), (4, 1)])
+def test_decode_sweep_shards_as_one_group_launch(rt, oracle, world, r):
+    """The bench's tensor-parallel decode sweep as rank r of `world` runs it: the ten ops (gate+up
+    and down at M = 1..16), each op's r-th N-shard, added with mm_lin_engine_add_tp and launched as
+    one group whose epilogue stores into two full-width outputs.  Both must hold the shard's
+    columns - against the oracle on windows at the shard's edges - and nothing else."""
+    torch = rt.torch
+    eng = mm.LinearEngine(rt, max_ops=12)
+    ops, keep = [], []
+    try:
+        for name in ("gate_up", "down"):
+            w = weight(rt, name)
+            K, N = SHAPES[name]
+            ns = N // world
+            assert ns * world == N and ns % 8 == 0
+            host = mm.NvFp4Weight(w.payload, w.scales, w.gs, w.N, w.K)
+            shard = host.rows(r * ns, (r + 1) * ns).to_device(rt.device)
+            for M in (1, 2, 4, 8, 16):
+                xb = mm.make_activations(M, K, seed=10 + M)
+                x = rt.to_device_bf16(xb)
+                outs = [torch.zeros((M, N), dtype=torch.bfloat16, device=rt.device) for _ in range(2)]
+                ptrs = (C.c_void_p * 2)(outs[0].data_ptr(), outs[1].data_ptr())
+                keep.append((x, ptrs, shard))
+                eng.add_tp(x, shard, outs[0], ptrs, 2, r * ns)
+                ops.append((name, M, xb, outs, ns))
+        torch.cuda.synchronize()
+        eng.capture()
+        for _ in range(2):
+            eng.launch()
+        rt.sync()
+        assert rt.device_status() == 0 and eng.n_group_launches() >= 1
+        for name, M, xb, outs, ns in ops:
+            w = weight(rt, name)
+            a, b = rt.from_device_bf16(outs[0]), rt.from_device_bf16(outs[1])
+            assert np.array_equal(a, b), (name, M)
+            assert not a[:, :r * ns].any() and not a[:, (r + 1) * ns:].any(), (name, M)
+            width = min(256, ns)
+            for lo in (r * ns, (r + 1) * ns - width):
+                want = oracle.gemm_f4(xb, w.payload, w.scales, w.gs, n_begin=lo, n_end=lo + width)
+                assert row_rel_l2(a[:, lo:lo + width], want) <= REL_L2_TOL, (name, M, lo)
+    finally:
+        eng.close()
