@@ -248,7 +248,10 @@ float     mm_norm_eps_get(void);
  * kernel's epilogue stores the slice into all `n_ranks` copies of the full
  * output y_all[r] ([M][ldy] bf16; y_all[0] is this GPU's own, the others are
  * peer-mapped device pointers, e.g. from a symmetric-memory rendezvous), so
- * the exchange rides on the compute kernel as plain peer stores over NVLink.
+ * the exchange rides on the compute kernel as unicast peer writes over NVLink
+ * (stores at decode sizes; at prefill sizes one bulk copy from shared memory per
+ * output-tile row and destination, and the CTAs of the first wave start spread over
+ * the time the link needs for one wave's tiles, mm_f4_tune key 12).
  * The caller must run a cross-rank barrier on `stream` after the op before any
  * rank reads its copy, and must not let a rank start the next write into a
  * buffer its peers still read.  n_ranks <= 8; col0 and ldy multiples of 8. */

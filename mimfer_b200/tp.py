@@ -9,7 +9,7 @@ NVLink; gloo on CPU in the tests) into [tp][M][N/tp] and laid out as [M][N].
 
 mode="fused" removes the separate exchange: every rank's full output lives in
 symmetric memory, and the kernel's epilogue stores each finished tile into all
-ranks' copies through peer-mapped pointers (plain stores over NVLink, no
+ranks' copies through peer-mapped pointers (stores and bulk copies over NVLink, no
 multicast), so the transfer overlaps the remaining tiles; one cross-rank barrier
 kernel of this library (a bounded device-side spin on flags in symmetric memory)
 on the stream closes the op.  The full outputs are double-buffered: call i of a
@@ -28,7 +28,7 @@ NVLink has taken them.  The reference has no multi-GPU path; this is new surface
 import ctypes as C
 import os
 
-# The kernels store to peers with plain stores: the symmetric buffers need no NVLink
+# The kernels write to peers with unicast stores and bulk copies: the symmetric buffers need no NVLink
 # multicast binding, and a rank that dies while bound to one disturbs the other GPUs.
 os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
