@@ -280,8 +280,8 @@ mm_status mm_f4_tp_barrier(void *const *flags_all, uint32_t n_ranks, uint32_t ra
  * compute stream itself goes on, so the next chunk's GEMM runs while the copy engines
  * drain this one over NVLink.  mm_f4_tp_push_join makes the compute stream wait for every
  * push since the last join; call it before mm_f4_tp_barrier.  ldy, col0 and cols are
- * multiples of 8 (16-byte rows); MM_ERR_SHAPE otherwise.  Inside a stream capture the
- * side streams join the capture, and the join must come before the capture ends. */
+ * multiples of 8 (16-byte rows); MM_ERR_SHAPE otherwise.  Issue both calls eagerly: they
+ * have not been exercised inside a stream capture. */
 mm_status mm_f4_tp_push(void *const *y_all, uint32_t n_ranks, uint32_t ldy, uint32_t col0, uint32_t cols,
                         uint32_t row0, uint32_t rows);
 mm_status mm_f4_tp_push_join(void);
