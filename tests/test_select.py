@@ -152,3 +152,41 @@ def test_gated_pair_plans(lib):
         with pytest.raises(mm.MimferError) as e:
             mm.select_plan(M, K, N, ptr_align=align, glu=True)
         assert e.value.status == 7                                    # MM_ERR_UNSUPPORTED
+
+
+def test_seeded_random_shapes_keep_the_plan_invariants(lib):
+    """600 seeded random legal shapes, with and without a workspace: whatever kernel the
+    selector picks, its tiles cover the output, the launch fits shared memory and the
+    workspace it was offered, and the split fields agree with each other."""
+    import random
+    rng = random.Random(7)
+    seen = set()
+    for _ in range(600):
+        M = rng.choice([rng.randint(1, 32), rng.randint(33, 9000)])
+        K = rng.choice([256 * rng.randint(1, 80), 16 * rng.randint(1, 600)])
+        N = rng.choice([8 * rng.randint(1, 20000), rng.randint(1, 40000)])
+        ws = rng.choice([0, 8 << 20, 64 << 20])
+        p = mm.select_plan(M, K, N, ws_bytes=ws)
+        seen.add(p.variant)
+        assert p.split_k >= 1 and p.ws_needed <= ws, (M, K, N, ws)
+        if p.variant == V_ROWWARP:
+            continue
+        assert p.smem_bytes <= SMEM_MAX and (p.stages >= 2 or p.stages == p.k_steps // p.split_k == 1), (M, K, N)
+        assert p.grid_x * p.tile_n >= N and (p.grid_x - 1) * p.tile_n < N, (M, K, N)
+        if p.variant in (V_MX, V_STREAM):
+            assert M <= 32 and K % 256 == 0 and p.k_steps == K // 256
+            assert p.grid_y == p.split_k and p.split_k <= p.k_steps
+            if ws == 0:
+                assert p.split_k == 1
+        if p.variant == V_MX:
+            assert p.tile_m == 24 * -(-M // 4)
+        if p.variant == V_UMMA:
+            assert M > 32 and N % 8 == 0 and K % 256 == 0 and p.k_steps == K // 64
+            tiles = p.grid_x * p.grid_y
+            assert p.grid_y * p.tile_m >= M and (p.grid_y - 1) * p.tile_m < M
+            if p.split_k > 1:
+                assert 0 < p.m_tiles <= tiles and p.m_tiles * p.split_k <= 148
+                assert p.ws_needed == 16384 + p.m_tiles * p.split_k * p.tile_m * p.tile_n * 4
+            else:
+                assert p.m_tiles == 0 and p.ws_needed == 0
+    assert seen == {V_ROWWARP, V_UMMA, V_MX} or seen == {V_ROWWARP, V_UMMA, V_MX, V_STREAM}
