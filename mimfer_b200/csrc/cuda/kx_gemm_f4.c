@@ -237,7 +237,8 @@ unsigned long long mm_f4_launch_count(int reset)
 /* The exchange of a tensor-parallel linear by the copy engines.  A prefill-size output
  * slice is hundreds of megabytes per rank: stored from the kernel's epilogue it holds the
  * SM until NVLink has taken it; pushed by the copy engines it leaves while the next row
- * chunk is multiplied.  One side stream and one event per peer, made on first use. */
+ * chunk is multiplied.  Side streams with an event each, up to TP_LANES per peer, made
+ * on first use. */
 #define TP_LANES 8u                     /* copy streams per peer at most */
 static struct {
     cudaStream_t side[MMB_MAX_PEERS][TP_LANES];
@@ -1301,10 +1302,10 @@ mm_status mm_f4_tp_push(void *const *y_all, uint32_t n_ranks, uint32_t ldy, uint
     if (!TP.ready)
         CK(cudaEventCreateWithFlags(&TP.ready, cudaEventDisableTiming));
     CK(cudaEventRecord(TP.ready, cs));                       /* the slice is complete in the own copy */
-    /* One copy engine moves a strided slice at a fraction of what NVLink carries (three
-     * streams, one per peer of four ranks, reached 370 GB/s together): every peer gets
-     * several streams, about eight over all peers, and a push is cut into as many runs of
-     * rows. */
+    /* One stream's copy reaches 757 GB/s to a single peer, but four ranks that push to
+     * three peers each got 360 GB/s per GPU out of one stream per peer and 425 out of
+     * three: every peer gets several streams, about eight over all peers, and a push is
+     * cut into as many runs of rows. */
     uint32_t lanes = G.tp_lanes ? G.tp_lanes : (TP_LANES + n_ranks - 2u) / (n_ranks - 1u);
     if (lanes > TP_LANES) lanes = TP_LANES;
     if (lanes > rows / 64u) lanes = rows / 64u ? rows / 64u : 1u;

@@ -109,10 +109,10 @@ f4_umma_kernel(const __grid_constant__ TmaDesc tm_x, const __grid_constant__ Tma
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     /* Tensor parallel: the epilogues store every tile to all ranks, and NVLink takes a
      * wave's tiles more slowly than the SMs make them.  CTAs that start together reach
-     * their epilogues together, share the link evenly, leave together and start the next
-     * tiles together: the link idles during every main loop and the SMs during every
-     * epilogue.  The first wave therefore starts spread over the time the link needs for
-     * one wave's tiles; later CTAs inherit the spread, and some CTAs are always storing. */
+     * their first epilogues together and share the link evenly; the first wave therefore
+     * starts spread over the time the link needs for one wave's tiles, and later CTAs
+     * inherit the spread.  Measured on four ranks: gate+up (3.7 waves) 0.86 -> 0.76 ms,
+     * the LM head (32 waves, whose CTAs drift apart by themselves) 3.24 -> 3.20 ms. */
     if (p.stagger_ns && blockIdx.x < p.stagger_ctas) {
         if (tid == 0) {
             const uint64_t t0 = globaltimer_ns();

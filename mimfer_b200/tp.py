@@ -22,8 +22,10 @@ mode="push" is for prefill sizes, where a rank's output slice is hundreds of
 megabytes: the kernel stores into the rank's own copy only, chunk of rows by chunk
 of rows, and the copy engines push every finished chunk to the peers
 (mm_f4_tp_push) while the SMs multiply the next one; a join and the same barrier
-kernel close the op.  Stored from the epilogue, the same bytes hold every SM until
-NVLink has taken them.  The reference has no multi-GPU path; this is new surface.
+kernel close the op.  Measured, the copy engines carry 757 GB/s to one peer but
+425 GB/s per GPU when four ranks push to three peers each, less than the epilogue's
+stores (617 GB/s), so "fused" is the faster form from four ranks on and the bench
+times both.  The reference has no multi-GPU path; this is new surface.
 """
 import ctypes as C
 import os
@@ -45,8 +47,9 @@ def shard_bounds(N, rank, world):
 
 
 def push_chunks(M, rows):
-    """(row0, rows) of the chunks of a pushed linear: `rows` at a time, the tail halved
-    chunk by chunk down to 256 rows (a tile's height) so the last push is a short one."""
+    """(row0, rows) of the chunks of a pushed linear: `rows` at a time; a last chunk of a
+    multiple of 512 rows is halved while more than 512 rows are left, so that the push
+    nothing overlaps is a short one (8192 rows by 1024: ..., 1024, 512, 512)."""
     out, r0 = [], 0
     while M - r0 > rows:
         out.append((r0, rows))
@@ -167,7 +170,7 @@ class TpLinear:
     def _forward_push(self, x, barrier=True):
         """Row chunks of push_rows: the chunk's GEMM into the own copy, then its push to the
         peers; the compute stream never waits for a push before the closing join.  The last
-        chunks are halved down to 256 rows so that little of the exchange is left when the
+        chunk is halved (push_chunks) so that little of the exchange is left when the
         multiplying ends."""
         M = x.shape[0]
         y, hdl, ptrs = self._symm_buffers(M, x)
